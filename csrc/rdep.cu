@@ -1,0 +1,491 @@
+// RDEP: expert parallelism by direct placement into the owner's memory, with no all-to-all.
+//
+// A rank that holds T tokens with top-K routing does, per MoE layer:
+//   count   stable rank of every (token, slot) pair inside its expert        (local)
+//   plan    publish my per-expert counts into every peer's table, wait for theirs, and derive
+//           -- identically on every rank -- the 128-row-aligned segment layout of every owner
+//   place   store each row (bf16) straight into its final position in the owner's activation
+//           buffer over NVLink (16-byte system-scope stores), plus a 16-byte meta record
+//           {source rank, token*K+slot, gate}; the owner zero-fills the padding rows of its own
+//           segments; the last block releases a per-peer "rows have landed" flag
+//   wait    bounded spin until all peers' flags reached this call's epoch
+// The owner then runs grouped GEMMs over its padded segments; the last GEMM's epilogue pushes
+// each output row (times its gate) into the source rank's (token, slot) return buffer, and a
+// reduce kernel on the source sums the K slots in a fixed order.
+//
+// Placement is deterministic (no remote atomics): position = segment start + rows of lower
+// ranks + stable local rank.  Every spin has an iteration bound and reports through a
+// StatusRecord instead of trapping.
+//
+// Replaces nmoe/csrc/rdep.cu:767-861 (dispatch), :1225-1367 (sort/offsets/pad map),
+// :1308-1440 (gathers), :2698-2900 (return + reduce), :3699-3762 (barriers) of the reference.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "common/ptx.cuh"
+
+namespace nmoe {
+
+constexpr int kMaxRanks = 8;
+constexpr int kMaxExperts = 512;
+constexpr int kCountThreads = 1024;
+constexpr uint32_t kFlagSpinBudget = 20u * 1000u * 1000u;   // ~ seconds with nanosleep(64)
+
+struct RdepMeta {          // 16 bytes, written by the source next to each row
+  int32_t src_rank;
+  int32_t tok_slot;        // token * K + slot on the source
+  float gate;
+  int32_t valid;           // 1 for a real row, 0 for padding
+};
+
+// ------------------------------------------------------------------ count
+// Block b owns pairs [b*1024, (b+1)*1024).  Outputs the per-block histogram and each pair's
+// stable rank among the pairs of the same expert inside the block.
+__global__ void __launch_bounds__(kCountThreads)
+k_rdep_count(const int* __restrict__ eid, int n_pairs, int E, int* __restrict__ block_hist,
+             int* __restrict__ rank_in_block, StatusRecord* status) {
+  extern __shared__ int s_warp_hist[];   // [32][E]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < 32 * E; i += blockDim.x) s_warp_hist[i] = 0;
+  __syncthreads();
+  const int i = blockIdx.x * kCountThreads + threadIdx.x;
+  int e = -1;
+  if (i < n_pairs) {
+    e = eid[i];
+    if (e < 0 || e >= E) {
+      report_status(status, kStatusBadIndex, 400, i, e);
+      e = -1;
+    }
+  }
+  const unsigned peers = __match_any_sync(0xffffffffu, e);
+  const int r_in_warp = __popc(peers & ((1u << lane) - 1u));
+  if (e >= 0 && r_in_warp == 0) s_warp_hist[warp * E + e] = __popc(peers);
+  __syncthreads();
+  // exclusive scan over warps, per expert
+  for (int x = threadIdx.x; x < E; x += blockDim.x) {
+    int run = 0;
+    for (int w = 0; w < 32; ++w) {
+      const int c = s_warp_hist[w * E + x];
+      s_warp_hist[w * E + x] = run;
+      run += c;
+    }
+    block_hist[blockIdx.x * E + x] = run;
+  }
+  __syncthreads();
+  if (i < n_pairs) rank_in_block[i] = (e >= 0) ? s_warp_hist[warp * E + e] + r_in_warp : -1;
+}
+
+// ------------------------------------------------------------------ plan
+struct PlanArgs {
+  int rank, world, E, n_local, n_blocks, capacity_rows, epoch;
+  int* block_hist;              // [n_blocks][E] in: counts, out: exclusive prefix over blocks
+  int* peer_counts[kMaxRanks];  // peer r's table [world][E]; we write row `rank`
+  uint32_t* peer_count_flags[kMaxRanks];   // peer r's flags [world]; we write entry `rank`
+  int* my_counts_table;         // == peer_counts[rank]
+  uint32_t* my_count_flags;     // == peer_count_flags[rank]
+  int* base;                    // out [E]: first position of my rows of expert e in the owner's buffer
+  int* offs_pad;                // out [n_local+1]: my (owner) padded segment offsets
+  int* seg_rows;                // out [n_local]: real rows in each of my segments
+  int* tile_expert;             // out [capacity_rows/128]
+  int* n_m_tiles;               // out [1]
+  int* send_counts;             // out [E]: my counts (for stats / loads)
+  StatusRecord* status;
+};
+
+__global__ void __launch_bounds__(512) k_rdep_plan(const PlanArgs a) {
+  __shared__ int s_cnt[kMaxExperts];
+  __shared__ int s_total[kMaxExperts];
+  __shared__ int s_lower[kMaxExperts];
+  __shared__ int s_ok;
+  const int E = a.E;
+  // 1. prefix over blocks -> my counts
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int run = 0;
+    for (int b = 0; b < a.n_blocks; ++b) {
+      const int c = a.block_hist[b * E + e];
+      a.block_hist[b * E + e] = run;
+      run += c;
+    }
+    s_cnt[e] = run;
+    a.send_counts[e] = run;
+  }
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  // 2. publish my counts to every peer, then flag
+  for (int r = 0; r < a.world; ++r)
+    for (int e = threadIdx.x; e < E; e += blockDim.x) a.peer_counts[r][a.rank * E + e] = s_cnt[e];
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < a.world) st_release_sys_u32(a.peer_count_flags[threadIdx.x] + a.rank, static_cast<uint32_t>(a.epoch));
+  // 3. wait for every peer's counts
+  if (threadIdx.x < a.world) {
+    if (!wait_flag_ge_sys(a.my_count_flags + threadIdx.x, static_cast<uint32_t>(a.epoch), kFlagSpinBudget)) {
+      report_status(a.status, kStatusWaitTimeout, 410, threadIdx.x, a.epoch);
+      s_ok = 0;
+    }
+  }
+  __syncthreads();
+  if (!s_ok) {
+    if (threadIdx.x == 0) *a.n_m_tiles = 0;
+    for (int e = threadIdx.x; e < E; e += blockDim.x) a.base[e] = -1;
+    return;
+  }
+  // 4. totals and rows of lower ranks
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int tot = 0, low = 0;
+    for (int r = 0; r < a.world; ++r) {
+      const int c = reinterpret_cast<volatile int*>(a.my_counts_table)[r * E + e];
+      if (r < a.rank) low += c;
+      tot += c;
+    }
+    s_total[e] = tot;
+    s_lower[e] = low;
+  }
+  __syncthreads();
+  // 5. segment starts per owner (serial per owner; E is small)
+  if (threadIdx.x < a.world) {
+    const int o = threadIdx.x;
+    int run = 0;
+    for (int le = 0; le < a.n_local; ++le) {
+      const int e = o * a.n_local + le;
+      const int padded = (s_total[e] + 127) & ~127;
+      if (run + padded > a.capacity_rows) {
+        report_status(a.status, kStatusCapacity, 411, o, run + padded);
+        a.base[e] = -1;          // rows for this expert are dropped by `place`
+      } else {
+        a.base[e] = run + s_lower[e];
+      }
+      if (o == a.rank) {
+        a.offs_pad[le] = run;
+        a.seg_rows[le] = (run + padded > a.capacity_rows) ? 0 : s_total[e];
+        if (run + padded <= a.capacity_rows)
+          for (int t = run / 128; t < (run + padded) / 128; ++t) a.tile_expert[t] = le;
+      }
+      if (run + padded <= a.capacity_rows) run += padded;
+    }
+    if (o == a.rank) {
+      a.offs_pad[a.n_local] = run;
+      *a.n_m_tiles = run / 128;
+    }
+  }
+}
+
+// ------------------------------------------------------------------ place
+struct PlaceArgs {
+  int rank, world, E, n_local, T, K, H, epoch;
+  const __nv_bfloat16* x;        // [T, H]
+  const int* eid;                // [T*K]
+  const float* gates;            // [T*K] or null (backward re-dispatch / dY dispatch)
+  const int* rank_in_block;      // [T*K]
+  const int* block_prefix;       // [n_blocks][E]
+  const int* base;               // [E]
+  __nv_bfloat16* peer_x[kMaxRanks];     // owner activation buffers [capacity, H]
+  RdepMeta* peer_meta[kMaxRanks];       // owner meta [capacity] (null: do not write meta)
+  uint32_t* peer_data_flags[kMaxRanks]; // owner's flags [world]; we release entry `rank`
+  int* pos_out;                  // [T*K] out: owner << 24 | position... stored as two arrays below
+  int* owner_out;                // [T*K] or null
+  const int* offs_pad;           // my segments (for pad zero-fill)
+  const int* seg_rows;
+  int* done_counter;             // grid-completion counter (zeroed by the last block)
+  int pad_blocks;                // trailing blocks that zero-fill my padding rows
+  StatusRecord* status;
+};
+
+__global__ void __launch_bounds__(256) k_rdep_place(const PlaceArgs a) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row_blocks = gridDim.x - a.pad_blocks;
+  const int nvec = a.H >> 3;
+  if (static_cast<int>(blockIdx.x) < row_blocks) {
+    const int n_pairs = a.T * a.K;
+    for (int i = blockIdx.x * 8 + warp; i < n_pairs; i += row_blocks * 8) {
+      const int e = a.eid[i];
+      const int rb = a.rank_in_block[i];
+      int pos = -1, owner = 0;
+      if (e >= 0 && e < a.E && rb >= 0 && a.base[e] >= 0) {
+        owner = e / a.n_local;
+        pos = a.base[e] + a.block_prefix[(i / kCountThreads) * a.E + e] + rb;
+      }
+      if (lane == 0) {
+        a.pos_out[i] = pos;
+        if (a.owner_out) a.owner_out[i] = owner;
+      }
+      if (pos < 0) continue;
+      const int tok = i / a.K;
+      const int4* src = reinterpret_cast<const int4*>(a.x + static_cast<size_t>(tok) * a.H);
+      int4* dst = reinterpret_cast<int4*>(a.peer_x[owner] + static_cast<size_t>(pos) * a.H);
+      for (int c = lane; c < nvec; c += 32) st_relaxed_sys_v4(dst + c, __ldg(src + c));
+      if (lane == 0 && a.peer_meta[owner] != nullptr) {
+        int4 m;
+        m.x = a.rank;
+        m.y = i;
+        m.z = __float_as_int(a.gates ? a.gates[i] : 1.f);
+        m.w = 1;
+        st_relaxed_sys_v4(a.peer_meta[owner] + pos, m);
+      }
+    }
+  } else {
+    // zero-fill the padding rows of my own segments (local stores)
+    const int pb = blockIdx.x - row_blocks;
+    for (int le = 0; le < a.n_local; ++le) {
+      const int r0 = a.offs_pad[le] + a.seg_rows[le];
+      const int r1 = a.offs_pad[le + 1];
+      for (int r = r0 + pb * 8 + warp; r < r1; r += a.pad_blocks * 8) {
+        int4* dst = reinterpret_cast<int4*>(a.peer_x[a.rank] + static_cast<size_t>(r) * a.H);
+        for (int c = lane; c < nvec; c += 32) dst[c] = make_int4(0, 0, 0, 0);
+        if (lane == 0 && a.peer_meta[a.rank] != nullptr) {
+          int4 m = make_int4(a.rank, 0, 0, 0);
+          *reinterpret_cast<int4*>(a.peer_meta[a.rank] + r) = m;
+        }
+      }
+    }
+  }
+  // grid completion -> release flags to every owner
+  __threadfence_system();
+  __syncthreads();
+  __shared__ int s_last;
+  if (threadIdx.x == 0) s_last = (atomicAdd(a.done_counter, 1) == static_cast<int>(gridDim.x) - 1);
+  __syncthreads();
+  if (s_last) {
+    __threadfence_system();
+    if (threadIdx.x < a.world)
+      st_release_sys_u32(a.peer_data_flags[threadIdx.x] + a.rank, static_cast<uint32_t>(a.epoch));
+    if (threadIdx.x == 0) *a.done_counter = 0;
+  }
+}
+
+// ------------------------------------------------------------------ flags
+// Release `epoch` into entry `rank` of every peer's flag array (used after a kernel whose
+// stores to peers must be visible, e.g. the return push of the last GEMM).
+__global__ void k_rdep_signal(uint32_t* const* peer_flags, int rank, int world, uint32_t epoch) {
+  __threadfence_system();
+  if (threadIdx.x < world) st_release_sys_u32(peer_flags[threadIdx.x] + rank, epoch);
+}
+struct PeerFlagPtrs { uint32_t* p[kMaxRanks]; };
+__global__ void k_rdep_signal_v(const PeerFlagPtrs f, int rank, int world, uint32_t epoch) {
+  __threadfence_system();
+  if (threadIdx.x < world) st_release_sys_u32(f.p[threadIdx.x] + rank, epoch);
+}
+
+// Bounded wait until my flags [world] all reached `epoch`.  budget_iters bounds the spin.
+__global__ void k_rdep_wait(const uint32_t* my_flags, int world, uint32_t epoch, uint32_t budget_iters,
+                            StatusRecord* status, int where) {
+  if (threadIdx.x < world) {
+    if (!wait_flag_ge_sys(my_flags + threadIdx.x, epoch, budget_iters))
+      report_status(status, kStatusWaitTimeout, where, threadIdx.x, static_cast<int>(epoch));
+  }
+  __threadfence_system();
+}
+
+// ------------------------------------------------------------------ return / reduce
+// Owner side, unfused variant: push rows of y[capacity, H] (scaled by the row's gate when
+// use_gate) into the source's return buffer ret[tok_slot, H].
+struct PushArgs {
+  int H, n_rows_cap, use_gate;
+  const __nv_bfloat16* y;
+  const RdepMeta* meta;
+  const int* n_m_tiles;
+  __nv_bfloat16* peer_ret[kMaxRanks];
+  float* peer_retg[kMaxRanks];      // optional per-row scalar return (gate gradients)
+  const float* rowval;              // optional per-row scalar to return
+};
+__global__ void __launch_bounds__(256) k_rdep_push(const PushArgs a) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int rows = min(*a.n_m_tiles * 128, a.n_rows_cap);
+  const int nvec = a.H >> 3;
+  for (int r = blockIdx.x * 8 + warp; r < rows; r += gridDim.x * 8) {
+    const int4 mv = __ldg(reinterpret_cast<const int4*>(a.meta + r));
+    if (mv.w == 0) continue;
+    const int src = mv.x, ts = mv.y;
+    const float g = a.use_gate ? __int_as_float(mv.z) : 1.f;
+    if (a.y != nullptr) {
+      const int4* s = reinterpret_cast<const int4*>(a.y + static_cast<size_t>(r) * a.H);
+      int4* d = reinterpret_cast<int4*>(a.peer_ret[src] + static_cast<size_t>(ts) * a.H);
+      for (int c = lane; c < nvec; c += 32) {
+        int4 v = ld_nc_v4(s + c);
+        if (a.use_gate) {
+          float2 f0 = unpack_bf16x2(v.x), f1 = unpack_bf16x2(v.y), f2 = unpack_bf16x2(v.z), f3 = unpack_bf16x2(v.w);
+          v.x = pack_bf16x2(f0.x * g, f0.y * g); v.y = pack_bf16x2(f1.x * g, f1.y * g);
+          v.z = pack_bf16x2(f2.x * g, f2.y * g); v.w = pack_bf16x2(f3.x * g, f3.y * g);
+        }
+        st_relaxed_sys_v4(d + c, v);
+      }
+    }
+    if (lane == 0 && a.rowval != nullptr) a.peer_retg[src][ts] = a.rowval[r];
+  }
+  __threadfence_system();
+}
+
+// Source side: out[t] = sum_k ret[t*K + k] for slots with pos >= 0 (fp32, fixed order).
+__global__ void __launch_bounds__(256)
+k_rdep_reduce(const __nv_bfloat16* __restrict__ ret, const int* __restrict__ pos, __nv_bfloat16* __restrict__ out,
+              int T, int K, int H) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nvec = H >> 3;
+  for (int t = blockIdx.x * 8 + warp; t < T; t += gridDim.x * 8) {
+    for (int c = lane; c < nvec; c += 32) {
+      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      for (int k = 0; k < K; ++k) {
+        if (pos[t * K + k] < 0) continue;
+        int4 v = ld_relaxed_sys_v4(reinterpret_cast<const int4*>(ret + (static_cast<size_t>(t) * K + k) * H) + c);
+        float2 f0 = unpack_bf16x2(v.x), f1 = unpack_bf16x2(v.y), f2 = unpack_bf16x2(v.z), f3 = unpack_bf16x2(v.w);
+        acc[0] += f0.x; acc[1] += f0.y; acc[2] += f1.x; acc[3] += f1.y;
+        acc[4] += f2.x; acc[5] += f2.y; acc[6] += f3.x; acc[7] += f3.y;
+      }
+      int4 o;
+      o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
+      o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
+      reinterpret_cast<int4*>(out + static_cast<size_t>(t) * H)[c] = o;
+    }
+  }
+}
+
+// Owner side helper: gather gate[pos] from meta into a dense fp32 vector (row scale for SwiGLU bwd).
+__global__ void k_rdep_row_gates(const RdepMeta* __restrict__ meta, const int* __restrict__ n_m_tiles, int cap,
+                                 float* __restrict__ out) {
+  const int rows = min(*n_m_tiles * 128, cap);
+  for (int r = blockIdx.x * blockDim.x + threadIdx.x; r < rows; r += gridDim.x * blockDim.x)
+    out[r] = meta[r].valid ? meta[r].gate : 0.f;
+}
+
+}  // namespace nmoe
+
+using namespace nmoe;
+
+#define CHECK_LAUNCH() do { cudaError_t e_ = cudaGetLastError(); if (e_ != cudaSuccess) return static_cast<int>(e_); } while (0)
+
+extern "C" {
+
+int nmoe_rdep_count_blocks(int n_pairs) { return (n_pairs + kCountThreads - 1) / kCountThreads; }
+
+int nmoe_rdep_count(const int* eid, int n_pairs, int E, int* block_hist, int* rank_in_block, void* status,
+                    cudaStream_t st) {
+  if (E > kMaxExperts) return -1;
+  const int nb = nmoe_rdep_count_blocks(n_pairs);
+  if (nb == 0) return 0;
+  const size_t smem = 32 * static_cast<size_t>(E) * sizeof(int);
+  cudaFuncSetAttribute(k_rdep_count, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+  k_rdep_count<<<nb, kCountThreads, smem, st>>>(eid, n_pairs, E, block_hist, rank_in_block,
+                                               static_cast<StatusRecord*>(status));
+  CHECK_LAUNCH();
+  return 0;
+}
+
+// peer_counts / peer_count_flags: arrays of `world` device pointers (host memory).
+int nmoe_rdep_plan(int rank, int world, int E, int n_local, int n_blocks, int capacity_rows, int epoch,
+                   int* block_hist, void* const* peer_counts, void* const* peer_count_flags, int* base,
+                   int* offs_pad, int* seg_rows, int* tile_expert, int* n_m_tiles, int* send_counts, void* status,
+                   cudaStream_t st) {
+  if (world > kMaxRanks || E > kMaxExperts || E != n_local * world) return -1;
+  PlanArgs a;
+  a.rank = rank; a.world = world; a.E = E; a.n_local = n_local; a.n_blocks = n_blocks;
+  a.capacity_rows = capacity_rows; a.epoch = epoch; a.block_hist = block_hist;
+  for (int r = 0; r < world; ++r) {
+    a.peer_counts[r] = static_cast<int*>(peer_counts[r]);
+    a.peer_count_flags[r] = static_cast<uint32_t*>(peer_count_flags[r]);
+  }
+  a.my_counts_table = a.peer_counts[rank];
+  a.my_count_flags = a.peer_count_flags[rank];
+  a.base = base; a.offs_pad = offs_pad; a.seg_rows = seg_rows; a.tile_expert = tile_expert;
+  a.n_m_tiles = n_m_tiles; a.send_counts = send_counts; a.status = static_cast<StatusRecord*>(status);
+  k_rdep_plan<<<1, 512, 0, st>>>(a);
+  CHECK_LAUNCH();
+  return 0;
+}
+
+int nmoe_rdep_place(int rank, int world, int E, int n_local, int T, int K, int H, int epoch, const void* x,
+                    const int* eid, const float* gates, const int* rank_in_block, const int* block_prefix,
+                    const int* base, void* const* peer_x, void* const* peer_meta, void* const* peer_data_flags,
+                    int* pos_out, int* owner_out, const int* offs_pad, const int* seg_rows, int* done_counter,
+                    void* status, cudaStream_t st) {
+  if (world > kMaxRanks || (H % 8) != 0) return -1;
+  PlaceArgs a;
+  a.rank = rank; a.world = world; a.E = E; a.n_local = n_local; a.T = T; a.K = K; a.H = H; a.epoch = epoch;
+  a.x = static_cast<const __nv_bfloat16*>(x); a.eid = eid; a.gates = gates; a.rank_in_block = rank_in_block;
+  a.block_prefix = block_prefix; a.base = base;
+  for (int r = 0; r < world; ++r) {
+    a.peer_x[r] = static_cast<__nv_bfloat16*>(peer_x[r]);
+    a.peer_meta[r] = peer_meta ? static_cast<RdepMeta*>(peer_meta[r]) : nullptr;
+    a.peer_data_flags[r] = static_cast<uint32_t*>(peer_data_flags[r]);
+  }
+  a.pos_out = pos_out; a.owner_out = owner_out; a.offs_pad = offs_pad; a.seg_rows = seg_rows;
+  a.done_counter = done_counter; a.pad_blocks = 16; a.status = static_cast<StatusRecord*>(status);
+  const int n_pairs = T * K;
+  int row_blocks = (n_pairs + 7) / 8;
+  if (row_blocks > 148 * 8) row_blocks = 148 * 8;
+  if (row_blocks < 1) row_blocks = 1;
+  k_rdep_place<<<row_blocks + a.pad_blocks, 256, 0, st>>>(a);
+  CHECK_LAUNCH();
+  return 0;
+}
+
+int nmoe_rdep_signal(void* const* peer_flags, int rank, int world, unsigned epoch, cudaStream_t st) {
+  if (world > kMaxRanks) return -1;
+  PeerFlagPtrs f;
+  for (int r = 0; r < world; ++r) f.p[r] = static_cast<uint32_t*>(peer_flags[r]);
+  k_rdep_signal_v<<<1, 32, 0, st>>>(f, rank, world, epoch);
+  CHECK_LAUNCH();
+  return 0;
+}
+
+// budget_iters == 0 selects the default (seconds).  Tests pass a small budget to exercise the timeout path.
+int nmoe_rdep_wait(const void* my_flags, int world, unsigned epoch, unsigned budget_iters, void* status, int where,
+                   cudaStream_t st) {
+  if (world > kMaxRanks) return -1;
+  k_rdep_wait<<<1, 32, 0, st>>>(static_cast<const uint32_t*>(my_flags), world, epoch,
+                                budget_iters ? budget_iters : kFlagSpinBudget, static_cast<StatusRecord*>(status), where);
+  CHECK_LAUNCH();
+  return 0;
+}
+
+int nmoe_rdep_push(const void* y, const void* meta, const int* n_m_tiles, int cap_rows, int H, int use_gate,
+                   void* const* peer_ret, void* const* peer_retg, const float* rowval, int world, cudaStream_t st) {
+  if (world > kMaxRanks || (H % 8) != 0) return -1;
+  PushArgs a;
+  a.H = H; a.n_rows_cap = cap_rows; a.use_gate = use_gate;
+  a.y = static_cast<const __nv_bfloat16*>(y); a.meta = static_cast<const RdepMeta*>(meta); a.n_m_tiles = n_m_tiles;
+  for (int r = 0; r < world; ++r) {
+    a.peer_ret[r] = peer_ret ? static_cast<__nv_bfloat16*>(peer_ret[r]) : nullptr;
+    a.peer_retg[r] = peer_retg ? static_cast<float*>(peer_retg[r]) : nullptr;
+  }
+  a.rowval = rowval;
+  k_rdep_push<<<148 * 4, 256, 0, st>>>(a);
+  CHECK_LAUNCH();
+  return 0;
+}
+
+int nmoe_rdep_reduce(const void* ret, const int* pos, void* out, int T, int K, int H, cudaStream_t st) {
+  if (T == 0) return 0;
+  if ((H % 8) != 0) return -1;
+  int blocks = (T + 7) / 8;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  k_rdep_reduce<<<blocks, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(ret), pos, static_cast<__nv_bfloat16*>(out),
+                                       T, K, H);
+  CHECK_LAUNCH();
+  return 0;
+}
+
+int nmoe_rdep_row_gates(const void* meta, const int* n_m_tiles, int cap, float* out, cudaStream_t st) {
+  k_rdep_row_gates<<<148, 256, 0, st>>>(static_cast<const RdepMeta*>(meta), n_m_tiles, cap, out);
+  CHECK_LAUNCH();
+  return 0;
+}
+
+// ---- peer memory (CUDA IPC).  Buffers come from cudaMalloc so that their handles can be exported.
+int nmoe_peer_alloc(size_t bytes, void** out) {
+  cudaError_t e = cudaMalloc(out, bytes);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  e = cudaMemset(*out, 0, bytes);
+  return static_cast<int>(e);
+}
+int nmoe_peer_free(void* p) { return static_cast<int>(cudaFree(p)); }
+int nmoe_peer_get_handle(void* p, void* handle64) {
+  return static_cast<int>(cudaIpcGetMemHandle(static_cast<cudaIpcMemHandle_t*>(handle64), p));
+}
+int nmoe_peer_open(const void* handle64, void** out) {
+  cudaIpcMemHandle_t h = *static_cast<const cudaIpcMemHandle_t*>(handle64);
+  return static_cast<int>(cudaIpcOpenMemHandle(out, h, cudaIpcMemLazyEnablePeerAccess));
+}
+int nmoe_peer_close(void* p) { return static_cast<int>(cudaIpcCloseMemHandle(p)); }
+
+}  // extern "C"

@@ -1,0 +1,5 @@
+"""Hot ops.  Each function runs a hand-written sm_100a kernel for CUDA tensors and the
+plain-PyTorch oracle (``nmoe_b200.ref``) for CPU tensors."""
+from .elementwise import embedding, rmsnorm, rope, swiglu, swiglu_bwd_fused
+from .tc_gemm import check_status, gemm, grouped_gemm, grouped_wgrad, linear
+from .optim import adamw_flat_, sumsq

@@ -1,0 +1,171 @@
+"""bf16 GEMMs on tcgen05 (``csrc/gemm.cu``): dense, grouped over ragged row segments, and
+grouped over ragged contraction ranges (expert wgrad), plus the ``linear`` autograd op.
+
+CPU tensors take the plain-PyTorch statement of the same contraction.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import _lib as L
+
+_STATUS: dict[torch.device, torch.Tensor] = {}
+
+
+def status_buffer(device: torch.device) -> torch.Tensor:
+  """Per-device int32[4] status record that kernels write when a bounded wait runs out."""
+  buf = _STATUS.get(device)
+  if buf is None:
+    buf = torch.zeros(4, dtype=torch.int32, device=device)
+    _STATUS[device] = buf
+  return buf
+
+
+def check_status(device: Optional[torch.device] = None) -> None:
+  """Synchronising check of the status record(s); raises if any kernel reported a failure."""
+  for dev, buf in _STATUS.items():
+    if device is not None and dev != device:
+      continue
+    rec = buf.tolist()
+    if rec[0] != 0:
+      buf.zero_()
+      raise L.NativeLibraryError(f"kernel reported status code={rec[0]} where={rec[1]} a={rec[2]} b={rec[3]} on {dev}")
+
+
+def _rows(t: torch.Tensor) -> int:
+  return t.numel() // t.size(-1)
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
+         out: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.bfloat16, accumulate: bool = False,
+         bn: int = 0) -> torch.Tensor:
+  """C[M,N] = op(A) @ op(B).
+
+  ``a``: [M,K] (a_mn False) or [K,M] (a_mn True).  ``b``: [N,K] (b_mn False, the nn.Linear
+  weight layout) or [K,N] (b_mn True).  Both 2-D with a dense last dim.
+  """
+  if not a.is_cuda:
+    A = a.t() if a_mn else a
+    Bm = b if b_mn else b.t()
+    c = (A.float() @ Bm.float())
+    if out is not None:
+      out.copy_(out.float() + c if accumulate else c)
+      return out
+    return c.to(out_dtype)
+  assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
+  assert a.dim() == 2 and b.dim() == 2 and a.stride(1) == 1 and b.stride(1) == 1
+  M, K = (a.size(1), a.size(0)) if a_mn else (a.size(0), a.size(1))
+  N = b.size(1) if b_mn else b.size(0)
+  assert (b.size(0) if b_mn else b.size(1)) == K, f"contraction mismatch {a.shape} {b.shape}"
+  if out is None:
+    assert not accumulate
+    out = torch.empty(M, N, dtype=out_dtype, device=a.device)
+  assert out.stride(1) == 1 and out.shape == (M, N)
+  st = status_buffer(a.device)
+  L.check(L.lib().nmoe_gemm_bf16(
+    L.ptr(a), L.ptr(b), L.ptr(out), M, N, K, L.c_ll(a.stride(0)), L.c_ll(b.stride(0)), L.c_ll(out.stride(0)),
+    int(a_mn), int(b_mn), 0, 1, None, None, None, L.c_ll(a.size(0)), L.c_ll(b.size(0)),
+    int(out.dtype == torch.float32), int(accumulate), bn, L.ptr(st), L.stream()), "gemm_bf16")
+  return out
+
+
+def grouped_gemm(a: torch.Tensor, b: torch.Tensor, tile_expert: torch.Tensor, n_m_tiles: torch.Tensor, *,
+                 b_mn: bool = False, out: Optional[torch.Tensor] = None, offs: Optional[torch.Tensor] = None,
+                 bn: int = 0) -> torch.Tensor:
+  """Rows of ``a`` [Mcap,K] are 128-aligned per-expert segments; row tile i belongs to expert
+  ``tile_expert[i]`` and only the first ``n_m_tiles[0]`` tiles are valid.  ``b``: [E,N,K]
+  (b_mn False) or [E,K,N] (b_mn True).  Returns [Mcap,N]; rows past the valid tiles are
+  left untouched.  ``offs`` ([E+1] row offsets) is only used by the CPU statement.
+  """
+  E = b.size(0)
+  N = b.size(2) if b_mn else b.size(1)
+  K = a.size(1)
+  if not a.is_cuda:
+    c = torch.zeros(a.size(0), N, dtype=a.dtype) if out is None else out
+    nt = int(n_m_tiles.item())
+    for i in range(nt):
+      e = int(tile_expert[i])
+      w = b[e] if b_mn else b[e].t()
+      c[i * 128:(i + 1) * 128] = (a[i * 128:(i + 1) * 128].float() @ w.float()).to(c.dtype)
+    return c
+  assert a.is_contiguous() and b.is_contiguous() and a.size(0) % 128 == 0
+  if out is None:
+    out = torch.empty(a.size(0), N, dtype=torch.bfloat16, device=a.device)
+  st = status_buffer(a.device)
+  b2_rows = E * (K if b_mn else N)
+  L.check(L.lib().nmoe_gemm_bf16(
+    L.ptr(a), L.ptr(b), L.ptr(out), a.size(0), N, K, L.c_ll(K), L.c_ll(N if b_mn else K), L.c_ll(out.stride(0)),
+    0, int(b_mn), 1, E, L.ptr(tile_expert), L.ptr(n_m_tiles), None, L.c_ll(a.size(0)), L.c_ll(b2_rows),
+    0, 0, bn, L.ptr(st), L.stream()), "grouped_gemm_bf16")
+  return out
+
+
+def grouped_wgrad(a: torch.Tensor, b: torch.Tensor, offs: torch.Tensor, E: int, *,
+                  out: Optional[torch.Tensor] = None, accumulate: bool = False, bn: int = 0) -> torch.Tensor:
+  """out[e] = a[rows_e]^T @ b[rows_e]  ([E, Ma, Nb]) with rows_e = offs[e]:offs[e+1] (128-aligned).
+
+  Rows of padding inside a segment must be zero in at least one operand.  Experts without
+  rows give zeros.
+  """
+  Ma, Nb = a.size(1), b.size(1)
+  if not a.is_cuda:
+    c = torch.zeros(E, Ma, Nb, dtype=torch.float32)
+    o = offs.tolist()
+    for e in range(E):
+      c[e] = a[o[e]:o[e + 1]].float().t() @ b[o[e]:o[e + 1]].float()
+    if out is not None:
+      out.copy_(out.float() + c if accumulate else c)
+      return out
+    return c.to(a.dtype)
+  assert a.is_contiguous() and b.is_contiguous() and a.size(0) == b.size(0)
+  if out is None:
+    assert not accumulate
+    out = torch.empty(E, Ma, Nb, dtype=torch.bfloat16, device=a.device)
+  assert out.is_contiguous()
+  st = status_buffer(a.device)
+  L.check(L.lib().nmoe_gemm_bf16(
+    L.ptr(a), L.ptr(b), L.ptr(out), Ma, Nb, 0, L.c_ll(Ma), L.c_ll(Nb), L.c_ll(Nb),
+    1, 1, 2, E, None, None, L.ptr(offs), L.c_ll(a.size(0)), L.c_ll(b.size(0)),
+    int(out.dtype == torch.float32), int(accumulate), bn, L.ptr(st), L.stream()), "grouped_wgrad_bf16")
+  return out
+
+
+class _Linear(torch.autograd.Function):
+  """y = x @ w^T (+ bias) with w in the [out, in] layout; dgrad and wgrad use the MN-major
+  operand forms of the same kernel, so no transpose is ever materialised."""
+
+  @staticmethod
+  def forward(ctx, x, w, bias):
+    x2 = x.reshape(-1, x.size(-1))
+    if not x2.is_contiguous():
+      x2 = x2.contiguous()
+    y = gemm(x2, w)
+    if bias is not None:
+      y += bias
+    ctx.save_for_backward(x2, w)
+    ctx.has_bias = bias is not None
+    ctx.xshape = x.shape
+    return y.view(*x.shape[:-1], w.size(0))
+
+  @staticmethod
+  def backward(ctx, dy):
+    x2, w = ctx.saved_tensors
+    dy2 = dy.reshape(-1, dy.size(-1))
+    if not dy2.is_contiguous():
+      dy2 = dy2.contiguous()
+    dx = dw = db = None
+    if ctx.needs_input_grad[0]:
+      dx = gemm(dy2, w, b_mn=True).view(ctx.xshape)            # [M,out] @ [out,in]
+    if ctx.needs_input_grad[1]:
+      dw = gemm(dy2, x2, a_mn=True, b_mn=True)                 # dy^T [out,M] @ x [M,in]
+    if ctx.has_bias and ctx.needs_input_grad[2]:
+      db = dy2.float().sum(0).to(dy.dtype)
+    return dx, dw, db
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+  if x.is_cuda and x.dtype == torch.bfloat16:
+    return _Linear.apply(x, w, bias)
+  return torch.nn.functional.linear(x, w, bias)

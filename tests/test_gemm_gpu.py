@@ -1,0 +1,102 @@
+"""tcgen05 GEMM family vs an fp32 PyTorch reference of the same contraction."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _close(c, ref, tol=2e-2):
+  err = (c.float() - ref).abs().max().item()
+  scale = ref.abs().max().item() + 1e-6
+  assert err / scale < tol, f"rel err {err / scale:.4g} (abs {err:.4g}, scale {scale:.4g})"
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
+@pytest.mark.parametrize("M,N,K,bn", [(128, 64, 64, 64), (256, 128, 128, 128), (384, 512, 320, 256),
+                                      (1000, 264, 200, 0), (4096, 2048, 2048, 0)])
+def test_dense_gemm(M, N, K, bn, a_mn, b_mn):
+  from nmoe_b200.ops import tc_gemm as G
+  torch.manual_seed(0)
+  A = torch.randn(M, K, device="cuda")
+  B = torch.randn(N, K, device="cuda")
+  a = (A.t().contiguous() if a_mn else A).bfloat16()
+  b = (B.t().contiguous() if b_mn else B).bfloat16()
+  ref = (a.float().t() if a_mn else a.float()) @ (b.float() if b_mn else b.float().t())
+  c = G.gemm(a, b, a_mn=a_mn, b_mn=b_mn, bn=bn)
+  torch.cuda.synchronize()
+  G.check_status()
+  _close(c, ref)
+
+
+def test_dense_gemm_fp32_accumulate():
+  from nmoe_b200.ops import tc_gemm as G
+  torch.manual_seed(1)
+  a = torch.randn(512, 256, device="cuda").bfloat16()
+  b = torch.randn(384, 256, device="cuda").bfloat16()
+  out = torch.ones(512, 384, device="cuda")
+  G.gemm(a, b, out=out, accumulate=True)
+  G.gemm(a, b, out=out, accumulate=True)
+  torch.cuda.synchronize()
+  G.check_status()
+  _close(out, 1 + 2 * (a.float() @ b.float().t()))
+
+
+@pytest.mark.parametrize("b_mn", [False, True])
+def test_grouped_gemm_rows(b_mn):
+  from nmoe_b200.ops import tc_gemm as G
+  torch.manual_seed(2)
+  E, N, K = 5, 384, 256
+  counts = [3, 0, 2, 1, 0]                       # 128-row tiles per expert (expert 1 and 4 empty)
+  te = [e for e, c in enumerate(counts) for _ in range(c)]
+  cap_tiles = 8
+  a = torch.randn(cap_tiles * 128, K, device="cuda").bfloat16()
+  w = torch.randn(E, N, K, device="cuda").bfloat16()
+  wb = w.transpose(1, 2).contiguous() if b_mn else w
+  tile_expert = torch.tensor(te + [-1] * (cap_tiles - len(te)), dtype=torch.int32, device="cuda")
+  n_tiles = torch.tensor([len(te)], dtype=torch.int32, device="cuda")
+  out = torch.full((cap_tiles * 128, N), 7.0, device="cuda", dtype=torch.bfloat16)
+  G.grouped_gemm(a, wb, tile_expert, n_tiles, b_mn=b_mn, out=out)
+  torch.cuda.synchronize()
+  G.check_status()
+  for i, e in enumerate(te):
+    _close(out[i * 128:(i + 1) * 128], a[i * 128:(i + 1) * 128].float() @ w[e].float().t())
+  assert (out[len(te) * 128:] == 7.0).all(), "rows past the valid tiles must not be written"
+
+
+def test_grouped_wgrad():
+  from nmoe_b200.ops import tc_gemm as G
+  torch.manual_seed(3)
+  E, Ma, Nb = 4, 320, 256
+  rows = [256, 0, 128, 384]
+  offs = torch.tensor([0] + list(torch.tensor(rows).cumsum(0)), dtype=torch.int32, device="cuda")
+  R = sum(rows)
+  a = torch.randn(R, Ma, device="cuda").bfloat16()
+  b = torch.randn(R, Nb, device="cuda").bfloat16()
+  out = G.grouped_wgrad(a, b, offs, E)
+  torch.cuda.synchronize()
+  G.check_status()
+  o = offs.tolist()
+  for e in range(E):
+    ref = a[o[e]:o[e + 1]].float().t() @ b[o[e]:o[e + 1]].float()
+    if rows[e] == 0:
+      assert (out[e] == 0).all()
+    else:
+      _close(out[e], ref)
+
+
+def test_linear_autograd():
+  from nmoe_b200.ops import tc_gemm as G
+  torch.manual_seed(4)
+  x = torch.randn(4, 96, 256, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+  w = (torch.randn(512, 256, device="cuda") * 0.05).bfloat16().requires_grad_()
+  y = G.linear(x, w)
+  g = torch.randn_like(y)
+  y.backward(g)
+  xf, wf = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+  yf = torch.nn.functional.linear(xf, wf)
+  yf.backward(g.float())
+  torch.cuda.synchronize()
+  G.check_status()
+  _close(y, yf.detach())
+  _close(x.grad, xf.grad)
+  _close(w.grad, wf.grad)
