@@ -181,7 +181,8 @@ __global__ void k_rope_inplace(__nv_bfloat16* __restrict__ x, const float* __res
 // ------------------------------------------------------------------ SwiGLU
 // h13 is [M, 2F] with gate at even columns and up at odd columns; a[M,F] = silu(gate) * up.
 __global__ void k_swiglu_fwd(const __nv_bfloat16* __restrict__ h13, __nv_bfloat16* __restrict__ a, long long M,
-                             int F) {
+                             int F, const int* __restrict__ n_tiles_dev) {
+  if (n_tiles_dev != nullptr) M = min(M, static_cast<long long>(*n_tiles_dev) * 128);
   const long long nvec = M * (F >> 2);      // 4 outputs (8 inputs = 16 bytes) per thread
   const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= nvec) return;
@@ -205,7 +206,8 @@ __global__ void k_swiglu_fwd(const __nv_bfloat16* __restrict__ h13, __nv_bfloat1
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 k_swiglu_bwd(const __nv_bfloat16* __restrict__ h13, const __nv_bfloat16* __restrict__ da,
              __nv_bfloat16* __restrict__ dh13, const float* __restrict__ row_scale, float* __restrict__ rowdot,
-             __nv_bfloat16* __restrict__ a_out, long long M, int F) {
+             __nv_bfloat16* __restrict__ a_out, long long M, int F, const int* __restrict__ n_tiles_dev) {
+  if (n_tiles_dev != nullptr) M = min(M, static_cast<long long>(*n_tiles_dev) * 128);
   const long long row = static_cast<long long>(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5);
   if (row >= M) return;
   const int lane = threadIdx.x & 31;
@@ -408,23 +410,24 @@ int nmoe_rope_inplace(void* x, const float* cos_t, const float* sin_t, long long
   return 0;
 }
 
-int nmoe_swiglu_fwd(const void* h13, void* a, long long M, int F, cudaStream_t st) {
+// n_tiles_dev (optional, device): only the first *n_tiles_dev * 128 rows are processed.
+int nmoe_swiglu_fwd(const void* h13, void* a, long long M, int F, const int* n_tiles_dev, cudaStream_t st) {
   if (M == 0) return 0;
   if (F % 4 != 0) return -1;
   const long long nvec = M * (F / 4);
   k_swiglu_fwd<<<static_cast<unsigned>((nvec + 255) / 256), 256, 0, st>>>(
-      static_cast<const __nv_bfloat16*>(h13), static_cast<__nv_bfloat16*>(a), M, F);
+      static_cast<const __nv_bfloat16*>(h13), static_cast<__nv_bfloat16*>(a), M, F, n_tiles_dev);
   CHECK_LAUNCH();
   return 0;
 }
 
 int nmoe_swiglu_bwd(const void* h13, const void* da, void* dh13, const float* row_scale, float* rowdot, void* a_out,
-                    long long M, int F, cudaStream_t st) {
+                    long long M, int F, const int* n_tiles_dev, cudaStream_t st) {
   if (M == 0) return 0;
   if (F % 4 != 0) return -1;
   k_swiglu_bwd<<<static_cast<unsigned>((M + kWarpsPerBlock - 1) / kWarpsPerBlock), kWarpsPerBlock * 32, 0, st>>>(
       static_cast<const __nv_bfloat16*>(h13), static_cast<const __nv_bfloat16*>(da),
-      static_cast<__nv_bfloat16*>(dh13), row_scale, rowdot, static_cast<__nv_bfloat16*>(a_out), M, F);
+      static_cast<__nv_bfloat16*>(dh13), row_scale, rowdot, static_cast<__nv_bfloat16*>(a_out), M, F, n_tiles_dev);
   CHECK_LAUNCH();
   return 0;
 }

@@ -3,3 +3,6 @@ plain-PyTorch oracle (``nmoe_b200.ref``) for CPU tensors."""
 from .elementwise import embedding, rmsnorm, rope, swiglu, swiglu_bwd_fused
 from .tc_gemm import check_status, gemm, grouped_gemm, grouped_wgrad, linear
 from .optim import adamw_flat_, sumsq
+from .router import router_bias_update_, router_topk
+from .attention import attention
+from .ce import lm_head_loss

@@ -96,7 +96,7 @@ class _SwiGLU(torch.autograd.Function):
     F2 = h13.size(-1)
     h = h13.contiguous().view(-1, F2)
     a = torch.empty(h.size(0), F2 // 2, dtype=h.dtype, device=h.device)
-    L.check(L.lib().nmoe_swiglu_fwd(L.ptr(h), L.ptr(a), L.c_ll(h.size(0)), F2 // 2, L.stream()), "swiglu_fwd")
+    L.check(L.lib().nmoe_swiglu_fwd(L.ptr(h), L.ptr(a), L.c_ll(h.size(0)), F2 // 2, None, L.stream()), "swiglu_fwd")
     ctx.save_for_backward(h)
     ctx.shape = h13.shape
     return a.view(*h13.shape[:-1], F2 // 2)
@@ -107,7 +107,7 @@ class _SwiGLU(torch.autograd.Function):
     M, F2 = h.shape
     d = da.contiguous().view(M, F2 // 2)
     dh = torch.empty_like(h)
-    L.check(L.lib().nmoe_swiglu_bwd(L.ptr(h), L.ptr(d), L.ptr(dh), None, None, None, L.c_ll(M), F2 // 2, L.stream()),
+    L.check(L.lib().nmoe_swiglu_bwd(L.ptr(h), L.ptr(d), L.ptr(dh), None, None, None, L.c_ll(M), F2 // 2, None, L.stream()),
             "swiglu_bwd")
     return dh.view(ctx.shape)
 
@@ -119,8 +119,18 @@ def swiglu(h13: torch.Tensor) -> torch.Tensor:
   return R.swiglu(h13[..., 0::2], h13[..., 1::2])
 
 
+def swiglu_rows(h13: torch.Tensor, n_tiles: torch.Tensor | None = None) -> torch.Tensor:
+  """No-autograd SwiGLU over [M,2F]; with ``n_tiles`` (device int32[1]) only rows < n_tiles*128 are computed."""
+  M, F2 = h13.shape
+  if h13.is_cuda:
+    a = torch.empty(M, F2 // 2, dtype=h13.dtype, device=h13.device)
+    L.check(L.lib().nmoe_swiglu_fwd(L.ptr(h13), L.ptr(a), L.c_ll(M), F2 // 2, L.ptr(n_tiles), L.stream()), "swiglu_fwd")
+    return a
+  return R.swiglu(h13[:, 0::2], h13[:, 1::2])
+
+
 def swiglu_bwd_fused(h13: torch.Tensor, da: torch.Tensor, row_scale: torch.Tensor | None, want_rowdot: bool,
-                     want_a: bool):
+                     want_a: bool, n_tiles: torch.Tensor | None = None):
   """MoE backward helper: returns (dh13, rowdot or None, a*scale or None).
 
   dh13 is the gradient of swiglu at h13 for upstream ``da * row_scale``; rowdot[m] =
@@ -132,7 +142,7 @@ def swiglu_bwd_fused(h13: torch.Tensor, da: torch.Tensor, row_scale: torch.Tenso
     rd = torch.empty(M, dtype=torch.float32, device=h13.device) if want_rowdot else None
     ao = torch.empty(M, F2 // 2, dtype=h13.dtype, device=h13.device) if want_a else None
     L.check(L.lib().nmoe_swiglu_bwd(L.ptr(h13), L.ptr(da), L.ptr(dh), L.ptr(row_scale), L.ptr(rd), L.ptr(ao),
-                                    L.c_ll(M), F2 // 2, L.stream()), "swiglu_bwd")
+                                    L.c_ll(M), F2 // 2, L.ptr(n_tiles), L.stream()), "swiglu_bwd")
     return dh, rd, ao
   g, u = h13[:, 0::2].float(), h13[:, 1::2].float()
   s = torch.sigmoid(g)

@@ -1,0 +1,99 @@
+"""Peer-mapped device memory over NVLink: one cudaMalloc'd slab per rank whose CUDA-IPC
+handle is exchanged through the process group, so that every rank holds a device
+pointer to every peer's slab and kernels can store into (or load from) a peer directly.
+
+world == 1 degenerates to a local slab with itself as its only "peer".
+Reference counterpart: nmoe/rdep.py:113-145 + nmoe/csrc/rdep.cu:511-538.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Dict, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from ..ops import _lib as L
+
+
+class PeerSlab:
+  """A byte slab carved into named regions at 256-byte-aligned offsets.
+
+  ``ptrs(name)`` returns a ctypes array of ``world`` device pointers (index = rank) to that
+  region in every rank's slab; ``local(name, dtype, shape)`` views this rank's region as a tensor.
+  """
+
+  def __init__(self, regions: List[Tuple[str, int]], group: Optional[dist.ProcessGroup] = None):
+    self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+    self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+    self.offsets: Dict[str, int] = {}
+    self.sizes: Dict[str, int] = {}
+    off = 0
+    for name, nbytes in regions:
+      self.offsets[name] = off
+      self.sizes[name] = nbytes
+      off += (nbytes + 255) & ~255
+    self.nbytes = max(off, 256)
+    lib = L.lib()
+    base = ctypes.c_void_p()
+    L.check(lib.nmoe_peer_alloc(ctypes.c_size_t(self.nbytes), ctypes.byref(base)), "peer_alloc", 0)
+    self.base = base.value
+    self.peer_bases: List[int] = [0] * self.world
+    self.peer_bases[self.rank] = self.base
+    self._opened: List[int] = []
+    if self.world > 1:
+      handle = (ctypes.c_ubyte * 64)()
+      L.check(lib.nmoe_peer_get_handle(ctypes.c_void_p(self.base), handle), "peer_get_handle", 0)
+      gathered: List[Optional[bytes]] = [None] * self.world
+      dist.all_gather_object(gathered, bytes(handle), group=group)
+      for r, h in enumerate(gathered):
+        if r == self.rank:
+          continue
+        buf = (ctypes.c_ubyte * 64).from_buffer_copy(h)
+        p = ctypes.c_void_p()
+        L.check(lib.nmoe_peer_open(buf, ctypes.byref(p)), f"peer_open(rank {r})", 0)
+        self.peer_bases[r] = p.value
+        self._opened.append(p.value)
+      dist.barrier(group=group)
+
+  def ptrs(self, name: str, extra_offset: int = 0):
+    arr = (ctypes.c_void_p * self.world)()
+    for r in range(self.world):
+      arr[r] = self.peer_bases[r] + self.offsets[name] + extra_offset
+    return arr
+
+  def local_ptr(self, name: str) -> int:
+    return self.base + self.offsets[name]
+
+  def local(self, name: str, dtype: torch.dtype, shape: Tuple[int, ...]) -> torch.Tensor:
+    """Zero-copy tensor view of this rank's region (kept alive by this object)."""
+    n = 1
+    for s in shape:
+      n *= s
+    esz = torch.empty(0, dtype=dtype).element_size()
+    assert n * esz <= self.sizes[name], f"region {name} too small"
+    return _tensor_from_ptr(self.local_ptr(name), n * esz, self).view(dtype).view(*shape)
+
+  def close(self) -> None:
+    if self.base:
+      torch.cuda.synchronize()
+      lib = L.lib()
+      for p in self._opened:
+        lib.nmoe_peer_close(ctypes.c_void_p(p))
+      self._opened = []
+      lib.nmoe_peer_free(ctypes.c_void_p(self.base))
+      self.base = 0
+
+
+class _CudaArrayView:
+  """Minimal ``__cuda_array_interface__`` holder so torch can wrap a raw device pointer."""
+
+  def __init__(self, ptr: int, nbytes: int, owner):
+    self.owner = owner
+    self.__cuda_array_interface__ = {
+      "shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3, "strides": None,
+    }
+
+
+def _tensor_from_ptr(ptr: int, nbytes: int, owner) -> torch.Tensor:
+  return torch.as_tensor(_CudaArrayView(ptr, nbytes, owner), device="cuda")

@@ -1,0 +1,224 @@
+"""RDEP expert parallelism: routing plan, direct placement into the owner's peer-mapped
+buffer, grouped expert GEMMs on the owner, gate-weighted return into the source's
+(token, slot) buffer and a fixed-order reduce.  No all-to-all collective, no host sync:
+row counts stay on the device and the grouped GEMMs read them from there.
+
+``Rdep.moe(x, gates, eid, W13, W2)`` is the differentiable entry point
+(reference: nmoe/rdep.py:34-145 and the autograd functions in nmoe/moe.py:52-617).
+
+Expert weight layout (chosen so that every forward GEMM reads a K-major B operand):
+  W13 [n_local, 2*Dff, H]   row 2j = gate projection j, row 2j+1 = up projection j
+  W2  [n_local, H, Dff]
+``to_reference_layout`` / ``from_reference_layout`` convert to the reference's
+W1,W3 [E,H,Dff], W2 [E,Dff,H] (nmoe/model.py:92-94) for checkpoints.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+from typing import Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from ..ops import _lib as L
+from ..ops import elementwise as EW
+from ..ops import tc_gemm as G
+from ..ref import ops as R
+from .peer import PeerSlab
+
+
+def to_reference_layout(W13: torch.Tensor, W2: torch.Tensor):
+  W1 = W13[:, 0::2, :].transpose(1, 2).contiguous()
+  W3 = W13[:, 1::2, :].transpose(1, 2).contiguous()
+  return W1, W3, W2.transpose(1, 2).contiguous()
+
+
+def from_reference_layout(W1: torch.Tensor, W3: torch.Tensor, W2: torch.Tensor):
+  E, H, F = W1.shape
+  W13 = torch.empty(E, 2 * F, H, dtype=W1.dtype, device=W1.device)
+  W13[:, 0::2, :] = W1.transpose(1, 2)
+  W13[:, 1::2, :] = W3.transpose(1, 2)
+  return W13, W2.transpose(1, 2).contiguous()
+
+
+@dataclass
+class Plan:
+  """Device-resident routing plan of one MoE call (kept for the backward re-dispatch)."""
+  eid: torch.Tensor            # [T*K] int32 global expert ids
+  rank_in_block: torch.Tensor  # [T*K]
+  block_prefix: torch.Tensor   # [n_blocks, E]
+  base: torch.Tensor           # [E]
+  offs_pad: torch.Tensor       # [n_local+1]
+  seg_rows: torch.Tensor       # [n_local]
+  tile_expert: torch.Tensor    # [cap/128]
+  n_m_tiles: torch.Tensor      # [1]
+  send_counts: torch.Tensor    # [E]
+  pos: torch.Tensor            # [T*K] position in the owner's buffer (-1 = dropped)
+  T: int
+  K: int
+
+
+class Rdep:
+  """Shared by all MoE layers of a model: peer slab, scratch, epochs."""
+
+  def __init__(self, dim: int, n_experts: int, topk: int, max_tokens: int, *, capacity_factor: float = 2.0,
+               group: Optional[dist.ProcessGroup] = None, device: Optional[torch.device] = None):
+    self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+    self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+    assert n_experts % self.world == 0
+    self.group = group
+    self.dim, self.E, self.K = dim, n_experts, topk
+    self.n_local = n_experts // self.world
+    self.max_tokens = max_tokens
+    self.device = device or torch.device("cuda", torch.cuda.current_device())
+    pairs = max_tokens * topk
+    worst = pairs * self.world
+    avg = pairs
+    rows = worst if self.world == 1 else min(worst, int(avg * capacity_factor))
+    self.capacity = ((rows + self.n_local * 127 + 127) // 128) * 128
+    H = dim
+    regions = [
+      ("x", self.capacity * H * 2), ("y", self.capacity * H * 2), ("meta", self.capacity * 16),
+      ("counts", self.world * self.E * 4), ("count_flags", 64), ("data_flags", 64), ("ret_flags", 64),
+      ("ret", pairs * H * 2), ("retg", pairs * 4),
+    ]
+    self.slab = PeerSlab(regions, group)
+    self.xbuf = self.slab.local("x", torch.bfloat16, (self.capacity, H))
+    self.ybuf = self.slab.local("y", torch.bfloat16, (self.capacity, H))
+    self.ret = self.slab.local("ret", torch.bfloat16, (pairs, H))
+    self.retg = self.slab.local("retg", torch.float32, (pairs,))
+    self.done_counter = torch.zeros(1, dtype=torch.int32, device=self.device)
+    self.epoch_count = 0
+    self.epoch_data = 0
+    self.epoch_ret = 0
+    self.wait_budget = 0          # 0 = library default (seconds); tests shrink it
+
+  # ---------------------------------------------------------------- building blocks
+  def plan(self, eid: torch.Tensor) -> Plan:
+    T, K = eid.shape
+    assert T <= self.max_tokens and K == self.K
+    dev = eid.device
+    n_pairs = T * K
+    lib = L.lib()
+    e32 = eid.reshape(-1).to(torch.int32).contiguous()
+    nb = lib.nmoe_rdep_count_blocks(n_pairs)
+    block_hist = torch.empty(max(nb, 1), self.E, dtype=torch.int32, device=dev)
+    rib = torch.empty(n_pairs, dtype=torch.int32, device=dev)
+    st = G.status_buffer(dev)
+    L.check(lib.nmoe_rdep_count(L.ptr(e32), n_pairs, self.E, L.ptr(block_hist), L.ptr(rib), L.ptr(st), L.stream()),
+            "rdep_count")
+    small = torch.empty(self.E * 2 + 2 * self.n_local + 2 + self.capacity // 128, dtype=torch.int32, device=dev)
+    o = 0
+    base = small[o:o + self.E]; o += self.E
+    send_counts = small[o:o + self.E]; o += self.E
+    offs_pad = small[o:o + self.n_local + 1]; o += self.n_local + 1
+    seg_rows = small[o:o + self.n_local]; o += self.n_local
+    n_m_tiles = small[o:o + 1]; o += 1
+    tile_expert = small[o:o + self.capacity // 128]
+    self.epoch_count += 1
+    L.check(lib.nmoe_rdep_plan(self.rank, self.world, self.E, self.n_local, nb, self.capacity, self.epoch_count,
+                               L.ptr(block_hist), self.slab.ptrs("counts"), self.slab.ptrs("count_flags"),
+                               L.ptr(base), L.ptr(offs_pad), L.ptr(seg_rows), L.ptr(tile_expert), L.ptr(n_m_tiles),
+                               L.ptr(send_counts), L.ptr(st), L.stream()), "rdep_plan")
+    pos = torch.empty(n_pairs, dtype=torch.int32, device=dev)
+    return Plan(e32, rib, block_hist, base, offs_pad, seg_rows, tile_expert, n_m_tiles, send_counts, pos, T, K)
+
+  def place(self, x: torch.Tensor, plan: Plan, gates: Optional[torch.Tensor], which: str, with_meta: bool) -> None:
+    """Store x's rows into every owner's ``which`` buffer ('x' or 'y') and release the data flags."""
+    self.epoch_data += 1
+    st = G.status_buffer(x.device)
+    L.check(L.lib().nmoe_rdep_place(
+      self.rank, self.world, self.E, self.n_local, plan.T, plan.K, self.dim, self.epoch_data, L.ptr(x),
+      L.ptr(plan.eid), L.ptr(gates), L.ptr(plan.rank_in_block), L.ptr(plan.block_prefix), L.ptr(plan.base),
+      self.slab.ptrs(which), self.slab.ptrs("meta") if with_meta else None, self.slab.ptrs("data_flags"),
+      L.ptr(plan.pos), None, L.ptr(plan.offs_pad), L.ptr(plan.seg_rows), L.ptr(self.done_counter), L.ptr(st),
+      L.stream()), "rdep_place")
+
+  def wait_data(self) -> None:
+    st = G.status_buffer(self.device)
+    L.check(L.lib().nmoe_rdep_wait(ctypes.c_void_p(self.slab.local_ptr("data_flags")), self.world,
+                                   ctypes.c_uint(self.epoch_data), ctypes.c_uint(self.wait_budget), L.ptr(st), 420,
+                                   L.stream()), "rdep_wait(data)")
+
+  def push_and_reduce(self, y: Optional[torch.Tensor], plan: Plan, use_gate: bool, rowval: Optional[torch.Tensor],
+                      out: torch.Tensor) -> None:
+    """Owner -> source return of rows (and optional per-row scalars), then the source-side K-way sum."""
+    lib = L.lib()
+    st = G.status_buffer(self.device)
+    L.check(lib.nmoe_rdep_push(L.ptr(y), ctypes.c_void_p(self.slab.local_ptr("meta")), L.ptr(plan.n_m_tiles),
+                               self.capacity, self.dim, int(use_gate), self.slab.ptrs("ret"),
+                               self.slab.ptrs("retg"), L.ptr(rowval), self.world, L.stream()), "rdep_push")
+    self.epoch_ret += 1
+    L.check(lib.nmoe_rdep_signal(self.slab.ptrs("ret_flags"), self.rank, self.world, ctypes.c_uint(self.epoch_ret),
+                                 L.stream()), "rdep_signal")
+    L.check(lib.nmoe_rdep_wait(ctypes.c_void_p(self.slab.local_ptr("ret_flags")), self.world,
+                               ctypes.c_uint(self.epoch_ret), ctypes.c_uint(self.wait_budget), L.ptr(st), 421,
+                               L.stream()), "rdep_wait(ret)")
+    L.check(lib.nmoe_rdep_reduce(ctypes.c_void_p(self.slab.local_ptr("ret")), L.ptr(plan.pos), L.ptr(out), plan.T,
+                                 plan.K, self.dim, L.stream()), "rdep_reduce")
+
+  def row_gates(self, plan: Plan) -> torch.Tensor:
+    out = torch.empty(self.capacity, dtype=torch.float32, device=self.device)
+    L.check(L.lib().nmoe_rdep_row_gates(ctypes.c_void_p(self.slab.local_ptr("meta")), L.ptr(plan.n_m_tiles),
+                                        self.capacity, L.ptr(out), L.stream()), "rdep_row_gates")
+    return out
+
+  # ---------------------------------------------------------------- differentiable MoE
+  def moe(self, x: torch.Tensor, gates: torch.Tensor, eid: torch.Tensor, W13: torch.Tensor, W2: torch.Tensor,
+          save_h13: bool = False) -> torch.Tensor:
+    """out[t] = sum_k gates[t,k] * Expert_{eid[t,k]}(x[t]); x [T,H] bf16, gates fp32 [T,K], eid [T,K]."""
+    return _MoEFused.apply(self, x, gates, eid, W13, W2, save_h13)
+
+  def close(self) -> None:
+    self.slab.close()
+
+
+class _MoEFused(torch.autograd.Function):
+  @staticmethod
+  def forward(ctx, rdep: Rdep, x, gates, eid, W13, W2, save_h13):
+    x = x.contiguous()
+    gates32 = gates.detach().float().contiguous()
+    plan = rdep.plan(eid)
+    rdep.place(x, plan, gates32.view(-1), "x", with_meta=True)
+    rdep.wait_data()
+    h13 = G.grouped_gemm(rdep.xbuf, W13, plan.tile_expert, plan.n_m_tiles)
+    a = EW.swiglu_rows(h13, plan.n_m_tiles)
+    y = G.grouped_gemm(a, W2, plan.tile_expert, plan.n_m_tiles)
+    out = torch.empty_like(x)
+    rdep.push_and_reduce(y, plan, True, None, out)
+    ctx.rdep, ctx.plan = rdep, plan
+    ctx.save_for_backward(x, gates32, W13, W2, h13 if save_h13 else None)
+    return out
+
+  @staticmethod
+  def backward(ctx, dout):
+    rdep: Rdep = ctx.rdep
+    plan: Plan = ctx.plan
+    x, gates32, W13, W2, h13 = ctx.saved_tensors
+    dout = dout.contiguous()
+    rdep.place(x, plan, gates32.view(-1), "x", with_meta=True)
+    rdep.place(dout, plan, None, "y", with_meta=False)
+    rdep.wait_data()
+    nt = plan.n_m_tiles
+    if h13 is None:
+      h13 = G.grouped_gemm(rdep.xbuf, W13, plan.tile_expert, nt)
+    # dA' = dYe @ W2 (un-gated); gate enters through the row scale of the SwiGLU backward
+    da = G.grouped_gemm(rdep.ybuf, W2, plan.tile_expert, nt, b_mn=True)
+    row_gate = rdep.row_gates(plan)
+    dh13, rowdot, a_scaled = EW.swiglu_bwd_fused(h13, da, row_gate, True, True, nt)
+    # every reader of the peer-written buffers runs before the kernel that returns rows to the sources
+    dW2 = G.grouped_wgrad(rdep.ybuf, a_scaled, plan.offs_pad, rdep.n_local)      # [E, H, Dff]
+    dW13 = G.grouped_wgrad(dh13, rdep.xbuf, plan.offs_pad, rdep.n_local)         # [E, 2Dff, H]
+    dxe = G.grouped_gemm(dh13, W13, plan.tile_expert, nt, b_mn=True)
+    dx = torch.empty_like(x)
+    rdep.push_and_reduce(dxe, plan, False, rowdot, dx)
+    dg = rdep.retg[: plan.T * plan.K].clone().view(plan.T, plan.K)
+    dg = torch.where(plan.pos.view(plan.T, plan.K) >= 0, dg, torch.zeros_like(dg))
+    return None, dx, dg, None, dW13, dW2, None
+
+
+def moe_reference(x, gates, eid, W13, W2):
+  """CPU / oracle statement with the same weight layout."""
+  W1, W3, W2r = to_reference_layout(W13, W2)
+  return R.moe(x, eid, gates, W1, W3, W2r)

@@ -1,0 +1,168 @@
+"""Training entry point: ``python -m nmoe_b200.train <config.toml> [--key=value ...]`` or
+``torchrun ... -m nmoe_b200.train <config.toml>``.
+
+One path: forward -> masked CE -> backward -> optimizer step -> log -> eval -> checkpoint
+(nmoe/train.py:36-184).  ``Trainer`` is the public step API; ``train(cfg)`` is the full loop
+with data loading, metrics, experiment tracking and checkpoint/resume.
+"""
+from __future__ import annotations
+
+import os
+import sys
+import time
+from contextlib import nullcontext
+from typing import Optional, Tuple
+
+os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
+
+import torch
+import torch.distributed as dist
+
+from . import runtime
+from .config import Config, fingerprint, from_toml
+from .log import print0
+from .models.transformer import Transformer
+from .opt import Optimizer
+
+
+class Trainer:
+  """Owns the model and optimizer of one rank and advances them one step at a time.
+
+  ``step(inputs, targets)`` takes host (ideally pinned) or device int64 tensors of shape
+  [micro_batch, seq_len], copies them to the device if needed, runs forward/backward/update and
+  returns the loss as a device scalar (call ``.item()`` to read it on the host).
+  """
+
+  def __init__(self, cfg: Config, *, rank: int = 0, world: int = 1, device: Optional[torch.device] = None,
+               fuse_expert_opt: Optional[bool] = None, init: bool = True):
+    self.cfg, self.rank, self.world = cfg, rank, world
+    self.device = device or torch.device("cpu")
+    on_cuda = self.device.type == "cuda"
+    dtype = torch.bfloat16 if on_cuda else torch.float32
+    self.model = Transformer(cfg, dtype=dtype, device=self.device)
+    if init:
+      self.model.init_weights()
+    self.model.train()
+    if fuse_expert_opt is None:
+      fuse_expert_opt = on_cuda and os.environ.get("NMOE_EXPERT_OPT_IN_BACKWARD", "1") == "1"
+    self.opt = Optimizer(self.model, cfg, fuse_expert_in_backward=fuse_expert_opt)
+    self.step_num = 0
+    self.tokens_seen = 0
+    self.gradnorm_sq = torch.zeros(1, dtype=torch.float32, device=self.device)
+    self.track_gradnorm = False
+    self.lr = 0.0
+    self.nvtx = os.environ.get("NMOE_NVTX", "0") in ("1", "true", "True") and on_cuda
+
+  def _range(self, tag: str):
+    return torch.cuda.nvtx.range(tag) if self.nvtx else nullcontext()
+
+  def step(self, inputs: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
+    if inputs.device != self.device:
+      inputs = inputs.to(self.device, non_blocking=True)
+      targets = targets.to(self.device, non_blocking=True)
+    gn = None
+    if self.track_gradnorm:
+      self.gradnorm_sq.zero_()
+      gn = self.gradnorm_sq
+    self.opt.dense.gradnorm_sq = gn
+    self.lr = self.opt.begin_step(self.step_num, self.tokens_seen, gn)
+    with self._range("train/fwd_total"):
+      loss = self.model.loss(inputs, targets)
+    with self._range("train/bwd_total"):
+      loss.backward()
+    with self._range("train/opt_step"):
+      self.opt.step()
+    self.step_num += 1
+    self.tokens_seen += self.cfg.batch_size * self.cfg.seq_len
+    return loss.detach()
+
+  def grad_norm(self) -> torch.Tensor:
+    """sqrt of the squared-gradient sum of the last step (all-reduced); needs track_gradnorm."""
+    g = self.gradnorm_sq.clone()
+    if dist.is_initialized() and self.world > 1:
+      dist.all_reduce(g)
+    return g.sqrt()
+
+
+def train(cfg: Config) -> dict:
+  from .checkpoint import Checkpointer, load_checkpoint, save_checkpoint
+  from .data.loader import build_loader
+  from .experiments import ExperimentTracker
+  from .metrics import MetricsSession, log_training_step
+  from .ops import tc_gemm
+
+  rank, world, device = runtime.init(cfg.seed)
+  cfg.validate(world)
+  tracker = None
+  run_id = os.environ.get("NMOE_RUN", "")
+  if rank == 0:
+    tracker = ExperimentTracker(cfg)
+    run_id = tracker.start_run(run_id=run_id or None)
+  checkpointer = Checkpointer(cfg.checkpoint_dir, keep_last=cfg.checkpoint_keep_last_n, async_io=True)
+  loader, plan = build_loader(cfg, rank, world)
+  trainer = Trainer(cfg, rank=rank, world=world, device=device)
+  metrics = MetricsSession(run_id or f"run_{int(time.time())}", cfg.metrics_dir, rank, world, trainer.model, cfg)
+  start_step, tokens_seen = load_checkpoint(checkpointer, trainer, loader, plan, cfg, rank, print0)
+  trainer.step_num, trainer.tokens_seen = start_step, tokens_seen
+  fp = fingerprint(cfg)
+  last_loss = None
+  try:
+    for step_num in range(start_step, cfg.steps):
+      t0 = time.perf_counter()
+      inputs, targets = loader.next()
+      loader_wait_ms = (time.perf_counter() - t0) * 1000.0
+      s = step_num + 1
+      trainer.track_gradnorm = (s % cfg.log_every == 0) or s == 1
+      with metrics.timer("time_ms/step"):
+        loss = trainer.step(inputs, targets)
+      last_loss = loss
+      log_training_step(metrics, s, trainer, loss, loader_wait_ms, print0)
+      if device.type == "cuda" and s % cfg.log_every == 0:
+        tc_gemm.check_status(device)
+      if cfg.eval_every > 0 and s % cfg.eval_every == 0:
+        try:
+          from .eval.choices import format_results, run_eval
+          res = run_eval(trainer.model, cfg, rank=rank, world=world, max_examples=cfg.eval_budget_max_examples)
+          print0(f"[eval] step={s} {format_results(res)}")
+          metrics.insert_many(s, [(f"eval_choices/{t}/{k}", float(v)) for t, r in res.items() for k, v in r.items()
+                                  if k in ("acc", "centered_acc", "n")])
+        except Exception as e:  # evaluation must never take the run down
+          print0(f"[eval] failed: {e}")
+      try:
+        from .eval.hooks import maybe_schedule_eval
+        maybe_schedule_eval(s, cfg, trainer.model, run_id, print0)
+      except Exception as e:
+        print0(f"[eval] scheduling failed: {e}")
+      save_checkpoint(checkpointer, s, trainer, loader, plan, cfg, rank, fp, print0)
+    print0(f"[nmoe] Training complete. {trainer.tokens_seen:,} tokens.")
+    results = {"final_loss": float(last_loss.item()) if last_loss is not None else 0.0,
+               "tokens_seen": trainer.tokens_seen, "steps_completed": cfg.steps}
+    if tracker is not None:
+      tracker.end_run(run_id, "completed", results)
+    return results
+  except Exception:
+    if tracker is not None:
+      tracker.end_run(run_id, "failed")
+    raise
+  finally:
+    checkpointer.close()
+    metrics.close()
+    if tracker is not None:
+      tracker.close()
+    if trainer.model.rdep is not None:
+      trainer.model.rdep.close()
+
+
+def main(argv: Optional[list] = None) -> None:
+  argv = list(sys.argv[1:] if argv is None else argv)
+  if not argv or argv[0].startswith("--"):
+    raise SystemExit("usage: python -m nmoe_b200.train <config.toml> [--key=value ...]")
+  cfg = from_toml(argv[0], argv[1:])
+  try:
+    train(cfg)
+  finally:
+    runtime.finalize()
+
+
+if __name__ == "__main__":
+  main()

@@ -1,0 +1,158 @@
+"""RDEP MoE (single GPU: plan -> place -> grouped GEMMs -> return/reduce) and router / CE kernels
+against the fp32 oracle."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel(a, b):
+  return ((a.float() - b.float()).abs().max() / (b.float().abs().max() + 1e-6)).item()
+
+
+@pytest.mark.parametrize("T,H,F,E,K", [(32, 128, 256, 4, 1), (300, 256, 128, 8, 2), (1024, 512, 384, 16, 6)])
+def test_moe_forward_backward_vs_oracle(T, H, F, E, K):
+  from nmoe_b200.parallel.rdep import Rdep, moe_reference
+  from nmoe_b200.ops import tc_gemm as G
+  torch.manual_seed(0)
+  dev = torch.device("cuda")
+  rd = Rdep(H, E, K, T, device=dev)
+  try:
+    x = (torch.randn(T, H, device=dev) * 0.5).bfloat16().requires_grad_()
+    W13 = (torch.randn(E, 2 * F, H, device=dev) * 0.05).bfloat16().requires_grad_()
+    W2 = (torch.randn(E, H, F, device=dev) * 0.05).bfloat16().requires_grad_()
+    eid = torch.stack([torch.randperm(E, device=dev)[:K] for _ in range(T)]).int()
+    gates = torch.rand(T, K, device=dev).requires_grad_()
+    for save in (False, True):
+      for t in (x, W13, W2, gates):
+        t.grad = None
+      out = rd.moe(x, gates, eid, W13, W2, save)
+      g = torch.randn_like(out)
+      out.backward(g)
+      torch.cuda.synchronize()
+      G.check_status()
+      xf, Wf, W2f, gf = [t.detach().float().cpu().requires_grad_() for t in (x, W13, W2, gates)]
+      ref = moe_reference(xf, gf, eid.cpu().long(), Wf, W2f)
+      ref.backward(g.float().cpu())
+      assert _rel(out.cpu(), ref) < 3e-2
+      assert _rel(x.grad.cpu(), xf.grad) < 3e-2
+      assert _rel(gates.grad.cpu(), gf.grad) < 3e-2
+      assert _rel(W13.grad.cpu(), Wf.grad) < 3e-2
+      assert _rel(W2.grad.cpu(), W2f.grad) < 3e-2
+  finally:
+    rd.close()
+
+
+def test_moe_all_tokens_to_one_expert_and_determinism():
+  from nmoe_b200.parallel.rdep import Rdep, moe_reference
+  torch.manual_seed(1)
+  dev = torch.device("cuda")
+  T, H, F, E, K = 500, 256, 128, 8, 2
+  rd = Rdep(H, E, K, T, device=dev)
+  try:
+    x = (torch.randn(T, H, device=dev) * 0.5).bfloat16()
+    W13 = (torch.randn(E, 2 * F, H, device=dev) * 0.05).bfloat16()
+    W2 = (torch.randn(E, H, F, device=dev) * 0.05).bfloat16()
+    eid = torch.tensor([[0, 3]] * T, device=dev, dtype=torch.int32)      # experts 1,2,4..7 empty
+    gates = torch.rand(T, K, device=dev)
+    o1 = rd.moe(x, gates, eid, W13, W2)
+    o2 = rd.moe(x, gates, eid, W13, W2)
+    assert torch.equal(o1, o2), "two runs must be bit-identical"
+    ref = moe_reference(x.float().cpu(), gates.cpu(), eid.cpu().long(), W13.float().cpu(), W2.float().cpu())
+    assert _rel(o1.cpu(), ref) < 3e-2
+  finally:
+    rd.close()
+
+
+def test_wait_timeout_reports_status_and_context_survives():
+  """A flag nobody sets: the bounded wait gives up, records a status, and the GPU stays usable."""
+  import ctypes
+  from nmoe_b200.ops import _lib as L, tc_gemm as G
+  dev = torch.device("cuda")
+  flags = torch.zeros(8, dtype=torch.int32, device=dev)
+  st = G.status_buffer(dev)
+  L.check(L.lib().nmoe_rdep_wait(L.ptr(flags), 1, ctypes.c_uint(5), ctypes.c_uint(2000), L.ptr(st), 999, L.stream()),
+          "rdep_wait")
+  torch.cuda.synchronize()
+  with pytest.raises(L.NativeLibraryError, match="where=999"):
+    G.check_status()
+  assert (torch.ones(4, device=dev) * 2).sum().item() == 8.0
+  G.check_status()
+
+
+@pytest.mark.parametrize("kind,E,K,ng,mg", [("sigmoid", 64, 6, 0, 0), ("softmax", 160, 6, 8, 3), ("sigmoid", 8, 2, 0, 0),
+                                            ("softmax", 256, 8, 0, 0)])
+def test_router_topk_vs_oracle(kind, E, K, ng, mg):
+  from nmoe_b200 import ops
+  from nmoe_b200.ref import ops as R
+  torch.manual_seed(2)
+  T = 333
+  logits = torch.randn(T, E, device="cuda").bfloat16().requires_grad_()
+  bias = (torch.randn(E, device="cuda") * 0.01) if kind == "sigmoid" else None
+  loads = torch.zeros(E, dtype=torch.int32, device="cuda")
+  w, idx = ops.router_topk(logits, bias, K, route_scale=2.446, kind=kind, n_groups=ng, max_groups=mg, loads=loads)
+  lf = logits.detach().float().requires_grad_()
+  wr, ir = R.router(lf, bias, K, route_scale=2.446, kind=kind, n_groups=ng, max_groups=mg)
+  assert torch.equal(idx.long().sort(-1).values, ir.sort(-1).values)
+  order = torch.argsort(idx.long(), -1), torch.argsort(ir, -1)
+  assert torch.allclose(torch.gather(w, 1, order[0]), torch.gather(wr, 1, order[1]), atol=1e-5)
+  assert torch.equal(loads.long(), torch.bincount(ir.reshape(-1), minlength=E))
+  gw = torch.randn_like(w)
+  w.backward(gw)
+  # align the upstream gradient with the oracle's slot order
+  inv = torch.empty_like(order[0]); inv.scatter_(1, order[0], torch.arange(K, device="cuda").expand(T, K))
+  gw_r = torch.gather(torch.gather(gw, 1, order[0]), 1, torch.argsort(order[1], -1))
+  wr.backward(gw_r)
+  assert _rel(logits.grad, lf.grad) < 2e-2
+
+
+def test_router_bias_update():
+  from nmoe_b200 import ops
+  E = 64
+  bias = torch.zeros(E, device="cuda")
+  loads = torch.randint(0, 100, (E,), device="cuda").float()
+  ref = torch.zeros(E)
+  ops.router_bias_update_(ref, loads.cpu(), 1e-3)
+  ops.router_bias_update_(bias, loads, 1e-3)
+  assert torch.allclose(bias.cpu(), ref, atol=1e-7)
+
+
+@pytest.mark.parametrize("V", [1024, 5000])
+def test_lm_head_loss_vs_oracle(V):
+  from nmoe_b200 import ops
+  from nmoe_b200.ref import ops as R
+  torch.manual_seed(3)
+  T, H = 700, 256
+  h = torch.randn(T, H, device="cuda").bfloat16().requires_grad_()
+  w = (torch.randn(V, H, device="cuda") * 0.06).bfloat16().requires_grad_()
+  tg = torch.randint(0, V, (T,), device="cuda")
+  tg[::7] = V - 1                                   # masked positions
+  loss = ops.lm_head_loss(h, w, tg, V - 1, 0.125, chunk_rows=256)
+  loss.backward()
+  hf, wf = h.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+  lr = R.lm_head_loss(hf, wf, tg, V - 1, 0.125)
+  lr.backward()
+  assert abs(loss.item() - lr.item()) < 2e-3 * max(1.0, abs(lr.item()))
+  assert _rel(h.grad, hf.grad) < 3e-2
+  assert _rel(w.grad, wf.grad) < 3e-2
+
+
+def test_toy_model_step_on_gpu():
+  import math
+  from nmoe_b200.config import Config
+  from nmoe_b200.train import Trainer
+  from nmoe_b200.ops import tc_gemm as G
+  torch.manual_seed(5)
+  cfg = Config(vocab_size=1024, eos_token_id=1023, dim=256, n_layers=3, n_heads=4, inter_dim=1024, moe_inter_dim=128,
+               n_routed_experts=8, n_activated_experts=2, n_shared_experts=1, n_dense_layers=1, q_lora_rank=96,
+               kv_lora_rank=64, qk_nope_head_dim=32, qk_rope_head_dim=32, v_head_dim=32, batch_size=2, seq_len=128,
+               max_position_embeddings=256, warmup_steps=1, lr_dense=3e-3, lr_expert=3e-3, lr_router=3e-3)
+  tr = Trainer(cfg, device=torch.device("cuda"))
+  tok = torch.randint(0, 1000, (2, 129))
+  x, y = tok[:, :-1].pin_memory(), tok[:, 1:].contiguous().pin_memory()
+  l0 = tr.step(x, y).item()
+  for _ in range(8):
+    l = tr.step(x, y).item()
+  G.check_status()
+  assert math.isfinite(l0) and l < l0 - 0.05, (l0, l)
+  tr.model.rdep.close()
