@@ -463,3 +463,34 @@ int nmoe_sumsq_bf16(const void* x, long long n, float* out, cudaStream_t st) {
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------ allocation-free variant
+#include "noalloc.h"
+
+namespace nmoe {
+// Scratch for nmoe_rmsnorm_bwd_noalloc.  In host code this name is only a handle for
+// cudaGetSymbolAddress; the kernels receive the resolved device pointer.
+static __device__ __align__(256) float g_rmsnorm_bwd_scratch[NMOE_NOALLOC_RMSNORM_MAX_BLOCKS * NMOE_NOALLOC_RMSNORM_MAX_H];
+constexpr int kNoallocMaxDevices = 64;
+static float* g_rmsnorm_bwd_scratch_ptr[kNoallocMaxDevices] = {nullptr};
+}  // namespace nmoe
+
+extern "C" int nmoe_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w, const float* rstd, void* dx,
+                                        void* dw, int M, int H, int accumulate, cudaStream_t st) {
+  if (M == 0) return 0;
+  if (H % 8 != 0 || H > NMOE_NOALLOC_RMSNORM_MAX_H) return -1;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (dev < 0 || dev >= nmoe::kNoallocMaxDevices) return -3;
+  if (nmoe::g_rmsnorm_bwd_scratch_ptr[dev] == nullptr) {
+    // once per device, with that device current
+    float* p = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), nmoe::g_rmsnorm_bwd_scratch);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    nmoe::g_rmsnorm_bwd_scratch_ptr[dev] = p;
+  }
+  // nmoe_rmsnorm_bwd_blocks(M) never exceeds NMOE_NOALLOC_RMSNORM_MAX_BLOCKS, and every partial
+  // row read by the column sum is written by the backward kernel of the same call.
+  return nmoe_rmsnorm_bwd(dy, x, w, rstd, dx, dw, nmoe::g_rmsnorm_bwd_scratch_ptr[dev], M, H, accumulate, st);
+}
