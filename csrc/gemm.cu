@@ -46,6 +46,15 @@ struct GemmParams {
   int accumulate;              // C += result instead of C = result
   long long b_rows_per_expert; // mode 1: rows of B's 2-D view per expert
   StatusRecord* status;
+  // Fused RDEP return (mode 1, bf16 output): when row_meta != nullptr the epilogue does not write C;
+  // it multiplies row r by its gate (push_use_gate) and stores it into the SOURCE rank's return
+  // buffer peer_ret[src] at row tok_slot (16-byte system-scope stores over NVLink), and forwards the
+  // optional per-row scalar rowval[r] to peer_retg[src][tok_slot].
+  const int4* row_meta;        // {src_rank, tok_slot, gate bits, valid} per row
+  __nv_bfloat16* peer_ret[8];
+  float* peer_retg[8];
+  const float* rowval;
+  int push_use_gate;
 };
 
 NMOE_DEVICE uint64_t globaltimer_ns() {
@@ -254,7 +263,18 @@ k_gemm_bf16(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     for (int t = blockIdx.x; decode_tile<BN, MODE>(p, t, m_tiles, n_tiles, tc); t += gridDim.x) {
       const int row = tc.m_blk * BM + q * 32 + lane;
       const int n0 = tc.n_blk * BN;
-      const bool row_ok = row < m_limit;
+      bool row_ok = row < m_limit;
+      __nv_bfloat16* push_dst = nullptr;
+      float push_gate = 1.f;
+      if (MODE == 1 && p.row_meta != nullptr && row_ok) {
+        const int4 mv = __ldg(p.row_meta + row);
+        row_ok = mv.w != 0;
+        if (row_ok) {
+          push_dst = p.peer_ret[mv.x] + static_cast<long long>(mv.y) * p.ldc;
+          if (p.push_use_gate) push_gate = __int_as_float(mv.z);
+          if (tc.n_blk == 0 && p.rowval != nullptr) p.peer_retg[mv.x][mv.y] = p.rowval[row];
+        }
+      }
       const long long crow = (MODE == 2) ? static_cast<long long>(tc.expert) * p.M + row : row;
       const bool have_acc = tc.kb_count > 0;
       if (have_acc) {
@@ -295,6 +315,21 @@ k_gemm_bf16(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             } else {
               for (int i = 0; i < 32 && col + i < p.N; ++i)
                 dst[i] = __uint_as_float(r[i]) + (p.accumulate ? dst[i] : 0.f);
+            }
+          } else if (MODE == 1 && push_dst != nullptr) {
+            __nv_bfloat16* dst = push_dst + col;
+            if (col + 32 <= p.N && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                int4 v;
+                v.x = pack_bf16x2(__uint_as_float(r[8 * i]) * push_gate, __uint_as_float(r[8 * i + 1]) * push_gate);
+                v.y = pack_bf16x2(__uint_as_float(r[8 * i + 2]) * push_gate, __uint_as_float(r[8 * i + 3]) * push_gate);
+                v.z = pack_bf16x2(__uint_as_float(r[8 * i + 4]) * push_gate, __uint_as_float(r[8 * i + 5]) * push_gate);
+                v.w = pack_bf16x2(__uint_as_float(r[8 * i + 6]) * push_gate, __uint_as_float(r[8 * i + 7]) * push_gate);
+                st_relaxed_sys_v4(reinterpret_cast<int4*>(dst) + i, v);
+              }
+            } else {
+              for (int i = 0; i < 32 && col + i < p.N; ++i) dst[i] = __float2bfloat16(__uint_as_float(r[i]) * push_gate);
             }
           } else {
             __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.C) + crow * p.ldc + col;
@@ -339,6 +374,7 @@ k_gemm_bf16(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   if (*abort_flag) {
     for (int i = 0; i < 2000; ++i) __nanosleep(1000);
   }
+  if (MODE == 1 && p.row_meta != nullptr) __threadfence_system();
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 1) {
@@ -425,7 +461,8 @@ extern "C" {
 int nmoe_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
                    long long ldc, int a_mn, int b_mn, int mode, int E, const int* tile_expert, const int* n_m_tiles,
                    const int* offs, long long a_rows, long long b_rows, int out_fp32, int accumulate, int bn,
-                   void* status, cudaStream_t st) {
+                   void* status, const void* row_meta, void* const* peer_ret, void* const* peer_retg,
+                   const float* rowval, int push_use_gate, int world, cudaStream_t st) {
   if (M <= 0 || N <= 0) return 0;
   if (mode != 2 && K <= 0) return -1;
   if ((lda % 8) || (ldb % 8)) return -2;
@@ -440,6 +477,14 @@ int nmoe_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, l
   p.C = C; p.ldc = ldc; p.out_fp32 = out_fp32; p.accumulate = accumulate;
   p.b_rows_per_expert = (mode == 1) ? (b_mn ? K : N) : 0;
   p.status = static_cast<StatusRecord*>(status);
+  p.row_meta = static_cast<const int4*>(row_meta);
+  p.rowval = rowval;
+  p.push_use_gate = push_use_gate;
+  for (int r = 0; r < 8; ++r) {
+    p.peer_ret[r] = (row_meta && peer_ret && r < world) ? static_cast<__nv_bfloat16*>(peer_ret[r]) : nullptr;
+    p.peer_retg[r] = (row_meta && peer_retg && r < world) ? static_cast<float*>(peer_retg[r]) : nullptr;
+  }
+  if (row_meta && (mode != 1 || out_fp32 || world > 8)) return -6;
 
   // Tensor maps.  a_rows / b_rows are the outer extents of the 2-D views (rows in memory).
   CUtensorMap tmA, tmB;

@@ -67,13 +67,14 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
   L.check(L.lib().nmoe_gemm_bf16(
     L.ptr(a), L.ptr(b), L.ptr(out), M, N, K, L.c_ll(a.stride(0)), L.c_ll(b.stride(0)), L.c_ll(out.stride(0)),
     int(a_mn), int(b_mn), 0, 1, None, None, None, L.c_ll(a.size(0)), L.c_ll(b.size(0)),
-    int(out.dtype == torch.float32), int(accumulate), bn, L.ptr(st), L.stream()), "gemm_bf16")
+    int(out.dtype == torch.float32), int(accumulate), bn, L.ptr(st), None, None, None, None, 0, 0, L.stream()),
+    "gemm_bf16")
   return out
 
 
 def grouped_gemm(a: torch.Tensor, b: torch.Tensor, tile_expert: torch.Tensor, n_m_tiles: torch.Tensor, *,
                  b_mn: bool = False, out: Optional[torch.Tensor] = None, offs: Optional[torch.Tensor] = None,
-                 bn: int = 0) -> torch.Tensor:
+                 bn: int = 0, push: Optional[dict] = None) -> Optional[torch.Tensor]:
   """Rows of ``a`` [Mcap,K] are 128-aligned per-expert segments; row tile i belongs to expert
   ``tile_expert[i]`` and only the first ``n_m_tiles[0]`` tiles are valid.  ``b``: [E,N,K]
   (b_mn False) or [E,K,N] (b_mn True).  Returns [Mcap,N]; rows past the valid tiles are
@@ -91,14 +92,22 @@ def grouped_gemm(a: torch.Tensor, b: torch.Tensor, tile_expert: torch.Tensor, n_
       c[i * 128:(i + 1) * 128] = (a[i * 128:(i + 1) * 128].float() @ w.float()).to(c.dtype)
     return c
   assert a.is_contiguous() and b.is_contiguous() and a.size(0) % 128 == 0
-  if out is None:
-    out = torch.empty(a.size(0), N, dtype=torch.bfloat16, device=a.device)
   st = status_buffer(a.device)
   b2_rows = E * (K if b_mn else N)
+  if push is not None:
+    # fused RDEP return: rows go to the source ranks' return buffers instead of a local C
+    L.check(L.lib().nmoe_gemm_bf16(
+      L.ptr(a), L.ptr(b), None, a.size(0), N, K, L.c_ll(K), L.c_ll(N if b_mn else K), L.c_ll(N),
+      0, int(b_mn), 1, E, L.ptr(tile_expert), L.ptr(n_m_tiles), None, L.c_ll(a.size(0)), L.c_ll(b2_rows),
+      0, 0, bn, L.ptr(st), push["meta"], push["peer_ret"], push.get("peer_retg"), L.ptr(push.get("rowval")),
+      int(push["use_gate"]), push["world"], L.stream()), "grouped_gemm_bf16(push)")
+    return None
+  if out is None:
+    out = torch.empty(a.size(0), N, dtype=torch.bfloat16, device=a.device)
   L.check(L.lib().nmoe_gemm_bf16(
     L.ptr(a), L.ptr(b), L.ptr(out), a.size(0), N, K, L.c_ll(K), L.c_ll(N if b_mn else K), L.c_ll(out.stride(0)),
     0, int(b_mn), 1, E, L.ptr(tile_expert), L.ptr(n_m_tiles), None, L.c_ll(a.size(0)), L.c_ll(b2_rows),
-    0, 0, bn, L.ptr(st), L.stream()), "grouped_gemm_bf16")
+    0, 0, bn, L.ptr(st), None, None, None, None, 0, 0, L.stream()), "grouped_gemm_bf16")
   return out
 
 
@@ -128,7 +137,8 @@ def grouped_wgrad(a: torch.Tensor, b: torch.Tensor, offs: torch.Tensor, E: int, 
   L.check(L.lib().nmoe_gemm_bf16(
     L.ptr(a), L.ptr(b), L.ptr(out), Ma, Nb, 0, L.c_ll(Ma), L.c_ll(Nb), L.c_ll(Nb),
     1, 1, 2, E, None, None, L.ptr(offs), L.c_ll(a.size(0)), L.c_ll(b.size(0)),
-    int(out.dtype == torch.float32), int(accumulate), bn, L.ptr(st), L.stream()), "grouped_wgrad_bf16")
+    int(out.dtype == torch.float32), int(accumulate), bn, L.ptr(st), None, None, None, None, 0, 0, L.stream()),
+    "grouped_wgrad_bf16")
   return out
 
 

@@ -93,6 +93,7 @@ class Rdep:
     self.epoch_data = 0
     self.epoch_ret = 0
     self.wait_budget = 0          # 0 = library default (seconds); tests shrink it
+    self.fused_return = True      # False: separate push kernel after the GEMM (kept for A/B tests)
 
   # ---------------------------------------------------------------- building blocks
   def plan(self, eid: torch.Tensor) -> Plan:
@@ -158,6 +159,25 @@ class Rdep:
     L.check(lib.nmoe_rdep_reduce(ctypes.c_void_p(self.slab.local_ptr("ret")), L.ptr(plan.pos), L.ptr(out), plan.T,
                                  plan.K, self.dim, L.stream()), "rdep_reduce")
 
+  def push_args(self, use_gate: bool, rowval: Optional[torch.Tensor] = None) -> dict:
+    """Arguments that make a grouped GEMM's epilogue store its rows straight into the source ranks'
+    return buffers (fused return) instead of a local output."""
+    return {"meta": ctypes.c_void_p(self.slab.local_ptr("meta")), "peer_ret": self.slab.ptrs("ret"),
+            "peer_retg": self.slab.ptrs("retg"), "rowval": rowval, "use_gate": use_gate, "world": self.world}
+
+  def finish_return(self, plan: Plan, out: torch.Tensor) -> None:
+    """After a kernel that pushed rows to the sources: publish, wait for every owner, sum the K slots."""
+    lib = L.lib()
+    st = G.status_buffer(self.device)
+    self.epoch_ret += 1
+    L.check(lib.nmoe_rdep_signal(self.slab.ptrs("ret_flags"), self.rank, self.world, ctypes.c_uint(self.epoch_ret),
+                                 L.stream()), "rdep_signal")
+    L.check(lib.nmoe_rdep_wait(ctypes.c_void_p(self.slab.local_ptr("ret_flags")), self.world,
+                               ctypes.c_uint(self.epoch_ret), ctypes.c_uint(self.wait_budget), L.ptr(st), 421,
+                               L.stream()), "rdep_wait(ret)")
+    L.check(lib.nmoe_rdep_reduce(ctypes.c_void_p(self.slab.local_ptr("ret")), L.ptr(plan.pos), L.ptr(out), plan.T,
+                                 plan.K, self.dim, L.stream()), "rdep_reduce")
+
   def row_gates(self, plan: Plan) -> torch.Tensor:
     out = torch.empty(self.capacity, dtype=torch.float32, device=self.device)
     L.check(L.lib().nmoe_rdep_row_gates(ctypes.c_void_p(self.slab.local_ptr("meta")), L.ptr(plan.n_m_tiles),
@@ -184,9 +204,14 @@ class _MoEFused(torch.autograd.Function):
     rdep.wait_data()
     h13 = G.grouped_gemm(rdep.xbuf, W13, plan.tile_expert, plan.n_m_tiles)
     a = EW.swiglu_rows(h13, plan.n_m_tiles)
-    y = G.grouped_gemm(a, W2, plan.tile_expert, plan.n_m_tiles)
     out = torch.empty_like(x)
-    rdep.push_and_reduce(y, plan, True, None, out)
+    if rdep.fused_return:
+      # down projection whose epilogue multiplies by the gate and stores into the source's (token, slot) rows
+      G.grouped_gemm(a, W2, plan.tile_expert, plan.n_m_tiles, push=rdep.push_args(True))
+      rdep.finish_return(plan, out)
+    else:
+      y = G.grouped_gemm(a, W2, plan.tile_expert, plan.n_m_tiles)
+      rdep.push_and_reduce(y, plan, True, None, out)
     ctx.rdep, ctx.plan = rdep, plan
     ctx.save_for_backward(x, gates32, W13, W2, h13 if save_h13 else None)
     return out
@@ -210,9 +235,13 @@ class _MoEFused(torch.autograd.Function):
     # every reader of the peer-written buffers runs before the kernel that returns rows to the sources
     dW2 = G.grouped_wgrad(rdep.ybuf, a_scaled, plan.offs_pad, rdep.n_local)      # [E, H, Dff]
     dW13 = G.grouped_wgrad(dh13, rdep.xbuf, plan.offs_pad, rdep.n_local)         # [E, 2Dff, H]
-    dxe = G.grouped_gemm(dh13, W13, plan.tile_expert, nt, b_mn=True)
     dx = torch.empty_like(x)
-    rdep.push_and_reduce(dxe, plan, False, rowdot, dx)
+    if rdep.fused_return:
+      G.grouped_gemm(dh13, W13, plan.tile_expert, nt, b_mn=True, push=rdep.push_args(False, rowdot))
+      rdep.finish_return(plan, dx)
+    else:
+      dxe = G.grouped_gemm(dh13, W13, plan.tile_expert, nt, b_mn=True)
+      rdep.push_and_reduce(dxe, plan, False, rowdot, dx)
     dg = rdep.retg[: plan.T * plan.K].clone().view(plan.T, plan.K)
     dg = torch.where(plan.pos.view(plan.T, plan.K) >= 0, dg, torch.zeros_like(dg))
     return None, dx, dg, None, dW13, dW2, None

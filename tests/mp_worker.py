@@ -1,0 +1,131 @@
+"""Multi-rank worker launched by test_multi_gpu.py through torch.distributed.run.
+
+Checks on 2+ GPUs: RDEP MoE forward/backward against the fp32 oracle evaluated over the tokens of
+ALL ranks, fused ZeRO-2 against the NCCL implementation, and a short lockstep training run."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from nmoe_b200 import runtime  # noqa: E402
+from nmoe_b200.ops import tc_gemm as G  # noqa: E402
+
+
+def rel(a, b):
+  return ((a.float() - b.float()).abs().max() / (b.float().abs().max() + 1e-6)).item()
+
+
+def check_moe(rank, world, dev):
+  from nmoe_b200.parallel.rdep import Rdep, moe_reference
+  T, H, F, E, K = 384, 256, 128, 8, 2
+  n_local = E // world
+  g = torch.Generator().manual_seed(7)
+  W13g = (torch.randn(E, 2 * F, H, generator=g) * 0.05).bfloat16()
+  W2g = (torch.randn(E, H, F, generator=g) * 0.05).bfloat16()
+  gr = torch.Generator().manual_seed(100 + rank)
+  x = (torch.randn(T, H, generator=gr) * 0.5).bfloat16()
+  eid = torch.stack([torch.randperm(E, generator=gr)[:K] for _ in range(T)]).int()
+  gates = torch.rand(T, K, generator=gr)
+  gout = torch.randn(T, H, generator=gr).bfloat16()
+  rd = Rdep(H, E, K, T, device=dev)
+  xd = x.to(dev).requires_grad_()
+  gd = gates.to(dev).requires_grad_()
+  W13 = W13g[rank * n_local:(rank + 1) * n_local].to(dev).requires_grad_()
+  W2 = W2g[rank * n_local:(rank + 1) * n_local].to(dev).requires_grad_()
+  for it in range(2):
+    for t in (xd, gd, W13, W2):
+      t.grad = None
+    out = rd.moe(xd, gd, eid.to(dev), W13, W2, bool(it))
+    out.backward(gout.to(dev))
+  torch.cuda.synchronize()
+  G.check_status()
+  # oracle over all ranks' tokens
+  def gather(t):
+    parts = [torch.empty_like(t.to(dev)) for _ in range(world)]
+    dist.all_gather(parts, t.to(dev).contiguous())
+    return torch.cat([p.cpu() for p in parts])
+  xa, ea, ga, goa = gather(x), gather(eid), gather(gates), gather(gout)
+  xf, gf = xa.float().requires_grad_(), ga.clone().requires_grad_()
+  Wf, W2f = W13g.float().requires_grad_(), W2g.float().requires_grad_()
+  ref = moe_reference(xf, gf, ea.long(), Wf, W2f)
+  ref.backward(goa.float())
+  sl = slice(rank * T, (rank + 1) * T)
+  es = slice(rank * n_local, (rank + 1) * n_local)
+  errs = {"out": rel(out.cpu(), ref[sl]), "dx": rel(xd.grad.cpu(), xf.grad[sl]), "dg": rel(gd.grad.cpu(), gf.grad[sl]),
+          "dW13": rel(W13.grad.cpu(), Wf.grad[es]), "dW2": rel(W2.grad.cpu(), W2f.grad[es])}
+  assert all(v < 3e-2 for v in errs.values()), errs
+  rd.close()
+  return errs
+
+
+def check_zero2(rank, world, dev):
+  from nmoe_b200.config import Config
+  from nmoe_b200.parallel.zero2 import Zero2
+  cfg = Config(dim=8, n_layers=1, n_heads=1)
+  results = {}
+  for impl in ("nccl", "fused"):
+    cfg.zero2_impl = impl
+    g = torch.Generator().manual_seed(3)
+    params = [torch.nn.Parameter((torch.randn(n, generator=g)).bfloat16().to(dev)) for n in (1000, 4096, 77, 130000)]
+    z = Zero2([{"name": "dense_decay", "params": params[:2], "lr": 1e-2, "weight_decay": 0.1},
+               {"name": "router", "params": params[2:], "lr": 5e-3, "weight_decay": 0.0}], cfg)
+    assert z.impl == impl
+    for step in range(3):
+      z.zero_grad()
+      gg = torch.Generator().manual_seed(1000 * step + rank)
+      for p in params:
+        p.grad.copy_((torch.randn(p.numel(), generator=gg) * 0.1).bfloat16().view_as(p))
+      z.step()
+    torch.cuda.synchronize()
+    G.check_status()
+    results[impl] = torch.cat([p.detach().float().cpu().view(-1) for p in params])
+    # every rank must hold identical parameters
+    ref = results[impl].to(dev)
+    other = ref.clone()
+    dist.broadcast(other, src=0)
+    assert torch.equal(ref, other), f"{impl}: ranks diverged"
+  err = rel(results["fused"], results["nccl"])
+  assert err < 1e-2, err
+  return err
+
+
+def check_train(rank, world, dev):
+  import math
+  from nmoe_b200.config import Config
+  from nmoe_b200.train import Trainer
+  cfg = Config(vocab_size=1024, eos_token_id=1023, dim=256, n_layers=3, n_heads=4, inter_dim=512, moe_inter_dim=128,
+               n_routed_experts=8, n_activated_experts=2, n_shared_experts=1, n_dense_layers=1, q_lora_rank=96,
+               kv_lora_rank=64, qk_nope_head_dim=32, qk_rope_head_dim=32, v_head_dim=32, batch_size=2 * world,
+               seq_len=128, max_position_embeddings=256, warmup_steps=1, lr_dense=3e-3, lr_expert=3e-3, lr_router=3e-3)
+  torch.manual_seed(11)                      # same dense init on every rank
+  tr = Trainer(cfg, rank=rank, world=world, device=dev)
+  g = torch.Generator().manual_seed(50 + rank)
+  tok = torch.randint(0, 1000, (2, 129), generator=g)
+  x, y = tok[:, :-1].contiguous(), tok[:, 1:].contiguous()
+  losses = [tr.step(x, y).item() for _ in range(8)]
+  G.check_status()
+  assert math.isfinite(losses[0]) and losses[-1] < losses[0] - 0.05, losses
+  # replicated parameters must stay identical across ranks
+  flat = torch.cat([g_.flat_param.float() for g_ in tr.opt.dense.groups])
+  other = flat.clone()
+  dist.broadcast(other, src=0)
+  assert torch.equal(flat, other)
+  tr.model.rdep.close()
+  return losses[0], losses[-1]
+
+
+def main():
+  rank, world, dev = runtime.init(0)
+  out = {"moe": check_moe(rank, world, dev), "zero2": check_zero2(rank, world, dev),
+         "train": check_train(rank, world, dev)}
+  dist.barrier()
+  if rank == 0:
+    print("MP_WORKER_OK", out, flush=True)
+  runtime.finalize()
+
+
+if __name__ == "__main__":
+  main()
