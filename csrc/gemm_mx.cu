@@ -1,0 +1,357 @@
+// Block-scaled FP8 GEMM (MXFP8: E4M3 values, one E8M0 scale per 32 elements of K) on tcgen05:
+// C[M,N] (bf16) = A[M,K] * B[N,K]^T with both operands K-major.  Same structure as the bf16
+// kernel (TMA producer warp, single-thread MMA issuer, 4 epilogue warps, persistent tiles,
+// accumulators in tensor memory); in addition each pipeline stage carries the 512-byte scale
+// atoms of its A and B tiles, which the MMA thread moves from shared to tensor memory with
+// tcgen05.cp right before the four K=32 `kind::mxf8f6f4.block_scale` instructions of the stage.
+//
+// mode 0: dense.  mode 1: rows of A/C are 128-aligned per-expert segments (tile -> expert table,
+// valid tile count on the device), B and its scales are stacked per expert.  The epilogue can
+// push rows straight into the source ranks' RDEP return buffers (see gemm.cu).
+// Requirements: K % 128 == 0; scales in the atom layout of common/sf_layout.cuh.
+//
+// Replaces the reference's CuTe-DSL grouped block-scaled kernel (nmoe/blockscaled/grouped.py:545-2093).
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#include "common/ptx.cuh"
+#include "common/tensormap.h"
+
+namespace nmoe {
+
+constexpr int MX_BM = 128;
+constexpr int MX_BK = 128;               // bytes == elements for fp8; one 128-byte swizzle span
+constexpr int kMxThreads = 192;
+constexpr int kMxGroupM = 16;
+constexpr uint64_t kMxWaitBudgetNs = 2000000000ull;
+
+struct MxParams {
+  int M, N, K, E;
+  const int* tile_expert;
+  const int* n_m_tiles;
+  __nv_bfloat16* C;
+  long long ldc;
+  const uint8_t* sfa;          // A scales, atoms [M/128][K/128]
+  const uint8_t* sfb;          // B scales, atoms [(E*N)/128][K/128]
+  StatusRecord* status;
+  const int4* row_meta;
+  __nv_bfloat16* peer_ret[8];
+  int push_use_gate;
+};
+
+NMOE_DEVICE uint64_t mx_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+NMOE_DEVICE bool mx_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = mx_timer_ns();
+  uint32_t it = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++it & 255u) == 0) {
+      if (*abort_flag) return false;
+      if (mx_timer_ns() - t0 > kMxWaitBudgetNs) return false;
+    }
+  }
+  return true;
+}
+// Untiled bulk copy global -> shared completing on an mbarrier (16-byte aligned, size % 16 == 0).
+NMOE_DEVICE void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+
+template <int BN>
+struct MxSmem {
+  static constexpr int kStageA = MX_BM * MX_BK;
+  static constexpr int kStageB = BN * MX_BK;
+  static constexpr int kStageSF = 512 + (BN / 128) * 512;
+  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  static constexpr int kAcc = (BN == 256) ? 1 : 2;
+  static constexpr int kBytes = kStages * (kStageA + kStageB + kStageSF) + 1024 + 256;
+};
+
+template <int BN, int MODE>
+NMOE_DEVICE bool mx_decode(const MxParams& p, int t, int m_tiles, int n_tiles, int& m_blk, int& n_blk, int& expert) {
+  if (t >= m_tiles * n_tiles) return false;
+  const int per_group = kMxGroupM * n_tiles;
+  const int g = t / per_group;
+  const int first_m = g * kMxGroupM;
+  const int gm = min(kMxGroupM, m_tiles - first_m);
+  const int r = t - g * per_group;
+  m_blk = first_m + r % gm;
+  n_blk = r / gm;
+  expert = (MODE == 1) ? p.tile_expert[m_blk] : 0;
+  return true;
+}
+
+template <int BN, int MODE>
+__global__ void __launch_bounds__(kMxThreads, 1)
+k_gemm_mxfp8(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const MxParams p) {
+  using S = MxSmem<BN>;
+  constexpr int kStages = S::kStages;
+  constexpr int kAcc = S::kAcc;
+  constexpr uint32_t kSfaCol = kAcc * BN;
+  constexpr uint32_t kSfbCol = kSfaCol + 4;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = sA + kStages * S::kStageA;
+  uint8_t* sSF = sB + kStages * S::kStageB;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sSF + kStages * S::kStageSF);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + kStages;
+  uint64_t* tmem_full = bars + 2 * kStages;
+  uint64_t* tmem_empty = tmem_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m_tiles = (MODE == 1) ? min(*p.n_m_tiles, (p.M + MX_BM - 1) / MX_BM) : (p.M + MX_BM - 1) / MX_BM;
+  const int n_tiles = (p.N + BN - 1) / BN;
+  const int k_blocks = p.K / MX_BK;
+  const int sf_k_atoms = k_blocks;                  // one atom column per 128 of K
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&tmem_full[b], 1); mbar_init(&tmem_empty[b], 4); }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      tma_prefetch_desc(&tmA);
+      tma_prefetch_desc(&tmB);
+      int stage = 0;
+      uint32_t phase = 0;
+      int m_blk, n_blk, expert;
+      bool ok = true;
+      for (int t = blockIdx.x; ok && mx_decode<BN, MODE>(p, t, m_tiles, n_tiles, m_blk, n_blk, expert); t += gridDim.x) {
+        const int m0 = m_blk * MX_BM, n0 = n_blk * BN;
+        const long long brow = (MODE == 1 ? static_cast<long long>(expert) * p.N : 0) + n0;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mx_wait(&empty[stage], phase ^ 1, abort_flag)) {
+            report_status(p.status, kStatusWaitTimeout, 600, stage, kb);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(&full[stage], S::kStageA + S::kStageB + S::kStageSF);
+          tma_load_2d(sA + stage * S::kStageA, &tmA, &full[stage], kb * MX_BK, m0);
+          tma_load_2d(sB + stage * S::kStageB, &tmB, &full[stage], kb * MX_BK, static_cast<int>(brow));
+          uint8_t* sf_dst = sSF + stage * S::kStageSF;
+          bulk_load(sf_dst, p.sfa + (static_cast<size_t>(m_blk) * sf_k_atoms + kb) * 512, 512, &full[stage]);
+#pragma unroll
+          for (int a = 0; a < BN / 128; ++a)
+            bulk_load(sf_dst + 512 * (a + 1), p.sfb + (static_cast<size_t>(brow / 128 + a) * sf_k_atoms + kb) * 512, 512,
+                      &full[stage]);
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      int m_blk, n_blk, expert;
+      bool ok = true;
+      for (int t = blockIdx.x; ok && mx_decode<BN, MODE>(p, t, m_tiles, n_tiles, m_blk, n_blk, expert); t += gridDim.x) {
+        if (!mx_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag)) {
+          report_status(p.status, kStatusWaitTimeout, 610, acc, t);
+          *abort_flag = 1;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mx_wait(&full[stage], phase, abort_flag)) {
+            report_status(p.status, kStatusWaitTimeout, 611, stage, kb);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_u32(sA + stage * S::kStageA);
+          const uint32_t b_addr = smem_u32(sB + stage * S::kStageB);
+          const uint32_t sf_addr = smem_u32(sSF + stage * S::kStageSF);
+          // scale atoms: 32 rows x 16 bytes, no swizzle, 8-row groups 128 bytes apart
+          tmem_cp_32x128b_warpx4(tmem_base + kSfaCol, make_smem_desc(sf_addr, 0, 128, kSwizzleNone));
+#pragma unroll
+          for (int a = 0; a < BN / 128; ++a)
+            tmem_cp_32x128b_warpx4(tmem_base + kSfbCol + 4 * a,
+                                   make_smem_desc(sf_addr + 512 * (a + 1), 0, 128, kSwizzleNone));
+#pragma unroll
+          for (int j = 0; j < MX_BK / 32; ++j) {
+            const uint64_t a_desc = make_smem_desc(a_addr + j * 32, 0, 1024, kSwizzle128B);
+            const uint64_t b_desc = make_smem_desc(b_addr + j * 32, 0, 1024, kSwizzle128B);
+            const uint32_t idesc = make_idesc_mx(MX_BM, BN, 0, 0, 1, static_cast<uint32_t>(j), static_cast<uint32_t>(j));
+            mma_mxf8f6f4_ss(d_tmem, a_desc, b_desc, idesc, tmem_base + kSfaCol, tmem_base + kSfbCol,
+                            (kb | j) != 0 ? 1u : 0u);
+          }
+          mma_commit(&empty[stage]);
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        mma_commit(&tmem_full[acc]);
+        if (++acc == kAcc) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+    __syncwarp();
+  } else {
+    const int q = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    int m_blk, n_blk, expert;
+    const int m_limit = (MODE == 1) ? m_tiles * MX_BM : p.M;
+    for (int t = blockIdx.x; mx_decode<BN, MODE>(p, t, m_tiles, n_tiles, m_blk, n_blk, expert); t += gridDim.x) {
+      const int row = m_blk * MX_BM + q * 32 + lane;
+      const int n0 = n_blk * BN;
+      bool row_ok = row < m_limit;
+      __nv_bfloat16* dst_row = row_ok ? p.C + static_cast<long long>(row) * p.ldc : nullptr;
+      float gate = 1.f;
+      if (MODE == 1 && p.row_meta != nullptr && row_ok) {
+        const int4 mv = __ldg(p.row_meta + row);
+        row_ok = mv.w != 0;
+        if (row_ok) {
+          dst_row = p.peer_ret[mv.x] + static_cast<long long>(mv.y) * p.ldc;
+          if (p.push_use_gate) gate = __int_as_float(mv.z);
+        }
+      }
+      bool ok = mx_wait(&tmem_full[acc], acc_phase, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) {
+        if (lane == 0) report_status(p.status, kStatusWaitTimeout, 620, acc, t);
+        *abort_flag = 1;
+        break;
+      }
+      tc_fence_after_sync();
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + c * 32, r);
+        tmem_ld_wait();
+        const int col = n0 + c * 32;
+        if (row_ok && col < p.N) {
+          __nv_bfloat16* dst = dst_row + col;
+          if (col + 32 <= p.N) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              int4 v;
+              v.x = pack_bf16x2(__uint_as_float(r[8 * i]) * gate, __uint_as_float(r[8 * i + 1]) * gate);
+              v.y = pack_bf16x2(__uint_as_float(r[8 * i + 2]) * gate, __uint_as_float(r[8 * i + 3]) * gate);
+              v.z = pack_bf16x2(__uint_as_float(r[8 * i + 4]) * gate, __uint_as_float(r[8 * i + 5]) * gate);
+              v.w = pack_bf16x2(__uint_as_float(r[8 * i + 6]) * gate, __uint_as_float(r[8 * i + 7]) * gate);
+              st_relaxed_sys_v4(reinterpret_cast<int4*>(dst) + i, v);
+            }
+          } else {
+            for (int i = 0; i < 32 && col + i < p.N; ++i) dst[i] = __float2bfloat16(__uint_as_float(r[i]) * gate);
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+      if (++acc == kAcc) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+
+  if (*abort_flag) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+  }
+  if (MODE == 1 && p.row_meta != nullptr) __threadfence_system();
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+static int mx_cached_map(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t pitch,
+                         uint32_t box_inner, uint32_t box_outer) {
+  using Key = std::tuple<const void*, uint64_t, uint64_t, uint64_t, uint32_t, uint32_t>;
+  static std::map<Key, CUtensorMap> cache;
+  static std::mutex mu;
+  Key k{base, inner, outer, pitch, box_inner, box_outer};
+  std::lock_guard<std::mutex> g(mu);
+  auto it = cache.find(k);
+  if (it != cache.end()) { *out = it->second; return 0; }
+  int rc = make_tensor_map_2d(out, base, kTmaU8, inner, outer, pitch, box_inner, box_outer, kTmaSwizzle128);
+  if (rc != 0) return rc;
+  if (cache.size() > 4096) cache.clear();
+  cache[k] = *out;
+  return 0;
+}
+
+template <int BN, int MODE>
+static int mx_launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const MxParams& p, int max_tiles, cudaStream_t st) {
+  auto kern = k_gemm_mxfp8<BN, MODE>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, MxSmem<BN>::kBytes);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int grid = max_tiles < sms ? max_tiles : sms;
+  if (grid < 1) return 0;
+  kern<<<grid, kMxThreads, MxSmem<BN>::kBytes, st>>>(tmA, tmB, p);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : static_cast<int>(e);
+}
+
+}  // namespace nmoe
+
+using namespace nmoe;
+
+// A: [a_rows, K] e4m3 bytes, sfa: its scales; B: [b_rows, K] e4m3 (b_rows = N, or E*N for mode 1), sfb likewise.
+// C: bf16 [*, ldc].  mode 1 additionally takes the tile table; row_meta/peer_ret select the fused RDEP return.
+extern "C" int nmoe_gemm_mxfp8(const void* A, const void* sfa, const void* B, const void* sfb, void* C, int M, int N,
+                               int K, long long ldc, int mode, int E, const int* tile_expert, const int* n_m_tiles,
+                               long long a_rows, long long b_rows, int bn, void* status, const void* row_meta,
+                               void* const* peer_ret, int push_use_gate, int world, cudaStream_t st) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || (K % MX_BK) != 0) return -1;
+  if (mode == 1 && (N % 128) != 0) return -2;
+  if (bn == 0) bn = (N % 256 == 0) ? 256 : 128;
+  if (bn != 128 && bn != 256) return -5;
+  MxParams p;
+  p.M = M; p.N = N; p.K = K; p.E = E; p.tile_expert = tile_expert; p.n_m_tiles = n_m_tiles;
+  p.C = static_cast<__nv_bfloat16*>(C); p.ldc = ldc;
+  p.sfa = static_cast<const uint8_t*>(sfa); p.sfb = static_cast<const uint8_t*>(sfb);
+  p.status = static_cast<StatusRecord*>(status);
+  p.row_meta = static_cast<const int4*>(row_meta); p.push_use_gate = push_use_gate;
+  for (int r = 0; r < 8; ++r)
+    p.peer_ret[r] = (row_meta && peer_ret && r < world) ? static_cast<__nv_bfloat16*>(peer_ret[r]) : nullptr;
+  if (row_meta && mode != 1) return -6;
+  CUtensorMap tmA, tmB;
+  int rc = mx_cached_map(&tmA, A, K, a_rows, K, MX_BK, MX_BM);
+  if (rc != 0) return rc;
+  rc = mx_cached_map(&tmB, B, K, b_rows, K, MX_BK, bn);
+  if (rc != 0) return rc;
+  const int max_tiles = ((M + MX_BM - 1) / MX_BM) * ((N + bn - 1) / bn);
+  if (bn == 256) return mode == 1 ? mx_launch<256, 1>(tmA, tmB, p, max_tiles, st) : mx_launch<256, 0>(tmA, tmB, p, max_tiles, st);
+  return mode == 1 ? mx_launch<128, 1>(tmA, tmB, p, max_tiles, st) : mx_launch<128, 0>(tmA, tmB, p, max_tiles, st);
+}

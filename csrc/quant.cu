@@ -1,0 +1,166 @@
+// Block-scaled quantisation: bf16 -> E4M3 with one E8M0 scale per 32 elements (MXFP8), scales
+// written directly in the tensor-core atom layout (common/sf_layout.cuh); fused SwiGLU + quantise
+// for the activation between the two expert GEMMs; dequantise for tests; E2M1 (4-bit) packing.
+// One warp per row, each lane owns one 32-element block at a time (64-byte loads, 32-byte stores).
+// Reference counterparts: nmoe/csrc/quant.cu:118-250 (quantise), :456-760 (SwiGLU+quantise),
+// :51,1772 (dequantise).
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "common/quant_dev.cuh"
+
+namespace nmoe {
+
+// x[M,K] bf16 -> q[M,K] e4m3, sf in atom layout with sf_cols = K/32 padded to a multiple of 4.
+// rows_per_group > 0: the matrix is a stack of groups (experts) of that many rows, each with its
+// own atom region (rows_per_group must be a multiple of 128).
+__global__ void __launch_bounds__(256)
+k_quant_mxfp8(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q, uint8_t* __restrict__ sf, long long M,
+              int K, int sf_cols_padded, const int* __restrict__ n_tiles_dev) {
+  if (n_tiles_dev != nullptr) M = min(M, static_cast<long long>(*n_tiles_dev) * 128);
+  const long long row = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  if (row >= M) return;
+  const int lane = threadIdx.x & 31;
+  const int nblk = K >> 5;
+  for (int b = lane; b < nblk; b += 32) {
+    float v[32];
+    load_block_bf16(x + row * K + b * 32, v);
+    const uint8_t s = quant_block_e4m3(v, q + row * K + b * 32);
+    sf[sf_mma_offset(static_cast<int>(row), b, sf_cols_padded)] = s;
+  }
+}
+
+// h13[M,2F] (gate even / up odd) -> a = silu(gate)*up quantised to e4m3 [M,F] + scales; optional bf16 copy.
+__global__ void __launch_bounds__(256)
+k_swiglu_quant_mxfp8(const __nv_bfloat16* __restrict__ h13, uint8_t* __restrict__ q, uint8_t* __restrict__ sf,
+                     long long M, int F, int sf_cols_padded, const int* __restrict__ n_tiles_dev) {
+  if (n_tiles_dev != nullptr) M = min(M, static_cast<long long>(*n_tiles_dev) * 128);
+  const long long row = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  if (row >= M) return;
+  const int lane = threadIdx.x & 31;
+  const int nblk = F >> 5;
+  for (int b = lane; b < nblk; b += 32) {
+    float v[32];
+    const __nv_bfloat16* src = h13 + row * 2 * F + b * 64;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int4 p = ld_nc_v4(reinterpret_cast<const int4*>(src) + i);
+      const float2 a = unpack_bf16x2(p.x), bb = unpack_bf16x2(p.y), c = unpack_bf16x2(p.z), d = unpack_bf16x2(p.w);
+      // round through bf16 like the unfused path (swiglu writes bf16, then quantise reads it)
+      v[4 * i] = __bfloat162float(__float2bfloat16(a.x / (1.f + __expf(-a.x)) * a.y));
+      v[4 * i + 1] = __bfloat162float(__float2bfloat16(bb.x / (1.f + __expf(-bb.x)) * bb.y));
+      v[4 * i + 2] = __bfloat162float(__float2bfloat16(c.x / (1.f + __expf(-c.x)) * c.y));
+      v[4 * i + 3] = __bfloat162float(__float2bfloat16(d.x / (1.f + __expf(-d.x)) * d.y));
+    }
+    const uint8_t s = quant_block_e4m3(v, q + row * F + b * 32);
+    sf[sf_mma_offset(static_cast<int>(row), b, sf_cols_padded)] = s;
+  }
+}
+
+__global__ void k_dequant_mxfp8(const uint8_t* __restrict__ q, const uint8_t* __restrict__ sf,
+                                __nv_bfloat16* __restrict__ out, long long M, int K, int sf_cols_padded) {
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= M * K) return;
+  const long long row = i / K;
+  const int col = static_cast<int>(i - row * K);
+  const uint8_t s = sf[sf_mma_offset(static_cast<int>(row), col >> 5, sf_cols_padded)];
+  const __half_raw h = __nv_cvt_fp8_to_halfraw(q[i], __NV_E4M3);
+  const float f = __half2float(*reinterpret_cast<const __half*>(&h)) * exp2f(static_cast<float>(s) - 127.f);
+  out[i] = __float2bfloat16(f);
+}
+
+// E2M1 (4-bit) with E8M0 scales per 32 elements: two values per byte, low nibble = even element.
+NMOE_DEVICE uint32_t e2m1_code(float x) {
+  const float a = fabsf(x);
+  uint32_t c;
+  // round to nearest, ties to even mantissa bit: grid 0,.5,1,1.5,2,3,4,6
+  if (a <= 0.25f) c = 0;
+  else if (a < 0.75f) c = 1;
+  else if (a <= 1.25f) c = 2;
+  else if (a < 1.75f) c = 3;
+  else if (a <= 2.5f) c = 4;
+  else if (a < 3.5f) c = 5;
+  else if (a <= 5.f) c = 6;
+  else c = 7;
+  return c | (x < 0.f ? 8u : 0u);
+}
+__global__ void __launch_bounds__(256)
+k_quant_mxfp4(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q, uint8_t* __restrict__ sf, long long M,
+              int K, int sf_cols_padded) {
+  const long long row = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  if (row >= M) return;
+  const int lane = threadIdx.x & 31;
+  for (int b = lane; b < (K >> 5); b += 32) {
+    float v[32];
+    load_block_bf16(x + row * K + b * 32, v);
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(v[i]));
+    const uint8_t s = e8m0_from_amax(amax, kInvFp4Max);
+    const float inv = e8m0_inv_scale(s);
+    uint32_t w[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int i = 0; i < 32; ++i) w[i >> 3] |= e2m1_code(v[i] * inv) << ((i & 7) * 4);
+    *reinterpret_cast<int4*>(q + row * (K >> 1) + b * 16) = make_int4(w[0], w[1], w[2], w[3]);
+    sf[sf_mma_offset(static_cast<int>(row), b, sf_cols_padded)] = s;
+  }
+}
+
+}  // namespace nmoe
+
+using namespace nmoe;
+#define CHECK_LAUNCH() do { cudaError_t e_ = cudaGetLastError(); if (e_ != cudaSuccess) return static_cast<int>(e_); } while (0)
+
+extern "C" {
+
+// Bytes of the scale buffer for [M,K] (M padded to 128 rows, K/32 padded to 4 columns).
+long long nmoe_sf_bytes(long long M, int K) {
+  const long long mt = (M + 127) / 128;
+  const long long kt = ((K / 32) + 3) / 4;
+  return mt * kt * 512;
+}
+
+int nmoe_quant_mxfp8(const void* x, void* q, void* sf, long long M, int K, const int* n_tiles_dev, cudaStream_t st) {
+  if (M == 0) return 0;
+  if (K % 32 != 0) return -1;
+  const int sfc = ((K / 32) + 3) & ~3;
+  k_quant_mxfp8<<<static_cast<unsigned>((M + 7) / 8), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x),
+      static_cast<uint8_t*>(q), static_cast<uint8_t*>(sf), M, K, sfc, n_tiles_dev);
+  CHECK_LAUNCH();
+  return 0;
+}
+
+int nmoe_swiglu_quant_mxfp8(const void* h13, void* q, void* sf, long long M, int F, const int* n_tiles_dev,
+                            cudaStream_t st) {
+  if (M == 0) return 0;
+  if (F % 32 != 0) return -1;
+  const int sfc = ((F / 32) + 3) & ~3;
+  k_swiglu_quant_mxfp8<<<static_cast<unsigned>((M + 7) / 8), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(h13),
+      static_cast<uint8_t*>(q), static_cast<uint8_t*>(sf), M, F, sfc, n_tiles_dev);
+  CHECK_LAUNCH();
+  return 0;
+}
+
+int nmoe_dequant_mxfp8(const void* q, const void* sf, void* out, long long M, int K, cudaStream_t st) {
+  if (M == 0) return 0;
+  const int sfc = ((K / 32) + 3) & ~3;
+  const long long n = M * K;
+  k_dequant_mxfp8<<<static_cast<unsigned>((n + 255) / 256), 256, 0, st>>>(static_cast<const uint8_t*>(q),
+      static_cast<const uint8_t*>(sf), static_cast<__nv_bfloat16*>(out), M, K, sfc);
+  CHECK_LAUNCH();
+  return 0;
+}
+
+int nmoe_quant_mxfp4(const void* x, void* q, void* sf, long long M, int K, cudaStream_t st) {
+  if (M == 0) return 0;
+  if (K % 32 != 0) return -1;
+  const int sfc = ((K / 32) + 3) & ~3;
+  k_quant_mxfp4<<<static_cast<unsigned>((M + 7) / 8), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x),
+      static_cast<uint8_t*>(q), static_cast<uint8_t*>(sf), M, K, sfc);
+  CHECK_LAUNCH();
+  return 0;
+}
+
+}  // extern "C"

@@ -24,6 +24,7 @@
 #include <stdint.h>
 
 #include "common/ptx.cuh"
+#include "common/quant_dev.cuh"
 
 namespace nmoe {
 
@@ -254,6 +255,91 @@ __global__ void __launch_bounds__(256) k_rdep_place(const PlaceArgs a) {
   }
 }
 
+// ------------------------------------------------------------------ place (quantising)
+// Same placement, but each row is quantised in registers to MXFP8 (E4M3 + one E8M0 scale per 32
+// elements) and what crosses NVLink is H bytes of values plus H/32 scale bytes, written straight
+// into the owner's GEMM-ready buffers: values row-major, scales at their tensor-core atom offsets
+// (four scale bytes per 4-byte store).  Padding rows of the owner's segments get zero values and
+// unit scales so that they stay finite through the expert MLP.
+struct PlaceMxArgs {
+  PlaceArgs base;
+  uint8_t* peer_xq[kMaxRanks];     // [capacity, H] e4m3
+  uint8_t* peer_sf[kMaxRanks];     // atoms [capacity/128][H/128]
+  int sf_cols_padded;
+};
+
+__global__ void __launch_bounds__(256) k_rdep_place_mx(const PlaceMxArgs am) {
+  const PlaceArgs& a = am.base;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row_blocks = gridDim.x - a.pad_blocks;
+  const int nblk = a.H >> 5;
+  if (static_cast<int>(blockIdx.x) < row_blocks) {
+    const int n_pairs = a.T * a.K;
+    for (int i = blockIdx.x * 8 + warp; i < n_pairs; i += row_blocks * 8) {
+      const int e = a.eid[i];
+      const int rb = a.rank_in_block[i];
+      int pos = -1, owner = 0;
+      if (e >= 0 && e < a.E && rb >= 0 && a.base[e] >= 0) {
+        owner = e / a.n_local;
+        pos = a.base[e] + a.block_prefix[(i / kCountThreads) * a.E + e] + rb;
+      }
+      if (lane == 0) a.pos_out[i] = pos;
+      if (pos < 0) continue;
+      const int tok = i / a.K;
+      const __nv_bfloat16* src = a.x + static_cast<size_t>(tok) * a.H;
+      uint8_t* qdst = am.peer_xq[owner] + static_cast<size_t>(pos) * a.H;
+      uint8_t* sfdst = am.peer_sf[owner];
+      for (int b0 = 0; b0 < nblk; b0 += 32) {
+        const int b = b0 + lane;
+        uint32_t s = 127;
+        if (b < nblk) {
+          float v[32];
+          uint32_t w[8];
+          load_block_bf16(src + b * 32, v);
+          s = quant_block_e4m3_regs(v, w);
+          st_relaxed_sys_v4(qdst + b * 32, make_int4(w[0], w[1], w[2], w[3]));
+          st_relaxed_sys_v4(qdst + b * 32 + 16, make_int4(w[4], w[5], w[6], w[7]));
+        }
+        uint32_t packed = s | (__shfl_down_sync(0xffffffffu, s, 1) << 8) | (__shfl_down_sync(0xffffffffu, s, 2) << 16) |
+                          (__shfl_down_sync(0xffffffffu, s, 3) << 24);
+        if ((lane & 3) == 0 && b < nblk)
+          asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(sfdst + sf_mma_offset(pos, b, am.sf_cols_padded)),
+                       "r"(packed) : "memory");
+      }
+      if (lane == 0 && a.peer_meta[owner] != nullptr) {
+        int4 m;
+        m.x = a.rank; m.y = i; m.z = __float_as_int(a.gates ? a.gates[i] : 1.f); m.w = 1;
+        st_relaxed_sys_v4(a.peer_meta[owner] + pos, m);
+      }
+    }
+  } else {
+    const int pb = blockIdx.x - row_blocks;
+    for (int le = 0; le < a.n_local; ++le) {
+      const int r0 = a.offs_pad[le] + a.seg_rows[le];
+      const int r1 = a.offs_pad[le + 1];
+      for (int r = r0 + pb * 8 + warp; r < r1; r += a.pad_blocks * 8) {
+        int4* dst = reinterpret_cast<int4*>(am.peer_xq[a.rank] + static_cast<size_t>(r) * a.H);
+        for (int c = lane; c < (a.H >> 4); c += 32) dst[c] = make_int4(0, 0, 0, 0);
+        for (int b = lane * 4; b < nblk; b += 128)
+          *reinterpret_cast<uint32_t*>(am.peer_sf[a.rank] + sf_mma_offset(r, b, am.sf_cols_padded)) = 0x7f7f7f7fu;
+        if (lane == 0 && a.peer_meta[a.rank] != nullptr)
+          *reinterpret_cast<int4*>(a.peer_meta[a.rank] + r) = make_int4(a.rank, 0, 0, 0);
+      }
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  __shared__ int s_last;
+  if (threadIdx.x == 0) s_last = (atomicAdd(a.done_counter, 1) == static_cast<int>(gridDim.x) - 1);
+  __syncthreads();
+  if (s_last) {
+    __threadfence_system();
+    if (threadIdx.x < a.world)
+      st_release_sys_u32(a.peer_data_flags[threadIdx.x] + a.rank, static_cast<uint32_t>(a.epoch));
+    if (threadIdx.x == 0) *a.done_counter = 0;
+  }
+}
+
 // ------------------------------------------------------------------ flags
 // Release `epoch` into entry `rank` of every peer's flag array (used after a kernel whose
 // stores to peers must be visible, e.g. the return push of the last GEMM).
@@ -415,6 +501,37 @@ int nmoe_rdep_place(int rank, int world, int E, int n_local, int T, int K, int H
   if (row_blocks > 148 * 8) row_blocks = 148 * 8;
   if (row_blocks < 1) row_blocks = 1;
   k_rdep_place<<<row_blocks + a.pad_blocks, 256, 0, st>>>(a);
+  CHECK_LAUNCH();
+  return 0;
+}
+
+// Quantising placement: x rows -> owner's e4m3 buffer peer_xq + scale atoms peer_sf (see k_rdep_place_mx).
+int nmoe_rdep_place_mx(int rank, int world, int E, int n_local, int T, int K, int H, int epoch, const void* x,
+                       const int* eid, const float* gates, const int* rank_in_block, const int* block_prefix,
+                       const int* base, void* const* peer_xq, void* const* peer_sf, void* const* peer_meta,
+                       void* const* peer_data_flags, int* pos_out, const int* offs_pad, const int* seg_rows,
+                       int* done_counter, void* status, cudaStream_t st) {
+  if (world > kMaxRanks || (H % 128) != 0) return -1;
+  PlaceMxArgs am;
+  PlaceArgs& a = am.base;
+  a.rank = rank; a.world = world; a.E = E; a.n_local = n_local; a.T = T; a.K = K; a.H = H; a.epoch = epoch;
+  a.x = static_cast<const __nv_bfloat16*>(x); a.eid = eid; a.gates = gates; a.rank_in_block = rank_in_block;
+  a.block_prefix = block_prefix; a.base = base;
+  for (int r = 0; r < world; ++r) {
+    a.peer_x[r] = nullptr;
+    am.peer_xq[r] = static_cast<uint8_t*>(peer_xq[r]);
+    am.peer_sf[r] = static_cast<uint8_t*>(peer_sf[r]);
+    a.peer_meta[r] = peer_meta ? static_cast<RdepMeta*>(peer_meta[r]) : nullptr;
+    a.peer_data_flags[r] = static_cast<uint32_t*>(peer_data_flags[r]);
+  }
+  am.sf_cols_padded = ((H / 32) + 3) & ~3;
+  a.pos_out = pos_out; a.owner_out = nullptr; a.offs_pad = offs_pad; a.seg_rows = seg_rows;
+  a.done_counter = done_counter; a.pad_blocks = 16; a.status = static_cast<StatusRecord*>(status);
+  const int n_pairs = T * K;
+  int row_blocks = (n_pairs + 7) / 8;
+  if (row_blocks > 148 * 8) row_blocks = 148 * 8;
+  if (row_blocks < 1) row_blocks = 1;
+  k_rdep_place_mx<<<row_blocks + a.pad_blocks, 256, 0, st>>>(am);
   CHECK_LAUNCH();
   return 0;
 }

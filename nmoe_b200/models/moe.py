@@ -54,6 +54,8 @@ class MoE(nn.Module):
     self.shared = MLP(self.dim, cfg.n_shared_experts * self.inter, dtype) if cfg.n_shared_experts else None
     self.register_buffer("loads", torch.zeros(cfg.n_routed_experts, dtype=torch.int32), persistent=False)
     self.save_h13 = False
+    self.expert_dtype = cfg.dtype
+    self._wcache = None
 
   def init_weights(self, init_std: float = 0.02) -> None:
     for W in (self.W13, self.W2):
@@ -66,7 +68,13 @@ class MoE(nn.Module):
     X = x.reshape(-1, x.size(-1))
     gates, eid = self.router(X, self.loads)
     if X.is_cuda:
-      out = self.rdep.moe(X, gates, eid, self.W13, self.W2, self.save_h13)
+      wq = None
+      if self.expert_dtype != "bf16":
+        if self._wcache is None:
+          from ..ops.quant import ExpertWeightCache
+          self._wcache = ExpertWeightCache()
+        wq = self._wcache.get(self.W13, self.W2)
+      out = self.rdep.moe(X, gates, eid, self.W13, self.W2, self.save_h13, wq)
     else:
       out = rdep_mod.moe_reference(X, gates, eid, self.W13, self.W2)
     if self.shared is not None:

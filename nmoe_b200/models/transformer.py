@@ -86,7 +86,8 @@ class Transformer(nn.Module):
     on_cuda = device is not None and torch.device(device).type == "cuda"
     if cfg.has_moe and on_cuda and rdep is None:
       tpr = tokens_per_rank or max(1, cfg.batch_size // world) * cfg.seq_len
-      rdep = Rdep(cfg.dim, cfg.n_routed_experts, cfg.n_activated_experts, tpr, device=torch.device(device))
+      rdep = Rdep(cfg.dim, cfg.n_routed_experts, cfg.n_activated_experts, tpr, device=torch.device(device),
+                  profile=cfg.dtype)
     self.rdep = rdep
     with torch.device(device or "cpu"):
       self.embedding = nn.Parameter(torch.empty(cfg.vocab_size, cfg.dim, dtype=dtype))

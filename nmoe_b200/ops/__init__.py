@@ -6,3 +6,4 @@ from .optim import adamw_flat_, sumsq
 from .router import router_bias_update_, router_topk
 from .attention import attention
 from .ce import lm_head_loss
+from .quant import dequant_mxfp8, gemm_mxfp8, grouped_gemm_mxfp8, quant_mxfp4, quant_mxfp8, swiglu_quant_mxfp8

@@ -1,0 +1,130 @@
+"""Block-scaled quantisation ops and the MXFP8 tensor-core GEMM (``csrc/quant.cu``, ``csrc/gemm_mx.cu``).
+
+MXFP8 = E4M3 values + one E8M0 (power-of-two) scale per 32 elements along K; scales live in the
+128x4 atom layout that block-scaled ``tcgen05.mma`` consumes.  CPU tensors use the bit-exact
+emulation in ``nmoe_b200.ref.quant``.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from ..ref import quant as RQ
+from . import _lib as L
+from .tc_gemm import status_buffer
+
+
+def sf_bytes(M: int, K: int) -> int:
+  return ((M + 127) // 128) * (((K // 32) + 3) // 4) * 512
+
+
+def quant_mxfp8(x: torch.Tensor, n_tiles: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+  """x [M,K] bf16 -> (q uint8 [M,K] holding e4m3 bytes, sf uint8 flat buffer in atom layout)."""
+  M, K = x.shape
+  if not x.is_cuda:
+    q, sf = RQ.quant_mxfp8(x.float())
+    Mp = (M + 127) // 128 * 128
+    sfp = torch.full((Mp, ((K // 32) + 3) // 4 * 4), 127, dtype=torch.uint8)
+    sfp[:M, :K // 32] = sf
+    return q.view(torch.uint8), RQ.sf_to_mma_layout(sfp)
+  q = torch.empty(M, K, dtype=torch.uint8, device=x.device)
+  sf = torch.full((sf_bytes(M, K),), 127, dtype=torch.uint8, device=x.device)
+  L.check(L.lib().nmoe_quant_mxfp8(L.ptr(x.contiguous()), L.ptr(q), L.ptr(sf), L.c_ll(M), K, L.ptr(n_tiles), L.stream()),
+          "quant_mxfp8")
+  return q, sf
+
+
+def dequant_mxfp8(q: torch.Tensor, sf: torch.Tensor) -> torch.Tensor:
+  M, K = q.shape
+  if not q.is_cuda:
+    Mp = (M + 127) // 128 * 128
+    s = RQ.sf_from_mma_layout(sf, Mp, ((K // 32) + 3) // 4 * 4)[:M, :K // 32]
+    return RQ.dequant_mxfp8(q.view(torch.float8_e4m3fn), s).to(torch.bfloat16)
+  out = torch.empty(M, K, dtype=torch.bfloat16, device=q.device)
+  L.check(L.lib().nmoe_dequant_mxfp8(L.ptr(q), L.ptr(sf), L.ptr(out), L.c_ll(M), K, L.stream()), "dequant_mxfp8")
+  return out
+
+
+def swiglu_quant_mxfp8(h13: torch.Tensor, n_tiles: Optional[torch.Tensor] = None):
+  """h13 [M,2F] (gate even / up odd) -> quantised silu(gate)*up: (q [M,F], sf atoms)."""
+  M, F2 = h13.shape
+  F = F2 // 2
+  q = torch.empty(M, F, dtype=torch.uint8, device=h13.device)
+  sf = torch.empty(sf_bytes(M, F), dtype=torch.uint8, device=h13.device)
+  L.check(L.lib().nmoe_swiglu_quant_mxfp8(L.ptr(h13), L.ptr(q), L.ptr(sf), L.c_ll(M), F, L.ptr(n_tiles), L.stream()),
+          "swiglu_quant_mxfp8")
+  return q, sf
+
+
+def quant_mxfp4(x: torch.Tensor):
+  """x [M,K] bf16 -> (packed uint8 [M,K/2] E2M1 nibbles, sf atoms with E8M0 per 32)."""
+  M, K = x.shape
+  if not x.is_cuda:
+    q, sf = RQ.quant_mxfp4(x.float())
+    Mp = (M + 127) // 128 * 128
+    sfp = torch.full((Mp, ((K // 32) + 3) // 4 * 4), 127, dtype=torch.uint8)
+    sfp[:M, :K // 32] = sf
+    return q, RQ.sf_to_mma_layout(sfp)
+  q = torch.empty(M, K // 2, dtype=torch.uint8, device=x.device)
+  sf = torch.full((sf_bytes(M, K),), 127, dtype=torch.uint8, device=x.device)
+  L.check(L.lib().nmoe_quant_mxfp4(L.ptr(x.contiguous()), L.ptr(q), L.ptr(sf), L.c_ll(M), K, L.stream()), "quant_mxfp4")
+  return q, sf
+
+
+def gemm_mxfp8(aq: torch.Tensor, asf: torch.Tensor, bq: torch.Tensor, bsf: torch.Tensor, *,
+               out: Optional[torch.Tensor] = None, bn: int = 0) -> torch.Tensor:
+  """C[M,N] bf16 = dequant(A)[M,K] @ dequant(B)[N,K]^T on the block-scaled tensor-core path."""
+  M, K = aq.shape
+  N = bq.size(0)
+  if out is None:
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=aq.device)
+  st = status_buffer(aq.device)
+  L.check(L.lib().nmoe_gemm_mxfp8(L.ptr(aq), L.ptr(asf), L.ptr(bq), L.ptr(bsf), L.ptr(out), M, N, K,
+                                  L.c_ll(out.stride(0)), 0, 1, None, None, L.c_ll(M), L.c_ll(N), bn, L.ptr(st), None,
+                                  None, 0, 0, L.stream()), "gemm_mxfp8")
+  return out
+
+
+def grouped_gemm_mxfp8(aq: torch.Tensor, asf: torch.Tensor, bq: torch.Tensor, bsf: torch.Tensor,
+                       tile_expert: torch.Tensor, n_m_tiles: torch.Tensor, *, out: Optional[torch.Tensor] = None,
+                       bn: int = 0, push: Optional[dict] = None) -> Optional[torch.Tensor]:
+  """Rows of aq [Mcap,K] are 128-aligned expert segments; bq [E,N,K] with stacked scale atoms."""
+  Mcap, K = aq.shape
+  E, N = bq.size(0), bq.size(1)
+  st = status_buffer(aq.device)
+  if push is not None:
+    L.check(L.lib().nmoe_gemm_mxfp8(L.ptr(aq), L.ptr(asf), L.ptr(bq), L.ptr(bsf), None, Mcap, N, K, L.c_ll(N), 1, E,
+                                    L.ptr(tile_expert), L.ptr(n_m_tiles), L.c_ll(Mcap), L.c_ll(E * N), bn, L.ptr(st),
+                                    push["meta"], push["peer_ret"], int(push["use_gate"]), push["world"], L.stream()),
+            "grouped_gemm_mxfp8(push)")
+    return None
+  if out is None:
+    out = torch.empty(Mcap, N, dtype=torch.bfloat16, device=aq.device)
+  L.check(L.lib().nmoe_gemm_mxfp8(L.ptr(aq), L.ptr(asf), L.ptr(bq), L.ptr(bsf), L.ptr(out), Mcap, N, K,
+                                  L.c_ll(out.stride(0)), 1, E, L.ptr(tile_expert), L.ptr(n_m_tiles), L.c_ll(Mcap),
+                                  L.c_ll(E * N), bn, L.ptr(st), None, None, 0, 0, L.stream()), "grouped_gemm_mxfp8")
+  return out
+
+
+class ExpertWeightCache:
+  """MXFP8 copies of the expert weights, re-quantised whenever the bf16 masters change
+  (detected through the tensors' version counters; the reference rebuilds its cache after every
+  optimizer step, nmoe/opt.py:118-125)."""
+
+  def __init__(self):
+    self.ver = (-1, -1)
+    self.W13q = self.W13sf = self.W2q = self.W2sf = None
+
+  @torch.no_grad()
+  def get(self, W13: torch.Tensor, W2: torch.Tensor):
+    ver = (W13._version, W2._version)
+    if ver != self.ver or self.W13q is None:
+      E, N13, H = W13.shape
+      q, self.W13sf = quant_mxfp8(W13.detach().view(E * N13, H))
+      self.W13q = q.view(E, N13, H)
+      _, H2, F = W2.shape
+      q2, self.W2sf = quant_mxfp8(W2.detach().view(E * H2, F))
+      self.W2q = q2.view(E, H2, F)
+      self.ver = ver
+    return self.W13q, self.W13sf, self.W2q, self.W2sf

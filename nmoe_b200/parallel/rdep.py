@@ -63,7 +63,8 @@ class Rdep:
   """Shared by all MoE layers of a model: peer slab, scratch, epochs."""
 
   def __init__(self, dim: int, n_experts: int, topk: int, max_tokens: int, *, capacity_factor: float = 2.0,
-               group: Optional[dist.ProcessGroup] = None, device: Optional[torch.device] = None):
+               group: Optional[dist.ProcessGroup] = None, device: Optional[torch.device] = None,
+               profile: str = "bf16"):
     self.world = dist.get_world_size(group) if dist.is_initialized() else 1
     self.rank = dist.get_rank(group) if dist.is_initialized() else 0
     assert n_experts % self.world == 0
@@ -83,7 +84,14 @@ class Rdep:
       ("counts", self.world * self.E * 4), ("count_flags", 64), ("data_flags", 64), ("ret_flags", 64),
       ("ret", pairs * H * 2), ("retg", pairs * 4),
     ]
+    self.profile = profile
+    if profile != "bf16":
+      from ..ops.quant import sf_bytes
+      regions += [("xq", self.capacity * H), ("sfa", sf_bytes(self.capacity, H))]
     self.slab = PeerSlab(regions, group)
+    if profile != "bf16":
+      self.xq = self.slab.local("xq", torch.uint8, (self.capacity, H))
+      self.sfa = self.slab.local("sfa", torch.uint8, (sf_bytes(self.capacity, H),))
     self.xbuf = self.slab.local("x", torch.bfloat16, (self.capacity, H))
     self.ybuf = self.slab.local("y", torch.bfloat16, (self.capacity, H))
     self.ret = self.slab.local("ret", torch.bfloat16, (pairs, H))
@@ -136,6 +144,17 @@ class Rdep:
       L.ptr(plan.pos), None, L.ptr(plan.offs_pad), L.ptr(plan.seg_rows), L.ptr(self.done_counter), L.ptr(st),
       L.stream()), "rdep_place")
 
+  def place_mx(self, x: torch.Tensor, plan: Plan, gates: Optional[torch.Tensor]) -> None:
+    """Quantise x's rows to MXFP8 in the placement kernel and store values + scales into the owners' buffers."""
+    self.epoch_data += 1
+    st = G.status_buffer(x.device)
+    L.check(L.lib().nmoe_rdep_place_mx(
+      self.rank, self.world, self.E, self.n_local, plan.T, plan.K, self.dim, self.epoch_data, L.ptr(x),
+      L.ptr(plan.eid), L.ptr(gates), L.ptr(plan.rank_in_block), L.ptr(plan.block_prefix), L.ptr(plan.base),
+      self.slab.ptrs("xq"), self.slab.ptrs("sfa"), self.slab.ptrs("meta"), self.slab.ptrs("data_flags"),
+      L.ptr(plan.pos), L.ptr(plan.offs_pad), L.ptr(plan.seg_rows), L.ptr(self.done_counter), L.ptr(st),
+      L.stream()), "rdep_place_mx")
+
   def wait_data(self) -> None:
     st = G.status_buffer(self.device)
     L.check(L.lib().nmoe_rdep_wait(ctypes.c_void_p(self.slab.local_ptr("data_flags")), self.world,
@@ -186,9 +205,13 @@ class Rdep:
 
   # ---------------------------------------------------------------- differentiable MoE
   def moe(self, x: torch.Tensor, gates: torch.Tensor, eid: torch.Tensor, W13: torch.Tensor, W2: torch.Tensor,
-          save_h13: bool = False) -> torch.Tensor:
-    """out[t] = sum_k gates[t,k] * Expert_{eid[t,k]}(x[t]); x [T,H] bf16, gates fp32 [T,K], eid [T,K]."""
-    return _MoEFused.apply(self, x, gates, eid, W13, W2, save_h13)
+          save_h13: bool = False, wq: Optional[tuple] = None) -> torch.Tensor:
+    """out[t] = sum_k gates[t,k] * Expert_{eid[t,k]}(x[t]); x [T,H] bf16, gates fp32 [T,K], eid [T,K].
+
+    ``wq`` = (W13q, W13sf, W2q, W2sf) selects the block-scaled FP8 forward (tokens are quantised inside
+    the placement kernel, both expert GEMMs run on the MXFP8 tensor-core path); the backward stays
+    bf16 with a straight-through estimator, like the reference (nmoe/moe.py:404-415)."""
+    return _MoEFused.apply(self, x, gates, eid, W13, W2, save_h13, wq)
 
   def close(self) -> None:
     self.slab.close()
@@ -196,15 +219,27 @@ class Rdep:
 
 class _MoEFused(torch.autograd.Function):
   @staticmethod
-  def forward(ctx, rdep: Rdep, x, gates, eid, W13, W2, save_h13):
+  def forward(ctx, rdep: Rdep, x, gates, eid, W13, W2, save_h13, wq=None):
     x = x.contiguous()
     gates32 = gates.detach().float().contiguous()
     plan = rdep.plan(eid)
+    out = torch.empty_like(x)
+    if wq is not None:
+      from ..ops import quant as Q
+      W13q, W13sf, W2q, W2sf = wq
+      rdep.place_mx(x, plan, gates32.view(-1))
+      rdep.wait_data()
+      h13 = Q.grouped_gemm_mxfp8(rdep.xq, rdep.sfa, W13q, W13sf, plan.tile_expert, plan.n_m_tiles)
+      aq, asf = Q.swiglu_quant_mxfp8(h13, plan.n_m_tiles)
+      Q.grouped_gemm_mxfp8(aq, asf, W2q, W2sf, plan.tile_expert, plan.n_m_tiles, push=rdep.push_args(True))
+      rdep.finish_return(plan, out)
+      ctx.rdep, ctx.plan = rdep, plan
+      ctx.save_for_backward(x, gates32, W13, W2, h13 if save_h13 else None)
+      return out
     rdep.place(x, plan, gates32.view(-1), "x", with_meta=True)
     rdep.wait_data()
     h13 = G.grouped_gemm(rdep.xbuf, W13, plan.tile_expert, plan.n_m_tiles)
     a = EW.swiglu_rows(h13, plan.n_m_tiles)
-    out = torch.empty_like(x)
     if rdep.fused_return:
       # down projection whose epilogue multiplies by the gate and stores into the source's (token, slot) rows
       G.grouped_gemm(a, W2, plan.tile_expert, plan.n_m_tiles, push=rdep.push_args(True))
@@ -244,7 +279,7 @@ class _MoEFused(torch.autograd.Function):
       rdep.push_and_reduce(dxe, plan, False, rowdot, dx)
     dg = rdep.retg[: plan.T * plan.K].clone().view(plan.T, plan.K)
     dg = torch.where(plan.pos.view(plan.T, plan.K) >= 0, dg, torch.zeros_like(dg))
-    return None, dx, dg, None, dW13, dW2, None
+    return None, dx, dg, None, dW13, dW2, None, None
 
 
 def moe_reference(x, gates, eid, W13, W2):

@@ -1,0 +1,86 @@
+"""MXFP8 quantisation kernels (bit-exact vs the CPU emulation) and the block-scaled tcgen05 GEMM
+(vs fp32 matmul of the dequantised operands)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel(a, b):
+  return ((a.float() - b.float()).abs().max() / (b.float().abs().max() + 1e-6)).item()
+
+
+def test_quant_mxfp8_bit_exact_vs_emulation():
+  from nmoe_b200 import ops
+  torch.manual_seed(0)
+  x = (torch.randn(300, 512, device="cuda") * torch.logspace(-3, 2, 300, device="cuda").unsqueeze(1)).bfloat16()
+  x[5, :64] = 0
+  q, sf = ops.quant_mxfp8(x)
+  qr, sfr = ops.quant_mxfp8(x.cpu())
+  assert torch.equal(q.cpu(), qr)
+  n = sfr.numel()
+  from nmoe_b200.ref import quant as RQ
+  got = RQ.sf_from_mma_layout(sf.cpu(), 384, 16)[:300]
+  want = RQ.sf_from_mma_layout(sfr, 384, 16)[:300]
+  assert torch.equal(got, want)
+  d = ops.dequant_mxfp8(q, sf)
+  assert _rel(d, x) < 0.07
+
+
+def test_quant_mxfp4_bit_exact_vs_emulation():
+  from nmoe_b200 import ops
+  torch.manual_seed(1)
+  x = (torch.randn(256, 256, device="cuda") * 3).bfloat16()
+  q, sf = ops.quant_mxfp4(x)
+  qr, sfr = ops.quant_mxfp4(x.cpu())
+  assert torch.equal(q.cpu(), qr)
+  assert torch.equal(sf.cpu(), sfr)
+
+
+@pytest.mark.parametrize("M,N,K,bn", [(128, 128, 128, 128), (256, 256, 256, 256), (1000, 384, 512, 0), (4096, 2816, 2048, 0)])
+def test_gemm_mxfp8_vs_dequantised_matmul(M, N, K, bn):
+  from nmoe_b200 import ops
+  from nmoe_b200.ops import tc_gemm as G
+  torch.manual_seed(2)
+  a = torch.randn(M, K, device="cuda").bfloat16()
+  b = (torch.randn(N, K, device="cuda") * 0.1).bfloat16()
+  aq, asf = ops.quant_mxfp8(a)
+  bq, bsf = ops.quant_mxfp8(b)
+  c = ops.gemm_mxfp8(aq, asf, bq, bsf, bn=bn)
+  torch.cuda.synchronize()
+  G.check_status()
+  ref = ops.dequant_mxfp8(aq, asf).float() @ ops.dequant_mxfp8(bq, bsf).float().t()
+  assert _rel(c, ref) < 1e-2
+  assert _rel(c, a.float() @ b.float().t()) < 8e-2
+
+
+def test_moe_fp8_forward_close_to_bf16_and_backward_runs():
+  from nmoe_b200.parallel.rdep import Rdep, moe_reference
+  from nmoe_b200.ops.quant import ExpertWeightCache
+  from nmoe_b200.ops import tc_gemm as G
+  torch.manual_seed(3)
+  dev = torch.device("cuda")
+  T, H, F, E, K = 512, 256, 128, 8, 2
+  rd = Rdep(H, E, K, T, device=dev, profile="fp8")
+  try:
+    x = (torch.randn(T, H, device=dev) * 0.5).bfloat16().requires_grad_()
+    W13 = (torch.randn(E, 2 * F, H, device=dev) * 0.05).bfloat16().requires_grad_()
+    W2 = (torch.randn(E, H, F, device=dev) * 0.05).bfloat16().requires_grad_()
+    eid = torch.stack([torch.randperm(E, device=dev)[:K] for _ in range(T)]).int()
+    gates = torch.rand(T, K, device=dev).requires_grad_()
+    cache = ExpertWeightCache()
+    out = rd.moe(x, gates, eid, W13, W2, False, cache.get(W13, W2))
+    out.backward(torch.randn_like(out))
+    torch.cuda.synchronize()
+    G.check_status()
+    ref = moe_reference(x.detach().float().cpu(), gates.detach().cpu(), eid.cpu().long(), W13.detach().float().cpu(),
+                        W2.detach().float().cpu())
+    assert (out.float().cpu() - ref).abs().max().item() < 8e-2 * ref.abs().max().item()   # two chained fp8 GEMMs
+    assert torch.isfinite(x.grad).all() and torch.isfinite(W13.grad).all() and torch.isfinite(W2.grad).all()
+    v0 = cache.ver
+    with torch.no_grad():
+      W13.mul_(1.01)
+    cache.get(W13, W2)
+    assert cache.ver != v0
+  finally:
+    rd.close()
