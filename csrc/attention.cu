@@ -1,0 +1,395 @@
+// Causal softmax attention forward on tcgen05: S = Q K^T and O += P V both run on the tensor
+// cores with accumulators in tensor memory; P never touches shared memory (the softmax warps
+// write it back into the S columns as bf16 and the second MMA reads its A operand from tensor
+// memory).  Covers MLA (d_qk 192, d_v 128), sliding-window attention (band mask), learned
+// per-head sinks (a logit that only enters the denominator) and grouped-query heads, and
+// returns the log-sum-exp per row for the backward.
+//
+// One CTA = one 128-row query tile of one (batch, head).  Warp 0 feeds K/V tiles with TMA
+// (2 stages each), warp 1 issues the MMAs (S for block i+1 is issued before P V of block i so the
+// tensor core works while the softmax warps exponentiate), warps 2-5 own one 32-row quadrant
+// each.  The running maximum is only raised when it grows by more than 2^8 (then O is rescaled in
+// tensor memory); otherwise the stale maximum is kept, which is exact after the final division.
+//
+// Replaces FlashAttention-4's forward (nmoe/attention/mla.py:71-91) and the Triton SWA forward
+// (nmoe/triton/swa.py:24-121) of the reference.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#include "common/ptx.cuh"
+#include "common/tensormap.h"
+
+namespace nmoe {
+
+constexpr int kAttnThreads = 192;
+constexpr int ATT_BM = 128;    // query rows per CTA
+constexpr int ATT_BN = 128;    // keys per block
+constexpr uint64_t kAttnWaitNs = 2000000000ull;
+constexpr float kRescaleThreshold = 8.f;   // log2 units
+
+struct AttnParams {
+  int B, S, Hq, Hkv, Dqk, Dv, window;
+  float scale_log2;
+  const float* sinks;
+  __nv_bfloat16* O;
+  float* lse;
+  StatusRecord* status;
+};
+
+NMOE_DEVICE uint64_t attn_timer() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+NMOE_DEVICE bool attn_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = attn_timer();
+  uint32_t it = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++it & 255u) == 0) {
+      if (*abort_flag) return false;
+      if (attn_timer() - t0 > kAttnWaitNs) return false;
+    }
+  }
+  return true;
+}
+// D[tmem] (+)= A[tmem] * B[smem desc]
+NMOE_DEVICE void mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+NMOE_DEVICE void tmem_st_32x32b_x16(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+
+template <int DQK, int DV>
+struct AttnSmem {
+  static constexpr int kQ = ATT_BM * DQK * 2;
+  static constexpr int kK = ATT_BN * DQK * 2;
+  static constexpr int kV = ATT_BN * DV * 2;
+  static constexpr int kBytes = kQ + 2 * kK + 2 * kV + 1024 + 256;
+};
+
+template <int DQK, int DV>
+__global__ void __launch_bounds__(kAttnThreads, 1)
+k_attn_fwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+           const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
+  using SM = AttnSmem<DQK, DV>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sK = sQ + SM::kQ;
+  uint8_t* sV = sK + 2 * SM::kK;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sV + 2 * SM::kV);
+  uint64_t* q_full = bars;            // [1]
+  uint64_t* k_full = bars + 1;        // [2]
+  uint64_t* k_empty = bars + 3;       // [2]
+  uint64_t* v_full = bars + 5;        // [2]
+  uint64_t* v_empty = bars + 7;       // [2]
+  uint64_t* s_full = bars + 9;        // [2]
+  uint64_t* p_full = bars + 11;       // [2]
+  uint64_t* pv_done = bars + 13;      // [1]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // heavy (late) query tiles first: better tail behaviour under the causal mask
+  const int q_tile = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int q0 = q_tile * ATT_BM;
+  const int hkv = h / (p.Hq / p.Hkv);
+  const int kb_end = min((q0 + ATT_BM + ATT_BN - 1) / ATT_BN, (p.S + ATT_BN - 1) / ATT_BN);
+  const int kb_start = p.window > 0 ? max(0, (q0 - p.window + 1) / ATT_BN) : 0;
+  const int n_blocks = kb_end - kb_start;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
+      mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
+      mbar_init(&s_full[i], 1); mbar_init(&p_full[i], 4);
+    }
+    mbar_init(pv_done, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_o = tmem_base + 256;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA loads
+    if (elect_one()) {
+      tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
+      const int row_q = b * p.S + q0;
+      mbar_expect_tx(q_full, SM::kQ);
+#pragma unroll
+      for (int c = 0; c < DQK / 64; ++c) tma_load_2d(sQ + c * (ATT_BM * 128), &tmQ, q_full, h * DQK + c * 64, row_q);
+      for (int i = 0; i < n_blocks; ++i) {
+        const int st = i & 1;
+        const uint32_t ph = (i >> 1) & 1;
+        const int row_k = b * p.S + (kb_start + i) * ATT_BN;
+        if (!attn_wait(&k_empty[st], ph ^ 1, abort_flag)) { report_status(p.status, kStatusWaitTimeout, 700, i, 0); *abort_flag = 1; break; }
+        mbar_expect_tx(&k_full[st], SM::kK);
+#pragma unroll
+        for (int c = 0; c < DQK / 64; ++c)
+          tma_load_2d(sK + st * SM::kK + c * (ATT_BN * 128), &tmK, &k_full[st], hkv * DQK + c * 64, row_k);
+        if (!attn_wait(&v_empty[st], ph ^ 1, abort_flag)) { report_status(p.status, kStatusWaitTimeout, 701, i, 0); *abort_flag = 1; break; }
+        mbar_expect_tx(&v_full[st], SM::kV);
+#pragma unroll
+        for (int c = 0; c < DV / 64; ++c)
+          tma_load_2d(sV + st * SM::kV + c * (ATT_BN * 128), &tmV, &v_full[st], hkv * DV + c * 64, row_k);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issue
+    if (elect_one()) {
+      constexpr uint32_t idesc_s = make_idesc_bf16(ATT_BM, ATT_BN, 0, 0);
+      constexpr uint32_t idesc_pv = make_idesc_bf16(ATT_BM, DV, 0, 1);
+      auto issue_s = [&](int i) -> bool {
+        const int st = i & 1;
+        if (!attn_wait(&k_full[st], (i >> 1) & 1, abort_flag)) { report_status(p.status, kStatusWaitTimeout, 710, i, 0); *abort_flag = 1; return false; }
+        tc_fence_after_sync();
+        const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK + st * SM::kK);
+#pragma unroll
+        for (int j = 0; j < DQK / 16; ++j) {
+          const uint32_t off = (j >> 2) * (ATT_BM * 128) + (j & 3) * 32;
+          mma_f16_ss(tmem_base + st * ATT_BN, make_smem_desc(qa + off, 0, 1024, kSwizzle128B),
+                     make_smem_desc(ka + off, 0, 1024, kSwizzle128B), idesc_s, j != 0 ? 1u : 0u);
+        }
+        mma_commit(&k_empty[st]);
+        mma_commit(&s_full[st]);
+        return true;
+      };
+      bool ok = n_blocks > 0 && attn_wait(q_full, 0, abort_flag);
+      if (ok) ok = issue_s(0);
+      for (int i = 0; ok && i < n_blocks; ++i) {
+        const int st = i & 1;
+        if (i + 1 < n_blocks) { ok = issue_s(i + 1); if (!ok) break; }
+        if (!attn_wait(&p_full[st], (i >> 1) & 1, abort_flag)) { report_status(p.status, kStatusWaitTimeout, 711, i, 0); *abort_flag = 1; break; }
+        if (!attn_wait(&v_full[st], (i >> 1) & 1, abort_flag)) { report_status(p.status, kStatusWaitTimeout, 712, i, 0); *abort_flag = 1; break; }
+        tc_fence_after_sync();
+        const uint32_t va = smem_u32(sV + st * SM::kV);
+#pragma unroll
+        for (int j = 0; j < ATT_BN / 16; ++j)
+          mma_f16_ts(tmem_o, tmem_base + st * ATT_BN + j * 8, make_smem_desc(va + j * 2048, ATT_BN * 128, 1024, kSwizzle128B),
+                     idesc_pv, (i | j) != 0 ? 1u : 0u);
+        mma_commit(&v_empty[st]);
+        mma_commit(pv_done);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------ softmax + epilogue (one 32-row quadrant per warp)
+    const int q = warp & 3;
+    const int row = q0 + q * 32 + lane;              // query position inside the sequence
+    const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
+    float m = -1e30f, l = 0.f;
+    if (p.sinks != nullptr) { m = p.sinks[h] * 1.4426950408889634f; l = 1.f; }
+    bool ok = true;
+    for (int i = 0; i < n_blocks; ++i) {
+      const int st = i & 1;
+      const uint32_t s_addr = tmem_base + lane_addr + st * ATT_BN;
+      ok = attn_wait(&s_full[st], (i >> 1) & 1, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) { if (lane == 0) report_status(p.status, kStatusWaitTimeout, 720, i, 0); *abort_flag = 1; break; }
+      tc_fence_after_sync();
+      const int k0 = (kb_start + i) * ATT_BN;
+      const bool need_mask = (k0 + ATT_BN - 1 > q0) || (p.window > 0 && k0 <= q0 + ATT_BM - 1 - p.window) || (k0 + ATT_BN > p.S);
+      // pass 1: row maximum
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < ATT_BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(s_addr + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int t = 0; t < 32; ++t) {
+          float v = __uint_as_float(r[t]);
+          if (need_mask) {
+            const int j = k0 + c * 32 + t;
+            if (j > row || j >= p.S || (p.window > 0 && j <= row - p.window)) v = -INFINITY;
+          }
+          mx = fmaxf(mx, v);
+        }
+      }
+      const float m_cand = fmaxf(m, mx * p.scale_log2);
+      float alpha = 1.f;
+      bool grow = (m_cand - m > kRescaleThreshold);
+      if (i == 0) { grow = false; if (m_cand > m) { l *= exp2f(m - m_cand); m = m_cand; } }
+      if (__any_sync(0xffffffffu, grow)) {
+        // O must be final for block i-1 before it is rescaled
+        ok = attn_wait(pv_done, (i - 1) & 1, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) { if (lane == 0) report_status(p.status, kStatusWaitTimeout, 721, i, 0); *abort_flag = 1; break; }
+        tc_fence_after_sync();
+        if (grow) { alpha = exp2f(m - m_cand); m = m_cand; l *= alpha; }
+#pragma unroll 1
+        for (int c = 0; c < DV / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(tmem_o + lane_addr + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int t = 0; t < 32; ++t) r[t] = __float_as_uint(__uint_as_float(r[t]) * alpha);
+          tmem_st_32x32b_x32(tmem_o + lane_addr + c * 32, r);
+        }
+        tmem_st_wait();
+      }
+      // pass 2: P = 2^(s*scale - m), written back as bf16 pairs into the first 64 columns of this S buffer
+      float rs = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < ATT_BN / 32; ++c) {
+        uint32_t r[32], pk[16];
+        tmem_ld_32x32b_x32(s_addr + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int t = 0; t < 32; t += 2) {
+          float v0 = __uint_as_float(r[t]), v1 = __uint_as_float(r[t + 1]);
+          if (need_mask) {
+            const int j = k0 + c * 32 + t;
+            if (j > row || j >= p.S || (p.window > 0 && j <= row - p.window)) v0 = -INFINITY;
+            if (j + 1 > row || j + 1 >= p.S || (p.window > 0 && j + 1 <= row - p.window)) v1 = -INFINITY;
+          }
+          const float p0 = exp2f(fmaf(v0, p.scale_log2, -m)), p1 = exp2f(fmaf(v1, p.scale_log2, -m));
+          rs += p0 + p1;
+          pk[t >> 1] = pack_bf16x2(p0, p1);
+        }
+        tmem_st_32x32b_x16(s_addr + c * 16, pk);
+      }
+      l += rs;
+      tmem_st_wait();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full[st]);
+    }
+    // epilogue
+    if (ok && n_blocks > 0) {
+      ok = attn_wait(pv_done, (n_blocks - 1) & 1, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) { if (lane == 0) report_status(p.status, kStatusWaitTimeout, 722, 0, 0); *abort_flag = 1; }
+    }
+    if (ok) {
+      tc_fence_after_sync();
+      const float inv_l = l > 0.f ? 1.f / l : 0.f;
+      const bool row_ok = row < p.S;
+      __nv_bfloat16* orow = p.O + (static_cast<size_t>(b) * p.S + row) * (static_cast<size_t>(p.Hq) * DV) + static_cast<size_t>(h) * DV;
+#pragma unroll 1
+      for (int c = 0; c < DV / 32; ++c) {
+        uint32_t r[32];
+        if (n_blocks > 0) {
+          tmem_ld_32x32b_x32(tmem_o + lane_addr + c * 32, r);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int t = 0; t < 32; ++t) r[t] = 0u;
+        }
+        if (row_ok) {
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            int4 v;
+            v.x = pack_bf16x2(__uint_as_float(r[8 * t]) * inv_l, __uint_as_float(r[8 * t + 1]) * inv_l);
+            v.y = pack_bf16x2(__uint_as_float(r[8 * t + 2]) * inv_l, __uint_as_float(r[8 * t + 3]) * inv_l);
+            v.z = pack_bf16x2(__uint_as_float(r[8 * t + 4]) * inv_l, __uint_as_float(r[8 * t + 5]) * inv_l);
+            v.w = pack_bf16x2(__uint_as_float(r[8 * t + 6]) * inv_l, __uint_as_float(r[8 * t + 7]) * inv_l);
+            reinterpret_cast<int4*>(orow + c * 32)[t] = v;
+          }
+        }
+      }
+      if (row_ok && p.lse != nullptr)
+        p.lse[(static_cast<size_t>(b) * p.Hq + h) * p.S + row] = l > 0.f ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
+    }
+  }
+
+  if (*abort_flag) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+static int attn_map(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t pitch_bytes) {
+  using Key = std::tuple<const void*, uint64_t, uint64_t, uint64_t>;
+  static std::map<Key, CUtensorMap> cache;
+  static std::mutex mu;
+  Key k{base, inner, outer, pitch_bytes};
+  std::lock_guard<std::mutex> g(mu);
+  auto it = cache.find(k);
+  if (it != cache.end()) { *out = it->second; return 0; }
+  int rc = make_tensor_map_2d(out, base, kTmaBf16, inner, outer, pitch_bytes, 64, 128, kTmaSwizzle128);
+  if (rc != 0) return rc;
+  if (cache.size() > 1024) cache.clear();
+  cache[k] = *out;
+  return 0;
+}
+
+template <int DQK, int DV>
+static int attn_launch(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& p,
+                       cudaStream_t st) {
+  auto kern = k_attn_fwd<DQK, DV>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnSmem<DQK, DV>::kBytes);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  dim3 grid((p.S + ATT_BM - 1) / ATT_BM, p.Hq, p.B);
+  kern<<<grid, kAttnThreads, AttnSmem<DQK, DV>::kBytes, st>>>(tq, tk, tv, p);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : static_cast<int>(e);
+}
+
+}  // namespace nmoe
+
+using namespace nmoe;
+
+// q [B,S,Hq,Dqk], k [B,S,Hkv,Dqk], v [B,S,Hkv,Dv], o [B,S,Hq,Dv] contiguous bf16; lse [B,Hq,S] fp32 (optional);
+// sinks [Hq] fp32 raw logits (optional); window 0 = full causal.  Supported head dims:
+// (Dqk, Dv) in {(192,128), (128,128), (64,64)}.
+extern "C" int nmoe_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, const float* sinks,
+                             int B, int S, int Hq, int Hkv, int Dqk, int Dv, int window, float scale, void* status,
+                             cudaStream_t st) {
+  if (B == 0 || S == 0) return 0;
+  if (Hq % Hkv != 0) return -1;
+  AttnParams p;
+  p.B = B; p.S = S; p.Hq = Hq; p.Hkv = Hkv; p.Dqk = Dqk; p.Dv = Dv; p.window = window;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.sinks = sinks; p.O = static_cast<__nv_bfloat16*>(o); p.lse = lse; p.status = static_cast<StatusRecord*>(status);
+  CUtensorMap tq, tk, tv;
+  const uint64_t rows = static_cast<uint64_t>(B) * S;
+  int rc = attn_map(&tq, q, static_cast<uint64_t>(Hq) * Dqk, rows, static_cast<uint64_t>(Hq) * Dqk * 2);
+  if (rc) return rc;
+  rc = attn_map(&tk, k, static_cast<uint64_t>(Hkv) * Dqk, rows, static_cast<uint64_t>(Hkv) * Dqk * 2);
+  if (rc) return rc;
+  rc = attn_map(&tv, v, static_cast<uint64_t>(Hkv) * Dv, rows, static_cast<uint64_t>(Hkv) * Dv * 2);
+  if (rc) return rc;
+  if (Dqk == 192 && Dv == 128) return attn_launch<192, 128>(tq, tk, tv, p, st);
+  if (Dqk == 128 && Dv == 128) return attn_launch<128, 128>(tq, tk, tv, p, st);
+  if (Dqk == 64 && Dv == 64) return attn_launch<64, 64>(tq, tk, tv, p, st);
+  return -2;
+}

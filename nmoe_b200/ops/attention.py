@@ -1,7 +1,11 @@
 """Softmax attention entry point: causal, optional sliding window, optional learned sinks, GQA.
 
 q,k: [B,S,Hq|Hkv,Dqk]; v: [B,S,Hkv,Dv] -> [B,S,Hq,Dv].  MLA calls it with (Dqk,Dv)=(192,128).
-CPU tensors run the eager oracle.
+
+Forward on CUDA = the tcgen05 kernel in ``csrc/attention.cu`` (head dims (192,128), (128,128),
+(64,64)); it also returns the log-sum-exp.  Backward: full-causal attention without sinks goes
+through the cuDNN fused backward (recomputed from q,k,v); windowed / sink attention differentiates
+a query-block-tiled eager statement.  CPU tensors run the fp32 oracle.
 """
 from __future__ import annotations
 
@@ -11,13 +15,17 @@ import torch
 import torch.nn.functional as F
 
 from ..ref import ops as R
+from . import _lib as L
+from .tc_gemm import status_buffer
+
+_KERNEL_DIMS = {(192, 128), (128, 128), (64, 64)}
 
 
 def _banded_eager(q, k, v, scale, window, sinks):
-  """Query-block tiled eager attention for windows/sinks on CUDA (library GEMMs).
+  """Query-block tiled eager attention (library GEMMs), differentiable.
 
   Each block of ``bq`` queries only sees keys in [start - window + 1, end], so the cost is
-  O(S * (bq + window)) instead of O(S^2).
+  O(S * (bq + window)) instead of O(S^2) when a window is set.
   """
   B, S, Hq, Dqk = q.shape
   Hkv = k.size(2)
@@ -48,13 +56,59 @@ def _banded_eager(q, k, v, scale, window, sinks):
   return torch.cat(outs, dim=1).to(q.dtype)
 
 
+def attention_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, window: int = 0,
+                      sinks: Optional[torch.Tensor] = None, need_lse: bool = True):
+  """Raw kernel call (no autograd): returns (o [B,S,Hq,Dv] bf16, lse [B,Hq,S] fp32 or None)."""
+  B, S, Hq, Dqk = q.shape
+  Hkv, Dv = k.size(2), v.size(3)
+  q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+  o = torch.empty(B, S, Hq, Dv, dtype=q.dtype, device=q.device)
+  lse = torch.empty(B, Hq, S, dtype=torch.float32, device=q.device) if need_lse else None
+  sk = sinks.detach().float().contiguous() if sinks is not None else None
+  st = status_buffer(q.device)
+  L.check(L.lib().nmoe_attn_fwd(L.ptr(q), L.ptr(k), L.ptr(v), L.ptr(o), L.ptr(lse), L.ptr(sk), B, S, Hq, Hkv, Dqk, Dv,
+                                int(window), L.c_float(scale), L.ptr(st), L.stream()), "attn_fwd")
+  return o, lse
+
+
+class _Attention(torch.autograd.Function):
+  @staticmethod
+  def forward(ctx, q, k, v, sinks, scale, window):
+    o, lse = attention_forward(q, k, v, scale, window, sinks, need_lse=False)
+    ctx.save_for_backward(q, k, v, sinks)
+    ctx.scale, ctx.window = scale, window
+    return o
+
+  @staticmethod
+  def backward(ctx, do):
+    q, k, v, sinks = ctx.saved_tensors
+    scale, window = ctx.scale, ctx.window
+    with torch.enable_grad():
+      qd, kd, vd = (t.detach().requires_grad_() for t in (q, k, v))
+      sd = sinks.detach().requires_grad_() if sinks is not None else None
+      if window == 0 and sinks is None:
+        Hq, Hkv = q.size(2), k.size(2)
+        o2 = F.scaled_dot_product_attention(qd.transpose(1, 2), kd.transpose(1, 2), vd.transpose(1, 2), is_causal=True,
+                                            scale=scale, enable_gqa=(Hq != Hkv)).transpose(1, 2)
+      else:
+        o2 = _banded_eager(qd, kd, vd, scale, window, sd)
+      ins = (qd, kd, vd) + ((sd,) if sd is not None else ())
+      grads = torch.autograd.grad(o2, ins, do)
+    dq, dk, dv = grads[:3]
+    ds = grads[3].to(sinks.dtype) if sd is not None else None
+    return dq, dk, dv, ds, None, None
+
+
 def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, *, causal: bool = True,
               window: int = 0, sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
   if not q.is_cuda:
     return R.attention(q, k, v, scale, causal=causal, window=window, sinks=sinks)
+  assert causal, "only causal attention is used by this framework"
+  if (q.size(-1), v.size(-1)) in _KERNEL_DIMS and q.dtype == torch.bfloat16:
+    return _Attention.apply(q, k, v, sinks, scale, int(window))
   if window > 0 or sinks is not None:
     return _banded_eager(q, k, v, scale, window, sinks)
   Hq, Hkv = q.size(2), k.size(2)
-  o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=causal,
+  o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=True,
                                      scale=scale, enable_gqa=(Hq != Hkv))
   return o.transpose(1, 2)

@@ -1,0 +1,69 @@
+"""tcgen05 attention forward vs the fp32 eager oracle: MLA dims, sliding window, sinks, GQA, ragged S."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel(a, b):
+  return ((a.float() - b.float()).abs().max() / (b.float().abs().max() + 1e-6)).item()
+
+
+@pytest.mark.parametrize("B,S,Hq,Hkv,Dqk,Dv,window,use_sinks", [
+  (2, 256, 4, 4, 192, 128, 0, False),
+  (1, 1024, 2, 2, 192, 128, 0, False),
+  (2, 384, 4, 2, 128, 128, 128, True),
+  (1, 512, 4, 4, 128, 128, 100, False),
+  (1, 300, 2, 1, 64, 64, 0, True),
+  (1, 640, 2, 2, 64, 64, 37, True),
+])
+def test_attention_forward_and_lse(B, S, Hq, Hkv, Dqk, Dv, window, use_sinks):
+  from nmoe_b200.ops.attention import attention_forward
+  from nmoe_b200.ops import tc_gemm as G
+  from nmoe_b200.ref import ops as R
+  torch.manual_seed(0)
+  q = torch.randn(B, S, Hq, Dqk, device="cuda").bfloat16()
+  k = torch.randn(B, S, Hkv, Dqk, device="cuda").bfloat16()
+  v = torch.randn(B, S, Hkv, Dv, device="cuda").bfloat16()
+  sinks = (torch.randn(Hq, device="cuda") * 2).bfloat16() if use_sinks else None
+  scale = Dqk ** -0.5
+  o, lse = attention_forward(q, k, v, scale, window, sinks)
+  torch.cuda.synchronize()
+  G.check_status()
+  ref = R.attention(q.float().cpu(), k.float().cpu(), v.float().cpu(), scale, window=window,
+                    sinks=sinks.float().cpu() if sinks is not None else None)
+  assert _rel(o.cpu(), ref) < 2e-2
+  # lse against eager
+  kk = k.float().cpu().repeat_interleave(Hq // Hkv, dim=2)
+  s = torch.einsum("bihd,bjhd->bhij", q.float().cpu(), kk) * scale
+  i = torch.arange(S).unsqueeze(-1); j = torch.arange(S).unsqueeze(0)
+  mask = j <= i
+  if window > 0:
+    mask &= j > i - window
+  s = s.masked_fill(~mask, float("-inf"))
+  if sinks is not None:
+    s = torch.cat((s, sinks.float().cpu().view(1, Hq, 1, 1).expand(B, Hq, S, 1)), -1)
+  assert torch.allclose(lse.cpu(), torch.logsumexp(s, -1), atol=2e-2, rtol=1e-3)
+
+
+def test_attention_backward_paths():
+  from nmoe_b200.ops.attention import attention
+  from nmoe_b200.ref import ops as R
+  torch.manual_seed(1)
+  for (Dqk, Dv, window, use_sinks) in [(192, 128, 0, False), (128, 128, 64, True)]:
+    q = torch.randn(1, 256, 2, Dqk, device="cuda").bfloat16().requires_grad_()
+    k = torch.randn(1, 256, 2, Dqk, device="cuda").bfloat16().requires_grad_()
+    v = torch.randn(1, 256, 2, Dv, device="cuda").bfloat16().requires_grad_()
+    sinks = torch.randn(2, device="cuda").bfloat16().requires_grad_() if use_sinks else None
+    o = attention(q, k, v, Dqk ** -0.5, window=window, sinks=sinks)
+    g = torch.randn_like(o)
+    o.backward(g)
+    qf, kf, vf = (t.detach().float().cpu().requires_grad_() for t in (q, k, v))
+    sf = sinks.detach().float().cpu().requires_grad_() if use_sinks else None
+    of = R.attention(qf, kf, vf, Dqk ** -0.5, window=window, sinks=sf)
+    of.backward(g.float().cpu())
+    assert _rel(o.cpu(), of.detach()) < 2e-2
+    for a, b in ((q.grad, qf.grad), (k.grad, kf.grad), (v.grad, vf.grad)):
+      assert _rel(a.cpu(), b) < 3e-2
+    if use_sinks:
+      assert _rel(sinks.grad.cpu(), sf.grad) < 5e-2

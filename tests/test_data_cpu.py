@@ -1,0 +1,91 @@
+"""Shard building, index, manifest verification, dedup, flow -- CPU only, `bytes` tokenizer."""
+import json
+
+import numpy as np
+import pytest
+
+from nmoe_b200.data import cli, dedup, diversity, flow as flow_mod, index, inspect as insp, sinks
+from nmoe_b200.data.errors import ShardChecksumError, SourceNotFoundError
+from nmoe_b200.data.sources import Document, JSONLSource
+
+
+def _write_jsonl(path, n=50):
+  with open(path, "w") as f:
+    for i in range(n):
+      f.write(json.dumps({"id": f"d{i}", "text": f"document number {i} " + "lorem ipsum " * (i % 7 + 1)}) + "\n")
+
+
+def test_prep_verify_inspect_roundtrip(tmp_path):
+  _write_jsonl(tmp_path / "a.jsonl")
+  out = tmp_path / "shards"
+  assert cli.main(["prep", "--source", "jsonl", "--input", str(tmp_path / "a.jsonl"), "--output", str(out), "--name", "toy",
+                   "--tokenizer", "bytes", "--num-shards", "3"]) == 0
+  m = sinks.verify_manifest(out)
+  assert m.total_documents == 50 and m.num_shards == 3 and m.eos_token_id == 256
+  s0 = out / m.shards[0].path
+  rd = index.IndexReader(index.index_path_for_shard(s0))
+  toks = np.load(s0)
+  for s, e in rd.iter_documents():
+    assert toks[e - 1] == 256 and (toks[s:e - 1] < 256).all()
+  doc = insp.document(s0, 0, "bytes")
+  assert doc["text"].startswith("document number")
+  # deterministic placement + index regeneration gives the same boundaries
+  before = rd.to_array()
+  index.index_path_for_shard(s0).unlink()
+  index.regenerate_index_from_shard(s0, 256)
+  assert (index.IndexReader(index.index_path_for_shard(s0)).to_array() == before).all()
+  # corruption is detected
+  arr = np.load(s0); arr[0] ^= 1; np.save(s0, arr)
+  with pytest.raises(ShardChecksumError):
+    sinks.verify_manifest(out)
+
+
+def test_parallel_prep_matches_serial(tmp_path):
+  from nmoe_b200.data.prep import ParallelPrepPipeline, PrepConfig, PrepPipeline
+  _write_jsonl(tmp_path / "a.jsonl", 80)
+  mk = lambda: JSONLSource(str(tmp_path / "a.jsonl"))
+  a = PrepPipeline(mk(), PrepConfig(str(tmp_path / "s"), "toy", tokenizer="bytes", num_shards=4, log_every=0)).run()
+  b = ParallelPrepPipeline(mk, PrepConfig(str(tmp_path / "p"), "toy", tokenizer="bytes", num_shards=4, log_every=0), workers=2).run()
+  assert [s.checksum for s in a.shards] == [s.checksum for s in b.shards]
+
+
+def test_sources_errors_and_sharding(tmp_path):
+  with pytest.raises(SourceNotFoundError):
+    JSONLSource(str(tmp_path / "missing"))
+  _write_jsonl(tmp_path / "a.jsonl", 10)
+  src = JSONLSource(str(tmp_path / "a.jsonl"))
+  ids = [d.doc_id for d in src]
+  parts = [[d.doc_id for d in src.shard(i, 3)] for i in range(3)]
+  assert sorted(sum(parts, [])) == sorted(ids) and parts[0] == ids[0::3]
+
+
+def test_dedup_exact_and_near():
+  docs = [Document("a", "the quick brown fox jumps over the lazy dog " * 5),
+          Document("b", "The quick brown fox jumps over the lazy dog " * 5),
+          Document("c", "the quick brown fox jumps over the lazy dog " * 5 + "again"),
+          Document("d", "completely different content about tensor cores and memory bandwidth " * 4)]
+  assert [d.doc_id for d in dedup.dedup_exact(docs)] == ["a", "c", "d"]
+  kept = [d.doc_id for d in dedup.stream_near_dedup(docs, threshold=0.7, num_perm=32, bands=8)]
+  assert kept == ["a", "d"]
+
+
+def test_cluster_coverage():
+  rng = np.random.default_rng(0)
+  x = np.concatenate([rng.normal(c, 0.1, size=(100, 8)) for c in (-3, 0, 3)])
+  _, assign = diversity.cluster_embeddings(x, 3)
+  m = diversity.coverage_metrics(assign, 3)
+  assert m["empty_clusters"] == 0 and m["max_share"] < 0.5
+
+
+def test_flow_env_overrides_and_guard(tmp_path):
+  _write_jsonl(tmp_path / "raw.jsonl", 30)
+  spec_path = tmp_path / "flow.toml"
+  spec_path.write_text(f'[source]\nkind = "jsonl"\npaths = "{tmp_path / "raw.jsonl"}"\n[prep]\noutput_dir = "{tmp_path / "out"}"\n'
+                       'dataset = "f"\ntokenizer = "bytes"\nnum_shards = 2\n[grade]\nenabled = true\nthreshold = 0.5\n')
+  spec = flow_mod.load_spec(spec_path, env={"NMOE_DATAFLOW__GRADE__THRESHOLD": "0.9"})
+  assert spec.grade["threshold"] == 0.9
+  m = flow_mod.run_flow(spec, grader=lambda texts: [1.0 if "1" in t else 0.0 for t in texts], print_fn=lambda *a: None)
+  assert 0 < m.total_documents < 30
+  other = flow_mod.load_spec(spec_path, env={})
+  with pytest.raises(RuntimeError, match="different flow"):
+    flow_mod.run_flow(other, grader=lambda t: [1.0] * len(t), print_fn=lambda *a: None)
