@@ -35,6 +35,12 @@ constexpr float kRescaleThreshold = 8.f;   // log2 units
 
 struct AttnParams {
   int B, S, Hq, Hkv, Dqk, Dv, window;
+  // column (element) addressing of the operands inside their 2-D [B*S, row_elems] views:
+  // head h of Q starts at h*q_hs; K chunk c (64 columns) comes from source 1 while c < k1_chunks
+  // (column hkv*k1_hs + k1_off + c*64) and from source 2 afterwards (hkv*k2_hs + k2_off + (c-k1_chunks)*64);
+  // V starts at hkv*v_hs + v_off.  This lets MLA read k_nope and v straight out of the fused kv
+  // projection and the shared rotary key from its own tensor without materialising K or V.
+  int q_hs, k1_hs, k1_off, k1_chunks, k2_hs, k2_off, v_hs, v_off;
   float scale_log2;
   const float* sinks;
   __nv_bfloat16* O;
@@ -88,7 +94,7 @@ struct AttnSmem {
 template <int DQK, int DV>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 k_attn_fwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-           const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
+           const __grid_constant__ CUtensorMap tmK2, const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
   using SM = AttnSmem<DQK, DV>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -141,11 +147,11 @@ k_attn_fwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
   if (warp == 0) {
     // ------------------------------------------------------------ TMA loads
     if (elect_one()) {
-      tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
+      tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmK2); tma_prefetch_desc(&tmV);
       const int row_q = b * p.S + q0;
       mbar_expect_tx(q_full, SM::kQ);
 #pragma unroll
-      for (int c = 0; c < DQK / 64; ++c) tma_load_2d(sQ + c * (ATT_BM * 128), &tmQ, q_full, h * DQK + c * 64, row_q);
+      for (int c = 0; c < DQK / 64; ++c) tma_load_2d(sQ + c * (ATT_BM * 128), &tmQ, q_full, h * p.q_hs + c * 64, row_q);
       for (int i = 0; i < n_blocks; ++i) {
         const int st = i & 1;
         const uint32_t ph = (i >> 1) & 1;
@@ -153,13 +159,18 @@ k_attn_fwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         if (!attn_wait(&k_empty[st], ph ^ 1, abort_flag)) { report_status(p.status, kStatusWaitTimeout, 700, i, 0); *abort_flag = 1; break; }
         mbar_expect_tx(&k_full[st], SM::kK);
 #pragma unroll
-        for (int c = 0; c < DQK / 64; ++c)
-          tma_load_2d(sK + st * SM::kK + c * (ATT_BN * 128), &tmK, &k_full[st], hkv * DQK + c * 64, row_k);
+        for (int c = 0; c < DQK / 64; ++c) {
+          if (c < p.k1_chunks)
+            tma_load_2d(sK + st * SM::kK + c * (ATT_BN * 128), &tmK, &k_full[st], hkv * p.k1_hs + p.k1_off + c * 64, row_k);
+          else
+            tma_load_2d(sK + st * SM::kK + c * (ATT_BN * 128), &tmK2, &k_full[st],
+                        hkv * p.k2_hs + p.k2_off + (c - p.k1_chunks) * 64, row_k);
+        }
         if (!attn_wait(&v_empty[st], ph ^ 1, abort_flag)) { report_status(p.status, kStatusWaitTimeout, 701, i, 0); *abort_flag = 1; break; }
         mbar_expect_tx(&v_full[st], SM::kV);
 #pragma unroll
         for (int c = 0; c < DV / 64; ++c)
-          tma_load_2d(sV + st * SM::kV + c * (ATT_BN * 128), &tmV, &v_full[st], hkv * DV + c * 64, row_k);
+          tma_load_2d(sV + st * SM::kV + c * (ATT_BN * 128), &tmV, &v_full[st], hkv * p.v_hs + p.v_off + c * 64, row_k);
       }
     }
     __syncwarp();
@@ -349,8 +360,8 @@ static int attn_map(CUtensorMap* out, const void* base, uint64_t inner, uint64_t
 }
 
 template <int DQK, int DV>
-static int attn_launch(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& p,
-                       cudaStream_t st) {
+static int attn_launch(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tk2, const CUtensorMap& tv,
+                       const AttnParams& p, cudaStream_t st) {
   auto kern = k_attn_fwd<DQK, DV>;
   static bool configured = false;
   if (!configured) {
@@ -359,7 +370,7 @@ static int attn_launch(const CUtensorMap& tq, const CUtensorMap& tk, const CUten
     configured = true;
   }
   dim3 grid((p.S + ATT_BM - 1) / ATT_BM, p.Hq, p.B);
-  kern<<<grid, kAttnThreads, AttnSmem<DQK, DV>::kBytes, st>>>(tq, tk, tv, p);
+  kern<<<grid, kAttnThreads, AttnSmem<DQK, DV>::kBytes, st>>>(tq, tk, tk2, tv, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : static_cast<int>(e);
 }
@@ -368,28 +379,44 @@ static int attn_launch(const CUtensorMap& tq, const CUtensorMap& tk, const CUten
 
 using namespace nmoe;
 
-// q [B,S,Hq,Dqk], k [B,S,Hkv,Dqk], v [B,S,Hkv,Dv], o [B,S,Hq,Dv] contiguous bf16; lse [B,Hq,S] fp32 (optional);
-// sinks [Hq] fp32 raw logits (optional); window 0 = full causal.  Supported head dims:
-// (Dqk, Dv) in {(192,128), (128,128), (64,64)}.
+// General form.  Every operand is a bf16 matrix with B*S rows; *_row is its row length in elements
+// (a multiple of 8) and the *_hs / *_off arguments place a head's columns inside a row (see AttnParams).
+// o [B,S,Hq,Dv] contiguous; lse [B,Hq,S] fp32 (optional); sinks [Hq] fp32 raw logits (optional);
+// window 0 = full causal.  Supported head dims (Dqk, Dv): (192,128), (128,128), (64,64).
+extern "C" int nmoe_attn_fwd_ex(const void* q, int q_row, int q_hs, const void* k1, int k1_row, int k1_hs, int k1_off,
+                                int k1_chunks, const void* k2, int k2_row, int k2_hs, int k2_off, const void* v,
+                                int v_row, int v_hs, int v_off, void* o, float* lse, const float* sinks, int B, int S,
+                                int Hq, int Hkv, int Dqk, int Dv, int window, float scale, void* status,
+                                cudaStream_t st) {
+  if (B == 0 || S == 0) return 0;
+  if (Hq % Hkv != 0) return -1;
+  if ((q_row | k1_row | k2_row | v_row) % 8 != 0) return -3;
+  AttnParams p;
+  p.B = B; p.S = S; p.Hq = Hq; p.Hkv = Hkv; p.Dqk = Dqk; p.Dv = Dv; p.window = window;
+  p.q_hs = q_hs; p.k1_hs = k1_hs; p.k1_off = k1_off; p.k1_chunks = k1_chunks; p.k2_hs = k2_hs; p.k2_off = k2_off;
+  p.v_hs = v_hs; p.v_off = v_off;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.sinks = sinks; p.O = static_cast<__nv_bfloat16*>(o); p.lse = lse; p.status = static_cast<StatusRecord*>(status);
+  CUtensorMap tq, tk, tk2, tv;
+  const uint64_t rows = static_cast<uint64_t>(B) * S;
+  int rc = attn_map(&tq, q, q_row, rows, static_cast<uint64_t>(q_row) * 2);
+  if (rc) return rc;
+  rc = attn_map(&tk, k1, k1_row, rows, static_cast<uint64_t>(k1_row) * 2);
+  if (rc) return rc;
+  rc = attn_map(&tk2, k2 ? k2 : k1, k2 ? k2_row : k1_row, rows, static_cast<uint64_t>(k2 ? k2_row : k1_row) * 2);
+  if (rc) return rc;
+  rc = attn_map(&tv, v, v_row, rows, static_cast<uint64_t>(v_row) * 2);
+  if (rc) return rc;
+  if (Dqk == 192 && Dv == 128) return attn_launch<192, 128>(tq, tk, tk2, tv, p, st);
+  if (Dqk == 128 && Dv == 128) return attn_launch<128, 128>(tq, tk, tk2, tv, p, st);
+  if (Dqk == 64 && Dv == 64) return attn_launch<64, 64>(tq, tk, tk2, tv, p, st);
+  return -2;
+}
+
+// q [B,S,Hq,Dqk], k [B,S,Hkv,Dqk], v [B,S,Hkv,Dv] contiguous.
 extern "C" int nmoe_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, const float* sinks,
                              int B, int S, int Hq, int Hkv, int Dqk, int Dv, int window, float scale, void* status,
                              cudaStream_t st) {
-  if (B == 0 || S == 0) return 0;
-  if (Hq % Hkv != 0) return -1;
-  AttnParams p;
-  p.B = B; p.S = S; p.Hq = Hq; p.Hkv = Hkv; p.Dqk = Dqk; p.Dv = Dv; p.window = window;
-  p.scale_log2 = scale * 1.4426950408889634f;
-  p.sinks = sinks; p.O = static_cast<__nv_bfloat16*>(o); p.lse = lse; p.status = static_cast<StatusRecord*>(status);
-  CUtensorMap tq, tk, tv;
-  const uint64_t rows = static_cast<uint64_t>(B) * S;
-  int rc = attn_map(&tq, q, static_cast<uint64_t>(Hq) * Dqk, rows, static_cast<uint64_t>(Hq) * Dqk * 2);
-  if (rc) return rc;
-  rc = attn_map(&tk, k, static_cast<uint64_t>(Hkv) * Dqk, rows, static_cast<uint64_t>(Hkv) * Dqk * 2);
-  if (rc) return rc;
-  rc = attn_map(&tv, v, static_cast<uint64_t>(Hkv) * Dv, rows, static_cast<uint64_t>(Hkv) * Dv * 2);
-  if (rc) return rc;
-  if (Dqk == 192 && Dv == 128) return attn_launch<192, 128>(tq, tk, tv, p, st);
-  if (Dqk == 128 && Dv == 128) return attn_launch<128, 128>(tq, tk, tv, p, st);
-  if (Dqk == 64 && Dv == 64) return attn_launch<64, 64>(tq, tk, tv, p, st);
-  return -2;
+  return nmoe_attn_fwd_ex(q, Hq * Dqk, Dqk, k, Hkv * Dqk, Dqk, 0, Dqk / 64, nullptr, 0, 0, 0, v, Hkv * Dv, Dv, 0, o, lse,
+                          sinks, B, S, Hq, Hkv, Dqk, Dv, window, scale, status, st);
 }

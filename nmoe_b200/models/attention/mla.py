@@ -8,7 +8,7 @@ import torch
 from torch import nn
 
 from ... import ops
-from ...ops.attention import attention
+from ...ops.attention import attention, mla_attention
 from ..norm import RMSNorm
 
 
@@ -46,7 +46,10 @@ class MLA(nn.Module):
     kv_lat, k_pe = torch.split(kv_a, [self.kv_lora_rank, self.rope_dim], dim=-1)
     k_pe = ops.rope(k_pe.reshape(B, S, 1, self.rope_dim), cos, sin)
     kv = ops.linear(self.kv_norm(kv_lat.contiguous()), self.wkv_b).view(B, S, h, self.nope + self.v_dim)
-    k_nope, v = torch.split(kv, [self.nope, self.v_dim], dim=-1)
-    k = torch.cat((k_nope, k_pe.expand(B, S, h, self.rope_dim)), dim=-1)
-    o = attention(q, k, v.contiguous(), self.softmax_scale, causal=True, window=self.window)
+    if self.window == 0:
+      o = mla_attention(q, kv, k_pe, self.softmax_scale, self.nope, self.v_dim)
+    else:
+      k_nope, v = torch.split(kv, [self.nope, self.v_dim], dim=-1)
+      k = torch.cat((k_nope, k_pe.expand(B, S, h, self.rope_dim)), dim=-1)
+      o = attention(q, k, v.contiguous(), self.softmax_scale, causal=True, window=self.window)
     return ops.linear(o.reshape(B, S, h * self.v_dim), self.wo)

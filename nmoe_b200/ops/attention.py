@@ -99,6 +99,53 @@ class _Attention(torch.autograd.Function):
     return dq, dk, dv, ds, None, None
 
 
+class _MLAAttention(torch.autograd.Function):
+  """MLA core attention reading k_nope / v straight out of the fused kv projection output and the
+  shared rotary key from its own tensor: the forward never materialises K [B,S,H,192] or a
+  contiguous V.  The backward assembles them once and uses the library fused backward."""
+
+  @staticmethod
+  def forward(ctx, q, kv, k_pe, scale, nope, vdim):
+    B, S, H, Dqk = q.shape
+    rope = Dqk - nope
+    q, kv, k_pe = q.contiguous(), kv.contiguous(), k_pe.contiguous()
+    o = torch.empty(B, S, H, vdim, dtype=q.dtype, device=q.device)
+    st = status_buffer(q.device)
+    row_kv = H * (nope + vdim)
+    L.check(L.lib().nmoe_attn_fwd_ex(
+      L.ptr(q), H * Dqk, Dqk, L.ptr(kv), row_kv, nope + vdim, 0, nope // 64, L.ptr(k_pe), rope, 0, 0,
+      L.ptr(kv), row_kv, nope + vdim, nope, L.ptr(o), None, None, B, S, H, H, Dqk, vdim, 0, L.c_float(scale),
+      L.ptr(st), L.stream()), "attn_fwd(mla)")
+    ctx.save_for_backward(q, kv, k_pe)
+    ctx.args = (scale, nope, vdim)
+    return o
+
+  @staticmethod
+  def backward(ctx, do):
+    q, kv, k_pe = ctx.saved_tensors
+    scale, nope, vdim = ctx.args
+    B, S, H, _ = q.shape
+    with torch.enable_grad():
+      qd, kvd, ped = (t.detach().requires_grad_() for t in (q, kv, k_pe))
+      k = torch.cat((kvd[..., :nope], ped.expand(B, S, H, ped.size(-1))), dim=-1)
+      v = kvd[..., nope:]
+      o2 = F.scaled_dot_product_attention(qd.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=True,
+                                          scale=scale).transpose(1, 2)
+      dq, dkv, dpe = torch.autograd.grad(o2, (qd, kvd, ped), do)
+    return dq, dkv, dpe, None, None, None
+
+
+def mla_attention(q: torch.Tensor, kv: torch.Tensor, k_pe: torch.Tensor, scale: float, nope: int, vdim: int) -> torch.Tensor:
+  """q [B,S,H,nope+rope] (rotary applied), kv [B,S,H,nope+vdim] (k_nope | v per head), k_pe [B,S,1,rope]
+  (rotary applied, shared by all heads) -> [B,S,H,vdim], full causal."""
+  rope = q.size(-1) - nope
+  if q.is_cuda and q.dtype == torch.bfloat16 and (q.size(-1), vdim) in _KERNEL_DIMS and nope % 64 == 0 and rope % 64 == 0:
+    return _MLAAttention.apply(q, kv, k_pe, scale, nope, vdim)
+  B, S, H, _ = q.shape
+  k = torch.cat((kv[..., :nope], k_pe.expand(B, S, H, rope)), dim=-1)
+  return attention(q, k, kv[..., nope:].contiguous(), scale)
+
+
 def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, *, causal: bool = True,
               window: int = 0, sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
   if not q.is_cuda:

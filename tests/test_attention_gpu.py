@@ -67,3 +67,22 @@ def test_attention_backward_paths():
       assert _rel(a.cpu(), b) < 3e-2
     if use_sinks:
       assert _rel(sinks.grad.cpu(), sf.grad) < 5e-2
+
+
+def test_mla_attention_split_sources_matches_materialised():
+  from nmoe_b200.ops.attention import attention, mla_attention
+  torch.manual_seed(2)
+  B, S, H, nope, rope, vd = 2, 384, 4, 128, 64, 128
+  q = torch.randn(B, S, H, nope + rope, device="cuda").bfloat16().requires_grad_()
+  kv = torch.randn(B, S, H, nope + vd, device="cuda").bfloat16().requires_grad_()
+  pe = torch.randn(B, S, 1, rope, device="cuda").bfloat16().requires_grad_()
+  o = mla_attention(q, kv, pe, 192 ** -0.5, nope, vd)
+  g = torch.randn_like(o)
+  o.backward(g)
+  q2, kv2, pe2 = (t.detach().clone().requires_grad_() for t in (q, kv, pe))
+  k = torch.cat((kv2[..., :nope], pe2.expand(B, S, H, rope)), -1)
+  o2 = attention(q2, k, kv2[..., nope:].contiguous(), 192 ** -0.5)
+  o2.backward(g)
+  assert torch.equal(o, o2)
+  for a, b in ((q.grad, q2.grad), (kv.grad, kv2.grad), (pe.grad, pe2.grad)):
+    assert _rel(a, b) < 2e-2

@@ -1,0 +1,83 @@
+"""Evaluation stack on CPU with a toy model, the `bytes` tokenizer and local JSONL tasks."""
+import json
+
+import torch
+
+from nmoe_b200.config import Config
+from nmoe_b200.eval import choices, execution, run_gen
+from nmoe_b200.eval.tasks import gpqa, gsm8k, humaneval
+from nmoe_b200.train import Trainer
+
+
+def _cfg(**kw):
+  base = dict(vocab_size=257, eos_token_id=256, tokenizer="bytes", dim=64, n_layers=2, n_heads=2, inter_dim=128,
+              moe_inter_dim=32, n_routed_experts=4, n_activated_experts=2, n_shared_experts=1, n_dense_layers=1,
+              q_lora_rank=32, kv_lora_rank=16, qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=16, batch_size=2,
+              seq_len=64, max_position_embeddings=512, activation_checkpoint="none")
+  base.update(kw)
+  return Config(**base)
+
+
+def test_chunked_lse_and_argmax_match_dense():
+  torch.manual_seed(0)
+  h, w = torch.randn(7, 32), torch.randn(1000, 32)
+  dense = torch.logsumexp((h @ w.t()) * 0.125, -1)
+  assert torch.allclose(choices.logsumexp_vocab_chunked(h, w, logit_scale=0.125, chunk=64), dense, atol=1e-5)
+  assert torch.equal(run_gen.argmax_vocab_chunked(h, w, chunk=64), (h @ w.t()).argmax(-1))
+  v, i = run_gen.topk_vocab_chunked(h, w, 5, chunk=64)
+  assert torch.equal(i, ((h @ w.t()) * 0.125).topk(5, -1).indices)
+
+
+def test_choice_eval_runs_and_option_scores_are_loglikelihoods(tmp_path):
+  torch.manual_seed(1)
+  cfg = _cfg()
+  tr = Trainer(cfg)
+  task_file = tmp_path / "t.jsonl"
+  with open(task_file, "w") as f:
+    for i in range(6):
+      f.write(json.dumps({"question": f"what is {i}?", "choices": ["yes", "no", "maybe"], "answer": i % 3}) + "\n")
+  toml = tmp_path / "tasks.toml"
+  toml.write_text(f'[tasks.toy]\nkind = "choices"\nsource = "jsonl:{task_file}"\n[groups]\ncore = ["toy"]\n')
+  res = choices.run_eval(tr.model, cfg, rank=0, world=1, max_examples=6, tasks_file=str(toml))
+  assert res["toy"]["n"] == 6 and 0.0 <= res["toy"]["acc"] <= 1.0
+  # score of an option == sum of per-token log-softmax from full logits
+  from nmoe_b200.data.transforms import get_tokenizer
+  from nmoe_b200.eval.adapters import Choice
+  enc = get_tokenizer("bytes")
+  ex = Choice("Question: hi\nAnswer:", ["yes", "no"], 0)
+  tr.model.eval()
+  s = choices.score_options(tr.model, enc, ex, pad_to=64, pad_id=256)
+  p = enc.encode_ordinary(ex.prompt); o = enc.encode_ordinary(" yes")
+  toks = torch.tensor([(p + o) + [256] * (64 - len(p + o))])
+  with torch.no_grad():
+    lp = torch.log_softmax(tr.model(toks)[0].float(), -1)
+  want = sum(lp[len(p) - 1 + j, o[j]].item() for j in range(len(o)))
+  assert abs(s[0] - want) < 1e-3
+
+
+def test_lockstep_generation_runs_fixed_number_of_forwards():
+  torch.manual_seed(2)
+  tr = Trainer(_cfg())
+  tr.model.eval()
+  calls = {"n": 0}
+  orig = tr.model.hidden
+  def counted(t):
+    calls["n"] += 1
+    return orig(t)
+  tr.model.hidden = counted
+  out = run_gen.generate_lockstep(tr.model, [72, 105], max_new=5, eos_id=256, steps_global=8)
+  assert calls["n"] == 8 and len(out) <= 5
+  calls["n"] = 0
+  assert run_gen.generate_lockstep(tr.model, [72], max_new=5, eos_id=256, steps_global=8, active=False) == []
+  assert calls["n"] == 8
+
+
+def test_task_scorers_and_sandbox():
+  assert gsm8k.is_correct("so the total is 1,234.", "#### 1234")
+  assert not gsm8k.is_correct("no number", "#### 5")
+  assert gpqa.is_correct(" B", "B") and gpqa.extract_answer("the answer is c") == "C"
+  assert humaneval.truncate("    return 1\n\ndef other():\n  pass") == "    return 1\n"
+  ok = execution.humaneval_check("def add(a, b):\n", "    return a + b\n", "def check(f):\n    assert f(1, 2) == 3\n", "add")
+  bad = execution.humaneval_check("def add(a, b):\n", "    return a - b\n", "def check(f):\n    assert f(1, 2) == 3\n", "add")
+  assert ok and not bad
+  assert execution.run_python("while True: pass", timeout_s=1.0) == (False, "timeout")
