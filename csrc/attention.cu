@@ -27,9 +27,10 @@
 
 namespace nmoe {
 
-constexpr int kAttnThreads = 192;
-constexpr int ATT_BM = 128;    // query rows per CTA
-constexpr int ATT_BN = 128;    // keys per block
+constexpr int kAttnThreads = 320;   // warp 0: TMA, warp 1: MMA, warps 2-9: softmax (two query tiles x four quadrants)
+constexpr int ATT_BM = 128;         // query rows per tile
+constexpr int ATT_TILES = 2;        // query tiles per CTA, sharing every K/V block that is loaded
+constexpr int ATT_BN = 64;          // keys per block
 constexpr uint64_t kAttnWaitNs = 2000000000ull;
 constexpr float kRescaleThreshold = 8.f;   // log2 units
 
@@ -82,14 +83,31 @@ NMOE_DEVICE void tmem_st_32x32b_x16(uint32_t taddr, const uint32_t* r) {
         "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
       : "memory");
 }
+NMOE_DEVICE float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 template <int DQK, int DV>
 struct AttnSmem {
-  static constexpr int kQ = ATT_BM * DQK * 2;
+  static constexpr int kQTile = ATT_BM * DQK * 2;
+  static constexpr int kQ = ATT_TILES * kQTile;
   static constexpr int kK = ATT_BN * DQK * 2;
   static constexpr int kV = ATT_BN * DV * 2;
   static constexpr int kBytes = kQ + 2 * kK + 2 * kV + 1024 + 256;
 };
+
+struct TileRange { int q0, kb_start, kb_end; };
+
+NMOE_DEVICE TileRange tile_range(const AttnParams& p, int q0) {
+  TileRange r;
+  r.q0 = q0;
+  if (q0 >= p.S) { r.kb_start = 0; r.kb_end = 0; return r; }
+  r.kb_end = min((q0 + ATT_BM + ATT_BN - 1) / ATT_BN, (p.S + ATT_BN - 1) / ATT_BN);
+  r.kb_start = p.window > 0 ? max(0, (q0 - p.window + 1) / ATT_BN) : 0;
+  return r;
+}
 
 template <int DQK, int DV>
 __global__ void __launch_bounds__(kAttnThreads, 1)
@@ -107,30 +125,31 @@ k_attn_fwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
   uint64_t* k_empty = bars + 3;       // [2]
   uint64_t* v_full = bars + 5;        // [2]
   uint64_t* v_empty = bars + 7;       // [2]
-  uint64_t* s_full = bars + 9;        // [2]
-  uint64_t* p_full = bars + 11;       // [2]
-  uint64_t* pv_done = bars + 13;      // [1]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+  uint64_t* s_full = bars + 9;        // [tile][buf]
+  uint64_t* p_full = bars + 13;       // [tile][buf]
+  uint64_t* pv_done = bars + 17;      // [tile]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 19);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // heavy (late) query tiles first: better tail behaviour under the causal mask
-  const int q_tile = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);
+  const int q_blk = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);
   const int h = blockIdx.y, b = blockIdx.z;
-  const int q0 = q_tile * ATT_BM;
+  const int q0 = q_blk * ATT_BM * ATT_TILES;
   const int hkv = h / (p.Hq / p.Hkv);
-  const int kb_end = min((q0 + ATT_BM + ATT_BN - 1) / ATT_BN, (p.S + ATT_BN - 1) / ATT_BN);
-  const int kb_start = p.window > 0 ? max(0, (q0 - p.window + 1) / ATT_BN) : 0;
-  const int n_blocks = kb_end - kb_start;
+  const TileRange tr0 = tile_range(p, q0), tr1 = tile_range(p, q0 + ATT_BM);
+  const int lo = tr0.kb_start;                      // tile 0 starts no later and ends no later than tile 1
+  const int hi = max(tr0.kb_end, tr1.kb_end);
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
       mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
-      mbar_init(&s_full[i], 1); mbar_init(&p_full[i], 4);
     }
-    mbar_init(pv_done, 1);
+    for (int i = 0; i < 4; ++i) { mbar_init(&s_full[i], 1); mbar_init(&p_full[i], 4); }
+    mbar_init(&pv_done[0], 1);
+    mbar_init(&pv_done[1], 1);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -142,7 +161,6 @@ k_attn_fwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_o = tmem_base + 256;
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA loads
@@ -151,11 +169,14 @@ k_attn_fwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       const int row_q = b * p.S + q0;
       mbar_expect_tx(q_full, SM::kQ);
 #pragma unroll
-      for (int c = 0; c < DQK / 64; ++c) tma_load_2d(sQ + c * (ATT_BM * 128), &tmQ, q_full, h * p.q_hs + c * 64, row_q);
-      for (int i = 0; i < n_blocks; ++i) {
-        const int st = i & 1;
-        const uint32_t ph = (i >> 1) & 1;
-        const int row_k = b * p.S + (kb_start + i) * ATT_BN;
+      for (int t = 0; t < ATT_TILES; ++t)
+#pragma unroll
+        for (int c = 0; c < DQK / 64; ++c)
+          tma_load_2d(sQ + t * SM::kQTile + c * (ATT_BM * 128), &tmQ, q_full, h * p.q_hs + c * 64, row_q + t * ATT_BM);
+      for (int i = lo; i < hi; ++i) {
+        const int gi = i - lo, st = gi & 1;
+        const uint32_t ph = (gi >> 1) & 1;
+        const int row_k = b * p.S + i * ATT_BN;
         if (!attn_wait(&k_empty[st], ph ^ 1, abort_flag)) { report_status(p.status, kStatusWaitTimeout, 700, i, 0); *abort_flag = 1; break; }
         mbar_expect_tx(&k_full[st], SM::kK);
 #pragma unroll
@@ -179,127 +200,133 @@ k_attn_fwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     if (elect_one()) {
       constexpr uint32_t idesc_s = make_idesc_bf16(ATT_BM, ATT_BN, 0, 0);
       constexpr uint32_t idesc_pv = make_idesc_bf16(ATT_BM, DV, 0, 1);
+      const TileRange trs[2] = {tr0, tr1};
+      bool ok = hi > lo && attn_wait(q_full, 0, abort_flag);
+      // S = Q_t K_i^T for both tiles that see block i; releases the K stage afterwards
       auto issue_s = [&](int i) -> bool {
-        const int st = i & 1;
-        if (!attn_wait(&k_full[st], (i >> 1) & 1, abort_flag)) { report_status(p.status, kStatusWaitTimeout, 710, i, 0); *abort_flag = 1; return false; }
+        const int gi = i - lo, st = gi & 1;
+        if (!attn_wait(&k_full[st], (gi >> 1) & 1, abort_flag)) { report_status(p.status, kStatusWaitTimeout, 710, i, 0); *abort_flag = 1; return false; }
         tc_fence_after_sync();
-        const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK + st * SM::kK);
+        const uint32_t ka = smem_u32(sK + st * SM::kK);
 #pragma unroll
-        for (int j = 0; j < DQK / 16; ++j) {
-          const uint32_t off = (j >> 2) * (ATT_BM * 128) + (j & 3) * 32;
-          mma_f16_ss(tmem_base + st * ATT_BN, make_smem_desc(qa + off, 0, 1024, kSwizzle128B),
-                     make_smem_desc(ka + off, 0, 1024, kSwizzle128B), idesc_s, j != 0 ? 1u : 0u);
+        for (int t = 0; t < ATT_TILES; ++t) {
+          if (i < trs[t].kb_start || i >= trs[t].kb_end) continue;
+          const int li = i - trs[t].kb_start;
+          const uint32_t qa = smem_u32(sQ + t * SM::kQTile);
+          const uint32_t d = tmem_base + t * 128 + (li & 1) * ATT_BN;
+#pragma unroll
+          for (int j = 0; j < DQK / 16; ++j)
+            mma_f16_ss(d, make_smem_desc(qa + (j >> 2) * (ATT_BM * 128) + (j & 3) * 32, 0, 1024, kSwizzle128B),
+                       make_smem_desc(ka + (j >> 2) * (ATT_BN * 128) + (j & 3) * 32, 0, 1024, kSwizzle128B), idesc_s,
+                       j != 0 ? 1u : 0u);
+          mma_commit(&s_full[t * 2 + (li & 1)]);
         }
         mma_commit(&k_empty[st]);
-        mma_commit(&s_full[st]);
         return true;
       };
-      bool ok = n_blocks > 0 && attn_wait(q_full, 0, abort_flag);
-      if (ok) ok = issue_s(0);
-      for (int i = 0; ok && i < n_blocks; ++i) {
-        const int st = i & 1;
-        if (i + 1 < n_blocks) { ok = issue_s(i + 1); if (!ok) break; }
-        if (!attn_wait(&p_full[st], (i >> 1) & 1, abort_flag)) { report_status(p.status, kStatusWaitTimeout, 711, i, 0); *abort_flag = 1; break; }
-        if (!attn_wait(&v_full[st], (i >> 1) & 1, abort_flag)) { report_status(p.status, kStatusWaitTimeout, 712, i, 0); *abort_flag = 1; break; }
-        tc_fence_after_sync();
+      if (ok) ok = issue_s(lo);
+      for (int i = lo; ok && i < hi; ++i) {
+        const int gi = i - lo, st = gi & 1;
+        if (i + 1 < hi) { ok = issue_s(i + 1); if (!ok) break; }
+        if (!attn_wait(&v_full[st], (gi >> 1) & 1, abort_flag)) { report_status(p.status, kStatusWaitTimeout, 712, i, 0); *abort_flag = 1; break; }
         const uint32_t va = smem_u32(sV + st * SM::kV);
 #pragma unroll
-        for (int j = 0; j < ATT_BN / 16; ++j)
-          mma_f16_ts(tmem_o, tmem_base + st * ATT_BN + j * 8, make_smem_desc(va + j * 2048, ATT_BN * 128, 1024, kSwizzle128B),
-                     idesc_pv, (i | j) != 0 ? 1u : 0u);
+        for (int t = 0; t < ATT_TILES; ++t) {
+          if (i < trs[t].kb_start || i >= trs[t].kb_end) continue;
+          const int li = i - trs[t].kb_start;
+          if (!attn_wait(&p_full[t * 2 + (li & 1)], (li >> 1) & 1, abort_flag)) { report_status(p.status, kStatusWaitTimeout, 711, i, t); *abort_flag = 1; ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t a_t = tmem_base + t * 128 + (li & 1) * ATT_BN;
+#pragma unroll
+          for (int j = 0; j < ATT_BN / 16; ++j)
+            mma_f16_ts(tmem_base + 256 + t * 128, a_t + j * 8, make_smem_desc(va + j * 2048, ATT_BN * 128, 1024, kSwizzle128B),
+                       idesc_pv, (li | j) != 0 ? 1u : 0u);
+          mma_commit(&pv_done[t]);
+        }
         mma_commit(&v_empty[st]);
-        mma_commit(pv_done);
       }
     }
     __syncwarp();
   } else {
-    // ------------------------------------------------------------ softmax + epilogue (one 32-row quadrant per warp)
+    // ------------------------------------------------------------ softmax + epilogue: warp -> (tile, 32-row quadrant)
+    const int tile = (warp - 2) >> 2;
     const int q = warp & 3;
-    const int row = q0 + q * 32 + lane;              // query position inside the sequence
+    const TileRange tr = tile ? tr1 : tr0;
+    const int n_blocks = tr.kb_end - tr.kb_start;
+    const int row = tr.q0 + q * 32 + lane;           // query position inside the sequence
     const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
+    const uint32_t tmem_o = tmem_base + 256 + tile * 128;
     float m = -1e30f, l = 0.f;
     if (p.sinks != nullptr) { m = p.sinks[h] * 1.4426950408889634f; l = 1.f; }
     bool ok = true;
     for (int i = 0; i < n_blocks; ++i) {
-      const int st = i & 1;
-      const uint32_t s_addr = tmem_base + lane_addr + st * ATT_BN;
-      ok = attn_wait(&s_full[st], (i >> 1) & 1, abort_flag);
+      const int bf = i & 1;
+      const uint32_t s_addr = tmem_base + lane_addr + tile * 128 + bf * ATT_BN;
+      ok = attn_wait(&s_full[tile * 2 + bf], (i >> 1) & 1, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
-      if (!ok) { if (lane == 0) report_status(p.status, kStatusWaitTimeout, 720, i, 0); *abort_flag = 1; break; }
+      if (!ok) { if (lane == 0) report_status(p.status, kStatusWaitTimeout, 720, i, tile); *abort_flag = 1; break; }
       tc_fence_after_sync();
-      const int k0 = (kb_start + i) * ATT_BN;
-      const bool need_mask = (k0 + ATT_BN - 1 > q0) || (p.window > 0 && k0 <= q0 + ATT_BM - 1 - p.window) || (k0 + ATT_BN > p.S);
-      // pass 1: row maximum
+      const int k0 = (tr.kb_start + i) * ATT_BN;
+      const bool need_mask = (k0 + ATT_BN - 1 > tr.q0) || (p.window > 0 && k0 <= tr.q0 + ATT_BM - 1 - p.window) || (k0 + ATT_BN > p.S);
+      uint32_t r[ATT_BN];
+      tmem_ld_32x32b_x32(s_addr, r);
+      tmem_ld_32x32b_x32(s_addr + 32, r + 32);
+      tmem_ld_wait();
       float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < ATT_BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(s_addr + c * 32, r);
-        tmem_ld_wait();
+      if (need_mask) {
 #pragma unroll
-        for (int t = 0; t < 32; ++t) {
-          float v = __uint_as_float(r[t]);
-          if (need_mask) {
-            const int j = k0 + c * 32 + t;
-            if (j > row || j >= p.S || (p.window > 0 && j <= row - p.window)) v = -INFINITY;
-          }
-          mx = fmaxf(mx, v);
+        for (int t = 0; t < ATT_BN; ++t) {
+          const int j = k0 + t;
+          if (j > row || j >= p.S || (p.window > 0 && j <= row - p.window)) r[t] = 0xff800000u;   // -inf
         }
       }
+#pragma unroll
+      for (int t = 0; t < ATT_BN; ++t) mx = fmaxf(mx, __uint_as_float(r[t]));
       const float m_cand = fmaxf(m, mx * p.scale_log2);
-      float alpha = 1.f;
       bool grow = (m_cand - m > kRescaleThreshold);
-      if (i == 0) { grow = false; if (m_cand > m) { l *= exp2f(m - m_cand); m = m_cand; } }
+      if (i == 0) { grow = false; if (m_cand > m) { l *= fast_exp2(m - m_cand); m = m_cand; } }
       if (__any_sync(0xffffffffu, grow)) {
         // O must be final for block i-1 before it is rescaled
-        ok = attn_wait(pv_done, (i - 1) & 1, abort_flag);
+        ok = attn_wait(&pv_done[tile], (i - 1) & 1, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
-        if (!ok) { if (lane == 0) report_status(p.status, kStatusWaitTimeout, 721, i, 0); *abort_flag = 1; break; }
+        if (!ok) { if (lane == 0) report_status(p.status, kStatusWaitTimeout, 721, i, tile); *abort_flag = 1; break; }
         tc_fence_after_sync();
-        if (grow) { alpha = exp2f(m - m_cand); m = m_cand; l *= alpha; }
+        float alpha = 1.f;
+        if (grow) { alpha = fast_exp2(m - m_cand); m = m_cand; l *= alpha; }
 #pragma unroll 1
         for (int c = 0; c < DV / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32b_x32(tmem_o + lane_addr + c * 32, r);
+          uint32_t o[32];
+          tmem_ld_32x32b_x32(tmem_o + lane_addr + c * 32, o);
           tmem_ld_wait();
 #pragma unroll
-          for (int t = 0; t < 32; ++t) r[t] = __float_as_uint(__uint_as_float(r[t]) * alpha);
-          tmem_st_32x32b_x32(tmem_o + lane_addr + c * 32, r);
+          for (int t = 0; t < 32; ++t) o[t] = __float_as_uint(__uint_as_float(o[t]) * alpha);
+          tmem_st_32x32b_x32(tmem_o + lane_addr + c * 32, o);
         }
         tmem_st_wait();
       }
-      // pass 2: P = 2^(s*scale - m), written back as bf16 pairs into the first 64 columns of this S buffer
+      // P = 2^(s*scale - m) as bf16 pairs, written over the first 32 columns of this S buffer
       float rs = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < ATT_BN / 32; ++c) {
-        uint32_t r[32], pk[16];
-        tmem_ld_32x32b_x32(s_addr + c * 32, r);
-        tmem_ld_wait();
+      uint32_t pk[ATT_BN / 2];
 #pragma unroll
-        for (int t = 0; t < 32; t += 2) {
-          float v0 = __uint_as_float(r[t]), v1 = __uint_as_float(r[t + 1]);
-          if (need_mask) {
-            const int j = k0 + c * 32 + t;
-            if (j > row || j >= p.S || (p.window > 0 && j <= row - p.window)) v0 = -INFINITY;
-            if (j + 1 > row || j + 1 >= p.S || (p.window > 0 && j + 1 <= row - p.window)) v1 = -INFINITY;
-          }
-          const float p0 = exp2f(fmaf(v0, p.scale_log2, -m)), p1 = exp2f(fmaf(v1, p.scale_log2, -m));
-          rs += p0 + p1;
-          pk[t >> 1] = pack_bf16x2(p0, p1);
-        }
-        tmem_st_32x32b_x16(s_addr + c * 16, pk);
+      for (int t = 0; t < ATT_BN; t += 2) {
+        const float p0 = fast_exp2(fmaf(__uint_as_float(r[t]), p.scale_log2, -m));
+        const float p1 = fast_exp2(fmaf(__uint_as_float(r[t + 1]), p.scale_log2, -m));
+        rs += p0 + p1;
+        pk[t >> 1] = pack_bf16x2(p0, p1);
       }
       l += rs;
+      tmem_st_32x32b_x16(s_addr, pk);
+      tmem_st_32x32b_x16(s_addr + 16, pk + 16);
       tmem_st_wait();
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&p_full[st]);
+      if (lane == 0) mbar_arrive(&p_full[tile * 2 + bf]);
     }
     // epilogue
     if (ok && n_blocks > 0) {
-      ok = attn_wait(pv_done, (n_blocks - 1) & 1, abort_flag);
+      ok = attn_wait(&pv_done[tile], (n_blocks - 1) & 1, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
-      if (!ok) { if (lane == 0) report_status(p.status, kStatusWaitTimeout, 722, 0, 0); *abort_flag = 1; }
+      if (!ok) { if (lane == 0) report_status(p.status, kStatusWaitTimeout, 722, 0, tile); *abort_flag = 1; }
     }
     if (ok) {
       tc_fence_after_sync();
@@ -308,22 +335,22 @@ k_attn_fwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       __nv_bfloat16* orow = p.O + (static_cast<size_t>(b) * p.S + row) * (static_cast<size_t>(p.Hq) * DV) + static_cast<size_t>(h) * DV;
 #pragma unroll 1
       for (int c = 0; c < DV / 32; ++c) {
-        uint32_t r[32];
+        uint32_t o[32];
         if (n_blocks > 0) {
-          tmem_ld_32x32b_x32(tmem_o + lane_addr + c * 32, r);
+          tmem_ld_32x32b_x32(tmem_o + lane_addr + c * 32, o);
           tmem_ld_wait();
         } else {
 #pragma unroll
-          for (int t = 0; t < 32; ++t) r[t] = 0u;
+          for (int t = 0; t < 32; ++t) o[t] = 0u;
         }
         if (row_ok) {
 #pragma unroll
           for (int t = 0; t < 4; ++t) {
             int4 v;
-            v.x = pack_bf16x2(__uint_as_float(r[8 * t]) * inv_l, __uint_as_float(r[8 * t + 1]) * inv_l);
-            v.y = pack_bf16x2(__uint_as_float(r[8 * t + 2]) * inv_l, __uint_as_float(r[8 * t + 3]) * inv_l);
-            v.z = pack_bf16x2(__uint_as_float(r[8 * t + 4]) * inv_l, __uint_as_float(r[8 * t + 5]) * inv_l);
-            v.w = pack_bf16x2(__uint_as_float(r[8 * t + 6]) * inv_l, __uint_as_float(r[8 * t + 7]) * inv_l);
+            v.x = pack_bf16x2(__uint_as_float(o[8 * t]) * inv_l, __uint_as_float(o[8 * t + 1]) * inv_l);
+            v.y = pack_bf16x2(__uint_as_float(o[8 * t + 2]) * inv_l, __uint_as_float(o[8 * t + 3]) * inv_l);
+            v.z = pack_bf16x2(__uint_as_float(o[8 * t + 4]) * inv_l, __uint_as_float(o[8 * t + 5]) * inv_l);
+            v.w = pack_bf16x2(__uint_as_float(o[8 * t + 6]) * inv_l, __uint_as_float(o[8 * t + 7]) * inv_l);
             reinterpret_cast<int4*>(orow + c * 32)[t] = v;
           }
         }
@@ -344,15 +371,16 @@ k_attn_fwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
   }
 }
 
-static int attn_map(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t pitch_bytes) {
-  using Key = std::tuple<const void*, uint64_t, uint64_t, uint64_t>;
+static int attn_map(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t pitch_bytes,
+                    uint32_t box_rows) {
+  using Key = std::tuple<const void*, uint64_t, uint64_t, uint64_t, uint32_t>;
   static std::map<Key, CUtensorMap> cache;
   static std::mutex mu;
-  Key k{base, inner, outer, pitch_bytes};
+  Key k{base, inner, outer, pitch_bytes, box_rows};
   std::lock_guard<std::mutex> g(mu);
   auto it = cache.find(k);
   if (it != cache.end()) { *out = it->second; return 0; }
-  int rc = make_tensor_map_2d(out, base, kTmaBf16, inner, outer, pitch_bytes, 64, 128, kTmaSwizzle128);
+  int rc = make_tensor_map_2d(out, base, kTmaBf16, inner, outer, pitch_bytes, 64, box_rows, kTmaSwizzle128);
   if (rc != 0) return rc;
   if (cache.size() > 1024) cache.clear();
   cache[k] = *out;
@@ -369,7 +397,7 @@ static int attn_launch(const CUtensorMap& tq, const CUtensorMap& tk, const CUten
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
-  dim3 grid((p.S + ATT_BM - 1) / ATT_BM, p.Hq, p.B);
+  dim3 grid((p.S + ATT_BM * ATT_TILES - 1) / (ATT_BM * ATT_TILES), p.Hq, p.B);
   kern<<<grid, kAttnThreads, AttnSmem<DQK, DV>::kBytes, st>>>(tq, tk, tk2, tv, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : static_cast<int>(e);
@@ -399,13 +427,13 @@ extern "C" int nmoe_attn_fwd_ex(const void* q, int q_row, int q_hs, const void* 
   p.sinks = sinks; p.O = static_cast<__nv_bfloat16*>(o); p.lse = lse; p.status = static_cast<StatusRecord*>(status);
   CUtensorMap tq, tk, tk2, tv;
   const uint64_t rows = static_cast<uint64_t>(B) * S;
-  int rc = attn_map(&tq, q, q_row, rows, static_cast<uint64_t>(q_row) * 2);
+  int rc = attn_map(&tq, q, q_row, rows, static_cast<uint64_t>(q_row) * 2, ATT_BM);
   if (rc) return rc;
-  rc = attn_map(&tk, k1, k1_row, rows, static_cast<uint64_t>(k1_row) * 2);
+  rc = attn_map(&tk, k1, k1_row, rows, static_cast<uint64_t>(k1_row) * 2, ATT_BN);
   if (rc) return rc;
-  rc = attn_map(&tk2, k2 ? k2 : k1, k2 ? k2_row : k1_row, rows, static_cast<uint64_t>(k2 ? k2_row : k1_row) * 2);
+  rc = attn_map(&tk2, k2 ? k2 : k1, k2 ? k2_row : k1_row, rows, static_cast<uint64_t>(k2 ? k2_row : k1_row) * 2, ATT_BN);
   if (rc) return rc;
-  rc = attn_map(&tv, v, v_row, rows, static_cast<uint64_t>(v_row) * 2);
+  rc = attn_map(&tv, v, v_row, rows, static_cast<uint64_t>(v_row) * 2, ATT_BN);
   if (rc) return rc;
   if (Dqk == 192 && Dv == 128) return attn_launch<192, 128>(tq, tk, tk2, tv, p, st);
   if (Dqk == 128 && Dv == 128) return attn_launch<128, 128>(tq, tk, tk2, tv, p, st);

@@ -105,6 +105,37 @@ class ExpertAdamW:
         self.state[int(i)][k].copy_(v)
 
 
+class _MuonExperts:
+  """Adapter giving ``ops.muon.Muon`` the interface the train loop expects from the expert optimizer."""
+
+  def __init__(self, params: List[torch.nn.Parameter], cfg: Config):
+    from .ops.muon import Muon
+    self.inner = Muon(params, lr=float(cfg.lr_expert), momentum=cfg.muon_momentum, weight_decay=cfg.weight_decay)
+    self.params = params
+    self.gradnorm_sq: Optional[torch.Tensor] = None
+
+  def begin_step(self, lr: float, gradnorm_sq: Optional[torch.Tensor] = None) -> None:
+    self.inner.lr = lr
+    self.gradnorm_sq = gradnorm_sq
+
+  def step(self) -> None:
+    if self.gradnorm_sq is not None:
+      for p in self.params:
+        if p.grad is not None:
+          ops.sumsq(p.grad.reshape(-1), self.gradnorm_sq)
+    self.inner.step()
+
+  @property
+  def step_count(self) -> int:
+    return self.inner.step_count
+
+  def state_dict(self) -> dict:
+    return self.inner.state_dict()
+
+  def load_state_dict(self, sd: dict) -> None:
+    self.inner.load_state_dict(sd)
+
+
 def build_param_groups(model: torch.nn.Module, cfg: Config):
   """Returns (expert_params, dense_groups) with the reference's name-based rules."""
   expert_params, _ = model.param_sets()
@@ -138,7 +169,11 @@ class Optimizer:
                group: Optional[dist.ProcessGroup] = None):
     self.model, self.cfg = model, cfg
     expert_params, groups = build_param_groups(model, cfg)
-    self.expert = ExpertAdamW(expert_params, cfg, fuse_expert_in_backward) if expert_params else None
+    self.expert = None
+    if expert_params and cfg.expert_optimizer == "muon":
+      self.expert = _MuonExperts(expert_params, cfg)
+    elif expert_params:
+      self.expert = ExpertAdamW(expert_params, cfg, fuse_expert_in_backward)
     self.dense = zero2.Zero2(groups, cfg, group=group)
     self.lrs = scheduled_lrs(0, 0, cfg)
 

@@ -88,3 +88,17 @@ def test_adamw_flat():
     R.adamw_step(pr, g.float(), mr, vr, lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, step=step)
     pr, mr, vr = pr.bfloat16().float(), mr.bfloat16().float(), vr.bfloat16().float()
   assert _rel(p, pr) < 2e-2
+
+
+def test_newton_schulz_orthogonalises():
+  from nmoe_b200.ops.muon import newton_schulz
+  from nmoe_b200.ref import ops as R
+  torch.manual_seed(5)
+  x = torch.randn(3, 128, 256, device="cuda").bfloat16()
+  y = newton_schulz(x)
+  ref = R.newton_schulz(x.float().cpu())
+  assert _rel(y.cpu(), ref) < 6e-2
+  s = torch.linalg.svdvals(y.float())
+  assert s.max() < 1.3 and s.min() > 0.5          # singular values pushed towards 1
+  t = newton_schulz(torch.randn(256, 128, device="cuda").bfloat16())
+  assert t.shape == (256, 128)

@@ -116,3 +116,21 @@ def test_masked_loss_ignores_eos_targets():
     per = F.cross_entropy(logits.reshape(-1, cfg.vocab_size), y.reshape(-1), reduction="none").view(2, 128)
   assert torch.allclose(base, per.mean(), atol=1e-5)
   assert torch.allclose(masked, per[:, 1::2].mean(), atol=1e-5)
+
+
+def test_muon_expert_optimizer_cpu():
+  from nmoe_b200.ops.muon import Muon, newton_schulz
+  torch.manual_seed(6)
+  w = torch.nn.Parameter(torch.randn(2, 16, 32))
+  y = newton_schulz(w.detach())
+  s = torch.linalg.svdvals(y)
+  assert s.max() < 1.3 and s.min() > 0.5
+  opt = Muon([w], lr=0.1, momentum=0.9)
+  target = torch.randn(2, 16, 32)
+  l0 = None
+  for _ in range(20):
+    loss = (w - target).pow(2).mean()
+    l0 = l0 or loss.item()
+    loss.backward()
+    opt.step()
+  assert loss.item() < l0
