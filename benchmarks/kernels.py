@@ -1,0 +1,113 @@
+"""Kernel micro-benchmarks (device-timed with CUDA events, L2 flushed between iterations).
+
+  python benchmarks/kernels.py gemm  --m 16384 --n 2048 --k 2048 [--a-mn] [--b-mn] [--bn 256]
+  python benchmarks/kernels.py mx    --m 16384 --n 2816 --k 2048
+  python benchmarks/kernels.py attn  --b 4 --s 4096 --h 16 --dqk 192 --dv 128 [--window 128]
+  python benchmarks/kernels.py moe   --tokens 16384 --hidden 2048 --inter 1408 --experts 64 --topk 6 [--dtype fp8]
+
+Each prints one JSON line with the time, achieved TFLOP/s or GB/s and the fraction of the measured
+peak (MEASURED_PEAKS.json next to the repository root, if present).  ``--iters 1 --warmup 1`` keeps a
+run short enough for a profiler capture.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+
+def peaks():
+  try:
+    return json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+  except OSError:
+    return {"bf16_tflops": 1590.0, "hbm_gbs": 6650.0, "fallback": True}
+
+
+def timed(fn, iters, warmup, flush):
+  for _ in range(warmup):
+    fn()
+  torch.cuda.synchronize()
+  total = 0.0
+  for _ in range(iters):
+    if flush is not None:
+      flush.zero_()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    fn()
+    e.record()
+    torch.cuda.synchronize()
+    total += s.elapsed_time(e)
+  return total / iters
+
+
+def main():
+  ap = argparse.ArgumentParser()
+  ap.add_argument("what", choices=["gemm", "mx", "attn", "moe"])
+  for k, d in (("m", 16384), ("n", 2048), ("k", 2048), ("bn", 0), ("b", 4), ("s", 4096), ("h", 16), ("dqk", 192), ("dv", 128),
+               ("window", 0), ("tokens", 16384), ("hidden", 2048), ("inter", 1408), ("experts", 64), ("topk", 6),
+               ("iters", 20), ("warmup", 3)):
+    ap.add_argument(f"--{k}", type=int, default=d)
+  ap.add_argument("--a-mn", action="store_true"); ap.add_argument("--b-mn", action="store_true")
+  ap.add_argument("--dtype", default="bf16"); ap.add_argument("--no-flush", action="store_true")
+  ap.add_argument("--backward", action="store_true")
+  a = ap.parse_args()
+  from nmoe_b200 import ops
+  from nmoe_b200.ops import tc_gemm as G
+  dev = torch.device("cuda")
+  pk = peaks()
+  flush = None if a.no_flush else torch.empty(256 << 20, dtype=torch.uint8, device=dev)   # > 126 MB L2
+  out = {"what": a.what}
+  if a.what == "gemm":
+    A = torch.randn((a.k, a.m) if a.a_mn else (a.m, a.k), device=dev).bfloat16()
+    B = torch.randn((a.k, a.n) if a.b_mn else (a.n, a.k), device=dev).bfloat16()
+    C = torch.empty(a.m, a.n, device=dev, dtype=torch.bfloat16)
+    ms = timed(lambda: G.gemm(A, B, a_mn=a.a_mn, b_mn=a.b_mn, out=C, bn=a.bn), a.iters, a.warmup, flush)
+    tf = 2.0 * a.m * a.n * a.k / ms / 1e9
+    out.update(shape=[a.m, a.n, a.k], a_mn=a.a_mn, b_mn=a.b_mn, ms=ms, tflops=tf, frac_of_measured_bf16_peak=tf / pk["bf16_tflops"])
+  elif a.what == "mx":
+    A = torch.randn(a.m, a.k, device=dev).bfloat16(); B = (torch.randn(a.n, a.k, device=dev) * 0.1).bfloat16()
+    aq, asf = ops.quant_mxfp8(A); bq, bsf = ops.quant_mxfp8(B)
+    C = torch.empty(a.m, a.n, device=dev, dtype=torch.bfloat16)
+    ms = timed(lambda: ops.gemm_mxfp8(aq, asf, bq, bsf, out=C, bn=a.bn), a.iters, a.warmup, flush)
+    tf = 2.0 * a.m * a.n * a.k / ms / 1e9
+    out.update(shape=[a.m, a.n, a.k], ms=ms, tflops=tf, frac_of_2x_measured_bf16_peak=tf / (2 * pk["bf16_tflops"]))
+  elif a.what == "attn":
+    from nmoe_b200.ops.attention import attention_forward
+    q = torch.randn(a.b, a.s, a.h, a.dqk, device=dev).bfloat16(); k = torch.randn_like(q)
+    v = torch.randn(a.b, a.s, a.h, a.dv, device=dev).bfloat16()
+    ms = timed(lambda: attention_forward(q, k, v, a.dqk ** -0.5, a.window), a.iters, a.warmup, flush)
+    keys = a.s / 2 if a.window == 0 else min(a.window, a.s / 2)
+    tf = 2.0 * a.b * a.h * a.s * keys * (a.dqk + a.dv) / ms / 1e9
+    out.update(shape=[a.b, a.s, a.h, a.dqk, a.dv], window=a.window, ms=ms, tflops=tf, frac_of_measured_bf16_peak=tf / pk["bf16_tflops"])
+  else:
+    from nmoe_b200.ops.quant import ExpertWeightCache
+    from nmoe_b200.parallel.rdep import Rdep
+    T, H, F, E, K = a.tokens, a.hidden, a.inter, a.experts, a.topk
+    rd = Rdep(H, E, K, T, device=dev, profile=a.dtype)
+    x = (torch.randn(T, H, device=dev) * 0.5).bfloat16().requires_grad_(a.backward)
+    W13 = (torch.randn(E, 2 * F, H, device=dev) * 0.02).bfloat16().requires_grad_(a.backward)
+    W2 = (torch.randn(E, H, F, device=dev) * 0.02).bfloat16().requires_grad_(a.backward)
+    eid = torch.stack([torch.randperm(E, device=dev)[:K] for _ in range(min(T, 4096))]).int().repeat((T + 4095) // 4096, 1)[:T].contiguous()
+    gates = torch.rand(T, K, device=dev)
+    wq = ExpertWeightCache().get(W13, W2) if a.dtype != "bf16" else None
+    g = torch.randn(T, H, device=dev).bfloat16()
+    def step():
+      o = rd.moe(x, gates, eid, W13, W2, False, wq)
+      if a.backward:
+        o.backward(g)
+    ms = timed(step, a.iters, a.warmup, flush)
+    fl = 2.0 * T * K * 3 * H * F * (3 if a.backward else 1) + (2.0 * T * K * 2 * F * H if a.backward else 0)
+    out.update(tokens=T, hidden=H, inter=F, experts=E, topk=K, dtype=a.dtype, backward=a.backward, ms=ms, tflops=fl / ms / 1e9)
+    rd.close()
+  G.check_status()
+  print(json.dumps(out))
+
+
+if __name__ == "__main__":
+  main()
