@@ -5,6 +5,7 @@ CPU tensors take the plain-PyTorch statement of the same contraction.
 """
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
@@ -32,6 +33,14 @@ def check_status(device: Optional[torch.device] = None) -> None:
     if rec[0] != 0:
       buf.zero_()
       raise L.NativeLibraryError(f"kernel reported status code={rec[0]} where={rec[1]} a={rec[2]} b={rec[3]} on {dev}")
+
+
+PAIR_MODE = os.environ.get("NMOE_GEMM_PAIR", "1") == "1"
+
+
+def use_pair(M: int, N: int) -> bool:
+  """The two-SM kernel (256x256 tiles, csrc/gemm2.cu) pays off once there are enough full tiles."""
+  return PAIR_MODE and M >= 512 and N >= 256 and N % 8 == 0
 
 
 def _rows(t: torch.Tensor) -> int:
@@ -64,6 +73,12 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     out = torch.empty(M, N, dtype=out_dtype, device=a.device)
   assert out.stride(1) == 1 and out.shape == (M, N)
   st = status_buffer(a.device)
+  if bn == 0 and use_pair(M, N):
+    L.check(L.lib().nmoe_gemm_bf16_pair(
+      L.ptr(a), L.ptr(b), L.ptr(out), M, N, K, L.c_ll(a.stride(0)), L.c_ll(b.stride(0)), L.c_ll(out.stride(0)),
+      int(a_mn), int(b_mn), 0, 1, None, None, None, L.c_ll(a.size(0)), L.c_ll(b.size(0)),
+      int(out.dtype == torch.float32), int(accumulate), L.ptr(st), L.stream()), "gemm_bf16_pair")
+    return out
   L.check(L.lib().nmoe_gemm_bf16(
     L.ptr(a), L.ptr(b), L.ptr(out), M, N, K, L.c_ll(a.stride(0)), L.c_ll(b.stride(0)), L.c_ll(out.stride(0)),
     int(a_mn), int(b_mn), 0, 1, None, None, None, L.c_ll(a.size(0)), L.c_ll(b.size(0)),
@@ -134,6 +149,12 @@ def grouped_wgrad(a: torch.Tensor, b: torch.Tensor, offs: torch.Tensor, E: int, 
     out = torch.empty(E, Ma, Nb, dtype=torch.bfloat16, device=a.device)
   assert out.is_contiguous()
   st = status_buffer(a.device)
+  if bn == 0 and use_pair(Ma, Nb):
+    L.check(L.lib().nmoe_gemm_bf16_pair(
+      L.ptr(a), L.ptr(b), L.ptr(out), Ma, Nb, 0, L.c_ll(Ma), L.c_ll(Nb), L.c_ll(Nb),
+      1, 1, 2, E, None, None, L.ptr(offs), L.c_ll(a.size(0)), L.c_ll(b.size(0)),
+      int(out.dtype == torch.float32), int(accumulate), L.ptr(st), L.stream()), "grouped_wgrad_bf16_pair")
+    return out
   L.check(L.lib().nmoe_gemm_bf16(
     L.ptr(a), L.ptr(b), L.ptr(out), Ma, Nb, 0, L.c_ll(Ma), L.c_ll(Nb), L.c_ll(Nb),
     1, 1, 2, E, None, None, L.ptr(offs), L.c_ll(a.size(0)), L.c_ll(b.size(0)),

@@ -100,3 +100,47 @@ def test_linear_autograd():
   _close(y, yf.detach())
   _close(x.grad, xf.grad)
   _close(w.grad, wf.grad)
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
+@pytest.mark.parametrize("M,N,K", [(512, 256, 64), (1024, 512, 320), (1000, 776, 200), (4096, 2048, 2048)])
+def test_pair_gemm(M, N, K, a_mn, b_mn):
+  """Two-SM (cta_group::2) kernel, selected automatically for M >= 512 and N >= 256."""
+  from nmoe_b200.ops import tc_gemm as G
+  assert G.use_pair(M, N)
+  torch.manual_seed(7)
+  A = torch.randn(M, K, device="cuda")
+  B = torch.randn(N, K, device="cuda")
+  a = (A.t().contiguous() if a_mn else A).bfloat16()
+  b = (B.t().contiguous() if b_mn else B).bfloat16()
+  ref = (a.float().t() if a_mn else a.float()) @ (b.float() if b_mn else b.float().t())
+  c = G.gemm(a, b, a_mn=a_mn, b_mn=b_mn)
+  c1 = G.gemm(a, b, a_mn=a_mn, b_mn=b_mn, bn=256)        # one-SM kernel for comparison
+  torch.cuda.synchronize()
+  G.check_status()
+  _close(c, ref)
+  _close(c, c1.float(), tol=1e-2)
+
+
+def test_pair_grouped_wgrad_and_fp32_accumulate():
+  from nmoe_b200.ops import tc_gemm as G
+  torch.manual_seed(8)
+  E, Ma, Nb = 3, 640, 512
+  rows = [256, 0, 384]
+  offs = torch.tensor([0, 256, 256, 640], dtype=torch.int32, device="cuda")
+  a = torch.randn(640, Ma, device="cuda").bfloat16()
+  b = torch.randn(640, Nb, device="cuda").bfloat16()
+  assert G.use_pair(Ma, Nb)
+  out = G.grouped_wgrad(a, b, offs, E)
+  acc = torch.ones(E, Ma, Nb, device="cuda")
+  G.grouped_wgrad(a, b, offs, E, out=acc, accumulate=True)
+  torch.cuda.synchronize()
+  G.check_status()
+  o = offs.tolist()
+  for e in range(E):
+    ref = a[o[e]:o[e + 1]].float().t() @ b[o[e]:o[e + 1]].float()
+    if rows[e] == 0:
+      assert (out[e] == 0).all() and (acc[e] == 1).all()
+    else:
+      _close(out[e], ref)
+      _close(acc[e], 1 + ref)
