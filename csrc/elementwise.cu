@@ -369,7 +369,7 @@ int nmoe_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int M, 
 
 // Number of fp32 partial rows the backward needs: scratch = nblocks * H floats.
 int nmoe_rmsnorm_bwd_blocks(int M) {
-  int b = (M + 63) / 64;
+  int b = (M + 23) / 24;      // ~3 rows per warp: enough blocks (<= 592 = 4 per SM) to cover the machine
   return b < 1 ? 1 : (b > 592 ? 592 : b);
 }
 

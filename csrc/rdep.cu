@@ -80,6 +80,7 @@ k_rdep_count(const int* __restrict__ eid, int n_pairs, int E, int* __restrict__ 
 // ------------------------------------------------------------------ plan
 struct PlanArgs {
   int rank, world, E, n_local, n_blocks, capacity_rows, epoch;
+  int align;                    // segment alignment in rows: 128, or 256 when the two-SM grouped GEMM is used
   int* block_hist;              // [n_blocks][E] in: counts, out: exclusive prefix over blocks
   int* peer_counts[kMaxRanks];  // peer r's table [world][E]; we write row `rank`
   uint32_t* peer_count_flags[kMaxRanks];   // peer r's flags [world]; we write entry `rank`
@@ -150,7 +151,7 @@ __global__ void __launch_bounds__(512) k_rdep_plan(const PlanArgs a) {
     int run = 0;
     for (int le = 0; le < a.n_local; ++le) {
       const int e = o * a.n_local + le;
-      const int padded = (s_total[e] + 127) & ~127;
+      const int padded = (s_total[e] + a.align - 1) & ~(a.align - 1);
       if (run + padded > a.capacity_rows) {
         report_status(a.status, kStatusCapacity, 411, o, run + padded);
         a.base[e] = -1;          // rows for this expert are dropped by `place`
@@ -458,12 +459,14 @@ int nmoe_rdep_count(const int* eid, int n_pairs, int E, int* block_hist, int* ra
 }
 
 // peer_counts / peer_count_flags: arrays of `world` device pointers (host memory).
-int nmoe_rdep_plan(int rank, int world, int E, int n_local, int n_blocks, int capacity_rows, int epoch,
+int nmoe_rdep_plan(int rank, int world, int E, int n_local, int n_blocks, int capacity_rows, int epoch, int align,
                    int* block_hist, void* const* peer_counts, void* const* peer_count_flags, int* base,
                    int* offs_pad, int* seg_rows, int* tile_expert, int* n_m_tiles, int* send_counts, void* status,
                    cudaStream_t st) {
   if (world > kMaxRanks || E > kMaxExperts || E != n_local * world) return -1;
+  if (align != 128 && align != 256) return -2;
   PlanArgs a;
+  a.align = align;
   a.rank = rank; a.world = world; a.E = E; a.n_local = n_local; a.n_blocks = n_blocks;
   a.capacity_rows = capacity_rows; a.epoch = epoch; a.block_hist = block_hist;
   for (int r = 0; r < world; ++r) {

@@ -89,7 +89,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
 
 def grouped_gemm(a: torch.Tensor, b: torch.Tensor, tile_expert: torch.Tensor, n_m_tiles: torch.Tensor, *,
                  b_mn: bool = False, out: Optional[torch.Tensor] = None, offs: Optional[torch.Tensor] = None,
-                 bn: int = 0, push: Optional[dict] = None) -> Optional[torch.Tensor]:
+                 bn: int = 0, push: Optional[dict] = None, align256: bool = False) -> Optional[torch.Tensor]:
   """Rows of ``a`` [Mcap,K] are 128-aligned per-expert segments; row tile i belongs to expert
   ``tile_expert[i]`` and only the first ``n_m_tiles[0]`` tiles are valid.  ``b``: [E,N,K]
   (b_mn False) or [E,K,N] (b_mn True).  Returns [Mcap,N]; rows past the valid tiles are
@@ -119,6 +119,13 @@ def grouped_gemm(a: torch.Tensor, b: torch.Tensor, tile_expert: torch.Tensor, n_
     return None
   if out is None:
     out = torch.empty(a.size(0), N, dtype=torch.bfloat16, device=a.device)
+  if align256 and bn == 0 and PAIR_MODE and N >= 256 and a.size(0) % 256 == 0:
+    # segments are 256-row aligned: both CTAs of a pair see one expert, so the two-SM kernel applies
+    L.check(L.lib().nmoe_gemm_bf16_pair(
+      L.ptr(a), L.ptr(b), L.ptr(out), a.size(0), N, K, L.c_ll(K), L.c_ll(N if b_mn else K), L.c_ll(out.stride(0)),
+      0, int(b_mn), 1, E, L.ptr(tile_expert), L.ptr(n_m_tiles), None, L.c_ll(a.size(0)), L.c_ll(b2_rows),
+      0, 0, L.ptr(st), L.stream()), "grouped_gemm_bf16_pair")
+    return out
   L.check(L.lib().nmoe_gemm_bf16(
     L.ptr(a), L.ptr(b), L.ptr(out), a.size(0), N, K, L.c_ll(K), L.c_ll(N if b_mn else K), L.c_ll(out.stride(0)),
     0, int(b_mn), 1, E, L.ptr(tile_expert), L.ptr(n_m_tiles), None, L.c_ll(a.size(0)), L.c_ll(b2_rows),

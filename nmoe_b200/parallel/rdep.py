@@ -15,6 +15,7 @@ W1,W3 [E,H,Dff], W2 [E,Dff,H] (nmoe/model.py:92-94) for checkpoints.
 from __future__ import annotations
 
 import ctypes
+import os
 from dataclasses import dataclass
 from typing import Optional, Tuple
 
@@ -77,7 +78,11 @@ class Rdep:
     worst = pairs * self.world
     avg = pairs
     rows = worst if self.world == 1 else min(worst, int(avg * capacity_factor))
-    self.capacity = ((rows + self.n_local * 127 + 127) // 128) * 128
+    # per-expert segments are padded to `align` rows: 256 lets the grouped GEMMs run on CTA pairs (two-SM MMA)
+    self.align = 256 if (G.PAIR_MODE and profile == "bf16") else 128
+    if os.environ.get("NMOE_RDEP_ALIGN"):
+      self.align = int(os.environ["NMOE_RDEP_ALIGN"])
+    self.capacity = ((rows + self.n_local * (self.align - 1) + 255) // 256) * 256
     H = dim
     regions = [
       ("x", self.capacity * H * 2), ("y", self.capacity * H * 2), ("meta", self.capacity * 16),
@@ -126,7 +131,7 @@ class Rdep:
     n_m_tiles = small[o:o + 1]; o += 1
     tile_expert = small[o:o + self.capacity // 128]
     self.epoch_count += 1
-    L.check(lib.nmoe_rdep_plan(self.rank, self.world, self.E, self.n_local, nb, self.capacity, self.epoch_count,
+    L.check(lib.nmoe_rdep_plan(self.rank, self.world, self.E, self.n_local, nb, self.capacity, self.epoch_count, self.align,
                                L.ptr(block_hist), self.slab.ptrs("counts"), self.slab.ptrs("count_flags"),
                                L.ptr(base), L.ptr(offs_pad), L.ptr(seg_rows), L.ptr(tile_expert), L.ptr(n_m_tiles),
                                L.ptr(send_counts), L.ptr(st), L.stream()), "rdep_plan")
@@ -238,7 +243,7 @@ class _MoEFused(torch.autograd.Function):
       return out
     rdep.place(x, plan, gates32.view(-1), "x", with_meta=True)
     rdep.wait_data()
-    h13 = G.grouped_gemm(rdep.xbuf, W13, plan.tile_expert, plan.n_m_tiles)
+    h13 = G.grouped_gemm(rdep.xbuf, W13, plan.tile_expert, plan.n_m_tiles, align256=rdep.align == 256)
     a = EW.swiglu_rows(h13, plan.n_m_tiles)
     if rdep.fused_return:
       # down projection whose epilogue multiplies by the gate and stores into the source's (token, slot) rows
@@ -262,9 +267,9 @@ class _MoEFused(torch.autograd.Function):
     rdep.wait_data()
     nt = plan.n_m_tiles
     if h13 is None:
-      h13 = G.grouped_gemm(rdep.xbuf, W13, plan.tile_expert, nt)
+      h13 = G.grouped_gemm(rdep.xbuf, W13, plan.tile_expert, nt, align256=rdep.align == 256)
     # dA' = dYe @ W2 (un-gated); gate enters through the row scale of the SwiGLU backward
-    da = G.grouped_gemm(rdep.ybuf, W2, plan.tile_expert, nt, b_mn=True)
+    da = G.grouped_gemm(rdep.ybuf, W2, plan.tile_expert, nt, b_mn=True, align256=rdep.align == 256)
     row_gate = rdep.row_gates(plan)
     dh13, rowdot, a_scaled = EW.swiglu_bwd_fused(h13, da, row_gate, True, True, nt)
     # every reader of the peer-written buffers runs before the kernel that returns rows to the sources
