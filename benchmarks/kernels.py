@@ -81,9 +81,18 @@ def main():
     from nmoe_b200.ops.attention import attention_forward
     q = torch.randn(a.b, a.s, a.h, a.dqk, device=dev).bfloat16(); k = torch.randn_like(q)
     v = torch.randn(a.b, a.s, a.h, a.dv, device=dev).bfloat16()
-    ms = timed(lambda: attention_forward(q, k, v, a.dqk ** -0.5, a.window), a.iters, a.warmup, flush)
     keys = a.s / 2 if a.window == 0 else min(a.window, a.s / 2)
-    tf = 2.0 * a.b * a.h * a.s * keys * (a.dqk + a.dv) / ms / 1e9
+    if a.backward:
+      # backward kernels alone (delta pre-pass + dK/dV + dQ): 2 recomputed and 3 gradient products
+      from nmoe_b200.ops.attention import attention_backward
+      o, lse = attention_forward(q, k, v, a.dqk ** -0.5, a.window)
+      do = torch.randn_like(o)
+      ms = timed(lambda: attention_backward(q, k, v, o, do, lse, a.dqk ** -0.5, a.window), a.iters, a.warmup, flush)
+      tf = 2.0 * a.b * a.h * a.s * keys * (3 * a.dqk + 2 * a.dv) / ms / 1e9
+      out["backward"] = True
+    else:
+      ms = timed(lambda: attention_forward(q, k, v, a.dqk ** -0.5, a.window), a.iters, a.warmup, flush)
+      tf = 2.0 * a.b * a.h * a.s * keys * (a.dqk + a.dv) / ms / 1e9
     out.update(shape=[a.b, a.s, a.h, a.dqk, a.dv], window=a.window, ms=ms, tflops=tf, frac_of_measured_bf16_peak=tf / pk["bf16_tflops"])
   else:
     from nmoe_b200.ops.quant import ExpertWeightCache

@@ -3,12 +3,13 @@
 q,k: [B,S,Hq|Hkv,Dqk]; v: [B,S,Hkv,Dv] -> [B,S,Hq,Dv].  MLA calls it with (Dqk,Dv)=(192,128).
 
 Forward on CUDA = the tcgen05 kernel in ``csrc/attention.cu`` (head dims (192,128), (128,128),
-(64,64)); it also returns the log-sum-exp.  Backward: full-causal attention without sinks goes
-through the cuDNN fused backward (recomputed from q,k,v); windowed / sink attention differentiates
-a query-block-tiled eager statement.  CPU tensors run the fp32 oracle.
+(64,64)); it also returns the log-sum-exp.  Backward on CUDA = the two tcgen05 kernels in
+``csrc/attention_bwd.cu`` (dK/dV per key block, dQ per query block), for every mask form the
+forward supports.  CPU tensors run the fp32 oracle.
 """
 from __future__ import annotations
 
+import ctypes
 from typing import Optional
 
 import torch
@@ -71,38 +72,55 @@ def attention_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: 
   return o, lse
 
 
+def attention_backward(q, k, v, o, do, lse, scale: float, window: int = 0):
+  """Raw backward kernels (``csrc/attention_bwd.cu``): returns (dq, dk, dv, delta).
+
+  ``delta`` [B,Hq,S] = rowsum(o * do) is what the sink gradient needs besides ``lse``."""
+  B, S, Hq, Dqk = q.shape
+  Hkv, Dv = k.size(2), v.size(3)
+  q, k, v, o, do = (t.contiguous() for t in (q, k, v, o, do))
+  g = Hq // Hkv
+  dq = torch.empty_like(q)
+  dk = torch.empty(B, S, Hq, Dqk, dtype=q.dtype, device=q.device)
+  dv = torch.empty(B, S, Hq, Dv, dtype=q.dtype, device=q.device)
+  delta = torch.empty(B, Hq, S, dtype=torch.float32, device=q.device)
+  addr = (ctypes.c_int * 11)(Hq * Dqk, Dqk, Hq * Dqk, Dqk, 0, Hq * Dqk, Dqk, 0, Hq * Dv, Dv, 0)
+  st = status_buffer(q.device)
+  L.check(L.lib().nmoe_attn_bwd_ex(
+    L.ptr(q), Hq * Dqk, Dqk, L.ptr(k), Hkv * Dqk, Dqk, 0, Dqk // 64, None, 0, 0, 0, L.ptr(v), Hkv * Dv, Dv, 0,
+    L.ptr(o), L.ptr(do), L.ptr(lse), L.ptr(delta), L.ptr(dq), L.ptr(dk), None, L.ptr(dv), addr, B, S, Hq, Hkv, Dqk, Dv,
+    int(window), L.c_float(scale), L.ptr(st), L.stream()), "attn_bwd", 3)
+  if g > 1:   # one slot per query head -> sum the group
+    dk = dk.view(B, S, Hkv, g, Dqk).sum(3, dtype=torch.float32).to(q.dtype)
+    dv = dv.view(B, S, Hkv, g, Dv).sum(3, dtype=torch.float32).to(q.dtype)
+  return dq, dk, dv, delta
+
+
 class _Attention(torch.autograd.Function):
   @staticmethod
   def forward(ctx, q, k, v, sinks, scale, window):
-    o, lse = attention_forward(q, k, v, scale, window, sinks, need_lse=False)
-    ctx.save_for_backward(q, k, v, sinks)
+    o, lse = attention_forward(q, k, v, scale, window, sinks, need_lse=True)
+    ctx.save_for_backward(q, k, v, sinks, o, lse)
     ctx.scale, ctx.window = scale, window
     return o
 
   @staticmethod
   def backward(ctx, do):
-    q, k, v, sinks = ctx.saved_tensors
-    scale, window = ctx.scale, ctx.window
-    with torch.enable_grad():
-      qd, kd, vd = (t.detach().requires_grad_() for t in (q, k, v))
-      sd = sinks.detach().requires_grad_() if sinks is not None else None
-      if window == 0 and sinks is None:
-        Hq, Hkv = q.size(2), k.size(2)
-        o2 = F.scaled_dot_product_attention(qd.transpose(1, 2), kd.transpose(1, 2), vd.transpose(1, 2), is_causal=True,
-                                            scale=scale, enable_gqa=(Hq != Hkv)).transpose(1, 2)
-      else:
-        o2 = _banded_eager(qd, kd, vd, scale, window, sd)
-      ins = (qd, kd, vd) + ((sd,) if sd is not None else ())
-      grads = torch.autograd.grad(o2, ins, do)
-    dq, dk, dv = grads[:3]
-    ds = grads[3].to(sinks.dtype) if sd is not None else None
+    q, k, v, sinks, o, lse = ctx.saved_tensors
+    dq, dk, dv, delta = attention_backward(q, k, v, o, do, lse, ctx.scale, ctx.window)
+    ds = None
+    if sinks is not None:
+      # the sink is one more logit with a zero value row: dsink = -sum_rows P_sink * delta
+      ds = -(torch.exp(sinks.detach().float().view(1, -1, 1) - lse) * delta).sum((0, 2)).to(sinks.dtype)
     return dq, dk, dv, ds, None, None
 
 
 class _MLAAttention(torch.autograd.Function):
   """MLA core attention reading k_nope / v straight out of the fused kv projection output and the
-  shared rotary key from its own tensor: the forward never materialises K [B,S,H,192] or a
-  contiguous V.  The backward assembles them once and uses the library fused backward."""
+  shared rotary key from its own tensor: neither direction materialises K [B,S,H,192] or a
+  contiguous V.  The backward writes d(k_nope) and dv into one [B,S,H,nope+vdim] buffer (the
+  gradient of the kv projection output) and the per-head rotary-key gradients into a small
+  buffer that is summed over heads."""
 
   @staticmethod
   def forward(ctx, q, kv, k_pe, scale, nope, vdim):
@@ -110,28 +128,37 @@ class _MLAAttention(torch.autograd.Function):
     rope = Dqk - nope
     q, kv, k_pe = q.contiguous(), kv.contiguous(), k_pe.contiguous()
     o = torch.empty(B, S, H, vdim, dtype=q.dtype, device=q.device)
+    lse = torch.empty(B, H, S, dtype=torch.float32, device=q.device)
     st = status_buffer(q.device)
     row_kv = H * (nope + vdim)
     L.check(L.lib().nmoe_attn_fwd_ex(
       L.ptr(q), H * Dqk, Dqk, L.ptr(kv), row_kv, nope + vdim, 0, nope // 64, L.ptr(k_pe), rope, 0, 0,
-      L.ptr(kv), row_kv, nope + vdim, nope, L.ptr(o), None, None, B, S, H, H, Dqk, vdim, 0, L.c_float(scale),
+      L.ptr(kv), row_kv, nope + vdim, nope, L.ptr(o), L.ptr(lse), None, B, S, H, H, Dqk, vdim, 0, L.c_float(scale),
       L.ptr(st), L.stream()), "attn_fwd(mla)")
-    ctx.save_for_backward(q, kv, k_pe)
+    ctx.save_for_backward(q, kv, k_pe, o, lse)
     ctx.args = (scale, nope, vdim)
     return o
 
   @staticmethod
   def backward(ctx, do):
-    q, kv, k_pe = ctx.saved_tensors
+    q, kv, k_pe, o, lse = ctx.saved_tensors
     scale, nope, vdim = ctx.args
-    B, S, H, _ = q.shape
-    with torch.enable_grad():
-      qd, kvd, ped = (t.detach().requires_grad_() for t in (q, kv, k_pe))
-      k = torch.cat((kvd[..., :nope], ped.expand(B, S, H, ped.size(-1))), dim=-1)
-      v = kvd[..., nope:]
-      o2 = F.scaled_dot_product_attention(qd.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=True,
-                                          scale=scale).transpose(1, 2)
-      dq, dkv, dpe = torch.autograd.grad(o2, (qd, kvd, ped), do)
+    B, S, H, Dqk = q.shape
+    rope = Dqk - nope
+    do = do.contiguous()
+    dq = torch.empty_like(q)
+    dkv = torch.empty_like(kv)
+    dpe_h = torch.empty(B, S, H, rope, dtype=q.dtype, device=q.device)
+    delta = torch.empty(B, H, S, dtype=torch.float32, device=q.device)
+    row_kv = H * (nope + vdim)
+    addr = (ctypes.c_int * 11)(H * Dqk, Dqk, row_kv, nope + vdim, 0, H * rope, rope, 0, row_kv, nope + vdim, nope)
+    st = status_buffer(q.device)
+    L.check(L.lib().nmoe_attn_bwd_ex(
+      L.ptr(q), H * Dqk, Dqk, L.ptr(kv), row_kv, nope + vdim, 0, nope // 64, L.ptr(k_pe), rope, 0, 0,
+      L.ptr(kv), row_kv, nope + vdim, nope, L.ptr(o), L.ptr(do), L.ptr(lse), L.ptr(delta), L.ptr(dq), L.ptr(dkv),
+      L.ptr(dpe_h), L.ptr(dkv), addr, B, S, H, H, Dqk, vdim, 0, L.c_float(scale), L.ptr(st), L.stream()),
+      "attn_bwd(mla)", 3)
+    dpe = dpe_h.sum(2, keepdim=True, dtype=torch.float32).to(q.dtype)
     return dq, dkv, dpe, None, None, None
 
 
