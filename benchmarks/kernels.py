@@ -72,11 +72,19 @@ def main():
     out.update(shape=[a.m, a.n, a.k], a_mn=a.a_mn, b_mn=a.b_mn, ms=ms, tflops=tf, frac_of_measured_bf16_peak=tf / pk["bf16_tflops"])
   elif a.what == "mx":
     A = torch.randn(a.m, a.k, device=dev).bfloat16(); B = (torch.randn(a.n, a.k, device=dev) * 0.1).bfloat16()
-    aq, asf = ops.quant_mxfp8(A); bq, bsf = ops.quant_mxfp8(B)
     C = torch.empty(a.m, a.n, device=dev, dtype=torch.bfloat16)
-    ms = timed(lambda: ops.gemm_mxfp8(aq, asf, bq, bsf, out=C, bn=a.bn), a.iters, a.warmup, flush)
+    if a.dtype in ("nvfp4", "mxfp4", "fp4"):
+      from nmoe_b200.ops.quant import gemm_mxfp4
+      aq, asf = ops.quant_mxfp4(A); bq, bsf = ops.quant_mxfp4(B)
+      ms = timed(lambda: gemm_mxfp4(aq, asf, bq, bsf, out=C, bn=a.bn), a.iters, a.warmup, flush)
+      mult = 4
+    else:
+      aq, asf = ops.quant_mxfp8(A); bq, bsf = ops.quant_mxfp8(B)
+      ms = timed(lambda: ops.gemm_mxfp8(aq, asf, bq, bsf, out=C, bn=a.bn), a.iters, a.warmup, flush)
+      mult = 2
     tf = 2.0 * a.m * a.n * a.k / ms / 1e9
-    out.update(shape=[a.m, a.n, a.k], ms=ms, tflops=tf, frac_of_2x_measured_bf16_peak=tf / (2 * pk["bf16_tflops"]))
+    out.update(shape=[a.m, a.n, a.k], dtype=a.dtype, ms=ms, tflops=tf)
+    out[f"frac_of_{mult}x_measured_bf16_peak"] = tf / (mult * pk["bf16_tflops"])
   elif a.what == "attn":
     from nmoe_b200.ops.attention import attention_forward
     q = torch.randn(a.b, a.s, a.h, a.dqk, device=dev).bfloat16(); k = torch.randn_like(q)
@@ -104,7 +112,7 @@ def main():
     W2 = (torch.randn(E, H, F, device=dev) * 0.02).bfloat16().requires_grad_(a.backward)
     eid = torch.stack([torch.randperm(E, device=dev)[:K] for _ in range(min(T, 4096))]).int().repeat((T + 4095) // 4096, 1)[:T].contiguous()
     gates = torch.rand(T, K, device=dev)
-    wq = ExpertWeightCache().get(W13, W2) if a.dtype != "bf16" else None
+    wq = ExpertWeightCache(a.dtype).get(W13, W2) if a.dtype != "bf16" else None
     g = torch.randn(T, H, device=dev).bfloat16()
     def step():
       o = rd.moe(x, gates, eid, W13, W2, False, wq)

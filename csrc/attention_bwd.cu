@@ -27,7 +27,8 @@
 
 namespace nmoe {
 
-constexpr int kBwdThreads = 192;           // warp 0: TMA, warp 1: MMA, warps 2-5: softmax / epilogue
+constexpr int kBwdThreads = 320;           // warp 0: TMA, warp 1: MMA, warps 2-9: softmax / epilogue (two column halves x four lane quadrants)
+constexpr int BWD_STAGES = 3;              // streamed-tile stages: a load is issued one full iteration before it is needed
 constexpr int BWD_BIG = 128;               // rows of the resident block
 constexpr int BWD_SMALL = 64;              // rows of the streamed block
 constexpr uint64_t kBwdWaitNs = 2000000000ull;
@@ -104,28 +105,28 @@ NMOE_DEVICE void store_row32(__nv_bfloat16* dst, const uint32_t* r, float s) {
   }
 }
 
-// delta[b,h,s] = sum_d O[b,s,h,d] * dO[b,s,h,d]   (one warp per (row, head))
+// delta[b,h,s] = sum_d O[b,s,h,d] * dO[b,s,h,d]   (Dv/8 lanes per (row, head), 16 bytes each)
 __global__ void __launch_bounds__(256)
 k_attn_delta(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o, float* __restrict__ delta,
              int B, int S, int H, int Dv) {
-  const long long idx = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
-  if (idx >= static_cast<long long>(B) * S * H) return;
-  const int lane = threadIdx.x & 31;
-  const int h = static_cast<int>(idx % H);
-  const long long bs = idx / H;
-  const __nv_bfloat16* po = o + idx * Dv;
-  const __nv_bfloat16* pd = d_o + idx * Dv;
+  const int lpr = Dv >> 3;                                     // lanes per row: 8 or 16
+  const long long tid = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x;
+  const long long idx = tid / lpr;
+  const int sub = static_cast<int>(tid % lpr);
+  const bool live = idx < static_cast<long long>(B) * S * H;
   float acc = 0.f;
-  for (int c = lane * 8; c < Dv; c += 256) {
-    const int4 a = ld_nc_v4(po + c), b = ld_nc_v4(pd + c);
+  if (live) {
+    const int4 a = ld_nc_v4(o + idx * Dv + sub * 8), b = ld_nc_v4(d_o + idx * Dv + sub * 8);
     const float2 a0 = unpack_bf16x2(a.x), a1 = unpack_bf16x2(a.y), a2 = unpack_bf16x2(a.z), a3 = unpack_bf16x2(a.w);
     const float2 b0 = unpack_bf16x2(b.x), b1 = unpack_bf16x2(b.y), b2 = unpack_bf16x2(b.z), b3 = unpack_bf16x2(b.w);
-    acc += a0.x * b0.x + a0.y * b0.y + a1.x * b1.x + a1.y * b1.y + a2.x * b2.x + a2.y * b2.y + a3.x * b3.x + a3.y * b3.y;
+    acc = a0.x * b0.x + a0.y * b0.y + a1.x * b1.x + a1.y * b1.y + a2.x * b2.x + a2.y * b2.y + a3.x * b3.x + a3.y * b3.y;
   }
-  acc = warp_sum(acc);
-  if (lane == 0) {
-    const int b = static_cast<int>(bs / S), s = static_cast<int>(bs % S);
-    delta[(static_cast<long long>(b) * H + h) * S + s] = acc;
+  for (int off = lpr >> 1; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if (live && sub == 0) {
+    const int h = static_cast<int>(idx % H);
+    const long long bs = idx / H;
+    const int b = static_cast<int>(bs / S), sq = static_cast<int>(bs % S);
+    delta[(static_cast<long long>(b) * H + h) * S + sq] = acc;
   }
 }
 
@@ -135,13 +136,14 @@ struct BwdSmem {
   static constexpr int kBigV = BWD_BIG * DV * 2;        // resident [128, DV] tile (dO or V)
   static constexpr int kSmallQK = BWD_SMALL * DQK * 2;  // streamed [64, DQK] tile
   static constexpr int kSmallV = BWD_SMALL * DV * 2;
-  static constexpr int kBytes = kBigQK + kBigV + 2 * kSmallQK + 2 * kSmallV + 1024 + 256 + 1024;  // align, barriers, row statistics
+  static constexpr int kBytes = kBigQK + kBigV + BWD_STAGES * (kSmallQK + kSmallV) + 1024 + 256 + 1536;  // align, barriers, row statistics
 };
 
 // ---------------------------------------------------------------------------------------------
-// dQ: CTA = (128-row query block, head, batch); streams 64-key blocks.
-// Tensor memory columns: S[2] at 0/64, dP[2] at 128/192 (dS as bf16 over the first 32 columns of
-// the same buffer), dQ accumulator at 256.
+// dQ: CTA = (128-row query block, head, batch); streams 64-key blocks through BWD_STAGES stages.
+// Tensor memory columns: S[2] at 0/64, dP[2] at 128/192, dQ accumulator at 256.  The eight
+// softmax warps split a block's 64 columns in two halves; each half writes its dS as bf16 over
+// the first 16 columns of the dP columns it has just read (columns 0-15 and 32-47 of the buffer).
 // ---------------------------------------------------------------------------------------------
 template <int DQK, int DV>
 __global__ void __launch_bounds__(kBwdThreads, 1)
@@ -154,15 +156,15 @@ k_attn_bwd_dq(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   uint8_t* sQ = smem;
   uint8_t* sdO = sQ + SM::kBigQK;
   uint8_t* sK = sdO + SM::kBigV;
-  uint8_t* sV = sK + 2 * SM::kSmallQK;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sV + 2 * SM::kSmallV);
+  uint8_t* sV = sK + BWD_STAGES * SM::kSmallQK;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sV + BWD_STAGES * SM::kSmallV);
   uint64_t* qdo_full = bars;          // [1]
-  uint64_t* kv_full = bars + 1;       // [2]
-  uint64_t* kv_empty = bars + 3;      // [2]
-  uint64_t* sdp_full = bars + 5;      // [2]  S and dP of a block are in tensor memory
-  uint64_t* ds_full = bars + 7;       // [2]  dS written by the four softmax warps
-  uint64_t* dq_done = bars + 9;       // [1]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  uint64_t* kv_full = bars + 1;       // [3]
+  uint64_t* kv_empty = bars + 4;      // [3]
+  uint64_t* sdp_full = bars + 7;      // [2]  S and dP of a block are in tensor memory
+  uint64_t* ds_full = bars + 9;       // [2]  dS written by the eight softmax warps
+  uint64_t* dq_done = bars + 11;      // [1]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -175,10 +177,8 @@ k_attn_bwd_dq(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 
   if (threadIdx.x == 0) {
     mbar_init(qdo_full, 1);
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1);
-      mbar_init(&sdp_full[i], 1); mbar_init(&ds_full[i], 4);
-    }
+    for (int i = 0; i < BWD_STAGES; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&sdp_full[i], 1); mbar_init(&ds_full[i], 8); }
     mbar_init(dq_done, 1);
     *abort_flag = 0;
     mbar_fence_init();
@@ -203,10 +203,10 @@ k_attn_bwd_dq(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       for (int c = 0; c < DQK / 64; ++c) tma_load_2d(sQ + c * (BWD_BIG * 128), &tmQ, qdo_full, h * p.q_hs + c * 64, row_q);
 #pragma unroll
       for (int c = 0; c < DV / 64; ++c) tma_load_2d(sdO + c * (BWD_BIG * 128), &tmdO, qdo_full, h * p.do_hs + c * 64, row_q);
+      int st = 0; uint32_t ph = 0;
       for (int i = lo; i < hi; ++i) {
-        const int gi = i - lo, st = gi & 1;
         const int row_k = b * p.S + i * BWD_SMALL;
-        if (!bwd_wait(&kv_empty[st], ((gi >> 1) & 1) ^ 1, abort_flag)) { report_status(p.status, kStatusWaitTimeout, 800, i, 0); *abort_flag = 1; break; }
+        if (!bwd_wait(&kv_empty[st], ph ^ 1, abort_flag)) { report_status(p.status, kStatusWaitTimeout, 800, i, 0); *abort_flag = 1; break; }
         mbar_expect_tx(&kv_full[st], SM::kSmallQK + SM::kSmallV);
 #pragma unroll
         for (int c = 0; c < DQK / 64; ++c) {
@@ -219,6 +219,7 @@ k_attn_bwd_dq(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 #pragma unroll
         for (int c = 0; c < DV / 64; ++c)
           tma_load_2d(sV + st * SM::kSmallV + c * (BWD_SMALL * 128), &tmV, &kv_full[st], hkv * p.v_hs + p.v_off + c * 64, row_k);
+        if (++st == BWD_STAGES) { st = 0; ph ^= 1; }
       }
     }
     __syncwarp();
@@ -228,90 +229,88 @@ k_attn_bwd_dq(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       constexpr uint32_t idesc_dq = make_idesc_bf16(BWD_BIG, DQK, 0, 1);
       bool ok = hi > lo && bwd_wait(qdo_full, 0, abort_flag);
       const uint32_t qa = smem_u32(sQ), doa = smem_u32(sdO);
+      int st_s = 0; uint32_t ph_s = 0;       // stage / phase of the next block whose S, dP get issued
       auto issue_sdp = [&](int i) -> bool {
-        const int gi = i - lo, st = gi & 1;
-        if (!bwd_wait(&kv_full[st], (gi >> 1) & 1, abort_flag)) { report_status(p.status, kStatusWaitTimeout, 810, i, 0); *abort_flag = 1; return false; }
+        const int bf = (i - lo) & 1;
+        if (!bwd_wait(&kv_full[st_s], ph_s, abort_flag)) { report_status(p.status, kStatusWaitTimeout, 810, i, 0); *abort_flag = 1; return false; }
         tc_fence_after_sync();
-        const uint32_t ka = smem_u32(sK + st * SM::kSmallQK), va = smem_u32(sV + st * SM::kSmallV);
+        const uint32_t ka = smem_u32(sK + st_s * SM::kSmallQK), va = smem_u32(sV + st_s * SM::kSmallV);
 #pragma unroll
         for (int j = 0; j < DQK / 16; ++j)
-          mma_f16_ss(tmem_base + kColS + st * BWD_SMALL,
+          mma_f16_ss(tmem_base + kColS + bf * BWD_SMALL,
                      make_smem_desc(qa + (j >> 2) * (BWD_BIG * 128) + (j & 3) * 32, 0, 1024, kSwizzle128B),
                      make_smem_desc(ka + (j >> 2) * (BWD_SMALL * 128) + (j & 3) * 32, 0, 1024, kSwizzle128B), idesc_s,
                      j != 0 ? 1u : 0u);
 #pragma unroll
         for (int j = 0; j < DV / 16; ++j)
-          mma_f16_ss(tmem_base + kColdP + st * BWD_SMALL,
+          mma_f16_ss(tmem_base + kColdP + bf * BWD_SMALL,
                      make_smem_desc(doa + (j >> 2) * (BWD_BIG * 128) + (j & 3) * 32, 0, 1024, kSwizzle128B),
                      make_smem_desc(va + (j >> 2) * (BWD_SMALL * 128) + (j & 3) * 32, 0, 1024, kSwizzle128B), idesc_s,
                      j != 0 ? 1u : 0u);
-        mma_commit(&sdp_full[st]);
+        mma_commit(&sdp_full[bf]);
+        if (++st_s == BWD_STAGES) { st_s = 0; ph_s ^= 1; }
         return true;
       };
       if (ok) ok = issue_sdp(lo);
+      int st = 0;
       for (int i = lo; ok && i < hi; ++i) {
-        const int gi = i - lo, st = gi & 1;
+        const int gi = i - lo, bf = gi & 1;
         if (i + 1 < hi) { ok = issue_sdp(i + 1); if (!ok) break; }
-        if (!bwd_wait(&ds_full[st], (gi >> 1) & 1, abort_flag)) { report_status(p.status, kStatusWaitTimeout, 811, i, 0); *abort_flag = 1; ok = false; break; }
+        if (!bwd_wait(&ds_full[bf], (gi >> 1) & 1, abort_flag)) { report_status(p.status, kStatusWaitTimeout, 811, i, 0); *abort_flag = 1; ok = false; break; }
         tc_fence_after_sync();
         const uint32_t ka = smem_u32(sK + st * SM::kSmallQK);
-        const uint32_t a_t = tmem_base + kColdP + st * BWD_SMALL;
+        const uint32_t a_t = tmem_base + kColdP + bf * BWD_SMALL;
 #pragma unroll
         for (int j = 0; j < BWD_SMALL / 16; ++j)
-          bwd_mma_ts(tmem_base + kColdQ, a_t + j * 8, make_smem_desc(ka + j * 2048, BWD_SMALL * 128, 1024, kSwizzle128B),
-                     idesc_dq, (gi | j) != 0 ? 1u : 0u);
+          bwd_mma_ts(tmem_base + kColdQ, a_t + (j >> 1) * 32 + (j & 1) * 8,
+                     make_smem_desc(ka + j * 2048, BWD_SMALL * 128, 1024, kSwizzle128B), idesc_dq, (gi | j) != 0 ? 1u : 0u);
         mma_commit(&kv_empty[st]);
+        if (++st == BWD_STAGES) st = 0;
       }
       if (ok) mma_commit(dq_done);
     }
     __syncwarp();
   } else {
     const int q = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int row = q0 + q * 32 + lane;
     const bool row_ok = row < p.S;
     const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
     const size_t stat_idx = (static_cast<size_t>(b) * p.Hq + h) * p.S + (row_ok ? row : 0);
-    const float lse2 = row_ok ? p.lse[stat_idx] * kLog2e : 0.f;
+    const float lse2 = row_ok ? p.lse[stat_idx] * kLog2e : 1e30f;    // rows past the sequence: P = 0
     const float dl = row_ok ? p.delta[stat_idx] : 0.f;
     bool ok = true;
     for (int i = lo; i < hi; ++i) {
-      const int gi = i - lo, st = gi & 1;
-      ok = bwd_wait(&sdp_full[st], (gi >> 1) & 1, abort_flag);
+      const int gi = i - lo, bf = gi & 1;
+      ok = bwd_wait(&sdp_full[bf], (gi >> 1) & 1, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) { if (lane == 0) report_status(p.status, kStatusWaitTimeout, 820, i, 0); *abort_flag = 1; break; }
       tc_fence_after_sync();
-      const int k0 = i * BWD_SMALL;
-      const bool need_mask = (k0 + BWD_SMALL - 1 > q0) || (p.window > 0 && k0 <= q0 + BWD_BIG - 1 - p.window) ||
-                             (k0 + BWD_SMALL > p.S) || (q0 + BWD_BIG > p.S);
-      const uint32_t s_addr = tmem_base + lane_addr + kColS + st * BWD_SMALL;
-      const uint32_t dp_addr = tmem_base + lane_addr + kColdP + st * BWD_SMALL;
-      uint32_t pk[BWD_SMALL / 2];
+      const int k0 = i * BWD_SMALL + half * 32;
+      const bool need_mask = (k0 + 31 > q0) || (p.window > 0 && k0 <= q0 + BWD_BIG - 1 - p.window) || (k0 + 32 > p.S);
+      const uint32_t s_addr = tmem_base + lane_addr + kColS + bf * BWD_SMALL + half * 32;
+      const uint32_t dp_addr = tmem_base + lane_addr + kColdP + bf * BWD_SMALL + half * 32;
+      uint32_t s[32], dp[32], pk[16];
+      tmem_ld_32x32b_x32(s_addr, s);
+      tmem_ld_32x32b_x32(dp_addr, dp);
+      tmem_ld_wait();
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t s[32], dp[32];
-        tmem_ld_32x32b_x32(s_addr + half * 32, s);
-        tmem_ld_32x32b_x32(dp_addr + half * 32, dp);
-        tmem_ld_wait();
-#pragma unroll
-        for (int t = 0; t < 32; t += 2) {
-          float p0 = bwd_exp2(fmaf(__uint_as_float(s[t]), p.scale_log2, -lse2));
-          float p1 = bwd_exp2(fmaf(__uint_as_float(s[t + 1]), p.scale_log2, -lse2));
-          if (need_mask) {
-            const int kk = k0 + half * 32 + t;
-            if (!row_ok || masked(row, kk, p.S, p.window)) p0 = 0.f;
-            if (!row_ok || masked(row, kk + 1, p.S, p.window)) p1 = 0.f;
-          }
-          const float d0 = p0 * (__uint_as_float(dp[t]) - dl) * p.scale;
-          const float d1 = p1 * (__uint_as_float(dp[t + 1]) - dl) * p.scale;
-          pk[half * 16 + (t >> 1)] = pack_bf16x2(d0, d1);
+      for (int t = 0; t < 32; t += 2) {
+        float p0 = bwd_exp2(fmaf(__uint_as_float(s[t]), p.scale_log2, -lse2));
+        float p1 = bwd_exp2(fmaf(__uint_as_float(s[t + 1]), p.scale_log2, -lse2));
+        if (need_mask) {
+          if (masked(row, k0 + t, p.S, p.window)) p0 = 0.f;
+          if (masked(row, k0 + t + 1, p.S, p.window)) p1 = 0.f;
         }
+        const float d0 = p0 * (__uint_as_float(dp[t]) - dl) * p.scale;
+        const float d1 = p1 * (__uint_as_float(dp[t + 1]) - dl) * p.scale;
+        pk[t >> 1] = pack_bf16x2(d0, d1);
       }
       bwd_tmem_st_x16(dp_addr, pk);
-      bwd_tmem_st_x16(dp_addr + 16, pk + 16);
       tmem_st_wait();
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&ds_full[st]);
+      if (lane == 0) mbar_arrive(&ds_full[bf]);
     }
     if (ok && hi > lo) {
       ok = bwd_wait(dq_done, 0, abort_flag);
@@ -322,15 +321,10 @@ k_attn_bwd_dq(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       tc_fence_after_sync();
       __nv_bfloat16* drow = p.dQ + (static_cast<size_t>(b) * p.S + (row_ok ? row : 0)) * p.dq_row + static_cast<size_t>(h) * p.dq_hs;
 #pragma unroll 1
-      for (int c = 0; c < DQK / 32; ++c) {
+      for (int c = half; c < DQK / 32; c += 2) {
         uint32_t o[32];
-        if (hi > lo) {
-          tmem_ld_32x32b_x32(tmem_base + lane_addr + kColdQ + c * 32, o);
-          tmem_ld_wait();
-        } else {
-#pragma unroll
-          for (int t = 0; t < 32; ++t) o[t] = 0u;
-        }
+        tmem_ld_32x32b_x32(tmem_base + lane_addr + kColdQ + c * 32, o);
+        tmem_ld_wait();
         if (row_ok) store_row32(drow + c * 32, o, 1.f);
       }
     }
@@ -349,8 +343,9 @@ k_attn_bwd_dq(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 
 // ---------------------------------------------------------------------------------------------
 // dK, dV: CTA = (128-key block, query head, batch); streams 64-row query blocks.
-// Tensor memory columns: S^T[2] at 0/64 (P^T as bf16 over the first 32 columns), dP^T at 128
-// (dS^T as bf16 over its first 32 columns), dV accumulator at 192, dK accumulator at 192+DV.
+// Tensor memory columns: S^T[2] at 0/64, dP^T at 128, dV accumulator at 192, dK accumulator at
+// 192+DV.  Each half of the eight softmax warps owns 32 of a block's 64 columns and writes P^T /
+// dS^T as bf16 over the first 16 of the columns it has just read (0-15 and 32-47).
 // ---------------------------------------------------------------------------------------------
 template <int DQK, int DV>
 __global__ void __launch_bounds__(kBwdThreads, 1)
@@ -364,19 +359,19 @@ k_attn_bwd_dkv(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   uint8_t* sK = smem;
   uint8_t* sV = sK + SM::kBigQK;
   uint8_t* sQ = sV + SM::kBigV;
-  uint8_t* sdO = sQ + 2 * SM::kSmallQK;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sdO + 2 * SM::kSmallV);
+  uint8_t* sdO = sQ + BWD_STAGES * SM::kSmallQK;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sdO + BWD_STAGES * SM::kSmallV);
   uint64_t* kv_full = bars;           // [1]
-  uint64_t* q_full = bars + 1;        // [2]  Q, dO tiles (TMA) and the row statistics (warp 0) of a block
-  uint64_t* q_empty = bars + 3;       // [2]
-  uint64_t* s_full = bars + 5;        // [2]
-  uint64_t* dp_full = bars + 7;       // [1]
-  uint64_t* pds_full = bars + 8;      // [1]  P^T and dS^T written by the four softmax warps
-  uint64_t* acc_done = bars + 9;      // [1]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  uint64_t* q_full = bars + 1;        // [3]  Q, dO tiles (TMA) and the row statistics (warp 0) of a block
+  uint64_t* q_empty = bars + 4;       // [3]
+  uint64_t* s_full = bars + 7;        // [2]
+  uint64_t* dp_full = bars + 9;       // [1]
+  uint64_t* pds_full = bars + 10;     // [1]  P^T and dS^T written by the eight softmax warps
+  uint64_t* acc_done = bars + 11;     // [1]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  float* s_lse = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + 256);   // [2][64], log2 units
-  float* s_delta = s_lse + 2 * BWD_SMALL;                                            // [2][64]
+  float* s_lse = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + 256);   // [stage][64], log2 units
+  float* s_delta = s_lse + BWD_STAGES * BWD_SMALL;                                   // [stage][64]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kb = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
@@ -388,11 +383,11 @@ k_attn_bwd_dkv(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&q_full[i], 2); mbar_init(&q_empty[i], 1); mbar_init(&s_full[i], 1);
-    }
+    for (int i = 0; i < BWD_STAGES; ++i) { mbar_init(&q_full[i], 2); mbar_init(&q_empty[i], 1); }
+    mbar_init(&s_full[0], 1);
+    mbar_init(&s_full[1], 1);
     mbar_init(dp_full, 1);
-    mbar_init(pds_full, 4);
+    mbar_init(pds_full, 8);
     mbar_init(acc_done, 1);
     *abort_flag = 0;
     mbar_fence_init();
@@ -427,9 +422,9 @@ k_attn_bwd_dkv(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         tma_load_2d(sV + c * (BWD_BIG * 128), &tmV, kv_full, hkv * p.v_hs + p.v_off + c * 64, row_k);
     }
     const size_t stat_base = (static_cast<size_t>(b) * p.Hq + h) * p.S;
+    int st = 0; uint32_t ph = 0;
     for (int i = lo; i < hi; ++i) {
-      const int gi = i - lo, st = gi & 1;
-      bool ok = bwd_wait(&q_empty[st], ((gi >> 1) & 1) ^ 1, abort_flag);
+      bool ok = bwd_wait(&q_empty[st], ph ^ 1, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) { if (lane == 0) report_status(p.status, kStatusWaitTimeout, 830, i, 0); *abort_flag = 1; break; }
       if (leader) {
@@ -451,6 +446,7 @@ k_attn_bwd_dkv(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&q_full[st]);
+      if (++st == BWD_STAGES) { st = 0; ph ^= 1; }
     }
     __syncwarp();
   } else if (warp == 1) {
@@ -460,22 +456,23 @@ k_attn_bwd_dkv(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       constexpr uint32_t idesc_dk = make_idesc_bf16(BWD_BIG, DQK, 0, 1);
       bool ok = hi > lo && bwd_wait(kv_full, 0, abort_flag);
       const uint32_t ka = smem_u32(sK), va = smem_u32(sV);
+      int st_s = 0; uint32_t ph_s = 0;       // stage / phase of the next block whose S^T gets issued
       auto issue_s = [&](int i) -> bool {
-        const int gi = i - lo, st = gi & 1;
-        if (!bwd_wait(&q_full[st], (gi >> 1) & 1, abort_flag)) { report_status(p.status, kStatusWaitTimeout, 840, i, 0); *abort_flag = 1; return false; }
+        const int bf = (i - lo) & 1;
+        if (!bwd_wait(&q_full[st_s], ph_s, abort_flag)) { report_status(p.status, kStatusWaitTimeout, 840, i, 0); *abort_flag = 1; return false; }
         tc_fence_after_sync();
-        const uint32_t qa = smem_u32(sQ + st * SM::kSmallQK);
+        const uint32_t qa = smem_u32(sQ + st_s * SM::kSmallQK);
 #pragma unroll
         for (int j = 0; j < DQK / 16; ++j)
-          mma_f16_ss(tmem_base + kColS + st * BWD_SMALL,
+          mma_f16_ss(tmem_base + kColS + bf * BWD_SMALL,
                      make_smem_desc(ka + (j >> 2) * (BWD_BIG * 128) + (j & 3) * 32, 0, 1024, kSwizzle128B),
                      make_smem_desc(qa + (j >> 2) * (BWD_SMALL * 128) + (j & 3) * 32, 0, 1024, kSwizzle128B), idesc_s,
                      j != 0 ? 1u : 0u);
-        mma_commit(&s_full[st]);
+        mma_commit(&s_full[bf]);
+        if (++st_s == BWD_STAGES) { st_s = 0; ph_s ^= 1; }
         return true;
       };
-      auto issue_dp = [&](int i) {
-        const int st = (i - lo) & 1;
+      auto issue_dp = [&](int st) {
         const uint32_t doa = smem_u32(sdO + st * SM::kSmallV);
 #pragma unroll
         for (int j = 0; j < DV / 16; ++j)
@@ -485,89 +482,98 @@ k_attn_bwd_dkv(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                      j != 0 ? 1u : 0u);
         mma_commit(dp_full);
       };
-      if (ok) { ok = issue_s(lo); if (ok) issue_dp(lo); }
+      if (ok) { ok = issue_s(lo); if (ok) issue_dp(0); }
+      int st = 0;
       for (int i = lo; ok && i < hi; ++i) {
-        const int gi = i - lo, st = gi & 1;
+        const int gi = i - lo, bf = gi & 1;
+        const int st_next = st + 1 == BWD_STAGES ? 0 : st + 1;
         if (i + 1 < hi) { ok = issue_s(i + 1); if (!ok) break; }
         if (!bwd_wait(pds_full, gi & 1, abort_flag)) { report_status(p.status, kStatusWaitTimeout, 841, i, 0); *abort_flag = 1; ok = false; break; }
         tc_fence_after_sync();
         const uint32_t qa = smem_u32(sQ + st * SM::kSmallQK), doa = smem_u32(sdO + st * SM::kSmallV);
-        const uint32_t p_t = tmem_base + kColS + st * BWD_SMALL, ds_t = tmem_base + kColdP;
+        const uint32_t p_t = tmem_base + kColS + bf * BWD_SMALL, ds_t = tmem_base + kColdP;
+        // dK first: it frees the dP^T columns, so the next block's dP^T (which the softmax warps
+        // wait for) is issued before dV
 #pragma unroll
         for (int j = 0; j < BWD_SMALL / 16; ++j)
-          bwd_mma_ts(tmem_base + kColdV, p_t + j * 8, make_smem_desc(doa + j * 2048, BWD_SMALL * 128, 1024, kSwizzle128B),
-                     idesc_dv, (gi | j) != 0 ? 1u : 0u);
+          bwd_mma_ts(tmem_base + kColdK, ds_t + (j >> 1) * 32 + (j & 1) * 8,
+                     make_smem_desc(qa + j * 2048, BWD_SMALL * 128, 1024, kSwizzle128B), idesc_dk, (gi | j) != 0 ? 1u : 0u);
+        if (i + 1 < hi) issue_dp(st_next);
 #pragma unroll
         for (int j = 0; j < BWD_SMALL / 16; ++j)
-          bwd_mma_ts(tmem_base + kColdK, ds_t + j * 8, make_smem_desc(qa + j * 2048, BWD_SMALL * 128, 1024, kSwizzle128B),
-                     idesc_dk, (gi | j) != 0 ? 1u : 0u);
+          bwd_mma_ts(tmem_base + kColdV, p_t + (j >> 1) * 32 + (j & 1) * 8,
+                     make_smem_desc(doa + j * 2048, BWD_SMALL * 128, 1024, kSwizzle128B), idesc_dv, (gi | j) != 0 ? 1u : 0u);
         mma_commit(&q_empty[st]);
-        if (i + 1 < hi) issue_dp(i + 1);
+        st = st_next;
       }
       if (ok) mma_commit(acc_done);
     }
     __syncwarp();
   } else {
     const int q = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int key = k0 + q * 32 + lane;
     const bool key_ok = key < p.S;
     const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
     bool ok = true;
+    int st = 0; uint32_t ph = 0;
     for (int i = lo; i < hi; ++i) {
-      const int gi = i - lo, st = gi & 1;
-      ok = bwd_wait(&q_full[st], (gi >> 1) & 1, abort_flag) && bwd_wait(&s_full[st], (gi >> 1) & 1, abort_flag);
+      const int gi = i - lo, bf = gi & 1;
+      ok = bwd_wait(&q_full[st], ph, abort_flag) && bwd_wait(&s_full[bf], (gi >> 1) & 1, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) { if (lane == 0) report_status(p.status, kStatusWaitTimeout, 850, i, 0); *abort_flag = 1; break; }
       tc_fence_after_sync();
-      const int r0 = i * BWD_SMALL;
-      const bool need_mask = (r0 < k0 + BWD_BIG - 1) || (p.window > 0 && r0 + BWD_SMALL - 1 - p.window >= k0) ||
-                             (k0 + BWD_BIG > p.S);
-      const uint32_t s_addr = tmem_base + lane_addr + kColS + st * BWD_SMALL;
-      const uint32_t dp_addr = tmem_base + lane_addr + kColdP;
-      const float* lse_s = s_lse + st * BWD_SMALL;
-      const float* dl_s = s_delta + st * BWD_SMALL;
-      float pf[BWD_SMALL];
+      const int r0 = i * BWD_SMALL + half * 32;
+      const bool need_mask = (r0 < k0 + BWD_BIG - 1) || (p.window > 0 && r0 + 31 - p.window >= k0) || (k0 + BWD_BIG > p.S);
+      const uint32_t s_addr = tmem_base + lane_addr + kColS + bf * BWD_SMALL + half * 32;
+      const uint32_t dp_addr = tmem_base + lane_addr + kColdP + half * 32;
+      const float4* lse4 = reinterpret_cast<const float4*>(s_lse + st * BWD_SMALL + half * 32);
+      const float4* dl4 = reinterpret_cast<const float4*>(s_delta + st * BWD_SMALL + half * 32);
+      float pf[32];
       {
-        uint32_t s[BWD_SMALL];
+        uint32_t s[32], pk[16];
         tmem_ld_32x32b_x32(s_addr, s);
-        tmem_ld_32x32b_x32(s_addr + 32, s + 32);
         tmem_ld_wait();
 #pragma unroll
-        for (int t = 0; t < BWD_SMALL; ++t) {
-          float v = bwd_exp2(fmaf(__uint_as_float(s[t]), p.scale_log2, -lse_s[t]));
-          if (need_mask && masked(r0 + t, key, p.S, p.window)) v = 0.f;
-          pf[t] = v;
+        for (int t = 0; t < 32; t += 4) {
+          const float4 l4 = lse4[t >> 2];
+          pf[t] = bwd_exp2(fmaf(__uint_as_float(s[t]), p.scale_log2, -l4.x));
+          pf[t + 1] = bwd_exp2(fmaf(__uint_as_float(s[t + 1]), p.scale_log2, -l4.y));
+          pf[t + 2] = bwd_exp2(fmaf(__uint_as_float(s[t + 2]), p.scale_log2, -l4.z));
+          pf[t + 3] = bwd_exp2(fmaf(__uint_as_float(s[t + 3]), p.scale_log2, -l4.w));
         }
-        uint32_t pk[BWD_SMALL / 2];
+        if (need_mask) {
 #pragma unroll
-        for (int t = 0; t < BWD_SMALL; t += 2) pk[t >> 1] = pack_bf16x2(pf[t], pf[t + 1]);
+          for (int t = 0; t < 32; ++t)
+            if (masked(r0 + t, key, p.S, p.window)) pf[t] = 0.f;
+        }
+#pragma unroll
+        for (int t = 0; t < 32; t += 2) pk[t >> 1] = pack_bf16x2(pf[t], pf[t + 1]);
         bwd_tmem_st_x16(s_addr, pk);
-        bwd_tmem_st_x16(s_addr + 16, pk + 16);
       }
       ok = bwd_wait(dp_full, gi & 1, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) { if (lane == 0) report_status(p.status, kStatusWaitTimeout, 851, i, 0); *abort_flag = 1; break; }
       tc_fence_after_sync();
-      uint32_t dk[BWD_SMALL / 2];
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t dp[32];
-        tmem_ld_32x32b_x32(dp_addr + half * 32, dp);
+      {
+        uint32_t dp[32], dk[16];
+        tmem_ld_32x32b_x32(dp_addr, dp);
         tmem_ld_wait();
 #pragma unroll
-        for (int t = 0; t < 32; t += 2) {
-          const int c = half * 32 + t;
-          const float d0 = pf[c] * (__uint_as_float(dp[t]) - dl_s[c]) * p.scale;
-          const float d1 = pf[c + 1] * (__uint_as_float(dp[t + 1]) - dl_s[c + 1]) * p.scale;
-          dk[c >> 1] = pack_bf16x2(d0, d1);
+        for (int t = 0; t < 32; t += 4) {
+          const float4 d4 = dl4[t >> 2];
+          dk[t >> 1] = pack_bf16x2(pf[t] * (__uint_as_float(dp[t]) - d4.x) * p.scale,
+                                   pf[t + 1] * (__uint_as_float(dp[t + 1]) - d4.y) * p.scale);
+          dk[(t >> 1) + 1] = pack_bf16x2(pf[t + 2] * (__uint_as_float(dp[t + 2]) - d4.z) * p.scale,
+                                         pf[t + 3] * (__uint_as_float(dp[t + 3]) - d4.w) * p.scale);
         }
+        bwd_tmem_st_x16(dp_addr, dk);
       }
-      bwd_tmem_st_x16(dp_addr, dk);
-      bwd_tmem_st_x16(dp_addr + 16, dk + 16);
       tmem_st_wait();
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(pds_full);
+      if (++st == BWD_STAGES) { st = 0; ph ^= 1; }
     }
     if (ok && hi > lo) {
       ok = bwd_wait(acc_done, 0, abort_flag);
@@ -579,14 +585,14 @@ k_attn_bwd_dkv(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       const size_t grow = static_cast<size_t>(b) * p.S + (key_ok ? key : 0);
       __nv_bfloat16* dv_row = p.dV + grow * p.dv_row + static_cast<size_t>(h) * p.dv_hs + p.dv_off;
 #pragma unroll 1
-      for (int c = 0; c < DV / 32; ++c) {
+      for (int c = half; c < DV / 32; c += 2) {
         uint32_t o[32];
         tmem_ld_32x32b_x32(tmem_base + lane_addr + kColdV + c * 32, o);
         tmem_ld_wait();
         if (key_ok) store_row32(dv_row + c * 32, o, 1.f);
       }
 #pragma unroll 1
-      for (int c = 0; c < DQK / 32; ++c) {
+      for (int c = half; c < DQK / 32; c += 2) {
         uint32_t o[32];
         tmem_ld_32x32b_x32(tmem_base + lane_addr + kColdK + c * 32, o);
         tmem_ld_wait();
@@ -701,7 +707,8 @@ extern "C" int nmoe_attn_bwd_ex(const void* q, int q_row, int q_hs, const void* 
   p.dV = static_cast<__nv_bfloat16*>(dv); p.dv_row = out_addr[8]; p.dv_hs = out_addr[9]; p.dv_off = out_addr[10];
   p.status = static_cast<StatusRecord*>(status);
   const long long n_rows = static_cast<long long>(B) * S * Hq;
-  k_attn_delta<<<static_cast<unsigned>((n_rows + 7) / 8), 256, 0, st>>>(
+  const long long n_thr = n_rows * (Dv / 8);
+  k_attn_delta<<<static_cast<unsigned>((n_thr + 255) / 256), 256, 0, st>>>(
       static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(d_o), delta, B, S, Hq, Dv);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return static_cast<int>(e);

@@ -39,6 +39,34 @@ NMOE_DEVICE uint8_t quant_block_e4m3(const float* v, uint8_t* dst) {
   return sf;
 }
 
+// E2M1 code (sign | 3 bits) of x: round to nearest on the grid 0,.5,1,1.5,2,3,4,6, ties to the even mantissa bit.
+NMOE_DEVICE uint32_t e2m1_code(float x) {
+  const float a = fabsf(x);
+  uint32_t c;
+  if (a <= 0.25f) c = 0;
+  else if (a < 0.75f) c = 1;
+  else if (a <= 1.25f) c = 2;
+  else if (a < 1.75f) c = 3;
+  else if (a <= 2.5f) c = 4;
+  else if (a < 3.5f) c = 5;
+  else if (a <= 5.f) c = 6;
+  else c = 7;
+  return c | (x < 0.f ? 8u : 0u);
+}
+
+// Quantise 32 floats to E2M1 nibbles (low nibble = even element); returns the E8M0 scale byte, 16 output bytes in w[4].
+NMOE_DEVICE uint8_t quant_block_e2m1_regs(const float* v, uint32_t* w) {
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(v[i]));
+  const uint8_t sf = e8m0_from_amax(amax, kInvFp4Max);
+  const float inv = e8m0_inv_scale(sf);
+  w[0] = w[1] = w[2] = w[3] = 0;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) w[i >> 3] |= e2m1_code(v[i] * inv) << ((i & 7) * 4);
+  return sf;
+}
+
 NMOE_DEVICE void load_block_bf16(const __nv_bfloat16* src, float* v) {
 #pragma unroll
   for (int i = 0; i < 4; ++i) {

@@ -10,6 +10,10 @@
 // push rows straight into the source ranks' RDEP return buffers (see gemm.cu).
 // Requirements: K % 128 == 0; scales in the atom layout of common/sf_layout.cuh.
 //
+// FP4 = true is the same kernel for MXFP4 operands (E2M1 nibbles, two per byte, E8M0 per 32):
+// a stage is still 128 bytes of K per row (256 elements, two scale atoms per 128 rows) and issues
+// four K=64 `kind::mxf4nvf4.block_scale.scale_vec::2X` instructions; K % 256 == 0.
+//
 // Replaces the reference's CuTe-DSL grouped block-scaled kernel (nmoe/blockscaled/grouped.py:545-2093).
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -69,11 +73,12 @@ NMOE_DEVICE void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uin
                : "memory");
 }
 
-template <int BN>
+template <int BN, bool FP4>
 struct MxSmem {
+  static constexpr int kKA = FP4 ? 2 : 1;                 // scale atoms (128 elements of K each) per stage
   static constexpr int kStageA = MX_BM * MX_BK;
   static constexpr int kStageB = BN * MX_BK;
-  static constexpr int kStageSF = 512 + (BN / 128) * 512;
+  static constexpr int kStageSF = kKA * (512 + (BN / 128) * 512);
   static constexpr int kStages = (BN == 256) ? 4 : 6;
   static constexpr int kAcc = (BN == 256) ? 1 : 2;
   static constexpr int kBytes = kStages * (kStageA + kStageB + kStageSF) + 1024 + 256;
@@ -93,14 +98,16 @@ NMOE_DEVICE bool mx_decode(const MxParams& p, int t, int m_tiles, int n_tiles, i
   return true;
 }
 
-template <int BN, int MODE>
+template <int BN, int MODE, bool FP4>
 __global__ void __launch_bounds__(kMxThreads, 1)
-k_gemm_mxfp8(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const MxParams p) {
-  using S = MxSmem<BN>;
+k_gemm_mx(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const MxParams p) {
+  using S = MxSmem<BN, FP4>;
   constexpr int kStages = S::kStages;
   constexpr int kAcc = S::kAcc;
+  constexpr int KA = S::kKA;
   constexpr uint32_t kSfaCol = kAcc * BN;
-  constexpr uint32_t kSfbCol = kSfaCol + 4;
+  constexpr uint32_t kSfbCol = kSfaCol + 4 * KA;
+  static_assert(kSfbCol + 4 * KA * (BN / 128) <= 512, "tensor memory budget");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
@@ -117,8 +124,11 @@ k_gemm_mxfp8(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m_tiles = (MODE == 1) ? min(*p.n_m_tiles, (p.M + MX_BM - 1) / MX_BM) : (p.M + MX_BM - 1) / MX_BM;
   const int n_tiles = (p.N + BN - 1) / BN;
-  const int k_blocks = p.K / MX_BK;
-  const int sf_k_atoms = k_blocks;                  // one atom column per 128 of K
+  const int k_blocks = (p.K + MX_BK * KA - 1) / (MX_BK * KA);   // a stage covers 128 bytes of K per row
+  // FP4 with K % 256 == 128: the last stage holds one scale atom and issues two instructions (the
+  // tile loads past K are zero-filled by TMA)
+  const int tail_atoms = (FP4 && (p.K % (MX_BK * KA)) != 0) ? 1 : KA;
+  const int sf_k_atoms = p.K / 128;                 // one atom column per 128 elements of K
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -153,15 +163,21 @@ k_gemm_mxfp8(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
             ok = false;
             break;
           }
-          mbar_expect_tx(&full[stage], S::kStageA + S::kStageB + S::kStageSF);
+          const int n_atoms = (kb == k_blocks - 1) ? tail_atoms : KA;
+          mbar_expect_tx(&full[stage], S::kStageA + S::kStageB + n_atoms * (512 + (BN / 128) * 512));
           tma_load_2d(sA + stage * S::kStageA, &tmA, &full[stage], kb * MX_BK, m0);
           tma_load_2d(sB + stage * S::kStageB, &tmB, &full[stage], kb * MX_BK, static_cast<int>(brow));
           uint8_t* sf_dst = sSF + stage * S::kStageSF;
-          bulk_load(sf_dst, p.sfa + (static_cast<size_t>(m_blk) * sf_k_atoms + kb) * 512, 512, &full[stage]);
 #pragma unroll
-          for (int a = 0; a < BN / 128; ++a)
-            bulk_load(sf_dst + 512 * (a + 1), p.sfb + (static_cast<size_t>(brow / 128 + a) * sf_k_atoms + kb) * 512, 512,
+          for (int ka = 0; ka < KA; ++ka) {
+            if (ka >= n_atoms) break;
+            bulk_load(sf_dst + 512 * ka, p.sfa + (static_cast<size_t>(m_blk) * sf_k_atoms + kb * KA + ka) * 512, 512,
                       &full[stage]);
+#pragma unroll
+            for (int a = 0; a < BN / 128; ++a)
+              bulk_load(sf_dst + 512 * (KA + ka * (BN / 128) + a),
+                        p.sfb + (static_cast<size_t>(brow / 128 + a) * sf_k_atoms + kb * KA + ka) * 512, 512, &full[stage]);
+          }
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
       }
@@ -195,18 +211,32 @@ k_gemm_mxfp8(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
           const uint32_t b_addr = smem_u32(sB + stage * S::kStageB);
           const uint32_t sf_addr = smem_u32(sSF + stage * S::kStageSF);
           // scale atoms: 32 rows x 16 bytes, no swizzle, 8-row groups 128 bytes apart
-          tmem_cp_32x128b_warpx4(tmem_base + kSfaCol, make_smem_desc(sf_addr, 0, 128, kSwizzleNone));
+          const int n_atoms = (kb == k_blocks - 1) ? tail_atoms : KA;
 #pragma unroll
-          for (int a = 0; a < BN / 128; ++a)
-            tmem_cp_32x128b_warpx4(tmem_base + kSfbCol + 4 * a,
-                                   make_smem_desc(sf_addr + 512 * (a + 1), 0, 128, kSwizzleNone));
+          for (int ka = 0; ka < KA; ++ka) {
+            if (ka >= n_atoms) break;
+            tmem_cp_32x128b_warpx4(tmem_base + kSfaCol + 4 * ka, make_smem_desc(sf_addr + 512 * ka, 0, 128, kSwizzleNone));
+#pragma unroll
+            for (int a = 0; a < BN / 128; ++a)
+              tmem_cp_32x128b_warpx4(tmem_base + kSfbCol + 4 * (ka * (BN / 128) + a),
+                                     make_smem_desc(sf_addr + 512 * (KA + ka * (BN / 128) + a), 0, 128, kSwizzleNone));
+          }
 #pragma unroll
           for (int j = 0; j < MX_BK / 32; ++j) {
             const uint64_t a_desc = make_smem_desc(a_addr + j * 32, 0, 1024, kSwizzle128B);
             const uint64_t b_desc = make_smem_desc(b_addr + j * 32, 0, 1024, kSwizzle128B);
-            const uint32_t idesc = make_idesc_mx(MX_BM, BN, 0, 0, 1, static_cast<uint32_t>(j), static_cast<uint32_t>(j));
-            mma_mxf8f6f4_ss(d_tmem, a_desc, b_desc, idesc, tmem_base + kSfaCol, tmem_base + kSfbCol,
-                            (kb | j) != 0 ? 1u : 0u);
+            if (FP4 && (j >> 1) >= n_atoms) break;
+            if (FP4) {
+              // K=64 per instruction: two scale bytes per row, picked by id 0 / 2 inside atom j/2
+              const uint32_t id = static_cast<uint32_t>(j & 1) * 2;
+              const uint32_t idesc = make_idesc_mx(MX_BM, BN, 1, 1, 1, id, id);
+              mma_mxf4_block32_ss(d_tmem, a_desc, b_desc, idesc, tmem_base + kSfaCol + 4 * (j >> 1),
+                                  tmem_base + kSfbCol + 4 * (BN / 128) * (j >> 1), (kb | j) != 0 ? 1u : 0u);
+            } else {
+              const uint32_t idesc = make_idesc_mx(MX_BM, BN, 0, 0, 1, static_cast<uint32_t>(j), static_cast<uint32_t>(j));
+              mma_mxf8f6f4_ss(d_tmem, a_desc, b_desc, idesc, tmem_base + kSfaCol, tmem_base + kSfbCol,
+                              (kb | j) != 0 ? 1u : 0u);
+            }
           }
           mma_commit(&empty[stage]);
           if (++stage == kStages) { stage = 0; phase ^= 1; }
@@ -303,12 +333,12 @@ static int mx_cached_map(CUtensorMap* out, const void* base, uint64_t inner, uin
   return 0;
 }
 
-template <int BN, int MODE>
+template <int BN, int MODE, bool FP4 = false>
 static int mx_launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const MxParams& p, int max_tiles, cudaStream_t st) {
-  auto kern = k_gemm_mxfp8<BN, MODE>;
+  auto kern = k_gemm_mx<BN, MODE, FP4>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, MxSmem<BN>::kBytes);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, MxSmem<BN, FP4>::kBytes);
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
@@ -317,7 +347,7 @@ static int mx_launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const MxPar
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int grid = max_tiles < sms ? max_tiles : sms;
   if (grid < 1) return 0;
-  kern<<<grid, kMxThreads, MxSmem<BN>::kBytes, st>>>(tmA, tmB, p);
+  kern<<<grid, kMxThreads, MxSmem<BN, FP4>::kBytes, st>>>(tmA, tmB, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : static_cast<int>(e);
 }
@@ -354,4 +384,35 @@ extern "C" int nmoe_gemm_mxfp8(const void* A, const void* sfa, const void* B, co
   const int max_tiles = ((M + MX_BM - 1) / MX_BM) * ((N + bn - 1) / bn);
   if (bn == 256) return mode == 1 ? mx_launch<256, 1>(tmA, tmB, p, max_tiles, st) : mx_launch<256, 0>(tmA, tmB, p, max_tiles, st);
   return mode == 1 ? mx_launch<128, 1>(tmA, tmB, p, max_tiles, st) : mx_launch<128, 0>(tmA, tmB, p, max_tiles, st);
+}
+
+// MXFP4 operands: A [a_rows, K/2] bytes (two E2M1 nibbles per byte, low nibble = even k), B likewise,
+// scales as for MXFP8 (E8M0 per 32 elements, atom layout).  K counts elements; K % 128 == 0.
+extern "C" int nmoe_gemm_mxfp4(const void* A, const void* sfa, const void* B, const void* sfb, void* C, int M, int N,
+                               int K, long long ldc, int mode, int E, const int* tile_expert, const int* n_m_tiles,
+                               long long a_rows, long long b_rows, int bn, void* status, const void* row_meta,
+                               void* const* peer_ret, int push_use_gate, int world, cudaStream_t st) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || (K % MX_BK) != 0) return -1;
+  if (mode == 1 && (N % 128) != 0) return -2;
+  if (bn == 0) bn = (N % 256 == 0) ? 256 : 128;
+  if (bn != 128 && bn != 256) return -5;
+  MxParams p;
+  p.M = M; p.N = N; p.K = K; p.E = E; p.tile_expert = tile_expert; p.n_m_tiles = n_m_tiles;
+  p.C = static_cast<__nv_bfloat16*>(C); p.ldc = ldc;
+  p.sfa = static_cast<const uint8_t*>(sfa); p.sfb = static_cast<const uint8_t*>(sfb);
+  p.status = static_cast<StatusRecord*>(status);
+  p.row_meta = static_cast<const int4*>(row_meta); p.push_use_gate = push_use_gate;
+  for (int r = 0; r < 8; ++r)
+    p.peer_ret[r] = (row_meta && peer_ret && r < world) ? static_cast<__nv_bfloat16*>(peer_ret[r]) : nullptr;
+  if (row_meta && mode != 1) return -6;
+  CUtensorMap tmA, tmB;
+  int rc = mx_cached_map(&tmA, A, K / 2, a_rows, K / 2, MX_BK, MX_BM);
+  if (rc != 0) return rc;
+  rc = mx_cached_map(&tmB, B, K / 2, b_rows, K / 2, MX_BK, bn);
+  if (rc != 0) return rc;
+  const int max_tiles = ((M + MX_BM - 1) / MX_BM) * ((N + bn - 1) / bn);
+  if (bn == 256)
+    return mode == 1 ? mx_launch<256, 1, true>(tmA, tmB, p, max_tiles, st) : mx_launch<256, 0, true>(tmA, tmB, p, max_tiles, st);
+  return mode == 1 ? mx_launch<128, 1, true>(tmA, tmB, p, max_tiles, st) : mx_launch<128, 0, true>(tmA, tmB, p, max_tiles, st);
 }

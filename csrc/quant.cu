@@ -59,6 +59,34 @@ k_swiglu_quant_mxfp8(const __nv_bfloat16* __restrict__ h13, uint8_t* __restrict_
   }
 }
 
+// Same for MXFP4 output: a = silu(gate)*up -> E2M1 nibbles [M,F/2] + scales.
+__global__ void __launch_bounds__(256)
+k_swiglu_quant_mxfp4(const __nv_bfloat16* __restrict__ h13, uint8_t* __restrict__ q, uint8_t* __restrict__ sf,
+                     long long M, int F, int sf_cols_padded, const int* __restrict__ n_tiles_dev) {
+  if (n_tiles_dev != nullptr) M = min(M, static_cast<long long>(*n_tiles_dev) * 128);
+  const long long row = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  if (row >= M) return;
+  const int lane = threadIdx.x & 31;
+  const int nblk = F >> 5;
+  for (int b = lane; b < nblk; b += 32) {
+    float v[32];
+    const __nv_bfloat16* src = h13 + row * 2 * F + b * 64;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int4 p = ld_nc_v4(reinterpret_cast<const int4*>(src) + i);
+      const float2 a = unpack_bf16x2(p.x), bb = unpack_bf16x2(p.y), c = unpack_bf16x2(p.z), d = unpack_bf16x2(p.w);
+      v[4 * i] = __bfloat162float(__float2bfloat16(a.x / (1.f + __expf(-a.x)) * a.y));
+      v[4 * i + 1] = __bfloat162float(__float2bfloat16(bb.x / (1.f + __expf(-bb.x)) * bb.y));
+      v[4 * i + 2] = __bfloat162float(__float2bfloat16(c.x / (1.f + __expf(-c.x)) * c.y));
+      v[4 * i + 3] = __bfloat162float(__float2bfloat16(d.x / (1.f + __expf(-d.x)) * d.y));
+    }
+    uint32_t w[4];
+    const uint8_t s = quant_block_e2m1_regs(v, w);
+    *reinterpret_cast<int4*>(q + row * (F >> 1) + b * 16) = make_int4(w[0], w[1], w[2], w[3]);
+    sf[sf_mma_offset(static_cast<int>(row), b, sf_cols_padded)] = s;
+  }
+}
+
 __global__ void k_dequant_mxfp8(const uint8_t* __restrict__ q, const uint8_t* __restrict__ sf,
                                 __nv_bfloat16* __restrict__ out, long long M, int K, int sf_cols_padded) {
   const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -72,20 +100,6 @@ __global__ void k_dequant_mxfp8(const uint8_t* __restrict__ q, const uint8_t* __
 }
 
 // E2M1 (4-bit) with E8M0 scales per 32 elements: two values per byte, low nibble = even element.
-NMOE_DEVICE uint32_t e2m1_code(float x) {
-  const float a = fabsf(x);
-  uint32_t c;
-  // round to nearest, ties to even mantissa bit: grid 0,.5,1,1.5,2,3,4,6
-  if (a <= 0.25f) c = 0;
-  else if (a < 0.75f) c = 1;
-  else if (a <= 1.25f) c = 2;
-  else if (a < 1.75f) c = 3;
-  else if (a <= 2.5f) c = 4;
-  else if (a < 3.5f) c = 5;
-  else if (a <= 5.f) c = 6;
-  else c = 7;
-  return c | (x < 0.f ? 8u : 0u);
-}
 __global__ void __launch_bounds__(256)
 k_quant_mxfp4(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q, uint8_t* __restrict__ sf, long long M,
               int K, int sf_cols_padded) {
@@ -95,14 +109,8 @@ k_quant_mxfp4(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q, uint
   for (int b = lane; b < (K >> 5); b += 32) {
     float v[32];
     load_block_bf16(x + row * K + b * 32, v);
-    float amax = 0.f;
-#pragma unroll
-    for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(v[i]));
-    const uint8_t s = e8m0_from_amax(amax, kInvFp4Max);
-    const float inv = e8m0_inv_scale(s);
-    uint32_t w[4] = {0, 0, 0, 0};
-#pragma unroll
-    for (int i = 0; i < 32; ++i) w[i >> 3] |= e2m1_code(v[i] * inv) << ((i & 7) * 4);
+    uint32_t w[4];
+    const uint8_t s = quant_block_e2m1_regs(v, w);
     *reinterpret_cast<int4*>(q + row * (K >> 1) + b * 16) = make_int4(w[0], w[1], w[2], w[3]);
     sf[sf_mma_offset(static_cast<int>(row), b, sf_cols_padded)] = s;
   }
@@ -149,6 +157,17 @@ int nmoe_dequant_mxfp8(const void* q, const void* sf, void* out, long long M, in
   const long long n = M * K;
   k_dequant_mxfp8<<<static_cast<unsigned>((n + 255) / 256), 256, 0, st>>>(static_cast<const uint8_t*>(q),
       static_cast<const uint8_t*>(sf), static_cast<__nv_bfloat16*>(out), M, K, sfc);
+  CHECK_LAUNCH();
+  return 0;
+}
+
+int nmoe_swiglu_quant_mxfp4(const void* h13, void* q, void* sf, long long M, int F, const int* n_tiles_dev,
+                            cudaStream_t st) {
+  if (M == 0) return 0;
+  if (F % 32 != 0) return -1;
+  const int sfc = ((F / 32) + 3) & ~3;
+  k_swiglu_quant_mxfp4<<<static_cast<unsigned>((M + 7) / 8), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(h13),
+      static_cast<uint8_t*>(q), static_cast<uint8_t*>(sf), M, F, sfc, n_tiles_dev);
   CHECK_LAUNCH();
   return 0;
 }

@@ -267,6 +267,7 @@ struct PlaceMxArgs {
   uint8_t* peer_xq[kMaxRanks];     // [capacity, H] e4m3
   uint8_t* peer_sf[kMaxRanks];     // atoms [capacity/128][H/128]
   int sf_cols_padded;
+  int fp4;                 // 0: E4M3 bytes (row = H bytes); 1: E2M1 nibbles (row = H/2 bytes)
 };
 
 __global__ void __launch_bounds__(256) k_rdep_place_mx(const PlaceMxArgs am) {
@@ -288,7 +289,8 @@ __global__ void __launch_bounds__(256) k_rdep_place_mx(const PlaceMxArgs am) {
       if (pos < 0) continue;
       const int tok = i / a.K;
       const __nv_bfloat16* src = a.x + static_cast<size_t>(tok) * a.H;
-      uint8_t* qdst = am.peer_xq[owner] + static_cast<size_t>(pos) * a.H;
+      const int row_bytes = am.fp4 ? (a.H >> 1) : a.H;
+      uint8_t* qdst = am.peer_xq[owner] + static_cast<size_t>(pos) * row_bytes;
       uint8_t* sfdst = am.peer_sf[owner];
       for (int b0 = 0; b0 < nblk; b0 += 32) {
         const int b = b0 + lane;
@@ -297,9 +299,14 @@ __global__ void __launch_bounds__(256) k_rdep_place_mx(const PlaceMxArgs am) {
           float v[32];
           uint32_t w[8];
           load_block_bf16(src + b * 32, v);
-          s = quant_block_e4m3_regs(v, w);
-          st_relaxed_sys_v4(qdst + b * 32, make_int4(w[0], w[1], w[2], w[3]));
-          st_relaxed_sys_v4(qdst + b * 32 + 16, make_int4(w[4], w[5], w[6], w[7]));
+          if (am.fp4) {
+            s = quant_block_e2m1_regs(v, w);
+            st_relaxed_sys_v4(qdst + b * 16, make_int4(w[0], w[1], w[2], w[3]));
+          } else {
+            s = quant_block_e4m3_regs(v, w);
+            st_relaxed_sys_v4(qdst + b * 32, make_int4(w[0], w[1], w[2], w[3]));
+            st_relaxed_sys_v4(qdst + b * 32 + 16, make_int4(w[4], w[5], w[6], w[7]));
+          }
         }
         uint32_t packed = s | (__shfl_down_sync(0xffffffffu, s, 1) << 8) | (__shfl_down_sync(0xffffffffu, s, 2) << 16) |
                           (__shfl_down_sync(0xffffffffu, s, 3) << 24);
@@ -319,8 +326,9 @@ __global__ void __launch_bounds__(256) k_rdep_place_mx(const PlaceMxArgs am) {
       const int r0 = a.offs_pad[le] + a.seg_rows[le];
       const int r1 = a.offs_pad[le + 1];
       for (int r = r0 + pb * 8 + warp; r < r1; r += a.pad_blocks * 8) {
-        int4* dst = reinterpret_cast<int4*>(am.peer_xq[a.rank] + static_cast<size_t>(r) * a.H);
-        for (int c = lane; c < (a.H >> 4); c += 32) dst[c] = make_int4(0, 0, 0, 0);
+        const int row_bytes = am.fp4 ? (a.H >> 1) : a.H;
+        int4* dst = reinterpret_cast<int4*>(am.peer_xq[a.rank] + static_cast<size_t>(r) * row_bytes);
+        for (int c = lane; c < (row_bytes >> 4); c += 32) dst[c] = make_int4(0, 0, 0, 0);
         for (int b = lane * 4; b < nblk; b += 128)
           *reinterpret_cast<uint32_t*>(am.peer_sf[a.rank] + sf_mma_offset(r, b, am.sf_cols_padded)) = 0x7f7f7f7fu;
         if (lane == 0 && a.peer_meta[a.rank] != nullptr)
@@ -508,14 +516,15 @@ int nmoe_rdep_place(int rank, int world, int E, int n_local, int T, int K, int H
   return 0;
 }
 
-// Quantising placement: x rows -> owner's e4m3 buffer peer_xq + scale atoms peer_sf (see k_rdep_place_mx).
+// Quantising placement: x rows -> owner's e4m3 (fp4 = 0) or e2m1 (fp4 = 1) buffer peer_xq + scale atoms peer_sf.
 int nmoe_rdep_place_mx(int rank, int world, int E, int n_local, int T, int K, int H, int epoch, const void* x,
                        const int* eid, const float* gates, const int* rank_in_block, const int* block_prefix,
                        const int* base, void* const* peer_xq, void* const* peer_sf, void* const* peer_meta,
                        void* const* peer_data_flags, int* pos_out, const int* offs_pad, const int* seg_rows,
-                       int* done_counter, void* status, cudaStream_t st) {
+                       int* done_counter, void* status, int fp4, cudaStream_t st) {
   if (world > kMaxRanks || (H % 128) != 0) return -1;
   PlaceMxArgs am;
+  am.fp4 = fp4;
   PlaceArgs& a = am.base;
   a.rank = rank; a.world = world; a.E = E; a.n_local = n_local; a.T = T; a.K = K; a.H = H; a.epoch = epoch;
   a.x = static_cast<const __nv_bfloat16*>(x); a.eid = eid; a.gates = gates; a.rank_in_block = rank_in_block;

@@ -72,7 +72,7 @@ class MoE(nn.Module):
       if self.expert_dtype != "bf16":
         if self._wcache is None:
           from ..ops.quant import ExpertWeightCache
-          self._wcache = ExpertWeightCache()
+          self._wcache = ExpertWeightCache(self.expert_dtype)
         wq = self._wcache.get(self.W13, self.W2)
       out = self.rdep.moe(X, gates, eid, self.W13, self.W2, self.save_h13, wq)
     else:

@@ -86,6 +86,42 @@ def gemm_mxfp8(aq: torch.Tensor, asf: torch.Tensor, bq: torch.Tensor, bsf: torch
   return out
 
 
+def gemm_mxfp4(aq: torch.Tensor, asf: torch.Tensor, bq: torch.Tensor, bsf: torch.Tensor, *,
+               out: Optional[torch.Tensor] = None, bn: int = 0) -> torch.Tensor:
+  """C[M,N] bf16 = dequant(A) @ dequant(B)^T for MXFP4 operands (packed [M,K/2] / [N,K/2] bytes,
+  E8M0 scale atoms) on ``kind::mxf4nvf4.block_scale``; K % 256 == 0."""
+  M, K = aq.size(0), aq.size(1) * 2
+  N = bq.size(0)
+  if out is None:
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=aq.device)
+  st = status_buffer(aq.device)
+  L.check(L.lib().nmoe_gemm_mxfp4(L.ptr(aq), L.ptr(asf), L.ptr(bq), L.ptr(bsf), L.ptr(out), M, N, K,
+                                  L.c_ll(out.stride(0)), 0, 1, None, None, L.c_ll(M), L.c_ll(N), bn, L.ptr(st), None,
+                                  None, 0, 0, L.stream()), "gemm_mxfp4")
+  return out
+
+
+def grouped_gemm_mxfp4(aq: torch.Tensor, asf: torch.Tensor, bq: torch.Tensor, bsf: torch.Tensor,
+                       tile_expert: torch.Tensor, n_m_tiles: torch.Tensor, *, out: Optional[torch.Tensor] = None,
+                       bn: int = 0, push: Optional[dict] = None) -> Optional[torch.Tensor]:
+  """Grouped form: rows of aq [Mcap,K/2] are 128-aligned expert segments; bq [E,N,K/2]."""
+  Mcap, K = aq.size(0), aq.size(1) * 2
+  E, N = bq.size(0), bq.size(1)
+  st = status_buffer(aq.device)
+  if push is not None:
+    L.check(L.lib().nmoe_gemm_mxfp4(L.ptr(aq), L.ptr(asf), L.ptr(bq), L.ptr(bsf), None, Mcap, N, K, L.c_ll(N), 1, E,
+                                    L.ptr(tile_expert), L.ptr(n_m_tiles), L.c_ll(Mcap), L.c_ll(E * N), bn, L.ptr(st),
+                                    push["meta"], push["peer_ret"], int(push["use_gate"]), push["world"], L.stream()),
+            "grouped_gemm_mxfp4(push)")
+    return None
+  if out is None:
+    out = torch.empty(Mcap, N, dtype=torch.bfloat16, device=aq.device)
+  L.check(L.lib().nmoe_gemm_mxfp4(L.ptr(aq), L.ptr(asf), L.ptr(bq), L.ptr(bsf), L.ptr(out), Mcap, N, K,
+                                  L.c_ll(out.stride(0)), 1, E, L.ptr(tile_expert), L.ptr(n_m_tiles), L.c_ll(Mcap),
+                                  L.c_ll(E * N), bn, L.ptr(st), None, None, 0, 0, L.stream()), "grouped_gemm_mxfp4")
+  return out
+
+
 def grouped_gemm_mxfp8(aq: torch.Tensor, asf: torch.Tensor, bq: torch.Tensor, bsf: torch.Tensor,
                        tile_expert: torch.Tensor, n_m_tiles: torch.Tensor, *, out: Optional[torch.Tensor] = None,
                        bn: int = 0, push: Optional[dict] = None) -> Optional[torch.Tensor]:
@@ -107,12 +143,30 @@ def grouped_gemm_mxfp8(aq: torch.Tensor, asf: torch.Tensor, bq: torch.Tensor, bs
   return out
 
 
+def swiglu_quant_mxfp4(h13: torch.Tensor, n_tiles: Optional[torch.Tensor] = None):
+  """h13 [M,2F] (gate even / up odd) -> silu(gate)*up as MXFP4: (q [M,F/2] nibbles, sf atoms)."""
+  M, F2 = h13.shape
+  F = F2 // 2
+  q = torch.empty(M, F // 2, dtype=torch.uint8, device=h13.device)
+  sf = torch.empty(sf_bytes(M, F), dtype=torch.uint8, device=h13.device)
+  L.check(L.lib().nmoe_swiglu_quant_mxfp4(L.ptr(h13), L.ptr(q), L.ptr(sf), L.c_ll(M), F, L.ptr(n_tiles), L.stream()),
+          "swiglu_quant_mxfp4")
+  return q, sf
+
+
+def is_fp4(profile: str) -> bool:
+  """The reference's "nvfp4" profile is E2M1 values with one E8M0 scale per 32 elements
+  (nmoe/quant.py:45-72), i.e. the OCP MXFP4 format; both names select it here."""
+  return profile in ("nvfp4", "mxfp4", "fp4")
+
+
 class ExpertWeightCache:
-  """MXFP8 copies of the expert weights, re-quantised whenever the bf16 masters change
+  """MXFP8 (or MXFP4) copies of the expert weights, re-quantised whenever the bf16 masters change
   (detected through the tensors' version counters; the reference rebuilds its cache after every
   optimizer step, nmoe/opt.py:118-125)."""
 
-  def __init__(self):
+  def __init__(self, profile: str = "fp8"):
+    self.fp4 = is_fp4(profile)
     self.ver = (-1, -1)
     self.W13q = self.W13sf = self.W2q = self.W2sf = None
 
@@ -120,11 +174,12 @@ class ExpertWeightCache:
   def get(self, W13: torch.Tensor, W2: torch.Tensor):
     ver = (W13._version, W2._version)
     if ver != self.ver or self.W13q is None:
+      quant = quant_mxfp4 if self.fp4 else quant_mxfp8
       E, N13, H = W13.shape
-      q, self.W13sf = quant_mxfp8(W13.detach().view(E * N13, H))
-      self.W13q = q.view(E, N13, H)
+      q, self.W13sf = quant(W13.detach().view(E * N13, H))
+      self.W13q = q.view(E, N13, -1)
       _, H2, F = W2.shape
-      q2, self.W2sf = quant_mxfp8(W2.detach().view(E * H2, F))
-      self.W2q = q2.view(E, H2, F)
+      q2, self.W2sf = quant(W2.detach().view(E * H2, F))
+      self.W2q = q2.view(E, H2, -1)
       self.ver = ver
     return self.W13q, self.W13sf, self.W2q, self.W2sf

@@ -94,8 +94,11 @@ class Rdep:
       from ..ops.quant import sf_bytes
       regions += [("xq", self.capacity * H), ("sfa", sf_bytes(self.capacity, H))]
     self.slab = PeerSlab(regions, group)
+    self.fp4 = profile in ("nvfp4", "mxfp4", "fp4")
     if profile != "bf16":
-      self.xq = self.slab.local("xq", torch.uint8, (self.capacity, H))
+      # fp4 rows use the first half of the region (H/2 bytes per row)
+      self.xq = (self.slab.local("xq", torch.uint8, (self.capacity, H)).view(-1)[:self.capacity * H // 2].view(self.capacity, H // 2)
+                 if self.fp4 else self.slab.local("xq", torch.uint8, (self.capacity, H)))
       self.sfa = self.slab.local("sfa", torch.uint8, (sf_bytes(self.capacity, H),))
     self.xbuf = self.slab.local("x", torch.bfloat16, (self.capacity, H))
     self.ybuf = self.slab.local("y", torch.bfloat16, (self.capacity, H))
@@ -150,7 +153,7 @@ class Rdep:
       L.stream()), "rdep_place")
 
   def place_mx(self, x: torch.Tensor, plan: Plan, gates: Optional[torch.Tensor]) -> None:
-    """Quantise x's rows to MXFP8 in the placement kernel and store values + scales into the owners' buffers."""
+    """Quantise x's rows to MXFP8 (or MXFP4) in the placement kernel and store values + scales into the owners' buffers."""
     self.epoch_data += 1
     st = G.status_buffer(x.device)
     L.check(L.lib().nmoe_rdep_place_mx(
@@ -158,7 +161,7 @@ class Rdep:
       L.ptr(plan.eid), L.ptr(gates), L.ptr(plan.rank_in_block), L.ptr(plan.block_prefix), L.ptr(plan.base),
       self.slab.ptrs("xq"), self.slab.ptrs("sfa"), self.slab.ptrs("meta"), self.slab.ptrs("data_flags"),
       L.ptr(plan.pos), L.ptr(plan.offs_pad), L.ptr(plan.seg_rows), L.ptr(self.done_counter), L.ptr(st),
-      L.stream()), "rdep_place_mx")
+      int(self.fp4), L.stream()), "rdep_place_mx")
 
   def wait_data(self) -> None:
     st = G.status_buffer(self.device)
@@ -234,9 +237,10 @@ class _MoEFused(torch.autograd.Function):
       W13q, W13sf, W2q, W2sf = wq
       rdep.place_mx(x, plan, gates32.view(-1))
       rdep.wait_data()
-      h13 = Q.grouped_gemm_mxfp8(rdep.xq, rdep.sfa, W13q, W13sf, plan.tile_expert, plan.n_m_tiles)
-      aq, asf = Q.swiglu_quant_mxfp8(h13, plan.n_m_tiles)
-      Q.grouped_gemm_mxfp8(aq, asf, W2q, W2sf, plan.tile_expert, plan.n_m_tiles, push=rdep.push_args(True))
+      ggemm = Q.grouped_gemm_mxfp4 if rdep.fp4 else Q.grouped_gemm_mxfp8
+      h13 = ggemm(rdep.xq, rdep.sfa, W13q, W13sf, plan.tile_expert, plan.n_m_tiles)
+      aq, asf = (Q.swiglu_quant_mxfp4 if rdep.fp4 else Q.swiglu_quant_mxfp8)(h13, plan.n_m_tiles)
+      ggemm(aq, asf, W2q, W2sf, plan.tile_expert, plan.n_m_tiles, push=rdep.push_args(True))
       rdep.finish_return(plan, out)
       ctx.rdep, ctx.plan = rdep, plan
       ctx.save_for_backward(x, gates32, W13, W2, h13 if save_h13 else None)

@@ -54,6 +54,33 @@ def test_gemm_mxfp8_vs_dequantised_matmul(M, N, K, bn):
   assert _rel(c, a.float() @ b.float().t()) < 8e-2
 
 
+@pytest.mark.parametrize("M,N,K,bn", [(128, 128, 256, 128), (256, 256, 512, 256), (1000, 384, 1024, 0), (512, 256, 1408, 0),
+                                     (4096, 2816, 2048, 0)])
+def test_gemm_mxfp4_vs_dequantised_matmul(M, N, K, bn):
+  """kind::mxf4nvf4 block-scaled GEMM vs fp32 matmul of the dequantised (E2M1 x E8M0) operands."""
+  from nmoe_b200 import ops
+  from nmoe_b200.ops import tc_gemm as G
+  from nmoe_b200.ops.quant import gemm_mxfp4
+  from nmoe_b200.ref import quant as RQ
+  torch.manual_seed(3)
+  a = torch.randn(M, K, device="cuda").bfloat16()
+  b = (torch.randn(N, K, device="cuda") * 0.1).bfloat16()
+  aq, asf = ops.quant_mxfp4(a)
+  bq, bsf = ops.quant_mxfp4(b)
+  c = gemm_mxfp4(aq, asf, bq, bsf, bn=bn)
+  torch.cuda.synchronize()
+  G.check_status()
+
+  def deq(q, sf, rows):
+    rp = (rows + 127) // 128 * 128
+    s = RQ.sf_from_mma_layout(sf.cpu(), rp, ((K // 32) + 3) // 4 * 4)[:rows, :K // 32]
+    return RQ.dequant_mxfp4(q.cpu(), s)
+
+  ref = deq(aq, asf, M) @ deq(bq, bsf, N).t()
+  assert _rel(c.cpu(), ref) < 1e-2
+  assert _rel(c.cpu(), a.float().cpu() @ b.float().cpu().t()) < 0.35     # 4-bit operands
+
+
 def test_moe_fp8_forward_close_to_bf16_and_backward_runs():
   from nmoe_b200.parallel.rdep import Rdep, moe_reference
   from nmoe_b200.ops.quant import ExpertWeightCache
@@ -82,5 +109,36 @@ def test_moe_fp8_forward_close_to_bf16_and_backward_runs():
       W13.mul_(1.01)
     cache.get(W13, W2)
     assert cache.ver != v0
+  finally:
+    rd.close()
+
+
+def test_moe_fp4_forward_close_to_bf16_and_backward_runs():
+  """The 4-bit expert profile (E2M1 + E8M0/32 for tokens, activations and weights): quantising
+  placement, both grouped GEMMs on kind::mxf4nvf4, fused return; bf16 straight-through backward."""
+  from nmoe_b200.parallel.rdep import Rdep, moe_reference
+  from nmoe_b200.ops.quant import ExpertWeightCache
+  from nmoe_b200.ops import tc_gemm as G
+  torch.manual_seed(4)
+  dev = torch.device("cuda")
+  T, H, F, E, K = 512, 256, 384, 8, 2           # F = 384: exercises the K % 256 == 128 tail of the down projection
+  rd = Rdep(H, E, K, T, device=dev, profile="nvfp4")
+  try:
+    x = (torch.randn(T, H, device=dev) * 0.5).bfloat16().requires_grad_()
+    W13 = (torch.randn(E, 2 * F, H, device=dev) * 0.05).bfloat16().requires_grad_()
+    W2 = (torch.randn(E, H, F, device=dev) * 0.05).bfloat16().requires_grad_()
+    eid = torch.stack([torch.randperm(E, device=dev)[:K] for _ in range(T)]).int()
+    gates = torch.rand(T, K, device=dev).requires_grad_()
+    cache = ExpertWeightCache("nvfp4")
+    out = rd.moe(x, gates, eid, W13, W2, False, cache.get(W13, W2))
+    out.backward(torch.randn_like(out))
+    torch.cuda.synchronize()
+    G.check_status()
+    ref = moe_reference(x.detach().float().cpu(), gates.detach().cpu(), eid.cpu().long(), W13.detach().float().cpu(),
+                        W2.detach().float().cpu())
+    err = (out.float().cpu() - ref).abs().max().item() / ref.abs().max().item()
+    cos = torch.nn.functional.cosine_similarity(out.float().cpu().flatten(), ref.flatten(), dim=0).item()
+    assert err < 0.5 and cos > 0.95, (err, cos)      # two chained 4-bit GEMMs
+    assert torch.isfinite(x.grad).all() and torch.isfinite(W13.grad).all() and torch.isfinite(W2.grad).all()
   finally:
     rd.close()
