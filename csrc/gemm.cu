@@ -23,6 +23,7 @@
 #include <mutex>
 #include <tuple>
 
+#include "common/epilogue.cuh"
 #include "common/ptx.cuh"
 #include "common/tensormap.h"
 
@@ -117,7 +118,8 @@ struct GemmSmem {
   static constexpr int kStageA = BM * BK * 2;
   static constexpr int kStageB = BN * BK * 2;
   static constexpr int kStages = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
-  static constexpr int kBytes = kStages * (kStageA + kStageB) + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int kEpiStage = 4 * kEpiStageBytesPerWarp;      // transposing store of the fused-return epilogue
+  static constexpr int kBytes = kStages * (kStageA + kStageB) + kEpiStage + 1024 /*align*/ + 256 /*barriers*/;
 };
 
 template <int BN, bool A_MN, bool B_MN, int MODE>
@@ -129,7 +131,8 @@ k_gemm_bf16(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
   uint8_t* sB = smem + kStages * S::kStageA;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * (S::kStageA + S::kStageB));
+  uint8_t* epi_stage = smem + kStages * (S::kStageA + S::kStageB);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(epi_stage + S::kEpiStage);
   uint64_t* full = bars;                    // [kStages]
   uint64_t* empty = bars + kStages;         // [kStages]
   uint64_t* tmem_full = bars + 2 * kStages; // [2]
@@ -287,6 +290,21 @@ k_gemm_bf16(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         }
         tc_fence_after_sync();
       }
+      if (MODE == 1 && p.row_meta != nullptr && have_acc && (p.N & 63) == 0 && (p.ldc & 7) == 0) {
+        // fused return, coalesced: 64 columns (128 bytes) of 4 rows per store instruction
+        uint8_t* stage = epi_stage + (warp - 2) * kEpiStageBytesPerWarp;
+#pragma unroll 1
+        for (int c = 0; c < BN / 64; ++c) {
+          const int col = n0 + c * 64;
+          if (col >= p.N) break;               // uniform over the warp
+          uint32_t r[64];
+          const uint32_t ta = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + c * 64;
+          tmem_ld_32x32b_x32(ta, r);
+          tmem_ld_32x32b_x32(ta + 32, r + 32);
+          tmem_ld_wait();
+          warp_store_rows_64cols(stage, r, push_gate, (row_ok && push_dst != nullptr) ? push_dst + col : nullptr, lane);
+        }
+      } else
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];

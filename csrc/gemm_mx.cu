@@ -24,6 +24,7 @@
 #include <mutex>
 #include <tuple>
 
+#include "common/epilogue.cuh"
 #include "common/ptx.cuh"
 #include "common/tensormap.h"
 
@@ -81,7 +82,8 @@ struct MxSmem {
   static constexpr int kStageSF = kKA * (512 + (BN / 128) * 512);
   static constexpr int kStages = (BN == 256) ? 4 : 6;
   static constexpr int kAcc = (BN == 256) ? 1 : 2;
-  static constexpr int kBytes = kStages * (kStageA + kStageB + kStageSF) + 1024 + 256;
+  static constexpr int kEpiStage = 4 * kEpiStageBytesPerWarp;      // transposing store of the fused-return epilogue
+  static constexpr int kBytes = kStages * (kStageA + kStageB + kStageSF) + kEpiStage + 1024 + 256;
 };
 
 template <int BN, int MODE>
@@ -113,7 +115,8 @@ k_gemm_mx(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
   uint8_t* sA = smem;
   uint8_t* sB = sA + kStages * S::kStageA;
   uint8_t* sSF = sB + kStages * S::kStageB;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sSF + kStages * S::kStageSF);
+  uint8_t* epi_stage = sSF + kStages * S::kStageSF;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(epi_stage + S::kEpiStage);
   uint64_t* full = bars;
   uint64_t* empty = bars + kStages;
   uint64_t* tmem_full = bars + 2 * kStages;
@@ -275,6 +278,21 @@ k_gemm_mx(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
         break;
       }
       tc_fence_after_sync();
+      if (MODE == 1 && p.row_meta != nullptr && (p.N & 63) == 0 && (p.ldc & 7) == 0) {
+        // fused return, coalesced: 64 columns (128 bytes) of 4 rows per store instruction
+        uint8_t* stage = epi_stage + (warp - 2) * kEpiStageBytesPerWarp;
+#pragma unroll 1
+        for (int c = 0; c < BN / 64; ++c) {
+          const int col = n0 + c * 64;
+          if (col >= p.N) break;
+          uint32_t r[64];
+          const uint32_t ta = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + c * 64;
+          tmem_ld_32x32b_x32(ta, r);
+          tmem_ld_32x32b_x32(ta + 32, r + 32);
+          tmem_ld_wait();
+          warp_store_rows_64cols(stage, r, gate, row_ok ? dst_row + col : nullptr, lane);
+        }
+      } else
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
