@@ -91,6 +91,7 @@ class Config:
   expert_optimizer: str = "adamw"     # adamw | muon
   zero2_impl: str = "auto"            # auto | nccl | fused   (fused = peer-memory RS+AdamW+AG kernel)
   zero2_bucket_mb: int = 64
+  rdep_capacity_factor: float = 0.0   # 0 = lossless receive buffers (worst case); > 0 = that multiple of the balanced share
 
   # ---- schedule (warmup by step, hold by tokens, cosine decay to an absolute floor)
   warmup_steps: int = 500

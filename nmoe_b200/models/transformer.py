@@ -87,7 +87,7 @@ class Transformer(nn.Module):
     if cfg.has_moe and on_cuda and rdep is None:
       tpr = tokens_per_rank or max(1, cfg.batch_size // world) * cfg.seq_len
       rdep = Rdep(cfg.dim, cfg.n_routed_experts, cfg.n_activated_experts, tpr, device=torch.device(device),
-                  profile=cfg.dtype)
+                  profile=cfg.dtype, capacity_factor=cfg.rdep_capacity_factor)
     self.rdep = rdep
     with torch.device(device or "cpu"):
       self.embedding = nn.Parameter(torch.empty(cfg.vocab_size, cfg.dim, dtype=dtype))

@@ -63,7 +63,7 @@ class Plan:
 class Rdep:
   """Shared by all MoE layers of a model: peer slab, scratch, epochs."""
 
-  def __init__(self, dim: int, n_experts: int, topk: int, max_tokens: int, *, capacity_factor: float = 2.0,
+  def __init__(self, dim: int, n_experts: int, topk: int, max_tokens: int, *, capacity_factor: float = 0.0,
                group: Optional[dist.ProcessGroup] = None, device: Optional[torch.device] = None,
                profile: str = "bf16"):
     self.world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -77,7 +77,10 @@ class Rdep:
     pairs = max_tokens * topk
     worst = pairs * self.world
     avg = pairs
-    rows = worst if self.world == 1 else min(worst, int(avg * capacity_factor))
+    # capacity_factor <= 0: room for every pair of every rank landing here (lossless, the reference's
+    # sizing: nmoe/model.py:203-204); > 0: that multiple of the balanced share, rows beyond it are
+    # dropped and reported through the status record
+    rows = worst if (self.world == 1 or capacity_factor <= 0) else min(worst, int(avg * capacity_factor))
     # per-expert segments are padded to `align` rows: 256 lets the grouped GEMMs run on CTA pairs (two-SM MMA)
     self.align = 256 if (G.PAIR_MODE and profile == "bf16") else 128
     if os.environ.get("NMOE_RDEP_ALIGN"):
