@@ -9,6 +9,7 @@ distribution with a KL loss) and ``sparse`` (attention over the selected tokens;
 from __future__ import annotations
 
 import torch
+from ..init import trunc_normal_
 import torch.nn.functional as F
 from torch import nn
 
@@ -41,7 +42,7 @@ class DSA(MLA):
   def init_weights(self, init_std: float = 0.02) -> None:
     super().init_weights(init_std)
     for w in (self.wq_idx, self.wk_idx, self.w_idx):
-      nn.init.trunc_normal_(w, mean=0.0, std=0.02)
+      trunc_normal_(w, mean=0.0, std=0.02)
 
   def _idx_inputs(self, x):
     B, T, _ = x.shape

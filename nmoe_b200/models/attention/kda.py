@@ -10,6 +10,7 @@ which is what the layer uses."""
 from __future__ import annotations
 
 import torch
+from ..init import trunc_normal_
 import torch.nn.functional as F
 from torch import nn
 
@@ -97,9 +98,9 @@ class KDA(nn.Module):
 
   def init_weights(self, init_std: float = 0.02) -> None:
     for w in (self.wq_a, self.wq_b, self.wkv_a, self.wkv_b, self.wg, self.wb):
-      nn.init.trunc_normal_(w, mean=0.0, std=0.02)
+      trunc_normal_(w, mean=0.0, std=0.02)
     nn.init.zeros_(self.wg_b)
-    nn.init.trunc_normal_(self.wo, mean=0.0, std=init_std)
+    trunc_normal_(self.wo, mean=0.0, std=init_std)
     self.q_norm.weight.data.fill_(1.0)
     self.kv_norm.weight.data.fill_(1.0)
 

@@ -5,6 +5,7 @@ dims per head; kv = wkv_a x split into a 512-d latent (normed, expanded by wkv_b
 k_nope and v) and one shared 64-d rotary key; softmax scale (nope+rope)^-0.5; output through wo.
 """
 import torch
+from ..init import trunc_normal_
 from torch import nn
 
 from ... import ops
@@ -32,8 +33,8 @@ class MLA(nn.Module):
 
   def init_weights(self, init_std: float = 0.02) -> None:
     for w in (self.wq_a, self.wq_b, self.wkv_a, self.wkv_b):
-      nn.init.trunc_normal_(w, mean=0.0, std=0.02)
-    nn.init.trunc_normal_(self.wo, mean=0.0, std=init_std)
+      trunc_normal_(w, mean=0.0, std=0.02)
+    trunc_normal_(self.wo, mean=0.0, std=init_std)
     self.q_norm.weight.data.fill_(1.0)
     self.kv_norm.weight.data.fill_(1.0)
 

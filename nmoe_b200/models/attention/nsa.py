@@ -12,6 +12,7 @@ Three causal paths mixed by per-token sigmoid gates (Eq. 5):
 from __future__ import annotations
 
 import torch
+from ..init import trunc_normal_
 from torch import nn
 
 from ... import ops
@@ -49,8 +50,8 @@ class NSA(nn.Module):
 
   def init_weights(self, init_std: float = 0.02) -> None:
     for w in (self.qkv_w, self.cmp_w1, self.cmp_w2, self.gate_w1, self.gate_w2, self.cmp_pos):
-      nn.init.trunc_normal_(w, mean=0.0, std=0.02)
-    nn.init.trunc_normal_(self.out_w, mean=0.0, std=init_std)
+      trunc_normal_(w, mean=0.0, std=0.02)
+    trunc_normal_(self.out_w, mean=0.0, std=init_std)
     for b in (self.qkv_b, self.out_b, self.sinks, self.cmp_b1, self.cmp_b2, self.gate_b1):
       nn.init.zeros_(b)
     with torch.no_grad():   # start close to pure sliding-window attention: sigmoid -> (0.1, 0.1, 0.8)

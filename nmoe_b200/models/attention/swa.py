@@ -3,6 +3,7 @@
 dims, the sink logit enters the softmax denominator only, window = ``self.window`` (0 = full causal).
 """
 import torch
+from ..init import trunc_normal_
 from torch import nn
 
 from ... import ops
@@ -31,8 +32,8 @@ class SWA(nn.Module):
     self.softmax_scale = self.head_dim ** -0.5
 
   def init_weights(self, init_std: float = 0.02) -> None:
-    nn.init.trunc_normal_(self.qkv_w, mean=0.0, std=0.02)
-    nn.init.trunc_normal_(self.out_w, mean=0.0, std=init_std)
+    trunc_normal_(self.qkv_w, mean=0.0, std=0.02)
+    trunc_normal_(self.out_w, mean=0.0, std=init_std)
     for p in (self.qkv_b, self.out_b, self.sinks):
       nn.init.zeros_(p)
 

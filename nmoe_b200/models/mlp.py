@@ -1,5 +1,6 @@
 """Dense SwiGLU MLP with the gate and up projections fused into one interleaved weight."""
 import torch
+from .init import normal_, trunc_normal_
 from torch import nn
 
 from .. import ops
@@ -18,8 +19,8 @@ class MLP(nn.Module):
     self.w2 = nn.Parameter(torch.empty(dim, inter_dim, dtype=dtype))
 
   def init_weights(self, init_std: float = 0.02) -> None:
-    nn.init.trunc_normal_(self.w13, mean=0.0, std=0.02)
-    nn.init.trunc_normal_(self.w2, mean=0.0, std=init_std)
+    trunc_normal_(self.w13, mean=0.0, std=0.02)
+    trunc_normal_(self.w2, mean=0.0, std=init_std)
 
   def forward(self, x: torch.Tensor) -> torch.Tensor:
     return ops.linear(ops.swiglu(ops.linear(x, self.w13)), self.w2)

@@ -6,6 +6,7 @@ from __future__ import annotations
 from typing import Optional
 
 import torch
+from .init import normal_, trunc_normal_
 from torch import nn
 
 from .. import ops
@@ -25,7 +26,7 @@ class Router(nn.Module):
     self.register_buffer("bias", torch.zeros(self.n_experts, dtype=torch.float32))
 
   def init_weights(self, init_std: float = 0.02) -> None:
-    nn.init.trunc_normal_(self.gate, mean=0.0, std=init_std)
+    trunc_normal_(self.gate, mean=0.0, std=init_std)
 
   def forward(self, x: torch.Tensor, loads: Optional[torch.Tensor] = None):
     logits = ops.linear(x, self.gate)
@@ -59,7 +60,7 @@ class MoE(nn.Module):
 
   def init_weights(self, init_std: float = 0.02) -> None:
     for W in (self.W13, self.W2):
-      nn.init.trunc_normal_(W, mean=0.0, std=init_std)
+      trunc_normal_(W, mean=0.0, std=init_std)
     self.router.init_weights(init_std)
     if self.shared is not None:
       self.shared.init_weights(init_std)

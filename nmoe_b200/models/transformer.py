@@ -14,6 +14,7 @@ from __future__ import annotations
 from typing import List, Optional, Tuple
 
 import torch
+from .init import normal_, trunc_normal_
 import torch.distributed as dist
 from torch import nn
 from torch.utils.checkpoint import checkpoint
@@ -102,11 +103,11 @@ class Transformer(nn.Module):
   # ------------------------------------------------------------------ init / param sets
   @torch.no_grad()
   def init_weights(self) -> None:
-    nn.init.normal_(self.embedding, mean=0.0, std=0.02)
+    normal_(self.embedding, mean=0.0, std=0.02)
     for blk in self.blocks:
       blk.init_weights()
     self.norm.weight.data.fill_(1.0)
-    nn.init.trunc_normal_(self.lm_head, mean=0.0, std=self.cfg.dim ** -0.5)
+    trunc_normal_(self.lm_head, mean=0.0, std=self.cfg.dim ** -0.5)
 
   def moe_layers(self) -> List[MoE]:
     return [b.ffn for b in self.blocks if isinstance(b.ffn, MoE)]

@@ -134,3 +134,18 @@ def test_muon_expert_optimizer_cpu():
     loss.backward()
     opt.step()
   assert loss.item() < l0
+
+
+def test_trunc_normal_init_has_no_outliers_in_bf16():
+  """Sampling happens in fp32: a bf16 weight must not pick up the +-2 outliers that the stock
+  low-precision ``trunc_normal_`` produces."""
+  import torch
+  from nmoe_b200.models.init import trunc_normal_
+  torch.manual_seed(0)
+  w = torch.empty(64, 2048, dtype=torch.bfloat16)
+  trunc_normal_(w, std=0.02)
+  assert w.float().abs().max().item() < 0.02 * 6.5
+  assert abs(w.float().std().item() - 0.02) < 1e-3
+  w2 = torch.empty(4096, dtype=torch.float32)
+  trunc_normal_(w2, std=1.0, a=-1.0, b=1.0)
+  assert w2.abs().max().item() <= 1.0
