@@ -8,11 +8,11 @@
 // mode 0: dense.  mode 1: rows of A/C are 128-aligned per-expert segments (tile -> expert table,
 // valid tile count on the device), B and its scales are stacked per expert.  The epilogue can
 // push rows straight into the source ranks' RDEP return buffers (see gemm.cu).
-// Requirements: K % 128 == 0; scales in the atom layout of common/sf_layout.cuh.
+// Requirements: K % 32 == 0 (FP8; a tail shorter than a stage is zero-filled by TMA); scales in the atom layout of common/sf_layout.cuh.
 //
 // FP4 = true is the same kernel for MXFP4 operands (E2M1 nibbles, two per byte, E8M0 per 32):
 // a stage is still 128 bytes of K per row (256 elements, two scale atoms per 128 rows) and issues
-// four K=64 `kind::mxf4nvf4.block_scale.scale_vec::2X` instructions; K % 256 == 0.
+// four K=64 `kind::mxf4nvf4.block_scale.scale_vec::2X` instructions; K % 128 == 0.
 //
 // Replaces the reference's CuTe-DSL grouped block-scaled kernel (nmoe/blockscaled/grouped.py:545-2093).
 #include <cuda.h>
@@ -131,7 +131,7 @@ k_gemm_mx(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
   // FP4 with K % 256 == 128: the last stage holds one scale atom and issues two instructions (the
   // tile loads past K are zero-filled by TMA)
   const int tail_atoms = (FP4 && (p.K % (MX_BK * KA)) != 0) ? 1 : KA;
-  const int sf_k_atoms = p.K / 128;                 // one atom column per 128 elements of K
+  const int sf_k_atoms = (p.K + 127) / 128;         // one atom column per 128 elements of K (last one may be partial)
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -381,7 +381,7 @@ extern "C" int nmoe_gemm_mxfp8(const void* A, const void* sfa, const void* B, co
                                long long a_rows, long long b_rows, int bn, void* status, const void* row_meta,
                                void* const* peer_ret, int push_use_gate, int world, cudaStream_t st) {
   if (M <= 0 || N <= 0) return 0;
-  if (K <= 0 || (K % MX_BK) != 0) return -1;
+  if (K <= 0 || (K % 32) != 0) return -1;         // a K tail shorter than 128 is zero-filled by TMA; its scale bytes are padding (127)
   if (mode == 1 && (N % 128) != 0) return -2;
   if (bn == 0) bn = (N % 256 == 0) ? 256 : 128;
   if (bn != 128 && bn != 256) return -5;

@@ -522,7 +522,8 @@ int nmoe_rdep_place_mx(int rank, int world, int E, int n_local, int T, int K, in
                        const int* base, void* const* peer_xq, void* const* peer_sf, void* const* peer_meta,
                        void* const* peer_data_flags, int* pos_out, const int* offs_pad, const int* seg_rows,
                        int* done_counter, void* status, int fp4, cudaStream_t st) {
-  if (world > kMaxRanks || (H % 128) != 0) return -1;
+  // 32-element blocks, 16-byte row stores; the scale bytes of a partial last atom are written as padding (127)
+  if (world > kMaxRanks || (H % 32) != 0 || (fp4 && (H % 64) != 0)) return -1;
   PlaceMxArgs am;
   am.fp4 = fp4;
   PlaceArgs& a = am.base;

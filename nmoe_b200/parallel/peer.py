@@ -23,9 +23,11 @@ class PeerSlab:
   region in every rank's slab; ``local(name, dtype, shape)`` views this rank's region as a tensor.
   """
 
-  def __init__(self, regions: List[Tuple[str, int]], group: Optional[dist.ProcessGroup] = None):
-    self.world = dist.get_world_size(group) if dist.is_initialized() else 1
-    self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+  def __init__(self, regions: List[Tuple[str, int]], group: Optional[dist.ProcessGroup] = None, *,
+               local_only: bool = False):
+    multi = dist.is_initialized() and not local_only
+    self.world = dist.get_world_size(group) if multi else 1
+    self.rank = dist.get_rank(group) if multi else 0
     self.offsets: Dict[str, int] = {}
     self.sizes: Dict[str, int] = {}
     off = 0

@@ -65,9 +65,12 @@ class Rdep:
 
   def __init__(self, dim: int, n_experts: int, topk: int, max_tokens: int, *, capacity_factor: float = 0.0,
                group: Optional[dist.ProcessGroup] = None, device: Optional[torch.device] = None,
-               profile: str = "bf16"):
-    self.world = dist.get_world_size(group) if dist.is_initialized() else 1
-    self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+               profile: str = "bf16", single_process: bool = False):
+    # single_process: every expert lives on this GPU even when a process group exists (each rank of a
+    # serving job runs its own replica of the grading model)
+    multi = dist.is_initialized() and not single_process
+    self.world = dist.get_world_size(group) if multi else 1
+    self.rank = dist.get_rank(group) if multi else 0
     assert n_experts % self.world == 0
     self.group = group
     self.dim, self.E, self.K = dim, n_experts, topk
@@ -96,8 +99,8 @@ class Rdep:
     if profile != "bf16":
       from ..ops.quant import sf_bytes
       regions += [("xq", self.capacity * H), ("sfa", sf_bytes(self.capacity, H))]
-    self.slab = PeerSlab(regions, group)
-    self.fp4 = profile in ("nvfp4", "mxfp4", "fp4")
+    self.slab = PeerSlab(regions, group, local_only=single_process)
+    self.fp4 =profile in ("nvfp4", "mxfp4", "fp4")
     if profile != "bf16":
       # fp4 rows use the first half of the region (H/2 bytes per row)
       self.xq = (self.slab.local("xq", torch.uint8, (self.capacity, H)).view(-1)[:self.capacity * H // 2].view(self.capacity, H // 2)

@@ -37,7 +37,8 @@ def test_quant_mxfp4_bit_exact_vs_emulation():
   assert torch.equal(sf.cpu(), sfr)
 
 
-@pytest.mark.parametrize("M,N,K,bn", [(128, 128, 128, 128), (256, 256, 256, 256), (1000, 384, 512, 0), (4096, 2816, 2048, 0)])
+@pytest.mark.parametrize("M,N,K,bn", [(128, 128, 128, 128), (256, 256, 256, 256), (1000, 384, 512, 0), (300, 256, 2880, 0),
+                                     (4096, 2816, 2048, 0)])
 def test_gemm_mxfp8_vs_dequantised_matmul(M, N, K, bn):
   from nmoe_b200 import ops
   from nmoe_b200.ops import tc_gemm as G
