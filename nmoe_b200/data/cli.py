@@ -1,8 +1,8 @@
 """``python -m nmoe_b200.data.cli <command>`` (nmoe/data/cli.py:1421-1643).
 
 prep | prep-mixture | verify | info | regenerate-index | dedup | cluster | inspect | merge-manifests | flow
-Corpus-curation commands that need a grading model (hydra-*, rephrase) and the download-only commands
-(arxiv-download, arxiv-prep) are registered too and explain what they need when it is missing."""
+hydra-grade | hydra-oracle-label | hydra-train | hydra-calibrate | rephrase   (grading model: --checkpoint)
+The download-only commands (arxiv-download, arxiv-prep) are registered too and say what they need."""
 from __future__ import annotations
 
 import argparse
@@ -126,10 +126,147 @@ def cmd_flow(a) -> int:
   return 0
 
 
-def cmd_needs_model(a) -> int:
-  print(f"'{a.command}' runs the HYDRA grading / rephrasing stack, which needs gpt-oss checkpoint files "
-        f"(--checkpoint) that are not part of this repository; see nmoe_b200/data/hydra.py", file=sys.stderr)
-  return 2
+def _read_jsonl(path: str, text_field: str, limit=None):
+  rows = []
+  with open(path, "r", encoding="utf-8") as f:
+    for line in f:
+      if line.strip():
+        j = json.loads(line)
+        if text_field in j:
+          rows.append(j)
+          if limit and len(rows) >= limit:
+            break
+  return rows
+
+
+def _tokenizer(name: str):
+  """tiktoken encoding when available, else the byte-level tokenizer (tests, offline boxes)."""
+  from .score import ByteTokenizer
+  if name == "bytes":
+    return ByteTokenizer()
+  try:
+    import tiktoken  # type: ignore
+    return tiktoken.get_encoding(name)
+  except Exception:
+    print(f"tokenizer {name!r} is not available here; using UTF-8 bytes", file=sys.stderr)
+    return ByteTokenizer()
+
+
+def _grading_model(a):
+  import torch
+  from ..serve.checkpoint import load_model
+  dev = "cuda" if torch.cuda.is_available() else "cpu"
+  return load_model(a.checkpoint, device=dev, dtype=torch.bfloat16 if dev == "cuda" else torch.float32), dev
+
+
+def cmd_hydra_grade(a) -> int:
+  """JSONL in -> JSONL out with q_probe / rubric scores / decision per document (probe early exit, judge)."""
+  from . import hydra as H
+  model, dev = _grading_model(a)
+  probe, judge = H.load_heads(a.heads, model.cfg.hidden_size, dev)
+  calib = H.Calibration.load(a.calibration or a.heads)
+  tok = _tokenizer(a.tokenizer)
+  rows = _read_jsonl(a.input, a.text_field, a.max_documents)
+  docs = [tok.encode(r[a.text_field])[:a.max_ctx] for r in rows]
+  ids = [str(r.get("id", i)) for i, r in enumerate(rows)]
+  out = H.grade(model, probe, judge, docs, ids, calib, batch_size=a.batch_size, max_ctx=a.max_ctx, early_exit=not a.no_early_exit)
+  with open(a.output, "w", encoding="utf-8") as f:
+    for r in out:
+      f.write(json.dumps(r) + "\n")
+  st = H.grade.last_stats
+  print(f"graded {len(out)} documents: {st['probe_only']} dropped at the probe, {st['judged']} judged -> {a.output}")
+  return 0
+
+
+def cmd_hydra_oracle_label(a) -> int:
+  """Ask the grading model itself for rubric scores (JSON answers) through the batching engine."""
+  from ..serve import Engine
+  from .score import grade_prompts
+  model, _ = _grading_model(a)
+  tok = _tokenizer(a.tokenizer)
+  rows = _read_jsonl(a.input, a.text_field, a.max_documents)
+  eng = Engine(model, max_seq_len=a.max_ctx, max_batch=a.batch_size)
+  res = grade_prompts(eng, tok, [r[a.text_field] for r in rows], max_new=a.max_new, max_ctx=a.max_ctx,
+                      stop_tokens=[getattr(tok, "eot", -1)])
+  with open(a.output, "w", encoding="utf-8") as f:
+    for r, g in zip(rows, res):
+      f.write(json.dumps({"id": r.get("id"), **g}) + "\n")
+  print(f"labelled {len(res)} documents ({sum(1 for g in res if g['scores'])} parsed) -> {a.output}")
+  return 0
+
+
+def cmd_hydra_calibrate(a) -> int:
+  """Fit rubric weights and keep/drop thresholds from judged rows joined with oracle labels."""
+  import torch
+  from . import hydra as H
+  judged = {str(j["doc_id"]): j for j in map(json.loads, open(a.judged, encoding="utf-8")) if j.get("scores")}
+  oracle = {str(j["id"]): j for j in map(json.loads, open(a.oracle, encoding="utf-8")) if j.get("aggregated") is not None}
+  keys = sorted(set(judged) & set(oracle))
+  if not keys:
+    print("no overlapping documents between --judged and --oracle", file=sys.stderr)
+    return 2
+  pred = torch.tensor([[judged[k]["scores"][d] for d in H.RUBRIC] for k in keys])
+  keep = torch.tensor([oracle[k]["aggregated"] >= a.oracle_keep for k in keys])
+  cal = H.calibrate(pred, keep, keep_precision=a.keep_precision)
+  p = cal.save(a.output)
+  print(f"{len(keys)} documents: tau_drop={cal.tau_drop:.3f} tau_keep={cal.tau_keep:.3f} -> {p}")
+  return 0
+
+
+def cmd_hydra_train(a) -> int:
+  """One training phase (A / B / C) of the probe and judge heads over frozen backbone features."""
+  import itertools
+  import torch
+  from . import hydra as H
+  from ..serve.model import pool_hidden
+  model, dev = _grading_model(a)
+  cfg = model.cfg
+  tok = _tokenizer(a.tokenizer)
+  rows = _read_jsonl(a.input, a.text_field, a.max_documents)
+  try:
+    probe, judge = H.load_heads(a.heads, cfg.hidden_size, dev)
+  except FileNotFoundError:
+    probe, judge = H.ProbeHead(cfg.hidden_size).to(dev), H.JudgeHead(cfg.hidden_size).to(dev)
+
+  def features(batch):
+    ids, pos, mask = H.pad_batch(batch["docs"], a.max_ctx, dev)
+    with torch.no_grad():
+      _, taps = model(ids, pos, up_to_layer=cfg.judge_layer, return_hidden_states=True, no_logits=True)
+    return pool_hidden(taps[cfg.probe_layer], mask), taps[cfg.judge_layer].float(), mask
+
+  def batches():
+    g = torch.Generator().manual_seed(0)
+    for _ in itertools.count():
+      idx = torch.randperm(len(rows), generator=g)[:a.batch_size].tolist()
+      b = {"docs": [tok.encode(rows[i][a.text_field])[:a.max_ctx] for i in idx]}
+      nan = float("nan")
+      b["targets"] = {k: torch.tensor([float(rows[i].get(k, nan)) for i in idx], device=dev)
+                      for k, (w, kind) in H.PROBE_TASKS.items() if kind == "reg"}
+      b["rubric"] = torch.tensor([[float((rows[i].get("scores") or {}).get(d, nan)) for d in H.RUBRIC] for i in idx], device=dev)
+      yield b
+
+  losses = H.train_heads(H.PhaseConfig(a.phase, steps=a.steps, lr=a.lr), probe, judge, batches(), features,
+                         log=lambda s, l: print(f"phase {a.phase} step {s} loss {l:.4f}"))
+  H.save_heads(a.heads, probe, judge)
+  print(f"phase {a.phase}: loss {losses[0]:.4f} -> {losses[-1]:.4f}; heads saved to {a.heads}")
+  return 0
+
+
+def cmd_rephrase(a) -> int:
+  from ..serve import Engine
+  from .rephrase import filter_by_fidelity, rephrase_batch
+  model, _ = _grading_model(a)
+  tok = _tokenizer(a.tokenizer)
+  rows = _read_jsonl(a.input, a.text_field, a.max_documents)
+  texts = [r[a.text_field] for r in rows]
+  eng = Engine(model, max_seq_len=a.max_ctx, max_batch=a.batch_size)
+  rew = rephrase_batch(eng, tok, texts, num_versions=a.num_versions, chunk_size=a.chunk_size, stop_tokens=[getattr(tok, "eot", -1)])
+  kept = filter_by_fidelity(texts, rew) if not a.no_filter else rew
+  with open(a.output, "w", encoding="utf-8") as f:
+    for r in kept:
+      f.write(json.dumps({"id": rows[r.doc].get("id", r.doc), "version": r.version, "style": r.style, "text": r.text}) + "\n")
+  print(f"{len(rew)} rewrites, {len(kept)} kept -> {a.output}")
+  return 0
 
 
 def cmd_needs_network(a) -> int:
@@ -160,8 +297,23 @@ def build_parser() -> argparse.ArgumentParser:
   p.add_argument("--start", type=int); p.add_argument("--length", type=int, default=64); p.add_argument("--tokenizer")
   p = sub.add_parser("merge-manifests"); p.set_defaults(fn=cmd_merge_manifests); p.add_argument("parts", nargs="+"); p.add_argument("--output", required=True)
   p = sub.add_parser("flow"); p.set_defaults(fn=cmd_flow); p.add_argument("spec")
-  for name in ("rephrase", "hydra-oracle-label", "hydra-calibrate", "hydra-grade", "hydra-train"):
-    p = sub.add_parser(name); p.set_defaults(fn=cmd_needs_model); p.add_argument("rest", nargs="*")
+  def model_args(p, heads=False):
+    p.add_argument("--checkpoint", required=True); p.add_argument("--input", required=True); p.add_argument("--output", required=True)
+    p.add_argument("--text-field", default="text"); p.add_argument("--tokenizer", default="o200k_harmony")
+    p.add_argument("--max-ctx", type=int, default=4096); p.add_argument("--batch-size", type=int, default=32)
+    p.add_argument("--max-documents", type=int)
+    if heads:
+      p.add_argument("--heads", required=True)
+  p = sub.add_parser("hydra-grade"); p.set_defaults(fn=cmd_hydra_grade); model_args(p, heads=True)
+  p.add_argument("--calibration"); p.add_argument("--no-early-exit", action="store_true")
+  p = sub.add_parser("hydra-oracle-label"); p.set_defaults(fn=cmd_hydra_oracle_label); model_args(p); p.add_argument("--max-new", type=int, default=256)
+  p = sub.add_parser("hydra-train"); p.set_defaults(fn=cmd_hydra_train); model_args(p, heads=True)
+  p.add_argument("--phase", choices=["A", "B", "C"], required=True); p.add_argument("--steps", type=int, default=1000); p.add_argument("--lr", type=float, default=1e-3)
+  p = sub.add_parser("hydra-calibrate"); p.set_defaults(fn=cmd_hydra_calibrate)
+  p.add_argument("--judged", required=True); p.add_argument("--oracle", required=True); p.add_argument("--output", required=True)
+  p.add_argument("--oracle-keep", type=float, default=0.6); p.add_argument("--keep-precision", type=float, default=0.9)
+  p = sub.add_parser("rephrase"); p.set_defaults(fn=cmd_rephrase); model_args(p)
+  p.add_argument("--num-versions", type=int, default=1); p.add_argument("--chunk-size", type=int, default=2048); p.add_argument("--no-filter", action="store_true")
   for name in ("arxiv-download", "arxiv-prep"):
     p = sub.add_parser(name); p.set_defaults(fn=cmd_needs_network); p.add_argument("rest", nargs="*")
   return ap
