@@ -1,16 +1,18 @@
 """Muon: momentum followed by a Newton-Schulz orthogonalisation of each 2-D update
 (reference: the orthogonaliser in nmoe/csrc/muon.cu:288-499, 5 steps of X <- aX + (bA + cA^2)X with
-A = X X^T after Frobenius normalisation).  The three matrix products of every step run on the
+A = X X^T after Frobenius normalisation).  The iteration is native (``csrc/muon.cu``): its products run on the
 tcgen05 bf16 GEMM (``ops.gemm``); the quintic coefficients are the usual (3.4445, -4.7750, 2.0315).
 """
 from __future__ import annotations
 
+import ctypes
 from typing import Dict, List, Tuple
 
 import torch
 
 from ..ref import ops as R
-from .tc_gemm import gemm
+from . import _lib as L
+from .tc_gemm import status_buffer
 
 COEFFS = (3.4445, -4.7750, 2.0315)
 
@@ -22,19 +24,20 @@ def newton_schulz(x: torch.Tensor, steps: int = 5, coeffs: Tuple[float, float, f
     return R.newton_schulz(x, steps, coeffs, eps)
   a, b, c = coeffs
   shp = x.shape
-  X = x.reshape(-1, shp[-2], shp[-1])
-  out = torch.empty_like(X, dtype=torch.bfloat16)
-  for i in range(X.size(0)):
-    m = X[i].float()
-    transposed = m.size(0) > m.size(1)
-    if transposed:
-      m = m.t()
-    m = (m / (m.norm() + eps)).bfloat16().contiguous()
-    for _ in range(steps):
-      A = gemm(m, m)                                   # X X^T                [M, M]
-      B = (b * A.float() + c * gemm(A, A).float()).bfloat16()   # A symmetric: A A^T = A^2
-      m = (a * m.float() + gemm(B, m, b_mn=True).float()).bfloat16()
-    out[i] = m.t() if transposed else m
+  X = x.reshape(-1, shp[-2], shp[-1]).to(torch.bfloat16).contiguous()
+  E, Rr, Cc = X.shape
+  if Rr % 8 or Cc % 8:
+    return R.newton_schulz(x.float(), steps, coeffs, eps).to(x.dtype)
+  # the whole iteration runs inside the library (csrc/muon.cu): normalise, then per step three
+  # tcgen05 GEMMs with the "a X +" term folded into the last one's accumulate mode
+  lib = L.lib()
+  lib.nmoe_muon_workspace_elems.restype = ctypes.c_longlong
+  ws = torch.empty(lib.nmoe_muon_workspace_elems(Rr, Cc), dtype=torch.bfloat16, device=x.device)
+  ssq = torch.empty(E, dtype=torch.float32, device=x.device)
+  out = torch.empty_like(X)
+  L.check(lib.nmoe_muon_orth(L.ptr(X), L.ptr(out), E, Rr, Cc, int(steps), L.c_float(a), L.c_float(b), L.c_float(c),
+                             L.c_float(eps), L.ptr(ws), L.ptr(ssq), L.ptr(status_buffer(x.device)), L.stream()),
+          "muon_orth", E * (3 + 5 * steps))
   return out.view(shp).to(x.dtype)
 
 

@@ -174,3 +174,16 @@ def test_metrics_store_and_experiments(tmp_path, monkeypatch):
   run = tr.get_run("runX")
   assert run["status"] == "completed" and json.loads(run["results_json"])["steps_completed"] == 6
   tr.close()
+
+
+def test_hybrid_routing_model_uses_same_index_proxy():
+  from nmoe_b200.parallel.hybrid import Hop, route, simulate_dispatch
+  assert route(3, 3, 8) == [Hop(3, 3, "local")]
+  assert route(1, 6, 8) == [Hop(1, 6, "peer")]
+  assert route(1, 14, 8) == [Hop(1, 9, "net"), Hop(9, 14, "peer")]       # node 1's GPU with local index 1 forwards
+  assert route(6, 14, 8) == [Hop(6, 14, "net")]                          # the proxy is the owner itself
+  eid = [[0, 5, 9, 15], [3, 3, 12, 8], [1, 14, 7, 2], [6, 10, 11, 13]]   # 4 ranks, 2 per node, 16 experts (4 per rank)
+  inbox, carried = simulate_dispatch(eid, 16, 4, 2)
+  assert sum(len(v) for v in inbox.values()) == 16
+  assert [t[2] for t in inbox[0]] == sorted(t[2] for t in inbox[0]) and all(e // 4 == 0 for _, _, e in inbox[0])
+  assert carried["net"] == sum(1 for r in range(4) for e in eid[r] if (e // 4) // 2 != r // 2)
