@@ -10,9 +10,11 @@
 // push rows straight into the source ranks' RDEP return buffers (see gemm.cu).
 // Requirements: K % 32 == 0 (FP8; a tail shorter than a stage is zero-filled by TMA); scales in the atom layout of common/sf_layout.cuh.
 //
-// FP4 = true is the same kernel for MXFP4 operands (E2M1 nibbles, two per byte, E8M0 per 32):
+// FMT = 1 is the same kernel for MXFP4 operands (E2M1 nibbles, two per byte, E8M0 per 32):
 // a stage is still 128 bytes of K per row (256 elements, two scale atoms per 128 rows) and issues
 // four K=64 `kind::mxf4nvf4.block_scale.scale_vec::2X` instructions; K % 128 == 0.
+// FMT = 2 is NVFP4: E2M1 nibbles with one UE4M3 scale per 16 elements (`scale_vec::4X`, four atoms per stage,
+// one per instruction) and a per-tensor fp32 scale pair folded into the epilogue (alpha); K % 64 == 0.
 //
 // Replaces the reference's CuTe-DSL grouped block-scaled kernel (nmoe/blockscaled/grouped.py:545-2093).
 #include <cuda.h>
@@ -48,6 +50,7 @@ struct MxParams {
   const int4* row_meta;
   __nv_bfloat16* peer_ret[8];
   int push_use_gate;
+  float alpha;                 // multiplies every output (NVFP4: product of the two per-tensor scales)
 };
 
 NMOE_DEVICE uint64_t mx_timer_ns() {
@@ -74,13 +77,18 @@ NMOE_DEVICE void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uin
                : "memory");
 }
 
-template <int BN, bool FP4>
+// FMT: 0 = MXFP8 (E4M3, E8M0 per 32), 1 = MXFP4 (E2M1, E8M0 per 32), 2 = NVFP4 (E2M1, UE4M3 per 16)
+template <int BN, int FMT>
 struct MxSmem {
-  static constexpr int kKA = FP4 ? 2 : 1;                 // scale atoms (128 elements of K each) per stage
+  static constexpr int kKA = FMT == 0 ? 1 : (FMT == 1 ? 2 : 4);   // scale atoms (4 scale bytes per row each) per stage
+  static constexpr int kStageK = FMT == 0 ? 128 : 256;            // elements of K per stage (always 128 bytes per row)
+  static constexpr int kAtomK = FMT == 2 ? 64 : 128;              // elements of K covered by one scale atom
   static constexpr int kStageA = MX_BM * MX_BK;
   static constexpr int kStageB = BN * MX_BK;
   static constexpr int kStageSF = kKA * (512 + (BN / 128) * 512);
-  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  static constexpr int kStages = (BN == 256) ? (FMT == 2 ? 3 : 4) : (FMT == 2 ? 5 : 6);
+  static_assert(kStages * (MX_BM * MX_BK + BN * MX_BK + kKA * (512 + (BN / 128) * 512)) + 4 * kEpiStageBytesPerWarp + 1280 <= 232448,
+                "shared memory budget");
   static constexpr int kAcc = (BN == 256) ? 1 : 2;
   static constexpr int kEpiStage = 4 * kEpiStageBytesPerWarp;      // transposing store of the fused-return epilogue
   static constexpr int kBytes = kStages * (kStageA + kStageB + kStageSF) + kEpiStage + 1024 + 256;
@@ -100,10 +108,11 @@ NMOE_DEVICE bool mx_decode(const MxParams& p, int t, int m_tiles, int n_tiles, i
   return true;
 }
 
-template <int BN, int MODE, bool FP4>
+template <int BN, int MODE, int FMT>
 __global__ void __launch_bounds__(kMxThreads, 1)
 k_gemm_mx(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const MxParams p) {
-  using S = MxSmem<BN, FP4>;
+  using S = MxSmem<BN, FMT>;
+  constexpr bool FP4 = FMT != 0;
   constexpr int kStages = S::kStages;
   constexpr int kAcc = S::kAcc;
   constexpr int KA = S::kKA;
@@ -127,11 +136,11 @@ k_gemm_mx(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m_tiles = (MODE == 1) ? min(*p.n_m_tiles, (p.M + MX_BM - 1) / MX_BM) : (p.M + MX_BM - 1) / MX_BM;
   const int n_tiles = (p.N + BN - 1) / BN;
-  const int k_blocks = (p.K + MX_BK * KA - 1) / (MX_BK * KA);   // a stage covers 128 bytes of K per row
-  // FP4 with K % 256 == 128: the last stage holds one scale atom and issues two instructions (the
-  // tile loads past K are zero-filled by TMA)
-  const int tail_atoms = (FP4 && (p.K % (MX_BK * KA)) != 0) ? 1 : KA;
-  const int sf_k_atoms = (p.K + 127) / 128;         // one atom column per 128 elements of K (last one may be partial)
+  const int k_blocks = (p.K + S::kStageK - 1) / S::kStageK;     // a stage covers 128 bytes of K per row
+  // 4-bit formats with a K tail shorter than a stage: the last stage loads only the scale atoms that
+  // exist and issues only their instructions (the tile loads past K are zero-filled by TMA)
+  const int tail_atoms = (FP4 && (p.K % S::kStageK) != 0) ? ((p.K % S::kStageK) + S::kAtomK - 1) / S::kAtomK : KA;
+  const int sf_k_atoms = (p.K + S::kAtomK - 1) / S::kAtomK;     // atom columns along K (the last one may be partial)
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -228,6 +237,14 @@ k_gemm_mx(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
           for (int j = 0; j < MX_BK / 32; ++j) {
             const uint64_t a_desc = make_smem_desc(a_addr + j * 32, 0, 1024, kSwizzle128B);
             const uint64_t b_desc = make_smem_desc(b_addr + j * 32, 0, 1024, kSwizzle128B);
+            if (FMT == 2) {
+              // NVFP4: K=64 per instruction, four UE4M3 scale bytes per row = one whole atom per instruction
+              if (j >= n_atoms) break;
+              const uint32_t idesc = make_idesc_mx(MX_BM, BN, 1, 1, 0, 0, 0);
+              mma_nvf4_block16_ss(d_tmem, a_desc, b_desc, idesc, tmem_base + kSfaCol + 4 * j,
+                                  tmem_base + kSfbCol + 4 * (BN / 128) * j, (kb | j) != 0 ? 1u : 0u);
+              continue;
+            }
             if (FP4 && (j >> 1) >= n_atoms) break;
             if (FP4) {
               // K=64 per instruction: two scale bytes per row, picked by id 0 / 2 inside atom j/2
@@ -261,13 +278,13 @@ k_gemm_mx(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
       const int n0 = n_blk * BN;
       bool row_ok = row < m_limit;
       __nv_bfloat16* dst_row = row_ok ? p.C + static_cast<long long>(row) * p.ldc : nullptr;
-      float gate = 1.f;
+      float gate = p.alpha;
       if (MODE == 1 && p.row_meta != nullptr && row_ok) {
         const int4 mv = __ldg(p.row_meta + row);
         row_ok = mv.w != 0;
         if (row_ok) {
           dst_row = p.peer_ret[mv.x] + static_cast<long long>(mv.y) * p.ldc;
-          if (p.push_use_gate) gate = __int_as_float(mv.z);
+          if (p.push_use_gate) gate = p.alpha * __int_as_float(mv.z);
         }
       }
       bool ok = mx_wait(&tmem_full[acc], acc_phase, abort_flag);
@@ -351,12 +368,12 @@ static int mx_cached_map(CUtensorMap* out, const void* base, uint64_t inner, uin
   return 0;
 }
 
-template <int BN, int MODE, bool FP4 = false>
+template <int BN, int MODE, int FMT = 0>
 static int mx_launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const MxParams& p, int max_tiles, cudaStream_t st) {
-  auto kern = k_gemm_mx<BN, MODE, FP4>;
+  auto kern = k_gemm_mx<BN, MODE, FMT>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, MxSmem<BN, FP4>::kBytes);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, MxSmem<BN, FMT>::kBytes);
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
@@ -365,7 +382,7 @@ static int mx_launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const MxPar
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int grid = max_tiles < sms ? max_tiles : sms;
   if (grid < 1) return 0;
-  kern<<<grid, kMxThreads, MxSmem<BN, FP4>::kBytes, st>>>(tmA, tmB, p);
+  kern<<<grid, kMxThreads, MxSmem<BN, FMT>::kBytes, st>>>(tmA, tmB, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : static_cast<int>(e);
 }
@@ -390,7 +407,7 @@ extern "C" int nmoe_gemm_mxfp8(const void* A, const void* sfa, const void* B, co
   p.C = static_cast<__nv_bfloat16*>(C); p.ldc = ldc;
   p.sfa = static_cast<const uint8_t*>(sfa); p.sfb = static_cast<const uint8_t*>(sfb);
   p.status = static_cast<StatusRecord*>(status);
-  p.row_meta = static_cast<const int4*>(row_meta); p.push_use_gate = push_use_gate;
+  p.row_meta = static_cast<const int4*>(row_meta); p.push_use_gate = push_use_gate; p.alpha = 1.f;
   for (int r = 0; r < 8; ++r)
     p.peer_ret[r] = (row_meta && peer_ret && r < world) ? static_cast<__nv_bfloat16*>(peer_ret[r]) : nullptr;
   if (row_meta && mode != 1) return -6;
@@ -420,7 +437,7 @@ extern "C" int nmoe_gemm_mxfp4(const void* A, const void* sfa, const void* B, co
   p.C = static_cast<__nv_bfloat16*>(C); p.ldc = ldc;
   p.sfa = static_cast<const uint8_t*>(sfa); p.sfb = static_cast<const uint8_t*>(sfb);
   p.status = static_cast<StatusRecord*>(status);
-  p.row_meta = static_cast<const int4*>(row_meta); p.push_use_gate = push_use_gate;
+  p.row_meta = static_cast<const int4*>(row_meta); p.push_use_gate = push_use_gate; p.alpha = 1.f;
   for (int r = 0; r < 8; ++r)
     p.peer_ret[r] = (row_meta && peer_ret && r < world) ? static_cast<__nv_bfloat16*>(peer_ret[r]) : nullptr;
   if (row_meta && mode != 1) return -6;
@@ -431,6 +448,34 @@ extern "C" int nmoe_gemm_mxfp4(const void* A, const void* sfa, const void* B, co
   if (rc != 0) return rc;
   const int max_tiles = ((M + MX_BM - 1) / MX_BM) * ((N + bn - 1) / bn);
   if (bn == 256)
-    return mode == 1 ? mx_launch<256, 1, true>(tmA, tmB, p, max_tiles, st) : mx_launch<256, 0, true>(tmA, tmB, p, max_tiles, st);
-  return mode == 1 ? mx_launch<128, 1, true>(tmA, tmB, p, max_tiles, st) : mx_launch<128, 0, true>(tmA, tmB, p, max_tiles, st);
+    return mode == 1 ? mx_launch<256, 1, 1>(tmA, tmB, p, max_tiles, st) : mx_launch<256, 0, 1>(tmA, tmB, p, max_tiles, st);
+  return mode == 1 ? mx_launch<128, 1, 1>(tmA, tmB, p, max_tiles, st) : mx_launch<128, 0, 1>(tmA, tmB, p, max_tiles, st);
+}
+
+// NVFP4 operands: packed E2M1 as for MXFP4; scales are UE4M3 bytes, one per 16 elements, in the same
+// 128-row x 4-byte atom layout (atoms [rows/128][K/64]); alpha = tensor_scale_a * tensor_scale_b.
+extern "C" int nmoe_gemm_nvfp4(const void* A, const void* sfa, const void* B, const void* sfb, void* C, int M, int N,
+                               int K, long long ldc, int mode, int E, const int* tile_expert, const int* n_m_tiles,
+                               long long a_rows, long long b_rows, int bn, float alpha, void* status, cudaStream_t st) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || (K % 64) != 0) return -1;
+  if (mode == 1 && (N % 128) != 0) return -2;
+  if (bn == 0) bn = (N % 256 == 0) ? 256 : 128;
+  if (bn != 128 && bn != 256) return -5;
+  MxParams p;
+  p.M = M; p.N = N; p.K = K; p.E = E; p.tile_expert = tile_expert; p.n_m_tiles = n_m_tiles;
+  p.C = static_cast<__nv_bfloat16*>(C); p.ldc = ldc;
+  p.sfa = static_cast<const uint8_t*>(sfa); p.sfb = static_cast<const uint8_t*>(sfb);
+  p.status = static_cast<StatusRecord*>(status);
+  p.row_meta = nullptr; p.push_use_gate = 0; p.alpha = alpha;
+  for (int r = 0; r < 8; ++r) p.peer_ret[r] = nullptr;
+  CUtensorMap tmA, tmB;
+  int rc = mx_cached_map(&tmA, A, K / 2, a_rows, K / 2, MX_BK, MX_BM);
+  if (rc != 0) return rc;
+  rc = mx_cached_map(&tmB, B, K / 2, b_rows, K / 2, MX_BK, bn);
+  if (rc != 0) return rc;
+  const int max_tiles = ((M + MX_BM - 1) / MX_BM) * ((N + bn - 1) / bn);
+  if (bn == 256)
+    return mode == 1 ? mx_launch<256, 1, 2>(tmA, tmB, p, max_tiles, st) : mx_launch<256, 0, 2>(tmA, tmB, p, max_tiles, st);
+  return mode == 1 ? mx_launch<128, 1, 2>(tmA, tmB, p, max_tiles, st) : mx_launch<128, 0, 2>(tmA, tmB, p, max_tiles, st);
 }

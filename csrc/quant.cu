@@ -116,6 +116,41 @@ k_quant_mxfp4(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q, uint
   }
 }
 
+// NVFP4: E2M1 values, one E4M3 scale per 16 elements (relative to the fp32 per-tensor scale *ts),
+// scales in the atom layout with sf_cols = K/16 padded to a multiple of 4.  x ~= e2m1 * e4m3 * ts.
+__global__ void __launch_bounds__(256)
+k_quant_nvfp4(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q, uint8_t* __restrict__ sf, long long M,
+              int K, int sf_cols_padded, const float* __restrict__ ts) {
+  const long long row = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  if (row >= M) return;
+  const int lane = threadIdx.x & 31;
+  const float tscale = *ts;
+  for (int b = lane; b < (K >> 5); b += 32) {
+    float v[32];
+    load_block_bf16(x + row * K + b * 32, v);
+    uint32_t w[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      float amax = 0.f;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[16 * h + i]));
+      const float want = fminf(amax / 6.f / tscale, 448.f);
+      const __nv_fp8_storage_t sb = __nv_cvt_float_to_fp8(want, __NV_SATFINITE, __NV_E4M3);
+      const __half_raw hr = __nv_cvt_fp8_to_halfraw(sb, __NV_E4M3);
+      const float denom = __half2float(*reinterpret_cast<const __half*>(&hr)) * tscale;
+      const float inv = denom > 0.f ? 1.f / denom : 0.f;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const int k = 16 * h + i;
+        w[k >> 3] |= e2m1_code(denom > 0.f ? v[k] / denom : 0.f) << ((k & 7) * 4);
+      }
+      (void)inv;
+      sf[sf_mma_offset(static_cast<int>(row), 2 * b + h, sf_cols_padded)] = sb;
+    }
+    *reinterpret_cast<int4*>(q + row * (K >> 1) + b * 16) = make_int4(w[0], w[1], w[2], w[3]);
+  }
+}
+
 }  // namespace nmoe
 
 using namespace nmoe;
@@ -178,6 +213,18 @@ int nmoe_quant_mxfp4(const void* x, void* q, void* sf, long long M, int K, cudaS
   const int sfc = ((K / 32) + 3) & ~3;
   k_quant_mxfp4<<<static_cast<unsigned>((M + 7) / 8), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x),
       static_cast<uint8_t*>(q), static_cast<uint8_t*>(sf), M, K, sfc);
+  CHECK_LAUNCH();
+  return 0;
+}
+
+// ts: device pointer to the fp32 per-tensor scale (amax / (6 * 448)); sf buffer: nmoe_sf_bytes(M, 2 * K) bytes
+// (one scale per 16 elements = twice the columns of the 32-element formats).
+int nmoe_quant_nvfp4(const void* x, void* q, void* sf, long long M, int K, const float* ts, cudaStream_t st) {
+  if (M == 0) return 0;
+  if (K % 32 != 0) return -1;
+  const int sfc = ((K / 16) + 3) & ~3;
+  k_quant_nvfp4<<<static_cast<unsigned>((M + 7) / 8), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x),
+      static_cast<uint8_t*>(q), static_cast<uint8_t*>(sf), M, K, sfc, ts);
   CHECK_LAUNCH();
   return 0;
 }

@@ -143,6 +143,41 @@ def grouped_gemm_mxfp8(aq: torch.Tensor, asf: torch.Tensor, bq: torch.Tensor, bs
   return out
 
 
+def quant_nvfp4(x: torch.Tensor):
+  """x [M,K] bf16 -> (packed E2M1 [M,K/2], UE4M3 scale atoms (one scale per 16 elements), fp32 tensor scale [1]).
+  x ~= e2m1 * block_scale * tensor_scale; K % 32 == 0."""
+  M, K = x.shape
+  ts = (x.detach().abs().amax().float() / (6.0 * 448.0)).clamp(min=1e-30).reshape(1)
+  if not x.is_cuda:
+    q, bs, _ = RQ.quant_nvfp4(x.float())
+    Mp = (M + 127) // 128 * 128
+    cols = ((K // 16) + 3) // 4 * 4
+    sfp = torch.zeros((Mp, cols), dtype=torch.uint8)
+    sfp[:M, :K // 16] = bs.view(torch.uint8)
+    return q, RQ.sf_to_mma_layout(sfp), ts
+  q = torch.empty(M, K // 2, dtype=torch.uint8, device=x.device)
+  sf = torch.zeros(sf_bytes(M, 2 * K), dtype=torch.uint8, device=x.device)
+  L.check(L.lib().nmoe_quant_nvfp4(L.ptr(x.contiguous()), L.ptr(q), L.ptr(sf), L.c_ll(M), K, L.ptr(ts), L.stream()),
+          "quant_nvfp4")
+  return q, sf, ts
+
+
+def gemm_nvfp4(aq: torch.Tensor, asf: torch.Tensor, ats: torch.Tensor, bq: torch.Tensor, bsf: torch.Tensor,
+               bts: torch.Tensor, *, out: Optional[torch.Tensor] = None, bn: int = 0) -> torch.Tensor:
+  """C[M,N] bf16 = dequant(A) @ dequant(B)^T for NVFP4 operands (E2M1, UE4M3 per 16, fp32 tensor scales) on
+  ``kind::mxf4nvf4.block_scale.scale_vec::4X``; the two tensor scales are applied in the epilogue.  K % 64 == 0."""
+  M, K = aq.size(0), aq.size(1) * 2
+  N = bq.size(0)
+  if out is None:
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=aq.device)
+  alpha = float(ats.item() * bts.item())
+  st = status_buffer(aq.device)
+  L.check(L.lib().nmoe_gemm_nvfp4(L.ptr(aq), L.ptr(asf), L.ptr(bq), L.ptr(bsf), L.ptr(out), M, N, K,
+                                  L.c_ll(out.stride(0)), 0, 1, None, None, L.c_ll(M), L.c_ll(N), bn, L.c_float(alpha),
+                                  L.ptr(st), L.stream()), "gemm_nvfp4")
+  return out
+
+
 def swiglu_quant_mxfp4(h13: torch.Tensor, n_tiles: Optional[torch.Tensor] = None):
   """h13 [M,2F] (gate even / up odd) -> silu(gate)*up as MXFP4: (q [M,F/2] nibbles, sf atoms)."""
   M, F2 = h13.shape
