@@ -147,9 +147,11 @@ def quant_nvfp4(x: torch.Tensor):
   """x [M,K] bf16 -> (packed E2M1 [M,K/2], UE4M3 scale atoms (one scale per 16 elements), fp32 tensor scale [1]).
   x ~= e2m1 * block_scale * tensor_scale; K % 32 == 0."""
   M, K = x.shape
-  ts = (x.detach().abs().amax().float() / (6.0 * 448.0)).clamp(min=1e-30).reshape(1)
+  # a multiplication (not a division) so that CPU and GPU produce the same bits: x / (scale * ts) lands on
+  # exact rounding ties surprisingly often for bf16 inputs, and a 1-ulp difference in ts flips them
+  ts = (x.detach().abs().amax().float() * (1.0 / (6.0 * 448.0))).clamp(min=1e-30).reshape(1)
   if not x.is_cuda:
-    q, bs, _ = RQ.quant_nvfp4(x.float())
+    q, bs, _ = RQ.quant_nvfp4(x.float(), ts)
     Mp = (M + 127) // 128 * 128
     cols = ((K // 16) + 3) // 4 * 4
     sfp = torch.zeros((Mp, cols), dtype=torch.uint8)

@@ -112,7 +112,7 @@ def dequant_mxfp4(packed: torch.Tensor, sf: torch.Tensor, block: int = 32) -> to
   return (v.view(M, -1, block) * e8m0_decode(sf).unsqueeze(-1)).view(M, Kh * 2)
 
 
-def quant_nvfp4(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+def quant_nvfp4(x: torch.Tensor, ts: torch.Tensor | None = None) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
   """True NVFP4: 16-element blocks, E4M3 block scales, one fp32 tensor scale.
 
   Returns (uint8 packed [M,K/2], float8_e4m3fn scales [M,K/16], fp32 tensor scale).
@@ -120,7 +120,9 @@ def quant_nvfp4(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, torch.Tens
   """
   M, K = x.shape
   xf = x.float()
-  ts = (xf.abs().amax() / (FP4_MAX * FP8_MAX)).clamp(min=1e-30)
+  if ts is None:
+    ts = (xf.abs().amax() / (FP4_MAX * FP8_MAX)).clamp(min=1e-30)
+  ts = ts.reshape(()).float()
   xb = xf.view(M, K // 16, 16)
   bs = (xb.abs().amax(-1) / FP4_MAX / ts).clamp(max=FP8_MAX).to(torch.float8_e4m3fn)
   denom = (bs.float() * ts).unsqueeze(-1)

@@ -188,15 +188,17 @@ class MoEMLP(nn.Module):
   def _quantised(self):
     if self._q is None:
       from ..ops import quant as Q
-      E, N1, H = self.w1.shape
-      w1q, w1sf = Q.quant_mxfp8(self.w1.detach().view(E * N1, H))
-      n2 = self.w2.size(1)
-      n2p = (n2 + 127) // 128 * 128                                     # scale atoms cover 128 rows: pad each expert
-      w2 = self.w2.detach()
-      if n2p != n2:
-        w2 = torch.cat((w2, w2.new_zeros(E, n2p - n2, w2.size(2))), dim=1)
-      w2q, w2sf = Q.quant_mxfp8(w2.reshape(E * n2p, -1))
-      self._q = (w1q.view(E, N1, H), w1sf, w2q.view(E, n2p, -1), w2sf, n2p)
+      def pack(w):
+        # scale atoms cover 128 output rows: pad every expert's row count to a multiple of 128 with zero rows
+        E, n, k = w.shape
+        n_pad = (n + 127) // 128 * 128
+        if n_pad != n:
+          w = torch.cat((w, w.new_zeros(E, n_pad - n, k)), dim=1)
+        q, sf = Q.quant_mxfp8(w.reshape(E * n_pad, k))
+        return q.view(E, n_pad, k), sf
+      w1q, w1sf = pack(self.w1.detach())
+      w2q, w2sf = pack(self.w2.detach())
+      self._q = (w1q, w1sf, w2q, w2sf)
     return self._q
 
   def forward(self, x: torch.Tensor) -> torch.Tensor:
@@ -216,7 +218,8 @@ class MoEMLP(nn.Module):
     from ..ops import quant as Q
     rd = self.rdep
     H = X.size(1)
-    w1q, w1sf, w2q, w2sf, n2p = self._quantised()
+    w1q, w1sf, w2q, w2sf = self._quantised()
+    N1 = self.w1.size(1)
     out = torch.empty_like(X)
     for t0 in range(0, X.size(0), rd.max_tokens):            # the dispatch scratch is sized for max_tokens rows
       xs, g, ei = xn[t0:t0 + rd.max_tokens].contiguous(), gates[t0:t0 + rd.max_tokens].contiguous(), eid[t0:t0 + rd.max_tokens]
@@ -226,7 +229,7 @@ class MoEMLP(nn.Module):
       h = Q.grouped_gemm_mxfp8(rd.xq, rd.sfa, w1q, w1sf, plan.tile_expert, plan.n_m_tiles)
       # rows past the valid tiles hold stale data; they are never read back (the pushes skip them)
       row_e = plan.tile_expert[:h.size(0) // 128].clamp(0, self.cfg.num_experts - 1).long().repeat_interleave(128)
-      a = clamped_swiglu(torch.nan_to_num(h + self.b1[row_e]), self.cfg.swiglu_limit)
+      a = clamped_swiglu(torch.nan_to_num(h[:, :N1] + self.b1[row_e]), self.cfg.swiglu_limit)
       aq, asf = Q.quant_mxfp8(a, plan.n_m_tiles)
       y = Q.grouped_gemm_mxfp8(aq, asf, w2q, w2sf, plan.tile_expert, plan.n_m_tiles)
       y = (y[:, :H] + self.b2[row_e]).contiguous()
