@@ -270,8 +270,24 @@ def cmd_rephrase(a) -> int:
 
 
 def cmd_needs_network(a) -> int:
-  print(f"'{a.command}' downloads from S3 / arXiv and needs network access and boto3", file=sys.stderr)
+  print(f"'{a.command}' downloads from S3 / arXiv and needs network access and boto3; "
+        f"'arxiv-prep' and 'stack-v2-materialize' work on files that are already on disk", file=sys.stderr)
   return 2
+
+
+def cmd_arxiv_prep(a) -> int:
+  from .arxiv import iter_arxiv, write_jsonl
+  n = write_jsonl(iter_arxiv(a.input, a.min_chars), a.output)
+  print(f"{n} papers -> {a.output}")
+  return 0
+
+
+def cmd_stack_v2(a) -> int:
+  from .arxiv import iter_stack_v2, write_jsonl
+  langs = set(a.languages.split(",")) if a.languages else None
+  n = write_jsonl(iter_stack_v2(a.table, a.blobs, langs, a.max_bytes), a.output)
+  print(f"{n} files -> {a.output}")
+  return 0
 
 
 def build_parser() -> argparse.ArgumentParser:
@@ -314,8 +330,12 @@ def build_parser() -> argparse.ArgumentParser:
   p.add_argument("--oracle-keep", type=float, default=0.6); p.add_argument("--keep-precision", type=float, default=0.9)
   p = sub.add_parser("rephrase"); p.set_defaults(fn=cmd_rephrase); model_args(p)
   p.add_argument("--num-versions", type=int, default=1); p.add_argument("--chunk-size", type=int, default=2048); p.add_argument("--no-filter", action="store_true")
-  for name in ("arxiv-download", "arxiv-prep"):
-    p = sub.add_parser(name); p.set_defaults(fn=cmd_needs_network); p.add_argument("rest", nargs="*")
+  p = sub.add_parser("arxiv-download"); p.set_defaults(fn=cmd_needs_network); p.add_argument("rest", nargs="*")
+  p = sub.add_parser("arxiv-prep"); p.set_defaults(fn=cmd_arxiv_prep)
+  p.add_argument("--input", required=True); p.add_argument("--output", required=True); p.add_argument("--min-chars", type=int, default=500)
+  p = sub.add_parser("stack-v2-materialize"); p.set_defaults(fn=cmd_stack_v2)
+  p.add_argument("--table", required=True); p.add_argument("--blobs", required=True); p.add_argument("--output", required=True)
+  p.add_argument("--languages"); p.add_argument("--max-bytes", type=int, default=1 << 20)
   return ap
 
 

@@ -89,3 +89,48 @@ def test_flow_env_overrides_and_guard(tmp_path):
   other = flow_mod.load_spec(spec_path, env={})
   with pytest.raises(RuntimeError, match="different flow"):
     flow_mod.run_flow(other, grader=lambda t: [1.0] * len(t), print_fn=lambda *a: None)
+
+
+def test_arxiv_prep_and_stack_v2_materialize(tmp_path):
+  import gzip, io, json, tarfile
+  from nmoe_b200.data.arxiv import latex_to_text
+  from nmoe_b200.data.cli import main
+  tex = r"""\documentclass{article}
+\usepackage{amsmath} % comment to drop
+\begin{document}
+\title{On \emph{Widgets}}
+\begin{abstract} We study widgets. \end{abstract}
+\section{Introduction}
+Widgets \cite{foo} satisfy $a^2 + b^2 = c^2$ and more~\ref{x}.
+\input{body}
+\begin{figure} \includegraphics{fig.png} \caption{gone} \end{figure}
+\begin{equation} E = mc^2 \label{e} \end{equation}
+\begin{thebibliography}{9} \bibitem{foo} Foo. \end{thebibliography}
+\end{document}"""
+  body = r"\subsection{Details} The \textbf{main} result holds for 100\% of cases."
+  src = tmp_path / "src"; src.mkdir()
+  buf = io.BytesIO()
+  with tarfile.open(fileobj=buf, mode="w:gz") as tf:
+    for name, data in (("main.tex", tex), ("body.tex", body)):
+      ti = tarfile.TarInfo(name); b = data.encode(); ti.size = len(b); tf.addfile(ti, io.BytesIO(b))
+  (src / "2401.00001.tar.gz").write_bytes(buf.getvalue())
+  out = tmp_path / "arxiv.jsonl"
+  assert main(["arxiv-prep", "--input", str(src), "--output", str(out), "--min-chars", "10"]) == 0
+  row = json.loads(out.read_text().splitlines()[0])
+  t = row["text"]
+  assert row["id"] == "2401.00001" and "Introduction" in t and "Details" in t and "main result holds for 100% of cases" in t
+  assert "$a^2 + b^2 = c^2$" in t and "$$E = mc^2$$" in t.replace(" $$", "$$").replace("$$ ", "$$")
+  assert "gone" not in t and "Foo." not in t and "\\" not in t.replace("$a^2", "").split("$$")[0] and "comment" not in t
+  assert latex_to_text(r"\begin{document}x \textit{\textbf{y}} z\end{document}") == "x y z"
+  blobs = tmp_path / "blobs"; (blobs / "ab").mkdir(parents=True)
+  (blobs / "ab" / "abcd1234.gz").write_bytes(gzip.compress("def f():\n  return 1\n".encode()))
+  (blobs / "ffee").write_bytes("fn main() {}".encode("utf-16"))
+  table = tmp_path / "ids.jsonl"
+  table.write_text("\n".join(json.dumps(r) for r in (
+    {"blob_id": "abcd1234", "src_encoding": "utf-8", "language": "Python", "path": "a.py"},
+    {"blob_id": "ffee", "src_encoding": "utf-16", "language": "Rust", "path": "m.rs"},
+    {"blob_id": "missing", "src_encoding": "utf-8", "language": "Python", "path": "x.py"})))
+  out2 = tmp_path / "code.jsonl"
+  assert main(["stack-v2-materialize", "--table", str(table), "--blobs", str(blobs), "--output", str(out2), "--languages", "Python,Rust"]) == 0
+  rows = [json.loads(l) for l in out2.read_text().splitlines()]
+  assert [r["id"] for r in rows] == ["abcd1234", "ffee"] and rows[0]["text"].startswith("def f()") and rows[1]["text"] == "fn main() {}"
