@@ -147,12 +147,22 @@ def main():
       sent = remote_pairs * (row_in + 2 * H + 4)          # dispatch out + (symmetric on average) return in
       comm_s = (d_us + r_us) * 1e-6
       flops = 2.0 * T * K * 3 * H * F
+      # roofline of the fused down-projection + return: the slower of its FLOPs at the measured sustained GEMM
+      # rate and its bytes over NVLink at the measured peer-copy rate (770 GB/s per direction)
+      peak = {"bf16": 1424e12, "fp8": 2848e12}.get(a.dtype, 5696e12)
+      try:
+        pk = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        peak = pk["bf16_tflops_sustained"] * 1e12 * {"bf16": 1, "fp8": 2}.get(a.dtype, 4)
+      except (OSError, KeyError):
+        pass
+      ret_floor_us = max(2.0 * rows_here * H * F / peak, remote_pairs * 2 * H / 770e9) * 1e6
       if rank == 0:
         print(json.dumps({
           "bench": "rdep", "n_gpus": world, "dtype": a.dtype, "routing": a.routing, "tokens_per_rank": T,
           "hidden": H, "inter": F, "experts": E, "topk": K, "padded_rows_rank0": rows_here,
           "dispatch_us": round(d_us, 1), "gemm13_us": round(g_us, 1), "gemm2_ret_us": round(r_us, 1),
           "total_us": round(d_us + g_us + r_us, 1),
+          "gemm2_ret_roofline_us": round(ret_floor_us, 1), "gemm2_ret_frac_of_roofline": round(ret_floor_us / max(r_us, 1e-9), 3),
           "tflops_per_gpu": round(flops / ((d_us + g_us + r_us) * 1e-6) / 1e12, 1),
           "remote_pairs_rank0": remote_pairs,
           "nvlink_gbs_rank0": round(sent / comm_s / 1e9, 1) if world > 1 else 0.0,
