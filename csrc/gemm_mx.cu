@@ -28,6 +28,7 @@
 
 #include "common/epilogue.cuh"
 #include "common/ptx.cuh"
+#include "common/quant_dev.cuh"
 #include "common/tensormap.h"
 
 namespace nmoe {
@@ -51,6 +52,12 @@ struct MxParams {
   __nv_bfloat16* peer_ret[8];
   int push_use_gate;
   float alpha;                 // multiplies every output (NVFP4: product of the two per-tensor scales)
+  // fused SwiGLU + quantise epilogue (act_q != nullptr): instead of C [rows, N], write the quantised
+  // activation [rows, N/2] (E4M3 bytes, or E2M1 nibbles when act_fp4) and its E8M0 scale atoms
+  uint8_t* act_q;
+  uint8_t* act_sf;
+  int act_sf_cols;
+  int act_fp4;
 };
 
 NMOE_DEVICE uint64_t mx_timer_ns() {
@@ -309,6 +316,43 @@ k_gemm_mx(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
           tmem_ld_wait();
           warp_store_rows_64cols(stage, r, gate, row_ok ? dst_row + col : nullptr, lane);
         }
+      } else if (p.act_q != nullptr) {
+        // fused SwiGLU + quantise (up/gate projection, columns interleaved gate even / up odd): 64 accumulator
+        // columns of a row give 32 activations = one scale block, owned by one thread, so no shuffles are
+        // needed; h13 itself is never written
+        const int F = p.N >> 1;
+#pragma unroll 1
+        for (int c = 0; c < BN / 64; ++c) {
+          const int col = n0 + c * 64;
+          if (col >= p.N) break;
+          uint32_t r[64];
+          const uint32_t ta = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + c * 64;
+          tmem_ld_32x32b_x32(ta, r);
+          tmem_ld_32x32b_x32(ta + 32, r + 32);
+          tmem_ld_wait();
+          if (!row_ok) continue;
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            // round through bf16 twice like the unfused path (h13 stored as bf16, activation stored as bf16)
+            const float g = __bfloat162float(__float2bfloat16(__uint_as_float(r[2 * i]) * p.alpha));
+            const float u = __bfloat162float(__float2bfloat16(__uint_as_float(r[2 * i + 1]) * p.alpha));
+            v[i] = __bfloat162float(__float2bfloat16(g / (1.f + __expf(-g)) * u));
+          }
+          const int b = col >> 6;                              // 32-element block index along F
+          uint32_t w[8];
+          uint8_t s;
+          if (p.act_fp4) {
+            s = quant_block_e2m1_regs(v, w);
+            *reinterpret_cast<int4*>(p.act_q + static_cast<long long>(row) * (F >> 1) + b * 16) = make_int4(w[0], w[1], w[2], w[3]);
+          } else {
+            s = quant_block_e4m3_regs(v, w);
+            int4* dq = reinterpret_cast<int4*>(p.act_q + static_cast<long long>(row) * F + b * 32);
+            dq[0] = make_int4(w[0], w[1], w[2], w[3]);
+            dq[1] = make_int4(w[4], w[5], w[6], w[7]);
+          }
+          p.act_sf[sf_mma_offset(row, b, p.act_sf_cols)] = s;
+        }
       } else
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
@@ -407,7 +451,7 @@ extern "C" int nmoe_gemm_mxfp8(const void* A, const void* sfa, const void* B, co
   p.C = static_cast<__nv_bfloat16*>(C); p.ldc = ldc;
   p.sfa = static_cast<const uint8_t*>(sfa); p.sfb = static_cast<const uint8_t*>(sfb);
   p.status = static_cast<StatusRecord*>(status);
-  p.row_meta = static_cast<const int4*>(row_meta); p.push_use_gate = push_use_gate; p.alpha = 1.f;
+  p.row_meta = static_cast<const int4*>(row_meta); p.push_use_gate = push_use_gate; p.alpha = 1.f; p.act_q = nullptr; p.act_sf = nullptr; p.act_sf_cols = 0; p.act_fp4 = 0;
   for (int r = 0; r < 8; ++r)
     p.peer_ret[r] = (row_meta && peer_ret && r < world) ? static_cast<__nv_bfloat16*>(peer_ret[r]) : nullptr;
   if (row_meta && mode != 1) return -6;
@@ -437,7 +481,7 @@ extern "C" int nmoe_gemm_mxfp4(const void* A, const void* sfa, const void* B, co
   p.C = static_cast<__nv_bfloat16*>(C); p.ldc = ldc;
   p.sfa = static_cast<const uint8_t*>(sfa); p.sfb = static_cast<const uint8_t*>(sfb);
   p.status = static_cast<StatusRecord*>(status);
-  p.row_meta = static_cast<const int4*>(row_meta); p.push_use_gate = push_use_gate; p.alpha = 1.f;
+  p.row_meta = static_cast<const int4*>(row_meta); p.push_use_gate = push_use_gate; p.alpha = 1.f; p.act_q = nullptr; p.act_sf = nullptr; p.act_sf_cols = 0; p.act_fp4 = 0;
   for (int r = 0; r < 8; ++r)
     p.peer_ret[r] = (row_meta && peer_ret && r < world) ? static_cast<__nv_bfloat16*>(peer_ret[r]) : nullptr;
   if (row_meta && mode != 1) return -6;
@@ -467,7 +511,7 @@ extern "C" int nmoe_gemm_nvfp4(const void* A, const void* sfa, const void* B, co
   p.C = static_cast<__nv_bfloat16*>(C); p.ldc = ldc;
   p.sfa = static_cast<const uint8_t*>(sfa); p.sfb = static_cast<const uint8_t*>(sfb);
   p.status = static_cast<StatusRecord*>(status);
-  p.row_meta = nullptr; p.push_use_gate = 0; p.alpha = alpha;
+  p.row_meta = nullptr; p.push_use_gate = 0; p.alpha = alpha; p.act_q = nullptr; p.act_sf = nullptr; p.act_sf_cols = 0; p.act_fp4 = 0;
   for (int r = 0; r < 8; ++r) p.peer_ret[r] = nullptr;
   CUtensorMap tmA, tmB;
   int rc = mx_cached_map(&tmA, A, K / 2, a_rows, K / 2, MX_BK, MX_BM);
@@ -478,4 +522,36 @@ extern "C" int nmoe_gemm_nvfp4(const void* A, const void* sfa, const void* B, co
   if (bn == 256)
     return mode == 1 ? mx_launch<256, 1, 2>(tmA, tmB, p, max_tiles, st) : mx_launch<256, 0, 2>(tmA, tmB, p, max_tiles, st);
   return mode == 1 ? mx_launch<128, 1, 2>(tmA, tmB, p, max_tiles, st) : mx_launch<128, 0, 2>(tmA, tmB, p, max_tiles, st);
+}
+
+// Grouped up/gate projection with the SwiGLU and the re-quantisation fused into the epilogue: rows of A are
+// 128-aligned expert segments, B = W13 [E, 2F, K] with gate / up rows interleaved; writes act_q [a_rows, F]
+// (E4M3) or [a_rows, F/2] (E2M1 when fp4 != 0) and act_sf (atom layout for [a_rows, F]).  Operands are MXFP8
+// (fp4 == 0) or MXFP4 (fp4 != 0).  N = 2F must be a multiple of 128.
+extern "C" int nmoe_gemm_mx_swiglu_quant(const void* A, const void* sfa, const void* B, const void* sfb, void* act_q,
+                                         void* act_sf, int M, int N, int K, int E, const int* tile_expert,
+                                         const int* n_m_tiles, long long a_rows, long long b_rows, int fp4, int bn,
+                                         void* status, cudaStream_t st) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || (K % (fp4 ? 128 : 32)) != 0 || (N % 128) != 0) return -1;
+  if (bn == 0) bn = (N % 256 == 0) ? 256 : 128;
+  if (bn != 128 && bn != 256) return -5;
+  MxParams p;
+  p.M = M; p.N = N; p.K = K; p.E = E; p.tile_expert = tile_expert; p.n_m_tiles = n_m_tiles;
+  p.C = nullptr; p.ldc = N;
+  p.sfa = static_cast<const uint8_t*>(sfa); p.sfb = static_cast<const uint8_t*>(sfb);
+  p.status = static_cast<StatusRecord*>(status);
+  p.row_meta = nullptr; p.push_use_gate = 0; p.alpha = 1.f;
+  for (int r = 0; r < 8; ++r) p.peer_ret[r] = nullptr;
+  p.act_q = static_cast<uint8_t*>(act_q); p.act_sf = static_cast<uint8_t*>(act_sf);
+  p.act_sf_cols = (((N / 2) / 32) + 3) & ~3; p.act_fp4 = fp4;
+  const int kb = fp4 ? K / 2 : K;
+  CUtensorMap tmA, tmB;
+  int rc = mx_cached_map(&tmA, A, kb, a_rows, kb, MX_BK, MX_BM);
+  if (rc != 0) return rc;
+  rc = mx_cached_map(&tmB, B, kb, b_rows, kb, MX_BK, bn);
+  if (rc != 0) return rc;
+  const int max_tiles = ((M + MX_BM - 1) / MX_BM) * ((N + bn - 1) / bn);
+  if (fp4) return bn == 256 ? mx_launch<256, 1, 1>(tmA, tmB, p, max_tiles, st) : mx_launch<128, 1, 1>(tmA, tmB, p, max_tiles, st);
+  return bn == 256 ? mx_launch<256, 1, 0>(tmA, tmB, p, max_tiles, st) : mx_launch<128, 1, 0>(tmA, tmB, p, max_tiles, st);
 }

@@ -191,6 +191,26 @@ def swiglu_quant_mxfp4(h13: torch.Tensor, n_tiles: Optional[torch.Tensor] = None
   return q, sf
 
 
+def grouped_gemm_swiglu_quant(aq: torch.Tensor, asf: torch.Tensor, bq: torch.Tensor, bsf: torch.Tensor,
+                              tile_expert: torch.Tensor, n_m_tiles: torch.Tensor, *, fp4: bool = False, bn: int = 0):
+  """Grouped up/gate projection whose epilogue applies SwiGLU and re-quantises: returns the quantised
+  activation (E4M3 [Mcap,F] or E2M1 [Mcap,F/2]) and its scale atoms; the bf16 H13 is never written.
+  ``bq`` = W13 [E, 2F, K(/2)] with gate / up rows interleaved."""
+  Mcap = aq.size(0)
+  K = aq.size(1) * (2 if fp4 else 1)
+  E, N = bq.size(0), bq.size(1)
+  F = N // 2
+  q = torch.empty(Mcap, F // 2 if fp4 else F, dtype=torch.uint8, device=aq.device)
+  sf = torch.empty(sf_bytes(Mcap, F), dtype=torch.uint8, device=aq.device)
+  if (F // 32) % 4:
+    sf.fill_(127)            # partial last atom: padding scale bytes must be valid
+  st = status_buffer(aq.device)
+  L.check(L.lib().nmoe_gemm_mx_swiglu_quant(L.ptr(aq), L.ptr(asf), L.ptr(bq), L.ptr(bsf), L.ptr(q), L.ptr(sf), Mcap, N, K, E,
+                                            L.ptr(tile_expert), L.ptr(n_m_tiles), L.c_ll(Mcap), L.c_ll(E * N), int(fp4), bn,
+                                            L.ptr(st), L.stream()), "grouped_gemm_swiglu_quant")
+  return q, sf
+
+
 def is_fp4(profile: str) -> bool:
   """The reference's "nvfp4" profile is E2M1 values with one E8M0 scale per 32 elements
   (nmoe/quant.py:45-72), i.e. the OCP MXFP4 format; both names select it here."""

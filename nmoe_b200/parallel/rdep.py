@@ -116,6 +116,7 @@ class Rdep:
     self.epoch_ret = 0
     self.wait_budget = 0          # 0 = library default (seconds); tests shrink it
     self.fused_return = True      # False: separate push kernel after the GEMM (kept for A/B tests)
+    self.fused_swiglu_quant = True  # block-scaled profiles: SwiGLU + quantise in the up/gate GEMM's epilogue
 
   # ---------------------------------------------------------------- building blocks
   def plan(self, eid: torch.Tensor) -> Plan:
@@ -244,8 +245,13 @@ class _MoEFused(torch.autograd.Function):
       rdep.place_mx(x, plan, gates32.view(-1))
       rdep.wait_data()
       ggemm = Q.grouped_gemm_mxfp4 if rdep.fp4 else Q.grouped_gemm_mxfp8
-      h13 = ggemm(rdep.xq, rdep.sfa, W13q, W13sf, plan.tile_expert, plan.n_m_tiles)
-      aq, asf = (Q.swiglu_quant_mxfp4 if rdep.fp4 else Q.swiglu_quant_mxfp8)(h13, plan.n_m_tiles)
+      if save_h13 or not rdep.fused_swiglu_quant:
+        h13 = ggemm(rdep.xq, rdep.sfa, W13q, W13sf, plan.tile_expert, plan.n_m_tiles)
+        aq, asf = (Q.swiglu_quant_mxfp4 if rdep.fp4 else Q.swiglu_quant_mxfp8)(h13, plan.n_m_tiles)
+      else:
+        # SwiGLU and the re-quantisation happen in the epilogue of the up/gate projection: H13 is never written
+        h13 = None
+        aq, asf = Q.grouped_gemm_swiglu_quant(rdep.xq, rdep.sfa, W13q, W13sf, plan.tile_expert, plan.n_m_tiles, fp4=rdep.fp4)
       ggemm(aq, asf, W2q, W2sf, plan.tile_expert, plan.n_m_tiles, push=rdep.push_args(True))
       rdep.finish_return(plan, out)
       ctx.rdep, ctx.plan = rdep, plan

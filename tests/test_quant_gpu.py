@@ -171,3 +171,62 @@ def test_gemm_nvfp4_vs_dequantised_matmul(M, N, K, bn):
   ref = deq(aq, asf, ats, M) @ deq(bq, bsf, bts, N).t()
   assert _rel(c.cpu(), ref) < 1e-2
   assert _rel(c.cpu(), a.float().cpu() @ b.float().cpu().t()) < 0.3
+
+
+@pytest.mark.parametrize("profile", ["fp8", "nvfp4"])
+def test_blockscaled_moe_worst_case_routing(profile):
+  """Every (token, slot) pair goes to expert 0 and the other experts are empty (the reference's worst-case
+  test, tests/test_blockscaled_expert_worst_case.py:19-191): block-scaled path vs the fp32 MoE loop."""
+  from nmoe_b200.parallel.rdep import Rdep, moe_reference
+  from nmoe_b200.ops.quant import ExpertWeightCache
+  from nmoe_b200.ops import tc_gemm as G
+  torch.manual_seed(7)
+  dev = torch.device("cuda")
+  T, H, F, E, K = 384, 256, 256, 8, 1
+  rd = Rdep(H, E, K, T, device=dev, profile=profile)
+  try:
+    x = (torch.randn(T, H, device=dev) * 0.5).bfloat16()
+    W13 = (torch.randn(E, 2 * F, H, device=dev) * 0.05).bfloat16()
+    W2 = (torch.randn(E, H, F, device=dev) * 0.05).bfloat16()
+    eid = torch.zeros(T, K, dtype=torch.int32, device=dev)
+    gates = torch.ones(T, K, device=dev)
+    out = rd.moe(x, gates, eid, W13, W2, False, ExpertWeightCache(profile).get(W13, W2))
+    torch.cuda.synchronize()
+    G.check_status()
+    ref = moe_reference(x.float().cpu(), gates.cpu(), eid.cpu().long(), W13.float().cpu(), W2.float().cpu())
+    err = (out.float().cpu() - ref).abs().max().item() / ref.abs().max().item()
+    assert torch.isfinite(out).all() and err < (8e-2 if profile == "fp8" else 0.5), err
+  finally:
+    rd.close()
+
+
+@pytest.mark.parametrize("fp4", [False, True])
+def test_fused_swiglu_quant_epilogue_matches_unfused(fp4):
+  """Up/gate grouped GEMM with SwiGLU + quantise in its epilogue == GEMM -> bf16 H13 -> swiglu+quant kernel."""
+  from nmoe_b200 import ops
+  from nmoe_b200.ops import quant as Q
+  from nmoe_b200.ops import tc_gemm as G
+  torch.manual_seed(8)
+  dev = torch.device("cuda")
+  E, H, F, rows = 3, 256, 192, 512
+  x = (torch.randn(rows, H, device=dev) * 0.5).bfloat16()
+  W13 = (torch.randn(E, 2 * F, H, device=dev) * 0.1).bfloat16()
+  quant = Q.quant_mxfp4 if fp4 else Q.quant_mxfp8
+  xq, xsf = quant(x)
+  wq, wsf = quant(W13.view(E * 2 * F, H))
+  wq = wq.view(E, 2 * F, -1)
+  tile_expert = torch.tensor([0, 0, 2, 1], dtype=torch.int32, device=dev)
+  n_tiles = torch.tensor([4], dtype=torch.int32, device=dev)
+  gg = Q.grouped_gemm_mxfp4 if fp4 else Q.grouped_gemm_mxfp8
+  h13 = gg(xq, xsf, wq, wsf, tile_expert, n_tiles)
+  aq_u, asf_u = (Q.swiglu_quant_mxfp4 if fp4 else Q.swiglu_quant_mxfp8)(h13, n_tiles)
+  aq_f, asf_f = Q.grouped_gemm_swiglu_quant(xq, xsf, wq, wsf, tile_expert, n_tiles, fp4=fp4)
+  torch.cuda.synchronize()
+  G.check_status()
+  assert torch.equal(aq_f, aq_u)
+  n = Q.sf_bytes(rows, F)
+  from nmoe_b200.ref import quant as RQ
+  cols = ((F // 32) + 3) // 4 * 4
+  su = RQ.sf_from_mma_layout(asf_u.cpu(), rows, cols)[:, :F // 32]
+  sf_ = RQ.sf_from_mma_layout(asf_f.cpu(), rows, cols)[:, :F // 32]
+  assert torch.equal(su, sf_)
