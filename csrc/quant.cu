@@ -116,6 +116,63 @@ k_quant_mxfp4(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q, uint
   }
 }
 
+// Expert AdamW fused with the refresh of the block-scaled weight cache: one pass over [rows, K] updates
+// p / m / v (bf16 storage, fp32 math, decoupled decay first, as k_adamw_flat) and writes the quantised
+// copy of the NEW weights (E4M3 or E2M1 + E8M0 atoms) that the next forward's expert GEMMs read.
+// One warp per row, a lane owns one 32-element block at a time.
+// Reference counterpart: expert_adamw_step emitting the fp8 / nvfp4 caches (nmoe/csrc/adamw.cu:73-489).
+template <bool FP4>
+__global__ void __launch_bounds__(256)
+k_adamw_quant(__nv_bfloat16* __restrict__ p, const __nv_bfloat16* __restrict__ g, __nv_bfloat16* __restrict__ m,
+              __nv_bfloat16* __restrict__ v, long long rows, int K, float lr, float beta1, float beta2, float eps,
+              float wd, float inv_bc1, float inv_bc2_sqrt, float grad_scale, uint8_t* __restrict__ q,
+              uint8_t* __restrict__ sf, int sf_cols_padded) {
+  const long long row = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  for (int b = lane; b < (K >> 5); b += 32) {
+    const long long off = row * K + b * 32;
+    float pf[32], gf[32], mf[32], vf[32];
+    load_block_bf16(p + off, pf);
+    load_block_bf16(g + off, gf);
+    load_block_bf16(m + off, mf);
+    load_block_bf16(v + off, vf);
+    uint32_t pw[16], mw[16], vw[16];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const float gi = gf[i] * grad_scale;
+      float x = pf[i] * (1.f - lr * wd);
+      mf[i] = beta1 * mf[i] + (1.f - beta1) * gi;
+      vf[i] = beta2 * vf[i] + (1.f - beta2) * gi * gi;
+      x -= lr * inv_bc1 * mf[i] / (sqrtf(vf[i]) * inv_bc2_sqrt + eps);
+      pf[i] = __bfloat162float(__float2bfloat16(x));            // the cache is quantised from the stored bf16 value
+    }
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      pw[i] = pack_bf16x2(pf[2 * i], pf[2 * i + 1]);
+      mw[i] = pack_bf16x2(mf[2 * i], mf[2 * i + 1]);
+      vw[i] = pack_bf16x2(vf[2 * i], vf[2 * i + 1]);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      reinterpret_cast<int4*>(p + off)[i] = make_int4(pw[4 * i], pw[4 * i + 1], pw[4 * i + 2], pw[4 * i + 3]);
+      reinterpret_cast<int4*>(m + off)[i] = make_int4(mw[4 * i], mw[4 * i + 1], mw[4 * i + 2], mw[4 * i + 3]);
+      reinterpret_cast<int4*>(v + off)[i] = make_int4(vw[4 * i], vw[4 * i + 1], vw[4 * i + 2], vw[4 * i + 3]);
+    }
+    uint32_t w[8];
+    uint8_t s;
+    if (FP4) {
+      s = quant_block_e2m1_regs(pf, w);
+      *reinterpret_cast<int4*>(q + row * (K >> 1) + b * 16) = make_int4(w[0], w[1], w[2], w[3]);
+    } else {
+      s = quant_block_e4m3_regs(pf, w);
+      reinterpret_cast<int4*>(q + row * K + b * 32)[0] = make_int4(w[0], w[1], w[2], w[3]);
+      reinterpret_cast<int4*>(q + row * K + b * 32)[1] = make_int4(w[4], w[5], w[6], w[7]);
+    }
+    sf[sf_mma_offset(static_cast<int>(row), b, sf_cols_padded)] = s;
+  }
+}
+
 // NVFP4: E2M1 values, one E4M3 scale per 16 elements (relative to the fp32 per-tensor scale *ts),
 // scales in the atom layout with sf_cols = K/16 padded to a multiple of 4.  x ~= e2m1 * e4m3 * ts.
 __global__ void __launch_bounds__(256)
@@ -213,6 +270,31 @@ int nmoe_quant_mxfp4(const void* x, void* q, void* sf, long long M, int K, cudaS
   const int sfc = ((K / 32) + 3) & ~3;
   k_quant_mxfp4<<<static_cast<unsigned>((M + 7) / 8), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x),
       static_cast<uint8_t*>(q), static_cast<uint8_t*>(sf), M, K, sfc);
+  CHECK_LAUNCH();
+  return 0;
+}
+
+// p, g, m, v: [rows, K] bf16; q: [rows, K] (E4M3) or [rows, K/2] (E2M1, fp4 != 0); sf: nmoe_sf_bytes(rows, K).
+// rows must be a multiple of 128 per expert (they are: expert matrices are stacked), K % 32 == 0.
+int nmoe_expert_adamw_quant(void* p, const void* g, void* m, void* v, long long rows, int K, float lr, float beta1,
+                            float beta2, float eps, float wd, int step, float grad_scale, void* q, void* sf, int fp4,
+                            cudaStream_t st) {
+  if (rows == 0) return 0;
+  if (K % 32 != 0) return -1;
+  const float inv_bc1 = 1.f / (1.f - powf(beta1, static_cast<float>(step)));
+  const float inv_bc2_sqrt = 1.f / sqrtf(1.f - powf(beta2, static_cast<float>(step)));
+  const int sfc = ((K / 32) + 3) & ~3;
+  const unsigned blocks = static_cast<unsigned>((rows + 7) / 8);
+  auto pp = static_cast<__nv_bfloat16*>(p);
+  auto gg = static_cast<const __nv_bfloat16*>(g);
+  auto mm = static_cast<__nv_bfloat16*>(m);
+  auto vv = static_cast<__nv_bfloat16*>(v);
+  if (fp4)
+    k_adamw_quant<true><<<blocks, 256, 0, st>>>(pp, gg, mm, vv, rows, K, lr, beta1, beta2, eps, wd, inv_bc1, inv_bc2_sqrt,
+                                                grad_scale, static_cast<uint8_t*>(q), static_cast<uint8_t*>(sf), sfc);
+  else
+    k_adamw_quant<false><<<blocks, 256, 0, st>>>(pp, gg, mm, vv, rows, K, lr, beta1, beta2, eps, wd, inv_bc1, inv_bc2_sqrt,
+                                                 grad_scale, static_cast<uint8_t*>(q), static_cast<uint8_t*>(sf), sfc);
   CHECK_LAUNCH();
   return 0;
 }

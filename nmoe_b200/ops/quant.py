@@ -218,25 +218,55 @@ def is_fp4(profile: str) -> bool:
 
 
 class ExpertWeightCache:
-  """MXFP8 (or MXFP4) copies of the expert weights, re-quantised whenever the bf16 masters change
-  (detected through the tensors' version counters; the reference rebuilds its cache after every
-  optimizer step, nmoe/opt.py:118-125)."""
+  """Block-scaled (MXFP8 or MXFP4) copies of one layer's expert weights.
+
+  The copies are rebuilt whenever the bf16 masters change (version counters), and the expert AdamW
+  refreshes them for free: the cache registers itself on the two parameters, and
+  ``expert_adamw_quant_`` writes the quantised NEW weights in the same pass that updates them
+  (the reference's fused kernel does the same, nmoe/csrc/adamw.cu:73-489 and nmoe/opt.py:118-125)."""
 
   def __init__(self, profile: str = "fp8"):
     self.fp4 = is_fp4(profile)
-    self.ver = (-1, -1)
-    self.W13q = self.W13sf = self.W2q = self.W2sf = None
+    self.ver = [-1, -1]
+    self.q = [None, None]        # 2-D views [E*rows, K(/2)]
+    self.sf = [None, None]
+    self.shape = [None, None]
+
+  def _quantise(self, idx: int, W: torch.Tensor) -> None:
+    E, n, k = W.shape
+    q, sf = (quant_mxfp4 if self.fp4 else quant_mxfp8)(W.detach().view(E * n, k))
+    if self.q[idx] is None or self.q[idx].shape != q.shape:
+      self.q[idx], self.sf[idx] = q, sf
+    else:
+      self.q[idx].copy_(q); self.sf[idx].copy_(sf)
+    self.shape[idx] = (E, n, q.size(1))
+    self.ver[idx] = W._version
+    W._nmoe_qcache = (self, idx)
+
+  def target(self, idx: int):
+    """(values [rows, K(/2)], scale atoms, fp4) that a fused optimizer step should overwrite."""
+    return self.q[idx], self.sf[idx], self.fp4
+
+  def mark_fresh(self, idx: int, version: int) -> None:
+    self.ver[idx] = version
 
   @torch.no_grad()
   def get(self, W13: torch.Tensor, W2: torch.Tensor):
-    ver = (W13._version, W2._version)
-    if ver != self.ver or self.W13q is None:
-      quant = quant_mxfp4 if self.fp4 else quant_mxfp8
-      E, N13, H = W13.shape
-      q, self.W13sf = quant(W13.detach().view(E * N13, H))
-      self.W13q = q.view(E, N13, -1)
-      _, H2, F = W2.shape
-      q2, self.W2sf = quant(W2.detach().view(E * H2, F))
-      self.W2q = q2.view(E, H2, -1)
-      self.ver = ver
-    return self.W13q, self.W13sf, self.W2q, self.W2sf
+    for idx, W in ((0, W13), (1, W2)):
+      if self.q[idx] is None or self.ver[idx] != W._version:
+        self._quantise(idx, W)
+    return self.q[0].view(self.shape[0]), self.sf[0], self.q[1].view(self.shape[1]), self.sf[1]
+
+
+def expert_adamw_quant_(p: torch.Tensor, g: torch.Tensor, m: torch.Tensor, v: torch.Tensor, q: torch.Tensor, sf: torch.Tensor,
+                        fp4: bool, *, lr: float, beta1: float, beta2: float, eps: float, weight_decay: float, step: int,
+                        grad_scale: float = 1.0) -> None:
+  """AdamW on a stack of expert matrices p [E, n, K] (bf16 p / g / m / v) that also writes the block-scaled
+  copy of the updated weights into (q, sf)."""
+  K = p.size(-1)
+  rows = p.numel() // K
+  assert p.is_contiguous() and g.is_contiguous() and m.is_contiguous() and v.is_contiguous() and g.dtype == p.dtype
+  L.check(L.lib().nmoe_expert_adamw_quant(L.ptr(p), L.ptr(g), L.ptr(m), L.ptr(v), L.c_ll(rows), K, L.c_float(lr),
+                                          L.c_float(beta1), L.c_float(beta2), L.c_float(eps), L.c_float(weight_decay),
+                                          int(step), L.c_float(grad_scale), L.ptr(q), L.ptr(sf), int(fp4), L.stream()),
+          "expert_adamw_quant")

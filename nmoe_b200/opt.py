@@ -67,9 +67,21 @@ class ExpertAdamW:
     st = self.state[i]
     if self.gradnorm_sq is not None:
       ops.sumsq(g.reshape(-1), self.gradnorm_sq)
+    qc = getattr(p, "_nmoe_qcache", None)
+    if qc is not None and p.is_cuda and g.dtype == p.dtype and g.is_contiguous():
+      # block-scaled profile: the same pass writes the quantised copy of the new weights for the next forward
+      from .ops.quant import expert_adamw_quant_
+      cache, idx = qc
+      q, sf, fp4 = cache.target(idx)
+      expert_adamw_quant_(p.data, g, st["exp_avg"], st["exp_avg_sq"], q, sf, fp4, lr=self.lr, beta1=self.betas[0],
+                          beta2=self.betas[1], eps=self.eps, weight_decay=self.wd, step=self.step_count + 1)
+      torch.autograd.graph.increment_version(p)
+      cache.mark_fresh(idx, p._version)
+      return
     ops.adamw_flat_(p.data.view(-1), g.reshape(-1).to(p.dtype), st["exp_avg"].view(-1), st["exp_avg_sq"].view(-1),
                     lr=self.lr, beta1=self.betas[0], beta2=self.betas[1], eps=self.eps, weight_decay=self.wd,
                     step=self.step_count + 1)
+    torch.autograd.graph.increment_version(p)      # the kernel wrote through a raw pointer: let caches notice
 
   def _make_hook(self, i: int):
     def hook(p: torch.Tensor) -> None:

@@ -230,3 +230,38 @@ def test_fused_swiglu_quant_epilogue_matches_unfused(fp4):
   su = RQ.sf_from_mma_layout(asf_u.cpu(), rows, cols)[:, :F // 32]
   sf_ = RQ.sf_from_mma_layout(asf_f.cpu(), rows, cols)[:, :F // 32]
   assert torch.equal(su, sf_)
+
+
+@pytest.mark.parametrize("profile", ["fp8", "nvfp4"])
+def test_expert_adamw_refreshes_block_scaled_cache(profile):
+  """The fused AdamW + quantise pass == flat AdamW followed by a fresh quantisation, and the optimizer
+  drives it through the cache that the MoE layer registered on its parameters."""
+  from nmoe_b200 import ops
+  from nmoe_b200.config import Config
+  from nmoe_b200.opt import ExpertAdamW
+  from nmoe_b200.ops.quant import ExpertWeightCache
+  torch.manual_seed(9)
+  dev = torch.device("cuda")
+  E, F, H = 4, 128, 256
+  W13 = torch.nn.Parameter((torch.randn(E, 2 * F, H, device=dev) * 0.05).bfloat16())
+  W2 = torch.nn.Parameter((torch.randn(E, H, F, device=dev) * 0.05).bfloat16())
+  ref13, ref2 = W13.detach().clone(), W2.detach().clone()
+  cache = ExpertWeightCache(profile)
+  cache.get(W13, W2)
+  cfg = Config()
+  opt = ExpertAdamW([W13, W2], cfg)
+  opt.begin_step(1e-2)
+  g13, g2 = torch.randn_like(W13), torch.randn_like(W2)
+  W13.grad, W2.grad = g13.clone(), g2.clone()
+  opt.step()
+  torch.cuda.synchronize()
+  # oracle: plain flat AdamW on copies, then quantise
+  for w, g in ((ref13, g13), (ref2, g2)):
+    ops.adamw_flat_(w.view(-1), g.reshape(-1), torch.zeros_like(w).view(-1), torch.zeros_like(w).view(-1), lr=1e-2,
+                    beta1=cfg.adam_beta1, beta2=cfg.adam_beta2_expert, eps=cfg.adam_eps, weight_decay=cfg.weight_decay, step=1)
+  assert torch.equal(W13.detach(), ref13) and torch.equal(W2.detach(), ref2)
+  fresh = ExpertWeightCache(profile)
+  q13, s13, q2, s2 = fresh.get(W13, W2)
+  c13, cs13, c2, cs2 = cache.get(W13, W2)
+  assert cache.ver == [W13._version, W2._version]
+  assert torch.equal(c13, q13) and torch.equal(c2, q2) and torch.equal(cs13, s13) and torch.equal(cs2, s2)
