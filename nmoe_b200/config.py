@@ -106,6 +106,7 @@ class Config:
   seed: int = 42
   log_every: int = 10
   activation_checkpoint: str = "attention"   # attention | none | full
+  moe_save_h13: bool = False        # keep the experts' up/gate output for backward instead of recomputing it (memory for time)
 
   # ---- checkpointing
   checkpoint_dir: str = "/data/checkpoints"

@@ -54,7 +54,7 @@ class MoE(nn.Module):
     self.W2 = nn.Parameter(torch.empty(n_local, self.dim, self.inter, dtype=dtype))
     self.shared = MLP(self.dim, cfg.n_shared_experts * self.inter, dtype) if cfg.n_shared_experts else None
     self.register_buffer("loads", torch.zeros(cfg.n_routed_experts, dtype=torch.int32), persistent=False)
-    self.save_h13 = False
+    self.save_h13 = bool(getattr(cfg, "moe_save_h13", False))
     self.expert_dtype = cfg.dtype
     self._wcache = None
 
