@@ -112,8 +112,7 @@ def main():
           marks[1].record()
         if quantised:
           gg = Q.grouped_gemm_mxfp4 if rd.fp4 else Q.grouped_gemm_mxfp8
-          h13 = gg(rd.xq, rd.sfa, wq[0], wq[1], plan.tile_expert, plan.n_m_tiles)
-          aq, asf = (Q.swiglu_quant_mxfp4 if rd.fp4 else Q.swiglu_quant_mxfp8)(h13, plan.n_m_tiles)
+          aq, asf = Q.grouped_gemm_swiglu_quant(rd.xq, rd.sfa, wq[0], wq[1], plan.tile_expert, plan.n_m_tiles, fp4=rd.fp4)
         else:
           h13 = G.grouped_gemm(rd.xbuf, W13, plan.tile_expert, plan.n_m_tiles, align256=rd.align == 256)
           act = EW.swiglu_rows(h13, plan.n_m_tiles)
@@ -122,7 +121,7 @@ def main():
         if quantised:
           gg(aq, asf, wq[2], wq[3], plan.tile_expert, plan.n_m_tiles, push=rd.push_args(True))
         else:
-          G.grouped_gemm(act, W2, plan.tile_expert, plan.n_m_tiles, push=rd.push_args(True))
+          G.grouped_gemm(act, W2, plan.tile_expert, plan.n_m_tiles, push=rd.push_args(True), align256=rd.align == 256)
         rd.finish_return(plan, out)
         if marks:
           marks[3].record()

@@ -18,6 +18,7 @@
 #include <mutex>
 #include <tuple>
 
+#include "common/epilogue.cuh"
 #include "common/ptx.cuh"
 #include "common/tensormap.h"
 
@@ -42,6 +43,12 @@ struct Gemm2Params {
   int out_fp32, accumulate;
   long long b_rows_per_expert;
   StatusRecord* status;
+  // fused RDEP return (mode 1, bf16): see GemmParams in gemm.cu
+  const int4* row_meta;
+  __nv_bfloat16* peer_ret[8];
+  float* peer_retg[8];
+  const float* rowval;
+  int push_use_gate;
 };
 
 NMOE_DEVICE uint32_t cluster_ctarank() {
@@ -139,7 +146,9 @@ NMOE_DEVICE bool decode_tile2(const Gemm2Params& p, int t, int m_tiles, int n_ti
 
 constexpr int kG2StageA = G2_BM * G2_BK * 2;
 constexpr int kG2StageB = (G2_BN / 2) * G2_BK * 2;
-constexpr int kG2SmemBytes = kG2Stages * (kG2StageA + kG2StageB) + 1024 + 256;
+constexpr int kG2EpiStage = 4 * kEpiStageBytesPerWarp;            // transposing store of the fused-return epilogue
+constexpr int kG2SmemBytes = kG2Stages * (kG2StageA + kG2StageB) + kG2EpiStage + 1024 + 256;
+static_assert(kG2SmemBytes <= 232448, "shared memory budget");
 
 template <bool A_MN, bool B_MN, int MODE>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kG2Threads, 1)
@@ -148,7 +157,8 @@ k_gemm_bf16_pair(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
   uint8_t* sB = smem + kG2Stages * kG2StageA;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kG2Stages * (kG2StageA + kG2StageB));
+  uint8_t* epi_stage = smem + kG2Stages * (kG2StageA + kG2StageB);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(epi_stage + kG2EpiStage);
   uint64_t* full = bars;
   uint64_t* empty = bars + kG2Stages;
   uint64_t* tmem_full = bars + 2 * kG2Stages;
@@ -281,9 +291,20 @@ k_gemm_bf16_pair(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     for (int t = cluster_id; decode_tile2<MODE>(p, t, m_tiles, n_tiles, tc); t += n_clusters) {
       const int row = tc.m_blk * 2 * G2_BM + static_cast<int>(rank) * G2_BM + q * 32 + lane;
       const int n0 = tc.n_blk * G2_BN;
-      const bool row_ok = row < m_limit;
+      bool row_ok = row < m_limit;
       const long long crow = (MODE == 2) ? static_cast<long long>(tc.expert) * p.M + row : row;
       const bool have_acc = tc.kb_count > 0;
+      __nv_bfloat16* push_dst = nullptr;
+      float push_gate = 1.f;
+      if (MODE == 1 && p.row_meta != nullptr && row_ok) {
+        const int4 mv = __ldg(p.row_meta + row);
+        row_ok = mv.w != 0;
+        if (row_ok) {
+          push_dst = p.peer_ret[mv.x] + static_cast<long long>(mv.y) * p.ldc;
+          if (p.push_use_gate) push_gate = __int_as_float(mv.z);
+          if (tc.n_blk == 0 && p.rowval != nullptr) p.peer_retg[mv.x][mv.y] = p.rowval[row];
+        }
+      }
       if (have_acc) {
         bool ok = g2_wait(&tmem_full[acc], acc_phase, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
@@ -294,6 +315,21 @@ k_gemm_bf16_pair(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
         tc_fence_after_sync();
       }
+      if (MODE == 1 && p.row_meta != nullptr && have_acc) {
+        // fused return, coalesced: 64 columns (128 bytes) of 4 rows per store instruction
+        uint8_t* stage = epi_stage + (warp - 2) * kEpiStageBytesPerWarp;
+#pragma unroll 1
+        for (int c = 0; c < G2_BN / 64; ++c) {
+          const int col = n0 + c * 64;
+          if (col >= p.N) break;
+          uint32_t r[64];
+          const uint32_t ta = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * G2_BN + c * 64;
+          tmem_ld_32x32b_x32(ta, r);
+          tmem_ld_32x32b_x32(ta + 32, r + 32);
+          tmem_ld_wait();
+          warp_store_rows_64cols(stage, r, push_gate, (row_ok && push_dst != nullptr) ? push_dst + col : nullptr, lane);
+        }
+      } else
 #pragma unroll 1
       for (int c = 0; c < G2_BN / 32; ++c) {
         uint32_t r[32];
@@ -363,6 +399,7 @@ k_gemm_bf16_pair(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   if (*abort_flag) {
     for (int i = 0; i < 2000; ++i) __nanosleep(1000);
   }
+  if (MODE == 1 && p.row_meta != nullptr) __threadfence_system();
   tc_fence_before_sync();
   cluster_sync_all();                 // neither CTA may free tensor memory or exit while its partner still uses the pair
   if (warp == 1) {
@@ -411,12 +448,16 @@ static int g2_launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const Gemm2
 
 using namespace nmoe;
 
-// Same contract as nmoe_gemm_bf16 (without the fused-return arguments); N tile is fixed at 256.
-extern "C" int nmoe_gemm_bf16_pair(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
-                                   long long ldb, long long ldc, int a_mn, int b_mn, int mode, int E,
-                                   const int* tile_expert, const int* n_m_tiles, const int* offs, long long a_rows,
-                                   long long b_rows, int out_fp32, int accumulate, void* status, cudaStream_t st) {
+// Same contract as nmoe_gemm_bf16 including the fused RDEP return (row_meta / peer_ret / peer_retg / rowval);
+// N tile is fixed at 256 and grouped row segments must be 256-aligned.
+extern "C" int nmoe_gemm_bf16_pair_push(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+                                        long long ldb, long long ldc, int a_mn, int b_mn, int mode, int E,
+                                        const int* tile_expert, const int* n_m_tiles, const int* offs, long long a_rows,
+                                        long long b_rows, int out_fp32, int accumulate, void* status, const void* row_meta,
+                                        void* const* peer_ret, void* const* peer_retg, const float* rowval,
+                                        int push_use_gate, int world, cudaStream_t st) {
   if (M <= 0 || N <= 0) return 0;
+  if (row_meta && (mode != 1 || out_fp32 || world > 8 || (N & 63) != 0 || (ldc & 7) != 0)) return -6;
   if (mode != 2 && K <= 0) return -1;
   if ((lda % 8) || (ldb % 8)) return -2;
   if (mode == 2 && !(a_mn && b_mn)) return -3;
@@ -426,6 +467,11 @@ extern "C" int nmoe_gemm_bf16_pair(const void* A, const void* B, void* C, int M,
   p.C = C; p.ldc = ldc; p.out_fp32 = out_fp32; p.accumulate = accumulate;
   p.b_rows_per_expert = (mode == 1) ? (b_mn ? K : N) : 0;
   p.status = static_cast<StatusRecord*>(status);
+  p.row_meta = static_cast<const int4*>(row_meta); p.rowval = rowval; p.push_use_gate = push_use_gate;
+  for (int r = 0; r < 8; ++r) {
+    p.peer_ret[r] = (row_meta && peer_ret && r < world) ? static_cast<__nv_bfloat16*>(peer_ret[r]) : nullptr;
+    p.peer_retg[r] = (row_meta && peer_retg && r < world) ? static_cast<float*>(peer_retg[r]) : nullptr;
+  }
   CUtensorMap tmA, tmB;
   int rc;
   if (a_mn) rc = g2_map(&tmA, A, static_cast<uint64_t>(M), static_cast<uint64_t>(a_rows), lda * 2, 64, G2_BK);
@@ -446,4 +492,13 @@ extern "C" int nmoe_gemm_bf16_pair(const void* A, const void* B, void* C, int M,
   if (mode == 1) return G2_GO(1);
   return g2_launch<true, true, 2>(tmA, tmB, p, max_tiles, st);
 #undef G2_GO
+}
+
+// Without the fused-return arguments.
+extern "C" int nmoe_gemm_bf16_pair(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+                                   long long ldb, long long ldc, int a_mn, int b_mn, int mode, int E,
+                                   const int* tile_expert, const int* n_m_tiles, const int* offs, long long a_rows,
+                                   long long b_rows, int out_fp32, int accumulate, void* status, cudaStream_t st) {
+  return nmoe_gemm_bf16_pair_push(A, B, C, M, N, K, lda, ldb, ldc, a_mn, b_mn, mode, E, tile_expert, n_m_tiles, offs, a_rows,
+                                  b_rows, out_fp32, accumulate, status, nullptr, nullptr, nullptr, nullptr, 0, 0, st);
 }

@@ -263,7 +263,7 @@ class _MoEFused(torch.autograd.Function):
     a = EW.swiglu_rows(h13, plan.n_m_tiles)
     if rdep.fused_return:
       # down projection whose epilogue multiplies by the gate and stores into the source's (token, slot) rows
-      G.grouped_gemm(a, W2, plan.tile_expert, plan.n_m_tiles, push=rdep.push_args(True))
+      G.grouped_gemm(a, W2, plan.tile_expert, plan.n_m_tiles, push=rdep.push_args(True), align256=rdep.align == 256)
       rdep.finish_return(plan, out)
     else:
       y = G.grouped_gemm(a, W2, plan.tile_expert, plan.n_m_tiles)
@@ -293,7 +293,7 @@ class _MoEFused(torch.autograd.Function):
     dW13 = G.grouped_wgrad(dh13, rdep.xbuf, plan.offs_pad, rdep.n_local)         # [E, 2Dff, H]
     dx = torch.empty_like(x)
     if rdep.fused_return:
-      G.grouped_gemm(dh13, W13, plan.tile_expert, nt, b_mn=True, push=rdep.push_args(False, rowdot))
+      G.grouped_gemm(dh13, W13, plan.tile_expert, nt, b_mn=True, push=rdep.push_args(False, rowdot), align256=rdep.align == 256)
       rdep.finish_return(plan, dx)
     else:
       dxe = G.grouped_gemm(dh13, W13, plan.tile_expert, nt, b_mn=True)
