@@ -199,31 +199,48 @@ __global__ void __launch_bounds__(256) k_rdep_place(const PlaceArgs a) {
   const int row_blocks = gridDim.x - a.pad_blocks;
   const int nvec = a.H >> 3;
   if (static_cast<int>(blockIdx.x) < row_blocks) {
-    const int n_pairs = a.T * a.K;
-    for (int i = blockIdx.x * 8 + warp; i < n_pairs; i += row_blocks * 8) {
-      const int e = a.eid[i];
-      const int rb = a.rank_in_block[i];
+    // one warp per token: lane k (< K) resolves the destination of slot k, then the row is read ONCE in
+    // chunks of 256 16-byte vectors and every chunk is stored to the K owners
+    for (int tok = blockIdx.x * 8 + warp; tok < a.T; tok += row_blocks * 8) {
       int pos = -1, owner = 0;
-      if (e >= 0 && e < a.E && rb >= 0 && a.base[e] >= 0) {
-        owner = e / a.n_local;
-        pos = a.base[e] + a.block_prefix[(i / kCountThreads) * a.E + e] + rb;
-      }
-      if (lane == 0) {
+      if (lane < a.K) {
+        const int i = tok * a.K + lane;
+        const int e = a.eid[i];
+        const int rb = a.rank_in_block[i];
+        if (e >= 0 && e < a.E && rb >= 0 && a.base[e] >= 0) {
+          owner = e / a.n_local;
+          pos = a.base[e] + a.block_prefix[(i / kCountThreads) * a.E + e] + rb;
+        }
         a.pos_out[i] = pos;
         if (a.owner_out) a.owner_out[i] = owner;
+        if (pos >= 0 && a.peer_meta[owner] != nullptr) {
+          int4 m;
+          m.x = a.rank;
+          m.y = i;
+          m.z = __float_as_int(a.gates ? a.gates[i] : 1.f);
+          m.w = 1;
+          st_relaxed_sys_v4(a.peer_meta[owner] + pos, m);
+        }
       }
-      if (pos < 0) continue;
-      const int tok = i / a.K;
       const int4* src = reinterpret_cast<const int4*>(a.x + static_cast<size_t>(tok) * a.H);
-      int4* dst = reinterpret_cast<int4*>(a.peer_x[owner] + static_cast<size_t>(pos) * a.H);
-      for (int c = lane; c < nvec; c += 32) st_relaxed_sys_v4(dst + c, __ldg(src + c));
-      if (lane == 0 && a.peer_meta[owner] != nullptr) {
-        int4 m;
-        m.x = a.rank;
-        m.y = i;
-        m.z = __float_as_int(a.gates ? a.gates[i] : 1.f);
-        m.w = 1;
-        st_relaxed_sys_v4(a.peer_meta[owner] + pos, m);
+      for (int c0 = 0; c0 < nvec; c0 += 256) {
+        int4 v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int c = c0 + j * 32 + lane;
+          v[j] = c < nvec ? __ldg(src + c) : make_int4(0, 0, 0, 0);
+        }
+        for (int k = 0; k < a.K; ++k) {
+          const int pk = __shfl_sync(0xffffffffu, pos, k);
+          const int ok = __shfl_sync(0xffffffffu, owner, k);
+          if (pk < 0) continue;
+          int4* dst = reinterpret_cast<int4*>(a.peer_x[ok] + static_cast<size_t>(pk) * a.H);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int c = c0 + j * 32 + lane;
+            if (c < nvec) st_relaxed_sys_v4(dst + c, v[j]);
+          }
+        }
       }
     }
   } else {
@@ -507,8 +524,8 @@ int nmoe_rdep_place(int rank, int world, int E, int n_local, int T, int K, int H
   }
   a.pos_out = pos_out; a.owner_out = owner_out; a.offs_pad = offs_pad; a.seg_rows = seg_rows;
   a.done_counter = done_counter; a.pad_blocks = 16; a.status = static_cast<StatusRecord*>(status);
-  const int n_pairs = T * K;
-  int row_blocks = (n_pairs + 7) / 8;
+  if (K > 32) return -1;
+  int row_blocks = (T + 7) / 8;              // one warp per token
   if (row_blocks > 148 * 8) row_blocks = 148 * 8;
   if (row_blocks < 1) row_blocks = 1;
   k_rdep_place<<<row_blocks + a.pad_blocks, 256, 0, st>>>(a);

@@ -36,6 +36,7 @@ def check_status(device: Optional[torch.device] = None) -> None:
 
 
 PAIR_MODE = os.environ.get("NMOE_GEMM_PAIR", "1") == "1"
+PAIR_PUSH = os.environ.get("NMOE_PAIR_PUSH", "1") == "1"      # fused-return grouped GEMMs on CTA pairs too
 
 
 def use_pair(M: int, N: int) -> bool:
@@ -109,7 +110,8 @@ def grouped_gemm(a: torch.Tensor, b: torch.Tensor, tile_expert: torch.Tensor, n_
   assert a.is_contiguous() and b.is_contiguous() and a.size(0) % 128 == 0
   st = status_buffer(a.device)
   b2_rows = E * (K if b_mn else N)
-  if push is not None and align256 and bn == 0 and PAIR_MODE and N >= 256 and N % 64 == 0 and a.size(0) % 256 == 0:
+  if (push is not None and align256 and bn == 0 and PAIR_MODE and PAIR_PUSH and N >= 256 and N % 64 == 0
+      and a.size(0) % 256 == 0):
     # fused RDEP return on CTA pairs (256-row aligned segments)
     L.check(L.lib().nmoe_gemm_bf16_pair_push(
       L.ptr(a), L.ptr(b), None, a.size(0), N, K, L.c_ll(K), L.c_ll(N if b_mn else K), L.c_ll(N),

@@ -58,6 +58,7 @@ class Plan:
   pos: torch.Tensor            # [T*K] position in the owner's buffer (-1 = dropped)
   T: int
   K: int
+  rows: int = 0                # host-known bound on the (padded) rows that landed on this rank; 0 = not read back
 
 
 class Rdep:
@@ -117,8 +118,22 @@ class Rdep:
     self.wait_budget = 0          # 0 = library default (seconds); tests shrink it
     self.fused_return = True      # False: separate push kernel after the GEMM (kept for A/B tests)
     self.fused_swiglu_quant = True  # block-scaled profiles: SwiGLU + quantise in the up/gate GEMM's epilogue
+    # world > 1: the receive buffers hold the worst case (world x the balanced share), but every per-layer
+    # tensor derived from them (H13, activations, their gradients) only needs the rows that arrived.  Reading
+    # that one number back costs a small host sync per MoE forward and cuts those tensors by ~world x.
+    self.trim_rows = self.world > 1
 
   # ---------------------------------------------------------------- building blocks
+  def rows_of(self, plan: Plan) -> int:
+    """Rows of the expert-side buffers that the layer's tensors must cover (multiple of 256)."""
+    if plan.rows == 0:
+      if self.trim_rows:
+        n = int(plan.n_m_tiles.item()) * 128
+        plan.rows = min(self.capacity, max(256, (n + 255) // 256 * 256))
+      else:
+        plan.rows = self.capacity
+    return plan.rows
+
   def plan(self, eid: torch.Tensor) -> Plan:
     T, K = eid.shape
     assert T <= self.max_tokens and K == self.K
@@ -238,6 +253,7 @@ class _MoEFused(torch.autograd.Function):
     x = x.contiguous()
     gates32 = gates.detach().float().contiguous()
     plan = rdep.plan(eid)
+    rows = rdep.rows_of(plan)
     out = torch.empty_like(x)
     if wq is not None:
       from ..ops import quant as Q
@@ -246,12 +262,12 @@ class _MoEFused(torch.autograd.Function):
       rdep.wait_data()
       ggemm = Q.grouped_gemm_mxfp4 if rdep.fp4 else Q.grouped_gemm_mxfp8
       if save_h13 or not rdep.fused_swiglu_quant:
-        h13 = ggemm(rdep.xq, rdep.sfa, W13q, W13sf, plan.tile_expert, plan.n_m_tiles)
+        h13 = ggemm(rdep.xq[:rows], rdep.sfa, W13q, W13sf, plan.tile_expert, plan.n_m_tiles)
         aq, asf = (Q.swiglu_quant_mxfp4 if rdep.fp4 else Q.swiglu_quant_mxfp8)(h13, plan.n_m_tiles)
       else:
         # SwiGLU and the re-quantisation happen in the epilogue of the up/gate projection: H13 is never written
         h13 = None
-        aq, asf = Q.grouped_gemm_swiglu_quant(rdep.xq, rdep.sfa, W13q, W13sf, plan.tile_expert, plan.n_m_tiles, fp4=rdep.fp4)
+        aq, asf = Q.grouped_gemm_swiglu_quant(rdep.xq[:rows], rdep.sfa, W13q, W13sf, plan.tile_expert, plan.n_m_tiles, fp4=rdep.fp4)
       ggemm(aq, asf, W2q, W2sf, plan.tile_expert, plan.n_m_tiles, push=rdep.push_args(True))
       rdep.finish_return(plan, out)
       ctx.rdep, ctx.plan = rdep, plan
@@ -259,7 +275,7 @@ class _MoEFused(torch.autograd.Function):
       return out
     rdep.place(x, plan, gates32.view(-1), "x", with_meta=True)
     rdep.wait_data()
-    h13 = G.grouped_gemm(rdep.xbuf, W13, plan.tile_expert, plan.n_m_tiles, align256=rdep.align == 256)
+    h13 = G.grouped_gemm(rdep.xbuf[:rows], W13, plan.tile_expert, plan.n_m_tiles, align256=rdep.align == 256)
     a = EW.swiglu_rows(h13, plan.n_m_tiles)
     if rdep.fused_return:
       # down projection whose epilogue multiplies by the gate and stores into the source's (token, slot) rows
@@ -282,15 +298,17 @@ class _MoEFused(torch.autograd.Function):
     rdep.place(dout, plan, None, "y", with_meta=False)
     rdep.wait_data()
     nt = plan.n_m_tiles
+    rows = rdep.rows_of(plan)
+    xb, yb = rdep.xbuf[:rows], rdep.ybuf[:rows]
     if h13 is None:
-      h13 = G.grouped_gemm(rdep.xbuf, W13, plan.tile_expert, nt, align256=rdep.align == 256)
+      h13 = G.grouped_gemm(xb, W13, plan.tile_expert, nt, align256=rdep.align == 256)
     # dA' = dYe @ W2 (un-gated); gate enters through the row scale of the SwiGLU backward
-    da = G.grouped_gemm(rdep.ybuf, W2, plan.tile_expert, nt, b_mn=True, align256=rdep.align == 256)
+    da = G.grouped_gemm(yb, W2, plan.tile_expert, nt, b_mn=True, align256=rdep.align == 256)
     row_gate = rdep.row_gates(plan)
     dh13, rowdot, a_scaled = EW.swiglu_bwd_fused(h13, da, row_gate, True, True, nt)
     # every reader of the peer-written buffers runs before the kernel that returns rows to the sources
-    dW2 = G.grouped_wgrad(rdep.ybuf, a_scaled, plan.offs_pad, rdep.n_local)      # [E, H, Dff]
-    dW13 = G.grouped_wgrad(dh13, rdep.xbuf, plan.offs_pad, rdep.n_local)         # [E, 2Dff, H]
+    dW2 = G.grouped_wgrad(yb, a_scaled, plan.offs_pad, rdep.n_local)             # [E, H, Dff]
+    dW13 = G.grouped_wgrad(dh13, xb, plan.offs_pad, rdep.n_local)                # [E, 2Dff, H]
     dx = torch.empty_like(x)
     if rdep.fused_return:
       G.grouped_gemm(dh13, W13, plan.tile_expert, nt, b_mn=True, push=rdep.push_args(False, rowdot), align256=rdep.align == 256)
