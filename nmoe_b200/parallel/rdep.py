@@ -122,6 +122,9 @@ class Rdep:
     # tensor derived from them (H13, activations, their gradients) only needs the rows that arrived.  Reading
     # that one number back costs a small host sync per MoE forward and cuts those tensors by ~world x.
     self.trim_rows = self.world > 1
+    # world > 1 (bf16): keep a copy of the dispatched rows for the weight gradient instead of sending x over
+    # NVLink a second time in backward (one of five transfers per layer; costs rows x H x 2 bytes per layer)
+    self.save_dispatched = self.world > 1
 
   # ---------------------------------------------------------------- building blocks
   def rows_of(self, plan: Plan) -> int:
@@ -271,7 +274,7 @@ class _MoEFused(torch.autograd.Function):
       ggemm(aq, asf, W2q, W2sf, plan.tile_expert, plan.n_m_tiles, push=rdep.push_args(True))
       rdep.finish_return(plan, out)
       ctx.rdep, ctx.plan = rdep, plan
-      ctx.save_for_backward(x, gates32, W13, W2, h13 if save_h13 else None)
+      ctx.save_for_backward(x, gates32, W13, W2, h13 if save_h13 else None, None)
       return out
     rdep.place(x, plan, gates32.view(-1), "x", with_meta=True)
     rdep.wait_data()
@@ -285,21 +288,26 @@ class _MoEFused(torch.autograd.Function):
       y = G.grouped_gemm(a, W2, plan.tile_expert, plan.n_m_tiles)
       rdep.push_and_reduce(y, plan, True, None, out)
     ctx.rdep, ctx.plan = rdep, plan
-    ctx.save_for_backward(x, gates32, W13, W2, h13 if save_h13 else None)
+    xd = rdep.xbuf[:rows].clone() if rdep.save_dispatched else None
+    ctx.save_for_backward(x, gates32, W13, W2, h13 if save_h13 else None, xd)
     return out
 
   @staticmethod
   def backward(ctx, dout):
     rdep: Rdep = ctx.rdep
     plan: Plan = ctx.plan
-    x, gates32, W13, W2, h13 = ctx.saved_tensors
+    x, gates32, W13, W2, h13, xd = ctx.saved_tensors
     dout = dout.contiguous()
-    rdep.place(x, plan, gates32.view(-1), "x", with_meta=True)
-    rdep.place(dout, plan, None, "y", with_meta=False)
+    if xd is None:
+      rdep.place(x, plan, gates32.view(-1), "x", with_meta=True)
+      rdep.place(dout, plan, None, "y", with_meta=False)
+    else:
+      # the dispatched x rows were kept: only dOut travels, and it carries the row metadata (source, slot, gate)
+      rdep.place(dout, plan, gates32.view(-1), "y", with_meta=True)
     rdep.wait_data()
     nt = plan.n_m_tiles
     rows = rdep.rows_of(plan)
-    xb, yb = rdep.xbuf[:rows], rdep.ybuf[:rows]
+    xb, yb = (rdep.xbuf[:rows] if xd is None else xd), rdep.ybuf[:rows]
     if h13 is None:
       h13 = G.grouped_gemm(xb, W13, plan.tile_expert, nt, align256=rdep.align == 256)
     # dA' = dYe @ W2 (un-gated); gate enters through the row scale of the SwiGLU backward
