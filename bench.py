@@ -29,7 +29,7 @@ PLANNING_HINT_TOK_S_PER_GPU = 30_000.0   # configs/flow_profiles.toml duration h
 
 
 def moonlight_cfg(n_gpus: int, micro_batch: int, seq_len: int, dtype: str, layers: int | None = None,
-                  activation_checkpoint: str = "none", save_h13: bool = True):
+                  activation_checkpoint: str = "none", save_h13: bool = True, overlap_shared: str = "auto"):
   from nmoe_b200.config import Config
   return Config(
     preset="moonlight", vocab_size=163840, eos_token_id=163839, dim=2048, inter_dim=11264, moe_inter_dim=1408,
@@ -37,7 +37,7 @@ def moonlight_cfg(n_gpus: int, micro_batch: int, seq_len: int, dtype: str, layer
     n_activated_experts=6, route_scale=2.446, q_lora_rank=1536, kv_lora_rank=512, qk_nope_head_dim=128,
     qk_rope_head_dim=64, v_head_dim=128, attn="mla", attn_global_every=1, dtype=dtype, lr_dense=3e-4, lr_router=3e-4,
     lr_expert=3e-4, batch_size=micro_batch * n_gpus, seq_len=seq_len, warmup_steps=500, seed=42,
-    activation_checkpoint=activation_checkpoint, moe_save_h13=save_h13)
+    activation_checkpoint=activation_checkpoint, moe_save_h13=save_h13, moe_overlap_shared=overlap_shared)
 
 
 class ClockSampler:
@@ -143,6 +143,7 @@ def main() -> None:
   ap.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (result is marked invalid)")
   ap.add_argument("--dtype", default="bf16")
   ap.add_argument("--no-e2e", action="store_true")
+  ap.add_argument("--overlap-shared", default="auto", choices=["auto", "0", "1"], help="shared-expert MLP on a second stream")
   ap.add_argument("--recompute-h13", action="store_true", help="recompute the experts' up/gate output in backward (saves ~16 GB on one GPU)")
   ap.add_argument("--activation-checkpoint", default="none", choices=["none", "attention", "full"],
                   help="activation recompute policy; 'none' keeps the ~4 GB of attention activations instead of recomputing them")
@@ -163,7 +164,7 @@ def main() -> None:
       raise SystemExit("--gpus N>1 must be launched with torch.distributed.run (one rank per GPU)")
   rank, world, device = runtime.init(42)
   cfg = moonlight_cfg(world, args.micro_batch, args.seq_len, args.dtype, args.layers, args.activation_checkpoint,
-                      not args.recompute_h13)
+                      not args.recompute_h13, args.overlap_shared)
   trainer = Trainer(cfg, rank=rank, world=world, device=device)
   mb, S = args.micro_batch, args.seq_len
   gen = torch.Generator().manual_seed(1234 + rank)

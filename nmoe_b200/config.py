@@ -106,6 +106,7 @@ class Config:
   seed: int = 42
   log_every: int = 10
   activation_checkpoint: str = "attention"   # attention | none | full
+  moe_overlap_shared: str = "auto"  # shared-expert MLP on a second stream: auto (when world > 1) | 1 | 0
   moe_save_h13: bool = False        # keep the experts' up/gate output for backward instead of recomputing it (memory for time)
 
   # ---- checkpointing

@@ -39,6 +39,17 @@ class Router(nn.Module):
     ops.router_bias_update_(self.bias, loads, gamma)
 
 
+_SIDE_STREAMS = {}
+
+
+def _side_stream(device: torch.device) -> "torch.cuda.Stream":
+  s = _SIDE_STREAMS.get(device)
+  if s is None:
+    s = torch.cuda.Stream(device=device)
+    _SIDE_STREAMS[device] = s
+  return s
+
+
 class MoE(nn.Module):
   """Routed experts (this rank holds ``n_local`` of them) + shared expert MLP."""
 
@@ -57,6 +68,10 @@ class MoE(nn.Module):
     self.save_h13 = bool(getattr(cfg, "moe_save_h13", False))
     self.expert_dtype = cfg.dtype
     self._wcache = None
+    # run the shared-expert MLP on a second stream next to the routed experts: it fills the bubbles in
+    # which this rank waits for its peers' rows (only worth it when there are peers)
+    ov = getattr(cfg, "moe_overlap_shared", "auto")
+    self.overlap_shared = (rdep is not None and rdep.world > 1) if ov == "auto" else str(ov).lower() in ("1", "true", "yes")
 
   def init_weights(self, init_std: float = 0.02) -> None:
     for W in (self.W13, self.W2):
@@ -75,6 +90,17 @@ class MoE(nn.Module):
           from ..ops.quant import ExpertWeightCache
           self._wcache = ExpertWeightCache(self.expert_dtype)
         wq = self._wcache.get(self.W13, self.W2)
+      if self.shared is not None and self.overlap_shared:
+        cur = torch.cuda.current_stream()
+        side = _side_stream(X.device)
+        side.wait_stream(cur)
+        with torch.cuda.stream(side):
+          sh = self.shared(X)
+        X.record_stream(side)
+        out = self.rdep.moe(X, gates, eid, self.W13, self.W2, self.save_h13, wq)
+        cur.wait_stream(side)
+        sh.record_stream(cur)
+        return (out + sh).view_as(x)
       out = self.rdep.moe(X, gates, eid, self.W13, self.W2, self.save_h13, wq)
     else:
       out = rdep_mod.moe_reference(X, gates, eid, self.W13, self.W2)
