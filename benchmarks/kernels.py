@@ -119,8 +119,22 @@ def main():
       if a.backward:
         o.backward(g)
     ms = timed(step, a.iters, a.warmup, flush)
+    # latency distribution (one event pair per call, L2 flushed in between), as the reference's MoE benchmark reports
+    lat = sorted(timed(step, 1, 0, flush) for _ in range(max(a.iters, 20)))
     fl = 2.0 * T * K * 3 * H * F * (3 if a.backward else 1) + (2.0 * T * K * 2 * F * H if a.backward else 0)
-    out.update(tokens=T, hidden=H, inter=F, experts=E, topk=K, dtype=a.dtype, backward=a.backward, ms=ms, tflops=fl / ms / 1e9)
+    out.update(tokens=T, hidden=H, inter=F, experts=E, topk=K, dtype=a.dtype, backward=a.backward, ms=ms, tflops=fl / ms / 1e9,
+               p50_ms=lat[len(lat) // 2], p99_ms=lat[min(len(lat) - 1, int(len(lat) * 0.99))])
+    if a.dtype != "bf16":
+      # accuracy of the block-scaled forward against the bf16 forward on the same inputs
+      with torch.no_grad():
+        y = rd.moe(x, gates, eid, W13, W2, False, wq).float()
+      rd.close()
+      rb = Rdep(H, E, K, T, device=dev, profile="bf16")
+      with torch.no_grad():
+        yb = rb.moe(x, gates, eid, W13, W2, False, None).float()
+      rd = rb
+      out.update(cos_vs_bf16=torch.nn.functional.cosine_similarity(y.flatten(), yb.flatten(), dim=0).item(),
+                 max_abs_err=(y - yb).abs().max().item(), rel_err=((y - yb).norm() / yb.norm()).item())
     rd.close()
   G.check_status()
   print(json.dumps(out))

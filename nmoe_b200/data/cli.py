@@ -121,8 +121,36 @@ def cmd_merge_manifests(a) -> int:
 
 
 def cmd_flow(a) -> int:
+  """Run a data flow; its grading / rephrasing stages load the grading model named in the spec
+  (``grade.checkpoint`` + ``grade.heads``, ``rephrase.checkpoint``)."""
   from .flow import load_spec, run_flow
-  run_flow(load_spec(Path(a.spec)))
+  spec = load_spec(Path(a.spec))
+  grader = rephraser = None
+  model = None
+  tok = None
+  if spec.grade.get("enabled") or spec.rephrase.get("enabled"):
+    import argparse as _ap
+    ck = spec.grade.get("checkpoint") or spec.rephrase.get("checkpoint")
+    if not ck:
+      print("the flow enables grading / rephrasing but names no checkpoint", file=sys.stderr)
+      return 2
+    model, dev = _grading_model(_ap.Namespace(checkpoint=ck))
+    tok = _tokenizer(spec.prep.get("tokenizer", "o200k_harmony"))
+  if spec.grade.get("enabled"):
+    from . import hydra as H
+    probe, judge = H.load_heads(spec.grade["heads"], model.cfg.hidden_size, dev)
+    calib = H.Calibration.load(spec.grade.get("calibration", spec.grade["heads"]))
+    grader = H.make_flow_grader(model, probe, judge, calib, tok, max_ctx=int(spec.grade.get("max_ctx", 4096)),
+                                batch_size=int(spec.grade.get("batch_size", 32)))
+  if spec.rephrase.get("enabled"):
+    from ..serve import Engine
+    from .rephrase import rephrase_batch
+    eng = Engine(model, max_seq_len=int(spec.rephrase.get("max_ctx", 4096)), max_batch=int(spec.rephrase.get("batch_size", 32)))
+    def rephraser(texts):
+      out = rephrase_batch(eng, tok, texts, num_versions=1, stop_tokens=[getattr(tok, "eot", -1)])
+      by_doc = {r.doc: r.text for r in out}
+      return [by_doc.get(i, t) for i, t in enumerate(texts)]
+  run_flow(spec, grader=grader, rephraser=rephraser)
   return 0
 
 

@@ -238,6 +238,17 @@ def grade(model, probe: Optional[ProbeHead], judge: JudgeHead, docs: Sequence[Se
   return out  # type: ignore[return-value]
 
 
+def make_flow_grader(model, probe: Optional[ProbeHead], judge: JudgeHead, calib: Calibration, tokenizer, *,
+                     max_ctx: int = 4096, batch_size: int = 32) -> Callable[[List[str]], List[float]]:
+  """texts -> aggregated scores, the callable a data flow's grading stage filters on
+  (``nmoe_b200.data.flow.run_flow(spec, grader=...)``)."""
+  def score(texts: List[str]) -> List[float]:
+    docs = [tokenizer.encode(t)[:max_ctx] or [0] for t in texts]
+    rows = grade(model, probe, judge, docs, [str(i) for i in range(len(docs))], calib, batch_size=batch_size, max_ctx=max_ctx)
+    return [float(r["aggregated"]) for r in rows]
+  return score
+
+
 # ---------------------------------------------------------------------------------------------- training
 @dataclass
 class PhaseConfig:

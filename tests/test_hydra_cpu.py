@@ -133,3 +133,51 @@ def test_cli_train_grade_roundtrip(tmp_path):
   blocks = torch.tensor([[[0x21, 0xF7] + [0] * 14]], dtype=torch.uint8)      # codes 1,2,7,15 -> 0.5, 1, 6, -6
   w = dequant_mxfp4(blocks, torch.tensor([[128]], dtype=torch.uint8), torch.float32)
   assert w[0, :4].tolist() == [1.0, 2.0, 12.0, -12.0]
+
+
+def test_flow_with_grading_stage_filters_documents(tmp_path):
+  """A data flow whose grading stage loads the grading model, heads and calibration named in its spec."""
+  import json
+  from nmoe_b200.data import hydra as H
+  from nmoe_b200.data.cli import main
+  from nmoe_b200.serve.checkpoint import save_model
+  m = backbone()
+  ck, heads = tmp_path / "ckpt", tmp_path / "heads"
+  save_model(m, str(ck))
+  torch.manual_seed(3)
+  probe, judge = H.ProbeHead(m.cfg.hidden_size), H.JudgeHead(m.cfg.hidden_size, mid_dim=32, n_heads=4)
+  H.save_heads(str(heads), probe, judge)
+  raw = tmp_path / "raw"; raw.mkdir()
+  with open(raw / "docs.jsonl", "w") as f:
+    for i in range(20):
+      f.write(json.dumps({"id": f"d{i}", "text": f"document number {i} " * 4}) + "\n")
+  # pick thresholds from the judge's own scores so that some documents pass and some do not
+  from nmoe_b200.data.score import ByteTokenizer
+  tok = ByteTokenizer()
+  texts = [json.loads(l)["text"] for l in open(raw / "docs.jsonl")]
+  scores = H.make_flow_grader(m, None, judge, H.Calibration(), tok, max_ctx=64)(texts)
+  thr = sorted(scores)[len(scores) // 2]
+  H.Calibration(tau_drop=0.0, tau_keep=1.0).save(str(heads))
+  out = tmp_path / "out"
+  spec = tmp_path / "flow.toml"
+  spec.write_text(f"""
+[source]
+kind = "jsonl"
+paths = "{raw / 'docs.jsonl'}"
+[grade]
+enabled = true
+threshold = {thr}
+batch_size = 8
+max_ctx = 64
+checkpoint = "{ck}"
+heads = "{heads}"
+[prep]
+output_dir = "{out}"
+dataset = "web"
+tokenizer = "bytes"
+num_shards = 1
+""")
+  assert main(["flow", str(spec)]) == 0
+  man = json.loads((out / "manifest.json").read_text())
+  kept = man["total_documents"] if "total_documents" in man else man["documents"]
+  assert 0 < kept < 20
