@@ -118,11 +118,16 @@ def main():
           act = EW.swiglu_rows(h13, plan.n_m_tiles)
         if marks:
           marks[2].record()
-        if quantised:
-          gg(aq, asf, wq[2], wq[3], plan.tile_expert, plan.n_m_tiles, push=rd.push_args(True))
+        if not rd.fused_return:      # NMOE_RDEP_FUSED_RETURN=0: GEMM into a local buffer, then a separate push kernel
+          y = (gg(aq, asf, wq[2], wq[3], plan.tile_expert, plan.n_m_tiles) if quantised
+               else G.grouped_gemm(act, W2, plan.tile_expert, plan.n_m_tiles, align256=rd.align == 256))
+          rd.push_and_reduce(y, plan, True, None, out)
         else:
-          G.grouped_gemm(act, W2, plan.tile_expert, plan.n_m_tiles, push=rd.push_args(True), align256=rd.align == 256)
-        rd.finish_return(plan, out)
+          if quantised:
+            gg(aq, asf, wq[2], wq[3], plan.tile_expert, plan.n_m_tiles, push=rd.push_args(True))
+          else:
+            G.grouped_gemm(act, W2, plan.tile_expert, plan.n_m_tiles, push=rd.push_args(True), align256=rd.align == 256)
+          rd.finish_return(plan, out)
         if marks:
           marks[3].record()
         return plan

@@ -148,6 +148,52 @@ k_rmsnorm_bwd(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restr
   }
 }
 
+// Wide rows (H > 4096): rowdot[m] = sum_c dy*w*x, one warp per row ...
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+k_rmsnorm_rowdot(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                 float* __restrict__ rowdot, int M, int H) {
+  const int row = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  if (row >= M) return;
+  const int lane = threadIdx.x & 31;
+  const int4* xr = reinterpret_cast<const int4*>(x + static_cast<size_t>(row) * H);
+  const int4* gr = reinterpret_cast<const int4*>(dy + static_cast<size_t>(row) * H);
+  float dot = 0.f;
+  for (int c = lane; c < (H >> 3); c += 32) {
+    Pack8 xv, gv, wv;
+    xv.v = ld_nc_v4(xr + c); gv.v = ld_nc_v4(gr + c); wv.v = __ldg(reinterpret_cast<const int4*>(w) + c);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 xf = __bfloat1622float2(xv.h[j]), gf = __bfloat1622float2(gv.h[j]), wf = __bfloat1622float2(wv.h[j]);
+      dot += gf.x * wf.x * xf.x + gf.y * wf.y * xf.y;
+    }
+  }
+  dot = warp_sum(dot);
+  if (lane == 0) rowdot[row] = dot;
+}
+
+// ... then a column-tiled pass: block (bx, by) owns 256 columns of a chunk of rows, one column per thread:
+// dx = dy*w*r - x*coef, and the per-column sums of dy*x*r go to dw_partial[by][c].
+__global__ void __launch_bounds__(256)
+k_rmsnorm_bwd_wide(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                   const float* __restrict__ rstd, const float* __restrict__ rowdot, __nv_bfloat16* __restrict__ dx,
+                   float* __restrict__ dw_partial, int M, int H, int rows_per_block) {
+  const int c = blockIdx.x * 256 + threadIdx.x;
+  const int row0 = blockIdx.y * rows_per_block;
+  const int row1 = min(M, row0 + rows_per_block);
+  if (c >= H) return;
+  const float wf = __bfloat162float(w[c]);
+  float acc = 0.f;
+  for (int row = row0; row < row1; ++row) {
+    const size_t i = static_cast<size_t>(row) * H + c;
+    const float r = rstd[row];
+    const float coef = rowdot[row] * r * r * r / static_cast<float>(H);
+    const float g = __bfloat162float(dy[i]), xv = __bfloat162float(x[i]);
+    dx[i] = __float2bfloat16(g * wf * r - xv * coef);
+    acc += g * xv * r;
+  }
+  dw_partial[static_cast<size_t>(blockIdx.y) * H + c] = acc;
+}
+
 // dw[c] = sum_b partial[b][c]  (+ existing dw when accumulate), written as bf16.
 __global__ void k_colsum_to_bf16(const float* __restrict__ partial, __nv_bfloat16* __restrict__ dw, int nblocks, int H,
                                  int accumulate) {
@@ -376,7 +422,7 @@ int nmoe_rmsnorm_bwd_blocks(int M) {
 int nmoe_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx, void* dw,
                      float* scratch, int M, int H, int accumulate, cudaStream_t st) {
   if (M == 0) return 0;
-  if (H % 8 != 0 || H > 4096) return -1;
+  if (H % 8 != 0 || H > 16384) return -1;
   const int nblocks = nmoe_rmsnorm_bwd_blocks(M);
   const int rpb = (M + nblocks - 1) / nblocks;
   const size_t smem = static_cast<size_t>(kWarpsPerBlock) * H * sizeof(float);
@@ -384,6 +430,18 @@ int nmoe_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* 
   auto b = static_cast<const __nv_bfloat16*>(x);
   auto c = static_cast<const __nv_bfloat16*>(w);
   auto d = static_cast<__nv_bfloat16*>(dx);
+  if (H > 4096) {
+    // wide rows (DeepSeek-V2/V3 hidden sizes): row dots first, then a column-tiled pass.  The row dots live
+    // in the M floats after the nblocks * H partial sums of `scratch`.
+    float* rowdot = scratch + static_cast<size_t>(nblocks) * H;
+    k_rmsnorm_rowdot<<<(M + kWarpsPerBlock - 1) / kWarpsPerBlock, kWarpsPerBlock * 32, 0, st>>>(a, b, c, rowdot, M, H);
+    CHECK_LAUNCH();
+    k_rmsnorm_bwd_wide<<<dim3((H + 255) / 256, nblocks), 256, 0, st>>>(a, b, c, rstd, rowdot, d, scratch, M, H, rpb);
+    CHECK_LAUNCH();
+    k_colsum_to_bf16<<<(H + 255) / 256, 256, 0, st>>>(scratch, static_cast<__nv_bfloat16*>(dw), nblocks, H, accumulate);
+    CHECK_LAUNCH();
+    return 0;
+  }
 #define LAUNCH_BWD(V)                                                                                      \
   do {                                                                                                     \
     cudaFuncSetAttribute(k_rmsnorm_bwd<V>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)); \

@@ -116,7 +116,8 @@ class Rdep:
     self.epoch_data = 0
     self.epoch_ret = 0
     self.wait_budget = 0          # 0 = library default (seconds); tests shrink it
-    self.fused_return = True      # False: separate push kernel after the GEMM (kept for A/B tests)
+    # False: separate push kernel after the GEMM (kept for A/B tests; NMOE_RDEP_FUSED_RETURN=0)
+    self.fused_return = os.environ.get("NMOE_RDEP_FUSED_RETURN", "1") == "1"
     self.fused_swiglu_quant = True  # block-scaled profiles: SwiGLU + quantise in the up/gate GEMM's epilogue
     # world > 1: the receive buffers hold the worst case (world x the balanced share), but every per-layer
     # tensor derived from them (H13, activations, their gradients) only needs the rows that arrived.  Reading

@@ -102,3 +102,21 @@ def test_newton_schulz_orthogonalises():
   assert s.max() < 1.3 and s.min() > 0.5          # singular values pushed towards 1
   t = newton_schulz(torch.randn(256, 128, device="cuda").bfloat16())
   assert t.shape == (256, 128)
+
+
+@pytest.mark.parametrize("M,H", [(300, 5120), (513, 7168)])
+def test_rmsnorm_wide_rows_forward_backward(M, H):
+  """Hidden sizes above 4096 (DeepSeek-V2 / V3 dims) take the two-pass backward."""
+  from nmoe_b200 import ops
+  from nmoe_b200.ref import ops as R
+  torch.manual_seed(0)
+  x = torch.randn(M, H, device="cuda").bfloat16().requires_grad_()
+  w = (1 + 0.1 * torch.randn(H, device="cuda")).bfloat16().requires_grad_()
+  y = ops.rmsnorm(x, w, 1e-6)
+  g = torch.randn_like(y)
+  y.backward(g)
+  xf, wf = x.detach().float().cpu().requires_grad_(), w.detach().float().cpu().requires_grad_()
+  yf = R.rmsnorm(xf, wf, 1e-6)
+  yf.backward(g.float().cpu())
+  rel = lambda a, b: ((a.float().cpu() - b).abs().max() / (b.abs().max() + 1e-6)).item()
+  assert rel(y, yf.detach()) < 1e-2 and rel(x.grad, xf.grad) < 2e-2 and rel(w.grad, wf.grad) < 2e-2

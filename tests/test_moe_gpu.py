@@ -156,3 +156,27 @@ def test_toy_model_step_on_gpu():
   G.check_status()
   assert math.isfinite(l0) and l < l0 - 0.05, (l0, l)
   tr.model.rdep.close()
+
+
+def test_wide_hidden_softmax_device_limited_slice_steps_on_gpu():
+  """A DeepSeek-V2-shaped slice (hidden 5120 > 4096, MLA 128+64 / 128 head dims, softmax router with
+  device-limited routing): a few steps run and the loss goes down."""
+  import math
+  from nmoe_b200.config import Config
+  from nmoe_b200.train import Trainer
+  from nmoe_b200.ops import tc_gemm as G
+  torch.manual_seed(6)
+  cfg = Config(vocab_size=2048, eos_token_id=2047, dim=5120, n_layers=2, n_heads=8, inter_dim=2048, moe_inter_dim=256,
+               n_routed_experts=16, n_activated_experts=4, n_shared_experts=1, n_dense_layers=1, q_lora_rank=256,
+               kv_lora_rank=128, qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128, batch_size=1, seq_len=256,
+               max_position_embeddings=512, warmup_steps=1, lr_dense=1e-3, lr_expert=1e-3, lr_router=1e-3,
+               router_type="softmax", route_n_groups=4, route_max_devices=2)
+  tr = Trainer(cfg, device=torch.device("cuda"))
+  tok = torch.randint(0, 2000, (1, 257))
+  x, y = tok[:, :-1].pin_memory(), tok[:, 1:].contiguous().pin_memory()
+  l0 = tr.step(x, y).item()
+  for _ in range(6):
+    l = tr.step(x, y).item()
+  G.check_status()
+  assert math.isfinite(l0) and l < l0 - 0.02, (l0, l)
+  tr.model.rdep.close()
