@@ -235,10 +235,19 @@ __global__ void __launch_bounds__(256) k_rdep_place(const PlaceArgs a) {
           const int ok = __shfl_sync(0xffffffffu, owner, k);
           if (pk < 0) continue;
           int4* dst = reinterpret_cast<int4*>(a.peer_x[ok] + static_cast<size_t>(pk) * a.H);
+          if (ok == a.rank) {
+            // rows that stay on this GPU: ordinary stores (the flag release at the end of the grid orders them)
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const int c = c0 + j * 32 + lane;
-            if (c < nvec) st_relaxed_sys_v4(dst + c, v[j]);
+            for (int j = 0; j < 8; ++j) {
+              const int c = c0 + j * 32 + lane;
+              if (c < nvec) dst[c] = v[j];
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const int c = c0 + j * 32 + lane;
+              if (c < nvec) st_relaxed_sys_v4(dst + c, v[j]);
+            }
           }
         }
       }
