@@ -226,24 +226,33 @@ __global__ void k_rope_inplace(__nv_bfloat16* __restrict__ x, const float* __res
 
 // ------------------------------------------------------------------ SwiGLU
 // h13 is [M, 2F] with gate at even columns and up at odd columns; a[M,F] = silu(gate) * up.
-__global__ void k_swiglu_fwd(const __nv_bfloat16* __restrict__ h13, __nv_bfloat16* __restrict__ a, long long M,
-                             int F, const int* __restrict__ n_tiles_dev) {
+__global__ void __launch_bounds__(256)
+k_swiglu_fwd(const __nv_bfloat16* __restrict__ h13, __nv_bfloat16* __restrict__ a, long long M,
+             int F, const int* __restrict__ n_tiles_dev) {
   if (n_tiles_dev != nullptr) M = min(M, static_cast<long long>(*n_tiles_dev) * 128);
-  const long long nvec = M * (F >> 2);      // 4 outputs (8 inputs = 16 bytes) per thread
-  const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (idx >= nvec) return;
-  Pack8 in;
-  in.v = ld_nc_v4(reinterpret_cast<const int4*>(h13) + idx);
-  __nv_bfloat162 o[2];
+  const long long nvec = M * (F >> 2);      // 4 outputs (8 inputs = 16 bytes) per vector
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  // grid-stride, two independent 16-byte loads in flight per thread
+  for (long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; idx < nvec; idx += 2 * stride) {
+    const long long idx2 = idx + stride;
+    Pack8 in[2];
+    in[0].v = ld_nc_v4(reinterpret_cast<const int4*>(h13) + idx);
+    if (idx2 < nvec) in[1].v = ld_nc_v4(reinterpret_cast<const int4*>(h13) + idx2);
 #pragma unroll
-  for (int j = 0; j < 2; ++j) {
-    float2 p0 = __bfloat1622float2(in.h[2 * j]);
-    float2 p1 = __bfloat1622float2(in.h[2 * j + 1]);
-    const float a0 = p0.x / (1.f + __expf(-p0.x)) * p0.y;
-    const float a1 = p1.x / (1.f + __expf(-p1.x)) * p1.y;
-    o[j] = __floats2bfloat162_rn(a0, a1);
+    for (int u = 0; u < 2; ++u) {
+      if (u == 1 && idx2 >= nvec) break;
+      __nv_bfloat162 o[2];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        float2 p0 = __bfloat1622float2(in[u].h[2 * j]);
+        float2 p1 = __bfloat1622float2(in[u].h[2 * j + 1]);
+        const float a0 = p0.x / (1.f + __expf(-p0.x)) * p0.y;
+        const float a1 = p1.x / (1.f + __expf(-p1.x)) * p1.y;
+        o[j] = __floats2bfloat162_rn(a0, a1);
+      }
+      reinterpret_cast<uint2*>(a)[u == 0 ? idx : idx2] = *reinterpret_cast<uint2*>(o);
+    }
   }
-  reinterpret_cast<uint2*>(a)[idx] = *reinterpret_cast<uint2*>(o);
 }
 
 // dh13 from (h13, da).  Optional per-row scale (the routing gate, applied to da) and
@@ -473,7 +482,9 @@ int nmoe_swiglu_fwd(const void* h13, void* a, long long M, int F, const int* n_t
   if (M == 0) return 0;
   if (F % 4 != 0) return -1;
   const long long nvec = M * (F / 4);
-  k_swiglu_fwd<<<static_cast<unsigned>((nvec + 255) / 256), 256, 0, st>>>(
+  long long blocks = (nvec + 511) / 512;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  k_swiglu_fwd<<<static_cast<unsigned>(blocks), 256, 0, st>>>(
       static_cast<const __nv_bfloat16*>(h13), static_cast<__nv_bfloat16*>(a), M, F, n_tiles_dev);
   CHECK_LAUNCH();
   return 0;

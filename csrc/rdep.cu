@@ -444,14 +444,26 @@ k_rdep_reduce(const __nv_bfloat16* __restrict__ ret, const int* __restrict__ pos
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nvec = H >> 3;
   for (int t = blockIdx.x * 8 + warp; t < T; t += gridDim.x * 8) {
+    // lane k remembers whether slot k was delivered (K <= 32); the bit mask is the same for every column
+    const unsigned live = __ballot_sync(0xffffffffu, lane < K && pos[t * K + lane] >= 0);
     for (int c = lane; c < nvec; c += 32) {
       float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-      for (int k = 0; k < K; ++k) {
-        if (pos[t * K + k] < 0) continue;
-        int4 v = ld_relaxed_sys_v4(reinterpret_cast<const int4*>(ret + (static_cast<size_t>(t) * K + k) * H) + c);
-        float2 f0 = unpack_bf16x2(v.x), f1 = unpack_bf16x2(v.y), f2 = unpack_bf16x2(v.z), f3 = unpack_bf16x2(v.w);
-        acc[0] += f0.x; acc[1] += f0.y; acc[2] += f1.x; acc[3] += f1.y;
-        acc[4] += f2.x; acc[5] += f2.y; acc[6] += f3.x; acc[7] += f3.y;
+      for (int k0 = 0; k0 < K; k0 += 8) {
+        // up to eight independent loads in flight, then the sum in slot order (bit-reproducible)
+        int4 v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int k = k0 + j;
+          v[j] = (k < K && ((live >> k) & 1u))
+                     ? ld_relaxed_sys_v4(reinterpret_cast<const int4*>(ret + (static_cast<size_t>(t) * K + k) * H) + c)
+                     : make_int4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float2 f0 = unpack_bf16x2(v[j].x), f1 = unpack_bf16x2(v[j].y), f2 = unpack_bf16x2(v[j].z), f3 = unpack_bf16x2(v[j].w);
+          acc[0] += f0.x; acc[1] += f0.y; acc[2] += f1.x; acc[3] += f1.y;
+          acc[4] += f2.x; acc[5] += f2.y; acc[6] += f3.x; acc[7] += f3.y;
+        }
       }
       int4 o;
       o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
