@@ -39,8 +39,8 @@ class _RMSNorm(torch.autograd.Function):
     dw = torch.empty_like(w)
     nb = L.lib().nmoe_rmsnorm_bwd_blocks(M)
     scratch = _scratch(x2.device, nb * H + M)      # partial column sums, then one row dot per row (wide rows only)
-    L.check(L.lib().nmoe_rmsnorm_bwd(L.ptr(dy2), L.ptr(x2), L.ptr(w), L.ptr(rstd), L.ptr(dx), L.ptr(dw),
-                                     L.ptr(scratch), M, H, 0, L.stream()), "rmsnorm_bwd", 2)
+    L.check(L.lib().nmoe_rmsnorm_bwd_twopass(L.ptr(dy2), L.ptr(x2), L.ptr(w), L.ptr(rstd), L.ptr(dx), L.ptr(dw),
+                                             L.ptr(scratch), M, H, 0, L.stream()), "rmsnorm_bwd", 3)
     return dx.view(ctx.shape), dw, None
 
 
