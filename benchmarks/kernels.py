@@ -48,10 +48,10 @@ def timed(fn, iters, warmup, flush):
 
 def main():
   ap = argparse.ArgumentParser()
-  ap.add_argument("what", choices=["gemm", "mx", "attn", "moe"])
+  ap.add_argument("what", choices=["gemm", "mx", "attn", "moe", "indexer"])
   for k, d in (("m", 16384), ("n", 2048), ("k", 2048), ("bn", 0), ("b", 4), ("s", 4096), ("h", 16), ("dqk", 192), ("dv", 128),
                ("window", 0), ("tokens", 16384), ("hidden", 2048), ("inter", 1408), ("experts", 64), ("topk", 6),
-               ("iters", 20), ("warmup", 3)):
+               ("idx-heads", 4), ("idx-dim", 64), ("iters", 20), ("warmup", 3)):
     ap.add_argument(f"--{k}", type=int, default=d)
   ap.add_argument("--a-mn", action="store_true"); ap.add_argument("--b-mn", action="store_true")
   ap.add_argument("--dtype", default="bf16"); ap.add_argument("--no-flush", action="store_true")
@@ -102,6 +102,18 @@ def main():
       ms = timed(lambda: attention_forward(q, k, v, a.dqk ** -0.5, a.window), a.iters, a.warmup, flush)
       tf = 2.0 * a.b * a.h * a.s * keys * (a.dqk + a.dv) / ms / 1e9
     out.update(shape=[a.b, a.s, a.h, a.dqk, a.dv], window=a.window, ms=ms, tflops=tf, frac_of_measured_bf16_peak=tf / pk["bf16_tflops"])
+  elif a.what == "indexer":
+    # sparse-attention indexer scores: fused GEMM + relu + head sum against the eager statement
+    from nmoe_b200.ops.indexer import indexer_scores, indexer_scores_ref
+    q = torch.randn(a.b, a.s, a.idx_heads, a.idx_dim, device=dev).bfloat16()
+    k = torch.randn(a.b, a.s, a.idx_dim, device=dev).bfloat16()
+    w = torch.randn(a.b, a.s, a.idx_heads, device=dev).bfloat16()
+    ms = timed(lambda: indexer_scores(q, k, w, True), a.iters, a.warmup, flush)
+    ms_ref = timed(lambda: indexer_scores_ref(q, k, w, True), max(2, a.iters // 5), 1, flush)
+    out_bytes = 4.0 * a.b * a.s * a.s
+    out.update(shape=[a.b, a.s, a.idx_heads, a.idx_dim], ms=ms, eager_ms=ms_ref, speedup=ms_ref / ms,
+               tflops=2.0 * a.b * a.s * (a.s / 2) * a.idx_heads * a.idx_dim / ms / 1e9,
+               output_gbs=out_bytes / ms / 1e6, frac_of_measured_hbm=out_bytes / ms / 1e6 / pk["hbm_gbs"])
   else:
     from nmoe_b200.ops.quant import ExpertWeightCache
     from nmoe_b200.parallel.rdep import Rdep

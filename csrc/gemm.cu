@@ -56,6 +56,11 @@ struct GemmParams {
   float* peer_retg[8];
   const float* rowval;
   int push_use_gate;
+  // Mode 3 (sparse-attention indexer): rows of A are keys, columns of B are (query, head) pairs; the epilogue
+  // writes C[query][key] = sum_head idx_w[query*heads + head] * relu(acc), -inf above the diagonal when causal.
+  const float* idx_w;
+  int idx_heads;
+  int idx_causal;
 };
 
 NMOE_DEVICE uint64_t globaltimer_ns() {
@@ -110,6 +115,11 @@ NMOE_DEVICE bool decode_tile(const GemmParams& p, int t, int m_tiles, int n_tile
   tc.expert = (MODE == 1) ? p.tile_expert[tc.m_blk] : 0;
   tc.kb_begin = 0;
   tc.kb_count = (p.K + BK - 1) / BK;
+  if (MODE == 3 && p.idx_causal) {
+    // every key of the tile lies after every query of the tile: nothing to multiply
+    const int last_query = (min((tc.n_blk + 1) * BN, p.N) - 1) / p.idx_heads;
+    if (tc.m_blk * BM > last_query) tc.kb_count = 0;
+  }
   return true;
 }
 
@@ -303,6 +313,38 @@ k_gemm_bf16(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           tmem_ld_32x32b_x32(ta + 32, r + 32);
           tmem_ld_wait();
           warp_store_rows_64cols(stage, r, push_gate, (row_ok && push_dst != nullptr) ? push_dst + col : nullptr, lane);
+        }
+      } else if (MODE == 3) {
+        // indexer scores: this thread owns one key; each group of idx_heads columns is one query
+        float* outp = static_cast<float*>(p.C);
+        const int hmask = p.idx_heads - 1;       // heads is a power of two that divides BN
+        const int hshift = 31 - __clz(p.idx_heads);
+        float accum = 0.f;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          const int col = n0 + c * 32;
+          if (col >= p.N) break;                 // uniform over the warp
+          uint32_t r[32];
+          if (have_acc) {
+            tmem_ld_32x32b_x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + c * 32, r);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = 0u;
+          }
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int cc = col + i;
+            if (cc < p.N) {
+              accum += fmaxf(__uint_as_float(r[i]), 0.f) * __ldg(p.idx_w + cc);
+              if ((cc & hmask) == hmask) {
+                const int tq = cc >> hshift;
+                if (row_ok)
+                  outp[static_cast<long long>(tq) * p.ldc + row] = (p.idx_causal && row > tq) ? -INFINITY : accum;
+                accum = 0.f;
+              }
+            }
+          }
         }
       } else
 #pragma unroll 1
@@ -498,6 +540,7 @@ int nmoe_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, l
   p.row_meta = static_cast<const int4*>(row_meta);
   p.rowval = rowval;
   p.push_use_gate = push_use_gate;
+  p.idx_w = nullptr; p.idx_heads = 1; p.idx_causal = 0;
   for (int r = 0; r < 8; ++r) {
     p.peer_ret[r] = (row_meta && peer_ret && r < world) ? static_cast<__nv_bfloat16*>(peer_ret[r]) : nullptr;
     p.peer_retg[r] = (row_meta && peer_retg && r < world) ? static_cast<float*>(peer_retg[r]) : nullptr;
@@ -526,6 +569,34 @@ int nmoe_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, l
   if (bn == 128) return GO(128);
   return GO(64);
 #undef GO
+}
+
+// Lightning-indexer scores of sparse attention, one batch element per call:
+//   out[t][s] = sum_h w[t*heads + h] * relu(q[t*heads + h, :] . k[s, :]),  -inf where s > t if causal.
+// k is [S, D] (row stride ldk), q is [T*heads, D] (row stride ldq), w is fp32 [T*heads], out is fp32 [T, ldo].
+// heads must be a power of two <= 128; D a multiple of 8.
+int nmoe_dsa_indexer_scores(const void* k, const void* q, const float* w, float* out, int S, int T, int heads, int D,
+                            long long ldk, long long ldq, long long ldo, int causal, void* status, cudaStream_t st) {
+  if (S <= 0 || T <= 0) return 0;
+  if (heads <= 0 || heads > 128 || (heads & (heads - 1)) != 0) return -1;
+  if (D <= 0 || (D % 8) || (ldk % 8) || (ldq % 8)) return -2;
+  constexpr int kBn = 128;
+  GemmParams p;
+  p.M = S; p.N = T * heads; p.K = D; p.E = 1;
+  p.tile_expert = nullptr; p.n_m_tiles = nullptr; p.offs = nullptr;
+  p.C = out; p.ldc = ldo; p.out_fp32 = 1; p.accumulate = 0;
+  p.b_rows_per_expert = 0;
+  p.status = static_cast<StatusRecord*>(status);
+  p.row_meta = nullptr; p.rowval = nullptr; p.push_use_gate = 0;
+  for (int r = 0; r < 8; ++r) { p.peer_ret[r] = nullptr; p.peer_retg[r] = nullptr; }
+  p.idx_w = w; p.idx_heads = heads; p.idx_causal = causal;
+  CUtensorMap tmA, tmB;
+  int rc = cached_map(&tmA, k, static_cast<uint64_t>(D), static_cast<uint64_t>(S), ldk * 2, BK, BM);
+  if (rc != 0) return rc;
+  rc = cached_map(&tmB, q, static_cast<uint64_t>(D), static_cast<uint64_t>(p.N), ldq * 2, BK, kBn);
+  if (rc != 0) return rc;
+  const int m_tiles = (S + BM - 1) / BM, n_tiles = (p.N + kBn - 1) / kBn;
+  return launch<kBn, false, false, 3>(tmA, tmB, p, m_tiles * n_tiles, st);
 }
 
 }  // extern "C"

@@ -14,17 +14,14 @@ import torch.nn.functional as F
 from torch import nn
 
 from ... import ops
+from ...ops.indexer import indexer_scores
 from .common import masked_attention
 from .mla import MLA
 
 
 def lightning_indexer(q_idx: torch.Tensor, k_idx: torch.Tensor, w: torch.Tensor, top_k: int, causal: bool = True):
   """q_idx [B,T,Hi,Di], k_idx [B,S,Di], w [B,T,Hi] -> (top scores [B,T,k], indices int32 [B,T,k])."""
-  s = torch.relu(torch.einsum("bmhd,bnd->bmhn", q_idx.float(), k_idx.float()))
-  s = (w.float().unsqueeze(-1) * s).sum(2)
-  if causal:
-    M, N = s.shape[1:]
-    s = s.masked_fill(torch.triu(torch.ones(M, N, dtype=torch.bool, device=s.device), 1), float("-inf"))
+  s = indexer_scores(q_idx, k_idx, w, causal)          # fused GEMM + relu + head sum on a GPU
   vals, idx = s.topk(min(top_k, s.size(-1)), dim=-1)
   return vals, idx.to(torch.int32)
 
@@ -68,7 +65,7 @@ class DSA(MLA):
     qi, ki, wi = self._idx_inputs(x.detach())
     if self.training_mode == "dense_warmup":
       o = masked_attention(q, k, v, causal, self.softmax_scale)
-      dense = (wi.float().unsqueeze(-1) * torch.relu(torch.einsum("bthd,bsd->bths", qi.float(), ki.float()))).sum(2)
+      dense = indexer_scores(qi, ki, wi, causal=False)
       with torch.no_grad():
         s = torch.einsum("bihd,bjhd->bhij", q.float(), k.float()) * self.softmax_scale
         p = torch.softmax(s.masked_fill(~causal, float("-inf")), -1)
