@@ -48,7 +48,7 @@ def timed(fn, iters, warmup, flush):
 
 def main():
   ap = argparse.ArgumentParser()
-  ap.add_argument("what", choices=["gemm", "mx", "attn", "moe", "indexer"])
+  ap.add_argument("what", choices=["gemm", "mx", "attn", "moe", "indexer", "elementwise"])
   for k, d in (("m", 16384), ("n", 2048), ("k", 2048), ("bn", 0), ("b", 4), ("s", 4096), ("h", 16), ("dqk", 192), ("dv", 128),
                ("window", 0), ("tokens", 16384), ("hidden", 2048), ("inter", 1408), ("experts", 64), ("topk", 6),
                ("idx-heads", 4), ("idx-dim", 64), ("iters", 20), ("warmup", 3)):
@@ -102,6 +102,37 @@ def main():
       ms = timed(lambda: attention_forward(q, k, v, a.dqk ** -0.5, a.window), a.iters, a.warmup, flush)
       tf = 2.0 * a.b * a.h * a.s * keys * (a.dqk + a.dv) / ms / 1e9
     out.update(shape=[a.b, a.s, a.h, a.dqk, a.dv], window=a.window, ms=ms, tflops=tf, frac_of_measured_bf16_peak=tf / pk["bf16_tflops"])
+  elif a.what == "elementwise":
+    # the memory-bound kernels of a step on the benchmark's shapes: algorithmic bytes / time against the measured copy rate
+    from nmoe_b200.ops.optim import adamw_flat_
+    T, H, F = a.tokens, a.hidden, a.inter
+    rows = T * a.topk
+    x = torch.randn(T, H, device=dev).bfloat16().requires_grad_(True)
+    wn = torch.ones(H, device=dev).bfloat16().requires_grad_(True)
+    gy = torch.randn(T, H, device=dev).bfloat16()
+    h13 = torch.randn(rows, 2 * F, device=dev).bfloat16().requires_grad_(True)
+    ga = torch.randn(rows, F, device=dev).bfloat16()
+    res = {}
+    def rec(name, ms, nbytes):
+      res[name] = {"ms": ms, "gbs": nbytes / ms / 1e6, "frac_of_measured_hbm": nbytes / ms / 1e6 / pk["hbm_gbs"]}
+    rec("rmsnorm_fwd", timed(lambda: ops.rmsnorm(x, wn, 1e-6), a.iters, a.warmup, flush), 2.0 * T * H * 2)
+    y = ops.rmsnorm(x, wn, 1e-6)
+    def nb():
+      x.grad = None; wn.grad = None
+      y.backward(gy, retain_graph=True)
+    rec("rmsnorm_bwd", timed(nb, a.iters, a.warmup, flush), 3.0 * T * H * 2)
+    rec("swiglu_fwd", timed(lambda: ops.swiglu(h13), a.iters, a.warmup, flush), 3.0 * rows * F * 2)
+    act = ops.swiglu(h13)
+    def sb():
+      h13.grad = None
+      act.backward(ga, retain_graph=True)
+    rec("swiglu_bwd", timed(sb, a.iters, a.warmup, flush), 5.0 * rows * F * 2)
+    n = 1 << 28
+    pw = torch.randn(n, device=dev).bfloat16(); g = torch.randn(n, device=dev).bfloat16()
+    m = torch.zeros(n, device=dev, dtype=torch.bfloat16); v = torch.zeros_like(m)
+    rec("adamw_flat_256M", timed(lambda: adamw_flat_(pw, g, m, v, lr=1e-3, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, step=3),
+                                 a.iters, a.warmup, flush), 7.0 * n * 2)
+    out.update(tokens=T, hidden=H, inter=F, rows=rows, kernels=res)
   elif a.what == "indexer":
     # sparse-attention indexer scores: fused GEMM + relu + head sum against the eager statement
     from nmoe_b200.ops.indexer import indexer_scores, indexer_scores_ref

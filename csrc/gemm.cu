@@ -320,29 +320,39 @@ k_gemm_bf16(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         const int hmask = p.idx_heads - 1;       // heads is a power of two that divides BN
         const int hshift = 31 - __clz(p.idx_heads);
         float accum = 0.f;
+        if (!have_acc) {
+          // tile skipped by the causal test in decode_tile: every key comes after every query
+          const int q_end = min(n0 + BN, p.N) >> hshift;
+          if (row_ok)
+            for (int tq = n0 >> hshift; tq < q_end; ++tq) outp[static_cast<long long>(tq) * p.ldc + row] = -INFINITY;
+        } else
 #pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          const int col = n0 + c * 32;
+        for (int c = 0; c < BN / 64; ++c) {
+          const int col = n0 + c * 64;
           if (col >= p.N) break;                 // uniform over the warp
-          uint32_t r[32];
+          // head weights of these 64 columns: two coalesced loads, handed out by shuffles below
+          const float w_lo = (col + lane < p.N) ? __ldg(p.idx_w + col + lane) : 0.f;
+          const float w_hi = (col + 32 + lane < p.N) ? __ldg(p.idx_w + col + 32 + lane) : 0.f;
+          uint32_t r[64];
           if (have_acc) {
-            tmem_ld_32x32b_x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + c * 32, r);
+            const uint32_t ta = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + c * 64;
+            tmem_ld_32x32b_x32(ta, r);
+            tmem_ld_32x32b_x32(ta + 32, r + 32);
             tmem_ld_wait();
           } else {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = 0u;
+            for (int i = 0; i < 64; ++i) r[i] = 0u;
           }
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
+          for (int i = 0; i < 64; ++i) {
             const int cc = col + i;
-            if (cc < p.N) {
-              accum += fmaxf(__uint_as_float(r[i]), 0.f) * __ldg(p.idx_w + cc);
-              if ((cc & hmask) == hmask) {
-                const int tq = cc >> hshift;
-                if (row_ok)
-                  outp[static_cast<long long>(tq) * p.ldc + row] = (p.idx_causal && row > tq) ? -INFINITY : accum;
-                accum = 0.f;
-              }
+            const float wv = __shfl_sync(0xffffffffu, i < 32 ? w_lo : w_hi, i & 31);   // zero past the last column
+            accum = fmaf(fmaxf(__uint_as_float(r[i]), 0.f), wv, accum);
+            if ((cc & hmask) == hmask && cc < p.N) {
+              const int tq = cc >> hshift;
+              if (row_ok)
+                outp[static_cast<long long>(tq) * p.ldc + row] = (p.idx_causal && row > tq) ? -INFINITY : accum;
+              accum = 0.f;
             }
           }
         }
