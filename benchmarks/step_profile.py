@@ -1,10 +1,11 @@
 """Device time of one Moonlight-16B-A3B training step by kernel (one GPU, torch profiler, CUDA activity only).
 
-  python benchmarks/step_profile.py [--top 40] [--activation-checkpoint none|attention] [--recompute-h13]
+  python benchmarks/step_profile.py [--top 40] [--gaps 20] [--activation-checkpoint none|attention] [--recompute-h13]
 
 Three warm-up steps, then one profiled step; prints the summed device time, and per kernel name the
 total milliseconds and the launch count.  Times under the profiler are a few percent higher than
-in a free run; use the shares, and ``bench.py`` for the step time itself.
+in a free run; use the shares, and ``bench.py`` for the step time itself.  ``--gaps N`` also lists where the
+device sat idle: the N largest sums of idle time, keyed by the kernel that ran before and the one that ran after.
 """
 from __future__ import annotations
 
@@ -22,6 +23,7 @@ from torch.profiler import ProfilerActivity, profile  # noqa: E402
 def main():
   ap = argparse.ArgumentParser()
   ap.add_argument("--top", type=int, default=40)
+  ap.add_argument("--gaps", type=int, default=0)
   ap.add_argument("--activation-checkpoint", default="none")
   ap.add_argument("--recompute-h13", action="store_true")
   a = ap.parse_args()
@@ -49,6 +51,25 @@ def main():
   print(f"total device ms {total / 1e3:.1f}")
   for e in sorted(ev, key=lambda e: -e.device_time_total)[:a.top]:
     print(f"{e.device_time_total / 1e3:8.2f} ms {e.count:6d}  {e.key[:120]}")
+  if a.gaps > 0:
+    from torch.autograd import DeviceType
+    ks = sorted((e for e in prof.events() if e.device_type == DeviceType.CUDA and e.time_range is not None),
+                key=lambda e: e.time_range.start)
+    idle, by_pair, busy_end = 0.0, {}, None
+    prev = None
+    for e in ks:
+      st, en = e.time_range.start, e.time_range.end
+      if busy_end is not None and st > busy_end:
+        g = st - busy_end
+        idle += g
+        key = (prev.name[:60], e.name[:60])
+        c = by_pair.setdefault(key, [0.0, 0, 0.0])
+        c[0] += g; c[1] += 1; c[2] = max(c[2], g)
+      if busy_end is None or en > busy_end:
+        busy_end, prev = en, e
+    print(f"idle device ms {idle / 1e3:.2f} over {len(ks)} kernels")
+    for (pa, pb), (g, n, mx) in sorted(by_pair.items(), key=lambda kv: -kv[1][0])[:a.gaps]:
+      print(f"{g / 1e3:8.3f} ms {n:5d} gaps (max {mx:7.1f} us)  {pa}  ->  {pb}")
   if tr.model.rdep is not None:
     tr.model.rdep.close()
 
