@@ -422,14 +422,27 @@ __global__ void __launch_bounds__(256) k_rdep_push(const PushArgs a) {
     if (a.y != nullptr) {
       const int4* s = reinterpret_cast<const int4*>(a.y + static_cast<size_t>(r) * a.H);
       int4* d = reinterpret_cast<int4*>(a.peer_ret[src] + static_cast<size_t>(ts) * a.H);
-      for (int c = lane; c < nvec; c += 32) {
-        int4 v = ld_nc_v4(s + c);
-        if (a.use_gate) {
-          float2 f0 = unpack_bf16x2(v.x), f1 = unpack_bf16x2(v.y), f2 = unpack_bf16x2(v.z), f3 = unpack_bf16x2(v.w);
-          v.x = pack_bf16x2(f0.x * g, f0.y * g); v.y = pack_bf16x2(f1.x * g, f1.y * g);
-          v.z = pack_bf16x2(f2.x * g, f2.y * g); v.w = pack_bf16x2(f3.x * g, f3.y * g);
+      // eight loads in flight per lane (4 KB of the row per pass), then the remote stores back to back
+      for (int c0 = 0; c0 < nvec; c0 += 256) {
+        int4 v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int c = c0 + j * 32 + lane;
+          if (c < nvec) v[j] = ld_nc_v4(s + c);
         }
-        st_relaxed_sys_v4(d + c, v);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int c = c0 + j * 32 + lane;
+          if (c < nvec) {
+            int4 o = v[j];
+            if (a.use_gate) {
+              float2 f0 = unpack_bf16x2(o.x), f1 = unpack_bf16x2(o.y), f2 = unpack_bf16x2(o.z), f3 = unpack_bf16x2(o.w);
+              o.x = pack_bf16x2(f0.x * g, f0.y * g); o.y = pack_bf16x2(f1.x * g, f1.y * g);
+              o.z = pack_bf16x2(f2.x * g, f2.y * g); o.w = pack_bf16x2(f3.x * g, f3.y * g);
+            }
+            st_relaxed_sys_v4(d + c, o);
+          }
+        }
       }
     }
     if (lane == 0 && a.rowval != nullptr) a.peer_retg[src][ts] = a.rowval[r];

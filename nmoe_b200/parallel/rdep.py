@@ -116,8 +116,12 @@ class Rdep:
     self.epoch_data = 0
     self.epoch_ret = 0
     self.wait_budget = 0          # 0 = library default (seconds); tests shrink it
-    # False: separate push kernel after the GEMM (kept for A/B tests; NMOE_RDEP_FUSED_RETURN=0)
-    self.fused_return = os.environ.get("NMOE_RDEP_FUSED_RETURN", "1") == "1"
+    # fused_return False: a local GEMM, then a separate push kernel (NMOE_RDEP_FUSED_RETURN=0/1 overrides).
+    # Default by measurement: with one peer the fused epilogue wins; from four ranks on, 3/4 or more of the rows
+    # leave the GPU and the four epilogue warps per SM cannot keep enough remote stores in flight, so a local GEMM
+    # followed by the wide push kernel is faster (8 GPUs, Moonlight shape: 1.82 ms against 2.37 ms per return).
+    env = os.environ.get("NMOE_RDEP_FUSED_RETURN", "")
+    self.fused_return = (env == "1") if env in ("0", "1") else (self.world <= 2)
     self.fused_swiglu_quant = True  # block-scaled profiles: SwiGLU + quantise in the up/gate GEMM's epilogue
     # world > 1: the receive buffers hold the worst case (world x the balanced share), but every per-layer
     # tensor derived from them (H13, activations, their gradients) only needs the rows that arrived.  Reading
@@ -286,7 +290,7 @@ class _MoEFused(torch.autograd.Function):
       G.grouped_gemm(a, W2, plan.tile_expert, plan.n_m_tiles, push=rdep.push_args(True), align256=rdep.align == 256)
       rdep.finish_return(plan, out)
     else:
-      y = G.grouped_gemm(a, W2, plan.tile_expert, plan.n_m_tiles)
+      y = G.grouped_gemm(a, W2, plan.tile_expert, plan.n_m_tiles, align256=rdep.align == 256)
       rdep.push_and_reduce(y, plan, True, None, out)
     ctx.rdep, ctx.plan = rdep, plan
     xd = rdep.xbuf[:rows].clone() if rdep.save_dispatched else None
@@ -323,7 +327,7 @@ class _MoEFused(torch.autograd.Function):
       G.grouped_gemm(dh13, W13, plan.tile_expert, nt, b_mn=True, push=rdep.push_args(False, rowdot), align256=rdep.align == 256)
       rdep.finish_return(plan, dx)
     else:
-      dxe = G.grouped_gemm(dh13, W13, plan.tile_expert, nt, b_mn=True)
+      dxe = G.grouped_gemm(dh13, W13, plan.tile_expert, nt, b_mn=True, align256=rdep.align == 256)
       rdep.push_and_reduce(dxe, plan, False, rowdot, dx)
     dg = rdep.retg[: plan.T * plan.K].clone().view(plan.T, plan.K)
     dg = torch.where(plan.pos.view(plan.T, plan.K) >= 0, dg, torch.zeros_like(dg))
