@@ -56,23 +56,29 @@ class _IndexerScores(torch.autograd.Function):
   @staticmethod
   def backward(ctx, d_scores):
     q_idx, k_idx, w = ctx.saved_tensors
-    B, T, Hi, D = q_idx.shape
-    d_scores = torch.nan_to_num(d_scores.float(), nan=0.0, posinf=0.0, neginf=0.0)
-    kf = k_idx.float()
-    dq = torch.empty_like(q_idx, dtype=torch.float32)
-    dw = torch.empty(B, T, Hi, dtype=torch.float32, device=q_idx.device)
-    dk = torch.zeros_like(kf)
-    chunk = max(1, min(T, (1 << 26) // max(1, Hi * k_idx.size(1))))     # bounds the [chunk, Hi, S] logits to 256 MB
-    for t0 in range(0, T, chunk):
-      t1 = min(T, t0 + chunk)
-      qf = q_idx[:, t0:t1].float()
-      pre = torch.einsum("bthd,bsd->bths", qf, kf)
-      g = d_scores[:, t0:t1].unsqueeze(2)                                # [B,c,1,S]; masked positions carry zero
-      dw[:, t0:t1] = (torch.relu(pre) * g).sum(-1)
-      dpre = (pre > 0).float() * g * w[:, t0:t1].float().unsqueeze(-1)
-      dq[:, t0:t1] = torch.einsum("bths,bsd->bthd", dpre, kf)
-      dk += torch.einsum("bths,bthd->bsd", dpre, qf)
-    return dq.to(q_idx.dtype), dk.to(k_idx.dtype), dw.to(w.dtype), None
+    return (*indexer_scores_backward(q_idx, k_idx, w, d_scores), None)
+
+
+def indexer_scores_backward(q_idx: torch.Tensor, k_idx: torch.Tensor, w: torch.Tensor, d_scores: torch.Tensor):
+  """Gradients of ``indexer_scores`` w.r.t. (q_idx, k_idx, w) for d_scores [B,T,S]; logits recomputed in query chunks.
+  Masked positions must carry zero (non-finite entries are treated as zero)."""
+  B, T, Hi, D = q_idx.shape
+  d_scores = torch.nan_to_num(d_scores.float(), nan=0.0, posinf=0.0, neginf=0.0)
+  kf = k_idx.float()
+  dq = torch.empty_like(q_idx, dtype=torch.float32)
+  dw = torch.empty(B, T, Hi, dtype=torch.float32, device=q_idx.device)
+  dk = torch.zeros_like(kf)
+  chunk = max(1, min(T, (1 << 26) // max(1, Hi * k_idx.size(1))))     # bounds the [chunk, Hi, S] logits to 256 MB
+  for t0 in range(0, T, chunk):
+    t1 = min(T, t0 + chunk)
+    qf = q_idx[:, t0:t1].float()
+    pre = torch.einsum("bthd,bsd->bths", qf, kf)
+    g = d_scores[:, t0:t1].unsqueeze(2)                                # [B,c,1,S]
+    dw[:, t0:t1] = (torch.relu(pre) * g).sum(-1)
+    dpre = (pre > 0).float() * g * w[:, t0:t1].float().unsqueeze(-1)
+    dq[:, t0:t1] = torch.einsum("bths,bsd->bthd", dpre, kf)
+    dk += torch.einsum("bths,bthd->bsd", dpre, qf)
+  return dq.to(q_idx.dtype), dk.to(k_idx.dtype), dw.to(w.dtype)
 
 
 def indexer_scores(q_idx: torch.Tensor, k_idx: torch.Tensor, w: torch.Tensor, causal: bool = True) -> torch.Tensor:

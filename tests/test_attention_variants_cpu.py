@@ -91,3 +91,16 @@ def test_kda_layer_training_step():
   for _ in range(4):
     l = tr.step(tok[:, :-1], tok[:, 1:]).item()
   assert math.isfinite(l0) and l < l0
+
+
+def test_indexer_backward_statement_matches_autograd():
+  from nmoe_b200.ops.indexer import indexer_scores_backward, indexer_scores_ref
+  torch.manual_seed(4)
+  q = torch.randn(2, 24, 3, 8, requires_grad=True)
+  k = torch.randn(2, 24, 8, requires_grad=True)
+  w = torch.randn(2, 24, 3, requires_grad=True)
+  g = torch.randn(2, 24, 24) * torch.tril(torch.ones(24, 24))
+  (indexer_scores_ref(q, k, w, True).masked_fill(torch.triu(torch.ones(24, 24, dtype=torch.bool), 1), 0.0) * g).sum().backward()
+  dq, dk, dw = indexer_scores_backward(q.detach(), k.detach(), w.detach(), g)
+  for a, b in ((dq, q.grad), (dk, k.grad), (dw, w.grad)):
+    assert torch.allclose(a, b, atol=1e-4, rtol=1e-4), (a - b).abs().max()
