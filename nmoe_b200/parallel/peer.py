@@ -23,18 +23,23 @@ class PeerSlab:
   region in every rank's slab; ``local(name, dtype, shape)`` views this rank's region as a tensor.
   """
 
+  GUARD_BYTE = 0xA5
+
   def __init__(self, regions: List[Tuple[str, int]], group: Optional[dist.ProcessGroup] = None, *,
-               local_only: bool = False):
+               local_only: bool = False, guard_bytes: int = 0):
     multi = dist.is_initialized() and not local_only
     self.world = dist.get_world_size(group) if multi else 1
     self.rank = dist.get_rank(group) if multi else 0
     self.offsets: Dict[str, int] = {}
     self.sizes: Dict[str, int] = {}
+    # guard_bytes > 0 (debug / tests): a canary area after every region, filled with GUARD_BYTE and checked by
+    # check_guards(): a kernel (local or a peer's) that writes past the end of a region shows up by name.
+    self.guard_bytes = (max(0, guard_bytes) + 255) & ~255
     off = 0
     for name, nbytes in regions:
       self.offsets[name] = off
       self.sizes[name] = nbytes
-      off += (nbytes + 255) & ~255
+      off += ((nbytes + 255) & ~255) + self.guard_bytes
     self.nbytes = max(off, 256)
     lib = L.lib()
     base = ctypes.c_void_p()
@@ -42,6 +47,10 @@ class PeerSlab:
     self.base = base.value
     self.peer_bases: List[int] = [0] * self.world
     self.peer_bases[self.rank] = self.base
+    if self.guard_bytes:
+      for name in self.offsets:
+        self._guard_view(name).fill_(self.GUARD_BYTE)
+      torch.cuda.synchronize()
     self._opened: List[int] = []
     if self.world > 1:
       handle = (ctypes.c_ubyte * 64)()
@@ -75,6 +84,18 @@ class PeerSlab:
     esz = torch.empty(0, dtype=dtype).element_size()
     assert n * esz <= self.sizes[name], f"region {name} too small"
     return _tensor_from_ptr(self.local_ptr(name), n * esz, self).view(dtype).view(*shape)
+
+  def _guard_view(self, name: str) -> torch.Tensor:
+    start = self.local_ptr(name) + self.sizes[name]
+    end = self.local_ptr(name) + ((self.sizes[name] + 255) & ~255) + self.guard_bytes
+    return _tensor_from_ptr(start, end - start, self)
+
+  def check_guards(self) -> List[str]:
+    """Names of this rank's regions whose trailing canary area was overwritten (empty without guards)."""
+    if not self.guard_bytes:
+      return []
+    torch.cuda.synchronize()
+    return [name for name in self.offsets if not bool((self._guard_view(name) == self.GUARD_BYTE).all())]
 
   def close(self) -> None:
     if self.base:

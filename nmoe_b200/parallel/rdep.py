@@ -100,7 +100,9 @@ class Rdep:
     if profile != "bf16":
       from ..ops.quant import sf_bytes
       regions += [("xq", self.capacity * H), ("sfa", sf_bytes(self.capacity, H))]
-    self.slab = PeerSlab(regions, group, local_only=single_process)
+    # NMOE_RDEP_GUARD=<bytes>: canary areas after every peer-visible region (see PeerSlab.check_guards)
+    self.slab = PeerSlab(regions, group, local_only=single_process,
+                         guard_bytes=int(os.environ.get("NMOE_RDEP_GUARD", "0")))
     self.fp4 =profile in ("nvfp4", "mxfp4", "fp4")
     if profile != "bf16":
       # fp4 rows use the first half of the region (H/2 bytes per row)

@@ -64,6 +64,32 @@ def test_moe_all_tokens_to_one_expert_and_determinism():
     rd.close()
 
 
+def test_peer_buffer_canaries_survive_forward_backward(monkeypatch):
+  """Canary areas after every peer-visible region stay intact through forward + backward (ragged token count,
+  all-to-one-expert and random routing); the check itself notices a poked byte."""
+  from nmoe_b200.parallel.rdep import Rdep
+  monkeypatch.setenv("NMOE_RDEP_GUARD", "4096")
+  torch.manual_seed(5)
+  dev = torch.device("cuda")
+  T, H, F, E, K = 500, 256, 128, 8, 2
+  rd = Rdep(H, E, K, T, device=dev)
+  try:
+    assert rd.slab.guard_bytes == 4096 and rd.slab.check_guards() == []
+    W13 = (torch.randn(E, 2 * F, H, device=dev) * 0.05).bfloat16().requires_grad_(True)
+    W2 = (torch.randn(E, H, F, device=dev) * 0.05).bfloat16().requires_grad_(True)
+    one = torch.tensor([[0, 3]] * T, device=dev, dtype=torch.int32)
+    rnd = torch.stack([torch.randperm(E, device=dev)[:K] for _ in range(T)]).int().contiguous()
+    for eid in (one, rnd):
+      x = (torch.randn(T, H, device=dev) * 0.5).bfloat16().requires_grad_(True)
+      gates = torch.rand(T, K, device=dev, requires_grad=True)
+      rd.moe(x, gates, eid, W13, W2).backward(torch.randn(T, H, device=dev).bfloat16())
+      assert rd.slab.check_guards() == []
+    rd.slab._guard_view("ret")[7] = 0
+    assert rd.slab.check_guards() == ["ret"]
+  finally:
+    rd.close()
+
+
 def test_wait_timeout_reports_status_and_context_survives():
   """A flag nobody sets: the bounded wait gives up, records a status, and the GPU stays usable."""
   import ctypes
