@@ -57,6 +57,9 @@ def check_moe(rank, world, dev):
   errs = {"out": rel(out.cpu(), ref[sl]), "dx": rel(xd.grad.cpu(), xf.grad[sl]), "dg": rel(gd.grad.cpu(), gf.grad[sl]),
           "dW13": rel(W13.grad.cpu(), Wf.grad[es]), "dW2": rel(W2.grad.cpu(), W2f.grad[es])}
   assert all(v < 3e-2 for v in errs.values()), errs
+  dist.barrier()                                   # every peer's stores have landed
+  assert rd.slab.check_guards() == [], rd.slab.check_guards()      # canaries (when NMOE_RDEP_GUARD is set)
+  dist.barrier()
   rd.close()
   return errs
 
