@@ -132,6 +132,26 @@ struct GemmSmem {
   static constexpr int kBytes = kStages * (kStageA + kStageB) + kEpiStage + 1024 /*align*/ + 256 /*barriers*/;
 };
 
+// Indexer epilogue (mode 3), 64 accumulator columns of one key: relu, head weight (handed out by shuffles from the
+// two coalesced loads w_lo / w_hi), sum over the heads of a query, one store per finished query.  HEADS > 0 fixes the
+// head count at compile time (col is a multiple of 64, so the query boundaries are static); 0 uses hmask / hshift.
+template <int HEADS>
+NMOE_DEVICE void indexer_cols64(const uint32_t (&r)[64], float w_lo, float w_hi, int col, int N, int hmask, int hshift,
+                                bool row_ok, int row, int causal, long long ldc, float* outp, float& accum) {
+#pragma unroll
+  for (int i = 0; i < 64; ++i) {
+    const float wv = __shfl_sync(0xffffffffu, i < 32 ? w_lo : w_hi, i & 31);   // zero past the last column
+    accum = fmaf(fmaxf(__uint_as_float(r[i]), 0.f), wv, accum);
+    const int cc = col + i;
+    const bool last = HEADS > 0 ? ((i & (HEADS - 1)) == HEADS - 1) : ((cc & hmask) == hmask);
+    if (last && cc < N) {
+      const int tq = HEADS > 0 ? cc / HEADS : (cc >> hshift);
+      if (row_ok) outp[static_cast<long long>(tq) * ldc + row] = (causal && row > tq) ? -INFINITY : accum;
+      accum = 0.f;
+    }
+  }
+}
+
 template <int BN, bool A_MN, bool B_MN, int MODE>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 k_gemm_bf16(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
@@ -343,18 +363,14 @@ k_gemm_bf16(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 #pragma unroll
             for (int i = 0; i < 64; ++i) r[i] = 0u;
           }
-#pragma unroll
-          for (int i = 0; i < 64; ++i) {
-            const int cc = col + i;
-            const float wv = __shfl_sync(0xffffffffu, i < 32 ? w_lo : w_hi, i & 31);   // zero past the last column
-            accum = fmaf(fmaxf(__uint_as_float(r[i]), 0.f), wv, accum);
-            if ((cc & hmask) == hmask && cc < p.N) {
-              const int tq = cc >> hshift;
-              if (row_ok)
-                outp[static_cast<long long>(tq) * p.ldc + row] = (p.idx_causal && row > tq) ? -INFINITY : accum;
-              accum = 0.f;
-            }
+#define NMOE_IDX_CASE(H_) \
+  case H_: indexer_cols64<H_>(r, w_lo, w_hi, col, p.N, hmask, hshift, row_ok, row, p.idx_causal, p.ldc, outp, accum); break
+          switch (p.idx_heads) {
+            NMOE_IDX_CASE(1); NMOE_IDX_CASE(2); NMOE_IDX_CASE(4); NMOE_IDX_CASE(8);
+            NMOE_IDX_CASE(16); NMOE_IDX_CASE(32); NMOE_IDX_CASE(64);
+            default: indexer_cols64<0>(r, w_lo, w_hi, col, p.N, hmask, hshift, row_ok, row, p.idx_causal, p.ldc, outp, accum);
           }
+#undef NMOE_IDX_CASE
         }
       } else
 #pragma unroll 1
