@@ -25,9 +25,6 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-PLANNING_HINT_TOK_S_PER_GPU = 30_000.0   # configs/flow_profiles.toml duration hints of the reference (not a measurement)
-
-
 def moonlight_cfg(n_gpus: int, micro_batch: int, seq_len: int, dtype: str, layers: int | None = None,
                   activation_checkpoint: str = "none", save_h13: bool = True, overlap_shared: str = "auto"):
   from nmoe_b200.config import Config
@@ -103,33 +100,116 @@ def flops_per_token(cfg) -> float:
   return 6.0 * active + 6.0 * L * cfg.n_heads * (cfg.qk_nope_head_dim + cfg.qk_rope_head_dim + cfg.v_head_dim) * cfg.seq_len
 
 
-def run_reference(args) -> None:
-  """The unmodified reference through its own entry point.  It hard-requires its compiled
-  `nmoe.csrc.rdep` extension plus FlashAttention-4 (`flash_attn.cute`) and FlashMLA for MLA
-  (nmoe/attention/mla.py:66-72); when any of these cannot be imported the arm is unavailable."""
-  why = None
-  sys.path.insert(0, os.path.join(ROOT, "baseline", "_ref"))
-  try:
-    import nmoe  # noqa: F401
-  except Exception as e:
-    why = f"reference package not installed under baseline/_ref: {type(e).__name__}: {e}"
-  if why is None:
-    for mod, what in (("nmoe.csrc.rdep", "compiled RDEP extension (its Makefile aborts without FlashMLA sources)"),
-                      ("flash_attn.cute.interface", "FlashAttention-4 CuTe forward used by its MLA"),
-                      ("nmoe.csrc.flashmla_sm100", "FlashMLA sm100 backward extension used by its MLA")):
-      try:
-        __import__(mod)
-      except Exception as e:
-        why = f"{mod} not importable ({what}): {type(e).__name__}"
-        break
-  if why is None:
+MOONLIGHT_REF_FIELDS = dict(
+  preset="moonlight", vocab_size=163840, eos_token_id=163839, dim=2048, inter_dim=11264, moe_inter_dim=1408, n_layers=27,
+  n_dense_layers=1, n_heads=16, n_routed_experts=64, n_shared_experts=2, n_activated_experts=6, route_scale=2.446,
+  q_lora_rank=1536, kv_lora_rank=512, qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128, attn="mla",
+  attn_global_every=1, lr_dense=3e-4, lr_router=3e-4, lr_expert=3e-4, warmup_steps=500)
+
+
+class _FailFlag:
+  """Lets every rank of the reference arm leave when one of them fails: the failing rank writes its reason to a file
+  keyed on the rendezvous port, a watcher thread in each other rank sees it within a second and exits the process, so
+  no rank is left waiting in a collective.  Rank 0 prints the `unavailable` line."""
+
+  def __init__(self, rank: int, deadline_s: float):
+    import threading
+    self.rank = rank
+    self.path = os.path.join(tempfile.gettempdir(), f"nmoe_bench_ref_fail_{os.environ.get('MASTER_PORT', '0')}_{os.getppid()}")
+    if rank == 0 and os.path.exists(self.path):
+      os.unlink(self.path)
+    self.deadline = time.time() + deadline_s
+    self.done = False
+    self.lock = threading.Lock()
+    self.t = threading.Thread(target=self._watch, daemon=True)
+    self.t.start()
+
+  def _emit_and_exit(self, why: str):
+    with self.lock:   # never released: the first caller prints and ends the process
+      if self.rank == 0:
+        print(json.dumps({"impl": "reference", "unavailable": why}), flush=True)
+      os._exit(0)
+
+  def _watch(self):
+    while not self.done:
+      time.sleep(0.5)
+      if os.path.exists(self.path):
+        time.sleep(0.2)
+        try:
+          why = open(self.path).read().strip() or "another rank failed"
+        except OSError:
+          why = "another rank failed"
+        self._emit_and_exit(why)
+      if time.time() > self.deadline:
+        self._emit_and_exit("reference arm exceeded its time limit (no step completed in time)")
+
+  def fail(self, why: str):
+    why = " ".join(str(why).split())[:400]
     try:
-      from nmoe.train import train as ref_train  # noqa: F401
-      why = "reference imports succeeded but its trainer needs pre-tokenized shards under data_path; no synthetic-data entry point"
-    except Exception as e:
-      why = f"nmoe.train not importable: {type(e).__name__}: {e}"
-  if int(os.environ.get("RANK", "0")) == 0:
-    print(json.dumps({"impl": "reference", "unavailable": why}))
+      with open(self.path, "x") as f:
+        f.write(why)
+    except OSError:
+      pass
+    self._emit_and_exit(why)
+
+  def finish(self):
+    self.done = True
+
+
+def run_reference(args) -> None:
+  """The unmodified reference (installed under baseline/_ref with its compiled RDEP extension) on the same model,
+  batch and synthetic data, through its own Config / Transformer / loader / optimizer objects; see baseline/ref_arm.py.
+  Its MLA needs FlashAttention-4 and FlashMLA, neither of which exists on this image; baseline/ref_env.py supplies
+  cuDNN's fused attention under those two names and the JSON line says so in `substitutions`."""
+  rank = int(os.environ.get("RANK", "0"))
+  world_env = int(os.environ.get("WORLD_SIZE", "1"))
+  flag = _FailFlag(rank, deadline_s=float(os.environ.get("NMOE_REF_ARM_DEADLINE_S", "1500")))
+  try:
+    from baseline import ref_arm, ref_env
+    dtype = args.ref_dtype
+    sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0")))
+    fields = dict(MOONLIGHT_REF_FIELDS)
+    if args.layers:
+      fields["n_layers"] = args.layers
+    clk = {}
+    r = ref_arm.run_train_steps(fields, micro_batch=args.micro_batch, seq_len=args.seq_len, steps=args.steps,
+                                warmup=args.warmup, dtype=dtype, e2e=not args.no_e2e,
+                                before_timed=(sampler.start if rank == 0 else None),
+                                after_timed=((lambda: clk.update(sampler.stop())) if rank == 0 else None))
+    clocks = clk or None
+    world = r["world"]
+    tokens = world * args.micro_batch * args.seq_len * args.steps
+    tok_s = tokens / (r["ms"] / 1e3)
+    e2e = None
+    if "e2e_ms" in r:
+      e2e = {"value": tokens / (r["e2e_ms"] / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": r["h2d_bytes_per_step"],
+             "d2h_bytes_per_step": r["d2h_bytes_per_step"], "ms_per_step": r["e2e_ms"] / args.steps}
+    flag.finish()
+    if rank == 0:
+      print(json.dumps({
+        "impl": "reference", "metric": "training throughput, Moonlight-16B-A3B (tokens/s whole job; MFU alongside)",
+        "value": tok_s, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": r["ms"] / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": dtype, "data": "synthetic uniform-random token ids (.npy shards through the reference's loader), random-init weights",
+        "config": {"model": "moonlight-16b-a3b" if not args.layers else f"INVALID-debug-{args.layers}-layers",
+                   "global_batch": world * args.micro_batch, "seq_len": args.seq_len,
+                   "parallelism": (f"rdep-ep{world}+zero2-dp{world}" if world > 1 else "single-gpu"),
+                   "expert_profile": dtype, "activation_checkpoint": "attention (the reference's only mode)",
+                   "l2": "per-step working set is far larger than the 126 MB L2"},
+        "final_loss": r["final_loss"], "peak_mem_gib": r["peak_mem_gib"], "clocks": clocks, "e2e": e2e,
+        "substitutions": ref_env.substitutions(),
+        "timed_loop": "nmoe/train.py:88-109 restated around the reference's own objects; logging/checkpoint/eval left out",
+      }), flush=True)
+    try:
+      from nmoe import runtime as ref_runtime
+      ref_runtime.finalize()
+    except Exception:
+      pass
+    os._exit(0)
+  except BaseException as e:  # noqa: BLE001 - every failure becomes the `unavailable` line
+    if isinstance(e, SystemExit):
+      raise
+    flag.fail(f"{type(e).__name__}: {e}" + (f" (world={world_env})" if world_env > 1 else ""))
 
 
 def main() -> None:
@@ -141,7 +221,11 @@ def main() -> None:
   ap.add_argument("--micro-batch", type=int, default=4)
   ap.add_argument("--seq-len", type=int, default=4096)
   ap.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (result is marked invalid)")
-  ap.add_argument("--dtype", default="bf16")
+  ap.add_argument("--dtype", default="fp8", choices=["bf16", "fp8", "nvfp4"],
+                  help="expert GEMM profile: fp8 = bf16 activations + block-scaled MXFP8 expert GEMMs (the headline configuration)")
+  ap.add_argument("--ref-dtype", default="bf16", choices=["bf16", "fp8", "nvfp4"],
+                  help="expert profile of the reference arm; its block-scaled profiles need its CuTe-DSL grouped GEMM, "
+                       "which only travels to 1-GPU boxes")
   ap.add_argument("--no-e2e", action="store_true")
   ap.add_argument("--overlap-shared", default="auto", choices=["auto", "0", "1"], help="shared-expert MLP on a second stream")
   ap.add_argument("--recompute-h13", action="store_true", help="recompute the experts' up/gate output in backward (saves ~16 GB on one GPU)")
@@ -250,7 +334,6 @@ def main() -> None:
       "tflops_per_gpu": tflops_per_gpu,
       "mfu_vs_nominal_2250": tflops_per_gpu / 2250.0,
       "mfu_vs_measured_sustained": (tflops_per_gpu / peaks["bf16_tflops_sustained"]) if peaks else None,
-      "vs_reference_planning_hint_30k_tok_s_per_gpu": tok_s / world / PLANNING_HINT_TOK_S_PER_GPU,
       "final_loss": final_loss, "peak_mem_gib": peak_alloc, "clocks": clocks, "e2e": e2e,
       "gpu_launches": launches, "zero2_impl": trainer.opt.dense.impl,
     }

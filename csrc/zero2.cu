@@ -7,7 +7,9 @@
 //      buffers straight over NVLink, sums in fp32 in rank order, scales by 1/W, applies AdamW
 //      (bf16 moments, fp32 math, decoupled decay first) and stores the new bf16 parameters into
 //      all W ranks' parameter buffers with 16-byte system-scope stores,
-//   3. after the last block finishes, releases a "my shard is published" flag to every peer.
+//   3. after the last block finishes, releases a "my shard is published" flag to every peer -- unless a block
+//      gave up waiting in step 1: then the shard was not updated, nothing is published, and the peers' own
+//      bounded waits on this rank's flag run out and report too, instead of training on a half-updated shard.
 // A following wait (nmoe_rdep_wait on the done flags) closes the step.  Replaces NCCL
 // reduce_scatter_tensor + six eager AdamW ops + all_gather_into_tensor (nmoe/zero2.py:221-279).
 #include <cuda_bf16.h>
@@ -96,12 +98,18 @@ __global__ void __launch_bounds__(256) k_zero2_fused(const Zero2Args a) {
   // 3. grid completion -> publish
   __threadfence_system();
   __syncthreads();
-  __shared__ int s_last;
-  if (threadIdx.x == 0) s_last = (atomicAdd(a.done_counter, 1) == static_cast<int>(gridDim.x) - 1);
+  __shared__ int s_last, s_failed;
+  if (threadIdx.x == 0) {
+    constexpr int kFailedBit = 1 << 30;
+    if (!s_ok) atomicOr(a.done_counter, kFailedBit);
+    const int old = atomicAdd(a.done_counter, 1);
+    s_last = ((old & (kFailedBit - 1)) == static_cast<int>(gridDim.x) - 1);
+    s_failed = s_last ? ((atomicOr(a.done_counter, 0) & kFailedBit) != 0) : 0;
+  }
   __syncthreads();
   if (s_last) {
     __threadfence_system();
-    if (threadIdx.x < a.world) st_release_sys_u32(a.peer_done_flags[threadIdx.x] + a.rank, a.epoch);
+    if (!s_failed && threadIdx.x < a.world) st_release_sys_u32(a.peer_done_flags[threadIdx.x] + a.rank, a.epoch);
     if (threadIdx.x == 0) *a.done_counter = 0;
   }
 }

@@ -240,6 +240,10 @@ def save_checkpoint(ck: Checkpointer, step: int, trainer, loader, plan, cfg: Con
   if not (force or step % max(1, cfg.checkpoint_every) == 0 or step == cfg.steps):
     return False
   world = trainer.world
+  # a bounded wait that ran out, or rows dropped by a full receive buffer, means some rank trained on stale or
+  # incomplete data: no rank may turn that state into a checkpoint
+  from .ops import tc_gemm
+  tc_gemm.check_status_collective(trainer.device, world)
   rd, dp = build_states(step, trainer, loader, plan, cfg, rank, world, fp)
   d = iteration_dir(ck.base, step)
   if rd is not None:

@@ -30,6 +30,43 @@ class _SourceState:
     self.dataset, self.cursor, self.emitted = dataset, Cursor(), 0
 
 
+class _PinnedRing:
+  """A few pinned host staging buffers used in turn.  A buffer is rewritten only after the host has waited for the
+  event recorded behind the last host->device copy that read it, so an asynchronous copy can never see the next
+  step's tokens (or a half-written batch), however far the host runs ahead of the device."""
+
+  def __init__(self, shape, n: int = 3):
+    self.cuda = torch.cuda.is_available()
+    self.bufs = [torch.empty(*shape, dtype=torch.int64) for _ in range(n)]
+    if self.cuda:
+      self.bufs = [b.pin_memory() for b in self.bufs]
+    self.events = [None] * n
+    self.i = -1
+
+  def acquire(self) -> torch.Tensor:
+    """Next buffer, safe to overwrite."""
+    self.i = (self.i + 1) % len(self.bufs)
+    ev = self.events[self.i]
+    if ev is not None:
+      ev.synchronize()
+      self.events[self.i] = None
+    return self.bufs[self.i]
+
+  def copied(self, stream=None) -> None:
+    """Call right after enqueueing the copy that reads the buffer returned by the last acquire()."""
+    if self.cuda:
+      ev = torch.cuda.Event()
+      ev.record(stream if stream is not None else torch.cuda.current_stream())
+      self.events[self.i] = ev
+
+  def to_device(self, buf: torch.Tensor, device: torch.device) -> torch.Tensor:
+    if device.type != "cuda":
+      return buf.clone()        # the caller must not alias a buffer that will be rewritten
+    out = buf.to(device, non_blocking=True)
+    self.copied()
+    return out
+
+
 class DeterministicLoader:
   def __init__(self, *, plan: MixturePlan, dp_world_size: int, dp_rank: int, seq_len: int, tokens_per_update: int,
                device: str | torch.device = "cuda"):
@@ -46,6 +83,7 @@ class DeterministicLoader:
     self._src: Dict[str, _SourceState] = {}
     self._enter_stage(0)
     self._pin: Optional[torch.Tensor] = None
+    self._ring: Optional[_PinnedRing] = None
 
   # ---------------------------------------------------------------- stream mechanics
   def _enter_stage(self, idx: int) -> None:
@@ -90,11 +128,11 @@ class DeterministicLoader:
 
   # ---------------------------------------------------------------- public
   def next_host(self) -> torch.Tensor:
-    """This rank's [mine, seq_len+1] int64 batch in pinned host memory."""
-    if self._pin is None:
-      self._pin = torch.empty(self.mine, self.seq_len + 1, dtype=torch.int64)
-      if torch.cuda.is_available():
-        self._pin = self._pin.pin_memory()
+    """This rank's [mine, seq_len+1] int64 batch in pinned host memory.  The buffer is one of a small ring; a
+    caller that copies it to the device itself should call ``staging.copied()`` right after enqueueing the copy."""
+    if self._ring is None:
+      self._ring = _PinnedRing((self.mine, self.seq_len + 1))
+    self._pin = self._ring.acquire()
     row = 0
     for i in range(self.seqs_per_step):
       self._maybe_advance_stage()
@@ -107,9 +145,14 @@ class DeterministicLoader:
       raise StopIteration
     return self._pin
 
+  @property
+  def staging(self) -> "_PinnedRing":
+    return self._ring
+
   @torch.no_grad()
   def next(self) -> Tuple[torch.Tensor, torch.Tensor]:
-    batch = self.next_host().to(self.device, non_blocking=True)
+    host = self.next_host()
+    batch = self._ring.to_device(host, torch.device(self.device))
     return batch[:, :-1], batch[:, 1:]
 
   def state_dict(self) -> Dict:
@@ -146,9 +189,7 @@ class SyntheticLoader:
     self.mine, self.seq_len, self.rank, self.seed = batch_per_rank, seq_len, rank, seed
     self.device = torch.device(device)
     self.step = 0
-    self._pin = torch.empty(self.mine, seq_len + 1, dtype=torch.int64)
-    if torch.cuda.is_available():
-      self._pin = self._pin.pin_memory()
+    self._ring = _PinnedRing((self.mine, seq_len + 1))
 
   def next_host(self) -> torch.Tensor:
     g = torch.Generator().manual_seed(self.seed * 1_000_003 + self.step * 1009 + self.rank)
@@ -156,12 +197,18 @@ class SyntheticLoader:
     t = torch.randint(0, hi, (self.mine, self.seq_len + 1), generator=g)
     if hi == self.vocab:
       t = torch.where(t == self.eos, (t + 1) % self.vocab, t)
-    self._pin.copy_(t)
+    pin = self._ring.acquire()
+    pin.copy_(t)
     self.step += 1
-    return self._pin
+    return pin
+
+  @property
+  def staging(self) -> "_PinnedRing":
+    return self._ring
 
   def next(self) -> Tuple[torch.Tensor, torch.Tensor]:
-    batch = self.next_host().to(self.device, non_blocking=True)
+    host = self.next_host()
+    batch = self._ring.to_device(host, self.device)
     return batch[:, :-1], batch[:, 1:]
 
   def state_dict(self) -> Dict:

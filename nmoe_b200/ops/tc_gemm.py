@@ -35,6 +35,69 @@ def check_status(device: Optional[torch.device] = None) -> None:
       raise L.NativeLibraryError(f"kernel reported status code={rec[0]} where={rec[1]} a={rec[2]} b={rec[3]} on {dev}")
 
 
+def check_status_collective(device: Optional[torch.device] = None, world: int = 1, group=None) -> None:
+  """``check_status`` for a point where every rank must agree before something irreversible happens (a checkpoint
+  is finalised, a run starts): raises on EVERY rank when ANY rank's kernels reported a failure, so no rank goes on
+  to write its share of a checkpoint that another rank's stale parameters would poison."""
+  err = None
+  try:
+    check_status(device)
+  except L.NativeLibraryError as e:
+    err = e
+  import torch.distributed as dist
+  if world > 1 and dist.is_available() and dist.is_initialized():
+    on_cuda = device is not None and device.type == "cuda" and dist.get_backend(group) == "nccl"
+    flag = torch.tensor([1 if err is not None else 0], dtype=torch.int32, device=device if on_cuda else "cpu")
+    dist.all_reduce(flag, op=dist.ReduceOp.MAX, group=group)
+    if err is None and int(flag.item()) != 0:
+      err = L.NativeLibraryError("a peer rank's kernels reported a failure (bounded wait ran out or rows were dropped)")
+  if err is not None:
+    raise err
+
+
+class StatusWatch:
+  """Looks at the status record after every step without making the host wait for the device: ``enqueue()`` copies
+  the record into pinned host memory behind the step's kernels, ``poll()`` raises for any earlier copy that has
+  arrived with a failure code.  A failure is therefore seen one step late at most, and no step pays a sync."""
+
+  def __init__(self, device: torch.device, depth: int = 4):
+    self.device = device
+    self.cuda = device.type == "cuda"
+    self.host = [torch.zeros(4, dtype=torch.int32) for _ in range(depth)]
+    if self.cuda:
+      self.host = [h.pin_memory() for h in self.host]
+    self.events = [None] * depth
+    self.i = 0
+
+  def _examine(self, k: int) -> None:
+    self.events[k] = None
+    rec = self.host[k].tolist()
+    if rec[0] != 0:
+      status_buffer(self.device).zero_()
+      raise L.NativeLibraryError(f"kernel reported status code={rec[0]} where={rec[1]} a={rec[2]} b={rec[3]} on {self.device}")
+
+  def enqueue(self) -> None:
+    k = self.i
+    self.i = (self.i + 1) % len(self.host)
+    if self.events[k] is not None:
+      self.events[k].synchronize()
+      self._examine(k)
+    self.host[k].copy_(status_buffer(self.device), non_blocking=True)
+    if self.cuda:
+      ev = torch.cuda.Event()
+      ev.record()
+      self.events[k] = ev
+    else:
+      self.events[k] = True
+
+  def poll(self) -> None:
+    for k, ev in enumerate(self.events):
+      if ev is None:
+        continue
+      if ev is True or ev.query():
+        self._examine(k)
+
+
 PAIR_MODE = os.environ.get("NMOE_GEMM_PAIR", "1") == "1"
 PAIR_PUSH = os.environ.get("NMOE_PAIR_PUSH", "1") == "1"      # fused-return grouped GEMMs on CTA pairs too
 

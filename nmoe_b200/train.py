@@ -106,6 +106,9 @@ def train(cfg: Config) -> dict:
   trainer.step_num, trainer.tokens_seen = start_step, tokens_seen
   fp = fingerprint(cfg)
   last_loss = None
+  watch = tc_gemm.StatusWatch(device) if (device.type == "cuda" and world > 1) else None
+  if device.type == "cuda":
+    tc_gemm.check_status_collective(device, world)      # nothing latched by set-up before the first step
   try:
     for step_num in range(start_step, cfg.steps):
       t0 = time.perf_counter()
@@ -117,6 +120,11 @@ def train(cfg: Config) -> dict:
         loss = trainer.step(inputs, targets)
       last_loss = loss
       log_training_step(metrics, s, trainer, loss, loader_wait_ms, print0)
+      if watch is not None:
+        # multi-rank: peers depend on this rank's flags and buffers, so look at the record every step (copied
+        # behind the step's kernels, examined when it has arrived: no host wait)
+        watch.poll()
+        watch.enqueue()
       if device.type == "cuda" and s % cfg.log_every == 0:
         tc_gemm.check_status(device)
       if cfg.eval_every > 0 and s % cfg.eval_every == 0:

@@ -187,3 +187,76 @@ def test_hybrid_routing_model_uses_same_index_proxy():
   assert sum(len(v) for v in inbox.values()) == 16
   assert [t[2] for t in inbox[0]] == sorted(t[2] for t in inbox[0]) and all(e // 4 == 0 for _, _, e in inbox[0])
   assert carried["net"] == sum(1 for r in range(4) for e in eid[r] if (e // 4) // 2 != r // 2)
+
+
+def test_loader_batches_do_not_alias_staging_buffers():
+  """Batches of consecutive steps must stay distinct objects with their own contents even though the loader
+  stages them through a small ring of reused host buffers."""
+  from nmoe_b200.data.loader import SyntheticLoader
+  ld = SyntheticLoader(vocab_size=1000, eos_token_id=999, batch_per_rank=2, seq_len=16, rank=0, seed=3, device="cpu")
+  kept = [ld.next()[0].clone() for _ in range(7)]
+  ld2 = SyntheticLoader(vocab_size=1000, eos_token_id=999, batch_per_rank=2, seq_len=16, rank=0, seed=3, device="cpu")
+  held = [ld2.next()[0] for _ in range(7)]      # no clone: must still hold each step's own tokens afterwards
+  for a, b in zip(kept, held):
+    assert torch.equal(a, b)
+  assert len({h.data_ptr() for h in held}) == 7
+
+
+@pytest.mark.gpu
+def test_loader_async_copies_see_their_own_step():
+  """Several steps without any host synchronisation: every device batch equals the host sequence of its step."""
+  from nmoe_b200.data.loader import SyntheticLoader
+  dev = torch.device("cuda", 0)
+  ld = SyntheticLoader(vocab_size=50000, eos_token_id=49999, batch_per_rank=8, seq_len=4096, rank=0, seed=5, device=dev)
+  ref = SyntheticLoader(vocab_size=50000, eos_token_id=49999, batch_per_rank=8, seq_len=4096, rank=0, seed=5, device="cpu")
+  big = torch.empty(1 << 28, dtype=torch.uint8, device=dev)
+  got = []
+  for _ in range(8):
+    big.zero_(); big.add_(1)            # keep the stream busy so the copies queue up behind device work
+    got.append(ld.next()[0])
+  torch.cuda.synchronize()
+  for g in got:
+    assert torch.equal(g.cpu(), ref.next()[0])
+
+
+def test_latched_kernel_status_blocks_the_checkpoint(tmp_path):
+  """A status record left by a kernel (a wait that ran out, dropped rows) must stop the checkpoint before any file
+  of the step exists; the record is cleared by the raise, so the next attempt goes through."""
+  from nmoe_b200.checkpoint import Checkpointer, iteration_dir, read_tracker, save_checkpoint
+  from nmoe_b200.data.loader import build_loader
+  from nmoe_b200.ops import _lib as L
+  from nmoe_b200.ops import tc_gemm
+  from nmoe_b200.train import Trainer
+  cfg = _tiny_cfg(tmp_path)
+  dev = torch.device("cpu")
+  tr = Trainer(cfg, device=dev)
+  loader, plan = build_loader(cfg, 0, 1, print_fn=lambda *a: None)
+  ck = Checkpointer(cfg.checkpoint_dir, async_io=False)
+  tc_gemm._STATUS[dev] = torch.tensor([2, 420, 1, 7], dtype=torch.int32)
+  try:
+    with pytest.raises(L.NativeLibraryError, match="code=2 where=420"):
+      save_checkpoint(ck, 3, tr, loader, plan, cfg, 0, C.fingerprint(cfg), print_fn=lambda *a: None, force=True)
+    assert not iteration_dir(cfg.checkpoint_dir, 3).exists() and read_tracker(cfg.checkpoint_dir) == -1
+    assert save_checkpoint(ck, 3, tr, loader, plan, cfg, 0, C.fingerprint(cfg), print_fn=lambda *a: None, force=True)
+    assert read_tracker(cfg.checkpoint_dir) == 3
+  finally:
+    tc_gemm._STATUS.pop(dev, None)
+    ck.close()
+
+
+def test_status_watch_reports_one_step_late_without_blocking():
+  from nmoe_b200.ops import _lib as L
+  from nmoe_b200.ops import tc_gemm
+  dev = torch.device("cpu")
+  tc_gemm._STATUS[dev] = torch.zeros(4, dtype=torch.int32)
+  try:
+    w = tc_gemm.StatusWatch(dev, depth=2)
+    for _ in range(5):
+      w.poll(); w.enqueue()
+    tc_gemm._STATUS[dev][:] = torch.tensor([1, 500, 3, 9], dtype=torch.int32)
+    w.poll(); w.enqueue()                       # the failing step's record is only copied here ...
+    with pytest.raises(L.NativeLibraryError, match="where=500"):
+      w.poll()                                  # ... and seen at the next step
+    assert int(tc_gemm._STATUS[dev][0]) == 0
+  finally:
+    tc_gemm._STATUS.pop(dev, None)
