@@ -145,6 +145,10 @@ def activate() -> None:
         sys.path.remove(p)
     sys.path.insert(0, p)
     os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")   # as nmoe/train.py:33 does
+    # torch first: its bundled cuBLAS / cuBLASLt must be the ones the process binds.  The extension links the
+    # toolkit's libcublas by soname; loaded first, it would shadow torch's copy and torch's GEMMs then fail with
+    # CUBLAS_STATUS_INVALID_VALUE (seen on the first nn.Linear of the reference model).
+    import torch  # noqa: F401
     try:
         importlib.import_module("nmoe.csrc.rdep")
     except Exception as e:

@@ -209,6 +209,8 @@ def run_reference(args) -> None:
   except BaseException as e:  # noqa: BLE001 - every failure becomes the `unavailable` line
     if isinstance(e, SystemExit):
       raise
+    import traceback
+    traceback.print_exc(file=sys.stderr)
     flag.fail(f"{type(e).__name__}: {e}" + (f" (world={world_env})" if world_env > 1 else ""))
 
 

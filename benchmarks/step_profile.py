@@ -1,6 +1,6 @@
 """Device time of one Moonlight-16B-A3B training step by kernel (one GPU, torch profiler, CUDA activity only).
 
-  python benchmarks/step_profile.py [--top 40] [--gaps 20] [--activation-checkpoint none|attention] [--recompute-h13]
+  python benchmarks/step_profile.py [--dtype fp8|bf16] [--top 40] [--gaps 20] [--activation-checkpoint none|attention] [--recompute-h13]
 
 Three warm-up steps, then one profiled step; prints the summed device time, and per kernel name the
 total milliseconds and the launch count.  Times under the profiler are a few percent higher than
@@ -26,12 +26,13 @@ def main():
   ap.add_argument("--gaps", type=int, default=0)
   ap.add_argument("--activation-checkpoint", default="none")
   ap.add_argument("--recompute-h13", action="store_true")
+  ap.add_argument("--dtype", default="fp8", choices=["bf16", "fp8", "nvfp4"], help="expert GEMM profile")
   a = ap.parse_args()
   import bench
   from nmoe_b200 import runtime
   from nmoe_b200.train import Trainer
   rank, world, device = runtime.init(42)
-  cfg = bench.moonlight_cfg(1, 4, 4096, "bf16", None, a.activation_checkpoint, not a.recompute_h13)
+  cfg = bench.moonlight_cfg(1, 4, 4096, a.dtype, None, a.activation_checkpoint, not a.recompute_h13)
   tr = Trainer(cfg, rank=rank, world=world, device=device)
   gen = torch.Generator().manual_seed(1234)
 

@@ -127,49 +127,65 @@ k_adamw_quant(__nv_bfloat16* __restrict__ p, const __nv_bfloat16* __restrict__ g
               __nv_bfloat16* __restrict__ v, long long rows, int K, float lr, float beta1, float beta2, float eps,
               float wd, float inv_bc1, float inv_bc2_sqrt, float grad_scale, uint8_t* __restrict__ q,
               uint8_t* __restrict__ sf, int sf_cols_padded) {
-  const long long row = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
-  if (row >= rows) return;
-  const int lane = threadIdx.x & 31;
-  for (int b = lane; b < (K >> 5); b += 32) {
-    const long long off = row * K + b * 32;
-    float pf[32], gf[32], mf[32], vf[32];
-    load_block_bf16(p + off, pf);
-    load_block_bf16(g + off, gf);
-    load_block_bf16(m + off, mf);
-    load_block_bf16(v + off, vf);
-    uint32_t pw[16], mw[16], vw[16];
+  // A thread owns 8 consecutive elements (one 16-byte vector of each tensor), so every load and store of a warp
+  // covers 512 contiguous bytes; the four lanes that share a 32-element block agree on its scale with two shuffles.
+  const long long nvec = rows * (K >> 3);
+  const int vec_per_row = K >> 3;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int4 p4 = reinterpret_cast<const int4*>(p)[i];
+    const int4 g4 = ld_nc_v4(reinterpret_cast<const int4*>(g) + i);
+    const int4 m4 = reinterpret_cast<const int4*>(m)[i];
+    const int4 v4 = reinterpret_cast<const int4*>(v)[i];
+    const uint32_t* pw = reinterpret_cast<const uint32_t*>(&p4);
+    const uint32_t* gw = reinterpret_cast<const uint32_t*>(&g4);
+    const uint32_t* mw = reinterpret_cast<const uint32_t*>(&m4);
+    const uint32_t* vw = reinterpret_cast<const uint32_t*>(&v4);
+    float x[8];
+    int4 po, mo, vo;
+    uint32_t* pow_ = reinterpret_cast<uint32_t*>(&po);
+    uint32_t* mow = reinterpret_cast<uint32_t*>(&mo);
+    uint32_t* vow = reinterpret_cast<uint32_t*>(&vo);
+    float amax = 0.f;
 #pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      const float gi = gf[i] * grad_scale;
-      float x = pf[i] * (1.f - lr * wd);
-      mf[i] = beta1 * mf[i] + (1.f - beta1) * gi;
-      vf[i] = beta2 * vf[i] + (1.f - beta2) * gi * gi;
-      x -= lr * inv_bc1 * mf[i] / (sqrtf(vf[i]) * inv_bc2_sqrt + eps);
-      pf[i] = __bfloat162float(__float2bfloat16(x));            // the cache is quantised from the stored bf16 value
+    for (int j = 0; j < 4; ++j) {
+      float2 pf = unpack_bf16x2(pw[j]), gf = unpack_bf16x2(gw[j]), mf = unpack_bf16x2(mw[j]), vf = unpack_bf16x2(vw[j]);
+      // same operation order as k_adamw_flat, so the two optimisers stay bit-identical
+      gf.x *= grad_scale; gf.y *= grad_scale;
+      pf.x *= (1.f - lr * wd); pf.y *= (1.f - lr * wd);
+      mf.x = beta1 * mf.x + (1.f - beta1) * gf.x; mf.y = beta1 * mf.y + (1.f - beta1) * gf.y;
+      vf.x = beta2 * vf.x + (1.f - beta2) * gf.x * gf.x; vf.y = beta2 * vf.y + (1.f - beta2) * gf.y * gf.y;
+      pf.x -= lr * inv_bc1 * mf.x / (sqrtf(vf.x) * inv_bc2_sqrt + eps);
+      pf.y -= lr * inv_bc1 * mf.y / (sqrtf(vf.y) * inv_bc2_sqrt + eps);
+      pow_[j] = pack_bf16x2(pf.x, pf.y); mow[j] = pack_bf16x2(mf.x, mf.y); vow[j] = pack_bf16x2(vf.x, vf.y);
+      const float2 pr = unpack_bf16x2(pow_[j]);            // the cache is quantised from the stored bf16 value
+      x[2 * j] = pr.x; x[2 * j + 1] = pr.y;
+      amax = fmaxf(amax, fmaxf(fabsf(pr.x), fabsf(pr.y)));
     }
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      pw[i] = pack_bf16x2(pf[2 * i], pf[2 * i + 1]);
-      mw[i] = pack_bf16x2(mf[2 * i], mf[2 * i + 1]);
-      vw[i] = pack_bf16x2(vf[2 * i], vf[2 * i + 1]);
-    }
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      reinterpret_cast<int4*>(p + off)[i] = make_int4(pw[4 * i], pw[4 * i + 1], pw[4 * i + 2], pw[4 * i + 3]);
-      reinterpret_cast<int4*>(m + off)[i] = make_int4(mw[4 * i], mw[4 * i + 1], mw[4 * i + 2], mw[4 * i + 3]);
-      reinterpret_cast<int4*>(v + off)[i] = make_int4(vw[4 * i], vw[4 * i + 1], vw[4 * i + 2], vw[4 * i + 3]);
-    }
-    uint32_t w[8];
-    uint8_t s;
+    reinterpret_cast<int4*>(p)[i] = po;
+    reinterpret_cast<int4*>(m)[i] = mo;
+    reinterpret_cast<int4*>(v)[i] = vo;
+    const unsigned live = __activemask();       // the vector count is a multiple of 4: a block's four lanes leave together
+    amax = fmaxf(amax, __shfl_xor_sync(live, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(live, amax, 2));
+    const uint8_t sb = e8m0_from_amax(amax, FP4 ? kInvFp4Max : kInvFp8Max);
+    const float inv = e8m0_inv_scale(sb);
     if (FP4) {
-      s = quant_block_e2m1_regs(pf, w);
-      *reinterpret_cast<int4*>(q + row * (K >> 1) + b * 16) = make_int4(w[0], w[1], w[2], w[3]);
+      uint32_t w = 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) w |= e2m1_code(x[j] * inv) << (j * 4);
+      reinterpret_cast<uint32_t*>(q)[i] = w;
     } else {
-      s = quant_block_e4m3_regs(pf, w);
-      reinterpret_cast<int4*>(q + row * K + b * 32)[0] = make_int4(w[0], w[1], w[2], w[3]);
-      reinterpret_cast<int4*>(q + row * K + b * 32)[1] = make_int4(w[4], w[5], w[6], w[7]);
+      int2 w;
+      w.x = pack4_e4m3(x[0] * inv, x[1] * inv, x[2] * inv, x[3] * inv);
+      w.y = pack4_e4m3(x[4] * inv, x[5] * inv, x[6] * inv, x[7] * inv);
+      reinterpret_cast<int2*>(q)[i] = w;
     }
-    sf[sf_mma_offset(static_cast<int>(row), b, sf_cols_padded)] = s;
+    if ((threadIdx.x & 3) == 0) {
+      const long long row = i / vec_per_row;
+      const int blk = static_cast<int>(i - row * vec_per_row) >> 2;
+      sf[sf_mma_offset(static_cast<int>(row), blk, sf_cols_padded)] = sb;
+    }
   }
 }
 
@@ -284,7 +300,9 @@ int nmoe_expert_adamw_quant(void* p, const void* g, void* m, void* v, long long 
   const float inv_bc1 = 1.f / (1.f - powf(beta1, static_cast<float>(step)));
   const float inv_bc2_sqrt = 1.f / sqrtf(1.f - powf(beta2, static_cast<float>(step)));
   const int sfc = ((K / 32) + 3) & ~3;
-  const unsigned blocks = static_cast<unsigned>((rows + 7) / 8);
+  const long long nvec = rows * (K / 8);
+  long long want = (nvec + 255) / 256;
+  const unsigned blocks = static_cast<unsigned>(want < 148 * 16 ? want : 148 * 16);
   auto pp = static_cast<__nv_bfloat16*>(p);
   auto gg = static_cast<const __nv_bfloat16*>(g);
   auto mm = static_cast<__nv_bfloat16*>(m);
