@@ -41,7 +41,11 @@ class Health:
     self.beat(0)
 
   def beat(self, step: int) -> None:
-    self.store.set(f"hb/{self.rank}", f"{int(step)}")
+    try:
+      self.store.set(f"hb/{self.rank}", f"{int(step)}")
+    except Exception as e:
+      raise PeerLost(f"the rendezvous store is unreachable ({type(e).__name__}): the rank that hosts it has left "
+                     "the job") from e
 
   def fail(self, reason: str) -> None:
     """Announce that this rank is leaving the job; never raises (it runs inside exception handlers)."""
@@ -51,6 +55,16 @@ class Health:
       pass
 
   def check(self) -> None:
+    try:
+      self._check()
+    except (PeerLost, PeerStalled):
+      raise
+    except Exception as e:
+      # the store lives in rank 0's process: when it cannot be reached any more, that process is gone
+      raise PeerLost(f"the rendezvous store is unreachable ({type(e).__name__}): the rank that hosts it has left "
+                     "the job") from e
+
+  def _check(self) -> None:
     now = time.monotonic()
     for r in range(self.world):
       if r == self.rank:

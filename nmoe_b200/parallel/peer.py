@@ -16,6 +16,27 @@ import torch.distributed as dist
 from ..ops import _lib as L
 
 
+class PeerExchangeError(RuntimeError):
+  """A rank did not take part in the exchange of peer-memory handles (it exited, or stalled past the group timeout)."""
+
+
+def exchange_handles(handle: bytes, group: Optional[dist.ProcessGroup] = None) -> List[bytes]:
+  """All-gather one opaque handle per rank.  Any failure of the collective -- a peer that exited before the
+  exchange, a peer that never arrives within the process-group timeout -- is raised as PeerExchangeError on the
+  ranks that did show up, so that start-up ends with a message instead of a hang."""
+  world = dist.get_world_size(group)
+  gathered: List[Optional[bytes]] = [None] * world
+  try:
+    dist.all_gather_object(gathered, bytes(handle), group=group)
+  except Exception as e:  # gloo / NCCL surface a lost or late peer as RuntimeError / DistBackendError
+    raise PeerExchangeError(f"peer handle exchange failed on rank {dist.get_rank(group)}: {type(e).__name__}: "
+                            f"{' '.join(str(e).split())[:300]}") from e
+  missing = [r for r, h in enumerate(gathered) if not h]
+  if missing:
+    raise PeerExchangeError(f"peer handle exchange: no handle from ranks {missing}")
+  return [bytes(h) for h in gathered]
+
+
 class PeerSlab:
   """A byte slab carved into named regions at 256-byte-aligned offsets.
 
@@ -55,8 +76,7 @@ class PeerSlab:
     if self.world > 1:
       handle = (ctypes.c_ubyte * 64)()
       L.check(lib.nmoe_peer_get_handle(ctypes.c_void_p(self.base), handle), "peer_get_handle", 0)
-      gathered: List[Optional[bytes]] = [None] * self.world
-      dist.all_gather_object(gathered, bytes(handle), group=group)
+      gathered = exchange_handles(bytes(handle), group)
       for r, h in enumerate(gathered):
         if r == self.rank:
           continue

@@ -107,10 +107,14 @@ def train(cfg: Config) -> dict:
   fp = fingerprint(cfg)
   last_loss = None
   watch = tc_gemm.StatusWatch(device) if (device.type == "cuda" and world > 1) else None
+  from .parallel.health import maybe_health
+  health = maybe_health(rank, world, stall_s=float(os.environ.get("NMOE_PEER_STALL_S", "600")))
   if device.type == "cuda":
     tc_gemm.check_status_collective(device, world)      # nothing latched by set-up before the first step
   try:
     for step_num in range(start_step, cfg.steps):
+      if health is not None:
+        health.check()            # a peer that died or stalled is reported here, before this step's kernels wait on it
       t0 = time.perf_counter()
       inputs, targets = loader.next()
       loader_wait_ms = (time.perf_counter() - t0) * 1000.0
@@ -120,6 +124,8 @@ def train(cfg: Config) -> dict:
         loss = trainer.step(inputs, targets)
       last_loss = loss
       log_training_step(metrics, s, trainer, loss, loader_wait_ms, print0)
+      if health is not None:
+        health.beat(s)
       if watch is not None:
         # multi-rank: peers depend on this rank's flags and buffers, so look at the record every step (copied
         # behind the step's kernels, examined when it has arrived: no host wait)
@@ -148,7 +154,9 @@ def train(cfg: Config) -> dict:
     if tracker is not None:
       tracker.end_run(run_id, "completed", results)
     return results
-  except Exception:
+  except Exception as e:
+    if health is not None:
+      health.fail(f"{type(e).__name__}: {e}")
     if tracker is not None:
       tracker.end_run(run_id, "failed")
     raise

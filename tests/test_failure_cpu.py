@@ -1,0 +1,65 @@
+"""Host-side failure detection, as gloo ranks on CPU: a rank that exits or stalls during the peer-handle exchange,
+a rank that leaves or stalls between steps.  The survivors must end with an error that names what happened, within
+seconds, instead of hanging.  No GPU is involved and nothing is faulted: every failure is made on the host."""
+import os
+import socket
+import subprocess
+import sys
+import time
+
+import pytest
+
+WORKER = os.path.join(os.path.dirname(os.path.abspath(__file__)), "mp_cpu_worker.py")
+
+
+def _free_port() -> int:
+  with socket.socket() as s:
+    s.bind(("127.0.0.1", 0))
+    return s.getsockname()[1]
+
+
+def _run(scenario: str, world: int, limit_s: float = 60.0):
+  port = _free_port()
+  procs = []
+  for r in range(world):
+    env = dict(os.environ, RANK=str(r), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
+               GLOO_SOCKET_IFNAME="lo")
+    procs.append(subprocess.Popen([sys.executable, WORKER, scenario], env=env, stdout=subprocess.PIPE,
+                                  stderr=subprocess.STDOUT, text=True))
+  t0 = time.time()
+  outs = []
+  for p in procs:
+    try:
+      out, _ = p.communicate(timeout=max(1.0, limit_s - (time.time() - t0)))
+    except subprocess.TimeoutExpired:
+      p.kill()
+      out, _ = p.communicate()
+      out += "\nKILLED BY TEST (hang)"
+    outs.append(out)
+  return outs, time.time() - t0
+
+
+def test_healthy_exchange_round_trips():
+  outs, _ = _run("healthy_exchange", 3)
+  assert all("EXCHANGE OK" in o for o in outs), outs
+
+
+@pytest.mark.parametrize("scenario", ["exit_before_exchange", "stall_in_exchange"])
+def test_lost_rank_in_handle_exchange_raises_on_the_others(scenario):
+  outs, took = _run(scenario, 2)
+  assert "DETECTED exchange" in outs[0] and "KILLED BY TEST" not in outs[0], outs
+  assert took < 45, took
+
+
+def test_rank_that_leaves_between_steps_is_seen_before_the_next_launch():
+  outs, took = _run("leave_between_steps", 3)
+  for o in outs[:2]:
+    assert "DETECTED lost" in o and "injected failure after step 3" in o, outs
+  assert took < 30, took
+
+
+def test_rank_that_stalls_between_steps_is_reported():
+  outs, took = _run("stall_between_steps", 3)
+  for o in outs[:2]:
+    assert "DETECTED stalled" in o and "rank 2" in o, outs
+  assert took < 30, took
