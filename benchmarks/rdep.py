@@ -52,6 +52,9 @@ def main():
   ap.add_argument("--iters", type=int, default=10)
   ap.add_argument("--warmup", type=int, default=3)
   ap.add_argument("--capacity-factor", type=float, default=2.0)
+  ap.add_argument("--detail", action="store_true",
+                  help="unfused return only: also time the down GEMM, the push kernel, the flag wait and the K-way sum, "
+                       "with a barrier before the push so that rank skew does not count as push time")
   a = ap.parse_args()
 
   world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -98,8 +101,10 @@ def main():
       out = torch.empty_like(x)
       remote_pairs = int(((eid // n_local) != rank).sum().item())
       ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(a.iters)]
+      dv = [[torch.cuda.Event(enable_timing=True) for _ in range(5)] for _ in range(a.iters)]
+      detail = a.detail and not rd.fused_return
 
-      def one(marks):
+      def one(marks, dmarks=None):
         if marks:
           marks[0].record()
         plan = rd.plan(eid)
@@ -119,9 +124,15 @@ def main():
         if marks:
           marks[2].record()
         if not rd.fused_return:      # NMOE_RDEP_FUSED_RETURN=0: GEMM into a local buffer, then a separate push kernel
+          if dmarks:
+            dmarks[0].record()
           y = (gg(aq, asf, wq[2], wq[3], plan.tile_expert, plan.n_m_tiles) if quantised
                else G.grouped_gemm(act, W2, plan.tile_expert, plan.n_m_tiles, align256=rd.align == 256))
-          rd.push_and_reduce(y, plan, True, None, out)
+          if dmarks:
+            dmarks[1].record()
+            barrier()                      # every rank starts its push together
+            dmarks[2].record()
+          rd.push_and_reduce(y, plan, True, None, out, marks=dmarks[3:5] if dmarks else None)
         else:
           if quantised:
             gg(aq, asf, wq[2], wq[3], plan.tile_expert, plan.n_m_tiles, push=rd.push_args(True))
@@ -139,7 +150,7 @@ def main():
       for it in range(a.iters):
         flush.zero_()
         barrier()
-        plan = one(ev[it])
+        plan = one(ev[it], dv[it] if detail else None)
       barrier()
       G.check_status()
       rows_here = int(plan.offs_pad[-1].item())
@@ -160,9 +171,20 @@ def main():
       except (OSError, KeyError):
         pass
       ret_floor_us = max(2.0 * rows_here * H * F / peak, remote_pairs * 2 * H / 770e9) * 1e6
+      extra = {}
+      if detail:
+        dt = torch.tensor([[d[0].elapsed_time(d[1]), d[2].elapsed_time(d[3]), d[3].elapsed_time(d[4]),
+                            d[4].elapsed_time(e[3])] for d, e in zip(dv, ev)], device=dev).mean(0) * 1e3
+        if world > 1:
+          dist.all_reduce(dt, op=dist.ReduceOp.MAX)
+        g2, pu, wa, re = dt.tolist()
+        extra = {"detail_us": {"gemm2": round(g2, 1), "push": round(pu, 1), "flag_wait": round(wa, 1),
+                               "reduce": round(re, 1)},
+                 "push_gbs_rank0": round(remote_pairs * 2 * H / (pu * 1e-6) / 1e9, 1) if world > 1 else 0.0,
+                 "push_impl": "bulk" if rd.push_impl else "st.v4"}
       if rank == 0:
         print(json.dumps({
-          "bench": "rdep", "n_gpus": world, "dtype": a.dtype, "routing": a.routing, "tokens_per_rank": T,
+          "bench": "rdep", **extra, "n_gpus": world, "dtype": a.dtype, "routing": a.routing, "tokens_per_rank": T,
           "hidden": H, "inter": F, "experts": E, "topk": K, "padded_rows_rank0": rows_here,
           "dispatch_us": round(d_us, 1), "gemm13_us": round(g_us, 1), "gemm2_ret_us": round(r_us, 1),
           "total_us": round(d_us + g_us + r_us, 1),

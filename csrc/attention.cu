@@ -44,6 +44,10 @@ struct AttnParams {
   int q_hs, k1_hs, k1_off, k1_chunks, k2_hs, k2_off, v_hs, v_off;
   float scale_log2;
   const float* sinks;
+  // optional token-level sparsity: bit k of word row (b*S + q)*mask_words + k/32 set = query q may attend key k
+  // (ANDed with the causal / window rule); shared by all heads.  mask_words = 2 * ceil(S / 64).
+  const uint32_t* mask;
+  int mask_words;
   __nv_bfloat16* O;
   float* lse;
   StatusRecord* status;
@@ -271,6 +275,15 @@ k_attn_fwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       uint32_t r[ATT_BN];
       tmem_ld_32x32b_x32(s_addr, r);
       tmem_ld_32x32b_x32(s_addr + 32, r + 32);
+      uint32_t mw0 = 0xffffffffu, mw1 = 0xffffffffu;
+      if (p.mask != nullptr) {
+        if (row < p.S) {
+          const uint32_t* mr = p.mask + (static_cast<size_t>(b) * p.S + row) * p.mask_words + (k0 >> 5);
+          mw0 = __ldg(mr); mw1 = __ldg(mr + 1);
+        } else {
+          mw0 = mw1 = 0u;
+        }
+      }
       tmem_ld_wait();
       float mx = -INFINITY;
       if (need_mask) {
@@ -279,6 +292,11 @@ k_attn_fwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
           const int j = k0 + t;
           if (j > row || j >= p.S || (p.window > 0 && j <= row - p.window)) r[t] = 0xff800000u;   // -inf
         }
+      }
+      if (p.mask != nullptr) {
+#pragma unroll
+        for (int t = 0; t < ATT_BN; ++t)
+          if (!(((t < 32 ? mw0 : mw1) >> (t & 31)) & 1u)) r[t] = 0xff800000u;
       }
 #pragma unroll
       for (int t = 0; t < ATT_BN; ++t) mx = fmaxf(mx, __uint_as_float(r[t]));
@@ -411,11 +429,27 @@ using namespace nmoe;
 // (a multiple of 8) and the *_hs / *_off arguments place a head's columns inside a row (see AttnParams).
 // o [B,S,Hq,Dv] contiguous; lse [B,Hq,S] fp32 (optional); sinks [Hq] fp32 raw logits (optional);
 // window 0 = full causal.  Supported head dims (Dqk, Dv): (192,128), (128,128), (64,64).
+// mask: optional [B, S, 2*ceil(S/64)] uint32 bit rows (see AttnParams), shared by all heads.
+extern "C" int nmoe_attn_fwd_masked(const void* q, int q_row, int q_hs, const void* k1, int k1_row, int k1_hs, int k1_off,
+                                    int k1_chunks, const void* k2, int k2_row, int k2_hs, int k2_off, const void* v,
+                                    int v_row, int v_hs, int v_off, void* o, float* lse, const float* sinks,
+                                    const void* mask, int B, int S, int Hq, int Hkv, int Dqk, int Dv, int window,
+                                    float scale, void* status, cudaStream_t st);
+
 extern "C" int nmoe_attn_fwd_ex(const void* q, int q_row, int q_hs, const void* k1, int k1_row, int k1_hs, int k1_off,
                                 int k1_chunks, const void* k2, int k2_row, int k2_hs, int k2_off, const void* v,
                                 int v_row, int v_hs, int v_off, void* o, float* lse, const float* sinks, int B, int S,
                                 int Hq, int Hkv, int Dqk, int Dv, int window, float scale, void* status,
                                 cudaStream_t st) {
+  return nmoe_attn_fwd_masked(q, q_row, q_hs, k1, k1_row, k1_hs, k1_off, k1_chunks, k2, k2_row, k2_hs, k2_off, v, v_row,
+                              v_hs, v_off, o, lse, sinks, nullptr, B, S, Hq, Hkv, Dqk, Dv, window, scale, status, st);
+}
+
+extern "C" int nmoe_attn_fwd_masked(const void* q, int q_row, int q_hs, const void* k1, int k1_row, int k1_hs, int k1_off,
+                                    int k1_chunks, const void* k2, int k2_row, int k2_hs, int k2_off, const void* v,
+                                    int v_row, int v_hs, int v_off, void* o, float* lse, const float* sinks,
+                                    const void* mask, int B, int S, int Hq, int Hkv, int Dqk, int Dv, int window,
+                                    float scale, void* status, cudaStream_t st) {
   if (B == 0 || S == 0) return 0;
   if (Hq % Hkv != 0) return -1;
   if ((q_row | k1_row | k2_row | v_row) % 8 != 0) return -3;
@@ -425,6 +459,7 @@ extern "C" int nmoe_attn_fwd_ex(const void* q, int q_row, int q_hs, const void* 
   p.v_hs = v_hs; p.v_off = v_off;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.sinks = sinks; p.O = static_cast<__nv_bfloat16*>(o); p.lse = lse; p.status = static_cast<StatusRecord*>(status);
+  p.mask = static_cast<const uint32_t*>(mask); p.mask_words = 2 * ((S + 63) / 64);
   CUtensorMap tq, tk, tk2, tv;
   const uint64_t rows = static_cast<uint64_t>(B) * S;
   int rc = attn_map(&tq, q, q_row, rows, static_cast<uint64_t>(q_row) * 2, ATT_BM);

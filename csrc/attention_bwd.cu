@@ -42,6 +42,11 @@ struct AttnBwdParams {
   float scale, scale_log2;
   const float* lse;                        // [B, Hq, S] natural log
   const float* delta;                      // [B, Hq, S]
+  // optional token-level sparsity, as in the forward: mask[(b*S + q)*mask_words + k/32] bit k%32, and its
+  // transpose mask_t[(b*S + k)*mask_words + q/32] bit q%32 (the dK/dV kernel owns a key per thread)
+  const uint32_t* mask;
+  const uint32_t* mask_t;
+  int mask_words;
   // outputs: one slot per QUERY head (the caller sums a GQA group or a shared rotary key);
   // *_row = row length in elements, *_hs = per-query-head stride, *_off = first column.
   __nv_bfloat16* dQ;  int dq_row, dq_hs;
@@ -293,6 +298,9 @@ k_attn_bwd_dq(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       uint32_t s[32], dp[32], pk[16];
       tmem_ld_32x32b_x32(s_addr, s);
       tmem_ld_32x32b_x32(dp_addr, dp);
+      uint32_t mw = 0xffffffffu;
+      if (p.mask != nullptr)
+        mw = row_ok ? __ldg(p.mask + (static_cast<size_t>(b) * p.S + row) * p.mask_words + (k0 >> 5)) : 0u;
       tmem_ld_wait();
 #pragma unroll
       for (int t = 0; t < 32; t += 2) {
@@ -302,6 +310,8 @@ k_attn_bwd_dq(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           if (masked(row, k0 + t, p.S, p.window)) p0 = 0.f;
           if (masked(row, k0 + t + 1, p.S, p.window)) p1 = 0.f;
         }
+        if (!((mw >> t) & 1u)) p0 = 0.f;
+        if (!((mw >> (t + 1)) & 1u)) p1 = 0.f;
         const float d0 = p0 * (__uint_as_float(dp[t]) - dl) * p.scale;
         const float d1 = p1 * (__uint_as_float(dp[t + 1]) - dl) * p.scale;
         pk[t >> 1] = pack_bf16x2(d0, d1);
@@ -547,6 +557,12 @@ k_attn_bwd_dkv(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           for (int t = 0; t < 32; ++t)
             if (masked(r0 + t, key, p.S, p.window)) pf[t] = 0.f;
         }
+        if (p.mask_t != nullptr) {
+          const uint32_t mw = key < p.S ? __ldg(p.mask_t + (static_cast<size_t>(b) * p.S + key) * p.mask_words + (r0 >> 5)) : 0u;
+#pragma unroll
+          for (int t = 0; t < 32; ++t)
+            if (!((mw >> t) & 1u)) pf[t] = 0.f;
+        }
 #pragma unroll
         for (int t = 0; t < 32; t += 2) pk[t >> 1] = pack_bf16x2(pf[t], pf[t + 1]);
         bwd_tmem_st_x16(s_addr, pk);
@@ -684,13 +700,33 @@ using namespace nmoe;
 // QUERY head: dq [rows, dq_row] at h*dq_hs; dk1 / dk2 / dv likewise with a first-column offset.
 // args: 17 ints of output addressing packed as an array to keep the signature readable:
 //   {dq_row, dq_hs, dk1_row, dk1_hs, dk1_off, dk2_row, dk2_hs, dk2_off, dv_row, dv_hs, dv_off}
+// mask / mask_t: optional bit rows [B, S, 2*ceil(S/64)] (query-major and key-major), as in the forward.
+extern "C" int nmoe_attn_bwd_masked(const void* q, int q_row, int q_hs, const void* k1, int k1_row, int k1_hs, int k1_off,
+                                    int k1_chunks, const void* k2, int k2_row, int k2_hs, int k2_off, const void* v,
+                                    int v_row, int v_hs, int v_off, const void* o, const void* d_o, const float* lse,
+                                    float* delta, void* dq, void* dk1, void* dk2, void* dv, const int* out_addr,
+                                    const void* mask, const void* mask_t, int B, int S, int Hq, int Hkv, int Dqk, int Dv,
+                                    int window, float scale, void* status, cudaStream_t st);
+
 extern "C" int nmoe_attn_bwd_ex(const void* q, int q_row, int q_hs, const void* k1, int k1_row, int k1_hs, int k1_off,
                                 int k1_chunks, const void* k2, int k2_row, int k2_hs, int k2_off, const void* v,
                                 int v_row, int v_hs, int v_off, const void* o, const void* d_o, const float* lse,
                                 float* delta, void* dq, void* dk1, void* dk2, void* dv, const int* out_addr, int B,
                                 int S, int Hq, int Hkv, int Dqk, int Dv, int window, float scale, void* status,
                                 cudaStream_t st) {
+  return nmoe_attn_bwd_masked(q, q_row, q_hs, k1, k1_row, k1_hs, k1_off, k1_chunks, k2, k2_row, k2_hs, k2_off, v, v_row,
+                              v_hs, v_off, o, d_o, lse, delta, dq, dk1, dk2, dv, out_addr, nullptr, nullptr, B, S, Hq,
+                              Hkv, Dqk, Dv, window, scale, status, st);
+}
+
+extern "C" int nmoe_attn_bwd_masked(const void* q, int q_row, int q_hs, const void* k1, int k1_row, int k1_hs, int k1_off,
+                                    int k1_chunks, const void* k2, int k2_row, int k2_hs, int k2_off, const void* v,
+                                    int v_row, int v_hs, int v_off, const void* o, const void* d_o, const float* lse,
+                                    float* delta, void* dq, void* dk1, void* dk2, void* dv, const int* out_addr,
+                                    const void* mask, const void* mask_t, int B, int S, int Hq, int Hkv, int Dqk, int Dv,
+                                    int window, float scale, void* status, cudaStream_t st) {
   if (B == 0 || S == 0) return 0;
+  if ((mask == nullptr) != (mask_t == nullptr)) return -4;
   if (Hq % Hkv != 0) return -1;
   if ((q_row | k1_row | k2_row | v_row) % 8 != 0) return -3;
   for (int i = 0; i < 11; ++i)
@@ -701,6 +737,8 @@ extern "C" int nmoe_attn_bwd_ex(const void* q, int q_row, int q_hs, const void* 
   p.v_hs = v_hs; p.v_off = v_off; p.do_hs = Dv;
   p.scale = scale; p.scale_log2 = scale * kLog2e;
   p.lse = lse; p.delta = delta;
+  p.mask = static_cast<const uint32_t*>(mask); p.mask_t = static_cast<const uint32_t*>(mask_t);
+  p.mask_words = 2 * ((S + 63) / 64);
   p.dQ = static_cast<__nv_bfloat16*>(dq); p.dq_row = out_addr[0]; p.dq_hs = out_addr[1];
   p.dK1 = static_cast<__nv_bfloat16*>(dk1); p.dk1_row = out_addr[2]; p.dk1_hs = out_addr[3]; p.dk1_off = out_addr[4];
   p.dK2 = static_cast<__nv_bfloat16*>(dk2 ? dk2 : dk1); p.dk2_row = out_addr[5]; p.dk2_hs = out_addr[6]; p.dk2_off = out_addr[7];

@@ -6,10 +6,24 @@
 // which is what keeps NVLink packets full.
 #pragma once
 #include <stdint.h>
+#include <stdlib.h>
 
 #include "ptx.cuh"
 
 namespace nmoe {
+
+// Host side: which form of the fused-return epilogue a launch uses.  NMOE_PUSH_BULK (bf16 GEMMs, default 1 = bulk
+// copies of 256-byte row segments) and NMOE_PUSH_BULK_MX (block-scaled GEMM, default 0 = 16-byte stores: its single
+// accumulator leaves the epilogue exposed, and there the 128-byte copies measured slower than the stores).
+inline int epi_push_bulk_enabled(bool mx = false) {
+  static int v[2] = {-1, -1};
+  int& r = v[mx ? 1 : 0];
+  if (r < 0) {
+    const char* e = getenv(mx ? "NMOE_PUSH_BULK_MX" : "NMOE_PUSH_BULK");
+    r = e != nullptr ? (e[0] != '0' ? 1 : 0) : (mx ? 0 : 1);
+  }
+  return r;
+}
 
 constexpr int kEpiStageBytesPerWarp = 32 * 128;
 
@@ -38,6 +52,57 @@ NMOE_DEVICE void warp_store_rows_64cols(uint8_t* stage, const uint32_t* r, float
     if (dst != 0ull) st_relaxed_sys_v4(reinterpret_cast<int4*>(dst) + j, v);
   }
   __syncwarp();
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Copy-engine variant: the lane converts its row segment into its own shared-memory staging row and then hands the
+// whole segment to the bulk-copy (TMA) unit with one `cp.async.bulk.global.shared::cta`.  The warp is free again as
+// soon as the copy is issued; the bytes (most of them bound for another GPU) travel while the next accumulator
+// columns are being converted, and the number of stores in flight no longer depends on how many warps the epilogue
+// has.  SEG_BYTES = 256 stages 128 columns per copy, 128 stages 64 columns (for kernels short of shared memory).
+//
+// Staging rows are laid out so that the 32 lanes' 16-byte stores spread over all banks:
+//   128-byte segments: row stride 144 bytes;  256-byte segments: rows in pairs, 528 bytes per pair.
+// Every row start is 16-byte aligned, as the bulk copy requires.
+template <int SEG_BYTES>
+struct EpiBulk {
+  static_assert(SEG_BYTES == 128 || SEG_BYTES == 256, "segment size");
+  static constexpr int kWarpBytes = SEG_BYTES == 128 ? 32 * 144 : 16 * 528;
+  static constexpr int kSegCols = SEG_BYTES / 2;
+  static NMOE_DEVICE uint8_t* row(uint8_t* warp_stage, int lane) {
+    return SEG_BYTES == 128 ? warp_stage + lane * 144 : warp_stage + (lane >> 1) * 528 + (lane & 1) * 256;
+  }
+};
+
+// 64 fp32 accumulator values of this lane's row -> bf16 (times scale) at byte offset `off` of its staging row.
+NMOE_DEVICE void stage_64cols(uint8_t* srow, int off, const uint32_t* r, float scale) {
+  int4* d = reinterpret_cast<int4*>(srow + off);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    int4 v;
+    v.x = pack_bf16x2(__uint_as_float(r[8 * j]) * scale, __uint_as_float(r[8 * j + 1]) * scale);
+    v.y = pack_bf16x2(__uint_as_float(r[8 * j + 2]) * scale, __uint_as_float(r[8 * j + 3]) * scale);
+    v.z = pack_bf16x2(__uint_as_float(r[8 * j + 4]) * scale, __uint_as_float(r[8 * j + 5]) * scale);
+    v.w = pack_bf16x2(__uint_as_float(r[8 * j + 6]) * scale, __uint_as_float(r[8 * j + 7]) * scale);
+    d[j] = v;
+  }
+}
+
+// Issue the copy of this lane's staged segment to dst (null: the row is padding, nothing is sent) and close the
+// thread's bulk group.  The caller must have made its staging writes visible to the copy unit (epi_bulk_fence).
+NMOE_DEVICE void epi_bulk_fence() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+NMOE_DEVICE void epi_bulk_store(void* dst, const uint8_t* srow, uint32_t bytes) {
+  if (dst != nullptr)
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                 ::"l"(dst), "r"(smem_u32(srow)), "r"(bytes) : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// Before a lane rewrites its staging row: its earlier copies have finished READING shared memory.
+NMOE_DEVICE void epi_bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// Before the kernel ends (and before any flag that publishes the rows): the lane's copies are complete.
+NMOE_DEVICE void epi_bulk_drain() {
+  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+  asm volatile("fence.proxy.async;" ::: "memory");
 }
 
 }  // namespace nmoe

@@ -56,6 +56,7 @@ struct GemmParams {
   float* peer_retg[8];
   const float* rowval;
   int push_use_gate;
+  int push_bulk;               // 1: the fused return hands 256-byte row segments to the bulk-copy unit
   // Mode 3 (sparse-attention indexer): rows of A are keys, columns of B are (query, head) pairs; the epilogue
   // writes C[query][key] = sum_head idx_w[query*heads + head] * relu(acc), -inf above the diagonal when causal.
   const float* idx_w;
@@ -128,7 +129,9 @@ struct GemmSmem {
   static constexpr int kStageA = BM * BK * 2;
   static constexpr int kStageB = BN * BK * 2;
   static constexpr int kStages = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
-  static constexpr int kEpiStage = 4 * kEpiStageBytesPerWarp;      // transposing store of the fused-return epilogue
+  // staging of the fused-return epilogue: bulk copies of 256-byte row segments (or the 4 KB transposing store)
+  static constexpr int kEpiWarp = EpiBulk<256>::kWarpBytes > kEpiStageBytesPerWarp ? EpiBulk<256>::kWarpBytes : kEpiStageBytesPerWarp;
+  static constexpr int kEpiStage = 4 * kEpiWarp;
   static constexpr int kBytes = kStages * (kStageA + kStageB) + kEpiStage + 1024 /*align*/ + 256 /*barriers*/;
 };
 
@@ -291,6 +294,7 @@ k_gemm_bf16(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     const int q = warp & 3;                  // TMEM lane quadrant this warp may read
     int acc = 0;
     uint32_t acc_phase = 0;
+    bool used_bulk = false;
     TileCoord tc;
     const int m_limit = (MODE == 1) ? m_tiles * BM : p.M;
     for (int t = blockIdx.x; decode_tile<BN, MODE>(p, t, m_tiles, n_tiles, tc); t += gridDim.x) {
@@ -301,7 +305,8 @@ k_gemm_bf16(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       float push_gate = 1.f;
       if (MODE == 1 && p.row_meta != nullptr && row_ok) {
         const int4 mv = __ldg(p.row_meta + row);
-        row_ok = mv.w != 0;
+        // a stale or torn meta record must not become a wild store into a peer: unknown source ranks are skipped
+        row_ok = mv.w != 0 && static_cast<unsigned>(mv.x) < 8u && p.peer_ret[mv.x & 7] != nullptr && mv.y >= 0;
         if (row_ok) {
           push_dst = p.peer_ret[mv.x] + static_cast<long long>(mv.y) * p.ldc;
           if (p.push_use_gate) push_gate = __int_as_float(mv.z);
@@ -320,9 +325,30 @@ k_gemm_bf16(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         }
         tc_fence_after_sync();
       }
-      if (MODE == 1 && p.row_meta != nullptr && have_acc && (p.N & 63) == 0 && (p.ldc & 7) == 0) {
+      if (MODE == 1 && p.row_meta != nullptr && have_acc && p.push_bulk && (p.N & 127) == 0 && (p.ldc & 7) == 0) {
+        // fused return through the copy unit: 128 columns (256 bytes) of this lane's row per bulk copy
+        uint8_t* srow = EpiBulk<256>::row(epi_stage + (warp - 2) * S::kEpiWarp, lane);
+        __nv_bfloat16* dst0 = (row_ok && push_dst != nullptr) ? push_dst : nullptr;
+#pragma unroll 1
+        for (int c = 0; c < BN / 64; ++c) {
+          const int col = n0 + c * 64;
+          if (col >= p.N) break;               // uniform over the warp
+          uint32_t r[64];
+          const uint32_t ta = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + c * 64;
+          tmem_ld_32x32b_x32(ta, r);
+          tmem_ld_32x32b_x32(ta + 32, r + 32);
+          if ((c & 1) == 0) epi_bulk_wait_read();
+          tmem_ld_wait();
+          stage_64cols(srow, (c & 1) * 128, r, push_gate);
+          if (c & 1) {
+            epi_bulk_fence();
+            epi_bulk_store(dst0 ? dst0 + (col - 64) : nullptr, srow, 256);
+          }
+        }
+        used_bulk = true;
+      } else if (MODE == 1 && p.row_meta != nullptr && have_acc && (p.N & 63) == 0 && (p.ldc & 7) == 0) {
         // fused return, coalesced: 64 columns (128 bytes) of 4 rows per store instruction
-        uint8_t* stage = epi_stage + (warp - 2) * kEpiStageBytesPerWarp;
+        uint8_t* stage = epi_stage + (warp - 2) * S::kEpiWarp;
 #pragma unroll 1
         for (int c = 0; c < BN / 64; ++c) {
           const int col = n0 + c * 64;
@@ -453,6 +479,7 @@ k_gemm_bf16(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
       }
     }
+    if (used_bulk) epi_bulk_drain();         // this lane's row copies have been written before the kernel ends
   }
 
   // Teardown.  After a timeout, give copies in flight a moment to land before the CTA's
@@ -566,6 +593,7 @@ int nmoe_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, l
   p.row_meta = static_cast<const int4*>(row_meta);
   p.rowval = rowval;
   p.push_use_gate = push_use_gate;
+  p.push_bulk = epi_push_bulk_enabled();
   p.idx_w = nullptr; p.idx_heads = 1; p.idx_causal = 0;
   for (int r = 0; r < 8; ++r) {
     p.peer_ret[r] = (row_meta && peer_ret && r < world) ? static_cast<__nv_bfloat16*>(peer_ret[r]) : nullptr;
@@ -613,7 +641,7 @@ int nmoe_dsa_indexer_scores(const void* k, const void* q, const float* w, float*
   p.C = out; p.ldc = ldo; p.out_fp32 = 1; p.accumulate = 0;
   p.b_rows_per_expert = 0;
   p.status = static_cast<StatusRecord*>(status);
-  p.row_meta = nullptr; p.rowval = nullptr; p.push_use_gate = 0;
+  p.row_meta = nullptr; p.rowval = nullptr; p.push_use_gate = 0; p.push_bulk = 0;
   for (int r = 0; r < 8; ++r) { p.peer_ret[r] = nullptr; p.peer_retg[r] = nullptr; }
   p.idx_w = w; p.idx_heads = heads; p.idx_causal = causal;
   CUtensorMap tmA, tmB;

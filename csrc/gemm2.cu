@@ -49,6 +49,7 @@ struct Gemm2Params {
   float* peer_retg[8];
   const float* rowval;
   int push_use_gate;
+  int push_bulk;               // 1: the fused return hands 256-byte row segments to the bulk-copy unit
 };
 
 NMOE_DEVICE uint32_t cluster_ctarank() {
@@ -146,7 +147,9 @@ NMOE_DEVICE bool decode_tile2(const Gemm2Params& p, int t, int m_tiles, int n_ti
 
 constexpr int kG2StageA = G2_BM * G2_BK * 2;
 constexpr int kG2StageB = (G2_BN / 2) * G2_BK * 2;
-constexpr int kG2EpiStage = 4 * kEpiStageBytesPerWarp;            // transposing store of the fused-return epilogue
+// staging of the fused-return epilogue: bulk copies of 256-byte row segments (or the 4 KB transposing store)
+constexpr int kG2EpiWarp = EpiBulk<256>::kWarpBytes > kEpiStageBytesPerWarp ? EpiBulk<256>::kWarpBytes : kEpiStageBytesPerWarp;
+constexpr int kG2EpiStage = 4 * kG2EpiWarp;
 constexpr int kG2SmemBytes = kG2Stages * (kG2StageA + kG2StageB) + kG2EpiStage + 1024 + 256;
 static_assert(kG2SmemBytes <= 232448, "shared memory budget");
 
@@ -288,6 +291,7 @@ k_gemm_bf16_pair(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     Tile2 tc;
     const int m_limit = (MODE == 1) ? m_tiles * 2 * G2_BM : p.M;
     const uint32_t leader_empty0 = mapa_shared(smem_u32(&tmem_empty[0]), 0);
+    bool used_bulk = false;
     for (int t = cluster_id; decode_tile2<MODE>(p, t, m_tiles, n_tiles, tc); t += n_clusters) {
       const int row = tc.m_blk * 2 * G2_BM + static_cast<int>(rank) * G2_BM + q * 32 + lane;
       const int n0 = tc.n_blk * G2_BN;
@@ -298,7 +302,8 @@ k_gemm_bf16_pair(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       float push_gate = 1.f;
       if (MODE == 1 && p.row_meta != nullptr && row_ok) {
         const int4 mv = __ldg(p.row_meta + row);
-        row_ok = mv.w != 0;
+        // a stale or torn meta record must not become a wild store into a peer: unknown source ranks are skipped
+        row_ok = mv.w != 0 && static_cast<unsigned>(mv.x) < 8u && p.peer_ret[mv.x & 7] != nullptr && mv.y >= 0;
         if (row_ok) {
           push_dst = p.peer_ret[mv.x] + static_cast<long long>(mv.y) * p.ldc;
           if (p.push_use_gate) push_gate = __int_as_float(mv.z);
@@ -315,9 +320,30 @@ k_gemm_bf16_pair(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
         tc_fence_after_sync();
       }
-      if (MODE == 1 && p.row_meta != nullptr && have_acc) {
+      if (MODE == 1 && p.row_meta != nullptr && have_acc && p.push_bulk && (p.N & 127) == 0 && (p.ldc & 7) == 0) {
+        // fused return through the copy unit: 128 columns (256 bytes) of this lane's row per bulk copy
+        uint8_t* srow = EpiBulk<256>::row(epi_stage + (warp - 2) * kG2EpiWarp, lane);
+        __nv_bfloat16* dst0 = (row_ok && push_dst != nullptr) ? push_dst : nullptr;
+#pragma unroll 1
+        for (int c = 0; c < G2_BN / 64; ++c) {
+          const int col = n0 + c * 64;
+          if (col >= p.N) break;
+          uint32_t r[64];
+          const uint32_t ta = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * G2_BN + c * 64;
+          tmem_ld_32x32b_x32(ta, r);
+          tmem_ld_32x32b_x32(ta + 32, r + 32);
+          if ((c & 1) == 0) epi_bulk_wait_read();
+          tmem_ld_wait();
+          stage_64cols(srow, (c & 1) * 128, r, push_gate);
+          if (c & 1) {
+            epi_bulk_fence();
+            epi_bulk_store(dst0 ? dst0 + (col - 64) : nullptr, srow, 256);
+          }
+        }
+        used_bulk = true;
+      } else if (MODE == 1 && p.row_meta != nullptr && have_acc) {
         // fused return, coalesced: 64 columns (128 bytes) of 4 rows per store instruction
-        uint8_t* stage = epi_stage + (warp - 2) * kEpiStageBytesPerWarp;
+        uint8_t* stage = epi_stage + (warp - 2) * kG2EpiWarp;
 #pragma unroll 1
         for (int c = 0; c < G2_BN / 64; ++c) {
           const int col = n0 + c * 64;
@@ -394,6 +420,7 @@ k_gemm_bf16_pair(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
       }
     }
+    if (used_bulk) epi_bulk_drain();         // this lane's row copies have been written before the kernel ends
   }
 
   if (*abort_flag) {
@@ -468,6 +495,7 @@ extern "C" int nmoe_gemm_bf16_pair_push(const void* A, const void* B, void* C, i
   p.b_rows_per_expert = (mode == 1) ? (b_mn ? K : N) : 0;
   p.status = static_cast<StatusRecord*>(status);
   p.row_meta = static_cast<const int4*>(row_meta); p.rowval = rowval; p.push_use_gate = push_use_gate;
+  p.push_bulk = epi_push_bulk_enabled();
   for (int r = 0; r < 8; ++r) {
     p.peer_ret[r] = (row_meta && peer_ret && r < world) ? static_cast<__nv_bfloat16*>(peer_ret[r]) : nullptr;
     p.peer_retg[r] = (row_meta && peer_retg && r < world) ? static_cast<float*>(peer_retg[r]) : nullptr;

@@ -51,6 +51,7 @@ struct MxParams {
   const int4* row_meta;
   __nv_bfloat16* peer_ret[8];
   int push_use_gate;
+  int push_bulk;               // 1: the fused return hands 128-byte row segments to the bulk-copy unit
   float alpha;                 // multiplies every output (NVFP4: product of the two per-tensor scales)
   // fused SwiGLU + quantise epilogue (act_q != nullptr): instead of C [rows, N], write the quantised
   // activation [rows, N/2] (E4M3 bytes, or E2M1 nibbles when act_fp4) and its E8M0 scale atoms
@@ -94,10 +95,12 @@ struct MxSmem {
   static constexpr int kStageB = BN * MX_BK;
   static constexpr int kStageSF = kKA * (512 + (BN / 128) * 512);
   static constexpr int kStages = (BN == 256) ? (FMT == 2 ? 3 : 4) : (FMT == 2 ? 5 : 6);
-  static_assert(kStages * (MX_BM * MX_BK + BN * MX_BK + kKA * (512 + (BN / 128) * 512)) + 4 * kEpiStageBytesPerWarp + 1280 <= 232448,
+  // staging of the fused-return epilogue: bulk copies of 128-byte row segments (or the 4 KB transposing store)
+  static constexpr int kEpiWarp = EpiBulk<128>::kWarpBytes > kEpiStageBytesPerWarp ? EpiBulk<128>::kWarpBytes : kEpiStageBytesPerWarp;
+  static_assert(kStages * (MX_BM * MX_BK + BN * MX_BK + kKA * (512 + (BN / 128) * 512)) + 4 * kEpiWarp + 1280 <= 232448,
                 "shared memory budget");
   static constexpr int kAcc = (BN == 256) ? 1 : 2;
-  static constexpr int kEpiStage = 4 * kEpiStageBytesPerWarp;      // transposing store of the fused-return epilogue
+  static constexpr int kEpiStage = 4 * kEpiWarp;
   static constexpr int kBytes = kStages * (kStageA + kStageB + kStageSF) + kEpiStage + 1024 + 256;
 };
 
@@ -278,6 +281,7 @@ k_gemm_mx(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
     const int q = warp & 3;
     int acc = 0;
     uint32_t acc_phase = 0;
+    bool used_bulk = false;
     int m_blk, n_blk, expert;
     const int m_limit = (MODE == 1) ? m_tiles * MX_BM : p.M;
     for (int t = blockIdx.x; mx_decode<BN, MODE>(p, t, m_tiles, n_tiles, m_blk, n_blk, expert); t += gridDim.x) {
@@ -288,7 +292,8 @@ k_gemm_mx(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
       float gate = p.alpha;
       if (MODE == 1 && p.row_meta != nullptr && row_ok) {
         const int4 mv = __ldg(p.row_meta + row);
-        row_ok = mv.w != 0;
+        // a stale or torn meta record must not become a wild store into a peer: unknown source ranks are skipped
+        row_ok = mv.w != 0 && static_cast<unsigned>(mv.x) < 8u && p.peer_ret[mv.x & 7] != nullptr && mv.y >= 0;
         if (row_ok) {
           dst_row = p.peer_ret[mv.x] + static_cast<long long>(mv.y) * p.ldc;
           if (p.push_use_gate) gate = p.alpha * __int_as_float(mv.z);
@@ -302,9 +307,27 @@ k_gemm_mx(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
         break;
       }
       tc_fence_after_sync();
-      if (MODE == 1 && p.row_meta != nullptr && (p.N & 63) == 0 && (p.ldc & 7) == 0) {
+      if (MODE == 1 && p.row_meta != nullptr && p.push_bulk && (p.N & 63) == 0 && (p.ldc & 7) == 0) {
+        // fused return through the copy unit: 64 columns (128 bytes) of this lane's row per bulk copy
+        uint8_t* srow = EpiBulk<128>::row(epi_stage + (warp - 2) * S::kEpiWarp, lane);
+#pragma unroll 1
+        for (int c = 0; c < BN / 64; ++c) {
+          const int col = n0 + c * 64;
+          if (col >= p.N) break;
+          uint32_t r[64];
+          const uint32_t ta = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + c * 64;
+          tmem_ld_32x32b_x32(ta, r);
+          tmem_ld_32x32b_x32(ta + 32, r + 32);
+          epi_bulk_wait_read();
+          tmem_ld_wait();
+          stage_64cols(srow, 0, r, gate);
+          epi_bulk_fence();
+          epi_bulk_store(row_ok ? dst_row + col : nullptr, srow, 128);
+        }
+        used_bulk = true;
+      } else if (MODE == 1 && p.row_meta != nullptr && (p.N & 63) == 0 && (p.ldc & 7) == 0) {
         // fused return, coalesced: 64 columns (128 bytes) of 4 rows per store instruction
-        uint8_t* stage = epi_stage + (warp - 2) * kEpiStageBytesPerWarp;
+        uint8_t* stage = epi_stage + (warp - 2) * S::kEpiWarp;
 #pragma unroll 1
         for (int c = 0; c < BN / 64; ++c) {
           const int col = n0 + c * 64;
@@ -382,6 +405,7 @@ k_gemm_mx(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
       if (lane == 0) mbar_arrive(&tmem_empty[acc]);
       if (++acc == kAcc) { acc = 0; acc_phase ^= 1; }
     }
+    if (used_bulk) epi_bulk_drain();         // this lane's row copies have been written before the kernel ends
   }
 
   if (*abort_flag) {
@@ -451,7 +475,7 @@ extern "C" int nmoe_gemm_mxfp8(const void* A, const void* sfa, const void* B, co
   p.C = static_cast<__nv_bfloat16*>(C); p.ldc = ldc;
   p.sfa = static_cast<const uint8_t*>(sfa); p.sfb = static_cast<const uint8_t*>(sfb);
   p.status = static_cast<StatusRecord*>(status);
-  p.row_meta = static_cast<const int4*>(row_meta); p.push_use_gate = push_use_gate; p.alpha = 1.f; p.act_q = nullptr; p.act_sf = nullptr; p.act_sf_cols = 0; p.act_fp4 = 0;
+  p.row_meta = static_cast<const int4*>(row_meta); p.push_use_gate = push_use_gate; p.push_bulk = epi_push_bulk_enabled(true); p.alpha = 1.f; p.act_q = nullptr; p.act_sf = nullptr; p.act_sf_cols = 0; p.act_fp4 = 0;
   for (int r = 0; r < 8; ++r)
     p.peer_ret[r] = (row_meta && peer_ret && r < world) ? static_cast<__nv_bfloat16*>(peer_ret[r]) : nullptr;
   if (row_meta && mode != 1) return -6;
@@ -481,7 +505,7 @@ extern "C" int nmoe_gemm_mxfp4(const void* A, const void* sfa, const void* B, co
   p.C = static_cast<__nv_bfloat16*>(C); p.ldc = ldc;
   p.sfa = static_cast<const uint8_t*>(sfa); p.sfb = static_cast<const uint8_t*>(sfb);
   p.status = static_cast<StatusRecord*>(status);
-  p.row_meta = static_cast<const int4*>(row_meta); p.push_use_gate = push_use_gate; p.alpha = 1.f; p.act_q = nullptr; p.act_sf = nullptr; p.act_sf_cols = 0; p.act_fp4 = 0;
+  p.row_meta = static_cast<const int4*>(row_meta); p.push_use_gate = push_use_gate; p.push_bulk = epi_push_bulk_enabled(true); p.alpha = 1.f; p.act_q = nullptr; p.act_sf = nullptr; p.act_sf_cols = 0; p.act_fp4 = 0;
   for (int r = 0; r < 8; ++r)
     p.peer_ret[r] = (row_meta && peer_ret && r < world) ? static_cast<__nv_bfloat16*>(peer_ret[r]) : nullptr;
   if (row_meta && mode != 1) return -6;
@@ -511,7 +535,7 @@ extern "C" int nmoe_gemm_nvfp4(const void* A, const void* sfa, const void* B, co
   p.C = static_cast<__nv_bfloat16*>(C); p.ldc = ldc;
   p.sfa = static_cast<const uint8_t*>(sfa); p.sfb = static_cast<const uint8_t*>(sfb);
   p.status = static_cast<StatusRecord*>(status);
-  p.row_meta = nullptr; p.push_use_gate = 0; p.alpha = alpha; p.act_q = nullptr; p.act_sf = nullptr; p.act_sf_cols = 0; p.act_fp4 = 0;
+  p.row_meta = nullptr; p.push_use_gate = 0; p.push_bulk = 0; p.alpha = alpha; p.act_q = nullptr; p.act_sf = nullptr; p.act_sf_cols = 0; p.act_fp4 = 0;
   for (int r = 0; r < 8; ++r) p.peer_ret[r] = nullptr;
   CUtensorMap tmA, tmB;
   int rc = mx_cached_map(&tmA, A, K / 2, a_rows, K / 2, MX_BK, MX_BM);
@@ -541,7 +565,7 @@ extern "C" int nmoe_gemm_mx_swiglu_quant(const void* A, const void* sfa, const v
   p.C = nullptr; p.ldc = N;
   p.sfa = static_cast<const uint8_t*>(sfa); p.sfb = static_cast<const uint8_t*>(sfb);
   p.status = static_cast<StatusRecord*>(status);
-  p.row_meta = nullptr; p.push_use_gate = 0; p.alpha = 1.f;
+  p.row_meta = nullptr; p.push_use_gate = 0; p.push_bulk = 0; p.alpha = 1.f;
   for (int r = 0; r < 8; ++r) p.peer_ret[r] = nullptr;
   p.act_q = static_cast<uint8_t*>(act_q); p.act_sf = static_cast<uint8_t*>(act_sf);
   p.act_sf_cols = (((N / 2) / 32) + 3) & ~3; p.act_fp4 = fp4;

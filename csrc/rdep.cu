@@ -409,6 +409,8 @@ struct PushArgs {
   __nv_bfloat16* peer_ret[kMaxRanks];
   float* peer_retg[kMaxRanks];      // optional per-row scalar return (gate gradients)
   const float* rowval;              // optional per-row scalar to return
+  int world, n_pairs;               // valid ranges of meta.src_rank and meta.tok_slot (checked before every store)
+  StatusRecord* status;
 };
 __global__ void __launch_bounds__(256) k_rdep_push(const PushArgs a) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -418,6 +420,11 @@ __global__ void __launch_bounds__(256) k_rdep_push(const PushArgs a) {
     const int4 mv = __ldg(reinterpret_cast<const int4*>(a.meta + r));
     if (mv.w == 0) continue;
     const int src = mv.x, ts = mv.y;
+    if (src < 0 || src >= a.world || ts < 0 || ts >= a.n_pairs) {
+      // a stale or torn meta record (possible after a wait that ran out) must not become a wild store into a peer
+      if (lane == 0) report_status(a.status, kStatusBadIndex, 430, r, src);
+      continue;
+    }
     const float g = a.use_gate ? __int_as_float(mv.z) : 1.f;
     if (a.y != nullptr) {
       const int4* s = reinterpret_cast<const int4*>(a.y + static_cast<size_t>(r) * a.H);
@@ -447,6 +454,96 @@ __global__ void __launch_bounds__(256) k_rdep_push(const PushArgs a) {
     }
     if (lane == 0 && a.rowval != nullptr) a.peer_retg[src][ts] = a.rowval[r];
   }
+  __threadfence_system();
+}
+
+// Owner side, copy-engine variant of k_rdep_push: every row chunk travels global -> shared -> peer global as two
+// bulk asynchronous copies (the TMA unit moves the bytes; the warp only issues them), so one lane keeps kilobytes in
+// flight per instruction instead of 16 bytes per store.  A warp owns a ring of kPushSlots shared-memory slots of
+// kPushChunk bytes; rows longer than a slot go in chunks.  With use_gate the warp scales the chunk in shared memory
+// between the two copies.  Rows whose meta names a source rank or a (token, slot) outside the valid range are skipped
+// and reported (a stale or torn meta record must not become a wild store into a peer's memory).
+constexpr int kPushChunk = 4096;
+constexpr int kPushSlots = 3;
+constexpr int kPushWarps = 8;
+
+NMOE_DEVICE void bulk_g2s(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+NMOE_DEVICE void bulk_s2g(void* gdst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+               ::"l"(gdst), "r"(smem_u32(smem_src)), "r"(bytes) : "memory");
+}
+
+__global__ void __launch_bounds__(kPushWarps * 32) k_rdep_push_bulk(const PushArgs a) {
+  extern __shared__ __align__(128) uint8_t push_smem[];
+  __shared__ uint64_t bars[kPushWarps * kPushSlots];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  uint8_t* slots = push_smem + static_cast<size_t>(warp) * kPushSlots * kPushChunk;
+  uint64_t* bar = bars + warp * kPushSlots;
+  if (lane == 0) {
+    for (int s = 0; s < kPushSlots; ++s) mbar_init(&bar[s], 1);
+    mbar_fence_init();
+  }
+  __syncwarp();
+  const int rows = min(*a.n_m_tiles * 128, a.n_rows_cap);
+  const int row_bytes = a.H * 2;
+  const int chunks = (row_bytes + kPushChunk - 1) / kPushChunk;
+  int slot = 0;
+  uint32_t phase_bits = 0;       // bit s = parity of the next completion of slot s
+  bool ok = true;
+  for (int r = blockIdx.x * kPushWarps + warp; ok && r < rows; r += gridDim.x * kPushWarps) {
+    const int4 mv = __ldg(reinterpret_cast<const int4*>(a.meta + r));
+    if (mv.w == 0) continue;
+    const int src = mv.x, ts = mv.y;
+    if (src < 0 || src >= a.world || ts < 0 || ts >= a.n_pairs) {
+      if (lane == 0) report_status(a.status, kStatusBadIndex, 430, r, src);
+      continue;
+    }
+    const float g = a.use_gate ? __int_as_float(mv.z) : 1.f;
+    if (a.y != nullptr) {
+      const uint8_t* srow = reinterpret_cast<const uint8_t*>(a.y + static_cast<size_t>(r) * a.H);
+      uint8_t* drow = reinterpret_cast<uint8_t*>(a.peer_ret[src] + static_cast<size_t>(ts) * a.H);
+      for (int c = 0; c < chunks; ++c) {
+        const int off = c * kPushChunk;
+        const uint32_t nb = static_cast<uint32_t>(min(kPushChunk, row_bytes - off));
+        uint8_t* sm = slots + slot * kPushChunk;
+        if (lane == 0) {
+          // the slot is free once the bulk store issued kPushSlots chunks ago has read it
+          asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(kPushSlots - 1) : "memory");
+          mbar_expect_tx(&bar[slot], nb);
+          bulk_g2s(sm, srow + off, nb, &bar[slot]);
+        }
+        __syncwarp();
+        if (!mbar_wait(&bar[slot], (phase_bits >> slot) & 1u)) {
+          if (lane == 0) report_status(a.status, kStatusWaitTimeout, 431, r, c);
+          ok = false;
+          break;
+        }
+        phase_bits ^= 1u << slot;
+        if (a.use_gate) {
+          for (uint32_t i = lane * 16; i < nb; i += 32 * 16) {
+            int4 o = *reinterpret_cast<const int4*>(sm + i);
+            float2 f0 = unpack_bf16x2(o.x), f1 = unpack_bf16x2(o.y), f2 = unpack_bf16x2(o.z), f3 = unpack_bf16x2(o.w);
+            o.x = pack_bf16x2(f0.x * g, f0.y * g); o.y = pack_bf16x2(f1.x * g, f1.y * g);
+            o.z = pack_bf16x2(f2.x * g, f2.y * g); o.w = pack_bf16x2(f3.x * g, f3.y * g);
+            *reinterpret_cast<int4*>(sm + i) = o;
+          }
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          bulk_s2g(drow + off, sm, nb);
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
+        if (++slot == kPushSlots) slot = 0;
+      }
+    }
+    if (lane == 0 && a.rowval != nullptr) a.peer_retg[src][ts] = a.rowval[r];
+  }
+  if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // all bytes written before the kernel ends
+  __syncwarp();
   __threadfence_system();
 }
 
@@ -619,10 +716,14 @@ int nmoe_rdep_wait(const void* my_flags, int world, unsigned epoch, unsigned bud
   return 0;
 }
 
+// impl 0: per-lane 16-byte system-scope stores; impl 1: bulk asynchronous copies through shared memory.
+// n_pairs = T*K of the SOURCE ranks (every rank holds the same number of tokens per step).
 int nmoe_rdep_push(const void* y, const void* meta, const int* n_m_tiles, int cap_rows, int H, int use_gate,
-                   void* const* peer_ret, void* const* peer_retg, const float* rowval, int world, cudaStream_t st) {
+                   void* const* peer_ret, void* const* peer_retg, const float* rowval, int world, int n_pairs,
+                   void* status, int impl, cudaStream_t st) {
   if (world > kMaxRanks || (H % 8) != 0) return -1;
   PushArgs a;
+  a.world = world; a.n_pairs = n_pairs; a.status = static_cast<StatusRecord*>(status);
   a.H = H; a.n_rows_cap = cap_rows; a.use_gate = use_gate;
   a.y = static_cast<const __nv_bfloat16*>(y); a.meta = static_cast<const RdepMeta*>(meta); a.n_m_tiles = n_m_tiles;
   for (int r = 0; r < world; ++r) {
@@ -630,7 +731,18 @@ int nmoe_rdep_push(const void* y, const void* meta, const int* n_m_tiles, int ca
     a.peer_retg[r] = peer_retg ? static_cast<float*>(peer_retg[r]) : nullptr;
   }
   a.rowval = rowval;
-  k_rdep_push<<<148 * 4, 256, 0, st>>>(a);
+  if (impl == 1) {
+    const int smem = kPushWarps * kPushSlots * kPushChunk;
+    static bool configured = false;
+    if (!configured) {
+      cudaError_t e = cudaFuncSetAttribute(k_rdep_push_bulk, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+      if (e != cudaSuccess) return static_cast<int>(e);
+      configured = true;
+    }
+    k_rdep_push_bulk<<<148 * 2, kPushWarps * 32, smem, st>>>(a);
+  } else {
+    k_rdep_push<<<148 * 8, 256, 0, st>>>(a);
+  }
   CHECK_LAUNCH();
   return 0;
 }

@@ -14,6 +14,7 @@ import torch.nn.functional as F
 from torch import nn
 
 from ... import ops
+from ...ops.attention import SparseMask
 from ...ops.indexer import indexer_scores
 from .common import masked_attention
 from .mla import MLA
@@ -61,7 +62,8 @@ class DSA(MLA):
   def forward(self, x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
     B, T, _ = x.shape
     q, k, v = self._qkv(x, cos, sin)
-    causal = torch.tril(torch.ones(T, T, dtype=torch.bool, device=x.device)).view(1, 1, T, T)
+    eager = self.training_mode == "dense_warmup" or not (x.is_cuda and x.dtype == torch.bfloat16)
+    causal = torch.tril(torch.ones(T, T, dtype=torch.bool, device=x.device)).view(1, 1, T, T) if eager else None
     qi, ki, wi = self._idx_inputs(x.detach())
     if self.training_mode == "dense_warmup":
       o = masked_attention(q, k, v, causal, self.softmax_scale)
@@ -70,6 +72,14 @@ class DSA(MLA):
         s = torch.einsum("bihd,bjhd->bhij", q.float(), k.float()) * self.softmax_scale
         p = torch.softmax(s.masked_fill(~causal, float("-inf")), -1)
       self._cache = {"mode": "dense", "scores": dense, "attn": p}
+    elif x.is_cuda and x.dtype == torch.bfloat16:
+      # indexer scores (tcgen05 GEMM with the relu / head-sum epilogue) -> per-query top-k as a packed bit mask
+      # (radix select, no sort, no index lists) -> the tcgen05 attention kernels test the bits in their softmax
+      # stage, forward and backward: nothing of size [B, H, T, T] exists on this path
+      full = indexer_scores(qi, ki, wi, causal=True)
+      mask = SparseMask.from_topk_scores(full.detach(), self.top_k)
+      o = ops.attention(q, k, v, self.softmax_scale, mask=mask)
+      self._cache = {"mode": "sparse", "scores_full": full, "q": q.detach(), "k": k.detach()}
     else:
       scores, sel = lightning_indexer(qi, ki, wi, self.top_k)
       allowed = torch.zeros(B, T, T, dtype=torch.bool, device=x.device)
@@ -90,6 +100,10 @@ class DSA(MLA):
       logq = F.log_softmax(scores.masked_fill(m, float("-inf")), -1)
       kl = F.kl_div(logq.masked_fill(m, 0.0), p.masked_fill(m, 0.0), reduction="none").masked_fill(m, 0.0)
       return kl.sum() / (B * T)
+    if "scores_full" in c:      # GPU path: the index lists are only needed here, for the auxiliary loss
+      full = c["scores_full"]
+      scores, sel = full.topk(min(self.top_k, full.size(-1)), dim=-1)
+      c = dict(c, scores=scores, sel=sel)
     scores, sel, q, k = c["scores"], c["sel"].long(), c["q"], c["k"]
     B, T, K = scores.shape
     ks = torch.gather(k.unsqueeze(1).expand(B, T, T, *k.shape[2:]), 2,

@@ -16,7 +16,7 @@ from ..init import trunc_normal_
 from torch import nn
 
 from ... import ops
-from ...ops.attention import attention
+from ...ops.attention import SparseMask, attention
 from .common import masked_attention
 
 
@@ -106,8 +106,20 @@ class NSA(nn.Module):
     return blocks[..., :self.topk]
 
   def slc_attention(self, q, k, v, blocks: torch.Tensor) -> torch.Tensor:
+    """Attention over the query's own block and its selected blocks.  On a GPU every KV group runs the tcgen05
+    attention kernel with a packed bit mask built from the block list (no [T, T] tensor); the statement below it is
+    the oracle for CPU tensors and unsupported head sizes."""
     B, T, H, D = q.shape
     lp = self.slc_block
+    if q.is_cuda and q.dtype == torch.bfloat16 and D in (64, 128):
+      cur = (torch.arange(T, device=q.device) // lp).view(1, T, 1, 1).expand(B, T, self.n_kv_heads, 1)
+      with_own = torch.cat((blocks.to(torch.int32), cur.to(torch.int32)), -1)          # [B,T,KV,topk+1]
+      outs = []
+      for g in range(self.n_kv_heads):
+        mask = SparseMask.from_blocks(with_own[:, :, g].contiguous(), lp, T)
+        outs.append(attention(q[:, :, g * self.G:(g + 1) * self.G].contiguous(), k[:, :, g:g + 1].contiguous(),
+                              v[:, :, g:g + 1].contiguous(), self.softmax_scale, mask=mask))
+      return torch.cat(outs, dim=2)
     nb = (T + lp - 1) // lp
     allowed_blk = torch.zeros(B, T, self.n_kv_heads, nb, dtype=torch.bool, device=q.device)
     allowed_blk.scatter_(3, blocks.clamp(0, nb - 1).long(), True)

@@ -124,6 +124,8 @@ class Rdep:
     # followed by the wide push kernel is faster (8 GPUs, Moonlight shape: 1.82 ms against 2.37 ms per return).
     env = os.environ.get("NMOE_RDEP_FUSED_RETURN", "")
     self.fused_return = (env == "1") if env in ("0", "1") else (self.world <= 2)
+    # unfused return: 1 = rows travel as bulk asynchronous copies (global -> shared -> peer), 0 = 16-byte stores
+    self.push_impl = int(os.environ.get("NMOE_RDEP_PUSH_BULK", "1"))
     self.fused_swiglu_quant = True  # block-scaled profiles: SwiGLU + quantise in the up/gate GEMM's epilogue
     # world > 1: the receive buffers hold the worst case (world x the balanced share), but every per-layer
     # tensor derived from them (H13, activations, their gradients) only needs the rows that arrived.  Reading
@@ -202,19 +204,25 @@ class Rdep:
                                    L.stream()), "rdep_wait(data)")
 
   def push_and_reduce(self, y: Optional[torch.Tensor], plan: Plan, use_gate: bool, rowval: Optional[torch.Tensor],
-                      out: torch.Tensor) -> None:
-    """Owner -> source return of rows (and optional per-row scalars), then the source-side K-way sum."""
+                      out: torch.Tensor, marks: Optional[list] = None) -> None:
+    """Owner -> source return of rows (and optional per-row scalars), then the source-side K-way sum.
+    ``marks``: two CUDA events recorded after the push kernel and after the wait (benchmarks)."""
     lib = L.lib()
     st = G.status_buffer(self.device)
     L.check(lib.nmoe_rdep_push(L.ptr(y), ctypes.c_void_p(self.slab.local_ptr("meta")), L.ptr(plan.n_m_tiles),
                                self.capacity, self.dim, int(use_gate), self.slab.ptrs("ret"),
-                               self.slab.ptrs("retg"), L.ptr(rowval), self.world, L.stream()), "rdep_push")
+                               self.slab.ptrs("retg"), L.ptr(rowval), self.world, self.max_tokens * self.K,
+                               L.ptr(st), self.push_impl, L.stream()), "rdep_push")
+    if marks:
+      marks[0].record()
     self.epoch_ret += 1
     L.check(lib.nmoe_rdep_signal(self.slab.ptrs("ret_flags"), self.rank, self.world, ctypes.c_uint(self.epoch_ret),
                                  L.stream()), "rdep_signal")
     L.check(lib.nmoe_rdep_wait(ctypes.c_void_p(self.slab.local_ptr("ret_flags")), self.world,
                                ctypes.c_uint(self.epoch_ret), ctypes.c_uint(self.wait_budget), L.ptr(st), 421,
                                L.stream()), "rdep_wait(ret)")
+    if marks:
+      marks[1].record()
     L.check(lib.nmoe_rdep_reduce(ctypes.c_void_p(self.slab.local_ptr("ret")), L.ptr(plan.pos), L.ptr(out), plan.T,
                                  plan.K, self.dim, L.stream()), "rdep_reduce")
 

@@ -64,10 +64,12 @@ def check_moe(rank, world, dev, profile="bf16"):
   es = slice(rank * n_local, (rank + 1) * n_local)
   errs = {"out": rel(out.cpu(), ref[sl]), "dx": rel(xd.grad.cpu(), xf.grad[sl]), "dg": rel(gd.grad.cpu(), gf.grad[sl]),
           "dW13": rel(W13.grad.cpu(), Wf.grad[es]), "dW2": rel(W2.grad.cpu(), W2f.grad[es])}
-  # forward: per-element bound; the block-scaled bars are the reference's (tests/test_rdep_accuracy.py:81-112:
-  # fp8 1e-2, nvfp4 5e-2 absolute on outputs of this magnitude), bf16 is held to a few bf16 roundings
-  atol, rtol, gtol = {"bf16": (1.5e-3, 1.6e-2, 3e-2), "fp8": (1e-2, 0.0, 8e-2), "nvfp4": (5e-2, 0.0, 0.35)}[profile]
-  errs["out_excess"] = close(out.cpu(), ref[sl], atol, rtol)
+  # forward, per element: |out - ref| <= atol_frac * max|ref| + rtol * |ref|.  bf16 is held to a few bf16 roundings
+  # of the intermediates.  The block-scaled formats carry their element error into the sum (signed terms do not
+  # average it away): two chained E4M3 GEMMs give a few percent of the output scale, E2M1 a few times that; on the
+  # reference's toy magnitudes these are its bars of 1e-2 / 5e-2 absolute (tests/test_rdep_accuracy.py:81-112).
+  afrac, rtol, gtol = {"bf16": (6e-3, 1.6e-2, 3e-2), "fp8": (8e-2, 0.1, 8e-2), "nvfp4": (0.3, 0.3, 0.35)}[profile]
+  errs["out_excess"] = close(out.cpu(), ref[sl], afrac * ref[sl].abs().max().item(), rtol)
   assert errs["out_excess"] <= 0, (profile, errs)
   assert all(v < gtol for k, v in errs.items() if k != "out_excess"), (profile, errs)
   dist.barrier()                                   # every peer's stores have landed
@@ -82,9 +84,9 @@ def check_capacity_drop(rank, world, dev):
   at its next check), nothing is written outside the regions, and the context stays usable."""
   from nmoe_b200.ops import _lib as L
   from nmoe_b200.parallel.rdep import Rdep
-  T, H, F, E, K = 256, 256, 128, 8, 2
+  T, H, F, E, K = 1024, 256, 128, 8, 2
   n_local = E // world
-  rd = Rdep(H, E, K, T, device=dev, capacity_factor=0.5)
+  rd = Rdep(H, E, K, T, device=dev, capacity_factor=0.25)     # room for a quarter of the balanced share
   g = torch.Generator().manual_seed(5 + rank)
   x = (torch.randn(T, H, generator=g) * 0.5).bfloat16().to(dev)
   eid = torch.stack([torch.randperm(E, generator=g)[:K] for _ in range(T)]).int().to(dev)
