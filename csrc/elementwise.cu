@@ -622,6 +622,8 @@ int nmoe_sumsq_bf16(const void* x, long long n, float* out, cudaStream_t st) {
 }  // extern "C"
 
 // ------------------------------------------------------------------ allocation-free variant
+#include <atomic>
+
 #include "noalloc.h"
 
 namespace nmoe {
@@ -629,7 +631,9 @@ namespace nmoe {
 // cudaGetSymbolAddress; the kernels receive the resolved device pointer.
 static __device__ __align__(256) float g_rmsnorm_bwd_scratch[NMOE_NOALLOC_RMSNORM_MAX_BLOCKS * NMOE_NOALLOC_RMSNORM_MAX_H];
 constexpr int kNoallocMaxDevices = 64;
-static float* g_rmsnorm_bwd_scratch_ptr[kNoallocMaxDevices] = {nullptr};
+// Per-device cache of the resolved address.  Atomic: two host threads may make the first call on a device at the
+// same time; both resolve the same address and both store it, which is harmless, but the accesses must not race.
+static std::atomic<float*> g_rmsnorm_bwd_scratch_ptr[kNoallocMaxDevices];
 }  // namespace nmoe
 
 extern "C" int nmoe_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w, const float* rstd, void* dx,
@@ -640,14 +644,14 @@ extern "C" int nmoe_rmsnorm_bwd_noalloc(const void* dy, const void* x, const voi
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return static_cast<int>(e);
   if (dev < 0 || dev >= nmoe::kNoallocMaxDevices) return -3;
-  if (nmoe::g_rmsnorm_bwd_scratch_ptr[dev] == nullptr) {
+  float* scratch = nmoe::g_rmsnorm_bwd_scratch_ptr[dev].load(std::memory_order_acquire);
+  if (scratch == nullptr) {
     // once per device, with that device current
-    float* p = nullptr;
-    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), nmoe::g_rmsnorm_bwd_scratch);
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&scratch), nmoe::g_rmsnorm_bwd_scratch);
     if (e != cudaSuccess) return static_cast<int>(e);
-    nmoe::g_rmsnorm_bwd_scratch_ptr[dev] = p;
+    nmoe::g_rmsnorm_bwd_scratch_ptr[dev].store(scratch, std::memory_order_release);
   }
   // nmoe_rmsnorm_bwd_blocks(M) never exceeds NMOE_NOALLOC_RMSNORM_MAX_BLOCKS, and every partial
   // row read by the column sum is written by the backward kernel of the same call.
-  return nmoe_rmsnorm_bwd(dy, x, w, rstd, dx, dw, nmoe::g_rmsnorm_bwd_scratch_ptr[dev], M, H, accumulate, st);
+  return nmoe_rmsnorm_bwd(dy, x, w, rstd, dx, dw, scratch, M, H, accumulate, st);
 }

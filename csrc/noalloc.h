@@ -28,7 +28,13 @@ extern "C" {
 //
 // The first call on each device resolves the device address of the built-in scratch (one
 // cudaGetSymbolAddress with that device current); make that first call outside of any
-// stream capture.  All calls on a device share the one scratch array, so two calls whose
+// stream capture.  Make it at start-up, before the process commits the rest of the device's
+// memory: with lazy module loading, that first symbol lookup or kernel launch can be what
+// loads this library's device image, built-in array included, and on a device with no
+// memory left it fails.  After one successful call per device, no later call can need memory.
+// Host threads may race on the first call; the address cache is atomic.
+//
+// All calls on a device share the one scratch array, so two calls whose
 // kernels may overlap on the GPU (different streams without an ordering between them) race
 // on it; issue them on one stream or order them yourself.  Nothing in the scratch needs to
 // be cleared between calls: each call overwrites every partial row it later reads.

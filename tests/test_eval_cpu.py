@@ -81,3 +81,41 @@ def test_task_scorers_and_sandbox():
   bad = execution.humaneval_check("def add(a, b):\n", "    return a - b\n", "def check(f):\n    assert f(1, 2) == 3\n", "add")
   assert ok and not bad
   assert execution.run_python("while True: pass", timeout_s=1.0) == (False, "timeout")
+
+
+def test_sandbox_kills_processes_the_program_left_behind(tmp_path):
+  """A generated program that forks a sleeper and returns (or times out) must not leave the sleeper running."""
+  import os
+  import time
+  from nmoe_b200.eval.execution import run_python
+  marker = tmp_path / "pid"
+  prog = f"""
+import os, time, sys
+pid = os.fork()
+if pid == 0:
+    os.close(1); os.close(2)          # detach from the pipes so that the parent's exit ends the run
+    time.sleep(60)
+    os._exit(0)
+open({str(marker)!r}, "w").write(str(pid))
+sys.exit(0)
+"""
+  ok, _ = run_python(prog, timeout_s=5.0)
+  assert ok
+  pid = int(marker.read_text())
+  deadline = time.time() + 3
+  alive = True
+  while time.time() < deadline:
+    try:
+      os.kill(pid, 0)
+      # a zombie still answers kill(0): look at its state
+      state = open(f"/proc/{pid}/stat").read().split()[2]
+      alive = state not in ("Z", "X")
+    except (ProcessLookupError, FileNotFoundError):
+      alive = False
+    if not alive:
+      break
+    time.sleep(0.1)
+  assert not alive, "forked child survived the sandbox"
+  # and a program that hangs is cut off with its children
+  ok, out = run_python("import os, time\nos.fork()\ntime.sleep(60)\n", timeout_s=1.0)
+  assert not ok and out == "timeout"

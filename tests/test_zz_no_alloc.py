@@ -47,6 +47,32 @@ def test_noalloc_matches_regular_entry_point_twice():
     assert torch.equal(dx, dx_ref) and torch.equal(dw, dw_ref), "same kernels, same order: bit-identical"
 
 
+def test_noalloc_reaches_the_end_of_the_built_in_scratch():
+  """The largest supported width with enough rows that every partial row of the array is used, and a look at the
+  driver's own free-memory figure: the caching allocator cannot see an allocation made by a library, the driver can."""
+  torch.manual_seed(1)
+  dev = torch.device("cuda")
+  M, H = 16384, 4096
+  x = torch.randn(M, H, device=dev).bfloat16()
+  w = (1 + 0.1 * torch.randn(H, device=dev)).bfloat16()
+  dy = torch.randn(M, H, device=dev).bfloat16()
+  rstd = torch.rsqrt(x.float().pow(2).mean(-1) + 1e-5)
+  dx_ref, dw_ref = _run("nmoe_rmsnorm_bwd", dy, x, w, rstd, True)
+  _run("nmoe_rmsnorm_bwd_noalloc", dy, x, w, rstd, False)          # first use on this device may load the module
+  from nmoe_b200.ops import _lib as L
+  lib = L.lib()
+  dx, dw = torch.empty_like(x), torch.empty_like(w)                # outputs exist before the measured call
+  torch.cuda.synchronize()
+  free_before, _ = torch.cuda.mem_get_info()
+  st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+  rc = lib.nmoe_rmsnorm_bwd_noalloc(L.ptr(dy), L.ptr(x), L.ptr(w), L.ptr(rstd), L.ptr(dx), L.ptr(dw), M, H, 0, st)
+  torch.cuda.synchronize()
+  free_after, _ = torch.cuda.mem_get_info()
+  assert rc == 0
+  assert free_before - free_after <= 0, (free_before, free_after)  # the driver handed out nothing during the call
+  assert torch.equal(dx, dx_ref) and torch.equal(dw, dw_ref)
+
+
 def test_noalloc_rejects_oversize():
   from nmoe_b200.ops import _lib as L
   lib = L.lib()
