@@ -1,13 +1,9 @@
-// Multi-node (hybrid) expert-parallel transport: entry points with the shape of the NVSHMEM-backed
-// path (uid bootstrap, symmetric-heap allocation, quiet/barrier on a stream) so that callers and
-// bindings do not change when a build with NVSHMEM is linked in.  This build has no NVSHMEM: every
-// entry point reports kHybridUnavailable and touches nothing.  The routing rule the device code of
-// such a build has to follow (inter-node traffic goes to the peer with the same local index on the
-// destination node, which forwards inside its node over peer memory) is modelled on the host in
-// nmoe_b200/parallel/hybrid.py and tested there.
+// Stand-ins, inside the main library, for the entry points of the NVSHMEM-backed inter-node transport.  The real ones
+// live in csrc/hybrid/rdep_nvshmem.cu and are built into their own library (libnmoe_hybrid.so) wherever an NVSHMEM
+// installation is found; when that library is not loaded, callers resolve these symbols instead and every one of them
+// reports kHybridUnavailable and touches nothing.
 //
-// Reference counterpart: nmoe/csrc/rdep_nvshmem.cu/.cuh and the nvshmem_* bindings
-// (nmoe/csrc/bindings.cpp:553-700).
+// Reference counterpart: nmoe/csrc/rdep_nvshmem.cu/.cuh and the nvshmem_* bindings (nmoe/csrc/bindings.cpp:929-995).
 #include <stddef.h>
 #include <string.h>
 

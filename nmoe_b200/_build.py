@@ -31,8 +31,12 @@ def _nvcc() -> str:
   return cand if Path(cand).exists() else "nvcc"
 
 
+HYBRID_SRC = CSRC / "hybrid" / "rdep_nvshmem.cu"        # built separately (needs NVSHMEM and relocatable device code)
+HYBRID_LIB_PATH = LIB_DIR / "libnmoe_hybrid.so"
+
+
 def _sources() -> list[Path]:
-  return sorted(p for p in CSRC.rglob("*") if p.suffix in (".cu", ".cpp"))
+  return sorted(p for p in CSRC.rglob("*") if p.suffix in (".cu", ".cpp") and p != HYBRID_SRC)
 
 
 def _headers_digest() -> str:
@@ -95,6 +99,64 @@ def build(verbose: bool = False, ptxas_v: bool = False, force: bool = False) -> 
   return LIB_PATH
 
 
+def nvshmem_home() -> Path | None:
+  """Root of an NVSHMEM installation with include/nvshmem.h and lib/libnvshmem_device.a: $NVSHMEM_HOME, the
+  nvidia-nvshmem-cu12 wheel, or the distribution's /usr paths."""
+  cands = []
+  if os.environ.get("NVSHMEM_HOME"):
+    cands.append(Path(os.environ["NVSHMEM_HOME"]))
+  try:
+    import nvidia.nvshmem as _n  # type: ignore
+    cands += [Path(p) for p in _n.__path__]
+  except Exception:
+    pass
+  cands.append(Path("/usr/local/nvshmem"))
+  for c in cands:
+    if (c / "include" / "nvshmem.h").exists() and (c / "lib" / "libnvshmem_device.a").exists():
+      return c
+  return None
+
+
+def build_hybrid(verbose: bool = False) -> Path | None:
+  """Build the NVSHMEM-backed inter-node transport (csrc/hybrid/rdep_nvshmem.cu) into lib/libnmoe_hybrid.so.
+  Returns None when no NVSHMEM installation is found.  Steps: compile with relocatable device code, device-link
+  against libnvshmem_device.a, link the host side against libnvshmem_host."""
+  home = nvshmem_home()
+  if home is None:
+    return None
+  OBJ_DIR.mkdir(parents=True, exist_ok=True)
+  tag = hashlib.sha256(HYBRID_SRC.read_bytes() + _headers_digest().encode() + str(home).encode()).hexdigest()[:16]
+  obj, dobj = OBJ_DIR / f"hybrid_rdep_nvshmem.{tag}.o", OBJ_DIR / f"hybrid_dlink.{tag}.o"
+  stamp = LIB_DIR / "hybrid.stamp"
+  if HYBRID_LIB_PATH.exists() and stamp.exists() and stamp.read_text() == tag:
+    return HYBRID_LIB_PATH
+  arch = ["-gencode", "arch=compute_100a,code=sm_100a"]
+  cuda_lib = str(Path(_nvcc()).resolve().parent.parent / "lib64") if Path(_nvcc()).exists() else "/usr/local/cuda/lib64"
+  host_so = next((p for p in sorted((home / "lib").glob("libnvshmem_host.so*"))), None)
+  if host_so is None:
+    return None
+  steps = [
+    [_nvcc(), *arch, "-O3", "-std=c++17", "-rdc=true", "-Xcompiler", "-fPIC", "-I", str(CSRC), "-I", str(home / "include"),
+     "-c", str(HYBRID_SRC), "-o", str(obj)],
+    [_nvcc(), *arch, "-dlink", "-Xcompiler", "-fPIC", "-o", str(dobj), str(obj), str(home / "lib" / "libnvshmem_device.a"),
+     "-lcudadevrt"],
+    ["g++", "-shared", "-o", str(HYBRID_LIB_PATH), str(obj), str(dobj), str(home / "lib" / "libnvshmem_device.a"),
+     f"-L{home / 'lib'}", f"-l:{host_so.name}", f"-L{cuda_lib}", f"-L{cuda_lib}/stubs", "-lcudadevrt", "-lcudart",
+     "-lcuda", f"-Wl,-rpath,{home / 'lib'}", f"-Wl,-rpath,{cuda_lib}"],
+  ]
+  for cmd in steps:
+    if verbose:
+      print(" ".join(cmd), flush=True)
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+      raise RuntimeError(f"hybrid build step failed: {' '.join(cmd[:4])} ...\n{r.stdout[-3000:]}\n{r.stderr[-3000:]}")
+  stamp.write_text(tag)
+  return HYBRID_LIB_PATH
+
+
 if __name__ == "__main__":
+  if "--hybrid" in sys.argv:
+    print(build_hybrid(verbose="-v" in sys.argv))
+    sys.exit(0)
   p = build(verbose="-v" in sys.argv, ptxas_v="--ptxas" in sys.argv, force="--force" in sys.argv)
   print(p)

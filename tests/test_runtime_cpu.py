@@ -260,3 +260,22 @@ def test_status_watch_reports_one_step_late_without_blocking():
     assert int(tc_gemm._STATUS[dev][0]) == 0
   finally:
     tc_gemm._STATUS.pop(dev, None)
+
+
+def test_nvshmem_transport_library_builds_and_exports_its_entry_points():
+  """Where an NVSHMEM installation exists, the inter-node transport compiles (relocatable device code, device link
+  against libnvshmem_device.a) and exports the dispatch / wait / return entry points next to the bootstrap ones."""
+  import ctypes
+  from nmoe_b200 import _build
+  if _build.nvshmem_home() is None:
+    pytest.skip("no NVSHMEM installation on this machine")
+  lib = _build.build_hybrid()
+  assert lib is not None and lib.exists()
+  h = ctypes.CDLL(str(lib))
+  for name in ("nmoe_hybrid_available", "nmoe_hybrid_uid_bytes", "nmoe_hybrid_get_uid", "nmoe_hybrid_init",
+               "nmoe_hybrid_alloc", "nmoe_hybrid_free", "nmoe_hybrid_dispatch", "nmoe_hybrid_wait",
+               "nmoe_hybrid_return", "nmoe_hybrid_quiet", "nmoe_hybrid_barrier", "nmoe_hybrid_finalize"):
+    assert hasattr(h, name), name
+  assert h.nmoe_hybrid_available() == 1 and h.nmoe_hybrid_uid_bytes() >= 64
+  # before initialisation every call that needs the runtime refuses instead of touching it
+  assert h.nmoe_hybrid_quiet(None) == -1 and h.nmoe_hybrid_alloc(ctypes.c_size_t(16), None) == -1
