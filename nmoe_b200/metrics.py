@@ -14,7 +14,7 @@ import math
 import os
 import sqlite3
 import time
-from contextlib import contextmanager
+from contextlib import contextmanager, nullcontext
 from pathlib import Path
 from typing import Dict, Iterable, List, Optional, Tuple
 
@@ -134,6 +134,69 @@ def router_stats(loads: torch.Tensor, biases: Optional[List[torch.Tensor]] = Non
   return out
 
 
+# The timers of the running session, for code below the training loop (ZeRO-2, expert dispatch / return) that wants
+# to time a span without being handed the session: ``with span("time_ms/zero2_reduce_scatter"): ...``
+_ACTIVE_TIMERS: Optional[EventTimers] = None
+
+
+def span(tag: str):
+  """Time a span under ``tag`` in the running metrics session; a no-op context when there is none."""
+  t = _ACTIVE_TIMERS
+  return t.time(tag) if t is not None else nullcontext()
+
+
+def register_model_timers(model: torch.nn.Module, timers: EventTimers) -> int:
+  """Forward / backward timers on the model's building blocks, without touching model code: module hooks record CUDA
+  events on the current stream, the durations are collected when the log line is written (nmoe/metrics.py:276-349 times
+  the dense MLP and the head this way; here attention, the MoE layer and the shared / dense MLPs are covered too).
+  Tags: time_ms/{attn,moe,dense_mlp}_{fwd,bwd}.  Returns the number of modules hooked."""
+  if not timers.enabled:
+    return 0
+  from .models.mlp import MLP
+  from .models.moe import MoE
+  n = 0
+
+  def install(mod: torch.nn.Module, tag: str) -> None:
+    slot = {}
+
+    def fwd_pre(_m, _inp):
+      ev = torch.cuda.Event(enable_timing=True)
+      ev.record()
+      slot["f"] = ev
+
+    def fwd_post(_m, _inp, _out):
+      ev = torch.cuda.Event(enable_timing=True)
+      ev.record()
+      if "f" in slot:
+        timers.pending.append((f"time_ms/{tag}_fwd", slot.pop("f"), ev))
+
+    def bwd_pre(_m, _g):
+      ev = torch.cuda.Event(enable_timing=True)
+      ev.record()
+      slot["b"] = ev
+
+    def bwd_post(_m, _gi, _go):
+      ev = torch.cuda.Event(enable_timing=True)
+      ev.record()
+      if "b" in slot:
+        timers.pending.append((f"time_ms/{tag}_bwd", slot.pop("b"), ev))
+
+    mod.register_forward_pre_hook(fwd_pre)
+    mod.register_forward_hook(fwd_post)
+    mod.register_full_backward_pre_hook(bwd_pre)
+    mod.register_full_backward_hook(bwd_post)
+
+  for blk in getattr(model, "blocks", []):
+    if hasattr(blk, "attn"):
+      install(blk.attn, "attn"); n += 1
+    ffn = getattr(blk, "ffn", None)
+    if isinstance(ffn, MoE):
+      install(ffn, "moe"); n += 1
+    elif isinstance(ffn, MLP):
+      install(ffn, "dense_mlp"); n += 1
+  return n
+
+
 class MetricsSession:
   def __init__(self, run: str, metrics_dir: str, rank: int, world: int, model, cfg):
     self.run, self.rank, self.world, self.cfg = run, rank, world, cfg
@@ -144,6 +207,13 @@ class MetricsSession:
       if rank == 0:
         print(f"[metrics] store disabled: {e}", flush=True)
     self.timers = EventTimers(os.environ.get("NMOE_TIMERS", "1") not in ("0", "false", "False"))
+    global _ACTIVE_TIMERS
+    _ACTIVE_TIMERS = self.timers
+    # per-module hooks break the block-level activation checkpointing's assumptions about module outputs only in
+    # "full" mode, where a block is re-run inside backward; they are installed for the other modes
+    if model is not None and getattr(cfg, "activation_checkpoint", "none") != "full" \
+        and os.environ.get("NMOE_MODULE_TIMERS", "1") not in ("0", "false", "False"):
+      register_model_timers(model, self.timers)
     self.fpt = flops_per_token(cfg)
     self.t_last = time.perf_counter()
     self.step_last = 0
@@ -164,6 +234,9 @@ class MetricsSession:
       self.writer.insert_many(step, items)
 
   def close(self) -> None:
+    global _ACTIVE_TIMERS
+    if _ACTIVE_TIMERS is self.timers:
+      _ACTIVE_TIMERS = None
     if self.gpu is not None:
       self.gpu.stop()
     if self.writer is not None:

@@ -1,7 +1,9 @@
 """RDEP expert parallelism: routing plan, direct placement into the owner's peer-mapped
 buffer, grouped expert GEMMs on the owner, gate-weighted return into the source's
-(token, slot) buffer and a fixed-order reduce.  No all-to-all collective, no host sync:
-row counts stay on the device and the grouped GEMMs read them from there.
+(token, slot) buffer and a fixed-order reduce.  No all-to-all collective; row counts stay on the
+device and the grouped GEMMs read them from there.  Host synchronisation: none on one GPU and none with
+a capacity factor; with lossless buffers on several GPUs, one 4-byte read per MoE forward sizes the
+layer's activations to the rows that actually arrived (see ``Rdep.trim_rows``).
 
 ``Rdep.moe(x, gates, eid, W13, W2)`` is the differentiable entry point
 (reference: nmoe/rdep.py:34-145 and the autograd functions in nmoe/moe.py:52-617).
@@ -25,6 +27,7 @@ import torch.distributed as dist
 from ..ops import _lib as L
 from ..ops import elementwise as EW
 from ..ops import tc_gemm as G
+from ..metrics import span
 from ..ref import ops as R
 from .peer import PeerSlab
 
@@ -127,10 +130,13 @@ class Rdep:
     # unfused return: 1 = rows travel as bulk asynchronous copies (global -> shared -> peer), 0 = 16-byte stores
     self.push_impl = int(os.environ.get("NMOE_RDEP_PUSH_BULK", "1"))
     self.fused_swiglu_quant = True  # block-scaled profiles: SwiGLU + quantise in the up/gate GEMM's epilogue
-    # world > 1: the receive buffers hold the worst case (world x the balanced share), but every per-layer
-    # tensor derived from them (H13, activations, their gradients) only needs the rows that arrived.  Reading
-    # that one number back costs a small host sync per MoE forward and cuts those tensors by ~world x.
-    self.trim_rows = self.world > 1
+    # world > 1, lossless sizing: the receive buffers hold the worst case (world x the balanced share), but every
+    # per-layer tensor derived from them (H13, activations, their gradients) only needs the rows that arrived.
+    # Reading that one number back costs one small host read per MoE forward (the shared-expert MLP is already
+    # queued on its own stream by then, so the device does not idle) and cuts those tensors by ~world x.
+    # With a capacity factor the buffers themselves are a small multiple of the balanced share: nothing is read
+    # back and the layer runs without any host synchronisation, at the price of dropping rows beyond that bound.
+    self.trim_rows = self.world > 1 and capacity_factor <= 0
     # world > 1 (bf16): keep a copy of the dispatched rows for the weight gradient instead of sending x over
     # NVLink a second time in backward (one of five transfers per layer; costs rows x H x 2 bytes per layer)
     self.save_dispatched = self.world > 1
@@ -276,8 +282,9 @@ class _MoEFused(torch.autograd.Function):
     if wq is not None:
       from ..ops import quant as Q
       W13q, W13sf, W2q, W2sf = wq
-      rdep.place_mx(x, plan, gates32.view(-1))
-      rdep.wait_data()
+      with span("time_ms/comm/rdep_dispatch"):
+        rdep.place_mx(x, plan, gates32.view(-1))
+        rdep.wait_data()
       ggemm = Q.grouped_gemm_mxfp4 if rdep.fp4 else Q.grouped_gemm_mxfp8
       if save_h13 or not rdep.fused_swiglu_quant:
         h13 = ggemm(rdep.xq[:rows], rdep.sfa, W13q, W13sf, plan.tile_expert, plan.n_m_tiles)
@@ -291,8 +298,9 @@ class _MoEFused(torch.autograd.Function):
       ctx.rdep, ctx.plan = rdep, plan
       ctx.save_for_backward(x, gates32, W13, W2, h13 if save_h13 else None, None)
       return out
-    rdep.place(x, plan, gates32.view(-1), "x", with_meta=True)
-    rdep.wait_data()
+    with span("time_ms/comm/rdep_dispatch"):
+      rdep.place(x, plan, gates32.view(-1), "x", with_meta=True)
+      rdep.wait_data()
     h13 = G.grouped_gemm(rdep.xbuf[:rows], W13, plan.tile_expert, plan.n_m_tiles, align256=rdep.align == 256)
     a = EW.swiglu_rows(h13, plan.n_m_tiles)
     if rdep.fused_return:

@@ -26,6 +26,7 @@ from .. import ops
 from ..config import Config
 from ..ops import _lib as L
 from ..ops import tc_gemm as G
+from ..metrics import span
 from .peer import PeerSlab
 
 _ALIGN = 256   # elements; keeps every shard 16-byte aligned and vectorisable
@@ -132,7 +133,8 @@ class Zero2:
         lo = self.rank * g.shard
         gshard = torch.empty(g.shard, dtype=g.flat_grad.dtype, device=self.device)
         if g.flat_grad.is_cuda:
-          dist.reduce_scatter_tensor(gshard, g.flat_grad, op=dist.ReduceOp.AVG, group=self.pg)
+          with span("time_ms/zero2_reduce_scatter"):
+            dist.reduce_scatter_tensor(gshard, g.flat_grad, op=dist.ReduceOp.AVG, group=self.pg)
         else:  # gloo has no reduce_scatter: all_reduce then slice (CPU tests only)
           full = g.flat_grad.float()
           dist.all_reduce(full, group=self.pg)
@@ -142,7 +144,8 @@ class Zero2:
         pshard = g.flat_param[lo:lo + g.shard]
         ops.adamw_flat_(pshard, gshard, g.exp_avg, g.exp_avg_sq, **kw)
         if g.flat_param.is_cuda:
-          dist.all_gather_into_tensor(g.flat_param, pshard.clone(), group=self.pg)
+          with span("time_ms/zero2_all_gather"):
+            dist.all_gather_into_tensor(g.flat_param, pshard.clone(), group=self.pg)
         else:
           parts = [torch.empty_like(pshard) for _ in range(self.world)]
           dist.all_gather(parts, pshard.clone(), group=self.pg)
@@ -150,6 +153,8 @@ class Zero2:
       elif self.impl == "fused":
         self.epoch += 1
         st = G.status_buffer(self.device)
+        _t = span("time_ms/zero2_fused")      # reduce-scatter + AdamW + all-gather in one kernel, plus the done wait
+        _t.__enter__()
         L.check(L.lib().nmoe_zero2_fused(
           self.rank, self.world, L.c_ll(g.shard), self.slab.ptrs(f"g{g.gi}g"), self.slab.ptrs(f"g{g.gi}p"),
           self.slab.ptrs("ready"), self.slab.ptrs("done"), L.ptr(g.exp_avg), L.ptr(g.exp_avg_sq),
@@ -159,6 +164,7 @@ class Zero2:
         L.check(L.lib().nmoe_rdep_wait(ctypes.c_void_p(self.slab.local_ptr("done")), self.world,
                                        ctypes.c_uint(self.epoch), ctypes.c_uint(0), L.ptr(st), 501, L.stream()),
                 "zero2_wait")
+        _t.__exit__(None, None, None)
       else:
         raise ValueError(f"unknown zero2 implementation {self.impl!r}")
 

@@ -11,6 +11,8 @@ Endpoints (same contract as the reference dashboard, nviz/app/api/*/route.ts):
   GET /api/gpu?run=R                              -> latest gpu/{i}/* telemetry grouped by GPU index
   GET /api/router?run=R                           -> latest router/layer_NN/* and router_agg/* grouped by layer
   GET /api/experiments                            -> experiments with their runs (config, git hash, status, results)
+  GET /api/datasets[/preview|/meta|/manifest|/shard/stats|/shard/window|/index/header|/index/doc|/pipeline]?path=P
+                                                  -> read-only dataset browser confined to NVIZ_DATASETS_DIR (viz/datasets.py)
   GET /                                           -> a single static page that plots a tag of a run
 
 All ``rank_*.duckdb`` / ``rank_*.sqlite`` files of a run are opened read-only and merged; when a
@@ -210,6 +212,36 @@ def make_handler(store: MetricStore, exp_db: Optional[str]):
       self.end_headers()
       self.wfile.write(data)
 
+    def _datasets(self, what: str, q: Dict[str, str]):
+      """Read-only dataset browser (viz/datasets.py); every path is confined to NVIZ_DATASETS_DIR."""
+      from . import datasets as D
+      path = q.get("path", "")
+      try:
+        if what == "":
+          return self._send(200, D.list_dir(path))
+        if what == "preview":
+          return self._send(200, D.preview_file(path, int(q.get("bytes", str(64 * 1024)))))
+        if what == "meta":
+          return self._send(200, D.meta(path))
+        if what == "manifest":
+          return self._send(200, D.manifest_preview(path, int(q.get("limit", "200"))))
+        if what == "shard/stats":
+          return self._send(200, D.shard_stats(path))
+        if what == "shard/window":
+          return self._send(200, D.token_window(path, int(q.get("offset", "0")), int(q.get("length", "256")),
+                                                q.get("tokenizer")))
+        if what == "index/header":
+          return self._send(200, D.index_header(path))
+        if what == "index/doc":
+          return self._send(200, D.index_doc(path, int(q.get("doc", "0")), q.get("tokenizer")))
+        if what == "pipeline":
+          return self._send(200, D.pipeline_inspect(path))
+        return self._send(404, {"error": "not found"})
+      except D.DatasetPathError as e:
+        return self._send(400, {"error": str(e)})
+      except (FileNotFoundError, IndexError) as e:
+        return self._send(404, {"error": str(e)})
+
     def do_GET(self):
       u = urlparse(self.path)
       q = {k: v[0] for k, v in parse_qs(u.query).items()}
@@ -222,6 +254,8 @@ def make_handler(store: MetricStore, exp_db: Optional[str]):
           return self._send(200, [store.run_info(r) for r in store.runs()])
         if u.path == "/api/experiments":
           return self._send(200, experiments(exp_db))
+        if u.path == "/api/datasets" or u.path.startswith("/api/datasets/"):
+          return self._datasets(u.path[len("/api/datasets"):].strip("/"), q)
         run = q.get("run", "")
         if u.path.startswith("/api/") and run not in store.runs():
           return self._send(404, {"error": f"unknown run {run!r}"})

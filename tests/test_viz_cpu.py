@@ -51,3 +51,52 @@ def test_endpoints_over_two_rank_files(tmp_path):
   finally:
     srv.shutdown()
     srv.server_close()
+
+
+def test_dataset_browser_routes(tmp_path, monkeypatch):
+  """/api/datasets/*: listing, shard statistics, token window, index header / document, manifest, flow directory,
+  and refusal of paths that leave the datasets directory."""
+  import urllib.error
+  import numpy as np
+  from nmoe_b200.data.sinks import ShardedWriter
+  root = tmp_path / "data"
+  src = root / "flows" / "dev" / "web"
+  w = ShardedWriter(src, "web", "v1", num_shards=2, tokenizer="bytes", vocab_size=300, eos_token_id=256)
+  rng = np.random.default_rng(0)
+  for i in range(40):
+    w.add_document(i % 2, rng.integers(0, 255, size=20 + i).tolist())
+  w.finalize()
+  (tmp_path / "secret.txt").write_text("outside")
+  monkeypatch.setenv("NVIZ_DATASETS_DIR", str(root))
+  srv = serve(str(tmp_path / "metrics"), None, port=0)
+  port = srv.server_address[1]
+  threading.Thread(target=srv.serve_forever, daemon=True).start()
+  try:
+    top = _get(port, "/api/datasets?path=flows/dev")
+    assert [e["name"] for e in top["entries"]] == ["web"] and top["entries"][0]["kind"] == "dir"
+    man = _get(port, "/api/datasets/manifest?path=flows/dev/web&limit=1")
+    assert man["manifest"]["dataset"] == "web" and len(man["shards"]) == 1 and man["manifest"]["num_shards_listed"] == 2
+    shard = "flows/dev/web/" + man["shards"][0]["path"]
+    assert _get(port, f"/api/datasets/meta?path={shard}") | {} == _get(port, f"/api/datasets/meta?path={shard}")
+    assert _get(port, f"/api/datasets/meta?path={shard}")["kind"] == "token_shard"
+    st = _get(port, f"/api/datasets/shard/stats?path={shard}")
+    assert st["documents"] == 20 and st["tokens"] == man["shards"][0]["num_tokens"] and st["max_token_id"] == 256
+    win = _get(port, f"/api/datasets/shard/window?path={shard}&offset=3&length=5")
+    assert len(win["ids"]) == 5 and win["start"] == 3
+    idx = shard[:-4] + ".idx"
+    hdr = _get(port, f"/api/datasets/index/header?path={idx}")
+    assert hdr["documents"] == 20 and hdr["tokens_covered"] == st["tokens"]
+    doc = _get(port, f"/api/datasets/index/doc?path={idx}&doc=1")
+    assert doc["tokens"] == len(doc["ids"]) and doc["ids"][-1] == 256
+    flow = _get(port, "/api/datasets/pipeline?path=flows/dev")
+    assert flow["sources"][0]["source"] == "web" and flow["total_tokens"] == man["manifest"]["total_tokens"]
+    pv = _get(port, "/api/datasets/preview?path=flows/dev/web/manifest.json&bytes=2048")
+    assert '"dataset"' in pv["text"]
+    for bad in ("/api/datasets?path=../", "/api/datasets/preview?path=../secret.txt"):
+      try:
+        _get(port, bad)
+        raise AssertionError("path traversal was served")
+      except urllib.error.HTTPError as e:
+        assert e.code == 400
+  finally:
+    srv.shutdown()
