@@ -134,3 +134,53 @@ Widgets \cite{foo} satisfy $a^2 + b^2 = c^2$ and more~\ref{x}.
   assert main(["stack-v2-materialize", "--table", str(table), "--blobs", str(blobs), "--output", str(out2), "--languages", "Python,Rust"]) == 0
   rows = [json.loads(l) for l in out2.read_text().splitlines()]
   assert [r["id"] for r in rows] == ["abcd1234", "ffee"] and rows[0]["text"].startswith("def f()") and rows[1]["text"] == "fn main() {}"
+
+
+def test_ar5iv_html_to_text_and_mathml():
+  from nmoe_b200.data.arxiv_html import (extract_html_metadata, html_to_text, load_metadata_snapshot, mathml_to_latex,
+                                          parse_atom_feed, parse_html)
+  html = """<html><head><link rel="canonical" href="https://arxiv.org/abs/2301.12345v2"></head><body>
+  <nav>menu</nav><article class="ltx_document">
+  <h1 class="ltx_title ltx_title_document">Sparse Things</h1>
+  <div class="ltx_authors"><span class="ltx_personname">Ada L.</span><span class="ltx_personname">Bob K.</span></div>
+  <div class="ltx_abstract"><h6>Abstract</h6><p>We study <math alttext="x^{2}"><msup><mi>x</mi><mn>2</mn></msup></math>.</p></div>
+  <section class="ltx_section"><h2>1 Intro</h2><p>Energy is
+   <math display="block"><mrow><mi>E</mi><mo>=</mo><mfrac><mn>1</mn><mn>2</mn></mfrac><mi>m</mi><msup><mi>v</mi><mn>2</mn></msup>
+   <mo>+</mo><munderover><mo>&#x2211;</mo><mrow><mi>i</mi><mo>=</mo><mn>1</mn></mrow><mi>n</mi></munderover><msub><mi>&#x3b1;</mi><mi>i</mi></msub></mrow></math>
+   as shown<cite>[3]</cite>.</p>
+   <section class="ltx_subsection"><h3>1.1 Detail</h3><p>Nested text.</p></section></section>
+  <section class="ltx_bibliography"><h2>References</h2><p>[3] Someone.</p></section>
+  </article><footer>foot</footer></body></html>"""
+  text = html_to_text(html)
+  assert text.startswith("Sparse Things")
+  assert "We study $x^{2}$." in text and "Abstract" not in text.split("\n")[2]
+  assert r"$$E=\frac{1}{2}mv^2+\sum_{i=1}^n\alpha_i$$" in text
+  assert "1 Intro" in text and "1.1 Detail" in text and text.count("Nested text.") == 1
+  assert "References" not in text and "menu" not in text and "foot" not in text and "[3]" not in text
+  assert "Abstract" not in html_to_text(html, include_abstract=False).replace("Sparse", "")
+  meta = extract_html_metadata(html)
+  assert meta.title == "Sparse Things" and meta.authors == ["Ada L.", "Bob K."] and meta.arxiv_id == "2301.12345"
+  root = parse_html("<math><msqrt><mi>x</mi></msqrt><mo>&#x2264;</mo><mover><mi>y</mi><mo>^</mo></mover>"
+                    "<mfenced open='[' close=']'><mi>a</mi><mi>b</mi></mfenced></math>")
+  assert mathml_to_latex(root.find("math")) == r"\sqrt{x}\leq \hat{y}\left[a,b\right]"
+  atom = """<feed xmlns="http://www.w3.org/2005/Atom" xmlns:arxiv="http://arxiv.org/schemas/atom">
+  <entry><id>http://arxiv.org/abs/2301.12345v2</id><title>Sparse
+   Things</title><summary> An abstract. </summary><author><name>Ada L.</name></author>
+   <published>2023-01-30T00:00:00Z</published><updated>2023-02-01T00:00:00Z</updated>
+   <arxiv:primary_category term="cs.LG"/><category term="cs.LG"/><category term="stat.ML"/>
+   <arxiv:doi>10.1/x</arxiv:doi></entry></feed>"""
+  m = parse_atom_feed(atom)["2301.12345"]
+  assert (m.title, m.primary_category, m.categories, m.doi, m.authors) == ("Sparse Things", "cs.LG", ["cs.LG", "stat.ML"], "10.1/x", ["Ada L."])
+
+
+def test_metadata_snapshot_filter(tmp_path):
+  from nmoe_b200.data.arxiv_html import load_metadata_snapshot
+  p = tmp_path / "snap.jsonl"
+  rows = [{"id": "2301.1", "title": "A\n b", "authors_parsed": [["Lovelace", "Ada", ""]], "categories": "cs.LG stat.ML",
+           "abstract": " x ", "versions": [{"created": "Mon"}, {"created": "Tue"}]},
+          {"id": "2301.2", "title": "B", "authors": "C. D. and E. F.", "categories": "math.AG", "abstract": "y"}]
+  p.write_text("\n".join(json.dumps(r) for r in rows))
+  got = list(load_metadata_snapshot(str(p), categories=["cs."]))
+  assert [g.arxiv_id for g in got] == ["2301.1"] and got[0].title == "A b" and got[0].authors == ["Ada Lovelace"]
+  assert got[0].submitted == "Mon" and got[0].updated == "Tue"
+  assert [g.authors for g in load_metadata_snapshot(str(p), categories=["math"])] == [["C. D.", "E. F."]]
