@@ -223,17 +223,23 @@ def main() -> None:
   ap.add_argument("--micro-batch", type=int, default=4)
   ap.add_argument("--seq-len", type=int, default=4096)
   ap.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (result is marked invalid)")
-  ap.add_argument("--dtype", default="fp8", choices=["bf16", "fp8", "nvfp4"],
+  ap.add_argument("--dtype", default=None, choices=["bf16", "fp8", "nvfp4"],
                   help="expert GEMM profile: fp8 = bf16 activations + block-scaled MXFP8 expert GEMMs (the headline configuration)")
   ap.add_argument("--ref-dtype", default="bf16", choices=["bf16", "fp8", "nvfp4"],
                   help="expert profile of the reference arm; its block-scaled profiles need its CuTe-DSL grouped GEMM, "
                        "which only travels to 1-GPU boxes")
   ap.add_argument("--no-e2e", action="store_true")
+  ap.add_argument("--config", default=None,
+                  help="a model TOML (configs/moonlet_swa.toml, configs/dsv2_slice.toml, ...) instead of the headline "
+                       "Moonlight-16B-A3B; its dtype applies unless --dtype is given, batch_size is split over the GPUs")
+  ap.add_argument("--zero2-impl", default=None, choices=["fused", "nccl"], help="ZeRO-2 implementation (default: fused peer kernel)")
   ap.add_argument("--overlap-shared", default="auto", choices=["auto", "0", "1"], help="shared-expert MLP on a second stream")
   ap.add_argument("--recompute-h13", action="store_true", help="recompute the experts' up/gate output in backward (saves ~16 GB on one GPU)")
   ap.add_argument("--activation-checkpoint", default="none", choices=["none", "attention", "full"],
                   help="activation recompute policy; 'none' keeps the ~4 GB of attention activations instead of recomputing them")
   args = ap.parse_args()
+  if args.dtype is None and args.config is None:
+    args.dtype = "fp8"
   if args.impl == "reference":
     run_reference(args)
     return
@@ -249,8 +255,26 @@ def main() -> None:
     if args.gpus > 1 and world_env == 1:
       raise SystemExit("--gpus N>1 must be launched with torch.distributed.run (one rank per GPU)")
   rank, world, device = runtime.init(42)
-  cfg = moonlight_cfg(world, args.micro_batch, args.seq_len, args.dtype, args.layers, args.activation_checkpoint,
-                      not args.recompute_h13, args.overlap_shared)
+  model_name = "moonlight-16b-a3b"
+  if args.config:
+    from nmoe_b200.config import from_toml
+    over = [f"--activation_checkpoint={args.activation_checkpoint}", f"--moe_save_h13={str(not args.recompute_h13).lower()}",
+            f"--moe_overlap_shared={args.overlap_shared}", "--data_path=synthetic"]
+    if args.dtype:
+      over.append(f"--dtype={args.dtype}")
+    if args.layers:
+      over.append(f"--n_layers={args.layers}")
+    cfg = from_toml(args.config, over, env={})
+    args.dtype = cfg.dtype
+    args.seq_len = cfg.seq_len
+    args.micro_batch = max(1, cfg.batch_size // max(1, world)) if cfg.batch_size >= world else args.micro_batch
+    cfg.batch_size = args.micro_batch * world
+    model_name = f"{cfg.preset} ({os.path.basename(args.config)})"
+  else:
+    cfg = moonlight_cfg(world, args.micro_batch, args.seq_len, args.dtype, args.layers, args.activation_checkpoint,
+                        not args.recompute_h13, args.overlap_shared)
+  if args.zero2_impl:
+    cfg.zero2_impl = args.zero2_impl
   trainer = Trainer(cfg, rank=rank, world=world, device=device)
   mb, S = args.micro_batch, args.seq_len
   gen = torch.Generator().manual_seed(1234 + rank)
@@ -323,14 +347,18 @@ def main() -> None:
     fpt = flops_per_token(cfg)
     tflops_per_gpu = tok_s / world * fpt / 1e12
     out = {
-      "metric": "training throughput, Moonlight-16B-A3B (tokens/s whole job; MFU alongside)",
+      "metric": ("training throughput, Moonlight-16B-A3B (tokens/s whole job; MFU alongside)" if not args.config
+                 else f"training throughput, {model_name} (tokens/s whole job)"),
       "value": tok_s, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
       "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
       "dtype": args.dtype, "data": "synthetic uniform-random token ids, random-init weights",
-      "config": {"model": "moonlight-16b-a3b" if args.layers is None else f"INVALID-debug-{args.layers}-layers",
+      "config": {"model": model_name if args.layers is None else f"INVALID-debug-{args.layers}-layers",
+                 "expert_gemms": {"fp8": "block-scaled MXFP8 (E4M3, E8M0 per 32)", "nvfp4": "block-scaled E2M1, E8M0 per 32",
+                                  "bf16": "bf16"}.get(args.dtype, args.dtype) + " forward, bf16 backward; bf16 activations",
                  "global_batch": world * mb, "seq_len": S,
                  "parallelism": (f"rdep-ep{world}+zero2-dp{world}" if world > 1 else "single-gpu"),
-                 "vocab": cfg.vocab_size, "layers": cfg.n_layers, "experts": "64 top-6 + 2 shared",
+                 "vocab": cfg.vocab_size, "layers": cfg.n_layers,
+                 "experts": f"{cfg.n_routed_experts} top-{cfg.n_activated_experts} + {cfg.n_shared_experts} shared",
                  "activation_checkpoint": args.activation_checkpoint, "moe_save_h13": not args.recompute_h13,
                  "l2": "per-step working set (32 GB of weights) is far larger than the 126 MB L2"},
       "tflops_per_gpu": tflops_per_gpu,

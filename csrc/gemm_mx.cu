@@ -354,6 +354,20 @@ k_gemm_mx(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
           tmem_ld_32x32b_x32(ta + 32, r + 32);
           tmem_ld_wait();
           if (!row_ok) continue;
+          if (p.C != nullptr) {
+            // the backward wants H13 itself: store the 64 bf16 values next to the quantised activation (one pass
+            // over the accumulator instead of a GEMM that writes H13 and a second kernel that reads it back)
+            int4* hrow = reinterpret_cast<int4*>(p.C + static_cast<long long>(row) * p.ldc + col);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              int4 h;
+              h.x = pack_bf16x2(__uint_as_float(r[8 * j]) * p.alpha, __uint_as_float(r[8 * j + 1]) * p.alpha);
+              h.y = pack_bf16x2(__uint_as_float(r[8 * j + 2]) * p.alpha, __uint_as_float(r[8 * j + 3]) * p.alpha);
+              h.z = pack_bf16x2(__uint_as_float(r[8 * j + 4]) * p.alpha, __uint_as_float(r[8 * j + 5]) * p.alpha);
+              h.w = pack_bf16x2(__uint_as_float(r[8 * j + 6]) * p.alpha, __uint_as_float(r[8 * j + 7]) * p.alpha);
+              hrow[j] = h;
+            }
+          }
           float v[32];
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
@@ -552,17 +566,32 @@ extern "C" int nmoe_gemm_nvfp4(const void* A, const void* sfa, const void* B, co
 // 128-aligned expert segments, B = W13 [E, 2F, K] with gate / up rows interleaved; writes act_q [a_rows, F]
 // (E4M3) or [a_rows, F/2] (E2M1 when fp4 != 0) and act_sf (atom layout for [a_rows, F]).  Operands are MXFP8
 // (fp4 == 0) or MXFP4 (fp4 != 0).  N = 2F must be a multiple of 128.
+extern "C" int nmoe_gemm_mx_swiglu_quant_h13(const void* A, const void* sfa, const void* B, const void* sfb, void* act_q,
+                                             void* act_sf, void* h13, int M, int N, int K, int E, const int* tile_expert,
+                                             const int* n_m_tiles, long long a_rows, long long b_rows, int fp4, int bn,
+                                             void* status, cudaStream_t st);
+
 extern "C" int nmoe_gemm_mx_swiglu_quant(const void* A, const void* sfa, const void* B, const void* sfb, void* act_q,
                                          void* act_sf, int M, int N, int K, int E, const int* tile_expert,
                                          const int* n_m_tiles, long long a_rows, long long b_rows, int fp4, int bn,
                                          void* status, cudaStream_t st) {
+  return nmoe_gemm_mx_swiglu_quant_h13(A, sfa, B, sfb, act_q, act_sf, nullptr, M, N, K, E, tile_expert, n_m_tiles, a_rows,
+                                       b_rows, fp4, bn, status, st);
+}
+
+// Same, and when h13 != nullptr the epilogue also writes the bf16 up/gate output H13 [a_rows, N] (for a backward that
+// keeps it instead of recomputing it).
+extern "C" int nmoe_gemm_mx_swiglu_quant_h13(const void* A, const void* sfa, const void* B, const void* sfb, void* act_q,
+                                             void* act_sf, void* h13, int M, int N, int K, int E, const int* tile_expert,
+                                             const int* n_m_tiles, long long a_rows, long long b_rows, int fp4, int bn,
+                                             void* status, cudaStream_t st) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || (K % (fp4 ? 128 : 32)) != 0 || (N % 128) != 0) return -1;
   if (bn == 0) bn = (N % 256 == 0) ? 256 : 128;
   if (bn != 128 && bn != 256) return -5;
   MxParams p;
   p.M = M; p.N = N; p.K = K; p.E = E; p.tile_expert = tile_expert; p.n_m_tiles = n_m_tiles;
-  p.C = nullptr; p.ldc = N;
+  p.C = static_cast<__nv_bfloat16*>(h13); p.ldc = N;
   p.sfa = static_cast<const uint8_t*>(sfa); p.sfb = static_cast<const uint8_t*>(sfb);
   p.status = static_cast<StatusRecord*>(status);
   p.row_meta = nullptr; p.push_use_gate = 0; p.push_bulk = 0; p.alpha = 1.f;

@@ -192,9 +192,11 @@ def swiglu_quant_mxfp4(h13: torch.Tensor, n_tiles: Optional[torch.Tensor] = None
 
 
 def grouped_gemm_swiglu_quant(aq: torch.Tensor, asf: torch.Tensor, bq: torch.Tensor, bsf: torch.Tensor,
-                              tile_expert: torch.Tensor, n_m_tiles: torch.Tensor, *, fp4: bool = False, bn: int = 0):
+                              tile_expert: torch.Tensor, n_m_tiles: torch.Tensor, *, fp4: bool = False, bn: int = 0,
+                              want_h13: bool = False):
   """Grouped up/gate projection whose epilogue applies SwiGLU and re-quantises: returns the quantised
-  activation (E4M3 [Mcap,F] or E2M1 [Mcap,F/2]) and its scale atoms; the bf16 H13 is never written.
+  activation (E4M3 [Mcap,F] or E2M1 [Mcap,F/2]) and its scale atoms.  The bf16 H13 is not written unless
+  ``want_h13`` (then it is returned as a third value, stored by the same epilogue pass).
   ``bq`` = W13 [E, 2F, K(/2)] with gate / up rows interleaved."""
   Mcap = aq.size(0)
   K = aq.size(1) * (2 if fp4 else 1)
@@ -205,10 +207,12 @@ def grouped_gemm_swiglu_quant(aq: torch.Tensor, asf: torch.Tensor, bq: torch.Ten
   if (F // 32) % 4:
     sf.fill_(127)            # partial last atom: padding scale bytes must be valid
   st = status_buffer(aq.device)
-  L.check(L.lib().nmoe_gemm_mx_swiglu_quant(L.ptr(aq), L.ptr(asf), L.ptr(bq), L.ptr(bsf), L.ptr(q), L.ptr(sf), Mcap, N, K, E,
-                                            L.ptr(tile_expert), L.ptr(n_m_tiles), L.c_ll(Mcap), L.c_ll(E * N), int(fp4), bn,
-                                            L.ptr(st), L.stream()), "grouped_gemm_swiglu_quant")
-  return q, sf
+  h13 = torch.empty(Mcap, N, dtype=torch.bfloat16, device=aq.device) if want_h13 else None
+  L.check(L.lib().nmoe_gemm_mx_swiglu_quant_h13(L.ptr(aq), L.ptr(asf), L.ptr(bq), L.ptr(bsf), L.ptr(q), L.ptr(sf),
+                                                L.ptr(h13), Mcap, N, K, E, L.ptr(tile_expert), L.ptr(n_m_tiles),
+                                                L.c_ll(Mcap), L.c_ll(E * N), int(fp4), bn, L.ptr(st), L.stream()),
+          "grouped_gemm_swiglu_quant")
+  return (q, sf, h13) if want_h13 else (q, sf)
 
 
 def is_fp4(profile: str) -> bool:

@@ -286,9 +286,13 @@ class _MoEFused(torch.autograd.Function):
         rdep.place_mx(x, plan, gates32.view(-1))
         rdep.wait_data()
       ggemm = Q.grouped_gemm_mxfp4 if rdep.fp4 else Q.grouped_gemm_mxfp8
-      if save_h13 or not rdep.fused_swiglu_quant:
+      if not rdep.fused_swiglu_quant:
         h13 = ggemm(rdep.xq[:rows], rdep.sfa, W13q, W13sf, plan.tile_expert, plan.n_m_tiles)
         aq, asf = (Q.swiglu_quant_mxfp4 if rdep.fp4 else Q.swiglu_quant_mxfp8)(h13, plan.n_m_tiles)
+      elif save_h13:
+        # one epilogue pass writes both the quantised activation and the bf16 H13 that the backward keeps
+        aq, asf, h13 = Q.grouped_gemm_swiglu_quant(rdep.xq[:rows], rdep.sfa, W13q, W13sf, plan.tile_expert,
+                                                   plan.n_m_tiles, fp4=rdep.fp4, want_h13=True)
       else:
         # SwiGLU and the re-quantisation happen in the epilogue of the up/gate projection: H13 is never written
         h13 = None

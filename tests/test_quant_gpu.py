@@ -230,6 +230,12 @@ def test_fused_swiglu_quant_epilogue_matches_unfused(fp4):
   su = RQ.sf_from_mma_layout(asf_u.cpu(), rows, cols)[:, :F // 32]
   sf_ = RQ.sf_from_mma_layout(asf_f.cpu(), rows, cols)[:, :F // 32]
   assert torch.equal(su, sf_)
+  # the variant that also keeps H13 for the backward: same quantised activation, H13 bit-equal to the plain GEMM's
+  aq_h, asf_h, h13_h = Q.grouped_gemm_swiglu_quant(xq, xsf, wq, wsf, tile_expert, n_tiles, fp4=fp4, want_h13=True)
+  torch.cuda.synchronize()
+  G.check_status()
+  assert torch.equal(aq_h, aq_u) and torch.equal(h13_h, h13)
+  assert torch.equal(RQ.sf_from_mma_layout(asf_h.cpu(), rows, cols)[:, :F // 32], su)
 
 
 @pytest.mark.parametrize("profile", ["fp8", "nvfp4"])
