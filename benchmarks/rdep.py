@@ -10,8 +10,8 @@ after a barrier; the reported time is the max over ranks.  One JSON line per tok
   dispatch_us   count + plan (count exchange over peer stores) + placement stores into the owners'
                 buffers (quantising for fp8 / nvfp4) + wait for every source's data flag
   gemm13_us     grouped up/gate projection + SwiGLU (fused quantise for fp8 / nvfp4)
-  gemm2_ret_us  grouped down projection whose epilogue pushes gate-scaled rows to the sources,
-                + flag exchange + the K-way sum at the source
+  gemm2_ret_us  grouped down projection whose epilogue streams each (expert, source) run of rows into the
+                source's return buffer, + flag exchange + the gate-weighted K-way sum at the source
   nvlink_gbs    bytes this rank stored to OTHER ranks during dispatch and return / their time
                 (fraction of the 900 GB/s per-direction link also given)
 
@@ -132,13 +132,13 @@ def main():
             dmarks[1].record()
             barrier()                      # every rank starts its push together
             dmarks[2].record()
-          rd.push_and_reduce(y, plan, True, None, out, marks=dmarks[3:5] if dmarks else None)
+          rd.push_and_reduce(y, plan, gates.view(-1), None, out, marks=dmarks[3:5] if dmarks else None)
         else:
           if quantised:
-            gg(aq, asf, wq[2], wq[3], plan.tile_expert, plan.n_m_tiles, push=rd.push_args(True))
+            gg(aq, asf, wq[2], wq[3], plan.tile_expert, plan.n_m_tiles, push=rd.push_args(plan))
           else:
-            G.grouped_gemm(act, W2, plan.tile_expert, plan.n_m_tiles, push=rd.push_args(True), align256=rd.align == 256)
-          rd.finish_return(plan, out)
+            G.grouped_gemm(act, W2, plan.tile_expert, plan.n_m_tiles, push=rd.push_args(plan), align256=rd.align == 256)
+          rd.finish_return(plan, out, gates.view(-1))
         if marks:
           marks[3].record()
         return plan

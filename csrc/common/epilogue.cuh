@@ -25,6 +25,26 @@ inline int epi_push_bulk_enabled(bool mx = false) {
   return r;
 }
 
+// Return runs of the expert-parallel layer (csrc/rdep.cu): inside an expert's segment of the owner's buffer the rows of
+// one source rank are contiguous, and they go back as one contiguous block of that source's return buffer.
+// runs = [3][n_local][world]: first row of the run in the owner's buffer, its length, its first row at the source.
+// Which source owns row r of the owner's buffer (expert le), and where the row goes in that source's return buffer.
+// False for padding rows and for rows of a dropped expert.
+NMOE_DEVICE bool run_lookup(const int* __restrict__ runs, int n_local, int world, int le, int r, int& src, int& drow) {
+  const int nlw = n_local * world;
+  const int* start = runs + le * world;
+#pragma unroll 1
+  for (int s = 0; s < world; ++s) {
+    const int off = r - __ldg(start + s);
+    if (off >= 0 && off < __ldg(start + nlw + s)) {
+      src = s;
+      drow = __ldg(start + 2 * nlw + s) + off;
+      return true;
+    }
+  }
+  return false;
+}
+
 constexpr int kEpiStageBytesPerWarp = 32 * 128;
 
 // r: 64 fp32 accumulator values (as bits) of this lane's row; scale: multiplier applied before

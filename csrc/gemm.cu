@@ -47,15 +47,16 @@ struct GemmParams {
   int accumulate;              // C += result instead of C = result
   long long b_rows_per_expert; // mode 1: rows of B's 2-D view per expert
   StatusRecord* status;
-  // Fused RDEP return (mode 1, bf16 output): when row_meta != nullptr the epilogue does not write C;
-  // it multiplies row r by its gate (push_use_gate) and stores it into the SOURCE rank's return
-  // buffer peer_ret[src] at row tok_slot (16-byte system-scope stores over NVLink), and forwards the
-  // optional per-row scalar rowval[r] to peer_retg[src][tok_slot].
-  const int4* row_meta;        // {src_rank, tok_slot, gate bits, valid} per row
+  // Fused RDEP return (mode 1, bf16 output): when push_runs != nullptr the epilogue does not write C; it stores
+  // row r into the SOURCE rank's return buffer peer_ret[src] at the row the run tables give (rows of one source are
+  // contiguous in the segment and at the destination, so a tile's rows stream to consecutive remote rows), and
+  // forwards the optional per-row scalar rowval[r] to peer_retg[src] at the same row.  Gates are applied by the
+  // source when it sums its slots.
+  const int* push_runs;        // [3][E][world] return-run tables from nmoe_rdep_plan (non-null selects the fused return)
   __nv_bfloat16* peer_ret[8];
   float* peer_retg[8];
   const float* rowval;
-  int push_use_gate;
+  int push_world, push_pairs;  // ranks in the run tables; rows of a source's return buffer (bound)
   int push_bulk;               // 1: the fused return hands 256-byte row segments to the bulk-copy unit
   // Mode 3 (sparse-attention indexer): rows of A are keys, columns of B are (query, head) pairs; the epilogue
   // writes C[query][key] = sum_head idx_w[query*heads + head] * relu(acc), -inf above the diagonal when causal.
@@ -303,14 +304,15 @@ k_gemm_bf16(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       bool row_ok = row < m_limit;
       __nv_bfloat16* push_dst = nullptr;
       float push_gate = 1.f;
-      if (MODE == 1 && p.row_meta != nullptr && row_ok) {
-        const int4 mv = __ldg(p.row_meta + row);
-        // a stale or torn meta record must not become a wild store into a peer: unknown source ranks are skipped
-        row_ok = mv.w != 0 && static_cast<unsigned>(mv.x) < 8u && p.peer_ret[mv.x & 7] != nullptr && mv.y >= 0;
+      if (MODE == 1 && p.push_runs != nullptr && row_ok) {
+        // rows of one source are contiguous in an expert's segment and land contiguously at that source:
+        // consecutive rows of this tile go to consecutive destination rows
+        int src = 0, drow = 0;
+        row_ok = run_lookup(p.push_runs, p.E, p.push_world, tc.expert, row, src, drow) && drow >= 0 && drow < p.push_pairs &&
+                 p.peer_ret[src & 7] != nullptr;
         if (row_ok) {
-          push_dst = p.peer_ret[mv.x] + static_cast<long long>(mv.y) * p.ldc;
-          if (p.push_use_gate) push_gate = __int_as_float(mv.z);
-          if (tc.n_blk == 0 && p.rowval != nullptr) p.peer_retg[mv.x][mv.y] = p.rowval[row];
+          push_dst = p.peer_ret[src] + static_cast<long long>(drow) * p.ldc;
+          if (tc.n_blk == 0 && p.rowval != nullptr) p.peer_retg[src][drow] = p.rowval[row];
         }
       }
       const long long crow = (MODE == 2) ? static_cast<long long>(tc.expert) * p.M + row : row;
@@ -325,7 +327,7 @@ k_gemm_bf16(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         }
         tc_fence_after_sync();
       }
-      if (MODE == 1 && p.row_meta != nullptr && have_acc && p.push_bulk && (p.N & 127) == 0 && (p.ldc & 7) == 0) {
+      if (MODE == 1 && p.push_runs != nullptr && have_acc && p.push_bulk && (p.N & 127) == 0 && (p.ldc & 7) == 0) {
         // fused return through the copy unit: 128 columns (256 bytes) of this lane's row per bulk copy
         uint8_t* srow = EpiBulk<256>::row(epi_stage + (warp - 2) * S::kEpiWarp, lane);
         __nv_bfloat16* dst0 = (row_ok && push_dst != nullptr) ? push_dst : nullptr;
@@ -346,7 +348,7 @@ k_gemm_bf16(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           }
         }
         used_bulk = true;
-      } else if (MODE == 1 && p.row_meta != nullptr && have_acc && (p.N & 63) == 0 && (p.ldc & 7) == 0) {
+      } else if (MODE == 1 && p.push_runs != nullptr && have_acc && (p.N & 63) == 0 && (p.ldc & 7) == 0) {
         // fused return, coalesced: 64 columns (128 bytes) of 4 rows per store instruction
         uint8_t* stage = epi_stage + (warp - 2) * S::kEpiWarp;
 #pragma unroll 1
@@ -487,7 +489,7 @@ k_gemm_bf16(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   if (*abort_flag) {
     for (int i = 0; i < 2000; ++i) __nanosleep(1000);
   }
-  if (MODE == 1 && p.row_meta != nullptr) __threadfence_system();
+  if (MODE == 1 && p.push_runs != nullptr) __threadfence_system();
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 1) {
@@ -574,8 +576,8 @@ extern "C" {
 int nmoe_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
                    long long ldc, int a_mn, int b_mn, int mode, int E, const int* tile_expert, const int* n_m_tiles,
                    const int* offs, long long a_rows, long long b_rows, int out_fp32, int accumulate, int bn,
-                   void* status, const void* row_meta, void* const* peer_ret, void* const* peer_retg,
-                   const float* rowval, int push_use_gate, int world, cudaStream_t st) {
+                   void* status, const void* push_runs, void* const* peer_ret, void* const* peer_retg,
+                   const float* rowval, int push_pairs, int world, cudaStream_t st) {
   if (M <= 0 || N <= 0) return 0;
   if (mode != 2 && K <= 0) return -1;
   if ((lda % 8) || (ldb % 8)) return -2;
@@ -590,16 +592,16 @@ int nmoe_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, l
   p.C = C; p.ldc = ldc; p.out_fp32 = out_fp32; p.accumulate = accumulate;
   p.b_rows_per_expert = (mode == 1) ? (b_mn ? K : N) : 0;
   p.status = static_cast<StatusRecord*>(status);
-  p.row_meta = static_cast<const int4*>(row_meta);
+  p.push_runs = static_cast<const int*>(push_runs);
   p.rowval = rowval;
-  p.push_use_gate = push_use_gate;
+  p.push_pairs = push_pairs; p.push_world = world;
   p.push_bulk = epi_push_bulk_enabled();
   p.idx_w = nullptr; p.idx_heads = 1; p.idx_causal = 0;
   for (int r = 0; r < 8; ++r) {
-    p.peer_ret[r] = (row_meta && peer_ret && r < world) ? static_cast<__nv_bfloat16*>(peer_ret[r]) : nullptr;
-    p.peer_retg[r] = (row_meta && peer_retg && r < world) ? static_cast<float*>(peer_retg[r]) : nullptr;
+    p.peer_ret[r] = (push_runs && peer_ret && r < world) ? static_cast<__nv_bfloat16*>(peer_ret[r]) : nullptr;
+    p.peer_retg[r] = (push_runs && peer_retg && r < world) ? static_cast<float*>(peer_retg[r]) : nullptr;
   }
-  if (row_meta && (mode != 1 || out_fp32 || world > 8)) return -6;
+  if (push_runs && (mode != 1 || out_fp32 || world > 8)) return -6;
 
   // Tensor maps.  a_rows / b_rows are the outer extents of the 2-D views (rows in memory).
   CUtensorMap tmA, tmB;
@@ -641,7 +643,7 @@ int nmoe_dsa_indexer_scores(const void* k, const void* q, const float* w, float*
   p.C = out; p.ldc = ldo; p.out_fp32 = 1; p.accumulate = 0;
   p.b_rows_per_expert = 0;
   p.status = static_cast<StatusRecord*>(status);
-  p.row_meta = nullptr; p.rowval = nullptr; p.push_use_gate = 0; p.push_bulk = 0;
+  p.push_runs = nullptr; p.rowval = nullptr; p.push_pairs = 0; p.push_world = 0; p.push_bulk = 0;
   for (int r = 0; r < 8; ++r) { p.peer_ret[r] = nullptr; p.peer_retg[r] = nullptr; }
   p.idx_w = w; p.idx_heads = heads; p.idx_causal = causal;
   CUtensorMap tmA, tmB;

@@ -44,11 +44,11 @@ struct Gemm2Params {
   long long b_rows_per_expert;
   StatusRecord* status;
   // fused RDEP return (mode 1, bf16): see GemmParams in gemm.cu
-  const int4* row_meta;
+  const int* push_runs;        // [3][E][world] return-run tables from nmoe_rdep_plan (non-null selects the fused return)
   __nv_bfloat16* peer_ret[8];
   float* peer_retg[8];
   const float* rowval;
-  int push_use_gate;
+  int push_world, push_pairs;  // ranks in the run tables; rows of a source's return buffer (bound)
   int push_bulk;               // 1: the fused return hands 256-byte row segments to the bulk-copy unit
 };
 
@@ -300,14 +300,13 @@ k_gemm_bf16_pair(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const bool have_acc = tc.kb_count > 0;
       __nv_bfloat16* push_dst = nullptr;
       float push_gate = 1.f;
-      if (MODE == 1 && p.row_meta != nullptr && row_ok) {
-        const int4 mv = __ldg(p.row_meta + row);
-        // a stale or torn meta record must not become a wild store into a peer: unknown source ranks are skipped
-        row_ok = mv.w != 0 && static_cast<unsigned>(mv.x) < 8u && p.peer_ret[mv.x & 7] != nullptr && mv.y >= 0;
+      if (MODE == 1 && p.push_runs != nullptr && row_ok) {
+        int src = 0, drow = 0;
+        row_ok = run_lookup(p.push_runs, p.E, p.push_world, tc.expert, row, src, drow) && drow >= 0 && drow < p.push_pairs &&
+                 p.peer_ret[src & 7] != nullptr;
         if (row_ok) {
-          push_dst = p.peer_ret[mv.x] + static_cast<long long>(mv.y) * p.ldc;
-          if (p.push_use_gate) push_gate = __int_as_float(mv.z);
-          if (tc.n_blk == 0 && p.rowval != nullptr) p.peer_retg[mv.x][mv.y] = p.rowval[row];
+          push_dst = p.peer_ret[src] + static_cast<long long>(drow) * p.ldc;
+          if (tc.n_blk == 0 && p.rowval != nullptr) p.peer_retg[src][drow] = p.rowval[row];
         }
       }
       if (have_acc) {
@@ -320,7 +319,7 @@ k_gemm_bf16_pair(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
         tc_fence_after_sync();
       }
-      if (MODE == 1 && p.row_meta != nullptr && have_acc && p.push_bulk && (p.N & 127) == 0 && (p.ldc & 7) == 0) {
+      if (MODE == 1 && p.push_runs != nullptr && have_acc && p.push_bulk && (p.N & 127) == 0 && (p.ldc & 7) == 0) {
         // fused return through the copy unit: 128 columns (256 bytes) of this lane's row per bulk copy
         uint8_t* srow = EpiBulk<256>::row(epi_stage + (warp - 2) * kG2EpiWarp, lane);
         __nv_bfloat16* dst0 = (row_ok && push_dst != nullptr) ? push_dst : nullptr;
@@ -341,7 +340,7 @@ k_gemm_bf16_pair(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
         }
         used_bulk = true;
-      } else if (MODE == 1 && p.row_meta != nullptr && have_acc) {
+      } else if (MODE == 1 && p.push_runs != nullptr && have_acc) {
         // fused return, coalesced: 64 columns (128 bytes) of 4 rows per store instruction
         uint8_t* stage = epi_stage + (warp - 2) * kG2EpiWarp;
 #pragma unroll 1
@@ -426,7 +425,7 @@ k_gemm_bf16_pair(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   if (*abort_flag) {
     for (int i = 0; i < 2000; ++i) __nanosleep(1000);
   }
-  if (MODE == 1 && p.row_meta != nullptr) __threadfence_system();
+  if (MODE == 1 && p.push_runs != nullptr) __threadfence_system();
   tc_fence_before_sync();
   cluster_sync_all();                 // neither CTA may free tensor memory or exit while its partner still uses the pair
   if (warp == 1) {
@@ -475,16 +474,16 @@ static int g2_launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const Gemm2
 
 using namespace nmoe;
 
-// Same contract as nmoe_gemm_bf16 including the fused RDEP return (row_meta / peer_ret / peer_retg / rowval);
+// Same contract as nmoe_gemm_bf16 including the fused RDEP return (push_runs / peer_ret / peer_retg / rowval);
 // N tile is fixed at 256 and grouped row segments must be 256-aligned.
 extern "C" int nmoe_gemm_bf16_pair_push(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
                                         long long ldb, long long ldc, int a_mn, int b_mn, int mode, int E,
                                         const int* tile_expert, const int* n_m_tiles, const int* offs, long long a_rows,
-                                        long long b_rows, int out_fp32, int accumulate, void* status, const void* row_meta,
+                                        long long b_rows, int out_fp32, int accumulate, void* status, const void* push_runs,
                                         void* const* peer_ret, void* const* peer_retg, const float* rowval,
-                                        int push_use_gate, int world, cudaStream_t st) {
+                                        int push_pairs, int world, cudaStream_t st) {
   if (M <= 0 || N <= 0) return 0;
-  if (row_meta && (mode != 1 || out_fp32 || world > 8 || (N & 63) != 0 || (ldc & 7) != 0)) return -6;
+  if (push_runs && (mode != 1 || out_fp32 || world > 8 || (N & 63) != 0 || (ldc & 7) != 0)) return -6;
   if (mode != 2 && K <= 0) return -1;
   if ((lda % 8) || (ldb % 8)) return -2;
   if (mode == 2 && !(a_mn && b_mn)) return -3;
@@ -494,11 +493,11 @@ extern "C" int nmoe_gemm_bf16_pair_push(const void* A, const void* B, void* C, i
   p.C = C; p.ldc = ldc; p.out_fp32 = out_fp32; p.accumulate = accumulate;
   p.b_rows_per_expert = (mode == 1) ? (b_mn ? K : N) : 0;
   p.status = static_cast<StatusRecord*>(status);
-  p.row_meta = static_cast<const int4*>(row_meta); p.rowval = rowval; p.push_use_gate = push_use_gate;
+  p.push_runs = static_cast<const int*>(push_runs); p.rowval = rowval; p.push_pairs = push_pairs; p.push_world = world;
   p.push_bulk = epi_push_bulk_enabled();
   for (int r = 0; r < 8; ++r) {
-    p.peer_ret[r] = (row_meta && peer_ret && r < world) ? static_cast<__nv_bfloat16*>(peer_ret[r]) : nullptr;
-    p.peer_retg[r] = (row_meta && peer_retg && r < world) ? static_cast<float*>(peer_retg[r]) : nullptr;
+    p.peer_ret[r] = (push_runs && peer_ret && r < world) ? static_cast<__nv_bfloat16*>(peer_ret[r]) : nullptr;
+    p.peer_retg[r] = (push_runs && peer_retg && r < world) ? static_cast<float*>(peer_retg[r]) : nullptr;
   }
   CUtensorMap tmA, tmB;
   int rc;

@@ -48,9 +48,9 @@ struct MxParams {
   const uint8_t* sfa;          // A scales, atoms [M/128][K/128]
   const uint8_t* sfb;          // B scales, atoms [(E*N)/128][K/128]
   StatusRecord* status;
-  const int4* row_meta;
+  const int* push_runs;        // [3][E][world] return-run tables from nmoe_rdep_plan (non-null selects the fused return)
   __nv_bfloat16* peer_ret[8];
-  int push_use_gate;
+  int push_world, push_pairs;  // ranks in the run tables; rows of a source's return buffer (bound)
   int push_bulk;               // 1: the fused return hands 128-byte row segments to the bulk-copy unit
   float alpha;                 // multiplies every output (NVFP4: product of the two per-tensor scales)
   // fused SwiGLU + quantise epilogue (act_q != nullptr): instead of C [rows, N], write the quantised
@@ -290,14 +290,11 @@ k_gemm_mx(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
       bool row_ok = row < m_limit;
       __nv_bfloat16* dst_row = row_ok ? p.C + static_cast<long long>(row) * p.ldc : nullptr;
       float gate = p.alpha;
-      if (MODE == 1 && p.row_meta != nullptr && row_ok) {
-        const int4 mv = __ldg(p.row_meta + row);
-        // a stale or torn meta record must not become a wild store into a peer: unknown source ranks are skipped
-        row_ok = mv.w != 0 && static_cast<unsigned>(mv.x) < 8u && p.peer_ret[mv.x & 7] != nullptr && mv.y >= 0;
-        if (row_ok) {
-          dst_row = p.peer_ret[mv.x] + static_cast<long long>(mv.y) * p.ldc;
-          if (p.push_use_gate) gate = p.alpha * __int_as_float(mv.z);
-        }
+      if (MODE == 1 && p.push_runs != nullptr && row_ok) {
+        int src = 0, drow = 0;
+        row_ok = run_lookup(p.push_runs, p.E, p.push_world, expert, row, src, drow) && drow >= 0 && drow < p.push_pairs &&
+                 p.peer_ret[src & 7] != nullptr;
+        if (row_ok) dst_row = p.peer_ret[src] + static_cast<long long>(drow) * p.ldc;
       }
       bool ok = mx_wait(&tmem_full[acc], acc_phase, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
@@ -307,7 +304,7 @@ k_gemm_mx(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
         break;
       }
       tc_fence_after_sync();
-      if (MODE == 1 && p.row_meta != nullptr && p.push_bulk && (p.N & 63) == 0 && (p.ldc & 7) == 0) {
+      if (MODE == 1 && p.push_runs != nullptr && p.push_bulk && (p.N & 63) == 0 && (p.ldc & 7) == 0) {
         // fused return through the copy unit: 64 columns (128 bytes) of this lane's row per bulk copy
         uint8_t* srow = EpiBulk<128>::row(epi_stage + (warp - 2) * S::kEpiWarp, lane);
 #pragma unroll 1
@@ -325,7 +322,7 @@ k_gemm_mx(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
           epi_bulk_store(row_ok ? dst_row + col : nullptr, srow, 128);
         }
         used_bulk = true;
-      } else if (MODE == 1 && p.row_meta != nullptr && (p.N & 63) == 0 && (p.ldc & 7) == 0) {
+      } else if (MODE == 1 && p.push_runs != nullptr && (p.N & 63) == 0 && (p.ldc & 7) == 0) {
         // fused return, coalesced: 64 columns (128 bytes) of 4 rows per store instruction
         uint8_t* stage = epi_stage + (warp - 2) * S::kEpiWarp;
 #pragma unroll 1
@@ -425,7 +422,7 @@ k_gemm_mx(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
   if (*abort_flag) {
     for (int i = 0; i < 2000; ++i) __nanosleep(1000);
   }
-  if (MODE == 1 && p.row_meta != nullptr) __threadfence_system();
+  if (MODE == 1 && p.push_runs != nullptr) __threadfence_system();
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 1) {
@@ -474,11 +471,11 @@ static int mx_launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const MxPar
 using namespace nmoe;
 
 // A: [a_rows, K] e4m3 bytes, sfa: its scales; B: [b_rows, K] e4m3 (b_rows = N, or E*N for mode 1), sfb likewise.
-// C: bf16 [*, ldc].  mode 1 additionally takes the tile table; row_meta/peer_ret select the fused RDEP return.
+// C: bf16 [*, ldc].  mode 1 additionally takes the tile table; push_runs/peer_ret select the fused RDEP return (see gemm.cu).
 extern "C" int nmoe_gemm_mxfp8(const void* A, const void* sfa, const void* B, const void* sfb, void* C, int M, int N,
                                int K, long long ldc, int mode, int E, const int* tile_expert, const int* n_m_tiles,
-                               long long a_rows, long long b_rows, int bn, void* status, const void* row_meta,
-                               void* const* peer_ret, int push_use_gate, int world, cudaStream_t st) {
+                               long long a_rows, long long b_rows, int bn, void* status, const void* push_runs,
+                               void* const* peer_ret, int push_pairs, int world, cudaStream_t st) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || (K % 32) != 0) return -1;         // a K tail shorter than 128 is zero-filled by TMA; its scale bytes are padding (127)
   if (mode == 1 && (N % 128) != 0) return -2;
@@ -489,10 +486,11 @@ extern "C" int nmoe_gemm_mxfp8(const void* A, const void* sfa, const void* B, co
   p.C = static_cast<__nv_bfloat16*>(C); p.ldc = ldc;
   p.sfa = static_cast<const uint8_t*>(sfa); p.sfb = static_cast<const uint8_t*>(sfb);
   p.status = static_cast<StatusRecord*>(status);
-  p.row_meta = static_cast<const int4*>(row_meta); p.push_use_gate = push_use_gate; p.push_bulk = epi_push_bulk_enabled(true); p.alpha = 1.f; p.act_q = nullptr; p.act_sf = nullptr; p.act_sf_cols = 0; p.act_fp4 = 0;
+  p.push_runs = static_cast<const int*>(push_runs); p.push_pairs = push_pairs; p.push_world = world;
+  p.push_bulk = epi_push_bulk_enabled(true); p.alpha = 1.f; p.act_q = nullptr; p.act_sf = nullptr; p.act_sf_cols = 0; p.act_fp4 = 0;
   for (int r = 0; r < 8; ++r)
-    p.peer_ret[r] = (row_meta && peer_ret && r < world) ? static_cast<__nv_bfloat16*>(peer_ret[r]) : nullptr;
-  if (row_meta && mode != 1) return -6;
+    p.peer_ret[r] = (push_runs && peer_ret && r < world) ? static_cast<__nv_bfloat16*>(peer_ret[r]) : nullptr;
+  if (push_runs && (mode != 1 || world > 8)) return -6;
   CUtensorMap tmA, tmB;
   int rc = mx_cached_map(&tmA, A, K, a_rows, K, MX_BK, MX_BM);
   if (rc != 0) return rc;
@@ -507,8 +505,8 @@ extern "C" int nmoe_gemm_mxfp8(const void* A, const void* sfa, const void* B, co
 // scales as for MXFP8 (E8M0 per 32 elements, atom layout).  K counts elements; K % 128 == 0.
 extern "C" int nmoe_gemm_mxfp4(const void* A, const void* sfa, const void* B, const void* sfb, void* C, int M, int N,
                                int K, long long ldc, int mode, int E, const int* tile_expert, const int* n_m_tiles,
-                               long long a_rows, long long b_rows, int bn, void* status, const void* row_meta,
-                               void* const* peer_ret, int push_use_gate, int world, cudaStream_t st) {
+                               long long a_rows, long long b_rows, int bn, void* status, const void* push_runs,
+                               void* const* peer_ret, int push_pairs, int world, cudaStream_t st) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || (K % MX_BK) != 0) return -1;
   if (mode == 1 && (N % 128) != 0) return -2;
@@ -519,10 +517,11 @@ extern "C" int nmoe_gemm_mxfp4(const void* A, const void* sfa, const void* B, co
   p.C = static_cast<__nv_bfloat16*>(C); p.ldc = ldc;
   p.sfa = static_cast<const uint8_t*>(sfa); p.sfb = static_cast<const uint8_t*>(sfb);
   p.status = static_cast<StatusRecord*>(status);
-  p.row_meta = static_cast<const int4*>(row_meta); p.push_use_gate = push_use_gate; p.push_bulk = epi_push_bulk_enabled(true); p.alpha = 1.f; p.act_q = nullptr; p.act_sf = nullptr; p.act_sf_cols = 0; p.act_fp4 = 0;
+  p.push_runs = static_cast<const int*>(push_runs); p.push_pairs = push_pairs; p.push_world = world;
+  p.push_bulk = epi_push_bulk_enabled(true); p.alpha = 1.f; p.act_q = nullptr; p.act_sf = nullptr; p.act_sf_cols = 0; p.act_fp4 = 0;
   for (int r = 0; r < 8; ++r)
-    p.peer_ret[r] = (row_meta && peer_ret && r < world) ? static_cast<__nv_bfloat16*>(peer_ret[r]) : nullptr;
-  if (row_meta && mode != 1) return -6;
+    p.peer_ret[r] = (push_runs && peer_ret && r < world) ? static_cast<__nv_bfloat16*>(peer_ret[r]) : nullptr;
+  if (push_runs && (mode != 1 || world > 8)) return -6;
   CUtensorMap tmA, tmB;
   int rc = mx_cached_map(&tmA, A, K / 2, a_rows, K / 2, MX_BK, MX_BM);
   if (rc != 0) return rc;
@@ -549,7 +548,7 @@ extern "C" int nmoe_gemm_nvfp4(const void* A, const void* sfa, const void* B, co
   p.C = static_cast<__nv_bfloat16*>(C); p.ldc = ldc;
   p.sfa = static_cast<const uint8_t*>(sfa); p.sfb = static_cast<const uint8_t*>(sfb);
   p.status = static_cast<StatusRecord*>(status);
-  p.row_meta = nullptr; p.push_use_gate = 0; p.push_bulk = 0; p.alpha = alpha; p.act_q = nullptr; p.act_sf = nullptr; p.act_sf_cols = 0; p.act_fp4 = 0;
+  p.push_runs = nullptr; p.push_pairs = 0; p.push_world = 0; p.push_bulk = 0; p.alpha = alpha; p.act_q = nullptr; p.act_sf = nullptr; p.act_sf_cols = 0; p.act_fp4 = 0;
   for (int r = 0; r < 8; ++r) p.peer_ret[r] = nullptr;
   CUtensorMap tmA, tmB;
   int rc = mx_cached_map(&tmA, A, K / 2, a_rows, K / 2, MX_BK, MX_BM);
@@ -594,7 +593,7 @@ extern "C" int nmoe_gemm_mx_swiglu_quant_h13(const void* A, const void* sfa, con
   p.C = static_cast<__nv_bfloat16*>(h13); p.ldc = N;
   p.sfa = static_cast<const uint8_t*>(sfa); p.sfb = static_cast<const uint8_t*>(sfb);
   p.status = static_cast<StatusRecord*>(status);
-  p.row_meta = nullptr; p.push_use_gate = 0; p.push_bulk = 0; p.alpha = 1.f;
+  p.push_runs = nullptr; p.push_pairs = 0; p.push_world = 0; p.push_bulk = 0; p.alpha = 1.f;
   for (int r = 0; r < 8; ++r) p.peer_ret[r] = nullptr;
   p.act_q = static_cast<uint8_t*>(act_q); p.act_sf = static_cast<uint8_t*>(act_sf);
   p.act_sf_cols = (((N / 2) / 32) + 3) & ~3; p.act_fp4 = fp4;

@@ -17,8 +17,8 @@
 extern "C" int nmoe_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
                               long long ldc, int a_mn, int b_mn, int mode, int E, const int* tile_expert,
                               const int* n_m_tiles, const int* offs, long long a_rows, long long b_rows, int out_fp32,
-                              int accumulate, int bn, void* status, const void* row_meta, void* const* peer_ret,
-                              void* const* peer_retg, const float* rowval, int push_use_gate, int world, cudaStream_t st);
+                              int accumulate, int bn, void* status, const void* push_runs, void* const* peer_ret,
+                              void* const* peer_retg, const float* rowval, int push_pairs, int world, cudaStream_t st);
 extern "C" int nmoe_gemm_bf16_pair(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
                                    long long ldc, int a_mn, int b_mn, int mode, int E, const int* tile_expert,
                                    const int* n_m_tiles, const int* offs, long long a_rows, long long b_rows, int out_fp32,

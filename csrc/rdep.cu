@@ -9,9 +9,12 @@
 //           {source rank, token*K+slot, gate}; the owner zero-fills the padding rows of its own
 //           segments; the last block releases a per-peer "rows have landed" flag
 //   wait    bounded spin until all peers' flags reached this call's epoch
-// The owner then runs grouped GEMMs over its padded segments; the last GEMM's epilogue pushes
-// each output row (times its gate) into the source rank's (token, slot) return buffer, and a
-// reduce kernel on the source sums the K slots in a fixed order.
+// The owner then runs grouped GEMMs over its padded segments.  Rows go back in RUNS: inside an expert's segment
+// the rows of one source rank are contiguous (placement is rank-major), so the owner writes each (expert, source)
+// run as one contiguous block into the source's return buffer, which is laid out in the source's own expert-major
+// order (offset = rows that source sent to lower experts).  Every transfer over NVLink is therefore a sequential
+// stream of whole rows -- from the last GEMM's epilogue or from the push kernel -- and needs no per-row metadata.
+// A reduce kernel on the source gathers its K slots by index, applies the gates and sums in a fixed order.
 //
 // Placement is deterministic (no remote atomics): position = segment start + rows of lower
 // ranks + stable local rank.  Every spin has an iteration bound and reports through a
@@ -23,6 +26,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "common/epilogue.cuh"
 #include "common/ptx.cuh"
 #include "common/quant_dev.cuh"
 
@@ -92,6 +96,11 @@ struct PlanArgs {
   int* tile_expert;             // out [capacity_rows/128]
   int* n_m_tiles;               // out [1]
   int* send_counts;             // out [E]: my counts (for stats / loads)
+  int* send_prefix;             // out [E]: exclusive prefix of my counts = row of my first pair of expert e in MY return buffer
+  // out [3][n_local][world], owner side, for local expert le and source rank s:
+  //   [0] first row of s's run inside my buffer, [1] its length (0 when the expert was dropped),
+  //   [2] first row of that run inside s's return buffer
+  int* runs;
   StatusRecord* status;
 };
 
@@ -145,6 +154,26 @@ __global__ void __launch_bounds__(512) k_rdep_plan(const PlanArgs a) {
     s_lower[e] = low;
   }
   __syncthreads();
+  // 4b. return-run tables.  Thread s < world walks source s's counts once: the running sum over experts is where
+  // that source keeps the rows of expert e in its return buffer.  Thread `world` scans my own counts the same way.
+  if (threadIdx.x < a.world) {
+    const int s = threadIdx.x;
+    const int nlw = a.n_local * a.world;
+    int run = 0;
+    for (int e = 0; e < E; ++e) {
+      const int c = reinterpret_cast<volatile int*>(a.my_counts_table)[s * E + e];
+      const int le = e - a.rank * a.n_local;
+      if (le >= 0 && le < a.n_local) {
+        a.runs[nlw + le * a.world + s] = c;          // length (zeroed below if the expert is dropped)
+        a.runs[2 * nlw + le * a.world + s] = run;    // row in s's return buffer
+      }
+      run += c;
+    }
+  } else if (threadIdx.x == a.world) {
+    int run = 0;
+    for (int e = 0; e < E; ++e) { a.send_prefix[e] = run; run += s_cnt[e]; }
+  }
+  __syncthreads();
   // 5. segment starts per owner (serial per owner; E is small)
   if (threadIdx.x < a.world) {
     const int o = threadIdx.x;
@@ -159,6 +188,15 @@ __global__ void __launch_bounds__(512) k_rdep_plan(const PlanArgs a) {
         a.base[e] = run + s_lower[e];
       }
       if (o == a.rank) {
+        // where each source's run starts inside my segment (rank-major), or an empty run when the expert is dropped
+        const bool dropped = run + padded > a.capacity_rows;
+        int at = run;
+        for (int s = 0; s < a.world; ++s) {
+          const int c = reinterpret_cast<volatile int*>(a.my_counts_table)[s * E + e];
+          a.runs[le * a.world + s] = at;
+          if (dropped) a.runs[a.n_local * a.world + le * a.world + s] = 0;
+          at += c;
+        }
         a.offs_pad[le] = run;
         a.seg_rows[le] = (run + padded > a.capacity_rows) ? 0 : s_total[e];
         if (run + padded <= a.capacity_rows)
@@ -182,6 +220,8 @@ struct PlaceArgs {
   const int* rank_in_block;      // [T*K]
   const int* block_prefix;       // [n_blocks][E]
   const int* base;               // [E]
+  const int* send_prefix;        // [E] row of my first pair of expert e in my return buffer
+  int* lpos_out;                 // [T*K] out: row of the pair in my return buffer (-1 = dropped)
   __nv_bfloat16* peer_x[kMaxRanks];     // owner activation buffers [capacity, H]
   RdepMeta* peer_meta[kMaxRanks];       // owner meta [capacity] (null: do not write meta)
   uint32_t* peer_data_flags[kMaxRanks]; // owner's flags [world]; we release entry `rank`
@@ -207,11 +247,15 @@ __global__ void __launch_bounds__(256) k_rdep_place(const PlaceArgs a) {
         const int i = tok * a.K + lane;
         const int e = a.eid[i];
         const int rb = a.rank_in_block[i];
+        int lp = -1;
         if (e >= 0 && e < a.E && rb >= 0 && a.base[e] >= 0) {
           owner = e / a.n_local;
-          pos = a.base[e] + a.block_prefix[(i / kCountThreads) * a.E + e] + rb;
+          const int within = a.block_prefix[(i / kCountThreads) * a.E + e] + rb;
+          pos = a.base[e] + within;
+          lp = a.send_prefix[e] + within;
         }
         a.pos_out[i] = pos;
+        if (a.lpos_out) a.lpos_out[i] = lp;
         if (a.owner_out) a.owner_out[i] = owner;
         if (pos >= 0 && a.peer_meta[owner] != nullptr) {
           int4 m;
@@ -306,12 +350,14 @@ __global__ void __launch_bounds__(256) k_rdep_place_mx(const PlaceMxArgs am) {
     for (int i = blockIdx.x * 8 + warp; i < n_pairs; i += row_blocks * 8) {
       const int e = a.eid[i];
       const int rb = a.rank_in_block[i];
-      int pos = -1, owner = 0;
+      int pos = -1, owner = 0, lp = -1;
       if (e >= 0 && e < a.E && rb >= 0 && a.base[e] >= 0) {
         owner = e / a.n_local;
-        pos = a.base[e] + a.block_prefix[(i / kCountThreads) * a.E + e] + rb;
+        const int within = a.block_prefix[(i / kCountThreads) * a.E + e] + rb;
+        pos = a.base[e] + within;
+        lp = a.send_prefix[e] + within;
       }
-      if (lane == 0) a.pos_out[i] = pos;
+      if (lane == 0) { a.pos_out[i] = pos; if (a.lpos_out) a.lpos_out[i] = lp; }
       if (pos < 0) continue;
       const int tok = i / a.K;
       const __nv_bfloat16* src = a.x + static_cast<size_t>(tok) * a.H;
@@ -402,30 +448,31 @@ __global__ void k_rdep_wait(const uint32_t* my_flags, int world, uint32_t epoch,
 // Owner side, unfused variant: push rows of y[capacity, H] (scaled by the row's gate when
 // use_gate) into the source's return buffer ret[tok_slot, H].
 struct PushArgs {
-  int H, n_rows_cap, use_gate;
+  int H, n_rows_cap;
   const __nv_bfloat16* y;
-  const RdepMeta* meta;
+  const int* runs;                  // [3][n_local][world]: run start in my buffer, run length, start in the source's buffer
+  const int* tile_expert;           // local expert of every 128-row tile
   const int* n_m_tiles;
   __nv_bfloat16* peer_ret[kMaxRanks];
   float* peer_retg[kMaxRanks];      // optional per-row scalar return (gate gradients)
   const float* rowval;              // optional per-row scalar to return
-  int world, n_pairs;               // valid ranges of meta.src_rank and meta.tok_slot (checked before every store)
+  int world, n_local, n_pairs;      // n_pairs = rows of a source's return buffer (bound for every destination row)
   StatusRecord* status;
 };
+
 __global__ void __launch_bounds__(256) k_rdep_push(const PushArgs a) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int rows = min(*a.n_m_tiles * 128, a.n_rows_cap);
   const int nvec = a.H >> 3;
+  // consecutive warps take consecutive rows: at any moment the grid writes a sliding window of consecutive
+  // destination rows per source
   for (int r = blockIdx.x * 8 + warp; r < rows; r += gridDim.x * 8) {
-    const int4 mv = __ldg(reinterpret_cast<const int4*>(a.meta + r));
-    if (mv.w == 0) continue;
-    const int src = mv.x, ts = mv.y;
-    if (src < 0 || src >= a.world || ts < 0 || ts >= a.n_pairs) {
-      // a stale or torn meta record (possible after a wait that ran out) must not become a wild store into a peer
-      if (lane == 0) report_status(a.status, kStatusBadIndex, 430, r, src);
+    int src, ts;
+    if (!run_lookup(a.runs, a.n_local, a.world, __ldg(a.tile_expert + (r >> 7)), r, src, ts)) continue;
+    if (ts < 0 || ts >= a.n_pairs) {
+      if (lane == 0) report_status(a.status, kStatusBadIndex, 430, r, ts);
       continue;
     }
-    const float g = a.use_gate ? __int_as_float(mv.z) : 1.f;
     if (a.y != nullptr) {
       const int4* s = reinterpret_cast<const int4*>(a.y + static_cast<size_t>(r) * a.H);
       int4* d = reinterpret_cast<int4*>(a.peer_ret[src] + static_cast<size_t>(ts) * a.H);
@@ -440,15 +487,7 @@ __global__ void __launch_bounds__(256) k_rdep_push(const PushArgs a) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           const int c = c0 + j * 32 + lane;
-          if (c < nvec) {
-            int4 o = v[j];
-            if (a.use_gate) {
-              float2 f0 = unpack_bf16x2(o.x), f1 = unpack_bf16x2(o.y), f2 = unpack_bf16x2(o.z), f3 = unpack_bf16x2(o.w);
-              o.x = pack_bf16x2(f0.x * g, f0.y * g); o.y = pack_bf16x2(f1.x * g, f1.y * g);
-              o.z = pack_bf16x2(f2.x * g, f2.y * g); o.w = pack_bf16x2(f3.x * g, f3.y * g);
-            }
-            st_relaxed_sys_v4(d + c, o);
-          }
+          if (c < nvec) st_relaxed_sys_v4(d + c, v[j]);
         }
       }
     }
@@ -460,9 +499,8 @@ __global__ void __launch_bounds__(256) k_rdep_push(const PushArgs a) {
 // Owner side, copy-engine variant of k_rdep_push: every row chunk travels global -> shared -> peer global as two
 // bulk asynchronous copies (the TMA unit moves the bytes; the warp only issues them), so one lane keeps kilobytes in
 // flight per instruction instead of 16 bytes per store.  A warp owns a ring of kPushSlots shared-memory slots of
-// kPushChunk bytes; rows longer than a slot go in chunks.  With use_gate the warp scales the chunk in shared memory
-// between the two copies.  Rows whose meta names a source rank or a (token, slot) outside the valid range are skipped
-// and reported (a stale or torn meta record must not become a wild store into a peer's memory).
+// kPushChunk bytes; rows longer than a slot go in chunks.  A destination row outside the source's return buffer
+// (only possible with a corrupt run table) is skipped and reported, never written.
 constexpr int kPushChunk = 4096;
 constexpr int kPushSlots = 3;
 constexpr int kPushWarps = 8;
@@ -494,14 +532,12 @@ __global__ void __launch_bounds__(kPushWarps * 32) k_rdep_push_bulk(const PushAr
   uint32_t phase_bits = 0;       // bit s = parity of the next completion of slot s
   bool ok = true;
   for (int r = blockIdx.x * kPushWarps + warp; ok && r < rows; r += gridDim.x * kPushWarps) {
-    const int4 mv = __ldg(reinterpret_cast<const int4*>(a.meta + r));
-    if (mv.w == 0) continue;
-    const int src = mv.x, ts = mv.y;
-    if (src < 0 || src >= a.world || ts < 0 || ts >= a.n_pairs) {
-      if (lane == 0) report_status(a.status, kStatusBadIndex, 430, r, src);
+    int src, ts;
+    if (!run_lookup(a.runs, a.n_local, a.world, __ldg(a.tile_expert + (r >> 7)), r, src, ts)) continue;
+    if (ts < 0 || ts >= a.n_pairs) {
+      if (lane == 0) report_status(a.status, kStatusBadIndex, 430, r, ts);
       continue;
     }
-    const float g = a.use_gate ? __int_as_float(mv.z) : 1.f;
     if (a.y != nullptr) {
       const uint8_t* srow = reinterpret_cast<const uint8_t*>(a.y + static_cast<size_t>(r) * a.H);
       uint8_t* drow = reinterpret_cast<uint8_t*>(a.peer_ret[src] + static_cast<size_t>(ts) * a.H);
@@ -522,15 +558,6 @@ __global__ void __launch_bounds__(kPushWarps * 32) k_rdep_push_bulk(const PushAr
           break;
         }
         phase_bits ^= 1u << slot;
-        if (a.use_gate) {
-          for (uint32_t i = lane * 16; i < nb; i += 32 * 16) {
-            int4 o = *reinterpret_cast<const int4*>(sm + i);
-            float2 f0 = unpack_bf16x2(o.x), f1 = unpack_bf16x2(o.y), f2 = unpack_bf16x2(o.z), f3 = unpack_bf16x2(o.w);
-            o.x = pack_bf16x2(f0.x * g, f0.y * g); o.y = pack_bf16x2(f1.x * g, f1.y * g);
-            o.z = pack_bf16x2(f2.x * g, f2.y * g); o.w = pack_bf16x2(f3.x * g, f3.y * g);
-            *reinterpret_cast<int4*>(sm + i) = o;
-          }
-        }
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
@@ -547,32 +574,39 @@ __global__ void __launch_bounds__(kPushWarps * 32) k_rdep_push_bulk(const PushAr
   __threadfence_system();
 }
 
-// Source side: out[t] = sum_k ret[t*K + k] for slots with pos >= 0 (fp32, fixed order).
+// Source side: out[t] = sum_k gate[t,k] * ret[lpos[t*K + k]] over the slots that were delivered (lpos >= 0), fp32,
+// fixed slot order (bit-reproducible).  gates == nullptr: plain sum (input-gradient return).
 __global__ void __launch_bounds__(256)
-k_rdep_reduce(const __nv_bfloat16* __restrict__ ret, const int* __restrict__ pos, __nv_bfloat16* __restrict__ out,
-              int T, int K, int H) {
+k_rdep_reduce(const __nv_bfloat16* __restrict__ ret, const int* __restrict__ lpos, const float* __restrict__ gates,
+              __nv_bfloat16* __restrict__ out, int T, int K, int H) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nvec = H >> 3;
   for (int t = blockIdx.x * 8 + warp; t < T; t += gridDim.x * 8) {
-    // lane k remembers whether slot k was delivered (K <= 32); the bit mask is the same for every column
-    const unsigned live = __ballot_sync(0xffffffffu, lane < K && pos[t * K + lane] >= 0);
+    // lane k holds slot k's row index and gate (K <= 32); handed out by shuffles below
+    const int my_row = lane < K ? lpos[t * K + lane] : -1;
+    const float my_gate = (lane < K && gates != nullptr) ? gates[t * K + lane] : 1.f;
     for (int c = lane; c < nvec; c += 32) {
       float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
       for (int k0 = 0; k0 < K; k0 += 8) {
-        // up to eight independent loads in flight, then the sum in slot order (bit-reproducible)
+        // up to eight independent loads in flight, then the sum in slot order
         int4 v[8];
+        float g[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           const int k = k0 + j;
-          v[j] = (k < K && ((live >> k) & 1u))
-                     ? ld_relaxed_sys_v4(reinterpret_cast<const int4*>(ret + (static_cast<size_t>(t) * K + k) * H) + c)
+          const int row = __shfl_sync(0xffffffffu, my_row, k & 31);
+          g[j] = __shfl_sync(0xffffffffu, my_gate, k & 31);
+          v[j] = (k < K && row >= 0)
+                     ? ld_relaxed_sys_v4(reinterpret_cast<const int4*>(ret + static_cast<size_t>(row) * H) + c)
                      : make_int4(0, 0, 0, 0);
         }
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           const float2 f0 = unpack_bf16x2(v[j].x), f1 = unpack_bf16x2(v[j].y), f2 = unpack_bf16x2(v[j].z), f3 = unpack_bf16x2(v[j].w);
-          acc[0] += f0.x; acc[1] += f0.y; acc[2] += f1.x; acc[3] += f1.y;
-          acc[4] += f2.x; acc[5] += f2.y; acc[6] += f3.x; acc[7] += f3.y;
+          acc[0] = fmaf(g[j], f0.x, acc[0]); acc[1] = fmaf(g[j], f0.y, acc[1]);
+          acc[2] = fmaf(g[j], f1.x, acc[2]); acc[3] = fmaf(g[j], f1.y, acc[3]);
+          acc[4] = fmaf(g[j], f2.x, acc[4]); acc[5] = fmaf(g[j], f2.y, acc[5]);
+          acc[6] = fmaf(g[j], f3.x, acc[6]); acc[7] = fmaf(g[j], f3.y, acc[7]);
         }
       }
       int4 o;
@@ -580,6 +614,15 @@ k_rdep_reduce(const __nv_bfloat16* __restrict__ ret, const int* __restrict__ pos
       o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
       reinterpret_cast<int4*>(out + static_cast<size_t>(t) * H)[c] = o;
     }
+  }
+}
+
+// Source side: per-pair scalars returned by the owners (gate gradients) back into (token, slot) order.
+__global__ void k_rdep_gather_scalar(const float* __restrict__ retg, const int* __restrict__ lpos, float* __restrict__ out,
+                                     int n_pairs) {
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n_pairs; i += gridDim.x * blockDim.x) {
+    const int r = lpos[i];
+    out[i] = r >= 0 ? retg[r] : 0.f;
   }
 }
 
@@ -617,8 +660,8 @@ int nmoe_rdep_count(const int* eid, int n_pairs, int E, int* block_hist, int* ra
 // peer_counts / peer_count_flags: arrays of `world` device pointers (host memory).
 int nmoe_rdep_plan(int rank, int world, int E, int n_local, int n_blocks, int capacity_rows, int epoch, int align,
                    int* block_hist, void* const* peer_counts, void* const* peer_count_flags, int* base,
-                   int* offs_pad, int* seg_rows, int* tile_expert, int* n_m_tiles, int* send_counts, void* status,
-                   cudaStream_t st) {
+                   int* offs_pad, int* seg_rows, int* tile_expert, int* n_m_tiles, int* send_counts, int* send_prefix,
+                   int* runs, void* status, cudaStream_t st) {
   if (world > kMaxRanks || E > kMaxExperts || E != n_local * world) return -1;
   if (align != 128 && align != 256) return -2;
   PlanArgs a;
@@ -632,7 +675,8 @@ int nmoe_rdep_plan(int rank, int world, int E, int n_local, int n_blocks, int ca
   a.my_counts_table = a.peer_counts[rank];
   a.my_count_flags = a.peer_count_flags[rank];
   a.base = base; a.offs_pad = offs_pad; a.seg_rows = seg_rows; a.tile_expert = tile_expert;
-  a.n_m_tiles = n_m_tiles; a.send_counts = send_counts; a.status = static_cast<StatusRecord*>(status);
+  a.n_m_tiles = n_m_tiles; a.send_counts = send_counts; a.send_prefix = send_prefix; a.runs = runs;
+  a.status = static_cast<StatusRecord*>(status);
   k_rdep_plan<<<1, 512, 0, st>>>(a);
   CHECK_LAUNCH();
   return 0;
@@ -642,9 +686,10 @@ int nmoe_rdep_place(int rank, int world, int E, int n_local, int T, int K, int H
                     const int* eid, const float* gates, const int* rank_in_block, const int* block_prefix,
                     const int* base, void* const* peer_x, void* const* peer_meta, void* const* peer_data_flags,
                     int* pos_out, int* owner_out, const int* offs_pad, const int* seg_rows, int* done_counter,
-                    void* status, cudaStream_t st) {
+                    void* status, const int* send_prefix, int* lpos_out, cudaStream_t st) {
   if (world > kMaxRanks || (H % 8) != 0) return -1;
   PlaceArgs a;
+  a.send_prefix = send_prefix; a.lpos_out = lpos_out;
   a.rank = rank; a.world = world; a.E = E; a.n_local = n_local; a.T = T; a.K = K; a.H = H; a.epoch = epoch;
   a.x = static_cast<const __nv_bfloat16*>(x); a.eid = eid; a.gates = gates; a.rank_in_block = rank_in_block;
   a.block_prefix = block_prefix; a.base = base;
@@ -669,12 +714,14 @@ int nmoe_rdep_place_mx(int rank, int world, int E, int n_local, int T, int K, in
                        const int* eid, const float* gates, const int* rank_in_block, const int* block_prefix,
                        const int* base, void* const* peer_xq, void* const* peer_sf, void* const* peer_meta,
                        void* const* peer_data_flags, int* pos_out, const int* offs_pad, const int* seg_rows,
-                       int* done_counter, void* status, int fp4, cudaStream_t st) {
+                       int* done_counter, void* status, int fp4, const int* send_prefix, int* lpos_out,
+                       cudaStream_t st) {
   // 32-element blocks, 16-byte row stores; the scale bytes of a partial last atom are written as padding (127)
   if (world > kMaxRanks || (H % 32) != 0 || (fp4 && (H % 64) != 0)) return -1;
   PlaceMxArgs am;
   am.fp4 = fp4;
   PlaceArgs& a = am.base;
+  a.send_prefix = send_prefix; a.lpos_out = lpos_out;
   a.rank = rank; a.world = world; a.E = E; a.n_local = n_local; a.T = T; a.K = K; a.H = H; a.epoch = epoch;
   a.x = static_cast<const __nv_bfloat16*>(x); a.eid = eid; a.gates = gates; a.rank_in_block = rank_in_block;
   a.block_prefix = block_prefix; a.base = base;
@@ -716,19 +763,20 @@ int nmoe_rdep_wait(const void* my_flags, int world, unsigned epoch, unsigned bud
   return 0;
 }
 
-// impl 0: per-lane 16-byte system-scope stores; impl 1: bulk asynchronous copies through shared memory.
-// n_pairs = T*K of the SOURCE ranks (every rank holds the same number of tokens per step).
-int nmoe_rdep_push(const void* y, const void* meta, const int* n_m_tiles, int cap_rows, int H, int use_gate,
-                   void* const* peer_ret, void* const* peer_retg, const float* rowval, int world, int n_pairs,
-                   void* status, int impl, cudaStream_t st) {
+// Owner -> sources return of y[capacity, H] in runs (see the header comment).  impl 0: per-lane 16-byte system-scope
+// stores; impl 1: bulk asynchronous copies through shared memory.  runs / tile_expert come from nmoe_rdep_plan;
+// n_pairs = T*K of the SOURCE ranks (rows of a return buffer).  y == nullptr sends only the per-row scalars.
+int nmoe_rdep_push(const void* y, const int* runs, const int* tile_expert, const int* n_m_tiles, int cap_rows, int H,
+                   void* const* peer_ret, void* const* peer_retg, const float* rowval, int world, int n_local,
+                   int n_pairs, void* status, int impl, cudaStream_t st) {
   if (world > kMaxRanks || (H % 8) != 0) return -1;
   PushArgs a;
-  a.world = world; a.n_pairs = n_pairs; a.status = static_cast<StatusRecord*>(status);
-  a.H = H; a.n_rows_cap = cap_rows; a.use_gate = use_gate;
-  a.y = static_cast<const __nv_bfloat16*>(y); a.meta = static_cast<const RdepMeta*>(meta); a.n_m_tiles = n_m_tiles;
-  for (int r = 0; r < world; ++r) {
-    a.peer_ret[r] = peer_ret ? static_cast<__nv_bfloat16*>(peer_ret[r]) : nullptr;
-    a.peer_retg[r] = peer_retg ? static_cast<float*>(peer_retg[r]) : nullptr;
+  a.world = world; a.n_local = n_local; a.n_pairs = n_pairs; a.status = static_cast<StatusRecord*>(status);
+  a.H = H; a.n_rows_cap = cap_rows;
+  a.y = static_cast<const __nv_bfloat16*>(y); a.runs = runs; a.tile_expert = tile_expert; a.n_m_tiles = n_m_tiles;
+  for (int r = 0; r < kMaxRanks; ++r) {
+    a.peer_ret[r] = (peer_ret && r < world) ? static_cast<__nv_bfloat16*>(peer_ret[r]) : nullptr;
+    a.peer_retg[r] = (peer_retg && r < world) ? static_cast<float*>(peer_retg[r]) : nullptr;
   }
   a.rowval = rowval;
   if (impl == 1) {
@@ -747,13 +795,22 @@ int nmoe_rdep_push(const void* y, const void* meta, const int* n_m_tiles, int ca
   return 0;
 }
 
-int nmoe_rdep_reduce(const void* ret, const int* pos, void* out, int T, int K, int H, cudaStream_t st) {
+// out[t] = sum_k gates[t,k] * ret[lpos[t,k]]  (gates may be null: plain sum)
+int nmoe_rdep_reduce(const void* ret, const int* lpos, const float* gates, void* out, int T, int K, int H,
+                     cudaStream_t st) {
   if (T == 0) return 0;
-  if ((H % 8) != 0) return -1;
+  if ((H % 8) != 0 || K > 32) return -1;
   int blocks = (T + 7) / 8;
   if (blocks > 148 * 8) blocks = 148 * 8;
-  k_rdep_reduce<<<blocks, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(ret), pos, static_cast<__nv_bfloat16*>(out),
-                                       T, K, H);
+  k_rdep_reduce<<<blocks, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(ret), lpos, gates,
+                                       static_cast<__nv_bfloat16*>(out), T, K, H);
+  CHECK_LAUNCH();
+  return 0;
+}
+
+int nmoe_rdep_gather_scalar(const float* retg, const int* lpos, float* out, int n_pairs, cudaStream_t st) {
+  if (n_pairs == 0) return 0;
+  k_rdep_gather_scalar<<<(n_pairs + 255) / 256 < 1184 ? (n_pairs + 255) / 256 : 1184, 256, 0, st>>>(retg, lpos, out, n_pairs);
   CHECK_LAUNCH();
   return 0;
 }

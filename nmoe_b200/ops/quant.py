@@ -111,7 +111,7 @@ def grouped_gemm_mxfp4(aq: torch.Tensor, asf: torch.Tensor, bq: torch.Tensor, bs
   if push is not None:
     L.check(L.lib().nmoe_gemm_mxfp4(L.ptr(aq), L.ptr(asf), L.ptr(bq), L.ptr(bsf), None, Mcap, N, K, L.c_ll(N), 1, E,
                                     L.ptr(tile_expert), L.ptr(n_m_tiles), L.c_ll(Mcap), L.c_ll(E * N), bn, L.ptr(st),
-                                    push["meta"], push["peer_ret"], int(push["use_gate"]), push["world"], L.stream()),
+                                    L.ptr(push["runs"]), push["peer_ret"], int(push["pairs"]), push["world"], L.stream()),
             "grouped_gemm_mxfp4(push)")
     return None
   if out is None:
@@ -132,7 +132,7 @@ def grouped_gemm_mxfp8(aq: torch.Tensor, asf: torch.Tensor, bq: torch.Tensor, bs
   if push is not None:
     L.check(L.lib().nmoe_gemm_mxfp8(L.ptr(aq), L.ptr(asf), L.ptr(bq), L.ptr(bsf), None, Mcap, N, K, L.c_ll(N), 1, E,
                                     L.ptr(tile_expert), L.ptr(n_m_tiles), L.c_ll(Mcap), L.c_ll(E * N), bn, L.ptr(st),
-                                    push["meta"], push["peer_ret"], int(push["use_gate"]), push["world"], L.stream()),
+                                    L.ptr(push["runs"]), push["peer_ret"], int(push["pairs"]), push["world"], L.stream()),
             "grouped_gemm_mxfp8(push)")
     return None
   if out is None:

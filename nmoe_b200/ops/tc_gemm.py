@@ -179,16 +179,16 @@ def grouped_gemm(a: torch.Tensor, b: torch.Tensor, tile_expert: torch.Tensor, n_
     L.check(L.lib().nmoe_gemm_bf16_pair_push(
       L.ptr(a), L.ptr(b), None, a.size(0), N, K, L.c_ll(K), L.c_ll(N if b_mn else K), L.c_ll(N),
       0, int(b_mn), 1, E, L.ptr(tile_expert), L.ptr(n_m_tiles), None, L.c_ll(a.size(0)), L.c_ll(b2_rows),
-      0, 0, L.ptr(st), push["meta"], push["peer_ret"], push.get("peer_retg"), L.ptr(push.get("rowval")),
-      int(push["use_gate"]), push["world"], L.stream()), "grouped_gemm_bf16_pair(push)")
+      0, 0, L.ptr(st), L.ptr(push["runs"]), push["peer_ret"], push.get("peer_retg"), L.ptr(push.get("rowval")),
+      int(push["pairs"]), push["world"], L.stream()), "grouped_gemm_bf16_pair(push)")
     return None
   if push is not None:
     # fused RDEP return: rows go to the source ranks' return buffers instead of a local C
     L.check(L.lib().nmoe_gemm_bf16(
       L.ptr(a), L.ptr(b), None, a.size(0), N, K, L.c_ll(K), L.c_ll(N if b_mn else K), L.c_ll(N),
       0, int(b_mn), 1, E, L.ptr(tile_expert), L.ptr(n_m_tiles), None, L.c_ll(a.size(0)), L.c_ll(b2_rows),
-      0, 0, bn, L.ptr(st), push["meta"], push["peer_ret"], push.get("peer_retg"), L.ptr(push.get("rowval")),
-      int(push["use_gate"]), push["world"], L.stream()), "grouped_gemm_bf16(push)")
+      0, 0, bn, L.ptr(st), L.ptr(push["runs"]), push["peer_ret"], push.get("peer_retg"), L.ptr(push.get("rowval")),
+      int(push["pairs"]), push["world"], L.stream()), "grouped_gemm_bf16(push)")
     return None
   if out is None:
     out = torch.empty(a.size(0), N, dtype=torch.bfloat16, device=a.device)

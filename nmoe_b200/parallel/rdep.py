@@ -58,7 +58,10 @@ class Plan:
   tile_expert: torch.Tensor    # [cap/128]
   n_m_tiles: torch.Tensor      # [1]
   send_counts: torch.Tensor    # [E]
+  send_prefix: torch.Tensor    # [E] row of this rank's first pair of expert e in its own return buffer
+  runs: torch.Tensor           # [3, n_local, world] owner side: run start / length / start at the source (see csrc/rdep.cu)
   pos: torch.Tensor            # [T*K] position in the owner's buffer (-1 = dropped)
+  lpos: torch.Tensor           # [T*K] row of the pair in this rank's return buffer (-1 = dropped)
   T: int
   K: int
   rows: int = 0                # host-known bound on the (padded) rows that landed on this rank; 0 = not read back
@@ -165,10 +168,13 @@ class Rdep:
     st = G.status_buffer(dev)
     L.check(lib.nmoe_rdep_count(L.ptr(e32), n_pairs, self.E, L.ptr(block_hist), L.ptr(rib), L.ptr(st), L.stream()),
             "rdep_count")
-    small = torch.empty(self.E * 2 + 2 * self.n_local + 2 + self.capacity // 128, dtype=torch.int32, device=dev)
+    nlw = self.n_local * self.world
+    small = torch.empty(self.E * 3 + 2 * self.n_local + 2 + 3 * nlw + self.capacity // 128, dtype=torch.int32, device=dev)
     o = 0
     base = small[o:o + self.E]; o += self.E
     send_counts = small[o:o + self.E]; o += self.E
+    send_prefix = small[o:o + self.E]; o += self.E
+    runs = small[o:o + 3 * nlw]; o += 3 * nlw
     offs_pad = small[o:o + self.n_local + 1]; o += self.n_local + 1
     seg_rows = small[o:o + self.n_local]; o += self.n_local
     n_m_tiles = small[o:o + 1]; o += 1
@@ -177,9 +183,10 @@ class Rdep:
     L.check(lib.nmoe_rdep_plan(self.rank, self.world, self.E, self.n_local, nb, self.capacity, self.epoch_count, self.align,
                                L.ptr(block_hist), self.slab.ptrs("counts"), self.slab.ptrs("count_flags"),
                                L.ptr(base), L.ptr(offs_pad), L.ptr(seg_rows), L.ptr(tile_expert), L.ptr(n_m_tiles),
-                               L.ptr(send_counts), L.ptr(st), L.stream()), "rdep_plan")
-    pos = torch.empty(n_pairs, dtype=torch.int32, device=dev)
-    return Plan(e32, rib, block_hist, base, offs_pad, seg_rows, tile_expert, n_m_tiles, send_counts, pos, T, K)
+                               L.ptr(send_counts), L.ptr(send_prefix), L.ptr(runs), L.ptr(st), L.stream()), "rdep_plan")
+    pos = torch.empty(2 * n_pairs, dtype=torch.int32, device=dev)
+    return Plan(e32, rib, block_hist, base, offs_pad, seg_rows, tile_expert, n_m_tiles, send_counts, send_prefix,
+                runs.view(3, self.n_local, self.world), pos[:n_pairs], pos[n_pairs:], T, K)
 
   def place(self, x: torch.Tensor, plan: Plan, gates: Optional[torch.Tensor], which: str, with_meta: bool) -> None:
     """Store x's rows into every owner's ``which`` buffer ('x' or 'y') and release the data flags."""
@@ -190,7 +197,7 @@ class Rdep:
       L.ptr(plan.eid), L.ptr(gates), L.ptr(plan.rank_in_block), L.ptr(plan.block_prefix), L.ptr(plan.base),
       self.slab.ptrs(which), self.slab.ptrs("meta") if with_meta else None, self.slab.ptrs("data_flags"),
       L.ptr(plan.pos), None, L.ptr(plan.offs_pad), L.ptr(plan.seg_rows), L.ptr(self.done_counter), L.ptr(st),
-      L.stream()), "rdep_place")
+      L.ptr(plan.send_prefix), L.ptr(plan.lpos), L.stream()), "rdep_place")
 
   def place_mx(self, x: torch.Tensor, plan: Plan, gates: Optional[torch.Tensor]) -> None:
     """Quantise x's rows to MXFP8 (or MXFP4) in the placement kernel and store values + scales into the owners' buffers."""
@@ -201,7 +208,7 @@ class Rdep:
       L.ptr(plan.eid), L.ptr(gates), L.ptr(plan.rank_in_block), L.ptr(plan.block_prefix), L.ptr(plan.base),
       self.slab.ptrs("xq"), self.slab.ptrs("sfa"), self.slab.ptrs("meta"), self.slab.ptrs("data_flags"),
       L.ptr(plan.pos), L.ptr(plan.offs_pad), L.ptr(plan.seg_rows), L.ptr(self.done_counter), L.ptr(st),
-      int(self.fp4), L.stream()), "rdep_place_mx")
+      int(self.fp4), L.ptr(plan.send_prefix), L.ptr(plan.lpos), L.stream()), "rdep_place_mx")
 
   def wait_data(self) -> None:
     st = G.status_buffer(self.device)
@@ -209,37 +216,29 @@ class Rdep:
                                    ctypes.c_uint(self.epoch_data), ctypes.c_uint(self.wait_budget), L.ptr(st), 420,
                                    L.stream()), "rdep_wait(data)")
 
-  def push_and_reduce(self, y: Optional[torch.Tensor], plan: Plan, use_gate: bool, rowval: Optional[torch.Tensor],
-                      out: torch.Tensor, marks: Optional[list] = None) -> None:
-    """Owner -> source return of rows (and optional per-row scalars), then the source-side K-way sum.
+  def push_and_reduce(self, y: Optional[torch.Tensor], plan: Plan, gates: Optional[torch.Tensor],
+                      rowval: Optional[torch.Tensor], out: torch.Tensor, marks: Optional[list] = None) -> None:
+    """Owner -> source return of rows in runs (and optional per-row scalars), then the source-side K-way sum with
+    the gates applied there (``gates`` fp32 [T*K], or None for a plain sum).
     ``marks``: two CUDA events recorded after the push kernel and after the wait (benchmarks)."""
     lib = L.lib()
     st = G.status_buffer(self.device)
-    L.check(lib.nmoe_rdep_push(L.ptr(y), ctypes.c_void_p(self.slab.local_ptr("meta")), L.ptr(plan.n_m_tiles),
-                               self.capacity, self.dim, int(use_gate), self.slab.ptrs("ret"),
-                               self.slab.ptrs("retg"), L.ptr(rowval), self.world, self.max_tokens * self.K,
-                               L.ptr(st), self.push_impl, L.stream()), "rdep_push")
+    L.check(lib.nmoe_rdep_push(L.ptr(y), L.ptr(plan.runs), L.ptr(plan.tile_expert), L.ptr(plan.n_m_tiles),
+                               self.capacity, self.dim, self.slab.ptrs("ret"), self.slab.ptrs("retg"), L.ptr(rowval),
+                               self.world, self.n_local, self.max_tokens * self.K, L.ptr(st), self.push_impl,
+                               L.stream()), "rdep_push")
     if marks:
       marks[0].record()
-    self.epoch_ret += 1
-    L.check(lib.nmoe_rdep_signal(self.slab.ptrs("ret_flags"), self.rank, self.world, ctypes.c_uint(self.epoch_ret),
-                                 L.stream()), "rdep_signal")
-    L.check(lib.nmoe_rdep_wait(ctypes.c_void_p(self.slab.local_ptr("ret_flags")), self.world,
-                               ctypes.c_uint(self.epoch_ret), ctypes.c_uint(self.wait_budget), L.ptr(st), 421,
-                               L.stream()), "rdep_wait(ret)")
-    if marks:
-      marks[1].record()
-    L.check(lib.nmoe_rdep_reduce(ctypes.c_void_p(self.slab.local_ptr("ret")), L.ptr(plan.pos), L.ptr(out), plan.T,
-                                 plan.K, self.dim, L.stream()), "rdep_reduce")
+    self.finish_return(plan, out, gates, marks[1] if marks else None)
 
-  def push_args(self, use_gate: bool, rowval: Optional[torch.Tensor] = None) -> dict:
+  def push_args(self, plan: Plan, rowval: Optional[torch.Tensor] = None) -> dict:
     """Arguments that make a grouped GEMM's epilogue store its rows straight into the source ranks'
     return buffers (fused return) instead of a local output."""
-    return {"meta": ctypes.c_void_p(self.slab.local_ptr("meta")), "peer_ret": self.slab.ptrs("ret"),
-            "peer_retg": self.slab.ptrs("retg"), "rowval": rowval, "use_gate": use_gate, "world": self.world}
+    return {"runs": plan.runs, "peer_ret": self.slab.ptrs("ret"), "peer_retg": self.slab.ptrs("retg"),
+            "rowval": rowval, "pairs": self.max_tokens * self.K, "world": self.world}
 
-  def finish_return(self, plan: Plan, out: torch.Tensor) -> None:
-    """After a kernel that pushed rows to the sources: publish, wait for every owner, sum the K slots."""
+  def finish_return(self, plan: Plan, out: torch.Tensor, gates: Optional[torch.Tensor] = None, mark=None) -> None:
+    """After a kernel that sent rows to the sources: publish, wait for every owner, sum the K slots (gate-weighted)."""
     lib = L.lib()
     st = G.status_buffer(self.device)
     self.epoch_ret += 1
@@ -248,8 +247,18 @@ class Rdep:
     L.check(lib.nmoe_rdep_wait(ctypes.c_void_p(self.slab.local_ptr("ret_flags")), self.world,
                                ctypes.c_uint(self.epoch_ret), ctypes.c_uint(self.wait_budget), L.ptr(st), 421,
                                L.stream()), "rdep_wait(ret)")
-    L.check(lib.nmoe_rdep_reduce(ctypes.c_void_p(self.slab.local_ptr("ret")), L.ptr(plan.pos), L.ptr(out), plan.T,
-                                 plan.K, self.dim, L.stream()), "rdep_reduce")
+    if mark is not None:
+      mark.record()
+    L.check(lib.nmoe_rdep_reduce(ctypes.c_void_p(self.slab.local_ptr("ret")), L.ptr(plan.lpos), L.ptr(gates), L.ptr(out),
+                                 plan.T, plan.K, self.dim, L.stream()), "rdep_reduce")
+
+  def returned_scalars(self, plan: Plan) -> torch.Tensor:
+    """The per-pair scalars the owners sent back with the last return, in (token, slot) order (0 for dropped pairs)."""
+    n = plan.T * plan.K
+    out = torch.empty(n, dtype=torch.float32, device=self.device)
+    L.check(L.lib().nmoe_rdep_gather_scalar(ctypes.c_void_p(self.slab.local_ptr("retg")), L.ptr(plan.lpos), L.ptr(out), n,
+                                            L.stream()), "rdep_gather_scalar")
+    return out.view(plan.T, plan.K)
 
   def row_gates(self, plan: Plan) -> torch.Tensor:
     out = torch.empty(self.capacity, dtype=torch.float32, device=self.device)
@@ -297,8 +306,12 @@ class _MoEFused(torch.autograd.Function):
         # SwiGLU and the re-quantisation happen in the epilogue of the up/gate projection: H13 is never written
         h13 = None
         aq, asf = Q.grouped_gemm_swiglu_quant(rdep.xq[:rows], rdep.sfa, W13q, W13sf, plan.tile_expert, plan.n_m_tiles, fp4=rdep.fp4)
-      ggemm(aq, asf, W2q, W2sf, plan.tile_expert, plan.n_m_tiles, push=rdep.push_args(True))
-      rdep.finish_return(plan, out)
+      if rdep.fused_return:
+        ggemm(aq, asf, W2q, W2sf, plan.tile_expert, plan.n_m_tiles, push=rdep.push_args(plan))
+        rdep.finish_return(plan, out, gates32.view(-1))
+      else:
+        y = ggemm(aq, asf, W2q, W2sf, plan.tile_expert, plan.n_m_tiles)
+        rdep.push_and_reduce(y, plan, gates32.view(-1), None, out)
       ctx.rdep, ctx.plan = rdep, plan
       ctx.save_for_backward(x, gates32, W13, W2, h13 if save_h13 else None, None)
       return out
@@ -309,11 +322,11 @@ class _MoEFused(torch.autograd.Function):
     a = EW.swiglu_rows(h13, plan.n_m_tiles)
     if rdep.fused_return:
       # down projection whose epilogue multiplies by the gate and stores into the source's (token, slot) rows
-      G.grouped_gemm(a, W2, plan.tile_expert, plan.n_m_tiles, push=rdep.push_args(True), align256=rdep.align == 256)
-      rdep.finish_return(plan, out)
+      G.grouped_gemm(a, W2, plan.tile_expert, plan.n_m_tiles, push=rdep.push_args(plan), align256=rdep.align == 256)
+      rdep.finish_return(plan, out, gates32.view(-1))
     else:
       y = G.grouped_gemm(a, W2, plan.tile_expert, plan.n_m_tiles, align256=rdep.align == 256)
-      rdep.push_and_reduce(y, plan, True, None, out)
+      rdep.push_and_reduce(y, plan, gates32.view(-1), None, out)
     ctx.rdep, ctx.plan = rdep, plan
     xd = rdep.xbuf[:rows].clone() if rdep.save_dispatched else None
     ctx.save_for_backward(x, gates32, W13, W2, h13 if save_h13 else None, xd)
@@ -346,13 +359,12 @@ class _MoEFused(torch.autograd.Function):
     dW13 = G.grouped_wgrad(dh13, xb, plan.offs_pad, rdep.n_local)                # [E, 2Dff, H]
     dx = torch.empty_like(x)
     if rdep.fused_return:
-      G.grouped_gemm(dh13, W13, plan.tile_expert, nt, b_mn=True, push=rdep.push_args(False, rowdot), align256=rdep.align == 256)
+      G.grouped_gemm(dh13, W13, plan.tile_expert, nt, b_mn=True, push=rdep.push_args(plan, rowdot), align256=rdep.align == 256)
       rdep.finish_return(plan, dx)
     else:
       dxe = G.grouped_gemm(dh13, W13, plan.tile_expert, nt, b_mn=True, align256=rdep.align == 256)
-      rdep.push_and_reduce(dxe, plan, False, rowdot, dx)
-    dg = rdep.retg[: plan.T * plan.K].clone().view(plan.T, plan.K)
-    dg = torch.where(plan.pos.view(plan.T, plan.K) >= 0, dg, torch.zeros_like(dg))
+      rdep.push_and_reduce(dxe, plan, None, rowdot, dx)
+    dg = rdep.returned_scalars(plan)
     return None, dx, dg, None, dW13, dW2, None, None
 
 

@@ -233,7 +233,7 @@ class MoEMLP(nn.Module):
       aq, asf = Q.quant_mxfp8(a, plan.n_m_tiles)
       y = Q.grouped_gemm_mxfp8(aq, asf, w2q, w2sf, plan.tile_expert, plan.n_m_tiles)
       y = (y[:, :H] + self.b2[row_e]).contiguous()
-      rd.push_and_reduce(y, plan, True, None, out[t0:t0 + xs.size(0)])
+      rd.push_and_reduce(y, plan, g.float().contiguous().view(-1), None, out[t0:t0 + xs.size(0)])
     return x + out.view(shape)
 
 
