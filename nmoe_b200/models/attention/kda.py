@@ -5,8 +5,10 @@ Per head, with L2-normalised q and k, per-key-channel log-decay g_t <= 0 and wri
 beta_t in (0,1), the state S [Dk, Dv] evolves as
     S <- diag(exp(g_t)) S ;  S <- S + beta_t k_t (v_t - S^T k_t)^T ;  o_t = S^T (q_t / sqrt(Dk))
 ``kda_recurrent`` is that recurrence token by token; ``kda_chunked`` processes ``chunk`` tokens at a
-time with the WY / UT-transform form (matrix products inside a chunk, one state update per chunk),
-which is what the layer uses."""
+time with the WY / UT-transform form (matrix products inside a chunk, one state update per chunk) as a
+plain PyTorch loop: the oracle, and the path for CPU tensors.  On a GPU the layer uses
+``ops.kda.kda_chunk_scan``: the same transform batched over all chunks, with the recurrence over
+chunks (forward and backward) on the scan kernel in ``csrc/kda.cu``."""
 from __future__ import annotations
 
 import torch
@@ -114,6 +116,11 @@ class KDA(nn.Module):
     k = torch.cat((kv[..., :self.nope], k_pe.unsqueeze(2).expand(B, T, h, self.rope_dim)), -1)
     g = F.logsigmoid(ops.linear(x, self.wg, self.wg_b).float()).view(B, T, h, self.qk_dim)
     beta = torch.sigmoid(ops.linear(x, self.wb).float()).view(B, T, h)
-    o = kda_chunked(q, k, kv[..., self.nope:], g, beta, chunk=self.chunk)
+    if x.is_cuda and self.chunk == 64 and self.v_dim % 64 == 0 and self.qk_dim % 4 == 0 and self.qk_dim <= 256:
+      # batched WY transform + the chunk recurrence on the CUDA scan kernel (csrc/kda.cu), forward and backward
+      from ...ops.kda import kda_chunk_scan
+      o = kda_chunk_scan(q, k, kv[..., self.nope:], g, beta)
+    else:
+      o = kda_chunked(q, k, kv[..., self.nope:], g, beta, chunk=self.chunk)
     o = torch.nan_to_num(o, nan=0.0, posinf=1e4, neginf=-1e4).to(x.dtype)
     return ops.linear(o.reshape(B, T, h * self.v_dim), self.wo)
