@@ -48,7 +48,7 @@ def timed(fn, iters, warmup, flush):
 
 def main():
   ap = argparse.ArgumentParser()
-  ap.add_argument("what", choices=["gemm", "mx", "attn", "moe", "indexer", "elementwise"])
+  ap.add_argument("what", choices=["gemm", "mx", "attn", "moe", "indexer", "elementwise", "adamwq", "kda", "sparse"])
   for k, d in (("m", 16384), ("n", 2048), ("k", 2048), ("bn", 0), ("b", 4), ("s", 4096), ("h", 16), ("dqk", 192), ("dv", 128),
                ("window", 0), ("tokens", 16384), ("hidden", 2048), ("inter", 1408), ("experts", 64), ("topk", 6),
                ("idx-heads", 4), ("idx-dim", 64), ("iters", 20), ("warmup", 3)):
@@ -102,6 +102,51 @@ def main():
       ms = timed(lambda: attention_forward(q, k, v, a.dqk ** -0.5, a.window), a.iters, a.warmup, flush)
       tf = 2.0 * a.b * a.h * a.s * keys * (a.dqk + a.dv) / ms / 1e9
     out.update(shape=[a.b, a.s, a.h, a.dqk, a.dv], window=a.window, ms=ms, tflops=tf, frac_of_measured_bf16_peak=tf / pk["bf16_tflops"])
+  elif a.what == "adamwq":
+    # expert AdamW that also writes the block-scaled copy of the new weights (one pass: 7 bf16 streams + the copy)
+    from nmoe_b200.ops.quant import expert_adamw_quant_, sf_bytes
+    rows, K = a.experts * 2 * a.inter, a.hidden
+    fp4 = a.dtype in ("nvfp4", "mxfp4", "fp4")
+    p_ = torch.randn(rows, K, device=dev).bfloat16(); g_ = torch.randn_like(p_) * 0.01
+    m_ = torch.zeros_like(p_); v_ = torch.zeros_like(p_)
+    q_ = torch.empty(rows, K // 2 if fp4 else K, dtype=torch.uint8, device=dev)
+    sf_ = torch.empty(sf_bytes(rows, K), dtype=torch.uint8, device=dev)
+    ms = timed(lambda: expert_adamw_quant_(p_, g_, m_, v_, q_, sf_, fp4, lr=1e-3, beta1=0.9, beta2=0.99, eps=1e-8,
+                                           weight_decay=0.1, step=3), a.iters, a.warmup, flush)
+    nbytes = rows * K * (14.0 + (0.5 if fp4 else 1.0) + 1.0 / 32)
+    out.update(rows=rows, K=K, dtype=a.dtype, ms=ms, gbs=nbytes / ms / 1e6, frac_of_measured_hbm=nbytes / ms / 1e6 / pk["hbm_gbs"])
+  elif a.what == "kda":
+    # gated delta rule, chunk form: batched WY transform (library products) + the chunk-recurrence scan kernel
+    from nmoe_b200.ops.kda import kda_chunk_scan, scan
+    B, T, H, Dk, Dv = a.b, a.s, a.h, a.dqk, a.dv
+    q = torch.randn(B, T, H, Dk, device=dev).requires_grad_(a.backward); k = torch.randn(B, T, H, Dk, device=dev)
+    v = torch.randn(B, T, H, Dv, device=dev); g = -torch.rand(B, T, H, Dk, device=dev) * 0.1; beta = torch.rand(B, T, H, device=dev)
+    def run():
+      o = kda_chunk_scan(q, k, v, g, beta)
+      if a.backward:
+        q.grad = None
+        o.sum().backward()
+    ms = timed(run, a.iters, a.warmup, flush)
+    n = T // 64
+    U = torch.randn(B * H, n, 64, Dv, device=dev); P = torch.randn(B * H, n, 64, Dk, device=dev) * 0.05
+    K2 = torch.randn(B * H, n, 64, Dk, device=dev) * 0.05; dec = torch.rand(B * H, n, Dk, device=dev)
+    ms_scan = timed(lambda: scan(U, P, K2, dec), a.iters, a.warmup, flush)
+    fl = 2.0 * B * H * n * 2 * 64 * Dk * Dv
+    out.update(shape=[B, T, H, Dk, Dv], backward=a.backward, ms=ms, scan_kernel_ms=ms_scan, scan_tflops=fl / ms_scan / 1e9)
+  elif a.what == "sparse":
+    # token-sparse attention: per-query top-k bit mask (radix select) + masked tcgen05 attention, against dense causal
+    from nmoe_b200.ops.attention import SparseMask, attention_forward
+    q = torch.randn(a.b, a.s, a.h, a.dqk, device=dev).bfloat16(); k = torch.randn_like(q)
+    v = torch.randn(a.b, a.s, a.h, a.dv, device=dev).bfloat16()
+    scores = torch.randn(a.b, a.s, a.s, device=dev)
+    topk = max(1, a.s // 4)
+    ms_mask = timed(lambda: SparseMask.from_topk_scores(scores, topk), a.iters, a.warmup, flush)
+    mask = SparseMask.from_topk_scores(scores, topk)
+    ms_sparse = timed(lambda: attention_forward(q, k, v, a.dqk ** -0.5, 0, mask=mask), a.iters, a.warmup, flush)
+    ms_dense = timed(lambda: attention_forward(q, k, v, a.dqk ** -0.5, 0), a.iters, a.warmup, flush)
+    ms_sort = timed(lambda: scores.topk(topk, dim=-1), max(2, a.iters // 4), 1, flush)
+    out.update(shape=[a.b, a.s, a.h, a.dqk, a.dv], top_k=topk, mask_topk_ms=ms_mask, torch_topk_ms=ms_sort,
+               masked_attention_ms=ms_sparse, dense_attention_ms=ms_dense)
   elif a.what == "elementwise":
     # the memory-bound kernels of a step on the benchmark's shapes: algorithmic bytes / time against the measured copy rate
     from nmoe_b200.ops.optim import adamw_flat_

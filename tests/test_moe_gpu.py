@@ -206,3 +206,42 @@ def test_wide_hidden_softmax_device_limited_slice_steps_on_gpu():
   G.check_status()
   assert math.isfinite(l0) and l < l0 - 0.02, (l0, l)
   tr.model.rdep.close()
+
+
+def test_moe_bf16_forward_within_bf16_roundings_of_a_faithful_loop():
+  """Per element, not against the global maximum: the bf16 expert path against a per-expert loop that accumulates in
+  fp32 and rounds to bf16 at the same three points the kernels do (H13, the activation, the expert output).  The
+  reference holds its bf16 path to bit equality with its own per-expert loop (tests/test_rdep_accuracy.py:81-98); two
+  different accumulation orders cannot promise bits, so the bar here is three bf16 roundings per element, relative to
+  the element and to the magnitude of the terms that were summed into it (cancellation)."""
+  from nmoe_b200.parallel.rdep import Rdep
+  torch.manual_seed(5)
+  dev = torch.device("cuda")
+  T, H, F, E, K = 512, 256, 512, 8, 2
+  rd = Rdep(H, E, K, T, device=dev)
+  try:
+    x = (torch.randn(T, H, device=dev) * 0.5).bfloat16()
+    W13 = (torch.randn(E, 2 * F, H, device=dev) * 0.05).bfloat16()
+    W2 = (torch.randn(E, H, F, device=dev) * 0.05).bfloat16()
+    eid = torch.stack([torch.randperm(E, device=dev)[:K] for _ in range(T)]).int()
+    gates = torch.rand(T, K, device=dev)
+    out = rd.moe(x, gates, eid, W13, W2).float()
+    torch.cuda.synchronize()
+    ref = torch.zeros(T, H, device=dev)
+    terms = torch.zeros(T, H, device=dev)
+    for k in range(K):
+      for e in range(E):
+        sel = (eid[:, k] == e).nonzero().flatten()
+        if sel.numel() == 0:
+          continue
+        h13 = (x[sel].float() @ W13[e].float().t()).bfloat16().float()
+        a = (torch.nn.functional.silu(h13[:, 0::2]) * h13[:, 1::2]).bfloat16().float()
+        y = (a @ W2[e].float().t()).bfloat16().float()
+        ref[sel] += gates[sel, k].unsqueeze(-1) * y
+        terms[sel] += (gates[sel, k].unsqueeze(-1) * y).abs()
+    ref = ref.bfloat16().float()
+    ulp = 2.0 ** -8
+    excess = (out - ref).abs() - (3 * ulp * ref.abs() + 3 * ulp * terms + 1e-6)
+    assert excess.max().item() <= 0, excess.max().item()
+  finally:
+    rd.close()
