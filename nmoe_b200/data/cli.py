@@ -9,6 +9,7 @@ import argparse
 import json
 import sys
 from pathlib import Path
+from typing import Optional
 
 from .errors import PipelineError
 
@@ -30,28 +31,116 @@ def cmd_prep(a) -> int:
   return 0
 
 
+def _parse_count(v) -> Optional[int]:
+  """'100M' / '1.5B' / '20000' -> int."""
+  if v is None:
+    return None
+  m = {"k": 1e3, "m": 1e6, "b": 1e9, "t": 1e12}
+  v = str(v).strip().lower()
+  return int(float(v[:-1]) * m[v[-1]]) if v and v[-1] in m else int(float(v))
+
+
+def _mixture_grader(a, mix: dict):
+  """The quality filter of ``prep-mixture --hydra-filter``: flags first, then the mixture file's [hydra] table."""
+  from . import hydra as H
+  h = mix.get("hydra", {})
+  ckpt = a.checkpoint or h.get("checkpoint")
+  heads = a.heads_dir or h.get("heads_dir")
+  calib_dir = a.calibration or h.get("calibration") or heads
+  if not ckpt or not heads:
+    raise SystemExit("--hydra-filter needs a grading checkpoint and a heads directory (flags, or [hydra] in the mixture file)")
+  a.checkpoint = ckpt
+  model, dev = _grading_model(a)
+  probe, judge = H.load_heads(heads, model.cfg.hidden_size, dev)
+  calib = H.Calibration.load(calib_dir)
+  score = H.make_flow_grader(model, probe, judge, calib, _tokenizer(a.tokenizer), max_ctx=a.hydra_max_ctx, batch_size=a.hydra_batch_size)
+  return score, calib.tau_keep
+
+
 def cmd_prep_mixture(a) -> int:
-  """Build every source of a mixture/flow under {data_root}/flows/{flow}/{stage}/{source}/train."""
+  """Build the sources of a mixture/flow under {output_root}/{stage}/{source}/{split}.
+
+  Several workers (``--worker-index i --num-workers n``) split the list of (stage, source) pairs round-robin, so an
+  indexed batch job prepares a large mixture in parallel without coordination.  ``--limit`` bounds the documents read
+  per source and prints a SHA-256 over the ids of the documents that were kept, which two runs with the same
+  ``--seed`` must reproduce.  Reference: nmoe/data/cli.py:1483-1511 (prep-mixture flags)."""
+  import hashlib
+  from ..config import load_toml
   from .mixture import resolve_plan
   from .prep import PrepConfig, PrepPipeline
-  from .sources import create_source
-  plan = resolve_plan(mixture_toml=Path(a.mixture), flow_profiles_toml=Path(a.flow_profiles),
-                      flow_section=f"flow.{a.flow}", seq_len=a.seq_len, active_params_b=a.active_params_b)
-  for st in plan.stages:
-    for sp in st.sources:
-      out = Path(a.data_root) / "flows" / a.flow / st.stage_id / sp.id / "train"
-      if sp.hf is not None:
-        src = create_source("hf", dataset=sp.hf.dataset, subset=sp.hf.subset, split=sp.hf.split,
-                            text_field=sp.hf.text_field, data_files=sp.hf.data_files)
-      elif a.local_root:
-        src = create_source("jsonl", paths=str(Path(a.local_root) / sp.id))
-      else:
-        print(f"skip {sp.id}: no hf_dataset in the mixture and no --local-root", file=sys.stderr)
+  from .sources import FilteredSource, create_source
+  mixture = a.mixture or a.config
+  if not mixture:
+    raise SystemExit("prep-mixture needs --mixture (or --config) <mixture.toml>")
+  mix = load_toml(mixture)
+  flow = a.flow
+  if flow is None:
+    flows = sorted(load_toml(a.flow_profiles).get("flow", {}))
+    if len(flows) != 1:
+      raise SystemExit(f"--flow is required: {a.flow_profiles} defines {flows}")
+    flow = flows[0]
+  plan = resolve_plan(mixture_toml=Path(mixture), flow_profiles_toml=Path(a.flow_profiles),
+                      flow_section=f"flow.{flow}", seq_len=a.seq_len, active_params_b=a.active_params_b)
+  root = Path(a.output or a.output_root or Path(a.data_root) / "flows" / flow)
+  jobs = [(st, sp) for st in plan.stages if a.stage in (None, st.stage_id) for sp in st.sources]
+  jobs = [j for i, j in enumerate(jobs) if i % max(1, a.num_workers) == a.worker_index]
+  grader = None
+  if a.hydra_filter and not a.dry_run:
+    grader = _mixture_grader(a, mix)
+  print(f"plan {plan.plan_id} hash {plan.plan_hash[:12]} seed {a.seed}: worker {a.worker_index}/{a.num_workers} takes "
+        f"{len(jobs)} source(s) -> {root}")
+  failed = 0
+  for st, sp in jobs:
+    for split in [x.strip() for x in a.splits.split(",") if x.strip()]:
+      out = root / st.stage_id / sp.id / split
+      need = _parse_count(a.max_tokens) or sp.quota_sequences * (a.seq_len + 1)
+      if a.dry_run:
+        where = f"hf:{sp.hf.dataset}" + (f"/{sp.hf.subset}" if sp.hf.subset else "") if sp.hf is not None else \
+                (str(Path(a.local_root) / sp.id) if a.local_root else "(no source)")
+        print(f"would build {st.stage_id}/{sp.id}/{split}: {need:,} tokens from {where} -> {out}")
         continue
-      need = sp.quota_sequences * (a.seq_len + 1)
-      m = PrepPipeline(src, PrepConfig(str(out), sp.id, tokenizer=a.tokenizer, num_shards=a.num_shards, max_tokens=need)).run()
-      print(f"{st.stage_id}/{sp.id}: {m.total_tokens:,} tokens (quota {need:,})")
-  return 0
+      if (out / "manifest.json").exists() and not a.force:
+        print(f"skip {st.stage_id}/{sp.id}/{split}: {out}/manifest.json exists (--force rebuilds)")
+        continue
+      try:
+        if sp.hf is not None:
+          hf_split = sp.hf.split if split == "train" else (sp.hf.valid_split or split)
+          src = create_source("hf", dataset=sp.hf.dataset, subset=sp.hf.subset, split=hf_split,
+                              text_field=sp.hf.text_field, data_files=sp.hf.data_files)
+        elif a.local_root:
+          src = create_source("jsonl", paths=str(Path(a.local_root) / sp.id))
+        else:
+          print(f"skip {sp.id}: no hf_dataset in the mixture and no --local-root", file=sys.stderr)
+          continue
+        digest = hashlib.sha256(f"seed={a.seed}".encode())
+        src = _Limited(src, a.limit, digest)
+        if grader is not None:
+          src = FilteredSource(src, grader[1], grader[0], a.hydra_batch_size)
+        m = PrepPipeline(src, PrepConfig(str(out), sp.id, tokenizer=a.tokenizer, num_shards=a.num_shards, max_tokens=need,
+                                         source_info={"plan_hash": plan.plan_hash, "seed": a.seed, "stage": st.stage_id})).run()
+        kept = f", kept {src.kept}/{src.seen} after the quality filter" if grader is not None else ""
+        print(f"{st.stage_id}/{sp.id}/{split}: {m.total_tokens:,} tokens (quota {need:,}){kept}; sample ids sha256 {digest.hexdigest()[:16]}")
+      except Exception as e:  # noqa: BLE001 - one bad source must not lose a night's work when asked to go on
+        if not a.continue_on_error:
+          raise
+        failed += 1
+        print(f"FAILED {st.stage_id}/{sp.id}/{split}: {type(e).__name__}: {e}", file=sys.stderr)
+  return 1 if failed else 0
+
+
+class _Limited:
+  """First ``limit`` documents of a source (all when None); folds every document id into ``digest``."""
+
+  def __init__(self, base, limit: Optional[int], digest):
+    self.base, self.limit, self.digest = base, limit, digest
+    self.name = getattr(base, "name", "source")
+
+  def __iter__(self):
+    for i, d in enumerate(self.base):
+      if self.limit is not None and i >= self.limit:
+        return
+      self.digest.update(str(d.doc_id).encode())
+      yield d
 
 
 def cmd_verify(a) -> int:
@@ -146,10 +235,16 @@ def cmd_flow(a) -> int:
     from ..serve import Engine
     from .rephrase import rephrase_batch
     eng = Engine(model, max_seq_len=int(spec.rephrase.get("max_ctx", 4096)), max_batch=int(spec.rephrase.get("batch_size", 32)))
+    rp = spec.rephrase
+    n_ver = int(rp.get("num_versions", 1))
     def rephraser(texts):
-      out = rephrase_batch(eng, tok, texts, num_versions=1, stop_tokens=[getattr(tok, "eot", -1)])
-      by_doc = {r.doc: r.text for r in out}
-      return [by_doc.get(i, t) for i, t in enumerate(texts)]
+      out = rephrase_batch(eng, tok, texts, num_versions=n_ver, chunk_size=int(rp.get("chunk_size", 2048)),
+                           use_style_diversity=bool(rp.get("style_diversity", True)), temperature=float(rp.get("temperature", 0.8)),
+                           top_p=float(rp.get("top_p", 0.9)), stop_tokens=[getattr(tok, "eot", -1)], seed=int(rp.get("seed", 0)))
+      by_doc = {}
+      for r in out:
+        by_doc.setdefault(r.doc, []).append(r.text)
+      return [by_doc.get(i, [t] if n_ver == 1 else []) for i, t in enumerate(texts)]
   run_flow(spec, grader=grader, rephraser=rephraser)
   return 0
 
@@ -328,9 +423,17 @@ def build_parser() -> argparse.ArgumentParser:
   p.add_argument("--num-shards", type=int, default=8); p.add_argument("--workers", type=int, default=1)
   p.add_argument("--max-documents", type=int); p.add_argument("--max-tokens", type=int)
   p = sub.add_parser("prep-mixture"); p.set_defaults(fn=cmd_prep_mixture)
-  p.add_argument("--mixture", required=True); p.add_argument("--flow-profiles", required=True); p.add_argument("--flow", required=True)
+  p.add_argument("--mixture"); p.add_argument("--config", help="same as --mixture")
+  p.add_argument("--flow-profiles", default="configs/flow_profiles.toml"); p.add_argument("--flow")
   p.add_argument("--data-root", default="/data"); p.add_argument("--seq-len", type=int, default=4096); p.add_argument("--local-root")
   p.add_argument("--active-params-b", type=float); p.add_argument("--tokenizer", default="o200k_harmony"); p.add_argument("--num-shards", type=int, default=8)
+  p.add_argument("--output"); p.add_argument("--output-root", help="same as --output; default {data-root}/flows/{flow}")
+  p.add_argument("--stage", choices=["pretrain", "mid", "long"]); p.add_argument("--splits", default="train")
+  p.add_argument("--seed", type=int, default=0); p.add_argument("--limit", type=int); p.add_argument("--max-tokens")
+  p.add_argument("--force", action="store_true"); p.add_argument("--dry-run", action="store_true"); p.add_argument("--continue-on-error", action="store_true")
+  p.add_argument("--worker-index", type=int, default=0); p.add_argument("--num-workers", type=int, default=1)
+  p.add_argument("--hydra-filter", action="store_true"); p.add_argument("--checkpoint"); p.add_argument("--heads-dir"); p.add_argument("--calibration")
+  p.add_argument("--hydra-batch-size", type=int, default=32); p.add_argument("--hydra-max-ctx", type=int, default=4096)
   p = sub.add_parser("verify"); p.set_defaults(fn=cmd_verify); p.add_argument("path"); p.add_argument("--fast", action="store_true")
   p = sub.add_parser("info"); p.set_defaults(fn=cmd_info); p.add_argument("path")
   p = sub.add_parser("regenerate-index"); p.set_defaults(fn=cmd_regenerate_index); p.add_argument("path"); p.add_argument("--eos-token-id", type=int, default=199999)

@@ -102,8 +102,19 @@ def run_flow(spec: FlowSpec, *, grader: Optional[Callable[[List[str]], List[floa
   if spec.rephrase.get("enabled"):
     if rephraser is None:
       raise RuntimeError("flow asks for rephrasing but no rephraser was provided")
+    keep_original = bool(spec.rephrase.get("keep_original", False))
     def _re(docs: List[Document]) -> List[Document]:
-      return [Document(d.doc_id, t, {**d.metadata, "rephrased": True}) for d, t in zip(docs, rephraser([d.text for d in docs]))]
+      # the rephraser answers one text per document, or a list of versions per document
+      out: List[Document] = []
+      for d, r in zip(docs, rephraser([d.text for d in docs])):
+        if keep_original:
+          out.append(d)
+        versions = [r] if isinstance(r, str) else list(r)
+        for v, t in enumerate(versions):
+          if t:
+            out.append(Document(d.doc_id if len(versions) == 1 else f"{d.doc_id}#v{v}", t,
+                                {**d.metadata, "rephrased": True, "version": v}))
+      return out
     src = _Mapped(src, _re, int(spec.rephrase.get("batch_size", 8)))
   p = dict(spec.prep)
   cfg = PrepConfig(output_dir=str(out_dir if n == 1 else out_dir / f"worker_{idx:04d}"), dataset=p.get("dataset", "flow"),

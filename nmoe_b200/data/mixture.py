@@ -111,7 +111,17 @@ def resolve_plan(*, mixture_toml: Path, flow_profiles_toml: Path, flow_section: 
   tokens_b = flow.get("tokens_b")
   ratio = flow.get("tokens_b_ratio")
   override: Dict[str, float] = flow.get("tokens_b_override", {})
-  stage_map: Dict[str, str] = flow.get("mixture", {})
+  stage_map: Dict[str, str] = dict(flow.get("mixture", {}))
+  # A mixture file may say itself which of its tables feeds which stage ([profiles]); that is used for a stage of the
+  # flow whose named table the file does not have, so that one set of flow profiles serves every mixture file.
+  own = {"pretrain": "pretrain_profile", "mid": "midtrain_profile", "long": "longctx_profile"}
+  for stage_id in flow.get("stages", list(stage_map)):
+    if stage_map.get(stage_id) not in mix.get("mixtures", {}):
+      alt = mix.get("profiles", {}).get(own.get(stage_id, ""))
+      if alt in mix.get("mixtures", {}):
+        stage_map[stage_id] = alt
+      elif stage_id in stage_map and "profiles" in mix:
+        del stage_map[stage_id]          # the file declares its stages and has none for this one
   if ratio is not None and tokens_b is None:
     if active_params_b is None:
       raise ValueError(f"{flow_section} uses tokens_b_ratio but active_params_b is not set")

@@ -110,19 +110,27 @@ def run_eval(model, cfg, *, rank: int, world: int, max_examples: int = 500, task
           for name, t in tasks.items()}
 
 
+def core_metric(res: Dict[str, Dict[str, float]]) -> float:
+  """Mean centred accuracy over the tasks (the CORE number when the group is the CORE suite)."""
+  return sum(v["centered_acc"] for v in res.values()) / len(res) if res else 0.0
+
+
 def format_results(res: Dict[str, Dict[str, float]]) -> str:
-  return " ".join(f"{k}:acc={v['acc']:.3f}(c={v['centered_acc']:.3f},n={int(v['n'])})" for k, v in res.items())
+  return f"mean_centered={core_metric(res):.4f} " + " ".join(f"{k}:acc={v['acc']:.3f}(c={v['centered_acc']:.3f},n={int(v['n'])})" for k, v in res.items())
 
 
 def main(argv=None) -> None:
   ap = argparse.ArgumentParser(description="score a checkpointed model on multiple-choice tasks")
   ap.add_argument("config"); ap.add_argument("--tasks-file"); ap.add_argument("--max-examples", type=int, default=500)
+  ap.add_argument("--group", help="task group of the file (default: the config's eval_tasks)")
   a = ap.parse_args(argv)
   from .. import runtime
   from ..checkpoint import Checkpointer, load_checkpoint
   from ..config import from_toml
   from ..train import Trainer
   cfg = from_toml(a.config)
+  if a.group:
+    cfg.eval_tasks = a.group
   rank, world, dev = runtime.init(cfg.seed)
   tr = Trainer(cfg, rank=rank, world=world, device=dev)
   load_checkpoint(Checkpointer(cfg.checkpoint_dir, async_io=False), tr, None, None, cfg, rank)

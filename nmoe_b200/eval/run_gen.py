@@ -86,22 +86,32 @@ def eval_gen_task(model, enc, name: str, task: Dict[str, Any], *, rank: int, wor
   was_training = model.training
   model.eval()
   correct = n = 0
+  f1_sum = 0.0
   for i in range(per_rank):
     ex = mine[i] if i < len(mine) else examples[0]
     toks = generate_lockstep(model, enc.encode_ordinary(ex.prompt), max_new=max_new, eos_id=eos_id, steps_global=max_new,
                              active=i < len(mine))
     if i < len(mine):
       text = enc.decode(toks)
-      ok = mod.is_correct(text, ex.meta, ex.prompt) if name == "humaneval" else mod.is_correct(text, ex.reference)
+      if mod is REGISTRY["humaneval"]:
+        ok = mod.is_correct(text, ex.meta, ex.prompt)
+      elif mod is REGISTRY["span"]:
+        ok = mod.is_correct(text, ex.reference, ex.meta)
+        f1_sum += mod.best_f1(text, ex.meta.get("answers") or [ex.reference])
+      else:
+        ok = mod.is_correct(text, ex.reference)
       correct += int(ok)
       n += 1
-  t = torch.tensor([correct, n], dtype=torch.float64, device=next(model.parameters()).device)
+  t = torch.tensor([correct, n, f1_sum], dtype=torch.float64, device=next(model.parameters()).device)
   if dist.is_initialized() and world > 1:
     dist.all_reduce(t)
   if was_training:
     model.train()
-  c, n = t.tolist()
-  return {"acc": c / n if n else 0.0, "n": n}
+  c, n, f = t.tolist()
+  out = {"acc": c / n if n else 0.0, "n": n}
+  if mod is REGISTRY["span"]:
+    out["f1"] = f / n if n else 0.0
+  return out
 
 
 def main(argv=None) -> None:
@@ -119,7 +129,7 @@ def main(argv=None) -> None:
   tr = Trainer(cfg, rank=rank, world=world, device=dev)
   load_checkpoint(Checkpointer(cfg.checkpoint_dir, async_io=False), tr, None, None, cfg, rank)
   with open(a.tasks_file, "rb") as f:
-    tasks = {k: v for k, v in tomllib.load(f).get("tasks", {}).items() if v.get("kind") == "gen"}
+    tasks = {k: v for k, v in tomllib.load(f).get("tasks", {}).items() if v.get("kind") in ("gen", "span")}
   enc = get_tokenizer(cfg.tokenizer)
   for name, t in tasks.items():
     r = eval_gen_task(tr.model, enc, name, t, rank=rank, world=world, max_examples=a.max_examples, eos_id=cfg.eos_token_id,

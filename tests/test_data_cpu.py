@@ -184,3 +184,55 @@ def test_metadata_snapshot_filter(tmp_path):
   assert [g.arxiv_id for g in got] == ["2301.1"] and got[0].title == "A b" and got[0].authors == ["Ada Lovelace"]
   assert got[0].submitted == "Mon" and got[0].updated == "Tue"
   assert [g.authors for g in load_metadata_snapshot(str(p), categories=["math"])] == [["C. D.", "E. F."]]
+
+
+def test_prep_mixture_profiles_workers_limit(tmp_path, capsys):
+  """A mixture file that names its own stage tables ([profiles]) resolves against the shared flow profiles; two
+  workers split the sources; --limit bounds the documents and the sample-id digest repeats for the same seed."""
+  from nmoe_b200.data.cli import main
+  from nmoe_b200.data.mixture import resolve_plan
+  mix = tmp_path / "mix.toml"
+  mix.write_text('[profiles]\npretrain_profile = "mine"\n[mixtures.mine]\ntotal_tokens_b = 0.001\n'
+                 'sources = [{id = "a", tokens_b = 3.0}, {id = "b", tokens_b = 1.0}]\n')
+  flows = tmp_path / "flows.toml"
+  flows.write_text('[flow.dev]\nmode = "dev"\nstages = ["pretrain", "mid"]\ntokens_b = 0.00002\n'
+                   '[flow.dev.mixture]\npretrain = "pretrain_main"\nmid = "mid_quality"\n')
+  plan = resolve_plan(mixture_toml=mix, flow_profiles_toml=flows, flow_section="flow.dev", seq_len=64)
+  assert [s.stage_id for s in plan.stages] == ["pretrain"] and [sp.id for sp in plan.stages[0].sources] == ["a", "b"]
+  q = [sp.quota_sequences for sp in plan.stages[0].sources]
+  assert q[0] == 3 * q[1] or abs(q[0] - 3 * q[1]) <= 3
+  for name in ("a", "b"):
+    d = tmp_path / "raw" / name
+    d.mkdir(parents=True)
+    (d / "x.jsonl").write_text("".join(json.dumps({"id": f"{name}{i}", "text": f"{name} document number {i} " * 8}) + "\n" for i in range(40)))
+  common = ["prep-mixture", "--config", str(mix), "--flow-profiles", str(flows), "--seq-len", "64", "--tokenizer", "bytes",
+            "--num-shards", "2", "--local-root", str(tmp_path / "raw"), "--seed", "7", "--limit", "10"]
+  outs = []
+  for w in (0, 1):
+    assert main(common + ["--output", str(tmp_path / "out"), "--worker-index", str(w), "--num-workers", "2"]) == 0
+    outs.append(capsys.readouterr().out)
+  assert "pretrain/a/train" in outs[0] and "pretrain/b/train" not in outs[0] and "pretrain/b/train" in outs[1]
+  assert (tmp_path / "out/pretrain/a/train/manifest.json").exists() and (tmp_path / "out/pretrain/b/train/manifest.json").exists()
+  # same seed, same documents -> same digest; an existing manifest is left alone without --force
+  assert main(common + ["--output", str(tmp_path / "out2"), "--stage", "pretrain"]) == 0
+  again = capsys.readouterr().out
+  dig = lambda text, key: [l.split("sha256 ")[1] for l in text.splitlines() if key in l and "sha256" in l][0]
+  assert dig(again, "pretrain/a/train") == dig(outs[0], "pretrain/a/train")
+  assert main(common + ["--output", str(tmp_path / "out2")]) == 0
+  assert "manifest.json exists" in capsys.readouterr().out
+  assert main(common + ["--output", str(tmp_path / "out3"), "--dry-run"]) == 0
+  assert "would build pretrain/a/train" in capsys.readouterr().out and not (tmp_path / "out3").exists()
+
+
+def test_flow_writes_every_rephrased_version(tmp_path):
+  """keep_original + a rephraser that answers a list per document: the shards hold the original and every version."""
+  raw = tmp_path / "raw.jsonl"
+  raw.write_text("".join(json.dumps({"id": f"d{i}", "text": f"text {i} " * 6}) + "\n" for i in range(5)))
+  spec = tmp_path / "flow.toml"
+  spec.write_text(f'[source]\nkind = "jsonl"\npaths = "{raw}"\n[prep]\noutput_dir = "{tmp_path / "out"}"\ndataset = "f"\n'
+                  'tokenizer = "bytes"\nnum_shards = 1\n[rephrase]\nenabled = true\nkeep_original = true\nnum_versions = 3\n')
+  s = flow_mod.load_spec(spec, env={})
+  m = flow_mod.run_flow(s, rephraser=lambda texts: [[t.upper(), t + "again", ""] for t in texts], env={}, print_fn=lambda *_: None)
+  assert m.total_documents == 5 * 3                # original + two non-empty versions
+  k2 = flow_mod.load_spec("configs/dataflow/dataprep_k2.toml", env={})
+  assert k2.rephrase["num_versions"] == 10 and k2.grade["enabled"] and k2.source["kind"] == "hf"

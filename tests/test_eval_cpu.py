@@ -119,3 +119,46 @@ sys.exit(0)
   # and a program that hangs is cut off with its children
   ok, out = run_python("import os, time\nos.fork()\ntime.sleep(60)\n", timeout_s=1.0)
   assert not ok and out == "timeout"
+
+
+def test_core_suite_row_formats_fewshot_and_span_scoring(tmp_path):
+  """Every task of configs/eval/tasks_core.toml parses rows of its dataset's layout; few-shot rows become a prefix;
+  the span scorer is SQuAD's exact match / F1 over the accepted answers."""
+  import json, tomllib
+  from nmoe_b200.eval import adapters as A
+  from nmoe_b200.eval.choices import load_tasks
+  from nmoe_b200.eval.tasks import span
+  tasks = tomllib.load(open("configs/eval/tasks_core.toml", "rb"))
+  assert set(load_tasks("configs/eval/tasks_core.toml", "core")) == set(tasks["groups"]["core"])
+  assert A.parse_hf_source("hf:allenai/ai2_arc:ARC-Easy:test", {}) == ("allenai/ai2_arc", "ARC-Easy", "test")
+  assert A.parse_hf_source("hf:google/boolq:validation", {}) == ("google/boolq", None, "validation")
+  rows = {
+    "arc_easy": {"question": "2+2?", "choices": {"text": ["3", "4", "5"], "label": ["1", "2", "3"]}, "answerKey": "2"},
+    "hellaswag": {"ctx": "A man is", "endings": ["x", "y", "z", "w"], "label": "3"},
+    "mmlu": {"question": "q", "choices": ["a", "b", "c", "d"], "answer": 2},
+    "openbookqa": {"question_stem": "stem", "choices": {"text": ["a", "b"], "label": ["A", "B"]}, "answerKey": "B"},
+    "winogrande": {"sentence": "The cup fell because _ was wet.", "option1": "the cup", "option2": "the table", "answer": "2"},
+    "boolq": {"passage": "p", "question": "is it", "answer": True},
+    "copa": {"premise": "It rained.", "choice1": "The road got wet.", "choice2": "The sun rose.", "question": "effect", "label": 0},
+  }
+  want = {"arc_easy": 1, "hellaswag": 3, "mmlu": 2, "openbookqa": 1, "winogrande": 1, "boolq": 1, "copa": 0}
+  for name, row in rows.items():
+    f = tmp_path / f"{name}.jsonl"
+    f.write_text("".join(json.dumps(row) + "\n" for _ in range(8)))
+    t = dict(tasks["tasks"][name], source=f"jsonl:{f}")
+    ex = list(A.iter_choices(t, max_examples=2))
+    assert len(ex) == 2 and ex[0].answer_idx == want[name], name
+    if name == "mmlu":
+      assert ex[0].prompt.count("Question: q") == 6          # five solved shots + the question
+    if name == "winogrande":
+      assert ex[0].prompt == "The cup fell because" and ex[0].options[1] == "the table was wet."
+    if name == "copa":
+      assert ex[0].prompt == "It rained therefore" and ex[0].options[0] == "the road got wet."
+  f = tmp_path / "squad.jsonl"
+  f.write_text("".join(json.dumps({"context": "Paris is in France.", "question": "Where is Paris?",
+                                   "answers": {"text": ["France", "in France"]}}) + "\n" for _ in range(4)))
+  sp = list(A.iter_span(dict(tasks["tasks"]["squad"], source=f"jsonl:{f}"), max_examples=5))
+  assert len(sp) == 2 and sp[0].meta["answers"] == ["France", "in France"] and sp[0].prompt.count("Answer:") == 3
+  assert span.is_correct(" The France.\nQuestion: next", "France", sp[0].meta)
+  assert not span.is_correct("Germany", "France", sp[0].meta)
+  assert abs(span.best_f1("in the country France", ["France", "in France"]) - 0.8) < 1e-6
