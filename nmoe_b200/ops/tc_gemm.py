@@ -136,6 +136,17 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     assert not accumulate
     out = torch.empty(M, N, dtype=out_dtype, device=a.device)
   assert out.stride(1) == 1 and out.shape == (M, N)
+  # TMA wants every row stride a multiple of 16 bytes.  Tiny projections (a per-head scalar gate: 4 outputs) break that
+  # in one of their backward products; pad the offending extent with zeros (a copy of a thin operand).
+  if K % 8 and not (a_mn and b_mn):
+    r = (-K) % 8
+    a = torch.nn.functional.pad(a, (0, 0, 0, r) if a_mn else (0, r))
+    b = torch.nn.functional.pad(b, (0, 0, 0, r) if b_mn else (0, r))
+    K += r
+  if a.stride(0) % 8:
+    a = torch.nn.functional.pad(a, (0, (-a.size(1)) % 8)) if a.size(1) % 8 else a.contiguous()
+  if b.stride(0) % 8:
+    b = torch.nn.functional.pad(b, (0, (-b.size(1)) % 8)) if b.size(1) % 8 else b.contiguous()
   st = status_buffer(a.device)
   if bn == 0 and use_pair(M, N):
     L.check(L.lib().nmoe_gemm_bf16_pair(

@@ -144,7 +144,50 @@ def check_zero2(rank, world, dev):
   return err
 
 
-def check_train(rank, world, dev):
+def check_zero2_overlap(rank, world, dev):
+  """Bucketed ZeRO-2 stepped from backward hooks on a side stream == the same buckets stepped after backward,
+  bit for bit (the update is elementwise and the ranks are summed in rank order either way)."""
+  import os
+  from nmoe_b200.config import Config
+  from nmoe_b200.parallel.zero2 import Zero2
+  cfg = Config(dim=8, n_layers=1, n_heads=1)
+  cfg.zero2_impl = "fused"
+  cfg.zero2_bucket_mb = 0.05                       # ~26k elements per bucket -> several buckets
+  results = {}
+  for overlap in (False, True):
+    cfg.zero2_overlap = True
+    g = torch.Generator().manual_seed(3)
+    params = [torch.nn.Parameter((torch.randn(n, generator=g)).bfloat16().to(dev)) for n in (1000, 40960, 77, 130000, 512, 30000)]
+    z = Zero2([{"name": "dense_decay", "params": params[:4], "lr": 1e-2, "weight_decay": 0.1},
+               {"name": "router", "params": params[4:], "lr": 5e-3, "weight_decay": 0.0}], cfg)
+    assert z.impl == "fused" and z.overlap and len(z.groups) >= 4, (z.impl, z.overlap, len(z.groups))
+    gn = torch.zeros(1, device=dev)
+    z.gradnorm_sq = gn
+    for step in range(3):
+      z.zero_grad()
+      if not overlap:
+        z._armed = False                           # same buckets, everything stepped by step()
+      gg = torch.Generator().manual_seed(1000 * step + rank)
+      loss = 0
+      for p in params:
+        c = (torch.randn(p.numel(), generator=gg) * 0.1).bfloat16().to(dev).view_as(p)
+        loss = loss + (p * c).sum()
+      loss.backward()
+      if overlap:
+        assert all(g_.launched for g_ in z.groups), [g_.launched for g_ in z.groups]
+      z.step()
+    torch.cuda.synchronize()
+    G.check_status()
+    results[overlap] = (torch.cat([p.detach().float().cpu().view(-1) for p in params]), float(gn.item()))
+    sd = z.state_dict()
+    z.load_state_dict(sd)
+    dist.barrier()
+  assert torch.equal(results[False][0], results[True][0])
+  assert abs(results[False][1] - results[True][1]) <= 1e-3 * abs(results[False][1])
+  return len(z.groups)
+
+
+def check_train(rank, world, dev, overlap=False):
   import math
   from nmoe_b200.config import Config
   from nmoe_b200.train import Trainer
@@ -152,8 +195,11 @@ def check_train(rank, world, dev):
                n_routed_experts=8, n_activated_experts=2, n_shared_experts=1, n_dense_layers=1, q_lora_rank=96,
                kv_lora_rank=64, qk_nope_head_dim=32, qk_rope_head_dim=32, v_head_dim=32, batch_size=2 * world,
                seq_len=128, max_position_embeddings=256, warmup_steps=1, lr_dense=3e-3, lr_expert=3e-3, lr_router=3e-3)
+  cfg.zero2_overlap = overlap
+  cfg.zero2_bucket_mb = 0.25
   torch.manual_seed(11)                      # same dense init on every rank
   tr = Trainer(cfg, rank=rank, world=world, device=dev)
+  assert tr.opt.dense.overlap == overlap
   g = torch.Generator().manual_seed(50 + rank)
   tok = torch.randint(0, 1000, (2, 129), generator=g)
   x, y = tok[:, :-1].contiguous(), tok[:, 1:].contiguous()
@@ -173,7 +219,9 @@ def main():
   rank, world, dev = runtime.init(0)
   out = {"moe": check_moe(rank, world, dev), "moe_fp8": check_moe(rank, world, dev, "fp8"),
          "moe_nvfp4": check_moe(rank, world, dev, "nvfp4"), "zero2": check_zero2(rank, world, dev),
-         "train": check_train(rank, world, dev), "capacity_drop": check_capacity_drop(rank, world, dev)}
+         "zero2_overlap": check_zero2_overlap(rank, world, dev),
+         "train": check_train(rank, world, dev), "train_overlap": check_train(rank, world, dev, overlap=True),
+         "capacity_drop": check_capacity_drop(rank, world, dev)}
   dist.barrier()
   if rank == 0:
     print("MP_WORKER_OK", out, flush=True)

@@ -144,3 +144,23 @@ def test_pair_grouped_wgrad_and_fp32_accumulate():
     else:
       _close(out[e], ref)
       _close(acc[e], 1 + ref)
+
+
+@pytest.mark.parametrize("out_features", [4, 12, 20])
+def test_linear_with_a_thin_output_has_a_right_backward(out_features):
+  """A per-head scalar projection (4 outputs): in its backward the thin extent becomes a row stride (dy [M,4],
+  dy^T), which TMA cannot address; the wrapper pads it.  Forward and both gradients against fp32."""
+  from nmoe_b200 import ops
+  torch.manual_seed(0)
+  dev = torch.device("cuda")
+  x = torch.randn(4096, 512, device=dev).bfloat16().requires_grad_(True)
+  w = (torch.randn(out_features, 512, device=dev) * 0.05).bfloat16().requires_grad_(True)
+  gy = torch.randn(4096, out_features, device=dev).bfloat16()
+  y = ops.linear(x, w)
+  y.backward(gy)
+  xr, wr = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+  yr = xr @ wr.t()
+  yr.backward(gy.float())
+  for got, ref, name in ((y, yr, "y"), (x.grad, xr.grad, "dx"), (w.grad, wr.grad, "dw")):
+    err = (got.float() - ref).abs().max().item()
+    assert err <= 2e-2 * ref.abs().max().item() + 1e-3, (name, err, ref.abs().max().item())

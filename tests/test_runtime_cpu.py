@@ -279,3 +279,26 @@ def test_nvshmem_transport_library_builds_and_exports_its_entry_points():
   assert h.nmoe_hybrid_available() == 1 and h.nmoe_hybrid_uid_bytes() >= 64
   # before initialisation every call that needs the runtime refuses instead of touching it
   assert h.nmoe_hybrid_quiet(None) == -1 and h.nmoe_hybrid_alloc(ctypes.c_size_t(16), None) == -1
+
+
+def test_zero2_buckets_walk_parameters_backwards_and_pin_the_checkpoint_layout():
+  import torch
+  from nmoe_b200.config import Config
+  from nmoe_b200.parallel.zero2 import Zero2, bucketize
+  ps = [torch.nn.Parameter(torch.zeros(n)) for n in (10, 20, 30, 40, 5)]
+  b = bucketize([{"name": "dense_decay", "params": ps, "lr": 1.0, "weight_decay": 0.0}], 45)
+  assert [[p.numel() for p in g["params"]] for g in b] == [[5, 40], [30, 20], [10]]
+  assert all(g["name"] == "dense_decay" for g in b)
+  assert bucketize([{"name": "x", "params": ps}], 0)[0]["params"] is ps
+  # on CPU overlap is refused (no streams), the layout is recorded, and a foreign layout is rejected on load
+  cfg = Config(dim=8, n_layers=1, n_heads=1)
+  cfg.zero2_overlap = True
+  z = Zero2([{"name": "dense_decay", "params": ps, "lr": 1e-2, "weight_decay": 0.0}], cfg)
+  assert not z.overlap and len(z.groups) == 1
+  sd = z.state_dict()
+  assert sd["zero2_layout"]["bucket_elems"] == 0
+  z.load_state_dict(sd)
+  sd["zero2_layout"] = {"bucket_elems": 123, "totals": [1]}
+  import pytest
+  with pytest.raises(ValueError, match="layout"):
+    z.load_state_dict(sd)

@@ -51,3 +51,36 @@ def test_loss_falls_on_a_moonlight_shaped_model(tmp_path, monkeypatch, dtype):
   if tags:
     assert any("attn_fwd" in t for t in tags) and any("moe_bwd" in t for t in tags), sorted(tags)[:40]
   w.close()
+
+
+def test_dense_updates_issued_from_backward_hooks_match_the_step_after_backward(tmp_path):
+  """ZeRO-2 overlap on one GPU: the dense parameters are cut into buckets and every bucket's AdamW is queued on a side
+  stream as soon as backward has written its last gradient.  The update is elementwise, so the parameters after a
+  few steps must equal, bit for bit, those of the plain step after backward."""
+  from nmoe_b200.ops import tc_gemm as G
+  from nmoe_b200.train import Trainer
+  dev = torch.device("cuda")
+  finals, losses = [], []
+  for overlap in (False, True):
+    cfg = _cfg(tmp_path, dtype="bf16", zero2_overlap=overlap, zero2_bucket_mb=1)
+    torch.manual_seed(5)
+    tr = Trainer(cfg, rank=0, world=1, device=dev, fuse_expert_opt=False)
+    assert tr.opt.dense.overlap == overlap and (len(tr.opt.dense.groups) > 3) == overlap
+    g = torch.Generator().manual_seed(9)
+    tok = torch.randint(0, 2000, (4, 257), generator=g)
+    x, y = tok[:, :-1].contiguous().to(dev), tok[:, 1:].contiguous().to(dev)
+    ls = []
+    for _ in range(4):
+      ls.append(float(tr.step(x, y).item()))
+      if overlap:
+        assert tr.opt.dense.side is not None
+    torch.cuda.synchronize()
+    G.check_status()
+    named = dict(tr.model.named_parameters())
+    dense = {id(p) for g_ in tr.opt.dense.groups for p in g_.params}
+    finals.append({n: p.detach().float().cpu().clone() for n, p in named.items() if id(p) in dense})
+    losses.append(ls)
+  assert losses[0] == losses[1], losses
+  assert finals[0].keys() == finals[1].keys() and len(finals[0]) > 5
+  for n in finals[0]:
+    assert torch.equal(finals[0][n], finals[1][n]), n
