@@ -301,8 +301,12 @@ int nmoe_expert_adamw_quant(void* p, const void* g, void* m, void* v, long long 
   const float inv_bc2_sqrt = 1.f / sqrtf(1.f - powf(beta2, static_cast<float>(step)));
   const int sfc = ((K / 32) + 3) & ~3;
   const long long nvec = rows * (K / 8);
+  // One vector per thread (the loop in the kernel only matters beyond 2^31 blocks): with short-lived blocks the
+  // hardware scheduler keeps every SM's load queues full, which a grid-stride loop whose body is ~200 instructions of
+  // packing between its loads and the next ones does not (measured: 0.92 against 1.06 of the copy rate for the
+  // plain AdamW kernel that is launched this way).
   long long want = (nvec + 255) / 256;
-  const unsigned blocks = static_cast<unsigned>(want < 148 * 16 ? want : 148 * 16);
+  const unsigned blocks = static_cast<unsigned>(want < 0x7fffffffLL ? want : 0x7fffffffLL);
   auto pp = static_cast<__nv_bfloat16*>(p);
   auto gg = static_cast<const __nv_bfloat16*>(g);
   auto mm = static_cast<__nv_bfloat16*>(m);

@@ -41,7 +41,9 @@ def main():
     assert got == [b"handle-of-%d" % r for r in range(world)], got
     print("EXCHANGE OK", flush=True)
   elif scenario in ("leave_between_steps", "stall_between_steps"):
-    h = Health(rank, world, stall_s=2.0)
+    # a loaded test machine can hold a healthy rank up for a second or two: the "leave" scenario must only ever see
+    # the loss, and the "stall" scenario's threshold sits well above scheduling noise
+    h = Health(rank, world, stall_s=30.0 if scenario == "leave_between_steps" else 4.0)
     dist.barrier()
     try:
       for step in range(1, 200):
@@ -55,7 +57,7 @@ def main():
               h.fail(repr(e))                      # what train()'s handler does
               os._exit(1)
           else:
-            time.sleep(8)                          # stops making progress, stays alive
+            time.sleep(14)                         # stops making progress, stays alive
             os._exit(0)
         h.beat(step)
       print("NOT DETECTED", flush=True)

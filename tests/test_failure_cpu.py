@@ -55,11 +55,11 @@ def test_rank_that_leaves_between_steps_is_seen_before_the_next_launch():
   outs, took = _run("leave_between_steps", 3)
   for o in outs[:2]:
     assert "DETECTED lost" in o and "injected failure after step 3" in o, outs
-  assert took < 30, took
+  assert took < 45, took
 
 
 def test_rank_that_stalls_between_steps_is_reported():
   outs, took = _run("stall_between_steps", 3)
   for o in outs[:2]:
     assert "DETECTED stalled" in o and "rank 2" in o, outs
-  assert took < 30, took
+  assert took < 45, took
