@@ -23,7 +23,10 @@ def cmd_prep(a) -> int:
     kw["text_field"] = a.text_field
   cfg = PrepConfig(output_dir=a.output, dataset=a.name, version=a.version, tokenizer=a.tokenizer, num_shards=a.num_shards,
                    max_documents=a.max_documents, max_tokens=a.max_tokens)
-  if a.workers > 1:
+  if a.runner != "process":
+    from .prep import run_beam_pipeline
+    m = run_beam_pipeline(create_source(a.source, **kw), cfg, runner=a.runner)
+  elif a.workers > 1:
     m = ParallelPrepPipeline(lambda: create_source(a.source, **kw), cfg, a.workers).run()
   else:
     m = PrepPipeline(create_source(a.source, **kw), cfg).run()
@@ -422,6 +425,8 @@ def build_parser() -> argparse.ArgumentParser:
   p.add_argument("--name", required=True); p.add_argument("--version", default="v1"); p.add_argument("--tokenizer", default="o200k_harmony")
   p.add_argument("--num-shards", type=int, default=8); p.add_argument("--workers", type=int, default=1)
   p.add_argument("--max-documents", type=int); p.add_argument("--max-tokens", type=int)
+  p.add_argument("--runner", default="process", choices=["process", "beam", "local", "auto"],
+                 help="process: worker processes on this host; beam / local / auto: the stage graph on Apache Beam or the built-in runner")
   p = sub.add_parser("prep-mixture"); p.set_defaults(fn=cmd_prep_mixture)
   p.add_argument("--mixture"); p.add_argument("--config", help="same as --mixture")
   p.add_argument("--flow-profiles", default="configs/flow_profiles.toml"); p.add_argument("--flow")

@@ -111,13 +111,91 @@ class ParallelPrepPipeline:
     return m
 
 
-def run_beam_pipeline(*_a, **_k):
-  """Apache Beam runner of the same transform chain; Beam is an optional dependency."""
-  try:
-    import apache_beam  # noqa: F401
-  except ImportError as e:
-    raise RuntimeError("the Beam runner needs the 'apache_beam' package; use ParallelPrepPipeline instead") from e
-  raise NotImplementedError("Beam runner: wire PrepPipeline's transforms into a beam.Pipeline for your runner")
+# ------------------------------------------------------------------ Beam runner
+# The same chain as a graph of three stages, so that a distributed runner can spread it over workers:
+#   documents --tokenise (element-wise)--> (shard id, (doc id, tokens)) --group by shard--> write one shard family each
+# With Apache Beam installed the stages become ParDo / GroupByKey / ParDo on any Beam runner (Dataflow, Flink, Direct);
+# without it the built-in runner below executes the very same stage functions in this process, which is also how the
+# stages are tested.  Documents inside a shard are written in doc-id order, so the output does not depend on the order
+# in which a runner delivers a group.  Reference: nmoe/data/prep.py:404-537 (TokenizeDoFn, AssignShardDoFn, WriteShardDoFn).
+
+def beam_tokenize_stage(cfg: PrepConfig):
+  """element {"doc_id", "text"} -> zero or one (shard id, (doc id, token list))."""
+  state = {}
+  def fn(doc: dict):
+    if "enc" not in state:                       # built on the worker, not pickled with the stage
+      state["enc"] = get_tokenizer(cfg.tokenizer)
+    text = normalize_text(doc["text"])
+    if len(text) < cfg.min_chars:
+      return
+    toks = state["enc"].encode_ordinary(text)
+    if toks:
+      yield get_shard_id(doc["doc_id"], cfg.num_shards), (doc["doc_id"], toks)
+  return fn
+
+
+def beam_write_stage(cfg: PrepConfig, source_name: str):
+  """(shard id, iterable of (doc id, tokens)) -> the manifest (as a dict) of that shard's files."""
+  def fn(group):
+    sid, docs = group
+    vocab, eos = tokenizer_info(cfg.tokenizer)
+    w = ShardedWriter(Path(cfg.output_dir), cfg.dataset, cfg.version, cfg.num_shards, cfg.tokenizer, vocab, eos,
+                      shard_ids=[int(sid)], source_info={"source": source_name, **cfg.source_info})
+    for _doc_id, toks in sorted(docs, key=lambda d: d[0]):
+      w.add_document(int(sid), toks)
+    yield w.finalize(write_manifest=False).to_dict()
+  return fn
+
+
+class LocalStageRunner:
+  """In-process execution of the stage graph (flat-map, group-by-key, flat-map)."""
+
+  def run(self, elements, tokenize, write) -> List[dict]:
+    groups: Dict[int, list] = {}
+    for el in elements:
+      for k, v in tokenize(el):
+        groups.setdefault(k, []).append(v)
+    out: List[dict] = []
+    for k in sorted(groups):
+      out.extend(write((k, groups[k])))
+    return out
+
+
+def run_beam_pipeline(source: DataSource, cfg: PrepConfig, pipeline_options=None, runner: str = "auto") -> ManifestInfo:
+  """Build the shards of ``source`` through the stage graph.  ``runner``: "beam" (needs apache_beam; ``pipeline_options``
+  go to ``beam.Pipeline``), "local" (built-in), or "auto" (beam when importable)."""
+  docs = ({"doc_id": d.doc_id, "text": d.text} for d in source)
+  if cfg.max_documents:
+    import itertools
+    docs = itertools.islice(docs, cfg.max_documents)
+  tokenize, write = beam_tokenize_stage(cfg), beam_write_stage(cfg, source.name)
+  beam = None
+  if runner in ("auto", "beam"):
+    try:
+      import apache_beam as beam  # type: ignore
+    except ImportError:
+      if runner == "beam":
+        raise RuntimeError("runner='beam' needs the 'apache_beam' package (pip install apache-beam[gcp]); "
+                           "runner='local' runs the same stages in this process")
+  Path(cfg.output_dir).mkdir(parents=True, exist_ok=True)
+  if beam is not None:
+    parts_path = Path(cfg.output_dir) / "manifest.parts.jsonl"
+    with beam.Pipeline(options=pipeline_options) as p:
+      (p | "Documents" >> beam.Create(list(docs))
+         | "Tokenize" >> beam.FlatMap(tokenize)
+         | "ByShard" >> beam.GroupByKey()
+         | "WriteShards" >> beam.FlatMap(write)
+         | "ToJson" >> beam.Map(json.dumps)
+         | "Parts" >> beam.io.WriteToText(str(parts_path), shard_name_template="", num_shards=1))
+    parts = [json.loads(l) for l in parts_path.read_text().splitlines() if l.strip()]
+    parts_path.unlink()
+  else:
+    parts = LocalStageRunner().run(docs, tokenize, write)
+  if not parts:
+    raise RuntimeError("the source produced no documents")
+  m = merge_manifests([ManifestInfo.from_dict(p) for p in parts])
+  write_manifest_file(Path(cfg.output_dir) / "manifest.json", m)
+  return m
 
 
 class ResumeState:

@@ -55,12 +55,37 @@ def test_loss_falls_on_a_moonlight_shaped_model(tmp_path, monkeypatch, dtype):
 
 def test_dense_updates_issued_from_backward_hooks_match_the_step_after_backward(tmp_path):
   """ZeRO-2 overlap on one GPU: the dense parameters are cut into buckets and every bucket's AdamW is queued on a side
-  stream as soon as backward has written its last gradient.  The update is elementwise, so the parameters after a
-  few steps must match those of the plain step after backward."""
+  stream as soon as backward has written its last gradient.  (a) With exactly reproducible gradients (loss = sum p*c)
+  the parameters equal, bit for bit, those of the same buckets stepped after backward.  (b) A whole model trains to
+  the same loss curve either way (its own reductions are not bitwise repeatable, so the curve is compared)."""
+  from nmoe_b200.config import Config
   from nmoe_b200.ops import tc_gemm as G
+  from nmoe_b200.parallel.zero2 import Zero2
   from nmoe_b200.train import Trainer
   dev = torch.device("cuda")
-  finals, losses = [], []
+  cfg0 = Config(dim=8, n_layers=1, n_heads=1)
+  cfg0.zero2_overlap, cfg0.zero2_bucket_mb = True, 0.05
+  res = {}
+  for from_hooks in (False, True):
+    g = torch.Generator().manual_seed(3)
+    params = [torch.nn.Parameter(torch.randn(n, generator=g).bfloat16().to(dev)) for n in (1000, 40960, 77, 130000, 512, 30000)]
+    z = Zero2([{"name": "dense_decay", "params": params[:4], "lr": 1e-2, "weight_decay": 0.1},
+               {"name": "router", "params": params[4:], "lr": 5e-3, "weight_decay": 0.0}], cfg0)
+    assert z.impl == "single" and z.overlap and len(z.groups) >= 4
+    for step in range(3):
+      z.zero_grad()
+      if not from_hooks:
+        z._armed = False
+      gg = torch.Generator().manual_seed(100 + step)
+      loss = sum((p * (torch.randn(p.numel(), generator=gg) * 0.1).bfloat16().to(dev).view_as(p)).sum() for p in params)
+      loss.backward()
+      assert all(g_.launched for g_ in z.groups) == from_hooks
+      z.step()
+    torch.cuda.synchronize()
+    res[from_hooks] = torch.cat([p.detach().float().cpu().view(-1) for p in params])
+  assert torch.equal(res[False], res[True])
+
+  losses = []
   for overlap in (False, True):
     cfg = _cfg(tmp_path, dtype="bf16", zero2_overlap=overlap, zero2_bucket_mb=1)
     torch.manual_seed(5)
@@ -69,24 +94,9 @@ def test_dense_updates_issued_from_backward_hooks_match_the_step_after_backward(
     g = torch.Generator().manual_seed(9)
     tok = torch.randint(0, 2000, (4, 257), generator=g)
     x, y = tok[:, :-1].contiguous().to(dev), tok[:, 1:].contiguous().to(dev)
-    ls = []
-    for _ in range(4):
-      ls.append(float(tr.step(x, y).item()))
-      if overlap:
-        assert tr.opt.dense.side is not None
+    losses.append([float(tr.step(x, y).item()) for _ in range(6)])
     torch.cuda.synchronize()
     G.check_status()
-    named = dict(tr.model.named_parameters())
-    dense = {id(p) for g_ in tr.opt.dense.groups for p in g_.params}
-    finals.append({n: p.detach().float().cpu().clone() for n, p in named.items() if id(p) in dense})
-    losses.append(ls)
-  # the model's own reductions are not bitwise repeatable run to run (the first loss already differs in the 7th digit),
-  # so: same loss curve, and all but a sliver of the elements within one bf16 rounding.  An update that raced its
-  # gradients would be wrong for whole parameters.
   for a, b in zip(*losses):
-    assert abs(a - b) <= 1e-4 * abs(a), losses
-  assert finals[0].keys() == finals[1].keys() and len(finals[0]) > 5
-  for n in finals[0]:
-    a, b = finals[0][n], finals[1][n]
-    close = (a - b).abs() <= 2.0 ** -7 * a.abs().clamp_min(1e-3)
-    assert close.float().mean().item() >= 0.99, (n, close.float().mean().item())
+    assert abs(a - b) <= 2e-3 * abs(a), losses
+  assert losses[1][-1] < losses[1][0] - 0.3, losses
