@@ -2,7 +2,7 @@
 
 prep | prep-mixture | verify | info | regenerate-index | dedup | cluster | inspect | merge-manifests | flow
 hydra-grade | hydra-oracle-label | hydra-train | hydra-calibrate | rephrase   (grading model: --checkpoint)
-The download-only commands (arxiv-download, arxiv-prep) are registered too and say what they need."""
+arxiv-download fetches the bulk source tars (aws CLI, an HTTP mirror or a directory); arxiv-prep converts them."""
 from __future__ import annotations
 
 import argparse
@@ -395,15 +395,38 @@ def cmd_rephrase(a) -> int:
   return 0
 
 
-def cmd_needs_network(a) -> int:
-  print(f"'{a.command}' downloads from S3 / arXiv and needs network access and boto3; "
-        f"'arxiv-prep' and 'stack-v2-materialize' work on files that are already on disk", file=sys.stderr)
-  return 2
+def cmd_arxiv_download(a) -> int:
+  """Fetch arXiv bulk source tars listed in the manifest: a month range and / or a byte budget, through the AWS
+  command-line client (requester pays), an HTTP mirror, or a directory.  ``--dry-run`` prints the selection and what the
+  S3 transfer would cost."""
+  from . import arxiv_download as AD
+  fetcher = None if a.dry_run else AD.make_fetcher(a.fetch, base_url=a.base_url, root=a.root, profile=a.aws_profile)
+  manifest = Path(a.manifest) if a.manifest else Path(a.output) / "arXiv_src_manifest.xml"
+  if not manifest.exists():
+    if fetcher is None:
+      print(f"no manifest at {manifest}: fetch it first (run without --dry-run) or pass --manifest", file=sys.stderr)
+      return 2
+    manifest.parent.mkdir(parents=True, exist_ok=True)
+    fetcher.fetch("src/arXiv_src_manifest.xml", manifest)
+  picked = AD.select(AD.parse_manifest(manifest), a.start, a.end, _parse_count(a.max_bytes), a.max_files)
+  print(json.dumps(AD.estimate_cost(picked)))
+  if a.dry_run:
+    for e in picked:
+      print(f"{e.key}\t{e.size}\t{e.items}")
+    return 0
+  rep = AD.download(picked, a.output, fetcher, workers=a.workers, verify=not a.no_verify, keep_going=a.keep_going)
+  print(f"fetched {len(rep.fetched)}, already complete {len(rep.skipped)}, failed {len(rep.failed)} -> {a.output}")
+  return 0 if rep.ok else 1
 
 
 def cmd_arxiv_prep(a) -> int:
+  """Papers -> JSONL of plain text.  ``--input`` holds per-paper archives, or (with ``--bulk``) arXiv's monthly tars."""
   from .arxiv import iter_arxiv, write_jsonl
-  n = write_jsonl(iter_arxiv(a.input, a.min_chars), a.output)
+  if a.bulk:
+    from .arxiv_download import iter_bulk_text
+    n = write_jsonl(iter_bulk_text(a.input, a.min_chars), a.output)
+  else:
+    n = write_jsonl(iter_arxiv(a.input, a.min_chars), a.output)
   print(f"{n} papers -> {a.output}")
   return 0
 
@@ -466,9 +489,14 @@ def build_parser() -> argparse.ArgumentParser:
   p.add_argument("--oracle-keep", type=float, default=0.6); p.add_argument("--keep-precision", type=float, default=0.9)
   p = sub.add_parser("rephrase"); p.set_defaults(fn=cmd_rephrase); model_args(p)
   p.add_argument("--num-versions", type=int, default=1); p.add_argument("--chunk-size", type=int, default=2048); p.add_argument("--no-filter", action="store_true")
-  p = sub.add_parser("arxiv-download"); p.set_defaults(fn=cmd_needs_network); p.add_argument("rest", nargs="*")
+  p = sub.add_parser("arxiv-download"); p.set_defaults(fn=cmd_arxiv_download)
+  p.add_argument("--output", required=True); p.add_argument("--manifest"); p.add_argument("--fetch", default="s3", choices=["s3", "http", "file"])
+  p.add_argument("--base-url"); p.add_argument("--root"); p.add_argument("--aws-profile"); p.add_argument("--start"); p.add_argument("--end")
+  p.add_argument("--max-bytes"); p.add_argument("--max-files", type=int); p.add_argument("--workers", type=int, default=4)
+  p.add_argument("--no-verify", action="store_true"); p.add_argument("--keep-going", action="store_true"); p.add_argument("--dry-run", action="store_true")
   p = sub.add_parser("arxiv-prep"); p.set_defaults(fn=cmd_arxiv_prep)
   p.add_argument("--input", required=True); p.add_argument("--output", required=True); p.add_argument("--min-chars", type=int, default=500)
+  p.add_argument("--bulk", action="store_true", help="--input holds arXiv's monthly bulk tars")
   p = sub.add_parser("stack-v2-materialize"); p.set_defaults(fn=cmd_stack_v2)
   p.add_argument("--table", required=True); p.add_argument("--blobs", required=True); p.add_argument("--output", required=True)
   p.add_argument("--languages"); p.add_argument("--max-bytes", type=int, default=1 << 20)

@@ -253,3 +253,138 @@ def test_stage_graph_runner_builds_the_same_shards_as_the_serial_pipeline(tmp_pa
     assert ta.size == tb.size and sorted(ta.tolist()) == sorted(tb.tolist())
   with pytest.raises(RuntimeError, match="apache_beam"):
     run_beam_pipeline(mk(), PrepConfig(str(tmp_path / "c"), "toy", tokenizer="bytes", num_shards=2), runner="beam")
+
+
+def _bulk_tar(path, papers):
+  """An arXiv-style monthly tar: <yymm>/<id>.gz members (gzipped tar of the submission, or a gzipped TeX file)."""
+  import gzip, io, tarfile
+  with tarfile.open(path, "w") as tf:
+    for pid, files in papers.items():
+      if isinstance(files, dict):
+        inner = io.BytesIO()
+        with tarfile.open(fileobj=inner, mode="w") as it:
+          for name, text in files.items():
+            b = text.encode()
+            ti = tarfile.TarInfo(name); ti.size = len(b)
+            it.addfile(ti, io.BytesIO(b))
+        blob = gzip.compress(inner.getvalue())
+        name = f"2301/{pid}.gz"
+      elif files is None:
+        blob, name = b"%PDF-1.4", f"2301/{pid}.pdf"
+      else:
+        blob, name = gzip.compress(files.encode()), f"2301/{pid}.gz"
+      ti = tarfile.TarInfo(name); ti.size = len(blob)
+      tf.addfile(ti, io.BytesIO(blob))
+
+
+def test_arxiv_bulk_download_over_http_resumes_verifies_and_converts(tmp_path):
+  """Manifest -> selection -> fetch from a local HTTP server (127.0.0.1) with resume of a partial file, md5 check that
+  rejects a corrupted tar, skip of complete files; then papers come out of the bulk tar as text."""
+  import functools, http.server, threading
+  from nmoe_b200.data import arxiv_download as AD
+  body = "Deep networks generalise. " * 40
+  doc = "\\documentclass{article}\\begin{document}\\section{Intro}" + body + "\\input{sec}\\end{document}"
+  srv_root = tmp_path / "srv" / "src"
+  srv_root.mkdir(parents=True)
+  _bulk_tar(srv_root / "arXiv_src_2301_001.tar", {"2301.00001": {"main.tex": doc, "sec.tex": "Second part. " * 30},
+                                                  "2301.00002": doc.replace("\\input{sec}", ""), "2301.00003": None})
+  _bulk_tar(srv_root / "arXiv_src_2302_001.tar", {"2302.00001": doc.replace("\\input{sec}", "")})
+  _bulk_tar(srv_root / "arXiv_src_9912_001.tar", {"9912.00001": doc.replace("\\input{sec}", "")})
+  ents = []
+  for f, yymm in (("arXiv_src_2302_001.tar", "2302"), ("arXiv_src_9912_001.tar", "9912"), ("arXiv_src_2301_001.tar", "2301")):
+    p = srv_root / f
+    ents.append(f"<file><filename>src/{f}</filename><md5sum>{AD.md5_of(p)}</md5sum><num_items>3</num_items>"
+                f"<seq_num>1</seq_num><size>{p.stat().st_size}</size><yymm>{yymm}</yymm></file>")
+  manifest = tmp_path / "manifest.xml"
+  manifest.write_text("<arXivSRC>" + "".join(ents) + "</arXivSRC>")
+  entries = AD.parse_manifest(manifest)
+  assert [e.yymm for e in entries] == ["9912", "2301", "2302"]           # chronological: 1999 before 2023
+  assert [e.yymm for e in AD.select(entries, start="2301")] == ["2301", "2302"]
+  assert [e.yymm for e in AD.select(entries, end="2301", max_files=1)] == ["9912"]
+  assert AD.estimate_cost(entries)["files"] == 3
+
+  handler = functools.partial(http.server.SimpleHTTPRequestHandler, directory=str(tmp_path / "srv"))
+  class Quiet(http.server.ThreadingHTTPServer):
+    pass
+  handler.log_message = lambda *a, **k: None
+  httpd = Quiet(("127.0.0.1", 0), handler)
+  th = threading.Thread(target=httpd.serve_forever, daemon=True)
+  th.start()
+  try:
+    out = tmp_path / "dl"
+    fetcher = AD.HttpFetcher(f"http://127.0.0.1:{httpd.server_address[1]}", retries=1, backoff_s=0.01)
+    picked = AD.select(entries, start="2301")
+    rep = AD.download(picked, out, fetcher, workers=2, print_fn=lambda *_: None)
+    assert rep.ok and sorted(rep.fetched) == ["arXiv_src_2301_001.tar", "arXiv_src_2302_001.tar"]
+    rep2 = AD.download(picked, out, fetcher, print_fn=lambda *_: None)
+    assert rep2.fetched == [] and len(rep2.skipped) == 2                 # complete files are left alone
+    # a corrupted local copy is re-fetched; a manifest with a wrong checksum is reported and leaves no file behind
+    (out / "arXiv_src_2302_001.tar").write_bytes(b"garbage")
+    rep3 = AD.download(picked, out, fetcher, print_fn=lambda *_: None)
+    assert rep3.fetched == ["arXiv_src_2302_001.tar"]
+    bad = [AD.TarEntry(picked[0].key, picked[0].size, "0" * 32, picked[0].yymm, 1, 3)]
+    rep4 = AD.download(bad, tmp_path / "dl2", fetcher, print_fn=lambda *_: None)
+    assert not rep4.ok and not list((tmp_path / "dl2").glob("*.tar*"))
+    missing = [AD.TarEntry("src/nope.tar", 1, "", "2303", 1, 0)]
+    assert "HTTP 404" in AD.download(missing, tmp_path / "dl3", fetcher, print_fn=lambda *_: None).failed["nope.tar"]
+    # the command-line face, through a directory fetcher
+    assert cli.main(["arxiv-download", "--output", str(tmp_path / "dl4"), "--manifest", str(manifest), "--fetch", "file",
+                     "--root", str(tmp_path / "srv"), "--start", "2301", "--end", "2301"]) == 0
+    assert [p.name for p in (tmp_path / "dl4").glob("*.tar")] == ["arXiv_src_2301_001.tar"]
+  finally:
+    httpd.shutdown()
+  papers = list(AD.iter_bulk_tar(out / "arXiv_src_2301_001.tar"))
+  assert [p["id"] for p in papers] == ["2301.00001", "2301.00002"]      # the PDF-only member has no sources
+  assert set(papers[0]["files"]) == {"main.tex", "sec.tex"}
+  assert cli.main(["arxiv-prep", "--bulk", "--input", str(out), "--output", str(tmp_path / "papers.jsonl"), "--min-chars", "100"]) == 0
+  rows = [json.loads(l) for l in (tmp_path / "papers.jsonl").read_text().splitlines()]
+  assert [r["id"] for r in rows] == ["2301.00001", "2301.00002", "2302.00001"]
+  assert "Second part." in rows[0]["text"] and "documentclass" not in rows[0]["text"]
+  # the S3 route builds the requester-pays command and reports the client's error text
+  calls = []
+  class R:
+    returncode, stderr = 1, "fatal error: Unable to locate credentials"
+  s3 = AD.S3CliFetcher(profile="lab", run=lambda cmd, **kw: (calls.append(cmd), R())[1])
+  with pytest.raises(AD.FetchError, match="credentials"):
+    s3.fetch("src/arXiv_src_2301_001.tar", tmp_path / "x.tar")
+  assert calls[0][:4] == ["aws", "s3", "cp", "s3://arxiv/src/arXiv_src_2301_001.tar"] and "requester" in calls[0] and "lab" in calls[0]
+
+
+def test_http_fetcher_continues_a_transfer_that_was_cut(tmp_path):
+  """First response: full Content-Length but only half the body, then the connection drops.  The retry must ask for
+  the rest with a Range header and append it."""
+  import http.server, threading
+  from nmoe_b200.data.arxiv_download import HttpFetcher
+  payload = bytes(range(256)) * 400
+  seen = []
+
+  class H(http.server.BaseHTTPRequestHandler):
+    def log_message(self, *a):
+      pass
+    def do_GET(self):
+      rng = self.headers.get("Range")
+      seen.append(rng)
+      if rng is None:
+        self.send_response(200)
+        self.send_header("Content-Length", str(len(payload)))
+        self.end_headers()
+        self.wfile.write(payload[:len(payload) // 2])
+        self.wfile.flush()
+        self.connection.close()
+        return
+      start = int(rng.split("=")[1].rstrip("-"))
+      self.send_response(206)
+      self.send_header("Content-Length", str(len(payload) - start))
+      self.send_header("Content-Range", f"bytes {start}-{len(payload) - 1}/{len(payload)}")
+      self.end_headers()
+      self.wfile.write(payload[start:])
+
+  httpd = http.server.ThreadingHTTPServer(("127.0.0.1", 0), H)
+  threading.Thread(target=httpd.serve_forever, daemon=True).start()
+  try:
+    dest = tmp_path / "f.bin"
+    HttpFetcher(f"http://127.0.0.1:{httpd.server_address[1]}", retries=2, backoff_s=0.01).fetch("x/f.bin", dest)
+  finally:
+    httpd.shutdown()
+  assert dest.read_bytes() == payload
+  assert seen[0] is None and seen[1] == f"bytes={len(payload) // 2}-"
