@@ -25,6 +25,58 @@ inline int epi_push_bulk_enabled(bool mx = false) {
   return r;
 }
 
+// SwiGLU backward as the epilogue of the GEMM that produces dA = dY W2^T (one accumulator row per lane).
+// With h13 = [gate | up] interleaved (gate in even columns), s = sigmoid(gate), A = gate * s * up and the row's routing
+// weight sc:   d(gate) = sc dA up s (1 + gate (1 - s)),   d(up) = sc dA gate s,   a_out = sc A   (operand of dW2),
+// and <A, dA> summed over the row is the gradient of the routing weight.  dA itself is never written.  The accumulator
+// is rounded to bf16 first, so dh13 and a_out are bit-identical to the two-kernel form (GEMM storing bf16 dA, then
+// k_swiglu_bwd).  rowdot_parts[n_tile][row] holds the partial dot product of each column tile: plain stores, summed
+// afterwards in a fixed order, so the result does not depend on scheduling.
+// Replaces k_swiglu_bwd_bf16 / k_dgate_from_adA_bf16 of the reference (nmoe/csrc/quant.cu:781, nmoe/csrc/rdep.cu:3517).
+struct SwigluBwdEpi {
+  const __nv_bfloat16* h13;     // [rows, 2N]; nullptr = epilogue off
+  __nv_bfloat16* dh13;          // [rows, 2N]
+  __nv_bfloat16* a_out;         // [rows, N] or nullptr
+  const float* row_scale;       // [rows] or nullptr (1)
+  float* rowdot_parts;          // [ceil(N / tile columns), rows_cap] or nullptr
+  long long rows_cap;
+};
+
+NMOE_DEVICE void swiglu_bwd_load(int4 (&h)[8], const __nv_bfloat16* h13_row, int col) {
+  const int4* src = reinterpret_cast<const int4*>(h13_row + 2 * col);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) h[j] = ld_nc_v4(src + j);
+}
+
+// r: 32 accumulator columns [col, col + 32) of this lane's row; h: the 64 h13 values of the same columns.
+NMOE_DEVICE void swiglu_bwd_cols32(const uint32_t* r, const int4 (&h)[8], __nv_bfloat16* dh_row, __nv_bfloat16* a_row,
+                                   int col, float sc, float& dot) {
+  int4* dh = reinterpret_cast<int4*>(dh_row + 2 * col);
+  uint32_t aw[4];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const uint32_t* hw = reinterpret_cast<const uint32_t*>(&h[j]);
+    uint32_t ow[4];
+    float av[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 gu = unpack_bf16x2(hw[i]);                      // x = gate, y = up
+      const float d = __bfloat162float(__float2bfloat16(__uint_as_float(r[4 * j + i])));
+      const float s = 1.f / (1.f + __expf(-gu.x));
+      const float a = gu.x * s * gu.y;
+      dot += a * d;
+      const float gd = d * sc;
+      ow[i] = pack_bf16x2(gd * gu.y * s * (1.f + gu.x * (1.f - s)), gd * gu.x * s);
+      av[i] = a * sc;
+    }
+    dh[j] = make_int4(ow[0], ow[1], ow[2], ow[3]);
+    aw[2 * (j & 1)] = pack_bf16x2(av[0], av[1]);
+    aw[2 * (j & 1) + 1] = pack_bf16x2(av[2], av[3]);
+    if ((j & 1) && a_row != nullptr)
+      *reinterpret_cast<int4*>(a_row + col + 8 * (j >> 1)) = make_int4(aw[0], aw[1], aw[2], aw[3]);
+  }
+}
+
 // Return runs of the expert-parallel layer (csrc/rdep.cu): inside an expert's segment of the owner's buffer the rows of
 // one source rank are contiguous, and they go back as one contiguous block of that source's return buffer.
 // runs = [3][n_local][world]: first row of the run in the owner's buffer, its length, its first row at the source.

@@ -63,6 +63,7 @@ struct GemmParams {
   const float* idx_w;
   int idx_heads;
   int idx_causal;
+  SwigluBwdEpi sb;             // mode 1: SwiGLU backward in the epilogue (sb.h13 != nullptr); C is not written
 };
 
 NMOE_DEVICE uint64_t globaltimer_ns() {
@@ -327,6 +328,34 @@ k_gemm_bf16(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         }
         tc_fence_after_sync();
       }
+      if (MODE == 1 && p.sb.h13 != nullptr && have_acc) {
+        // SwiGLU backward in the epilogue: the accumulator is dA; dh13 and the scaled activation leave, dA does not
+        const float sc = (row_ok && p.sb.row_scale != nullptr) ? p.sb.row_scale[row] : 1.f;
+        const long long hrow = static_cast<long long>(row_ok ? row : 0);
+        const __nv_bfloat16* h_row = p.sb.h13 + hrow * 2 * p.N;
+        __nv_bfloat16* dh_row = p.sb.dh13 + hrow * 2 * p.N;
+        __nv_bfloat16* a_row = p.sb.a_out != nullptr ? p.sb.a_out + hrow * p.N : nullptr;
+        float dot = 0.f;
+        int4 h[8];
+        if (row_ok && n0 < p.N) swiglu_bwd_load(h, h_row, n0);
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          const int col = n0 + c * 32;
+          if (col >= p.N) break;               // uniform over the warp
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + c * 32, r);
+          int4 hn[8];
+          const bool more = row_ok && col + 32 < p.N && c + 1 < BN / 32;
+          if (more) swiglu_bwd_load(hn, h_row, col + 32);       // next chunk's h13 is in flight during this one's maths
+          tmem_ld_wait();
+          if (row_ok) swiglu_bwd_cols32(r, h, dh_row, a_row, col, sc, dot);
+          if (more) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) h[j] = hn[j];
+          }
+        }
+        if (row_ok && p.sb.rowdot_parts != nullptr) p.sb.rowdot_parts[static_cast<long long>(tc.n_blk) * p.sb.rows_cap + row] = dot;
+      } else
       if (MODE == 1 && p.push_runs != nullptr && have_acc && p.push_bulk && (p.N & 127) == 0 && (p.ldc & 7) == 0) {
         // fused return through the copy unit: 128 columns (256 bytes) of this lane's row per bulk copy
         uint8_t* srow = EpiBulk<256>::row(epi_stage + (warp - 2) * S::kEpiWarp, lane);
@@ -573,11 +602,11 @@ extern "C" {
 //   mode 2: A is [R,M] and B is [R,N] (both MN-major, rows = contraction), offs[E+1] gives each
 //           expert's row range; C holds E stacked [M,N] outputs.
 // bn selects the N tile (64, 128 or 256; 0 = choose).  status may be null.
-int nmoe_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
-                   long long ldc, int a_mn, int b_mn, int mode, int E, const int* tile_expert, const int* n_m_tiles,
-                   const int* offs, long long a_rows, long long b_rows, int out_fp32, int accumulate, int bn,
-                   void* status, const void* push_runs, void* const* peer_ret, void* const* peer_retg,
-                   const float* rowval, int push_pairs, int world, cudaStream_t st) {
+static int gemm_bf16_go(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                        long long ldc, int a_mn, int b_mn, int mode, int E, const int* tile_expert, const int* n_m_tiles,
+                        const int* offs, long long a_rows, long long b_rows, int out_fp32, int accumulate, int bn,
+                        void* status, const void* push_runs, void* const* peer_ret, void* const* peer_retg,
+                        const float* rowval, int push_pairs, int world, const SwigluBwdEpi* sb, cudaStream_t st) {
   if (M <= 0 || N <= 0) return 0;
   if (mode != 2 && K <= 0) return -1;
   if ((lda % 8) || (ldb % 8)) return -2;
@@ -597,6 +626,11 @@ int nmoe_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, l
   p.push_pairs = push_pairs; p.push_world = world;
   p.push_bulk = epi_push_bulk_enabled();
   p.idx_w = nullptr; p.idx_heads = 1; p.idx_causal = 0;
+  p.sb = SwigluBwdEpi{nullptr, nullptr, nullptr, nullptr, nullptr, 0};
+  if (sb != nullptr) {
+    if (mode != 1 || push_runs != nullptr || (N % 32) != 0) return -7;
+    p.sb = *sb;
+  }
   for (int r = 0; r < 8; ++r) {
     p.peer_ret[r] = (push_runs && peer_ret && r < world) ? static_cast<__nv_bfloat16*>(peer_ret[r]) : nullptr;
     p.peer_retg[r] = (push_runs && peer_retg && r < world) ? static_cast<float*>(peer_retg[r]) : nullptr;
@@ -627,6 +661,29 @@ int nmoe_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, l
 #undef GO
 }
 
+int nmoe_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                   long long ldc, int a_mn, int b_mn, int mode, int E, const int* tile_expert, const int* n_m_tiles,
+                   const int* offs, long long a_rows, long long b_rows, int out_fp32, int accumulate, int bn,
+                   void* status, const void* push_runs, void* const* peer_ret, void* const* peer_retg,
+                   const float* rowval, int push_pairs, int world, cudaStream_t st) {
+  return gemm_bf16_go(A, B, C, M, N, K, lda, ldb, ldc, a_mn, b_mn, mode, E, tile_expert, n_m_tiles, offs, a_rows, b_rows,
+                      out_fp32, accumulate, bn, status, push_runs, peer_ret, peer_retg, rowval, push_pairs, world, nullptr, st);
+}
+
+// Grouped dA = dY W2^T (mode 1) whose epilogue is the SwiGLU backward: reads h13 [M, 2N], writes dh13 [M, 2N], the
+// scaled activation a_out [M, N] (optional) and per-column-tile partial row dots rowdot_parts [ceil(N/256), rows_cap]
+// (optional).  dA is not written.  N % 32 == 0.  The column tile is 256.
+int nmoe_gemm_bf16_swiglu_bwd(const void* A, const void* B, int M, int N, int K, long long lda, long long ldb, int b_mn,
+                              int E, const int* tile_expert, const int* n_m_tiles, long long a_rows, long long b_rows,
+                              const void* h13, void* dh13, void* a_out, const float* row_scale, float* rowdot_parts,
+                              long long rows_cap, void* status, cudaStream_t st) {
+  SwigluBwdEpi sb{static_cast<const __nv_bfloat16*>(h13), static_cast<__nv_bfloat16*>(dh13), static_cast<__nv_bfloat16*>(a_out),
+                  row_scale, rowdot_parts, rows_cap};
+  if (h13 == nullptr || dh13 == nullptr) return -7;
+  return gemm_bf16_go(A, B, dh13, M, N, K, lda, ldb, N, 0, b_mn, 1, E, tile_expert, n_m_tiles, nullptr, a_rows, b_rows,
+                      0, 0, 256, status, nullptr, nullptr, nullptr, nullptr, 0, 0, &sb, st);
+}
+
 // Lightning-indexer scores of sparse attention, one batch element per call:
 //   out[t][s] = sum_h w[t*heads + h] * relu(q[t*heads + h, :] . k[s, :]),  -inf where s > t if causal.
 // k is [S, D] (row stride ldk), q is [T*heads, D] (row stride ldq), w is fp32 [T*heads], out is fp32 [T, ldo].
@@ -646,6 +703,7 @@ int nmoe_dsa_indexer_scores(const void* k, const void* q, const float* w, float*
   p.push_runs = nullptr; p.rowval = nullptr; p.push_pairs = 0; p.push_world = 0; p.push_bulk = 0;
   for (int r = 0; r < 8; ++r) { p.peer_ret[r] = nullptr; p.peer_retg[r] = nullptr; }
   p.idx_w = w; p.idx_heads = heads; p.idx_causal = causal;
+  p.sb = SwigluBwdEpi{nullptr, nullptr, nullptr, nullptr, nullptr, 0};
   CUtensorMap tmA, tmB;
   int rc = cached_map(&tmA, k, static_cast<uint64_t>(D), static_cast<uint64_t>(S), ldk * 2, BK, BM);
   if (rc != 0) return rc;

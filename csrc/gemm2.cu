@@ -50,6 +50,7 @@ struct Gemm2Params {
   const float* rowval;
   int push_world, push_pairs;  // ranks in the run tables; rows of a source's return buffer (bound)
   int push_bulk;               // 1: the fused return hands 256-byte row segments to the bulk-copy unit
+  SwigluBwdEpi sb;             // mode 1: SwiGLU backward in the epilogue (sb.h13 != nullptr); C is not written
 };
 
 NMOE_DEVICE uint32_t cluster_ctarank() {
@@ -319,6 +320,34 @@ k_gemm_bf16_pair(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
         tc_fence_after_sync();
       }
+      if (MODE == 1 && p.sb.h13 != nullptr && have_acc) {
+        // SwiGLU backward in the epilogue: the accumulator is dA; dh13 and the scaled activation leave, dA does not
+        const float sc = (row_ok && p.sb.row_scale != nullptr) ? p.sb.row_scale[row] : 1.f;
+        const long long hrow = static_cast<long long>(row_ok ? row : 0);
+        const __nv_bfloat16* h_row = p.sb.h13 + hrow * 2 * p.N;
+        __nv_bfloat16* dh_row = p.sb.dh13 + hrow * 2 * p.N;
+        __nv_bfloat16* a_row = p.sb.a_out != nullptr ? p.sb.a_out + hrow * p.N : nullptr;
+        float dot = 0.f;
+        int4 h[8];
+        if (row_ok && n0 < p.N) swiglu_bwd_load(h, h_row, n0);
+#pragma unroll 1
+        for (int c = 0; c < G2_BN / 32; ++c) {
+          const int col = n0 + c * 32;
+          if (col >= p.N) break;               // uniform over the warp
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * G2_BN + c * 32, r);
+          int4 hn[8];
+          const bool more = row_ok && col + 32 < p.N && c + 1 < G2_BN / 32;
+          if (more) swiglu_bwd_load(hn, h_row, col + 32);       // next chunk's h13 is in flight during this one's maths
+          tmem_ld_wait();
+          if (row_ok) swiglu_bwd_cols32(r, h, dh_row, a_row, col, sc, dot);
+          if (more) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) h[j] = hn[j];
+          }
+        }
+        if (row_ok && p.sb.rowdot_parts != nullptr) p.sb.rowdot_parts[static_cast<long long>(tc.n_blk) * p.sb.rows_cap + row] = dot;
+      } else
       if (MODE == 1 && p.push_runs != nullptr && have_acc && p.push_bulk && (p.N & 127) == 0 && (p.ldc & 7) == 0) {
         // fused return through the copy unit: 128 columns (256 bytes) of this lane's row per bulk copy
         uint8_t* srow = EpiBulk<256>::row(epi_stage + (warp - 2) * kG2EpiWarp, lane);
@@ -476,12 +505,12 @@ using namespace nmoe;
 
 // Same contract as nmoe_gemm_bf16 including the fused RDEP return (push_runs / peer_ret / peer_retg / rowval);
 // N tile is fixed at 256 and grouped row segments must be 256-aligned.
-extern "C" int nmoe_gemm_bf16_pair_push(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+static int g2_go(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
                                         long long ldb, long long ldc, int a_mn, int b_mn, int mode, int E,
                                         const int* tile_expert, const int* n_m_tiles, const int* offs, long long a_rows,
                                         long long b_rows, int out_fp32, int accumulate, void* status, const void* push_runs,
                                         void* const* peer_ret, void* const* peer_retg, const float* rowval,
-                                        int push_pairs, int world, cudaStream_t st) {
+                                        int push_pairs, int world, const SwigluBwdEpi* sb, cudaStream_t st) {
   if (M <= 0 || N <= 0) return 0;
   if (push_runs && (mode != 1 || out_fp32 || world > 8 || (N & 63) != 0 || (ldc & 7) != 0)) return -6;
   if (mode != 2 && K <= 0) return -1;
@@ -495,6 +524,11 @@ extern "C" int nmoe_gemm_bf16_pair_push(const void* A, const void* B, void* C, i
   p.status = static_cast<StatusRecord*>(status);
   p.push_runs = static_cast<const int*>(push_runs); p.rowval = rowval; p.push_pairs = push_pairs; p.push_world = world;
   p.push_bulk = epi_push_bulk_enabled();
+  p.sb = SwigluBwdEpi{nullptr, nullptr, nullptr, nullptr, nullptr, 0};
+  if (sb != nullptr) {
+    if (mode != 1 || push_runs != nullptr || (N % 32) != 0) return -7;
+    p.sb = *sb;
+  }
   for (int r = 0; r < 8; ++r) {
     p.peer_ret[r] = (push_runs && peer_ret && r < world) ? static_cast<__nv_bfloat16*>(peer_ret[r]) : nullptr;
     p.peer_retg[r] = (push_runs && peer_retg && r < world) ? static_cast<float*>(peer_retg[r]) : nullptr;
@@ -519,6 +553,29 @@ extern "C" int nmoe_gemm_bf16_pair_push(const void* A, const void* B, void* C, i
   if (mode == 1) return G2_GO(1);
   return g2_launch<true, true, 2>(tmA, tmB, p, max_tiles, st);
 #undef G2_GO
+}
+
+extern "C" int nmoe_gemm_bf16_pair_push(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+                                        long long ldb, long long ldc, int a_mn, int b_mn, int mode, int E,
+                                        const int* tile_expert, const int* n_m_tiles, const int* offs, long long a_rows,
+                                        long long b_rows, int out_fp32, int accumulate, void* status, const void* push_runs,
+                                        void* const* peer_ret, void* const* peer_retg, const float* rowval,
+                                        int push_pairs, int world, cudaStream_t st) {
+  return g2_go(A, B, C, M, N, K, lda, ldb, ldc, a_mn, b_mn, mode, E, tile_expert, n_m_tiles, offs, a_rows, b_rows, out_fp32, accumulate, status, push_runs, peer_ret, peer_retg, rowval, push_pairs, world, nullptr, st);
+}
+
+// Grouped dA = dY W2^T on CTA pairs whose epilogue is the SwiGLU backward (see SwigluBwdEpi): reads h13 [M, 2N], writes
+// dh13 [M, 2N], a_out [M, N] (optional) and rowdot_parts [ceil(N/256), rows_cap] (optional).  N % 32 == 0.
+extern "C" int nmoe_gemm_bf16_pair_swiglu_bwd(const void* A, const void* B, int M, int N, int K, long long lda, long long ldb,
+                                              int b_mn, int E, const int* tile_expert, const int* n_m_tiles, long long a_rows,
+                                              long long b_rows, const void* h13, void* dh13, void* a_out,
+                                              const float* row_scale, float* rowdot_parts, long long rows_cap, void* status,
+                                              cudaStream_t st) {
+  if (h13 == nullptr || dh13 == nullptr) return -7;
+  SwigluBwdEpi sb{static_cast<const __nv_bfloat16*>(h13), static_cast<__nv_bfloat16*>(dh13), static_cast<__nv_bfloat16*>(a_out),
+                  row_scale, rowdot_parts, rows_cap};
+  return g2_go(A, B, dh13, M, N, K, lda, ldb, N, 0, b_mn, 1, E, tile_expert, n_m_tiles, nullptr, a_rows, b_rows, 0, 0, status,
+               nullptr, nullptr, nullptr, nullptr, 0, 0, &sb, st);
 }
 
 // Without the fused-return arguments.

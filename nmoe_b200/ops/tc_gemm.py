@@ -217,6 +217,36 @@ def grouped_gemm(a: torch.Tensor, b: torch.Tensor, tile_expert: torch.Tensor, n_
   return out
 
 
+FUSED_SWIGLU_BWD = os.environ.get("NMOE_FUSED_SWIGLU_BWD", "1") == "1"
+
+
+def grouped_gemm_swiglu_bwd(dy: torch.Tensor, w2: torch.Tensor, tile_expert: torch.Tensor, n_m_tiles: torch.Tensor,
+                            h13: torch.Tensor, row_scale: Optional[torch.Tensor], *, want_a: bool = True,
+                            align256: bool = False):
+  """The expert MLP's dA GEMM with the SwiGLU backward as its epilogue.
+
+  ``dy`` [Mcap, H] (grouped rows), ``w2`` [E, H, F] so that dA = dy @ w2[e] is [Mcap, F]; ``h13`` [Mcap, 2F] (gate in
+  even columns).  Returns (dh13 [Mcap, 2F], rowdot [Mcap] fp32 = <swiglu(h13), dA>, a_scaled [Mcap, F] or None), the
+  same three tensors as ``grouped_gemm(..., b_mn=True)`` followed by ``ops.swiglu_bwd_fused``; dA itself is never
+  written.  Rows past the valid tiles are left untouched.  Returns None when this shape has no fused form
+  (the caller then runs the two-kernel form)."""
+  E, K, F = w2.size(0), w2.size(1), w2.size(2)
+  M = dy.size(0)
+  if not (dy.is_cuda and FUSED_SWIGLU_BWD and F % 32 == 0 and h13.size(1) == 2 * F and K % 64 == 0):
+    return None
+  assert dy.is_contiguous() and w2.is_contiguous() and h13.is_contiguous() and M % 128 == 0 and dy.size(1) == K
+  st = status_buffer(dy.device)
+  dh = torch.empty_like(h13)
+  ao = torch.empty(M, F, dtype=h13.dtype, device=h13.device) if want_a else None
+  parts = torch.empty((F + 255) // 256, M, dtype=torch.float32, device=dy.device)
+  pair = align256 and PAIR_MODE and F >= 256 and M % 256 == 0
+  fn = L.lib().nmoe_gemm_bf16_pair_swiglu_bwd if pair else L.lib().nmoe_gemm_bf16_swiglu_bwd
+  L.check(fn(L.ptr(dy), L.ptr(w2), M, F, K, L.c_ll(K), L.c_ll(F), 1, E, L.ptr(tile_expert), L.ptr(n_m_tiles),
+             L.c_ll(M), L.c_ll(E * K), L.ptr(h13), L.ptr(dh), L.ptr(ao), L.ptr(row_scale), L.ptr(parts), L.c_ll(M),
+             L.ptr(st), L.stream()), "grouped_gemm_swiglu_bwd")
+  return dh, parts.sum(0), ao
+
+
 def grouped_wgrad(a: torch.Tensor, b: torch.Tensor, offs: torch.Tensor, E: int, *,
                   out: Optional[torch.Tensor] = None, accumulate: bool = False, bn: int = 0) -> torch.Tensor:
   """out[e] = a[rows_e]^T @ b[rows_e]  ([E, Ma, Nb]) with rows_e = offs[e]:offs[e+1] (128-aligned).

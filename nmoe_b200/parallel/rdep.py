@@ -350,10 +350,15 @@ class _MoEFused(torch.autograd.Function):
     xb, yb = (rdep.xbuf[:rows] if xd is None else xd), rdep.ybuf[:rows]
     if h13 is None:
       h13 = G.grouped_gemm(xb, W13, plan.tile_expert, nt, align256=rdep.align == 256)
-    # dA' = dYe @ W2 (un-gated); gate enters through the row scale of the SwiGLU backward
-    da = G.grouped_gemm(yb, W2, plan.tile_expert, nt, b_mn=True, align256=rdep.align == 256)
+    # dA' = dYe @ W2 (un-gated); gate enters through the row scale of the SwiGLU backward, which runs as the
+    # epilogue of that GEMM (dA' is never written); shapes without the fused form take the two kernels
     row_gate = rdep.row_gates(plan)
-    dh13, rowdot, a_scaled = EW.swiglu_bwd_fused(h13, da, row_gate, True, True, nt)
+    fused = G.grouped_gemm_swiglu_bwd(yb, W2, plan.tile_expert, nt, h13, row_gate, align256=rdep.align == 256)
+    if fused is not None:
+      dh13, rowdot, a_scaled = fused
+    else:
+      da = G.grouped_gemm(yb, W2, plan.tile_expert, nt, b_mn=True, align256=rdep.align == 256)
+      dh13, rowdot, a_scaled = EW.swiglu_bwd_fused(h13, da, row_gate, True, True, nt)
     # every reader of the peer-written buffers runs before the kernel that returns rows to the sources
     dW2 = G.grouped_wgrad(yb, a_scaled, plan.offs_pad, rdep.n_local)             # [E, H, Dff]
     dW13 = G.grouped_wgrad(dh13, xb, plan.offs_pad, rdep.n_local)                # [E, 2Dff, H]

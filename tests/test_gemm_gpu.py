@@ -164,3 +164,52 @@ def test_linear_with_a_thin_output_has_a_right_backward(out_features):
   for got, ref, name in ((y, yr, "y"), (x.grad, xr.grad, "dx"), (w.grad, wr.grad, "dw")):
     err = (got.float() - ref).abs().max().item()
     assert err <= 2e-2 * ref.abs().max().item() + 1e-3, (name, err, ref.abs().max().item())
+
+
+@pytest.mark.parametrize("pair", [False, True])
+def test_grouped_da_gemm_with_swiglu_backward_epilogue(pair):
+  """dA = dY W2 with the SwiGLU backward as its epilogue, against (a) the two-kernel form it replaces (same roundings:
+  equal but for rare last-bit differences) and (b) an fp32 statement of the maths."""
+  from nmoe_b200 import ops
+  from nmoe_b200.ops import tc_gemm as G
+  torch.manual_seed(5)
+  dev = torch.device("cuda")
+  E, H, F = 4, 512, 1408                         # F = 5.5 column tiles of 256: a ragged last tile
+  counts = [4, 0, 2, 2] if pair else [3, 0, 2, 1]   # 128-row tiles per expert (256-aligned segments for CTA pairs)
+  te = [e for e, c in enumerate(counts) for _ in range(c)]
+  cap_tiles = 10
+  M = cap_tiles * 128
+  dy = (torch.randn(M, H, device=dev) * 0.5).bfloat16()
+  w2 = (torch.randn(E, H, F, device=dev) * 0.05).bfloat16()
+  h13 = torch.randn(M, 2 * F, device=dev).bfloat16()
+  gate = torch.rand(M, device=dev) + 0.1
+  tile_expert = torch.tensor(te + [-1] * (cap_tiles - len(te)), dtype=torch.int32, device=dev)
+  n_tiles = torch.tensor([len(te)], dtype=torch.int32, device=dev)
+  valid = len(te) * 128
+  got = G.grouped_gemm_swiglu_bwd(dy, w2, tile_expert, n_tiles, h13, gate, align256=pair)
+  assert got is not None
+  dh, rowdot, a = got
+  torch.cuda.synchronize()
+  G.check_status()
+  da = G.grouped_gemm(dy, w2, tile_expert, n_tiles, b_mn=True, align256=pair)
+  dh2, rowdot2, a2 = ops.swiglu_bwd_fused(h13, da, gate, True, True, n_tiles)
+  torch.cuda.synchronize()
+  for x, y, name in ((dh, dh2, "dh13"), (a, a2, "a")):
+    x, y = x[:valid].float(), y[:valid].float()
+    same = (x == y).float().mean().item()
+    assert same > 0.999, (name, same)
+    assert ((x - y).abs() <= 2.0 ** -7 * y.abs() + 1e-30).all(), name          # never more than one bf16 step
+  assert torch.allclose(rowdot[:valid], rowdot2[:valid], rtol=2e-3, atol=2e-2)
+  # fp32 statement
+  w_rows = torch.stack([w2[e] for e in te]).float()                              # [tiles, H, F]
+  dA = torch.bmm(dy[:valid].float().view(len(te), 128, H), w_rows).view(valid, F)
+  g, u = h13[:valid, 0::2].float(), h13[:valid, 1::2].float()
+  s = torch.sigmoid(g)
+  d = dA * gate[:valid].unsqueeze(-1)
+  ref = torch.empty(valid, 2 * F, device=dev)
+  ref[:, 0::2] = d * u * s * (1 + g * (1 - s))
+  ref[:, 1::2] = d * g * s
+  _close(dh[:valid], ref)
+  _close(a[:valid], g * s * u * gate[:valid].unsqueeze(-1))
+  rd = (g * s * u * dA).sum(-1)
+  assert (rowdot[:valid] - rd).abs().max().item() <= 2e-2 * rd.abs().max().item()
