@@ -70,22 +70,11 @@ class NSA(nn.Module):
     return torch.nn.functional.linear(h, self.cmp_w2, self.cmp_b2).view(B, Tc, KV, D)
 
   def cmp_attention(self, qh: torch.Tensor, k_cmp: torch.Tensor, v_cmp: torch.Tensor, T: int):
-    """Attention of the group-mean queries over compressed tokens + block scores [B,T,KV,Ns]."""
-    B, _, KV, D = qh.shape
-    Tc, Ns = k_cmp.size(1), T // self.slc_block
-    if Tc == 0 or Ns == 0:
-      return qh.new_zeros(B, T, KV, D), qh.new_zeros(B, T, KV, max(Ns, 1))
-    s = torch.einsum("bthd,bchd->bhtc", qh.float(), k_cmp.float()) * self.softmax_scale
-    t = torch.arange(T, device=qh.device).unsqueeze(1)
-    ends = torch.arange(Tc, device=qh.device).unsqueeze(0) * self.cmp_stride + self.cmp_len - 1
-    s = s.masked_fill((ends > t).view(1, 1, T, Tc), -1e6)
-    p = torch.exp(s - s.amax(-1, keepdim=True).clamp(min=0))
-    p = p / p.sum(-1, keepdim=True).clamp(min=1e-6)
-    out = torch.einsum("bhtc,bchd->bthd", p, v_cmp.float()).to(qh.dtype)
-    centers = torch.arange(Tc, device=qh.device) * self.cmp_stride + self.cmp_len // 2
-    scatter = torch.zeros(Tc, Ns, device=qh.device)
-    scatter[torch.arange(Tc, device=qh.device), (centers // self.slc_block).clamp(max=Ns - 1)] = 1.0
-    return out, torch.einsum("bhtc,cn->bthn", p, scatter)
+    """Attention of the group-mean queries over compressed tokens + block scores [B,T,KV,Ns] (one kernel forward, two
+    backward on a GPU: ops/nsa.py; the same statement in PyTorch otherwise)."""
+    from ...ops.nsa import cmp_attention
+    return cmp_attention(qh, k_cmp, v_cmp, cmp_len=self.cmp_len, cmp_stride=self.cmp_stride, slc_block=self.slc_block,
+                         scale=self.softmax_scale)
 
   @torch.no_grad()
   def select_blocks(self, block_scores: torch.Tensor, T: int) -> torch.Tensor:

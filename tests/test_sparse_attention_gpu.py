@@ -163,3 +163,47 @@ def test_dsa_at_4096_tokens_builds_no_per_head_quadratic_tensor():
   # (including the head-summed indexer scores [B, T, T], 128 MiB) stay below that
   assert peak < 1.5 * 2 ** 30, peak / 2 ** 30
   assert torch.isfinite(x.grad.float()).all()
+
+
+@pytest.mark.parametrize("D,T,mode", [(128, 1024, "random"), (64, 1000, "random"), (128, 4096, "random"), (128, 512, "negative")])
+def test_nsa_compressed_attention_kernels_vs_statement(D, T, mode):
+  """Forward (output + selection-block scores) and the three gradients of the compressed branch against the PyTorch
+  statement in fp32.  "negative" makes every score negative and large, so the floors of the maximum (0) and of the
+  denominator (1e-6) are what decides the result."""
+  from nmoe_b200.ops import nsa as N
+  from nmoe_b200.ops import tc_gemm as G
+  torch.manual_seed(0)
+  dev = torch.device("cuda")
+  B, KV, l, d, blk = 2, 2, 32, 16, 64
+  Tc = (T - l) // d + 1
+  q = torch.randn(B, T, KV, D, device=dev)
+  kc = torch.randn(B, Tc, KV, D, device=dev)
+  vc = torch.randn(B, Tc, KV, D, device=dev)
+  scale = D ** -0.5
+  if mode == "negative":
+    q, kc, scale = q.abs(), -kc.abs() - 0.2, 0.25
+  q, kc, vc = (x.bfloat16().requires_grad_(True) for x in (q, kc, vc))
+  assert N.kernel_ok(q, kc, blk)
+  out, scores = N.cmp_attention(q, kc, vc, cmp_len=l, cmp_stride=d, slc_block=blk, scale=scale)
+  go = torch.randn_like(out)
+  out.backward(go)
+  torch.cuda.synchronize()
+  G.check_status()
+  qf, kf, vf = (x.detach().float().requires_grad_(True) for x in (q, kc, vc))
+  ro, rs = N.cmp_attention_reference(qf, kf, vf, cmp_len=l, cmp_stride=d, slc_block=blk, scale=scale)
+  ro.backward(go.float())
+  assert not scores.requires_grad and scores.shape == rs.shape
+  def close(a, b, name, tol=2e-2):
+    err = (a.float() - b.float()).abs().max().item()
+    ref = b.float().abs().max().item()
+    assert err <= tol * ref + 1e-6, (name, err, ref)
+  close(out, ro, "out")
+  close(scores, rs, "scores", 5e-3)
+  assert (scores[:, :l - 1] == 0).all() and (out[:, :l - 1] == 0).all()       # nothing visible before the first block ends
+  close(q.grad, qf.grad, "dq")
+  close(kc.grad, kf.grad, "dkc")
+  close(vc.grad, vf.grad, "dvc")
+  if mode == "negative":
+    assert float(ro.abs().max()) > 0            # the case is not degenerate: some rows sit on the denominator's floor
+    den = torch.exp((torch.einsum("bthd,bchd->bhtc", qf, kf) * scale)[..., -1, :]).sum(-1)
+    assert (den < 1e-6).any()
