@@ -42,16 +42,35 @@ struct SwigluBwdEpi {
   long long rows_cap;
 };
 
-NMOE_DEVICE void swiglu_bwd_load(int4 (&h)[8], const __nv_bfloat16* h13_row, int col) {
-  const int4* src = reinterpret_cast<const int4*>(h13_row + 2 * col);
+// Each lane owns one accumulator row, but rows are 2N (h13, dh13) or N (a_out) elements apart in memory, so a lane that
+// touched its own row directly would make every load / store instruction hit 32 different lines, and four epilogue
+// warps cannot issue enough of those.  Rows therefore go through two 4 KB shared-memory tiles per warp (16-byte chunks
+// XOR-swizzled by row, conflict-free in both directions): every global instruction moves 4 rows x 128 contiguous bytes
+// (h13, dh13) or 8 rows x 64 bytes (a_out).  row0 = first row of the warp's 32-row slab, rows_ok = rows of it that exist.
+NMOE_DEVICE void sb_issue_loads(int4 (&g)[8], const __nv_bfloat16* h13, long long row0, int rows_ok, long long n2, int col,
+                                int lane) {
 #pragma unroll
-  for (int j = 0; j < 8; ++j) h[j] = ld_nc_v4(src + j);
+  for (int it = 0; it < 8; ++it) {
+    const int row = it * 4 + (lane >> 3);
+    g[it] = row < rows_ok ? ld_nc_v4(h13 + (row0 + row) * n2 + 2 * col + (lane & 7) * 8) : make_int4(0, 0, 0, 0);
+  }
+}
+NMOE_DEVICE void sb_stage_h(uint8_t* t0, const int4 (&g)[8], int lane) {
+#pragma unroll
+  for (int it = 0; it < 8; ++it) {
+    const int row = it * 4 + (lane >> 3);
+    *reinterpret_cast<int4*>(t0 + row * 128 + (((lane & 7) ^ (row & 7)) << 4)) = g[it];
+  }
 }
 
-// r: 32 accumulator columns [col, col + 32) of this lane's row; h: the 64 h13 values of the same columns.
-NMOE_DEVICE void swiglu_bwd_cols32(const uint32_t* r, const int4 (&h)[8], __nv_bfloat16* dh_row, __nv_bfloat16* a_row,
-                                   int col, float sc, float& dot) {
-  int4* dh = reinterpret_cast<int4*>(dh_row + 2 * col);
+// r: 32 accumulator columns [col, col + 32) of this lane's row (dA).  t0 holds the warp's h13 tile for these columns
+// (staged and visible); t1 is scratch.  All 32 lanes must call.
+NMOE_DEVICE void swiglu_bwd_cols32(const uint32_t* r, uint8_t* t0, uint8_t* t1, __nv_bfloat16* dh13, __nv_bfloat16* a_out,
+                                   long long row0, int rows_ok, long long n, int col, float sc, float& dot, int lane) {
+  int4 h[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) h[j] = *reinterpret_cast<const int4*>(t0 + lane * 128 + ((j ^ (lane & 7)) << 4));
+  __syncwarp();                                   // every lane has its h13 row: t0 may be overwritten
   uint32_t aw[4];
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
@@ -69,12 +88,28 @@ NMOE_DEVICE void swiglu_bwd_cols32(const uint32_t* r, const int4 (&h)[8], __nv_b
       ow[i] = pack_bf16x2(gd * gu.y * s * (1.f + gu.x * (1.f - s)), gd * gu.x * s);
       av[i] = a * sc;
     }
-    dh[j] = make_int4(ow[0], ow[1], ow[2], ow[3]);
+    *reinterpret_cast<int4*>(t1 + lane * 128 + ((j ^ (lane & 7)) << 4)) = make_int4(ow[0], ow[1], ow[2], ow[3]);
     aw[2 * (j & 1)] = pack_bf16x2(av[0], av[1]);
     aw[2 * (j & 1) + 1] = pack_bf16x2(av[2], av[3]);
-    if ((j & 1) && a_row != nullptr)
-      *reinterpret_cast<int4*>(a_row + col + 8 * (j >> 1)) = make_int4(aw[0], aw[1], aw[2], aw[3]);
+    if (j & 1)       // 8 activations = one 16-byte chunk of the 64-byte a_out row; rows 64 bytes apart, swizzled by row pair
+      *reinterpret_cast<int4*>(t0 + lane * 64 + (((j >> 1) ^ ((lane >> 1) & 3)) << 4)) = make_int4(aw[0], aw[1], aw[2], aw[3]);
   }
+  __syncwarp();
+#pragma unroll
+  for (int it = 0; it < 8; ++it) {
+    const int row = it * 4 + (lane >> 3);
+    const int4 v = *reinterpret_cast<const int4*>(t1 + row * 128 + (((lane & 7) ^ (row & 7)) << 4));
+    if (row < rows_ok) *reinterpret_cast<int4*>(dh13 + (row0 + row) * 2 * n + 2 * col + (lane & 7) * 8) = v;
+  }
+  if (a_out != nullptr) {
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+      const int row = it * 8 + (lane >> 2);
+      const int4 v = *reinterpret_cast<const int4*>(t0 + row * 64 + (((lane & 3) ^ ((row >> 1) & 3)) << 4));
+      if (row < rows_ok) *reinterpret_cast<int4*>(a_out + (row0 + row) * n + col + (lane & 3) * 8) = v;
+    }
+  }
+  __syncwarp();                                   // both tiles are free again
 }
 
 // Return runs of the expert-parallel layer (csrc/rdep.cu): inside an expert's segment of the owner's buffer the rows of

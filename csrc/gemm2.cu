@@ -323,27 +323,30 @@ k_gemm_bf16_pair(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       if (MODE == 1 && p.sb.h13 != nullptr && have_acc) {
         // SwiGLU backward in the epilogue: the accumulator is dA; dh13 and the scaled activation leave, dA does not
         const float sc = (row_ok && p.sb.row_scale != nullptr) ? p.sb.row_scale[row] : 1.f;
-        const long long hrow = static_cast<long long>(row_ok ? row : 0);
-        const __nv_bfloat16* h_row = p.sb.h13 + hrow * 2 * p.N;
-        __nv_bfloat16* dh_row = p.sb.dh13 + hrow * 2 * p.N;
-        __nv_bfloat16* a_row = p.sb.a_out != nullptr ? p.sb.a_out + hrow * p.N : nullptr;
+        const long long row0 = static_cast<long long>(row - lane);           // first row of this warp's 32-row slab
+        const int rows_ok = max(0, min(32, m_limit - static_cast<int>(row0)));
+        uint8_t* t0 = epi_stage + (warp - 2) * kG2EpiWarp;
+        uint8_t* t1 = t0 + 4096;
         float dot = 0.f;
-        int4 h[8];
-        if (row_ok && n0 < p.N) swiglu_bwd_load(h, h_row, n0);
+        int4 g[8];
+        if (n0 < p.N) {
+          sb_issue_loads(g, p.sb.h13, row0, rows_ok, 2LL * p.N, n0, lane);
+          sb_stage_h(t0, g, lane);
+          __syncwarp();
+        }
 #pragma unroll 1
         for (int c = 0; c < G2_BN / 32; ++c) {
           const int col = n0 + c * 32;
           if (col >= p.N) break;               // uniform over the warp
           uint32_t r[32];
           tmem_ld_32x32b_x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * G2_BN + c * 32, r);
-          int4 hn[8];
-          const bool more = row_ok && col + 32 < p.N && c + 1 < G2_BN / 32;
-          if (more) swiglu_bwd_load(hn, h_row, col + 32);       // next chunk's h13 is in flight during this one's maths
+          const bool more = col + 32 < p.N && c + 1 < G2_BN / 32;
+          if (more) sb_issue_loads(g, p.sb.h13, row0, rows_ok, 2LL * p.N, col + 32, lane);   // in flight during this chunk
           tmem_ld_wait();
-          if (row_ok) swiglu_bwd_cols32(r, h, dh_row, a_row, col, sc, dot);
+          swiglu_bwd_cols32(r, t0, t1, p.sb.dh13, p.sb.a_out, row0, rows_ok, p.N, col, sc, dot, lane);
           if (more) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) h[j] = hn[j];
+            sb_stage_h(t0, g, lane);
+            __syncwarp();
           }
         }
         if (row_ok && p.sb.rowdot_parts != nullptr) p.sb.rowdot_parts[static_cast<long long>(tc.n_blk) * p.sb.rows_cap + row] = dot;

@@ -22,8 +22,10 @@
 namespace nmoe {
 
 constexpr int KDA_C = 64;        // tokens per chunk
-constexpr int KDA_VL = 64;       // Dv columns per CTA
 constexpr int KDA_THREADS = 256;
+// Dv columns per CTA (VL) is a template parameter: 64, 32 or 16.  The recurrence is a dependency chain per (head,
+// column slice), so with few heads a narrower slice puts more CTAs on the machine and shortens every chain; the price
+// is that P and K2 of a chunk are read (from L2) once per slice.
 
 struct KdaScanArgs {
   int n_chunks, Dk, Dv, reverse;
@@ -39,7 +41,12 @@ struct KdaScanArgs {
 };
 
 // Shared memory: S [Dk][VL] | Wc [C][VL] | X [C][Dk]
+template <int KDA_VL>
 __global__ void __launch_bounds__(KDA_THREADS) k_kda_scan(const KdaScanArgs a) {
+  constexpr int NQ = KDA_VL / 4;               // column quads of the slice
+  constexpr int RG = KDA_THREADS / NQ;         // row groups: 16 / 32 / 64
+  constexpr int RPT = KDA_C / RG;              // rows of a [C][VL] tile per thread: 4 / 2 / 1
+  constexpr int GS = KDA_VL == 16 ? 2 : 4;     // state rows per thread and pass of the update
   extern __shared__ float kda_smem[];
   const int Dk = a.Dk, Dv = a.Dv;
   float* S = kda_smem;                       // [Dk][VL]
@@ -48,9 +55,9 @@ __global__ void __launch_bounds__(KDA_THREADS) k_kda_scan(const KdaScanArgs a) {
   const int bh = blockIdx.x;
   const int v_base = blockIdx.y * KDA_VL;
   const int t = threadIdx.x;
-  // [C][VL] outputs: thread -> 4 rows x 4 columns
-  const int vq = (t & 15) * 4;               // column quad inside the slice
-  const int rq = (t >> 4) * 4;               // first of 4 rows (16 groups x 4 = 64 rows)
+  // [C][VL] outputs: thread -> RPT rows x 4 columns
+  const int vq = (t % NQ) * 4;               // column quad inside the slice
+  const int rq = (t / NQ) * RPT;             // first of its rows
 
   // initial state
   for (int i = t; i < Dk * (KDA_VL / 4); i += KDA_THREADS) {
@@ -79,25 +86,31 @@ __global__ void __launch_bounds__(KDA_THREADS) k_kda_scan(const KdaScanArgs a) {
     __syncthreads();
     // W = U - P S
     {
-      float acc[4][4];
+      float acc[RPT][4];
       const float* Uc = a.U + chunk * KDA_C * Dv;
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
+      for (int j = 0; j < RPT; ++j) {
         const float4 u = *reinterpret_cast<const float4*>(Uc + static_cast<size_t>(rq + j) * Dv + v_base + vq);
         acc[j][0] = u.x; acc[j][1] = u.y; acc[j][2] = u.z; acc[j][3] = u.w;
       }
-      for (int k = 0; k < Dk; ++k) {
-        const float4 s = *reinterpret_cast<const float4*>(S + k * KDA_VL + vq);
+      for (int k = 0; k < Dk; k += 4) {
+        float4 s4[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float p = X[(rq + j) * Dk + k];
-          acc[j][0] = fmaf(-p, s.x, acc[j][0]); acc[j][1] = fmaf(-p, s.y, acc[j][1]);
-          acc[j][2] = fmaf(-p, s.z, acc[j][2]); acc[j][3] = fmaf(-p, s.w, acc[j][3]);
+        for (int kk = 0; kk < 4; ++kk) s4[kk] = *reinterpret_cast<const float4*>(S + (k + kk) * KDA_VL + vq);
+#pragma unroll
+        for (int j = 0; j < RPT; ++j) {
+          const float4 p4 = *reinterpret_cast<const float4*>(X + (rq + j) * Dk + k);
+          const float pv[4] = {p4.x, p4.y, p4.z, p4.w};
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            acc[j][0] = fmaf(-pv[kk], s4[kk].x, acc[j][0]); acc[j][1] = fmaf(-pv[kk], s4[kk].y, acc[j][1]);
+            acc[j][2] = fmaf(-pv[kk], s4[kk].z, acc[j][2]); acc[j][3] = fmaf(-pv[kk], s4[kk].w, acc[j][3]);
+          }
         }
       }
       float* Wg = a.W + chunk * KDA_C * Dv;
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
+      for (int j = 0; j < RPT; ++j) {
         const float4 w = make_float4(acc[j][0], acc[j][1], acc[j][2], acc[j][3]);
         *reinterpret_cast<float4*>(Wc + (rq + j) * KDA_VL + vq) = w;
         *reinterpret_cast<float4*>(Wg + static_cast<size_t>(rq + j) * Dv + v_base + vq) = w;
@@ -113,26 +126,26 @@ __global__ void __launch_bounds__(KDA_THREADS) k_kda_scan(const KdaScanArgs a) {
     {
       const float* dc = a.dec + chunk * Dk;
       const float* Gc = a.G != nullptr ? a.G + chunk * Dk * Dv : nullptr;
-      const int kq = t >> 4;                  // 0..15
-      for (int k0 = kq; k0 < Dk; k0 += 64) {  // rows k0, k0+16, k0+32, k0+48
-        float acc[4][4];
+      const int kq = t / NQ;                  // 0..RG-1
+      for (int k0 = kq; k0 < Dk; k0 += GS * RG) {  // rows k0, k0 + RG, ...
+        float acc[GS][4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i)
+        for (int i = 0; i < GS; ++i)
 #pragma unroll
           for (int x = 0; x < 4; ++x) acc[i][x] = 0.f;
         for (int j = 0; j < KDA_C; ++j) {
           const float4 w = *reinterpret_cast<const float4*>(Wc + j * KDA_VL + vq);
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int k = k0 + 16 * i;
+          for (int i = 0; i < GS; ++i) {
+            const int k = k0 + RG * i;
             const float kv = k < Dk ? X[j * Dk + k] : 0.f;
             acc[i][0] = fmaf(kv, w.x, acc[i][0]); acc[i][1] = fmaf(kv, w.y, acc[i][1]);
             acc[i][2] = fmaf(kv, w.z, acc[i][2]); acc[i][3] = fmaf(kv, w.w, acc[i][3]);
           }
         }
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int k = k0 + 16 * i;
+        for (int i = 0; i < GS; ++i) {
+          const int k = k0 + RG * i;
           if (k >= Dk) continue;
           const float d = dc[k];
           float4 s = *reinterpret_cast<const float4*>(S + k * KDA_VL + vq);
@@ -162,21 +175,30 @@ __global__ void __launch_bounds__(KDA_THREADS) k_kda_scan(const KdaScanArgs a) {
 using namespace nmoe;
 
 // All tensors fp32 and contiguous with the shapes given in KdaScanArgs; chunk length is 64 tokens.
-// Dk % 4 == 0 (<= 256), Dv % 64 == 0.  reverse != 0 walks the chunks from last to first (S_hist then holds, per
+// Dk % 4 == 0 (<= 256), Dv % 64 == 0 (the column slice per CTA is chosen from the grid size).  reverse != 0 walks the chunks from last to first (S_hist then holds, per
 // chunk, the state the reverse walk entered it with).
 extern "C" int nmoe_kda_scan(const float* U, const float* P, const float* K2, const float* dec, const float* G,
                              const float* S0, float* W, float* S_hist, float* S_final, int BH, int n_chunks, int Dk,
                              int Dv, int reverse, cudaStream_t st) {
   if (BH == 0 || n_chunks == 0) return 0;
-  if (Dk % 4 != 0 || Dk > 256 || Dv % KDA_VL != 0) return -1;
+  if (Dk % 4 != 0 || Dk > 256 || Dv % 64 != 0) return -1;
   KdaScanArgs a;
   a.n_chunks = n_chunks; a.Dk = Dk; a.Dv = Dv; a.reverse = reverse;
   a.U = U; a.P = P; a.K2 = K2; a.dec = dec; a.G = G; a.S0 = S0; a.W = W; a.S_hist = S_hist; a.S_final = S_final;
-  const int smem = (Dk * KDA_VL + KDA_C * KDA_VL + KDA_C * Dk) * static_cast<int>(sizeof(float));
-  cudaError_t e = cudaFuncSetAttribute(k_kda_scan, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-  if (e != cudaSuccess) return static_cast<int>(e);
-  dim3 grid(BH, Dv / KDA_VL);
-  k_kda_scan<<<grid, KDA_THREADS, smem, st>>>(a);
+  // the widest column slice that still gives every SM a CTA (narrowest otherwise)
+  int sms = 148, dev = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int vl = (static_cast<long long>(BH) * (Dv / 64) >= sms) ? 64 : (static_cast<long long>(BH) * (Dv / 32) >= sms) ? 32 : 16;
+  const int smem = (Dk * vl + KDA_C * vl + KDA_C * Dk) * static_cast<int>(sizeof(float));
+  dim3 grid(BH, Dv / vl);
+  cudaError_t e;
+#define KDA_GO(VL_)                                                                                             \
+  e = cudaFuncSetAttribute(k_kda_scan<VL_>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);                 \
+  if (e != cudaSuccess) return static_cast<int>(e);                                                             \
+  k_kda_scan<VL_><<<grid, KDA_THREADS, smem, st>>>(a)
+  if (vl == 64) { KDA_GO(64); } else if (vl == 32) { KDA_GO(32); } else { KDA_GO(16); }
+#undef KDA_GO
   e = cudaGetLastError();
   return e == cudaSuccess ? 0 : static_cast<int>(e);
 }

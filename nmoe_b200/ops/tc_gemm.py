@@ -217,7 +217,7 @@ def grouped_gemm(a: torch.Tensor, b: torch.Tensor, tile_expert: torch.Tensor, n_
   return out
 
 
-FUSED_SWIGLU_BWD = os.environ.get("NMOE_FUSED_SWIGLU_BWD", "1") == "1"
+FUSED_SWIGLU_BWD = os.environ.get("NMOE_FUSED_SWIGLU_BWD", "0") == "1"   # off until it measures faster than the two kernels
 
 
 def grouped_gemm_swiglu_bwd(dy: torch.Tensor, w2: torch.Tensor, tile_expert: torch.Tensor, n_m_tiles: torch.Tensor,

@@ -167,11 +167,12 @@ def test_linear_with_a_thin_output_has_a_right_backward(out_features):
 
 
 @pytest.mark.parametrize("pair", [False, True])
-def test_grouped_da_gemm_with_swiglu_backward_epilogue(pair):
+def test_grouped_da_gemm_with_swiglu_backward_epilogue(pair, monkeypatch):
   """dA = dY W2 with the SwiGLU backward as its epilogue, against (a) the two-kernel form it replaces (same roundings:
   equal but for rare last-bit differences) and (b) an fp32 statement of the maths."""
   from nmoe_b200 import ops
   from nmoe_b200.ops import tc_gemm as G
+  monkeypatch.setattr(G, "FUSED_SWIGLU_BWD", True)
   torch.manual_seed(5)
   dev = torch.device("cuda")
   E, H, F = 4, 512, 1408                         # F = 5.5 column tiles of 256: a ragged last tile

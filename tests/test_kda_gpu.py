@@ -11,7 +11,9 @@ def _rel(a, b):
 
 
 @pytest.mark.parametrize("BH,n,Dk,Dv,reverse,with_g", [(3, 5, 192, 128, False, False), (2, 7, 64, 64, True, True),
-                                                       (4, 3, 100, 192, False, True)])
+                                                       (4, 3, 100, 192, False, True),
+                                                       # enough (head, slice) pairs for 32- and 64-column slices per CTA
+                                                       (40, 3, 128, 128, True, True), (80, 2, 128, 128, False, False)])
 def test_scan_kernel_matches_loop(BH, n, Dk, Dv, reverse, with_g):
   from nmoe_b200.ops import kda as K
   torch.manual_seed(0)
