@@ -233,6 +233,9 @@ def main() -> None:
                   help="a model TOML (configs/moonlet_swa.toml, configs/dsv2_slice.toml, ...) instead of the headline "
                        "Moonlight-16B-A3B; its dtype applies unless --dtype is given, batch_size is split over the GPUs")
   ap.add_argument("--zero2-impl", default=None, choices=["fused", "nccl"], help="ZeRO-2 implementation (default: fused peer kernel)")
+  ap.add_argument("--capacity-factor", type=float, default=None,
+                  help="expert receive buffers as a multiple of the balanced share (rows beyond it are dropped and reported); "
+                       "default: lossless buffers, which at N>1 cost one small host read per MoE layer")
   ap.add_argument("--overlap-shared", default="auto", choices=["auto", "0", "1"], help="shared-expert MLP on a second stream")
   ap.add_argument("--recompute-h13", action="store_true", help="recompute the experts' up/gate output in backward (saves ~16 GB on one GPU)")
   ap.add_argument("--activation-checkpoint", default="none", choices=["none", "attention", "full"],
@@ -275,6 +278,8 @@ def main() -> None:
                         not args.recompute_h13, args.overlap_shared)
   if args.zero2_impl:
     cfg.zero2_impl = args.zero2_impl
+  if args.capacity_factor is not None:
+    cfg.rdep_capacity_factor = args.capacity_factor
   trainer = Trainer(cfg, rank=rank, world=world, device=device)
   mb, S = args.micro_batch, args.seq_len
   gen = torch.Generator().manual_seed(1234 + rank)
@@ -360,6 +365,7 @@ def main() -> None:
                  "vocab": cfg.vocab_size, "layers": cfg.n_layers,
                  "experts": f"{cfg.n_routed_experts} top-{cfg.n_activated_experts} + {cfg.n_shared_experts} shared",
                  "activation_checkpoint": args.activation_checkpoint, "moe_save_h13": not args.recompute_h13,
+                 "rdep_capacity_factor": cfg.rdep_capacity_factor, "zero2_overlap": bool(getattr(trainer.opt.dense, "overlap", False)),
                  "l2": "per-step working set (32 GB of weights) is far larger than the 126 MB L2"},
       "tflops_per_gpu": tflops_per_gpu,
       "mfu_vs_nominal_2250": tflops_per_gpu / 2250.0,

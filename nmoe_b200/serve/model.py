@@ -226,7 +226,11 @@ class MoEMLP(nn.Module):
       plan = rd.plan(ei.int().contiguous())
       rd.place_mx(xs, plan, g.view(-1))
       rd.wait_data()
-      h = Q.grouped_gemm_mxfp8(rd.xq, rd.sfa, w1q, w1sf, plan.tile_expert, plan.n_m_tiles)
+      # the dispatch scratch is sized for max_tokens, but this call's rows (each expert's segment padded to 128) cannot
+      # exceed T*K + E*127: everything below works on that prefix, so a decode step of a few sequences does not pay
+      # for elementwise passes over tens of thousands of unused rows
+      n_rows = min(rd.xq.size(0), (xs.size(0) * self.cfg.experts_per_token + self.cfg.num_experts * 127 + 127) // 128 * 128)
+      h = Q.grouped_gemm_mxfp8(rd.xq[:n_rows], rd.sfa, w1q, w1sf, plan.tile_expert, plan.n_m_tiles)
       # rows past the valid tiles hold stale data; they are never read back (the pushes skip them)
       row_e = plan.tile_expert[:h.size(0) // 128].clamp(0, self.cfg.num_experts - 1).long().repeat_interleave(128)
       a = clamped_swiglu(torch.nan_to_num(h[:, :N1] + self.b1[row_e]), self.cfg.swiglu_limit)
