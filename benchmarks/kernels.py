@@ -48,7 +48,7 @@ def timed(fn, iters, warmup, flush):
 
 def main():
   ap = argparse.ArgumentParser()
-  ap.add_argument("what", choices=["gemm", "mx", "attn", "moe", "indexer", "elementwise", "adamwq", "kda", "sparse"])
+  ap.add_argument("what", choices=["gemm", "mx", "attn", "moe", "indexer", "elementwise", "adamwq", "kda", "sparse", "nsa"])
   for k, d in (("m", 16384), ("n", 2048), ("k", 2048), ("bn", 0), ("b", 4), ("s", 4096), ("h", 16), ("dqk", 192), ("dv", 128),
                ("window", 0), ("tokens", 16384), ("hidden", 2048), ("inter", 1408), ("experts", 64), ("topk", 6),
                ("idx-heads", 4), ("idx-dim", 64), ("iters", 20), ("warmup", 3)):
@@ -147,6 +147,25 @@ def main():
     ms_sort = timed(lambda: scores.topk(topk, dim=-1), max(2, a.iters // 4), 1, flush)
     out.update(shape=[a.b, a.s, a.h, a.dqk, a.dv], top_k=topk, mask_topk_ms=ms_mask, torch_topk_ms=ms_sort,
                masked_attention_ms=ms_sparse, dense_attention_ms=ms_dense)
+  elif a.what == "nsa":
+    # compressed branch of native sparse attention (group-mean queries over MLP-compressed keys, block scores fused):
+    # the kernels against the PyTorch statement of the same maths, forward and forward + backward
+    from nmoe_b200.ops import nsa as N
+    B, T, KV, D, l, d, blk = a.b, a.s, a.h, a.dv, 32, 16, 64
+    Tc = (T - l) // d + 1
+    mk = lambda *sh: torch.randn(*sh, device=dev).bfloat16().requires_grad_(a.backward)
+    q, kc, vc = mk(B, T, KV, D), mk(B, Tc, KV, D), mk(B, Tc, KV, D)
+    def run(fn):
+      def f():
+        o, sc = fn(q, kc, vc, cmp_len=l, cmp_stride=d, slc_block=blk, scale=D ** -0.5)
+        if a.backward:
+          for x in (q, kc, vc):
+            x.grad = None
+          o.float().sum().backward()
+      return f
+    ms = timed(run(N.cmp_attention), a.iters, a.warmup, flush)
+    ms_ref = timed(run(N.cmp_attention_reference), max(2, a.iters // 4), 1, flush)
+    out.update(shape=[B, T, KV, D], compressed_keys=Tc, backward=a.backward, ms=ms, statement_ms=ms_ref, speedup=ms_ref / ms)
   elif a.what == "elementwise":
     # the memory-bound kernels of a step on the benchmark's shapes: algorithmic bytes / time against the measured copy rate
     from nmoe_b200.ops.optim import adamw_flat_
