@@ -54,12 +54,17 @@ def test_lost_rank_in_handle_exchange_raises_on_the_others(scenario):
 def test_rank_that_leaves_between_steps_is_seen_before_the_next_launch():
   outs, took = _run("leave_between_steps", 3)
   for o in outs[:2]:
-    assert "DETECTED lost" in o and "injected failure after step 3" in o, outs
+    assert "DETECTED lost" in o, outs
+  # rank 0 hosts the store and can always read why the peer left; rank 1 reads the same unless rank 0 (having raised
+  # first) is already gone, in which case it reports the lost store -- also a named PeerLost, not a hang
+  assert "injected failure after step 3" in outs[0], outs
+  assert "injected failure after step 3" in outs[1] or "store" in outs[1], outs
   assert took < 45, took
 
 
 def test_rank_that_stalls_between_steps_is_reported():
   outs, took = _run("stall_between_steps", 3)
-  for o in outs[:2]:
-    assert "DETECTED stalled" in o and "rank 2" in o, outs
+  assert "DETECTED stalled" in outs[0] and "rank 2" in outs[0], outs
+  # rank 1 sees the same stall, unless rank 0 has already raised and taken the store with it (a named PeerLost)
+  assert ("DETECTED stalled" in outs[1] and "rank 2" in outs[1]) or ("DETECTED lost" in outs[1] and "store" in outs[1]), outs
   assert took < 45, took
