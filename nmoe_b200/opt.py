@@ -10,6 +10,7 @@ is produced, so a full set of expert gradients never has to be resident (on one 
 from __future__ import annotations
 
 import math
+import os
 from typing import Dict, List, Optional
 
 import torch
@@ -59,6 +60,13 @@ class ExpertAdamW:
     self.fuse_in_backward = fuse_in_backward
     self.gradnorm_sq: Optional[torch.Tensor] = None
     self._hooks = []
+    # In-backward updates run on a side stream: the update of a layer's experts streams 14 bytes per parameter through
+    # HBM and uses no tensor core, the backward GEMMs of the layers below it are tensor-bound and do not depend on it,
+    # so the two overlap instead of taking turns (NMOE_EXPERT_OPT_SIDE_STREAM=0 keeps them on one stream).
+    self.side: Optional[torch.cuda.Stream] = None
+    if fuse_in_backward and params and params[0].is_cuda and os.environ.get("NMOE_EXPERT_OPT_SIDE_STREAM", "1") == "1":
+      self.side = torch.cuda.Stream(device=params[0].device)
+      self._events = [torch.cuda.Event() for _ in params]
     if fuse_in_backward:
       for i, p in enumerate(params):
         self._hooks.append(p.register_post_accumulate_grad_hook(self._make_hook(i)))
@@ -87,8 +95,19 @@ class ExpertAdamW:
     def hook(p: torch.Tensor) -> None:
       if p.grad is None:
         return
+      g = p.grad
       with torch.no_grad():
-        self._apply(i, p, p.grad)
+        if self.side is None:
+          self._apply(i, p, g)
+        else:
+          # everything that reads this layer's weights in backward (the dgrad GEMMs inside the MoE function) is already
+          # queued on the current stream; the update waits for that point and for the gradient itself
+          cur = torch.cuda.current_stream(p.device)
+          self._events[i].record(cur)
+          with torch.cuda.stream(self.side):
+            self.side.wait_event(self._events[i])
+            self._apply(i, p, g)
+          g.record_stream(self.side)               # the allocator must not hand the gradient's memory out early
       p.grad = None
     return hook
 
@@ -104,6 +123,8 @@ class ExpertAdamW:
         if p.grad is not None:
           self._apply(i, p, p.grad)
           p.grad = None
+    if self.side is not None:
+      torch.cuda.current_stream(self.params[0].device).wait_stream(self.side)   # the next forward reads the new weights
     self.step_count += 1
 
   def state_dict(self) -> dict:

@@ -100,3 +100,31 @@ def test_dense_updates_issued_from_backward_hooks_match_the_step_after_backward(
   for a, b in zip(*losses):
     assert abs(a - b) <= 2e-3 * abs(a), losses
   assert losses[1][-1] < losses[1][0] - 0.3, losses
+
+
+def test_expert_updates_on_a_side_stream_train_like_updates_on_the_compute_stream(tmp_path, monkeypatch):
+  """The in-backward expert AdamW runs on its own stream so that it overlaps the backward GEMMs of the layers below;
+  ordering is by events only.  Same loss curve as with everything on one stream (a raced update would not give it),
+  and the side stream is joined before the step returns."""
+  from nmoe_b200.ops import tc_gemm as G
+  from nmoe_b200.train import Trainer
+  dev = torch.device("cuda")
+  curves = []
+  for side in ("0", "1"):
+    monkeypatch.setenv("NMOE_EXPERT_OPT_SIDE_STREAM", side)
+    cfg = _cfg(tmp_path, dtype="fp8", n_layers=3)
+    torch.manual_seed(5)
+    tr = Trainer(cfg, rank=0, world=1, device=dev)
+    assert (tr.opt.expert.side is not None) == (side == "1")
+    g = torch.Generator().manual_seed(9)
+    tok = torch.randint(0, 2000, (4, 257), generator=g)
+    x, y = tok[:, :-1].contiguous().to(dev), tok[:, 1:].contiguous().to(dev)
+    ls = []
+    for _ in range(10):
+      ls.append(float(tr.step(x, y).item()))
+    torch.cuda.synchronize()
+    G.check_status()
+    curves.append(ls)
+  for a, b in zip(*curves):
+    assert abs(a - b) <= 5e-3 * abs(a), curves
+  assert curves[1][-1] < curves[1][0] - 0.5, curves
