@@ -128,8 +128,12 @@ class Zero2:
       impl = "fused" if on_gpu else "nccl"
     self.impl = impl
     env = os.environ.get("NMOE_ZERO2_OVERLAP", "")
-    self.overlap = ((env == "1") if env in ("0", "1") else bool(getattr(cfg, "zero2_overlap", False))) \
-        and on_gpu and impl in ("single", "fused")
+    want = getattr(cfg, "zero2_overlap", "auto")
+    if env in ("0", "1"):
+      want = env == "1"
+    elif isinstance(want, str):
+      want = (self.world > 1) if want.lower() == "auto" else want.lower() in ("1", "true", "yes", "on")
+    self.overlap = bool(want) and on_gpu and impl in ("single", "fused")
     self.bucket_elems = 0
     if self.overlap:
       mb = float(os.environ.get("NMOE_ZERO2_BUCKET_MB", getattr(cfg, "zero2_bucket_mb", 64)))
