@@ -236,6 +236,8 @@ def main() -> None:
   ap.add_argument("--capacity-factor", type=float, default=None,
                   help="expert receive buffers as a multiple of the balanced share (rows beyond it are dropped and reported); "
                        "default: lossless buffers, which at N>1 cost one small host read per MoE layer")
+  ap.add_argument("--moe-pipeline", action="store_true",
+                  help="run the two halves of every MoE layer's tokens on two streams (dispatch / return of one half under the other's GEMMs)")
   ap.add_argument("--overlap-shared", default="auto", choices=["auto", "0", "1"], help="shared-expert MLP on a second stream")
   ap.add_argument("--recompute-h13", action="store_true", help="recompute the experts' up/gate output in backward (saves ~16 GB on one GPU)")
   ap.add_argument("--activation-checkpoint", default="none", choices=["none", "attention", "full"],
@@ -280,6 +282,8 @@ def main() -> None:
     cfg.zero2_impl = args.zero2_impl
   if args.capacity_factor is not None:
     cfg.rdep_capacity_factor = args.capacity_factor
+  if args.moe_pipeline:
+    cfg.moe_pipeline = "true"
   trainer = Trainer(cfg, rank=rank, world=world, device=device)
   mb, S = args.micro_batch, args.seq_len
   gen = torch.Generator().manual_seed(1234 + rank)
@@ -365,7 +369,8 @@ def main() -> None:
                  "vocab": cfg.vocab_size, "layers": cfg.n_layers,
                  "experts": f"{cfg.n_routed_experts} top-{cfg.n_activated_experts} + {cfg.n_shared_experts} shared",
                  "activation_checkpoint": args.activation_checkpoint, "moe_save_h13": not args.recompute_h13,
-                 "rdep_capacity_factor": cfg.rdep_capacity_factor, "zero2_overlap": bool(getattr(trainer.opt.dense, "overlap", False)),
+                 "rdep_capacity_factor": cfg.rdep_capacity_factor,
+                 "moe_pipeline": bool(trainer.model.rdep is not None and trainer.model.rdep.halves is not None), "zero2_overlap": bool(getattr(trainer.opt.dense, "overlap", False)),
                  "l2": "per-step working set (32 GB of weights) is far larger than the 126 MB L2"},
       "tflops_per_gpu": tflops_per_gpu,
       "mfu_vs_nominal_2250": tflops_per_gpu / 2250.0,

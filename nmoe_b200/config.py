@@ -93,6 +93,8 @@ class Config:
   zero2_bucket_mb: int = 64           # with zero2_overlap: size of one bucket of the flat buffers (MB of bf16 parameters)
   zero2_overlap: str = "auto"         # auto | true | false: step every bucket on a side stream as soon as backward has
                                       # finished its gradients (auto = with more than one rank, where it measured +6 %)
+  moe_pipeline: str = "false"         # auto | true | false: run the two halves of every MoE layer's tokens on two streams
+                                      # so that one half's dispatch / return overlaps the other half's GEMMs
   rdep_capacity_factor: float = 0.0   # 0 = lossless receive buffers (worst case); > 0 = that multiple of the balanced share
 
   # ---- schedule (warmup by step, hold by tokens, cosine decay to an absolute floor)

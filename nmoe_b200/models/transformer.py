@@ -11,6 +11,8 @@ never materialises the [tokens, vocab] logits.
 """
 from __future__ import annotations
 
+import os
+
 from typing import List, Optional, Tuple
 
 import torch
@@ -89,6 +91,9 @@ class Transformer(nn.Module):
       tpr = tokens_per_rank or max(1, cfg.batch_size // world) * cfg.seq_len
       rdep = Rdep(cfg.dim, cfg.n_routed_experts, cfg.n_activated_experts, tpr, device=torch.device(device),
                   profile=cfg.dtype, capacity_factor=cfg.rdep_capacity_factor)
+    pipe = os.environ.get("NMOE_MOE_PIPELINE", str(getattr(cfg, "moe_pipeline", "false"))).lower()
+    if rdep is not None and (pipe in ("1", "true", "yes", "on")):
+      rdep.make_halves()
     self.rdep = rdep
     with torch.device(device or "cpu"):
       self.embedding = nn.Parameter(torch.empty(cfg.vocab_size, cfg.dim, dtype=dtype))

@@ -80,6 +80,10 @@ class Rdep:
     self.rank = dist.get_rank(group) if multi else 0
     assert n_experts % self.world == 0
     self.group = group
+    self._capacity_factor, self._profile, self._single_process = capacity_factor, profile, single_process
+    self.halves: Optional[list] = None          # see make_halves()
+    self.pipe_streams: list = []
+    self.pipe_min_tokens = int(os.environ.get("NMOE_MOE_PIPELINE_MIN_TOKENS", "1024"))
     self.dim, self.E, self.K = dim, n_experts, topk
     self.n_local = n_experts // self.world
     self.max_tokens = max_tokens
@@ -274,10 +278,118 @@ class Rdep:
     ``wq`` = (W13q, W13sf, W2q, W2sf) selects the block-scaled FP8 forward (tokens are quantised inside
     the placement kernel, both expert GEMMs run on the MXFP8 tensor-core path); the backward stays
     bf16 with a straight-through estimator, like the reference (nmoe/moe.py:404-415)."""
+    if self.halves is not None and x.is_cuda and x.size(0) >= 2 * self.pipe_min_tokens \
+        and (x.size(0) + 1) // 2 <= self.halves[0].max_tokens:
+      return _MoEPipelined.apply(self, x, gates, eid, W13, W2, save_h13, wq)
     return _MoEFused.apply(self, x, gates, eid, W13, W2, save_h13, wq)
 
+  def make_halves(self) -> None:
+    """Collective (every rank of the group must call it at the same point): two more instances, each sized for half of
+    ``max_tokens`` with its own peer buffers and flags, and two streams.  ``moe`` then runs the halves of a call
+    side by side (``_MoEPipelined``)."""
+    if self.halves is not None:
+      return
+    half = (self.max_tokens + 1) // 2
+    mk = lambda: Rdep(self.dim, self.E, self.K, half, capacity_factor=self._capacity_factor, group=self.group,
+                      device=self.device, profile=self._profile, single_process=self._single_process)
+    self.halves = [mk(), mk()]
+    for h in self.halves:
+      h.fused_return, h.push_impl, h.wait_budget = self.fused_return, self.push_impl, self.wait_budget
+    self.pipe_streams = [torch.cuda.Stream(device=self.device), torch.cuda.Stream(device=self.device)]
+
   def close(self) -> None:
+    for h in (self.halves or []):
+      h.close()
     self.slab.close()
+
+
+def _moe_forward(rdep: "Rdep", x, gates32, eid, W13, W2, save_h13, wq, out):
+  """Forward of the routed experts for the tokens of ``x`` on the current stream, result into ``out`` (same shape as
+  x).  Returns (plan, h13 kept for backward or None, dispatched rows kept for backward or None)."""
+  plan = rdep.plan(eid)
+  rows = rdep.rows_of(plan)
+  if wq is not None:
+    from ..ops import quant as Q
+    W13q, W13sf, W2q, W2sf = wq
+    with span("time_ms/comm/rdep_dispatch"):
+      rdep.place_mx(x, plan, gates32.view(-1))
+      rdep.wait_data()
+    ggemm = Q.grouped_gemm_mxfp4 if rdep.fp4 else Q.grouped_gemm_mxfp8
+    if not rdep.fused_swiglu_quant:
+      h13 = ggemm(rdep.xq[:rows], rdep.sfa, W13q, W13sf, plan.tile_expert, plan.n_m_tiles)
+      aq, asf = (Q.swiglu_quant_mxfp4 if rdep.fp4 else Q.swiglu_quant_mxfp8)(h13, plan.n_m_tiles)
+    elif save_h13:
+      # one epilogue pass writes both the quantised activation and the bf16 H13 that the backward keeps
+      aq, asf, h13 = Q.grouped_gemm_swiglu_quant(rdep.xq[:rows], rdep.sfa, W13q, W13sf, plan.tile_expert,
+                                                 plan.n_m_tiles, fp4=rdep.fp4, want_h13=True)
+    else:
+      # SwiGLU and the re-quantisation happen in the epilogue of the up/gate projection: H13 is never written
+      h13 = None
+      aq, asf = Q.grouped_gemm_swiglu_quant(rdep.xq[:rows], rdep.sfa, W13q, W13sf, plan.tile_expert, plan.n_m_tiles, fp4=rdep.fp4)
+    if rdep.fused_return:
+      ggemm(aq, asf, W2q, W2sf, plan.tile_expert, plan.n_m_tiles, push=rdep.push_args(plan))
+      rdep.finish_return(plan, out, gates32.view(-1))
+    else:
+      y = ggemm(aq, asf, W2q, W2sf, plan.tile_expert, plan.n_m_tiles)
+      rdep.push_and_reduce(y, plan, gates32.view(-1), None, out)
+    return plan, (h13 if save_h13 else None), None
+  with span("time_ms/comm/rdep_dispatch"):
+    rdep.place(x, plan, gates32.view(-1), "x", with_meta=True)
+    rdep.wait_data()
+  h13 = G.grouped_gemm(rdep.xbuf[:rows], W13, plan.tile_expert, plan.n_m_tiles, align256=rdep.align == 256)
+  a = EW.swiglu_rows(h13, plan.n_m_tiles)
+  if rdep.fused_return:
+    # down projection whose epilogue stores its rows straight into the sources' return buffers
+    G.grouped_gemm(a, W2, plan.tile_expert, plan.n_m_tiles, push=rdep.push_args(plan), align256=rdep.align == 256)
+    rdep.finish_return(plan, out, gates32.view(-1))
+  else:
+    y = G.grouped_gemm(a, W2, plan.tile_expert, plan.n_m_tiles, align256=rdep.align == 256)
+    rdep.push_and_reduce(y, plan, gates32.view(-1), None, out)
+  xd = rdep.xbuf[:rows].clone() if rdep.save_dispatched else None
+  return plan, (h13 if save_h13 else None), xd
+
+
+def _moe_backward(rdep: "Rdep", plan: Plan, x, gates32, W13, W2, h13, xd, dout, dx, dW13=None, dW2=None, *,
+                  accumulate: bool = False, before_wgrad=None, after_wgrad=None):
+  """Backward of ``_moe_forward`` on the current stream: dx into ``dx``.  The weight gradients go to fresh tensors, or
+  into ``dW13`` / ``dW2`` when given (overwritten, or added to with ``accumulate``: the second half of a pipelined
+  layer).  ``before_wgrad`` / ``after_wgrad``: events waited for / recorded around the two weight-gradient GEMMs.
+  Returns (dgates [T,K], dW13, dW2)."""
+  if xd is None:
+    rdep.place(x, plan, gates32.view(-1), "x", with_meta=True)
+    rdep.place(dout, plan, None, "y", with_meta=False)
+  else:
+    # the dispatched x rows were kept: only dOut travels, and it carries the row metadata (source, slot, gate)
+    rdep.place(dout, plan, gates32.view(-1), "y", with_meta=True)
+  rdep.wait_data()
+  nt = plan.n_m_tiles
+  rows = rdep.rows_of(plan)
+  xb, yb = (rdep.xbuf[:rows] if xd is None else xd), rdep.ybuf[:rows]
+  if h13 is None:
+    h13 = G.grouped_gemm(xb, W13, plan.tile_expert, nt, align256=rdep.align == 256)
+  # dA' = dYe @ W2 (un-gated); the gate enters through the row scale of the SwiGLU backward (optionally the epilogue of
+  # that GEMM, NMOE_FUSED_SWIGLU_BWD=1; by default the two kernels, which measured faster)
+  row_gate = rdep.row_gates(plan)
+  fused = G.grouped_gemm_swiglu_bwd(yb, W2, plan.tile_expert, nt, h13, row_gate, align256=rdep.align == 256)
+  if fused is not None:
+    dh13, rowdot, a_scaled = fused
+  else:
+    da = G.grouped_gemm(yb, W2, plan.tile_expert, nt, b_mn=True, align256=rdep.align == 256)
+    dh13, rowdot, a_scaled = EW.swiglu_bwd_fused(h13, da, row_gate, True, True, nt)
+  # every reader of the peer-written buffers runs before the kernel that returns rows to the sources
+  if before_wgrad is not None:
+    torch.cuda.current_stream(x.device).wait_event(before_wgrad)
+  dW2 = G.grouped_wgrad(yb, a_scaled, plan.offs_pad, rdep.n_local, out=dW2, accumulate=accumulate)       # [E, H, Dff]
+  dW13 = G.grouped_wgrad(dh13, xb, plan.offs_pad, rdep.n_local, out=dW13, accumulate=accumulate)         # [E, 2Dff, H]
+  if after_wgrad is not None:
+    after_wgrad.record(torch.cuda.current_stream(x.device))
+  if rdep.fused_return:
+    G.grouped_gemm(dh13, W13, plan.tile_expert, nt, b_mn=True, push=rdep.push_args(plan, rowdot), align256=rdep.align == 256)
+    rdep.finish_return(plan, dx)
+  else:
+    dxe = G.grouped_gemm(dh13, W13, plan.tile_expert, nt, b_mn=True, align256=rdep.align == 256)
+    rdep.push_and_reduce(dxe, plan, None, rowdot, dx)
+  return rdep.returned_scalars(plan), dW13, dW2
 
 
 class _MoEFused(torch.autograd.Function):
@@ -285,91 +397,86 @@ class _MoEFused(torch.autograd.Function):
   def forward(ctx, rdep: Rdep, x, gates, eid, W13, W2, save_h13, wq=None):
     x = x.contiguous()
     gates32 = gates.detach().float().contiguous()
-    plan = rdep.plan(eid)
-    rows = rdep.rows_of(plan)
     out = torch.empty_like(x)
-    if wq is not None:
-      from ..ops import quant as Q
-      W13q, W13sf, W2q, W2sf = wq
-      with span("time_ms/comm/rdep_dispatch"):
-        rdep.place_mx(x, plan, gates32.view(-1))
-        rdep.wait_data()
-      ggemm = Q.grouped_gemm_mxfp4 if rdep.fp4 else Q.grouped_gemm_mxfp8
-      if not rdep.fused_swiglu_quant:
-        h13 = ggemm(rdep.xq[:rows], rdep.sfa, W13q, W13sf, plan.tile_expert, plan.n_m_tiles)
-        aq, asf = (Q.swiglu_quant_mxfp4 if rdep.fp4 else Q.swiglu_quant_mxfp8)(h13, plan.n_m_tiles)
-      elif save_h13:
-        # one epilogue pass writes both the quantised activation and the bf16 H13 that the backward keeps
-        aq, asf, h13 = Q.grouped_gemm_swiglu_quant(rdep.xq[:rows], rdep.sfa, W13q, W13sf, plan.tile_expert,
-                                                   plan.n_m_tiles, fp4=rdep.fp4, want_h13=True)
-      else:
-        # SwiGLU and the re-quantisation happen in the epilogue of the up/gate projection: H13 is never written
-        h13 = None
-        aq, asf = Q.grouped_gemm_swiglu_quant(rdep.xq[:rows], rdep.sfa, W13q, W13sf, plan.tile_expert, plan.n_m_tiles, fp4=rdep.fp4)
-      if rdep.fused_return:
-        ggemm(aq, asf, W2q, W2sf, plan.tile_expert, plan.n_m_tiles, push=rdep.push_args(plan))
-        rdep.finish_return(plan, out, gates32.view(-1))
-      else:
-        y = ggemm(aq, asf, W2q, W2sf, plan.tile_expert, plan.n_m_tiles)
-        rdep.push_and_reduce(y, plan, gates32.view(-1), None, out)
-      ctx.rdep, ctx.plan = rdep, plan
-      ctx.save_for_backward(x, gates32, W13, W2, h13 if save_h13 else None, None)
-      return out
-    with span("time_ms/comm/rdep_dispatch"):
-      rdep.place(x, plan, gates32.view(-1), "x", with_meta=True)
-      rdep.wait_data()
-    h13 = G.grouped_gemm(rdep.xbuf[:rows], W13, plan.tile_expert, plan.n_m_tiles, align256=rdep.align == 256)
-    a = EW.swiglu_rows(h13, plan.n_m_tiles)
-    if rdep.fused_return:
-      # down projection whose epilogue multiplies by the gate and stores into the source's (token, slot) rows
-      G.grouped_gemm(a, W2, plan.tile_expert, plan.n_m_tiles, push=rdep.push_args(plan), align256=rdep.align == 256)
-      rdep.finish_return(plan, out, gates32.view(-1))
-    else:
-      y = G.grouped_gemm(a, W2, plan.tile_expert, plan.n_m_tiles, align256=rdep.align == 256)
-      rdep.push_and_reduce(y, plan, gates32.view(-1), None, out)
+    plan, h13, xd = _moe_forward(rdep, x, gates32, eid, W13, W2, save_h13, wq, out)
     ctx.rdep, ctx.plan = rdep, plan
-    xd = rdep.xbuf[:rows].clone() if rdep.save_dispatched else None
-    ctx.save_for_backward(x, gates32, W13, W2, h13 if save_h13 else None, xd)
+    ctx.save_for_backward(x, gates32, W13, W2, h13, xd)
+    return out
+
+  @staticmethod
+  def backward(ctx, dout):
+    x, gates32, W13, W2, h13, xd = ctx.saved_tensors
+    dx = torch.empty_like(x)
+    dg, dW13, dW2 = _moe_backward(ctx.rdep, ctx.plan, x, gates32, W13, W2, h13, xd, dout.contiguous(), dx)
+    return None, dx, dg, None, dW13, dW2, None, None
+
+
+class _MoEPipelined(torch.autograd.Function):
+  """The same layer with its tokens cut in two halves that run on two streams, each through its own ``Rdep`` (own
+  peer buffers, flags and epochs).  The kernels of one half that only move data between GPUs (placement, return, the
+  small waits) then run under the other half's GEMMs instead of in front of them: the dispatch of the second half
+  overlaps the up/gate projection of the first, the return of the first overlaps the projections of the second, and the
+  same in backward.  Nothing waits on another launch except through stream order and the cross-rank flags the halves
+  already use.  The second half ADDS its weight gradients to the first half's (ordered by an event), so no extra
+  gradient tensor exists.  This is the coarse (two-chunk) form of consuming dispatched rows while others still arrive."""
+
+  @staticmethod
+  def forward(ctx, rdep: Rdep, x, gates, eid, W13, W2, save_h13, wq=None):
+    x = x.contiguous()
+    gates32 = gates.detach().float().contiguous()
+    eid = eid.contiguous()
+    T = x.size(0)
+    cut = min(rdep.halves[0].max_tokens, (T + 1) // 2)
+    bounds = ((0, cut), (cut, T))
+    out = torch.empty_like(x)
+    main = torch.cuda.current_stream(x.device)
+    saved, plans = [], []
+    for h, (lo, hi) in enumerate(bounds):
+      s = rdep.pipe_streams[h]
+      s.wait_stream(main)
+      with torch.cuda.stream(s):
+        plan, h13, xd = _moe_forward(rdep.halves[h], x[lo:hi], gates32[lo:hi], eid[lo:hi], W13, W2, save_h13, wq, out[lo:hi])
+      plans.append(plan)
+      saved += [h13, xd]
+    for t in (x, gates32, eid, out):
+      for s in rdep.pipe_streams:
+        t.record_stream(s)
+    for s in rdep.pipe_streams:
+      main.wait_stream(s)
+    ctx.rdep, ctx.plans, ctx.bounds = rdep, plans, bounds
+    ctx.save_for_backward(x, gates32, W13, W2, *saved)
     return out
 
   @staticmethod
   def backward(ctx, dout):
     rdep: Rdep = ctx.rdep
-    plan: Plan = ctx.plan
-    x, gates32, W13, W2, h13, xd = ctx.saved_tensors
+    x, gates32, W13, W2, h13_0, xd_0, h13_1, xd_1 = ctx.saved_tensors
     dout = dout.contiguous()
-    if xd is None:
-      rdep.place(x, plan, gates32.view(-1), "x", with_meta=True)
-      rdep.place(dout, plan, None, "y", with_meta=False)
-    else:
-      # the dispatched x rows were kept: only dOut travels, and it carries the row metadata (source, slot, gate)
-      rdep.place(dout, plan, gates32.view(-1), "y", with_meta=True)
-    rdep.wait_data()
-    nt = plan.n_m_tiles
-    rows = rdep.rows_of(plan)
-    xb, yb = (rdep.xbuf[:rows] if xd is None else xd), rdep.ybuf[:rows]
-    if h13 is None:
-      h13 = G.grouped_gemm(xb, W13, plan.tile_expert, nt, align256=rdep.align == 256)
-    # dA' = dYe @ W2 (un-gated); gate enters through the row scale of the SwiGLU backward, which runs as the
-    # epilogue of that GEMM (dA' is never written); shapes without the fused form take the two kernels
-    row_gate = rdep.row_gates(plan)
-    fused = G.grouped_gemm_swiglu_bwd(yb, W2, plan.tile_expert, nt, h13, row_gate, align256=rdep.align == 256)
-    if fused is not None:
-      dh13, rowdot, a_scaled = fused
-    else:
-      da = G.grouped_gemm(yb, W2, plan.tile_expert, nt, b_mn=True, align256=rdep.align == 256)
-      dh13, rowdot, a_scaled = EW.swiglu_bwd_fused(h13, da, row_gate, True, True, nt)
-    # every reader of the peer-written buffers runs before the kernel that returns rows to the sources
-    dW2 = G.grouped_wgrad(yb, a_scaled, plan.offs_pad, rdep.n_local)             # [E, H, Dff]
-    dW13 = G.grouped_wgrad(dh13, xb, plan.offs_pad, rdep.n_local)                # [E, 2Dff, H]
+    main = torch.cuda.current_stream(x.device)
     dx = torch.empty_like(x)
-    if rdep.fused_return:
-      G.grouped_gemm(dh13, W13, plan.tile_expert, nt, b_mn=True, push=rdep.push_args(plan, rowdot), align256=rdep.align == 256)
-      rdep.finish_return(plan, dx)
-    else:
-      dxe = G.grouped_gemm(dh13, W13, plan.tile_expert, nt, b_mn=True, align256=rdep.align == 256)
-      rdep.push_and_reduce(dxe, plan, None, rowdot, dx)
-    dg = rdep.returned_scalars(plan)
+    dg = torch.empty(x.size(0), rdep.K, dtype=torch.float32, device=x.device)
+    dW13 = torch.empty_like(W13)
+    dW2 = torch.empty_like(W2)
+    first_done = torch.cuda.Event()
+    for h, (lo, hi) in enumerate(ctx.bounds):
+      s = rdep.pipe_streams[h]
+      s.wait_stream(main)
+      with torch.cuda.stream(s):
+        half = rdep.halves[h]
+        h13, xd = (h13_0, xd_0) if h == 0 else (h13_1, xd_1)
+        if h == 0:
+          # fresh weight gradients: the kernels write every element of dW13 / dW2 (experts without rows get zeros)
+          g, _, _ = _moe_backward(half, ctx.plans[h], x[lo:hi], gates32[lo:hi], W13, W2, h13, xd, dout[lo:hi], dx[lo:hi],
+                                       dW13, dW2, accumulate=False, before_wgrad=None, after_wgrad=first_done)
+        else:
+          g, _, _ = _moe_backward(half, ctx.plans[h], x[lo:hi], gates32[lo:hi], W13, W2, h13, xd, dout[lo:hi], dx[lo:hi],
+                                       dW13, dW2, accumulate=True, before_wgrad=first_done, after_wgrad=None)
+        dg[lo:hi].copy_(g)
+    for t in (dout, dx, dg, dW13, dW2, x, gates32):
+      for s in rdep.pipe_streams:
+        t.record_stream(s)
+    for s in rdep.pipe_streams:
+      main.wait_stream(s)
     return None, dx, dg, None, dW13, dW2, None, None
 
 

@@ -24,7 +24,7 @@ def close(a, ref, atol, rtol):
   return ((a - ref).abs() - (atol + rtol * ref.abs())).max().item()
 
 
-def check_moe(rank, world, dev, profile="bf16"):
+def check_moe(rank, world, dev, profile="bf16", pipeline=False):
   from nmoe_b200.ops.quant import ExpertWeightCache
   from nmoe_b200.parallel.rdep import Rdep, moe_reference
   T, H, F, E, K = 384, 256, 128, 8, 2
@@ -38,6 +38,10 @@ def check_moe(rank, world, dev, profile="bf16"):
   gates = torch.rand(T, K, generator=gr)
   gout = torch.randn(T, H, generator=gr).bfloat16()
   rd = Rdep(H, E, K, T, device=dev, profile=profile)
+  if pipeline:
+    # the two halves of the tokens on two streams, each through its own peer buffers
+    rd.make_halves()
+    rd.pipe_min_tokens = 1
   xd = x.to(dev).requires_grad_()
   gd = gates.to(dev).requires_grad_()
   W13 = W13g[rank * n_local:(rank + 1) * n_local].to(dev).requires_grad_()
@@ -75,6 +79,8 @@ def check_moe(rank, world, dev, profile="bf16"):
   assert all(v < gtol for k, v in errs.items() if k != "out_excess"), (profile, errs)
   dist.barrier()                                   # every peer's stores have landed
   assert rd.slab.check_guards() == [], rd.slab.check_guards()      # canaries (when NMOE_RDEP_GUARD is set)
+  for h in (rd.halves or []):
+    assert h.slab.check_guards() == [], h.slab.check_guards()
   dist.barrier()
   rd.close()
   return errs
@@ -219,6 +225,8 @@ def main():
   rank, world, dev = runtime.init(0)
   out = {"moe": check_moe(rank, world, dev), "moe_fp8": check_moe(rank, world, dev, "fp8"),
          "moe_nvfp4": check_moe(rank, world, dev, "nvfp4"), "zero2": check_zero2(rank, world, dev),
+         "moe_pipelined": check_moe(rank, world, dev, "bf16", pipeline=True),
+         "moe_fp8_pipelined": check_moe(rank, world, dev, "fp8", pipeline=True),
          "zero2_overlap": check_zero2_overlap(rank, world, dev),
          "train": check_train(rank, world, dev), "train_overlap": check_train(rank, world, dev, overlap=True),
          "capacity_drop": check_capacity_drop(rank, world, dev)}

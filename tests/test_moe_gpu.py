@@ -10,13 +10,19 @@ def _rel(a, b):
   return ((a.float() - b.float()).abs().max() / (b.float().abs().max() + 1e-6)).item()
 
 
-@pytest.mark.parametrize("T,H,F,E,K", [(32, 128, 256, 4, 1), (300, 256, 128, 8, 2), (1024, 512, 384, 16, 6)])
-def test_moe_forward_backward_vs_oracle(T, H, F, E, K):
+@pytest.mark.parametrize("pipeline", [False, True])
+@pytest.mark.parametrize("T,H,F,E,K", [(32, 128, 256, 4, 1), (300, 256, 128, 8, 2), (1024, 512, 384, 16, 6), (601, 256, 128, 8, 2)])
+def test_moe_forward_backward_vs_oracle(T, H, F, E, K, pipeline):
+  """``pipeline``: the two halves of the tokens run on two streams through their own buffers, the second half adding
+  its weight gradients to the first half's (an odd token count gives unequal halves)."""
   from nmoe_b200.parallel.rdep import Rdep, moe_reference
   from nmoe_b200.ops import tc_gemm as G
   torch.manual_seed(0)
   dev = torch.device("cuda")
   rd = Rdep(H, E, K, T, device=dev)
+  if pipeline:
+    rd.make_halves()
+    rd.pipe_min_tokens = 1
   try:
     x = (torch.randn(T, H, device=dev) * 0.5).bfloat16().requires_grad_()
     W13 = (torch.randn(E, 2 * F, H, device=dev) * 0.05).bfloat16().requires_grad_()
