@@ -25,6 +25,8 @@ namespace nmoe {
 constexpr int NSA_WARPS = 8;
 constexpr int NSA_QB = 32;        // queries per CTA (forward, dQ): 4 per warp
 constexpr int NSA_CK = 128;       // compressed keys per shared-memory chunk
+constexpr int NSA_KPW = 1;       // compressed keys per warp in the dKc / dVc kernel
+constexpr int NSA_KB = NSA_WARPS * NSA_KPW;
 constexpr int NSA_MAX_NS = 256;   // selection blocks per sequence (T <= 16384 at 64-token blocks)
 
 struct NsaCmpArgs {
@@ -299,8 +301,9 @@ __global__ void __launch_bounds__(NSA_WARPS * 32) k_nsa_cmp_dq(const NsaCmpArgs 
   }
 }
 
-// dKc / dVc: one CTA per 32 compressed keys (4 per warp), streaming the queries that can see them in chunks of CK.
-// Shared memory: Qs [CK][D+2] bf16 | dOs [CK][D+2] bf16 | ks [32][D] f32 (scaled) | vs [32][D] f32 |
+// dKc / dVc: one CTA per NSA_KB compressed keys (one per warp: Tc is small, so few keys per CTA is what fills the
+// machine), streaming the queries that can see them in chunks of CK.
+// Shared memory: Qs [CK][D+2] bf16 | dOs [CK][D+2] bf16 | ks [KB][D] f32 (scaled) | vs [KB][D] f32 |
 //                pw [WARPS][CK] f32 | dw [WARPS][CK] f32 | qstat [CK][3] f32 (m, 1/den, delta)
 template <int D>
 __global__ void __launch_bounds__(NSA_WARPS * 32) k_nsa_cmp_dkv(const NsaCmpArgs a, const float* __restrict__ delta) {
@@ -310,23 +313,23 @@ __global__ void __launch_bounds__(NSA_WARPS * 32) k_nsa_cmp_dkv(const NsaCmpArgs
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(nsa_smem);
   __nv_bfloat16* dOs = Qs + NSA_CK * P;
   float* ks = reinterpret_cast<float*>(dOs + NSA_CK * P);
-  float* vs = ks + 32 * D;
-  float* pw = vs + 32 * D;
+  float* vs = ks + NSA_KB * D;
+  float* pw = vs + NSA_KB * D;
   float* dw = pw + NSA_WARPS * NSA_CK;
   float* qstat = dw + NSA_WARPS * NSA_CK;
-  const int b = blockIdx.z, kv = blockIdx.y, cb = blockIdx.x * 32;
+  const int b = blockIdx.z, kv = blockIdx.y, cb = blockIdx.x * NSA_KB;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long pitch = static_cast<long long>(a.KV) * D;
   const long long tok0 = (static_cast<long long>(b) * a.T * a.KV + kv) * D;
   const long long key0 = (static_cast<long long>(b) * a.Tc * a.KV + kv) * D;
-  for (int i = threadIdx.x; i < 32 * D; i += blockDim.x) {
+  for (int i = threadIdx.x; i < NSA_KB * D; i += blockDim.x) {
     const int r = i / D, d = i % D, c = cb + r;
     ks[i] = c < a.Tc ? __bfloat162float(a.kc[key0 + c * pitch + d]) * a.scale : 0.f;
     vs[i] = c < a.Tc ? __bfloat162float(a.vc[key0 + c * pitch + d]) : 0.f;
   }
-  float gk[4][2 * NP], gv[4][2 * NP];
+  float gk[NSA_KPW][2 * NP], gv[NSA_KPW][2 * NP];
 #pragma unroll
-  for (int ki = 0; ki < 4; ++ki)
+  for (int ki = 0; ki < NSA_KPW; ++ki)
 #pragma unroll
     for (int x = 0; x < 2 * NP; ++x) { gk[ki][x] = 0.f; gv[ki][x] = 0.f; }
   const int t_first = cb * a.cmp_stride + a.cmp_len - 1;          // first query that sees the CTA's first key
@@ -346,8 +349,8 @@ __global__ void __launch_bounds__(NSA_WARPS * 32) k_nsa_cmp_dkv(const NsaCmpArgs
     }
     __syncthreads();
 #pragma unroll
-    for (int ki = 0; ki < 4; ++ki) {
-      const int r = warp * 4 + ki, c = cb + r;
+    for (int ki = 0; ki < NSA_KPW; ++ki) {
+      const int r = warp * NSA_KPW + ki, c = cb + r;
       if (c >= a.Tc) continue;
       const int t_min = c * a.cmp_stride + a.cmp_len - 1;
       if (t_min >= q0 + valid) continue;
@@ -392,8 +395,8 @@ __global__ void __launch_bounds__(NSA_WARPS * 32) k_nsa_cmp_dkv(const NsaCmpArgs
     }
   }
 #pragma unroll
-  for (int ki = 0; ki < 4; ++ki) {
-    const int c = cb + warp * 4 + ki;
+  for (int ki = 0; ki < NSA_KPW; ++ki) {
+    const int c = cb + warp * NSA_KPW + ki;
     if (c >= a.Tc) continue;
     float* rk = a.dkc + key0 + c * pitch;
     float* rv = a.dvc + key0 + c * pitch;
@@ -411,7 +414,7 @@ static int nsa_smem_fwd(int Ns) {
 }
 template <int D>
 static int nsa_smem_dkv() {
-  return 2 * NSA_CK * (D + 2) * 2 + (2 * 32 * D + 2 * NSA_WARPS * NSA_CK + 3 * NSA_CK) * 4;
+  return 2 * NSA_CK * (D + 2) * 2 + (2 * NSA_KB * D + 2 * NSA_WARPS * NSA_CK + 3 * NSA_CK) * 4;
 }
 
 template <int D>
@@ -432,7 +435,7 @@ static int nsa_bwd_launch(const NsaCmpArgs& a, float* delta, cudaStream_t st) {
   if (e != cudaSuccess) return static_cast<int>(e);
   e = cudaFuncSetAttribute(k_nsa_cmp_dkv<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_k);
   if (e != cudaSuccess) return static_cast<int>(e);
-  dim3 gq((a.T + NSA_QB - 1) / NSA_QB, a.KV, a.B), gk((a.Tc + 31) / 32, a.KV, a.B);
+  dim3 gq((a.T + NSA_QB - 1) / NSA_QB, a.KV, a.B), gk((a.Tc + NSA_KB - 1) / NSA_KB, a.KV, a.B);
   k_nsa_cmp_dq<D><<<gq, NSA_WARPS * 32, smem_q, st>>>(a, delta);
   k_nsa_cmp_dkv<D><<<gk, NSA_WARPS * 32, smem_k, st>>>(a, delta);
   e = cudaGetLastError();
