@@ -32,7 +32,9 @@ CUDA_SRCS = ("rdep", "quant", "ptx", "adamw", "gemm")
 
 
 def _default_reference() -> Path:
-    return Path(os.environ.get("NMOE_REFERENCE", "/root/reference"))
+    """$NMOE_REFERENCE, else a checkout named ``reference`` next to this repository."""
+    env = os.environ.get("NMOE_REFERENCE")
+    return Path(env) if env else HERE.parent.parent / "reference"
 
 
 def ext_path() -> Path:
