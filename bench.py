@@ -223,7 +223,7 @@ def main() -> None:
   ap.add_argument("--micro-batch", type=int, default=4)
   ap.add_argument("--seq-len", type=int, default=4096)
   ap.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (result is marked invalid)")
-  ap.add_argument("--dtype", default=None, choices=["bf16", "fp8", "nvfp4"],
+  ap.add_argument("--dtype", default=None, choices=["bf16", "fp8", "nvfp4", "nvfp4x16"],
                   help="expert GEMM profile: fp8 = bf16 activations + block-scaled MXFP8 expert GEMMs (the headline configuration)")
   ap.add_argument("--ref-dtype", default="bf16", choices=["bf16", "fp8", "nvfp4"],
                   help="expert profile of the reference arm; its block-scaled profiles need its CuTe-DSL grouped GEMM, "
@@ -362,7 +362,7 @@ def main() -> None:
       "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
       "dtype": args.dtype, "data": "synthetic uniform-random token ids, random-init weights",
       "config": {"model": model_name if args.layers is None else f"INVALID-debug-{args.layers}-layers",
-                 "expert_gemms": {"fp8": "block-scaled MXFP8 (E4M3, E8M0 per 32)", "nvfp4": "block-scaled E2M1, E8M0 per 32",
+                 "expert_gemms": {"fp8": "block-scaled MXFP8 (E4M3, E8M0 per 32)", "nvfp4": "block-scaled E2M1, E8M0 per 32", "nvfp4x16": "block-scaled NVFP4 (E2M1, UE4M3 per 16, fp32 tensor scale)",
                                   "bf16": "bf16"}.get(args.dtype, args.dtype) + " forward, bf16 backward; bf16 activations",
                  "global_batch": world * mb, "seq_len": S,
                  "parallelism": (f"rdep-ep{world}+zero2-dp{world}" if world > 1 else "single-gpu"),

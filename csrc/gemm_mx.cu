@@ -53,6 +53,7 @@ struct MxParams {
   int push_world, push_pairs;  // ranks in the run tables; rows of a source's return buffer (bound)
   int push_bulk;               // 1: the fused return hands 128-byte row segments to the bulk-copy unit
   float alpha;                 // multiplies every output (NVFP4: product of the two per-tensor scales)
+  const float* alpha_dev;      // optional second factor read from device memory (a scale that only the device knows)
   // fused SwiGLU + quantise epilogue (act_q != nullptr): instead of C [rows, N], write the quantised
   // activation [rows, N/2] (E4M3 bytes, or E2M1 nibbles when act_fp4) and its E8M0 scale atoms
   uint8_t* act_q;
@@ -289,7 +290,7 @@ k_gemm_mx(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
       const int n0 = n_blk * BN;
       bool row_ok = row < m_limit;
       __nv_bfloat16* dst_row = row_ok ? p.C + static_cast<long long>(row) * p.ldc : nullptr;
-      float gate = p.alpha;
+      float gate = p.alpha * (p.alpha_dev != nullptr ? __ldg(p.alpha_dev) : 1.f);
       if (MODE == 1 && p.push_runs != nullptr && row_ok) {
         int src = 0, drow = 0;
         row_ok = run_lookup(p.push_runs, p.E, p.push_world, expert, row, src, drow) && drow >= 0 && drow < p.push_pairs &&
@@ -487,7 +488,7 @@ extern "C" int nmoe_gemm_mxfp8(const void* A, const void* sfa, const void* B, co
   p.sfa = static_cast<const uint8_t*>(sfa); p.sfb = static_cast<const uint8_t*>(sfb);
   p.status = static_cast<StatusRecord*>(status);
   p.push_runs = static_cast<const int*>(push_runs); p.push_pairs = push_pairs; p.push_world = world;
-  p.push_bulk = epi_push_bulk_enabled(true); p.alpha = 1.f; p.act_q = nullptr; p.act_sf = nullptr; p.act_sf_cols = 0; p.act_fp4 = 0;
+  p.push_bulk = epi_push_bulk_enabled(true); p.alpha = 1.f; p.alpha_dev = nullptr; p.act_q = nullptr; p.act_sf = nullptr; p.act_sf_cols = 0; p.act_fp4 = 0;
   for (int r = 0; r < 8; ++r)
     p.peer_ret[r] = (push_runs && peer_ret && r < world) ? static_cast<__nv_bfloat16*>(peer_ret[r]) : nullptr;
   if (push_runs && (mode != 1 || world > 8)) return -6;
@@ -518,7 +519,7 @@ extern "C" int nmoe_gemm_mxfp4(const void* A, const void* sfa, const void* B, co
   p.sfa = static_cast<const uint8_t*>(sfa); p.sfb = static_cast<const uint8_t*>(sfb);
   p.status = static_cast<StatusRecord*>(status);
   p.push_runs = static_cast<const int*>(push_runs); p.push_pairs = push_pairs; p.push_world = world;
-  p.push_bulk = epi_push_bulk_enabled(true); p.alpha = 1.f; p.act_q = nullptr; p.act_sf = nullptr; p.act_sf_cols = 0; p.act_fp4 = 0;
+  p.push_bulk = epi_push_bulk_enabled(true); p.alpha = 1.f; p.alpha_dev = nullptr; p.act_q = nullptr; p.act_sf = nullptr; p.act_sf_cols = 0; p.act_fp4 = 0;
   for (int r = 0; r < 8; ++r)
     p.peer_ret[r] = (push_runs && peer_ret && r < world) ? static_cast<__nv_bfloat16*>(peer_ret[r]) : nullptr;
   if (push_runs && (mode != 1 || world > 8)) return -6;
@@ -535,9 +536,10 @@ extern "C" int nmoe_gemm_mxfp4(const void* A, const void* sfa, const void* B, co
 
 // NVFP4 operands: packed E2M1 as for MXFP4; scales are UE4M3 bytes, one per 16 elements, in the same
 // 128-row x 4-byte atom layout (atoms [rows/128][K/64]); alpha = tensor_scale_a * tensor_scale_b.
-extern "C" int nmoe_gemm_nvfp4(const void* A, const void* sfa, const void* B, const void* sfb, void* C, int M, int N,
-                               int K, long long ldc, int mode, int E, const int* tile_expert, const int* n_m_tiles,
-                               long long a_rows, long long b_rows, int bn, float alpha, void* status, cudaStream_t st) {
+static int gemm_nvfp4_go(const void* A, const void* sfa, const void* B, const void* sfb, void* C, int M, int N,
+                         int K, long long ldc, int mode, int E, const int* tile_expert, const int* n_m_tiles,
+                         long long a_rows, long long b_rows, int bn, float alpha, const float* alpha_dev, void* status,
+                         cudaStream_t st) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || (K % 64) != 0) return -1;
   if (mode == 1 && (N % 128) != 0) return -2;
@@ -548,7 +550,7 @@ extern "C" int nmoe_gemm_nvfp4(const void* A, const void* sfa, const void* B, co
   p.C = static_cast<__nv_bfloat16*>(C); p.ldc = ldc;
   p.sfa = static_cast<const uint8_t*>(sfa); p.sfb = static_cast<const uint8_t*>(sfb);
   p.status = static_cast<StatusRecord*>(status);
-  p.push_runs = nullptr; p.push_pairs = 0; p.push_world = 0; p.push_bulk = 0; p.alpha = alpha; p.act_q = nullptr; p.act_sf = nullptr; p.act_sf_cols = 0; p.act_fp4 = 0;
+  p.push_runs = nullptr; p.push_pairs = 0; p.push_world = 0; p.push_bulk = 0; p.alpha = alpha; p.alpha_dev = alpha_dev; p.act_q = nullptr; p.act_sf = nullptr; p.act_sf_cols = 0; p.act_fp4 = 0;
   for (int r = 0; r < 8; ++r) p.peer_ret[r] = nullptr;
   CUtensorMap tmA, tmB;
   int rc = mx_cached_map(&tmA, A, K / 2, a_rows, K / 2, MX_BK, MX_BM);
@@ -559,6 +561,23 @@ extern "C" int nmoe_gemm_nvfp4(const void* A, const void* sfa, const void* B, co
   if (bn == 256)
     return mode == 1 ? mx_launch<256, 1, 2>(tmA, tmB, p, max_tiles, st) : mx_launch<256, 0, 2>(tmA, tmB, p, max_tiles, st);
   return mode == 1 ? mx_launch<128, 1, 2>(tmA, tmB, p, max_tiles, st) : mx_launch<128, 0, 2>(tmA, tmB, p, max_tiles, st);
+}
+
+extern "C" int nmoe_gemm_nvfp4(const void* A, const void* sfa, const void* B, const void* sfb, void* C, int M, int N,
+                               int K, long long ldc, int mode, int E, const int* tile_expert, const int* n_m_tiles,
+                               long long a_rows, long long b_rows, int bn, float alpha, void* status, cudaStream_t st) {
+  return gemm_nvfp4_go(A, sfa, B, sfb, C, M, N, K, ldc, mode, E, tile_expert, n_m_tiles, a_rows, b_rows, bn, alpha, nullptr,
+                       status, st);
+}
+
+// The same with the product of the two tensor scales left on the device: out = alpha * (*alpha_dev) * (A B^T).
+// Used by the grouped expert GEMMs, whose weight scale comes out of a device-side amax.
+extern "C" int nmoe_gemm_nvfp4_dev(const void* A, const void* sfa, const void* B, const void* sfb, void* C, int M, int N,
+                                   int K, long long ldc, int mode, int E, const int* tile_expert, const int* n_m_tiles,
+                                   long long a_rows, long long b_rows, int bn, float alpha, const float* alpha_dev,
+                                   void* status, cudaStream_t st) {
+  return gemm_nvfp4_go(A, sfa, B, sfb, C, M, N, K, ldc, mode, E, tile_expert, n_m_tiles, a_rows, b_rows, bn, alpha, alpha_dev,
+                       status, st);
 }
 
 // Grouped up/gate projection with the SwiGLU and the re-quantisation fused into the epilogue: rows of A are
@@ -593,7 +612,7 @@ extern "C" int nmoe_gemm_mx_swiglu_quant_h13(const void* A, const void* sfa, con
   p.C = static_cast<__nv_bfloat16*>(h13); p.ldc = N;
   p.sfa = static_cast<const uint8_t*>(sfa); p.sfb = static_cast<const uint8_t*>(sfb);
   p.status = static_cast<StatusRecord*>(status);
-  p.push_runs = nullptr; p.push_pairs = 0; p.push_world = 0; p.push_bulk = 0; p.alpha = 1.f;
+  p.push_runs = nullptr; p.push_pairs = 0; p.push_world = 0; p.push_bulk = 0; p.alpha = 1.f; p.alpha_dev = nullptr;
   for (int r = 0; r < 8; ++r) p.peer_ret[r] = nullptr;
   p.act_q = static_cast<uint8_t*>(act_q); p.act_sf = static_cast<uint8_t*>(act_sf);
   p.act_sf_cols = (((N / 2) / 32) + 3) & ~3; p.act_fp4 = fp4;

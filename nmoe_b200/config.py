@@ -20,7 +20,7 @@ from dataclasses import dataclass, field
 from pathlib import Path
 from typing import Any, Dict, Optional
 
-EXPERT_DTYPES = ("bf16", "fp8", "nvfp4")
+EXPERT_DTYPES = ("bf16", "fp8", "nvfp4", "nvfp4x16")   # nvfp4 = E2M1 + E8M0/32 (the reference's profile), nvfp4x16 = E2M1 + UE4M3/16 + tensor scale
 ATTENTION_KINDS = ("mla", "swa", "nsa", "dsa", "kda")
 ROUTER_KINDS = ("sigmoid", "softmax")
 
@@ -75,7 +75,7 @@ class Config:
   route_n_groups: int = 0             # number of expert groups for device-limited routing (0 = world size)
 
   # ---- precision of the expert GEMMs
-  dtype: Optional[str] = "bf16"       # bf16 | fp8 (E4M3 + 1x32 E8M0) | nvfp4 (E2M1)
+  dtype: Optional[str] = "bf16"       # bf16 | fp8 (E4M3 + 1x32 E8M0) | nvfp4 (E2M1 + 1x32 E8M0) | nvfp4x16 (E2M1 + 1x16 UE4M3 + tensor scale)
   nvfp4_block: int = 32               # 32: E8M0 scales (reference-compatible); 16: E4M3 scales (true NVFP4)
 
   # ---- optimizer

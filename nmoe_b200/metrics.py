@@ -21,7 +21,7 @@ from typing import Dict, Iterable, List, Optional, Tuple
 import torch
 import torch.distributed as dist
 
-B200_PEAK_TFLOPS = {"bf16": 2250.0, "fp8": 4500.0, "nvfp4": 9000.0}
+B200_PEAK_TFLOPS = {"bf16": 2250.0, "fp8": 4500.0, "nvfp4": 9000.0, "nvfp4x16": 9000.0}
 _SCHEMA = ("CREATE TABLE IF NOT EXISTS metrics (run TEXT, tag TEXT, step INTEGER, ts_ms BIGINT, value DOUBLE, "
            "PRIMARY KEY (run, tag, step))")
 

@@ -87,8 +87,8 @@ class MoE(nn.Module):
       wq = None
       if self.expert_dtype != "bf16":
         if self._wcache is None:
-          from ..ops.quant import ExpertWeightCache
-          self._wcache = ExpertWeightCache(self.expert_dtype)
+          from ..ops.quant import NVFP4_PROFILE, ExpertWeightCache, ExpertWeightCacheNV16
+          self._wcache = ExpertWeightCacheNV16() if self.expert_dtype == NVFP4_PROFILE else ExpertWeightCache(self.expert_dtype)
         wq = self._wcache.get(self.W13, self.W2)
       if self.shared is not None and self.overlap_shared:
         cur = torch.cuda.current_stream()

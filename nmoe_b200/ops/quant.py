@@ -274,3 +274,83 @@ def expert_adamw_quant_(p: torch.Tensor, g: torch.Tensor, m: torch.Tensor, v: to
                                           L.c_float(beta1), L.c_float(beta2), L.c_float(eps), L.c_float(weight_decay),
                                           int(step), L.c_float(grad_scale), L.ptr(q), L.ptr(sf), int(fp4), L.stream()),
           "expert_adamw_quant")
+
+
+# ------------------------------------------------------------------ NVFP4 proper (16-element blocks, UE4M3 scales)
+# A second 4-bit expert profile next to the reference's "nvfp4" (which is E2M1 with one E8M0 scale per 32 elements):
+# NVIDIA's NVFP4, E2M1 values with one UE4M3 scale per 16 elements and an fp32 scale per tensor.  Activations use a
+# FIXED tensor scale (rows of one expert segment come from different ranks, and post-norm activations are O(1): with
+# 1/64 a block maximum between 1.8e-4 and 42 is representable), weights a scale from their own maximum, kept on the
+# device; the product reaches the GEMM epilogue through a device pointer, so the layer has no host read.
+NVFP4_PROFILE = "nvfp4x16"
+NVFP4_ACT_SCALE = 1.0 / 64.0
+
+
+def nvfp4_act_scale(device) -> torch.Tensor:
+  t = _ACT_SCALE.get(device)
+  if t is None:
+    t = torch.full((1,), NVFP4_ACT_SCALE, dtype=torch.float32, device=device)
+    _ACT_SCALE[device] = t
+  return t
+
+
+_ACT_SCALE: dict = {}
+
+
+def quant_nvfp4_rows(x: torch.Tensor, ts: torch.Tensor):
+  """x [M,K] bf16 -> (E2M1 nibbles [M,K/2], UE4M3 scale atoms) against the given tensor scale ``ts`` (fp32 [1], on the
+  device): no reduction over x, so rows that hold stale data cannot disturb the others."""
+  M, K = x.shape
+  if not x.is_cuda:
+    q, bs, _ = RQ.quant_nvfp4(x.float(), ts)
+    Mp = (M + 127) // 128 * 128
+    cols = ((K // 16) + 3) // 4 * 4
+    sfp = torch.zeros((Mp, cols), dtype=torch.uint8)
+    sfp[:M, :K // 16] = bs.view(torch.uint8)
+    return q, RQ.sf_to_mma_layout(sfp)
+  q = torch.empty(M, K // 2, dtype=torch.uint8, device=x.device)
+  sf = torch.zeros(sf_bytes(M, 2 * K), dtype=torch.uint8, device=x.device)
+  L.check(L.lib().nmoe_quant_nvfp4(L.ptr(x.contiguous()), L.ptr(q), L.ptr(sf), L.c_ll(M), K, L.ptr(ts), L.stream()),
+          "quant_nvfp4")
+  return q, sf
+
+
+def grouped_gemm_nvfp4(aq: torch.Tensor, asf: torch.Tensor, bq: torch.Tensor, bsf: torch.Tensor, alpha_dev: torch.Tensor,
+                       tile_expert: torch.Tensor, n_m_tiles: torch.Tensor, *, out: Optional[torch.Tensor] = None,
+                       bn: int = 0) -> torch.Tensor:
+  """Rows of aq [Mcap, K/2] are 128-aligned expert segments; bq [E, N, K/2] with stacked UE4M3 scale atoms;
+  ``alpha_dev`` (fp32 [1] on the device) = product of the two tensor scales.  Returns bf16 [Mcap, N]."""
+  Mcap, K = aq.size(0), aq.size(1) * 2
+  E, N = bq.size(0), bq.size(1)
+  if out is None:
+    out = torch.empty(Mcap, N, dtype=torch.bfloat16, device=aq.device)
+  st = status_buffer(aq.device)
+  L.check(L.lib().nmoe_gemm_nvfp4_dev(L.ptr(aq), L.ptr(asf), L.ptr(bq), L.ptr(bsf), L.ptr(out), Mcap, N, K,
+                                      L.c_ll(out.stride(0)), 1, E, L.ptr(tile_expert), L.ptr(n_m_tiles), L.c_ll(Mcap),
+                                      L.c_ll(E * N), bn, L.c_float(1.0), L.ptr(alpha_dev), L.ptr(st), L.stream()),
+          "grouped_gemm_nvfp4")
+  return out
+
+
+class ExpertWeightCacheNV16:
+  """NVFP4 copies of one layer's expert weights: (W13q, W13sf, alpha13, W2q, W2sf, alpha2) with alpha = weight tensor
+  scale x the fixed activation scale, all on the device.  Rebuilt when the bf16 masters change (version counters)."""
+
+  def __init__(self):
+    self.ver = [-1, -1]
+    self.q = [None, None]
+    self.sf = [None, None]
+    self.alpha = [None, None]
+
+  @torch.no_grad()
+  def get(self, W13: torch.Tensor, W2: torch.Tensor):
+    for idx, W in ((0, W13), (1, W2)):
+      if self.q[idx] is None or self.ver[idx] != W._version:
+        E, n, k = W.shape
+        w2d = W.detach().view(E * n, k)
+        ts = (w2d.abs().amax().float() * (1.0 / (6.0 * 448.0))).clamp(min=1e-30).reshape(1)
+        q, sf = quant_nvfp4_rows(w2d, ts)
+        self.q[idx], self.sf[idx] = q.view(E, n, k // 2), sf
+        self.alpha[idx] = ts * NVFP4_ACT_SCALE
+        self.ver[idx] = W._version
+    return self.q[0], self.sf[0], self.alpha[0], self.q[1], self.sf[1], self.alpha[1]

@@ -96,6 +96,10 @@ class Rdep:
     # dropped and reported through the status record
     rows = worst if (self.world == 1 or capacity_factor <= 0) else min(worst, int(avg * capacity_factor))
     # per-expert segments are padded to `align` rows: 256 lets the grouped GEMMs run on CTA pairs (two-SM MMA)
+    # "nvfp4x16" (NVFP4 proper): rows travel and are kept in bf16 like the bf16 profile, and are quantised on the owner
+    self.nv16 = profile == "nvfp4x16"
+    if self.nv16:
+      profile = "bf16"
     self.align = 256 if (G.PAIR_MODE and profile == "bf16") else 128
     if os.environ.get("NMOE_RDEP_ALIGN"):
       self.align = int(os.environ["NMOE_RDEP_ALIGN"])
@@ -308,6 +312,23 @@ def _moe_forward(rdep: "Rdep", x, gates32, eid, W13, W2, save_h13, wq, out):
   x).  Returns (plan, h13 kept for backward or None, dispatched rows kept for backward or None)."""
   plan = rdep.plan(eid)
   rows = rdep.rows_of(plan)
+  if wq is not None and rdep.nv16:
+    # NVFP4 proper: bf16 rows are placed as in the bf16 profile, quantised on the owner (16-element blocks, UE4M3 scales,
+    # fixed activation tensor scale), both projections on the kind::mxf4nvf4 scale_vec::4X tensor-core path
+    from ..ops import quant as Q
+    W13q, W13sf, a13, W2q, W2sf, a2 = wq
+    ts = Q.nvfp4_act_scale(x.device)
+    with span("time_ms/comm/rdep_dispatch"):
+      rdep.place(x, plan, gates32.view(-1), "x", with_meta=True)
+      rdep.wait_data()
+    xq, xsf = Q.quant_nvfp4_rows(rdep.xbuf[:rows], ts)
+    h13 = Q.grouped_gemm_nvfp4(xq, xsf, W13q, W13sf, a13, plan.tile_expert, plan.n_m_tiles)
+    a = EW.swiglu_rows(h13, plan.n_m_tiles)
+    aq, asf = Q.quant_nvfp4_rows(a, ts)
+    y = Q.grouped_gemm_nvfp4(aq, asf, W2q, W2sf, a2, plan.tile_expert, plan.n_m_tiles)
+    rdep.push_and_reduce(y, plan, gates32.view(-1), None, out)
+    xd = rdep.xbuf[:rows].clone() if rdep.save_dispatched else None
+    return plan, (h13 if save_h13 else None), xd
   if wq is not None:
     from ..ops import quant as Q
     W13q, W13sf, W2q, W2sf = wq

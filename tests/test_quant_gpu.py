@@ -145,6 +145,45 @@ def test_moe_fp4_forward_close_to_bf16_and_backward_runs():
     rd.close()
 
 
+def test_moe_nvfp4_proper_is_closer_to_the_oracle_than_the_32_element_profile():
+  """"nvfp4x16": E2M1 with one UE4M3 scale per 16 elements and an fp32 tensor scale (fixed for activations, from the
+  maximum for weights, both left on the device) as an expert profile through the whole layer.  Finer blocks and a
+  mantissa in the scale must give a smaller error than the E8M0-per-32 profile on the same data; backward is the bf16
+  straight-through one and must match the bf16 profile's gradients closely."""
+  from nmoe_b200.parallel.rdep import Rdep, moe_reference
+  from nmoe_b200.ops.quant import ExpertWeightCache, ExpertWeightCacheNV16
+  from nmoe_b200.ops import tc_gemm as G
+  dev = torch.device("cuda")
+  T, H, F, E, K = 512, 256, 384, 8, 2
+  res = {}
+  for profile in ("nvfp4", "nvfp4x16", "bf16"):
+    torch.manual_seed(4)
+    rd = Rdep(H, E, K, T, device=dev, profile=profile)
+    try:
+      x = (torch.randn(T, H, device=dev) * 0.5).bfloat16().requires_grad_()
+      W13 = (torch.randn(E, 2 * F, H, device=dev) * 0.05).bfloat16().requires_grad_()
+      W2 = (torch.randn(E, H, F, device=dev) * 0.05).bfloat16().requires_grad_()
+      eid = torch.stack([torch.randperm(E, device=dev)[:K] for _ in range(T)]).int()
+      gates = torch.rand(T, K, device=dev).requires_grad_()
+      wq = None if profile == "bf16" else (ExpertWeightCacheNV16() if profile == "nvfp4x16" else ExpertWeightCache("nvfp4")).get(W13, W2)
+      torch.manual_seed(9)
+      out = rd.moe(x, gates, eid, W13, W2, False, wq)
+      out.backward(torch.randn_like(out))
+      torch.cuda.synchronize()
+      G.check_status()
+      ref = moe_reference(x.detach().float().cpu(), gates.detach().cpu(), eid.cpu().long(), W13.detach().float().cpu(),
+                          W2.detach().float().cpu())
+      err = ((out.float().cpu() - ref).pow(2).mean().sqrt() / ref.pow(2).mean().sqrt()).item()
+      res[profile] = (err, x.grad.float().cpu(), W13.grad.float().cpu())
+    finally:
+      rd.close()
+  assert res["nvfp4x16"][0] < 0.8 * res["nvfp4"][0], {k: v[0] for k, v in res.items()}
+  assert res["nvfp4x16"][0] < 0.2, res["nvfp4x16"][0]
+  for i in (1, 2):     # straight-through backward on the saved bf16 rows: the bf16 profile's gradients up to roundings
+    a, b = res["nvfp4x16"][i], res["bf16"][i]
+    assert (a - b).abs().max().item() <= 3e-2 * b.abs().max().item()
+
+
 @pytest.mark.parametrize("M,N,K,bn", [(128, 128, 256, 128), (256, 256, 512, 256), (1000, 384, 1088, 0), (2048, 2816, 2048, 0)])
 def test_gemm_nvfp4_vs_dequantised_matmul(M, N, K, bn):
   """True NVFP4 (16-element blocks, UE4M3 scales, fp32 tensor scale): quantiser bit-exact vs the emulation,
