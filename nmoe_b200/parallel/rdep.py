@@ -132,12 +132,12 @@ class Rdep:
     self.epoch_data = 0
     self.epoch_ret = 0
     self.wait_budget = 0          # 0 = library default (seconds); tests shrink it
-    # fused_return False: a local GEMM, then a separate push kernel (NMOE_RDEP_FUSED_RETURN=0/1 overrides).
-    # Default by measurement: with one peer the fused epilogue wins; from four ranks on, 3/4 or more of the rows
-    # leave the GPU and the four epilogue warps per SM cannot keep enough remote stores in flight, so a local GEMM
-    # followed by the wide push kernel is faster (8 GPUs, Moonlight shape: 1.82 ms against 2.37 ms per return).
+    # fused_return: the down-projection GEMM's epilogue sends its rows to the sources itself (bulk copies of contiguous
+    # runs); False: a local GEMM, then a separate push kernel (NMOE_RDEP_FUSED_RETURN=0/1 overrides).  Default by
+    # measurement with the run-ordered return, Moonlight shape, GEMM + return: 531 us against ~800 us at 2 GPUs and
+    # 624 us against 1145 us at 4 GPUs (the push kernel alone moves its bytes at 647 GB/s there).
     env = os.environ.get("NMOE_RDEP_FUSED_RETURN", "")
-    self.fused_return = (env == "1") if env in ("0", "1") else (self.world <= 2)
+    self.fused_return = (env == "1") if env in ("0", "1") else True
     # unfused return: 1 = rows travel as bulk asynchronous copies (global -> shared -> peer), 0 = 16-byte stores
     self.push_impl = int(os.environ.get("NMOE_RDEP_PUSH_BULK", "1"))
     self.fused_swiglu_quant = True  # block-scaled profiles: SwiGLU + quantise in the up/gate GEMM's epilogue
@@ -148,6 +148,10 @@ class Rdep:
     # With a capacity factor the buffers themselves are a small multiple of the balanced share: nothing is read
     # back and the layer runs without any host synchronisation, at the price of dropping rows beyond that bound.
     self.trim_rows = self.world > 1 and capacity_factor <= 0
+    # start the mark a little above the balanced share (pairs + half a tile of padding per expert), on a 4096-row grid
+    self._rows_grain = 4096
+    start = int(1.04 * pairs) + self.n_local * self.align // 2
+    self._rows_hwm = min(self.capacity, (start + self._rows_grain - 1) // self._rows_grain * self._rows_grain)
     # world > 1 (bf16): keep a copy of the dispatched rows for the weight gradient instead of sending x over
     # NVLink a second time in backward (one of five transfers per layer; costs rows x H x 2 bytes per layer)
     self.save_dispatched = self.world > 1
@@ -158,7 +162,12 @@ class Rdep:
     if plan.rows == 0:
       if self.trim_rows:
         n = int(plan.n_m_tiles.item()) * 128
-        plan.rows = min(self.capacity, max(256, (n + 255) // 256 * 256))
+        # Not the exact count but a high-water mark on a coarse grid: the per-layer tensors then have the SAME size in
+        # every layer and step (until routing sets a new maximum), so the caching allocator hands the same blocks round
+        # instead of meeting a new size in every layer of every step -- which it answers with cudaMalloc / cudaFree for
+        # the first dozens of steps (measured at 4 GPUs: 462 ms per step while that lasts, 394 ms after).
+        self._rows_hwm = max(self._rows_hwm, (n + self._rows_grain - 1) // self._rows_grain * self._rows_grain)
+        plan.rows = min(self.capacity, self._rows_hwm)
       else:
         plan.rows = self.capacity
     return plan.rows

@@ -73,7 +73,7 @@ def check_moe(rank, world, dev, profile="bf16", pipeline=False):
   # average it away): two chained E4M3 GEMMs give a few percent of the output scale, E2M1 (two mantissa levels per
   # octave) several times that on contractions as short as this toy's 256 / 128; on the
   # reference's toy magnitudes these are its bars of 1e-2 / 5e-2 absolute (tests/test_rdep_accuracy.py:81-112).
-  afrac, rtol, gtol = {"bf16": (6e-3, 1.6e-2, 3e-2), "fp8": (8e-2, 0.1, 8e-2), "nvfp4": (0.4, 0.5, 0.35)}[profile]
+  afrac, rtol, gtol = {"bf16": (6e-3, 1.6e-2, 3e-2), "fp8": (8e-2, 0.1, 8e-2), "nvfp4": (0.4, 0.5, 0.45)}[profile]
   errs["out_excess"] = close(out.cpu(), ref[sl], afrac * ref[sl].abs().max().item(), rtol)
   assert errs["out_excess"] <= 0, (profile, errs)
   assert all(v < gtol for k, v in errs.items() if k != "out_excess"), (profile, errs)
