@@ -370,6 +370,7 @@ def main() -> None:
                  "experts": f"{cfg.n_routed_experts} top-{cfg.n_activated_experts} + {cfg.n_shared_experts} shared",
                  "activation_checkpoint": args.activation_checkpoint, "moe_save_h13": not args.recompute_h13,
                  "rdep_capacity_factor": cfg.rdep_capacity_factor,
+                 "rdep_rows": (trainer.model.rdep.rows_mode if (trainer.model.rdep is not None and trainer.model.rdep.trim_rows) else "fixed"),
                  "moe_pipeline": bool(trainer.model.rdep is not None and trainer.model.rdep.halves is not None), "zero2_overlap": bool(getattr(trainer.opt.dense, "overlap", False)),
                  "l2": "per-step working set (32 GB of weights) is far larger than the 126 MB L2"},
       "tflops_per_gpu": tflops_per_gpu,

@@ -634,6 +634,12 @@ __global__ void k_rdep_row_gates(const RdepMeta* __restrict__ meta, const int* _
     out[r] = meta[r].valid ? meta[r].gate : 0.f;
 }
 
+__global__ void k_rdep_clamp_tiles(int* n_m_tiles, int limit_tiles, int* seen) {
+  const int n = *n_m_tiles;
+  if (seen != nullptr) *reinterpret_cast<volatile int*>(seen) = n;
+  if (n > limit_tiles) *n_m_tiles = limit_tiles;
+}
+
 }  // namespace nmoe
 
 using namespace nmoe;
@@ -811,6 +817,16 @@ int nmoe_rdep_reduce(const void* ret, const int* lpos, const float* gates, void*
 int nmoe_rdep_gather_scalar(const float* retg, const int* lpos, float* out, int n_pairs, cudaStream_t st) {
   if (n_pairs == 0) return 0;
   k_rdep_gather_scalar<<<(n_pairs + 255) / 256 < 1184 ? (n_pairs + 255) / 256 : 1184, 256, 0, st>>>(retg, lpos, out, n_pairs);
+  CHECK_LAUNCH();
+  return 0;
+}
+
+// Rows that landed on this rank against the rows the layer's tensors were sized for (see Rdep.rows_of): the count
+// goes to `seen` (pinned host memory the host looks at later, without waiting) and n_m_tiles is cut to the limit, so
+// that every consumer -- they all read n_m_tiles on the device -- stays inside its tensors.  Rows beyond the limit are
+// not computed; the host notices from `seen` one step late, says so and enlarges the limit.
+int nmoe_rdep_clamp_tiles(int* n_m_tiles, int limit_tiles, int* seen, cudaStream_t st) {
+  k_rdep_clamp_tiles<<<1, 1, 0, st>>>(n_m_tiles, limit_tiles, seen);
   CHECK_LAUNCH();
   return 0;
 }

@@ -16,8 +16,10 @@ W1,W3 [E,H,Dff], W2 [E,Dff,H] (nmoe/model.py:92-94) for checkpoints.
 """
 from __future__ import annotations
 
+import collections
 import ctypes
 import os
+import sys
 from dataclasses import dataclass
 from typing import Optional, Tuple
 
@@ -147,10 +149,17 @@ class Rdep:
     # queued on its own stream by then, so the device does not idle) and cuts those tensors by ~world x.
     # With a capacity factor the buffers themselves are a small multiple of the balanced share: nothing is read
     # back and the layer runs without any host synchronisation, at the price of dropping rows beyond that bound.
-    self.trim_rows = self.world > 1 and capacity_factor <= 0
+    self.trim_rows = (self.world > 1 or os.environ.get("NMOE_RDEP_TRIM") == "1") and capacity_factor <= 0
     # start the mark a little above the balanced share (pairs + half a tile of padding per expert), on a 4096-row grid
+    # NMOE_RDEP_ROWS: "stale" (default) sizes them from the mark without reading anything back; "exact" reads the
+    # count of every call (one 4-byte host read per MoE forward) and can never fall short
+    self.rows_mode = os.environ.get("NMOE_RDEP_ROWS", "stale")
+    self.rows_overflows = 0
+    self._seen = torch.full((256,), -1, dtype=torch.int32).pin_memory() if self.device.type == "cuda" else None
+    self._seen_next = 0
+    self._seen_pending = collections.deque()
     self._rows_grain = 4096
-    start = int(1.04 * pairs) + self.n_local * self.align // 2
+    start = int(1.06 * pairs) + self.n_local * self.align // 2
     self._rows_hwm = min(self.capacity, (start + self._rows_grain - 1) // self._rows_grain * self._rows_grain)
     # world > 1 (bf16): keep a copy of the dispatched rows for the weight gradient instead of sending x over
     # NVLink a second time in backward (one of five transfers per layer; costs rows x H x 2 bytes per layer)
@@ -160,7 +169,19 @@ class Rdep:
   def rows_of(self, plan: Plan) -> int:
     """Rows of the expert-side buffers that the layer's tensors must cover (multiple of 256)."""
     if plan.rows == 0:
-      if self.trim_rows:
+      if self.trim_rows and self.rows_mode == "stale":
+        # no host read: size by the mark, let a one-thread kernel cut the device-side tile count to it and leave the true
+        # count in pinned memory, which the host looks at on later calls (see _poll_seen)
+        self._poll_seen()
+        limit = min(self.capacity, self._rows_hwm)
+        slot = self._seen_next
+        self._seen_next = (slot + 1) % self._seen.numel()
+        self._seen[slot] = -1
+        L.check(L.lib().nmoe_rdep_clamp_tiles(L.ptr(plan.n_m_tiles), limit // 128,
+                                              ctypes.c_void_p(self._seen.data_ptr() + 4 * slot), L.stream()), "rdep_clamp_tiles")
+        self._seen_pending.append((slot, limit // 128))
+        plan.rows = limit
+      elif self.trim_rows:
         n = int(plan.n_m_tiles.item()) * 128
         # Not the exact count but a high-water mark on a coarse grid: the per-layer tensors then have the SAME size in
         # every layer and step (until routing sets a new maximum), so the caching allocator hands the same blocks round
@@ -171,6 +192,25 @@ class Rdep:
       else:
         plan.rows = self.capacity
     return plan.rows
+
+  def _poll_seen(self) -> None:
+    """Look at the row counts that earlier calls left in pinned memory (those whose kernel has run by now): a count
+    near the mark raises the mark before it is hit; a count above the limit it was given means that call computed only
+    the rows that fitted -- reported once per occurrence, and the mark jumps past it."""
+    while self._seen_pending:
+      slot, limit_tiles = self._seen_pending[0]
+      n = int(self._seen[slot])
+      if n < 0:
+        break                                   # that kernel has not run yet; later entries have not either
+      self._seen_pending.popleft()
+      if n > limit_tiles:
+        self.rows_overflows += 1
+        print(f"[nmoe] rank {self.rank}: {n * 128} expert rows arrived where {limit_tiles * 128} were provided for; "
+              f"{(n - limit_tiles) * 128} rows of that call were not computed (raising the bound)", file=sys.stderr, flush=True)
+      need = n * 128
+      if need > 0.92 * self._rows_hwm:
+        g = self._rows_grain
+        self._rows_hwm = min(self.capacity, (int(need * 1.08) + g - 1) // g * g)
 
   def plan(self, eid: torch.Tensor) -> Plan:
     T, K = eid.shape

@@ -251,3 +251,53 @@ def test_moe_bf16_forward_within_bf16_roundings_of_a_faithful_loop():
     assert excess.max().item() <= 0, excess.max().item()
   finally:
     rd.close()
+
+
+def test_rows_sized_without_a_host_read_recover_from_an_underestimate(monkeypatch, capfd):
+  """Lossless receive buffers, per-layer tensors sized from a running bound instead of the exact count (no host read).
+  Forced here on one GPU with a bound that is far too small: the first call computes only the rows that fit (every
+  consumer sees the clamped tile count: no out-of-range access, status clean), the host then learns the true count
+  from pinned memory, says so, raises the bound, and the next call is exact again."""
+  from nmoe_b200.parallel.rdep import Rdep, moe_reference
+  from nmoe_b200.ops import tc_gemm as G
+  monkeypatch.setenv("NMOE_RDEP_TRIM", "1")
+  monkeypatch.setenv("NMOE_RDEP_ROWS", "stale")
+  torch.manual_seed(0)
+  dev = torch.device("cuda")
+  T, H, F, E, K = 1024, 256, 128, 8, 2
+  rd = Rdep(H, E, K, T, device=dev)
+  try:
+    assert rd.trim_rows and rd.rows_mode == "stale"
+    x = (torch.randn(T, H, device=dev) * 0.5).bfloat16().requires_grad_()
+    W13 = (torch.randn(E, 2 * F, H, device=dev) * 0.05).bfloat16().requires_grad_()
+    W2 = (torch.randn(E, H, F, device=dev) * 0.05).bfloat16().requires_grad_()
+    eid = torch.stack([torch.randperm(E, device=dev)[:K] for _ in range(T)]).int()
+    gates = torch.rand(T, K, device=dev).requires_grad_()
+    ref = moe_reference(x.detach().float().cpu(), gates.detach().cpu(), eid.cpu().long(), W13.detach().float().cpu(),
+                        W2.detach().float().cpu())
+    rd._rows_hwm = 512                                   # 2048 pairs (+ padding) will arrive
+    out = rd.moe(x, gates, eid, W13, W2, True)
+    out.backward(torch.randn_like(out))
+    torch.cuda.synchronize()
+    G.check_status()                                     # nothing faulted, nothing timed out
+    assert torch.isfinite(out.float()).all()
+    bad = _rel(out.cpu(), ref)
+    assert bad > 0.1                                     # most rows were not computed
+    for _ in range(2):                                   # the count of the first call is visible now
+      for t in (x, W13, W2, gates):
+        t.grad = None
+      out = rd.moe(x, gates, eid, W13, W2, True)
+    torch.cuda.synchronize()
+    G.check_status()
+    assert rd.rows_overflows >= 1 and rd._rows_hwm >= 2048
+    assert "were not computed" in capfd.readouterr().err
+    assert _rel(out.cpu(), ref) < 3e-2
+    g = torch.randn_like(out)
+    out.backward(g)
+    torch.cuda.synchronize()
+    xf, Wf, W2f, gf = [t.detach().float().cpu().requires_grad_() for t in (x, W13, W2, gates)]
+    r2 = moe_reference(xf, gf, eid.cpu().long(), Wf, W2f)
+    r2.backward(g.float().cpu())
+    assert _rel(x.grad.cpu(), xf.grad) < 3e-2 and _rel(W13.grad.cpu(), Wf.grad) < 3e-2
+  finally:
+    rd.close()
