@@ -346,50 +346,58 @@ __global__ void __launch_bounds__(256) k_rdep_place_mx(const PlaceMxArgs am) {
   const int row_blocks = gridDim.x - a.pad_blocks;
   const int nblk = a.H >> 5;
   if (static_cast<int>(blockIdx.x) < row_blocks) {
-    const int n_pairs = a.T * a.K;
-    for (int i = blockIdx.x * 8 + warp; i < n_pairs; i += row_blocks * 8) {
-      const int e = a.eid[i];
-      const int rb = a.rank_in_block[i];
-      int pos = -1, owner = 0, lp = -1;
-      if (e >= 0 && e < a.E && rb >= 0 && a.base[e] >= 0) {
-        owner = e / a.n_local;
-        const int within = a.block_prefix[(i / kCountThreads) * a.E + e] + rb;
-        pos = a.base[e] + within;
-        lp = a.send_prefix[e] + within;
+    // One warp per TOKEN: its row is loaded and quantised once, then stored to each of its K destinations (lane k
+    // works out slot k's destination; the others get it by shuffle).  K <= 32.
+    const int row_bytes = am.fp4 ? (a.H >> 1) : a.H;
+    for (int tok = blockIdx.x * 8 + warp; tok < a.T; tok += row_blocks * 8) {
+      int my_pos = -1, my_owner = 0;
+      if (lane < a.K) {
+        const int i = tok * a.K + lane;
+        const int e = a.eid[i];
+        const int rb = a.rank_in_block[i];
+        int lp = -1;
+        if (e >= 0 && e < a.E && rb >= 0 && a.base[e] >= 0) {
+          my_owner = e / a.n_local;
+          const int within = a.block_prefix[(i / kCountThreads) * a.E + e] + rb;
+          my_pos = a.base[e] + within;
+          lp = a.send_prefix[e] + within;
+        }
+        a.pos_out[i] = my_pos;
+        if (a.lpos_out) a.lpos_out[i] = lp;
       }
-      if (lane == 0) { a.pos_out[i] = pos; if (a.lpos_out) a.lpos_out[i] = lp; }
-      if (pos < 0) continue;
-      const int tok = i / a.K;
       const __nv_bfloat16* src = a.x + static_cast<size_t>(tok) * a.H;
-      const int row_bytes = am.fp4 ? (a.H >> 1) : a.H;
-      uint8_t* qdst = am.peer_xq[owner] + static_cast<size_t>(pos) * row_bytes;
-      uint8_t* sfdst = am.peer_sf[owner];
       for (int b0 = 0; b0 < nblk; b0 += 32) {
         const int b = b0 + lane;
         uint32_t s = 127;
+        uint32_t w[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         if (b < nblk) {
           float v[32];
-          uint32_t w[8];
           load_block_bf16(src + b * 32, v);
+          s = am.fp4 ? quant_block_e2m1_regs(v, w) : quant_block_e4m3_regs(v, w);
+        }
+        const uint32_t packed = s | (__shfl_down_sync(0xffffffffu, s, 1) << 8) | (__shfl_down_sync(0xffffffffu, s, 2) << 16) |
+                                (__shfl_down_sync(0xffffffffu, s, 3) << 24);
+        for (int k = 0; k < a.K; ++k) {
+          const int pos = __shfl_sync(0xffffffffu, my_pos, k);
+          const int owner = __shfl_sync(0xffffffffu, my_owner, k);
+          if (pos < 0 || b >= nblk) continue;
+          uint8_t* qdst = am.peer_xq[owner] + static_cast<size_t>(pos) * row_bytes;
           if (am.fp4) {
-            s = quant_block_e2m1_regs(v, w);
             st_relaxed_sys_v4(qdst + b * 16, make_int4(w[0], w[1], w[2], w[3]));
           } else {
-            s = quant_block_e4m3_regs(v, w);
             st_relaxed_sys_v4(qdst + b * 32, make_int4(w[0], w[1], w[2], w[3]));
             st_relaxed_sys_v4(qdst + b * 32 + 16, make_int4(w[4], w[5], w[6], w[7]));
           }
+          if ((lane & 3) == 0)
+            asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(am.peer_sf[owner] + sf_mma_offset(pos, b, am.sf_cols_padded)),
+                         "r"(packed) : "memory");
         }
-        uint32_t packed = s | (__shfl_down_sync(0xffffffffu, s, 1) << 8) | (__shfl_down_sync(0xffffffffu, s, 2) << 16) |
-                          (__shfl_down_sync(0xffffffffu, s, 3) << 24);
-        if ((lane & 3) == 0 && b < nblk)
-          asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(sfdst + sf_mma_offset(pos, b, am.sf_cols_padded)),
-                       "r"(packed) : "memory");
       }
-      if (lane == 0 && a.peer_meta[owner] != nullptr) {
+      if (lane < a.K && my_pos >= 0 && a.peer_meta[my_owner] != nullptr) {
+        const int i = tok * a.K + lane;
         int4 m;
         m.x = a.rank; m.y = i; m.z = __float_as_int(a.gates ? a.gates[i] : 1.f); m.w = 1;
-        st_relaxed_sys_v4(a.peer_meta[owner] + pos, m);
+        st_relaxed_sys_v4(a.peer_meta[my_owner] + my_pos, m);
       }
     }
   } else {
