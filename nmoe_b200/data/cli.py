@@ -7,6 +7,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import os
 import sys
 from pathlib import Path
 from typing import Optional
@@ -248,7 +249,11 @@ def cmd_flow(a) -> int:
       for r in out:
         by_doc.setdefault(r.doc, []).append(r.text)
       return [by_doc.get(i, [t] if n_ver == 1 else []) for i, t in enumerate(texts)]
-  run_flow(spec, grader=grader, rephraser=rephraser)
+  if a.staged or spec.prep.get("staged"):
+    from .staged import run_flow_staged      # every stage on disk; an interrupted run continues
+    run_flow_staged(spec, grader=grader, rephraser=rephraser)
+  else:
+    run_flow(spec, grader=grader, rephraser=rephraser)
   return 0
 
 
@@ -285,22 +290,67 @@ def _grading_model(a):
   return load_model(a.checkpoint, device=dev, dtype=torch.bfloat16 if dev == "cuda" else torch.float32), dev
 
 
+def _grading_inputs(a, tok):
+  """(ids, token lists) of the documents to grade: a JSONL of texts (``--input``), or a list of shard references
+  (``--input-docids`` with ``--data-root``) whose tokens are read from the shards without going through text.
+  With ``--resume``, ids already present in the output file are left out."""
+  done = set()
+  if getattr(a, "resume", False) and os.path.exists(a.output):
+    for line in open(a.output, encoding="utf-8"):
+      try:
+        done.add(str(json.loads(line).get("doc_id")))
+      except json.JSONDecodeError:      # a line cut by a crash: its document is graded again
+        pass
+  if getattr(a, "input_docids", None):
+    if not a.data_root:
+      raise SystemExit("--input-docids needs --data-root")
+    from .docid import SpanReader, read_refs
+    reader = SpanReader(a.data_root)
+    refs = list(read_refs(a.input_docids, skip=done))[:a.max_documents]
+    return [str(r) for r in refs], [reader.tokens(r, a.max_ctx) for r in refs], len(done)
+  if not a.input:
+    raise SystemExit("one of --input / --input-docids is required")
+  rows = _read_jsonl(a.input, a.text_field, a.max_documents)
+  ids = [str(r.get("doc_id", r.get("id", i))) for i, r in enumerate(rows)]
+  keep = [i for i, d in enumerate(ids) if d not in done]
+  return [ids[i] for i in keep], [tok.encode(rows[i][a.text_field])[:a.max_ctx] for i in keep], len(done)
+
+
 def cmd_hydra_grade(a) -> int:
-  """JSONL in -> JSONL out with q_probe / rubric scores / decision per document (probe early exit, judge)."""
+  """Documents in -> JSONL out with q_probe / rubric scores / decision per document (probe early exit, judge)."""
   from . import hydra as H
+  if not a.output:
+    raise SystemExit("hydra-grade needs --output")
   model, dev = _grading_model(a)
   probe, judge = H.load_heads(a.heads, model.cfg.hidden_size, dev)
   calib = H.Calibration.load(a.calibration or a.heads)
-  tok = _tokenizer(a.tokenizer)
-  rows = _read_jsonl(a.input, a.text_field, a.max_documents)
-  docs = [tok.encode(r[a.text_field])[:a.max_ctx] for r in rows]
-  ids = [str(r.get("id", i)) for i, r in enumerate(rows)]
-  out = H.grade(model, probe, judge, docs, ids, calib, batch_size=a.batch_size, max_ctx=a.max_ctx, early_exit=not a.no_early_exit)
-  with open(a.output, "w", encoding="utf-8") as f:
-    for r in out:
-      f.write(json.dumps(r) + "\n")
-  st = H.grade.last_stats
-  print(f"graded {len(out)} documents: {st['probe_only']} dropped at the probe, {st['judged']} judged -> {a.output}")
+  ids, docs, n_done = _grading_inputs(a, _tokenizer(a.tokenizer))
+  probe_only = judged = 0
+  with open(a.output, "a" if n_done else "w", encoding="utf-8") as f:
+    # graded in slabs so that a long run leaves its finished part on disk for --resume
+    for i0 in range(0, len(docs), a.flush_every):
+      out = H.grade(model, probe, judge, docs[i0:i0 + a.flush_every], ids[i0:i0 + a.flush_every], calib,
+                    batch_size=a.batch_size, max_ctx=a.max_ctx, early_exit=not a.no_early_exit)
+      for r in out:
+        f.write(json.dumps(r) + "\n")
+      f.flush()
+      probe_only += H.grade.last_stats["probe_only"]
+      judged += H.grade.last_stats["judged"]
+  print(f"graded {len(docs)} documents ({n_done} already done): {probe_only} dropped at the probe, {judged} judged -> {a.output}")
+  return 0
+
+
+def cmd_docids(a) -> int:
+  """List the documents of a prepared dataset as shard references (optionally a hash-sampled fraction of them)."""
+  from .docid import enumerate_refs, sample_refs, write_refs
+  refs = enumerate_refs(a.data_root, a.source, a.subdir, a.min_tokens)
+  if a.fraction < 1.0:
+    refs = sample_refs(refs, a.fraction, a.seed)
+  if a.limit:
+    import itertools
+    refs = itertools.islice(refs, a.limit)
+  n = write_refs(a.output, refs)
+  print(f"{n} document references -> {a.output}")
   return 0
 
 
@@ -348,7 +398,11 @@ def cmd_hydra_train(a) -> int:
   model, dev = _grading_model(a)
   cfg = model.cfg
   tok = _tokenizer(a.tokenizer)
-  rows = _read_jsonl(a.input, a.text_field, a.max_documents)
+  rows = _read_jsonl(a.input, a.text_field, a.max_documents) if a.input else []
+  if not rows and not (a.labels or a.oracle_labels):
+    raise SystemExit("hydra-train needs --input, or --labels / --oracle-labels")
+  if a.oracle_labels and not a.data_root:
+    raise SystemExit("--oracle-labels needs --data-root")
   try:
     probe, judge = H.load_heads(a.heads, cfg.hidden_size, dev)
   except FileNotFoundError:
@@ -371,7 +425,23 @@ def cmd_hydra_train(a) -> int:
       b["rubric"] = torch.tensor([[float((rows[i].get("scores") or {}).get(d, nan)) for d in H.RUBRIC] for i in idx], device=dev)
       yield b
 
-  losses = H.train_heads(H.PhaseConfig(a.phase, steps=a.steps, lr=a.lr), probe, judge, batches(), features,
+  def label_batches():
+    """Batches from label tables / oracle labels over shards instead of one flat JSONL."""
+    from . import hydra_labels as L
+    tables = [L.TableLabels(spec.split(":", 2)[2], L.FIELD_MAPS[spec.split(":", 2)[0]], spec.split(":", 2)[1], a.max_ctx)
+              for spec in (a.labels or [])]          # each: <field map>:<domain>:<path or glob>
+    if a.phase == "A":
+      return L.probe_batches(L.mix(tables, seed=a.seed), a.batch_size, tok.encode, a.max_ctx, dev)
+    graded = [t for t in tables if t.fields.grade]
+    pairs = L.GradedPairs(L.mix(graded, seed=a.seed), seed=a.seed) if graded else None
+    if a.oracle_labels:
+      oracle = L.OracleLabels(a.oracle_labels, a.data_root, a.max_ctx)
+    else:
+      oracle = L.mix(tables, seed=a.seed + 1)        # phase C needs documents only
+    return L.judge_batches(oracle, a.batch_size, tok.encode, a.max_ctx, pairs, a.pairs_per_batch if pairs else 0, dev)
+
+  use_labels = bool(a.labels or a.oracle_labels)
+  losses = H.train_heads(H.PhaseConfig(a.phase, steps=a.steps, lr=a.lr), probe, judge, label_batches() if use_labels else batches(), features,
                          log=lambda s, l: print(f"phase {a.phase} step {s} loss {l:.4f}"))
   H.save_heads(a.heads, probe, judge)
   print(f"phase {a.phase}: loss {losses[0]:.4f} -> {losses[-1]:.4f}; heads saved to {a.heads}")
@@ -471,9 +541,9 @@ def build_parser() -> argparse.ArgumentParser:
   p = sub.add_parser("inspect"); p.set_defaults(fn=cmd_inspect); p.add_argument("shard"); p.add_argument("--doc", type=int)
   p.add_argument("--start", type=int); p.add_argument("--length", type=int, default=64); p.add_argument("--tokenizer")
   p = sub.add_parser("merge-manifests"); p.set_defaults(fn=cmd_merge_manifests); p.add_argument("parts", nargs="+"); p.add_argument("--output", required=True)
-  p = sub.add_parser("flow"); p.set_defaults(fn=cmd_flow); p.add_argument("spec")
+  p = sub.add_parser("flow"); p.set_defaults(fn=cmd_flow); p.add_argument("spec"); p.add_argument("--staged", action="store_true")
   def model_args(p, heads=False):
-    p.add_argument("--checkpoint", required=True); p.add_argument("--input", required=True); p.add_argument("--output", required=True)
+    p.add_argument("--checkpoint", required=True); p.add_argument("--input", required=not heads); p.add_argument("--output", required=not heads)
     p.add_argument("--text-field", default="text"); p.add_argument("--tokenizer", default="o200k_harmony")
     p.add_argument("--max-ctx", type=int, default=4096); p.add_argument("--batch-size", type=int, default=32)
     p.add_argument("--max-documents", type=int)
@@ -481,9 +551,18 @@ def build_parser() -> argparse.ArgumentParser:
       p.add_argument("--heads", required=True)
   p = sub.add_parser("hydra-grade"); p.set_defaults(fn=cmd_hydra_grade); model_args(p, heads=True)
   p.add_argument("--calibration"); p.add_argument("--no-early-exit", action="store_true")
+  p.add_argument("--input-docids", help="JSONL of {doc_id: shard reference}; tokens are read from the shards"); p.add_argument("--data-root")
+  p.add_argument("--resume", action="store_true"); p.add_argument("--flush-every", type=int, default=4096)
+  p = sub.add_parser("docids"); p.set_defaults(fn=cmd_docids)
+  p.add_argument("--data-root", required=True); p.add_argument("--source", required=True); p.add_argument("--output", required=True)
+  p.add_argument("--subdir", default=""); p.add_argument("--min-tokens", type=int, default=0); p.add_argument("--fraction", type=float, default=1.0)
+  p.add_argument("--seed", type=int, default=0); p.add_argument("--limit", type=int)
   p = sub.add_parser("hydra-oracle-label"); p.set_defaults(fn=cmd_hydra_oracle_label); model_args(p); p.add_argument("--max-new", type=int, default=256)
   p = sub.add_parser("hydra-train"); p.set_defaults(fn=cmd_hydra_train); model_args(p, heads=True)
   p.add_argument("--phase", choices=["A", "B", "C"], required=True); p.add_argument("--steps", type=int, default=1000); p.add_argument("--lr", type=float, default=1e-3)
+  p.add_argument("--labels", action="append", help="<eai|fineweb_edu>:<web|code|science|math>:<parquet/JSONL path or glob>; repeatable")
+  p.add_argument("--oracle-labels", help="JSONL of {doc_id: shard reference, scores}"); p.add_argument("--data-root")
+  p.add_argument("--pairs-per-batch", type=int, default=8); p.add_argument("--seed", type=int, default=0)
   p = sub.add_parser("hydra-calibrate"); p.set_defaults(fn=cmd_hydra_calibrate)
   p.add_argument("--judged", required=True); p.add_argument("--oracle", required=True); p.add_argument("--output", required=True)
   p.add_argument("--oracle-keep", type=float, default=0.6); p.add_argument("--keep-precision", type=float, default=0.9)

@@ -238,6 +238,65 @@ def test_flow_writes_every_rephrased_version(tmp_path):
   assert k2.rephrase["num_versions"] == 10 and k2.grade["enabled"] and k2.source["kind"] == "hf"
 
 
+def test_staged_flow_keeps_stage_files_and_continues_after_an_interruption(tmp_path):
+  """Each stage writes its own file; a run cut in the grading or rephrasing stage computes only what is missing when
+  it is started again, and ends with the same shards as the streaming flow."""
+  from nmoe_b200.data.staged import StagedFlow, run_flow_staged
+  raw = tmp_path / "raw.jsonl"
+  raw.write_text("".join(json.dumps({"id": f"d{i}", "text": f"text {i} " * 6, "lang": "en"}) + "\n" for i in range(20)))
+  def spec_for(out):
+    sp = tmp_path / f"{out}.toml"
+    sp.write_text(f'[source]\nkind = "jsonl"\npaths = "{raw}"\n[prep]\noutput_dir = "{tmp_path / out}"\ndataset = "f"\n'
+                  'tokenizer = "bytes"\nnum_shards = 2\n[grade]\nenabled = true\nthreshold = 0.5\nbatch_size = 4\n'
+                  '[rephrase]\nenabled = true\nkeep_original = true\nbatch_size = 3\n')
+    return flow_mod.load_spec(sp, env={})
+  score_of = lambda t: float(int(t.split()[1]) % 2)          # odd documents are kept
+  calls = {"grade": 0, "re": 0}
+  class Cut(Exception):
+    pass
+  def grader(texts, fail_after=None):
+    if fail_after is not None and calls["grade"] >= fail_after:
+      raise Cut()
+    calls["grade"] += len(texts)
+    return [score_of(t) for t in texts]
+  def rephraser(texts, fail_after=None):
+    if fail_after is not None and calls["re"] >= fail_after:
+      raise Cut()
+    calls["re"] += len(texts)
+    return [[t.upper(), ""] for t in texts]
+  quiet = dict(env={}, print_fn=lambda *_: None)
+  s = spec_for("staged")
+  with pytest.raises(Cut):
+    run_flow_staged(s, grader=lambda t: grader(t, fail_after=8), rephraser=rephraser, **quiet)
+  st = tmp_path / "staged" / "stages"
+  assert calls["grade"] == 8 and len((st / "scores.jsonl").read_text().splitlines()) == 8
+  with open(st / "scores.jsonl", "a") as f:
+    f.write('{"id": "d8", "sco')                             # the write the crash cut short
+  with pytest.raises(Cut):
+    run_flow_staged(s, grader=grader, rephraser=lambda t: rephraser(t, fail_after=3), **quiet)
+  assert calls["grade"] == 20                                # 12 more, not 20 more
+  assert json.loads((st / "state.json").read_text())["done"] == {"raw": 20, "scores": 20, "kept": 10}
+  m = run_flow_staged(s, grader=lambda t: 1 / 0, rephraser=rephraser, **quiet)      # grading is not run again
+  assert calls["re"] == 10 and m.total_documents == 20       # 10 kept originals + 10 rephrased versions
+  rows = [json.loads(l) for l in open(st / "rephrased.jsonl")]
+  assert len(rows) == 20 and sum(1 for r in rows if r.get("rephrased")) == 10 and all(r["lang"] == "en" for r in rows)
+  assert {r["id"] for r in rows if r.get("rephrased")} == {f"d{i}#v0" for i in range(1, 20, 2)}
+  assert all(r["score"] == 1.0 for r in map(json.loads, open(st / "kept.jsonl")))
+  again = StagedFlow(s, grader=None, rephraser=None, **quiet)                          # everything is done: no model needed
+  assert all(again.done(x) for x in ("raw", "scores", "kept", "rephrased", "shards"))
+  assert again.run().total_tokens == m.total_tokens
+  # same tokens as the streaming flow
+  calls.update(grade=0, re=0)
+  m2 = flow_mod.run_flow(spec_for("stream"), grader=grader, rephraser=rephraser, **quiet)
+  assert (m2.total_documents, m2.total_tokens) == (m.total_documents, m.total_tokens)
+  sinks.verify_manifest(tmp_path / "staged")
+  # a different specification in the same directory is refused
+  sp = tmp_path / "staged.toml"
+  sp.write_text(sp.read_text().replace("threshold = 0.5", "threshold = 0.7"))
+  with pytest.raises(RuntimeError, match="different flow specification"):
+    StagedFlow(flow_mod.load_spec(sp, env={}), **quiet)
+
+
 def test_stage_graph_runner_builds_the_same_shards_as_the_serial_pipeline(tmp_path):
   """The Beam-shaped stage graph (tokenise -> group by shard -> write), run by the built-in runner, must produce a
   dataset that verifies and holds the same tokens per shard as the serial pipeline."""

@@ -181,3 +181,191 @@ num_shards = 1
   man = json.loads((out / "manifest.json").read_text())
   kept = man["total_documents"] if "total_documents" in man else man["documents"]
   assert 0 < kept < 20
+
+
+# ---------------------------------------------------------------------------------------------- shard references
+def _tiny_dataset(root, n_docs=40, seed=0):
+  """Two shards with index files under root/web/v1; returns the documents' token lists in reference order."""
+  import numpy as np
+  from nmoe_b200.data.sinks import ShardWriter
+  rng = np.random.default_rng(seed)
+  d = root / "web" / "v1"
+  d.mkdir(parents=True)
+  docs = []
+  for sh in range(2):
+    w = ShardWriter(d, "web", "v1", sh, eos_token_id=255)
+    for _ in range(n_docs // 2):
+      t = rng.integers(1, 250, size=int(rng.integers(5, 60))).tolist()
+      w.add_document(t)
+      docs.append(t)
+    w.finalize()
+  return docs
+
+
+def test_shard_reference_roundtrip_reader_and_sampling(tmp_path):
+  import pytest
+  from nmoe_b200.data import docid as D
+  r = D.SpanRef.make("common_crawl", "/cc\\v1/shard_000001.npy", 12, 40)
+  assert str(r) == "common_crawl//cc/v1/shard_000001.npy#s=12:e=40" and len(r) == 28
+  assert D.SpanRef.parse(str(r)) == r and D.is_ref(str(r)) and not D.is_ref("row:17")
+  for bad in ("nosource.npy#s=1:e=2", "a//b.npy", "a//b.npy#s=5", "a//b.npy#s=x:e=3"):
+    with pytest.raises(ValueError):
+      D.SpanRef.parse(bad)
+  with pytest.raises(ValueError):
+    D.SpanRef("a", "b.npy", 9, 3)
+  with pytest.raises(ValueError):
+    D.SpanRef.parse("a//../../etc/x.npy#s=0:e=1").path(tmp_path)      # must not leave the data root
+
+  docs = _tiny_dataset(tmp_path)
+  refs = list(D.enumerate_refs(tmp_path, "web"))
+  assert len(refs) == len(docs) and all(x.rel_path.startswith("web/v1/") for x in refs)
+  reader = D.SpanReader(tmp_path, max_open=1)
+  for ref, t in zip(refs, docs):
+    assert reader.tokens(ref) == t + [255]                     # the span includes the end-of-document token
+    assert reader.tokens(str(ref), drop_eos=255) == t
+  assert reader.tokens(refs[0], max_tokens=3) == docs[0][:3]
+  with pytest.raises(ValueError):
+    reader.tokens(D.SpanRef("web", refs[0].rel_path, 0, 10 ** 9))
+  assert len(list(D.enumerate_refs(tmp_path, "web", min_tokens=30))) < len(refs)
+
+  half = set(map(str, D.sample_refs(refs, 0.5, seed=3)))
+  assert 5 < len(half) < 35
+  assert half == set(map(str, D.sample_refs(reversed(refs), 0.5, seed=3)))       # order-independent
+  assert half <= set(map(str, D.sample_refs(refs, 0.8, seed=3)))                 # growing the fraction only adds
+  assert half != set(map(str, D.sample_refs(refs, 0.5, seed=4)))
+  p = tmp_path / "refs.jsonl"
+  assert D.write_refs(p, refs) == len(refs)
+  assert list(D.read_refs(p, skip=[str(refs[0])])) == refs[1:]
+
+
+def _write_parquet(path, rows):
+  import pyarrow as pa
+  import pyarrow.parquet as pq
+  pq.write_table(pa.Table.from_pylist(rows), str(path))
+
+
+def test_label_tables_oracle_labels_and_pair_sampler(tmp_path):
+  import json
+  import random
+  from nmoe_b200.data import docid as D
+  from nmoe_b200.data import hydra_labels as L
+  # a table with nested quality signals and taxonomy codes
+  eai = tmp_path / "eai.parquet"
+  _write_parquet(eai, [
+    {"text": "alpha " * 50, "quality_signals": {"fasttext": {"dclm": 0.7, "fineweb_edu_approx": 0.2, "eai_web_code": 0.0,
+                                                              "eai_general_math": 0.1, "english": 0.99}},
+     "eai_taxonomy": {"extraction_artifacts": {"primary": {"code": 3}}, "missing_content": {"primary": {"code": 1}}}},
+    {"text": "", "quality_signals": {"fasttext": {"dclm": 0.1, "fineweb_edu_approx": 0.1, "eai_web_code": 0.1,
+                                                   "eai_general_math": 0.1, "english": 0.5}},
+     "eai_taxonomy": {"extraction_artifacts": {"primary": {"code": 0}}, "missing_content": {"primary": {"code": 0}}}},
+    {"text": "beta", "quality_signals": {"fasttext": {"dclm": None, "fineweb_edu_approx": 0.4, "eai_web_code": 0.9,
+                                                       "eai_general_math": 0.0, "english": 0.8}},
+     "eai_taxonomy": {"extraction_artifacts": {"primary": {"code": 99}}, "missing_content": {"primary": {"code": None}}}},
+  ])
+  got = list(L.TableLabels(eai, L.EAI_FIELDS, "code", max_ctx=16))
+  assert len(got) == 2 and got[0].domain == "code"                            # the empty text is skipped
+  assert len(got[0].text) == 64                                               # 16 tokens x 4 characters
+  assert got[0].signals["fasttext_dclm"] == 0.7 and got[0].classes == {"extraction_artifacts": 3, "missing_content": 1}
+  assert "fasttext_dclm" not in got[1].signals and got[1].classes == {}       # null and out-of-range stay unset
+  t = L.probe_targets(got)
+  assert torch.isnan(t["fasttext_dclm"][1]) and t["extraction_artifacts"].tolist() == [3, -1] and t["domain"].tolist() == [1, 1]
+
+  # graded rows (JSON lines work like parquet), filtered by the language score
+  rnd = random.Random(0)
+  fw = tmp_path / "fw.jsonl"
+  with open(fw, "w") as f:
+    for i in range(600):
+      f.write(json.dumps({"text": f"doc {i}", "language_score": 0.95 if i % 10 else 0.3, "int_score": rnd.choice([0, 1, 2, 3, 4, 5]),
+                          "token_count": rnd.choice([100, 300, 700, 1500, 3000])}) + "\n")
+  src = L.TableLabels(str(tmp_path / "fw.*"), L.FINEWEB_EDU_FIELDS)
+  rows = list(src)
+  assert len(rows) == 540 and all(r.signals["lang_score"] >= 0.9 for r in rows)
+  assert [L.length_bucket(n) for n in (None, 0, 255, 256, 1024, 2047, 2048, 10 ** 6)] == [2, 0, 0, 1, 3, 3, 4, 4]
+  ps = L.GradedPairs(src, seed=1)
+  pairs = ps.next_pairs(50)
+  assert len(pairs) == 50 and ps.relaxed == 0
+  for hi, lo in pairs:
+    assert hi.grade - lo.grade >= 2 and L.length_bucket(hi.n_tokens) == L.length_bucket(lo.n_tokens)
+  assert {L.length_bucket(hi.n_tokens) for hi, _ in pairs} == {0, 1, 2, 3, 4}
+  assert [(a.text, b.text) for a, b in L.GradedPairs(src, seed=1).next_pairs(50)] == [(a.text, b.text) for a, b in pairs]
+  # only adjacent grades available: relaxed pairs are issued, but held to the allowed share
+  near = [L.Labelled(text=f"n{i}", grade=2 + i % 2, n_tokens=100) for i in range(40)]
+  ps2 = L.GradedPairs(near, max_relaxed_frac=1.0, seed=0)
+  assert all(hi.grade - lo.grade == 1 for hi, lo in ps2.next_pairs(10)) and ps2.relaxed == 10
+  import pytest
+  with pytest.raises(RuntimeError):
+    L.GradedPairs([L.Labelled(text="x", grade=3, n_tokens=10)] * 4, seed=0).next_pairs(1)
+  # reservoir: a cell holds at most cell_cap documents and later arrivals do get in
+  ps3 = L.GradedPairs([], cell_cap=8, seed=0)
+  for i in range(400):
+    ps3.add(L.Labelled(text=str(i), grade=1, n_tokens=10))
+  kept = [int(s.text) for s in ps3.cells[0][1]]
+  assert len(kept) == 8 and max(kept) >= 8 and ps3.arrived[0][1] == 400
+
+  # oracle labels over shard references
+  docs = _tiny_dataset(tmp_path / "data")
+  refs = list(D.enumerate_refs(tmp_path / "data", "web"))
+  lab = tmp_path / "oracle.jsonl"
+  with open(lab, "w") as f:
+    for i, r in enumerate(refs[:10]):
+      f.write(json.dumps({"doc_id": str(r), "ok": True, "scores": {d: (i + k) % 5 for k, d in enumerate(L.RUBRIC)}}) + "\n")
+    f.write(json.dumps({"doc_id": str(refs[10]), "scores": {"helpfulness": 3}}) + "\n")          # incomplete
+    f.write(json.dumps({"doc_id": "web//web/v1/missing.npy#s=0:e=4", "scores": {d: 1 for d in L.RUBRIC}}) + "\n")
+    f.write(json.dumps({"doc_id": str(refs[11]), "ok": False, "scores": {d: 1 for d in L.RUBRIC}}) + "\n")
+  orc = L.OracleLabels(lab, tmp_path / "data", max_ctx=32, eos_token_id=255)
+  labelled = list(orc)
+  assert len(labelled) == 10 and orc.skipped == 3
+  assert labelled[0].tokens == docs[0][:32] and labelled[3].rubric == (3.0, 4.0, 0.0, 1.0, 2.0)
+
+  # batches in the shape train_heads reads
+  enc = lambda s: list(s.encode())
+  b = next(L.probe_batches(L.mix([L.TableLabels(eai, L.EAI_FIELDS, "web")]), 4, enc, 16))
+  assert len(b["docs"]) == 4 and "gate" not in b["targets"] and b["targets"]["lang_score"].shape == (4,)
+  jb = next(L.judge_batches(orc, 6, enc, 32, pairs=ps, pairs_per_batch=3))
+  assert len(jb["docs"]) == 12 and jb["rubric"].shape == (12, 5) and jb["pairs"].tolist() == [[6, 7], [8, 9], [10, 11]]
+  assert torch.isfinite(jb["rubric"][:6]).all() and torch.isnan(jb["rubric"][6:]).all()
+
+
+def test_cli_docids_grade_from_shards_with_resume_and_train_from_labels(tmp_path):
+  import json
+  from nmoe_b200.data.cli import main
+  from nmoe_b200.data import docid as D
+  from nmoe_b200.serve.checkpoint import save_model
+  m = backbone()
+  ck = tmp_path / "ckpt"
+  save_model(m, str(ck))
+  root = tmp_path / "data"
+  _tiny_dataset(root)
+  refs_file = tmp_path / "refs.jsonl"
+  assert main(["docids", "--data-root", str(root), "--source", "web", "--output", str(refs_file)]) == 0
+  refs = list(D.read_refs(refs_file))
+  assert len(refs) == 40
+  heads = tmp_path / "heads"
+  H.save_heads(str(heads), H.ProbeHead(32), H.JudgeHead(32))
+  H.Calibration(tau_drop=-1.0, tau_keep=2.0).save(str(heads))
+  out = tmp_path / "graded.jsonl"
+  base = ["--checkpoint", str(ck), "--tokenizer", "bytes", "--max-ctx", "64", "--batch-size", "8", "--heads", str(heads)]
+  grade = ["hydra-grade", *base, "--input-docids", str(refs_file), "--data-root", str(root), "--output", str(out)]
+  assert main([*grade, "--max-documents", "15"]) == 0
+  first = [json.loads(l) for l in open(out)]
+  assert [r["doc_id"] for r in first] == [str(r) for r in refs[:15]]
+  with open(out, "a") as f:
+    f.write('{"doc_id": "web//cut')                    # a line cut by a crash
+  out.write_text(out.read_text().rsplit("\n", 1)[0] + "\n")      # (dropped again: the file must stay line-parseable)
+  assert main([*grade, "--resume"]) == 0
+  rows = [json.loads(l) for l in open(out)]
+  assert [r["doc_id"] for r in rows] == [str(r) for r in refs] and rows[:15] == first
+
+  # training from label tables and oracle labels over the same shards
+  fw = tmp_path / "fw.jsonl"
+  with open(fw, "w") as f:
+    for i in range(120):
+      f.write(json.dumps({"text": "word " * (5 + i % 7), "language_score": 0.97, "int_score": i % 6, "token_count": 100 + i}) + "\n")
+  lab = tmp_path / "oracle.jsonl"
+  with open(lab, "w") as f:
+    for i, r in enumerate(refs):
+      f.write(json.dumps({"doc_id": str(r), "scores": {d: i % 5 for d in H.RUBRIC}}) + "\n")
+  train = ["hydra-train", *base, "--steps", "6", "--lr", "0.01", "--labels", f"fineweb_edu:web:{fw}"]
+  assert main([*train, "--phase", "A"]) == 0
+  assert main([*train, "--phase", "B", "--oracle-labels", str(lab), "--data-root", str(root), "--pairs-per-batch", "2"]) == 0
+  assert main([*train, "--phase", "C"]) == 0
