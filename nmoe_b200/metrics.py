@@ -290,10 +290,8 @@ def log_training_step(ms: MetricsSession, step: int, trainer, loss: torch.Tensor
               ("router_agg/dead_experts", sum(cfg.n_routed_experts - s["experts_active"] for s in stats))]
     rs_line = f" | router: cv {agg_cv:.3f} max {agg_max:.4f} bias[{bmin:+.4f},{bmax:+.4f}]"
   if ms.gpu is not None:
-    for i, g in enumerate(ms.gpu.snapshot()):
-      for k, v in g.items():
-        if isinstance(v, (int, float)):
-          items.append((f"gpu/{i}/{k}", float(v)))
+    from .utils.gpu_telemetry import dashboard_items
+    items += dashboard_items(ms.gpu.snapshot())
   ms.insert_many(step, items)
   gn_s = f"{gn.item():.3f}" if gn is not None else "-"
   print_fn(f"step {step:>6} loss {lv.item():.4f} grad_norm {gn_s} memory {mem_max:.1f}GiB tps {tps:,.0f} "

@@ -2,18 +2,30 @@
 
   python -m nmoe_b200.viz.server --metrics-dir /data/metrics --experiments-db /data/experiments.db --port 3000
 
-Endpoints (same contract as the reference dashboard, nviz/app/api/*/route.ts):
+Endpoints.  Paths, query parameters and the JSON keys named here are those of the reference dashboard's routes
+(nviz/app/api/*/route.ts, client types in nviz/lib/api.ts), so a front end written against one works with the other:
 
-  GET /api/health
-  GET /api/runs                                   -> [{run, ranks, last_step, last_ts_ms}]
-  GET /api/series?run=R&tag=T[&points=N][&rank=r] -> {run, tag, points:[[step,value],...]}  (LTTB down-sampled, <= N, default 1000)
-  GET /api/summary?run=R                          -> latest value of every non-per-rank tag
-  GET /api/gpu?run=R                              -> latest gpu/{i}/* telemetry grouped by GPU index
-  GET /api/router?run=R                           -> latest router/layer_NN/* and router_agg/* grouped by layer
-  GET /api/experiments                            -> experiments with their runs (config, git hash, status, results)
+  GET /api/health                                 -> {ok, runs}
+  GET /api/runs                                   -> {runs: [{run, last_ts, last_step, ranks, status?, experiment_id?,
+                                                     started_at?, ended_at?}]}: metric files merged with the
+                                                     experiments DB (a run known only to the DB has last_step 0),
+                                                     newest first
+  GET /api/tags?run=R                             -> {run, tags: [...]}
+  GET /api/series?run=R&tag=T[&points=N][&rank=r] -> {run, tag, series: [{step, ts_ms, value}]}  (LTTB, <= N, default 1000)
+  GET /api/summary?run=R                          -> {run, summary: {tag: latest value}, steps: {tag: step}} without
+                                                     per-rank timers, per-GPU and per-layer tags
+  GET /api/gpu?run=R                              -> {run, gpus: [{index, <metric>: value}], agg: {"gpu_agg/*": value}}
+  GET /api/router?run=R                           -> {run, layers: [{idx, cv, entropy, max_load, bias_range,
+                                                     experts_active}], agg: {"router_agg/*": value}}
+  GET /api/experiments                            -> {experiments: [{id, name, project, description, created_at,
+                                                     runs_total, runs_running, runs_completed, runs_failed,
+                                                     runs_killed, last_started_at}]}
+  GET /api/experiments/runs[?experiment_id=E][&limit=N] -> {runs: [run row + last_ts, last_step]}
+  GET /api/experiments/run?run=R                  -> {run: row} or 404
   GET /api/datasets[/preview|/meta|/manifest|/shard/stats|/shard/window|/index/header|/index/doc|/pipeline]?path=P
                                                   -> read-only dataset browser confined to NVIZ_DATASETS_DIR (viz/datasets.py)
-  GET /                                           -> a single static page that plots a tag of a run
+  GET /, /static/*                                -> the dashboard page (viz/static/): runs, charts with run comparison,
+                                                     GPU monitor, router heat map, experiments table, dataset browser
 
 All ``rank_*.duckdb`` / ``rank_*.sqlite`` files of a run are opened read-only and merged; when a
 (tag, step) appears in several rank files the newest ``ts_ms`` wins (the reference does the same
@@ -112,9 +124,23 @@ class MetricStore:
     return best
 
   def series(self, run: str, tag: str, points: int = 1000, rank: Optional[int] = None) -> List[Point]:
+    return [(s, v) for s, _, v in self.series_ts(run, tag, points, rank)]
+
+  def series_ts(self, run: str, tag: str, points: int = 1000, rank: Optional[int] = None) -> List[Tuple[int, int, float]]:
+    """(step, ts_ms, value) of a tag, down-sampled on (step, value)."""
     m = self._merged(run, "tag = ?", (tag,), rank)
+    ts = {step: t for (_, step), (t, _) in m.items()}
     pts = sorted((step, v) for (_, step), (_, v) in m.items())
-    return lttb(pts, points)
+    return [(s, ts[s], v) for s, v in lttb(pts, points)]
+
+  def tags(self, run: str) -> List[str]:
+    out = set()
+    for f in self._files(run):
+      try:
+        out.update(r[0] for r in self._query(f, "SELECT DISTINCT tag FROM metrics WHERE run = ?", (run,)))
+      except (sqlite3.Error, ImportError):
+        continue
+    return sorted(out)
 
   def latest(self, run: str, like: str) -> Dict[str, Tuple[int, float]]:
     """tag -> (step, value) at each tag's last step, for tags matching the SQL LIKE pattern."""
@@ -136,95 +162,157 @@ class MetricStore:
       if rows and rows[0][0] is not None:
         last_step = max(last_step, int(rows[0][0]))
         last_ts = max(last_ts, int(rows[0][1]))
-    return {"run": run, "ranks": len(files), "last_step": last_step, "last_ts_ms": last_ts}
+    return {"run": run, "ranks": len(files), "last_step": max(last_step, 0), "last_ts": last_ts}
 
 
-def group_gpu(latest: Dict[str, Tuple[int, float]]) -> Dict[str, Dict[str, float]]:
-  out: Dict[str, Dict[str, float]] = {}
+def group_gpu(latest: Dict[str, Tuple[int, float]]) -> Tuple[List[dict], Dict[str, float]]:
+  """Latest ``gpu/{i}/{metric}`` values as one record per GPU index, and the ``gpu_agg/*`` values by full tag."""
+  by_idx: Dict[int, dict] = {}
+  agg: Dict[str, float] = {}
   for tag, (_, v) in latest.items():
-    m = re.fullmatch(r"gpu/(\d+)/(.+)", tag)
+    m = re.fullmatch(r"gpu/(\d+)/(\w+)", tag)
     if m:
-      out.setdefault(m.group(1), {})[m.group(2)] = v
-  return out
+      by_idx.setdefault(int(m.group(1)), {"index": int(m.group(1))})[m.group(2)] = v
+    elif tag.startswith("gpu_agg/"):
+      agg[tag] = v
+  return [by_idx[i] for i in sorted(by_idx)], agg
 
 
-def group_router(latest: Dict[str, Tuple[int, float]]) -> Dict[str, Dict[str, float]]:
-  out: Dict[str, Dict[str, float]] = {}
+def group_router(latest: Dict[str, Tuple[int, float]]) -> Tuple[List[dict], Dict[str, float]]:
+  """Latest ``router/layer_NN/{metric}`` values as one record per layer, and the ``router_agg/*`` values by full tag."""
+  by_idx: Dict[int, dict] = {}
+  agg: Dict[str, float] = {}
   for tag, (_, v) in latest.items():
-    m = re.fullmatch(r"router/layer_(\d+)/(.+)", tag)
+    m = re.fullmatch(r"router/layer_(\d+)/(\w+)", tag)
     if m:
-      out.setdefault(f"layer_{m.group(1)}", {})[m.group(2)] = v
+      by_idx.setdefault(int(m.group(1)), {"idx": int(m.group(1))})[m.group(2)] = v
     elif tag.startswith("router_agg/"):
-      out.setdefault("agg", {})[tag.split("/", 1)[1]] = v
-  return out
+      agg[tag] = v
+  return [by_idx[i] for i in sorted(by_idx)], agg
 
 
-def experiments(db_path: Optional[str]) -> List[dict]:
-  if not db_path or not Path(db_path).exists():
-    return []
-  con = sqlite3.connect(f"file:{db_path}?mode=ro", uri=True, timeout=5.0)
-  con.row_factory = sqlite3.Row
-  try:
-    exps = [dict(r) for r in con.execute("SELECT * FROM experiments ORDER BY created_at DESC")]
+class ExperimentsView:
+  """Read-only queries on the experiments database (nviz/lib/server/experiments.ts:106-290).  Every call opens the
+  file afresh in read-only mode, so a training job that is writing to it is never blocked; a missing or unreadable
+  database reads as empty."""
+
+  RUN_COLS = ("id", "experiment_id", "status", "started_at", "ended_at", "git_hash", "git_dirty", "config_json", "results_json")
+
+  def __init__(self, db_path: Optional[str]):
+    self.path = db_path
+
+  def _rows(self, sql: str, args: Tuple = ()) -> List[sqlite3.Row]:
+    if not self.path or not Path(self.path).exists():
+      return []
+    try:
+      con = sqlite3.connect(f"file:{self.path}?mode=ro", uri=True, timeout=5.0)
+    except sqlite3.Error:
+      return []
+    con.row_factory = sqlite3.Row
+    try:
+      return con.execute(sql, args).fetchall()
+    except sqlite3.Error:
+      return []
+    finally:
+      con.close()
+
+  def _run_row(self, r: sqlite3.Row) -> dict:
+    d = {k: r[k] for k in self.RUN_COLS}
+    d["run"] = d.pop("id")
+    return d
+
+  def run_states(self) -> List[dict]:
+    return [{"run": r["id"], "experiment_id": r["experiment_id"], "status": r["status"], "started_at": r["started_at"],
+             "ended_at": r["ended_at"]} for r in self._rows("SELECT id, experiment_id, status, started_at, ended_at FROM runs")]
+
+  def summaries(self) -> List[dict]:
+    exps = self._rows("SELECT * FROM experiments ORDER BY created_at DESC, id")
+    out = []
     for e in exps:
-      runs = [dict(r) for r in con.execute("SELECT * FROM runs WHERE experiment_id = ? ORDER BY started_at DESC", (e["id"],))]
-      for r in runs:
-        for k in ("config_json", "results_json"):
-          if r.get(k):
-            try:
-              r[k[:-5]] = json.loads(r.pop(k))
-            except ValueError:
-              pass
-      e["runs"] = runs
-    return exps
-  except sqlite3.Error:
-    return []
-  finally:
-    con.close()
+      keys = e.keys()
+      d = {"id": e["id"], "name": e["name"] if "name" in keys else e["id"], "project": e["project"] if "project" in keys else "default",
+           "description": e["description"], "created_at": e["created_at"]}
+      counts = {r["status"]: r["n"] for r in self._rows("SELECT status, COUNT(*) AS n FROM runs WHERE experiment_id = ? GROUP BY status", (e["id"],))}
+      d["runs_total"] = sum(counts.values())
+      for st in ("running", "completed", "failed", "killed"):
+        d[f"runs_{st}"] = counts.get(st, 0)
+      last = self._rows("SELECT MAX(started_at) AS t FROM runs WHERE experiment_id = ?", (e["id"],))
+      d["last_started_at"] = last[0]["t"] if last else None
+      out.append(d)
+    return out
+
+  def runs(self, experiment_id: Optional[str] = None, limit: int = 200) -> List[dict]:
+    limit = max(1, min(int(limit), 2000))
+    cols = ", ".join(self.RUN_COLS)
+    if experiment_id:
+      rows = self._rows(f"SELECT {cols} FROM runs WHERE experiment_id = ? ORDER BY started_at DESC, id LIMIT ?", (experiment_id, limit))
+    else:
+      rows = self._rows(f"SELECT {cols} FROM runs ORDER BY started_at DESC, id LIMIT ?", (limit,))
+    return [self._run_row(r) for r in rows]
+
+  def run(self, run_id: str) -> Optional[dict]:
+    rows = self._rows(f"SELECT {', '.join(self.RUN_COLS)} FROM runs WHERE id = ?", (run_id,))
+    return self._run_row(rows[0]) if rows else None
 
 
-_PAGE = """<!doctype html><meta charset=utf-8><title>nmoe_b200 runs</title>
-<style>body{font:14px system-ui;margin:2em;max-width:1100px}select,input{font:inherit;margin-right:1em}canvas{border:1px solid #ccc;width:100%;height:420px}</style>
-<h2>Training runs</h2><div><select id=run></select><input id=tag value="train/loss" size=32><button onclick=draw()>plot</button></div>
-<canvas id=c width=1100 height=420></canvas><pre id=sum></pre>
-<script>
-async function j(u){return (await fetch(u)).json()}
-async function init(){const r=await j('/api/runs');run.innerHTML=r.map(x=>`<option>${x.run}</option>`).join('');draw()}
-async function draw(){if(!run.value)return;const s=await j(`/api/series?run=${run.value}&tag=${encodeURIComponent(tag.value)}&points=800`);
-const p=s.points,g=c.getContext('2d');g.clearRect(0,0,c.width,c.height);if(!p.length)return;
-const xs=p.map(a=>a[0]),ys=p.map(a=>a[1]),x0=Math.min(...xs),x1=Math.max(...xs),y0=Math.min(...ys),y1=Math.max(...ys);
-g.beginPath();p.forEach((a,i)=>{const x=20+(a[0]-x0)/(x1-x0||1)*(c.width-40),y=c.height-20-(a[1]-y0)/(y1-y0||1)*(c.height-40);i?g.lineTo(x,y):g.moveTo(x,y)});g.stroke();
-g.fillText(`${tag.value}: ${y0.toPrecision(4)} .. ${y1.toPrecision(4)}  steps ${x0}..${x1}`,24,14);
-sum.textContent=JSON.stringify(await j(`/api/summary?run=${run.value}`),null,1)}
-init()</script>"""
+def merged_runs(store: MetricStore, exps: ExperimentsView) -> List[dict]:
+  """Runs that have metric files, joined with the runs the experiments database knows (nviz/app/api/runs/route.ts:5-43);
+  newest activity first, then newest start, then highest step, then name."""
+  by_id: Dict[str, dict] = {r: store.run_info(r) for r in store.runs()}
+  for st in exps.run_states():
+    cur = by_id.setdefault(st["run"], {"run": st["run"], "ranks": 0, "last_ts": 0, "last_step": 0})
+    cur.update({k: st[k] for k in ("experiment_id", "status", "started_at", "ended_at")})
+  runs = list(by_id.values())
+  runs.sort(key=lambda r: r["run"])
+  runs.sort(key=lambda r: (r.get("last_ts") or 0, str(r.get("started_at") or ""), r.get("last_step") or 0), reverse=True)
+  return runs
+
+
+STATIC_DIR = Path(__file__).resolve().parent / "static"
+_CTYPES = {".html": "text/html; charset=utf-8", ".js": "text/javascript; charset=utf-8", ".css": "text/css; charset=utf-8",
+           ".svg": "image/svg+xml", ".json": "application/json"}
+
+
+def static_file(rel: str) -> Optional[Tuple[bytes, str]]:
+  """A file of the dashboard page; names are matched against the directory listing, so no path can leave it."""
+  name = rel.strip("/") or "index.html"
+  for f in STATIC_DIR.iterdir() if STATIC_DIR.is_dir() else ():
+    if f.is_file() and f.name == name and f.suffix in _CTYPES:
+      return f.read_bytes(), _CTYPES[f.suffix]
+  return None
 
 
 def make_handler(store: MetricStore, exp_db: Optional[str]):
+  exps = ExperimentsView(exp_db)
+
   class Handler(BaseHTTPRequestHandler):
     def log_message(self, fmt, *args):   # quiet
       pass
 
     def _send(self, code: int, body, ctype: str = "application/json") -> None:
-      data = body.encode() if isinstance(body, str) else json.dumps(body).encode()
+      data = body if isinstance(body, bytes) else body.encode() if isinstance(body, str) else json.dumps(body).encode()
       self.send_response(code)
       self.send_header("Content-Type", ctype)
+      self.send_header("Cache-Control", "private, max-age=2")
       self.send_header("Content-Length", str(len(data)))
       self.end_headers()
       self.wfile.write(data)
 
     def _datasets(self, what: str, q: Dict[str, str]):
-      """Read-only dataset browser (viz/datasets.py); every path is confined to NVIZ_DATASETS_DIR."""
+      """Read-only dataset browser (viz/datasets.py); every path is confined to NVIZ_DATASETS_DIR.  Query parameters
+      take the names of the reference's routes (``max_bytes``, ``limit_shards``, ``shard_path`` / ``doc_idx`` /
+      ``max_tokens``) as well as the shorter ones this server started with."""
       from . import datasets as D
       path = q.get("path", "")
       try:
         if what == "":
           return self._send(200, D.list_dir(path))
         if what == "preview":
-          return self._send(200, D.preview_file(path, int(q.get("bytes", str(64 * 1024)))))
+          return self._send(200, D.preview_file(path, int(q.get("max_bytes", q.get("bytes", str(64 * 1024))))))
         if what == "meta":
           return self._send(200, D.meta(path))
         if what == "manifest":
-          return self._send(200, D.manifest_preview(path, int(q.get("limit", "200"))))
+          return self._send(200, D.manifest_preview(path, int(q.get("limit_shards", q.get("limit", "200")))))
         if what == "shard/stats":
           return self._send(200, D.shard_stats(path))
         if what == "shard/window":
@@ -233,7 +321,10 @@ def make_handler(store: MetricStore, exp_db: Optional[str]):
         if what == "index/header":
           return self._send(200, D.index_header(path))
         if what == "index/doc":
-          return self._send(200, D.index_doc(path, int(q.get("doc", "0")), q.get("tokenizer")))
+          if not path and q.get("shard_path"):      # the document may be named by its shard instead of its index file
+            path = re.sub(r"\.npy$", ".idx", q["shard_path"])
+          return self._send(200, D.index_doc(path, int(q.get("doc_idx", q.get("doc", "0"))), q.get("tokenizer"),
+                                             int(q.get("max_tokens", "8192"))))
         if what == "pipeline":
           return self._send(200, D.pipeline_inspect(path))
         return self._send(404, {"error": "not found"})
@@ -246,36 +337,55 @@ def make_handler(store: MetricStore, exp_db: Optional[str]):
       u = urlparse(self.path)
       q = {k: v[0] for k, v in parse_qs(u.query).items()}
       try:
-        if u.path == "/":
-          return self._send(200, _PAGE, "text/html; charset=utf-8")
+        if u.path == "/" or u.path.startswith("/static/"):
+          hit = static_file("" if u.path == "/" else u.path[len("/static/"):])
+          if hit is None:
+            return self._send(404, {"error": "not found"})
+          return self._send(200, hit[0], hit[1])
         if u.path == "/api/health":
           return self._send(200, {"ok": True, "runs": len(store.runs())})
         if u.path == "/api/runs":
-          return self._send(200, [store.run_info(r) for r in store.runs()])
+          return self._send(200, {"runs": merged_runs(store, exps)})
         if u.path == "/api/experiments":
-          return self._send(200, experiments(exp_db))
+          return self._send(200, {"experiments": exps.summaries()})
+        if u.path == "/api/experiments/runs":
+          info = {r: store.run_info(r) for r in store.runs()}
+          rows = exps.runs(q.get("experiment_id") or None, int(q.get("limit", "200")))
+          for r in rows:
+            m = info.get(r["run"], {})
+            r["last_ts"], r["last_step"] = m.get("last_ts", 0), m.get("last_step", 0)
+          return self._send(200, {"runs": rows})
+        if u.path == "/api/experiments/run":
+          if not q.get("run"):
+            return self._send(400, {"error": "Missing 'run'"})
+          row = exps.run(q["run"])
+          return self._send(200, {"run": row}) if row else self._send(404, {"error": "Not found"})
         if u.path == "/api/datasets" or u.path.startswith("/api/datasets/"):
           return self._datasets(u.path[len("/api/datasets"):].strip("/"), q)
         run = q.get("run", "")
+        if u.path.startswith("/api/") and not run:
+          return self._send(400, {"error": "Missing 'run'"})
         if u.path.startswith("/api/") and run not in store.runs():
           return self._send(404, {"error": f"unknown run {run!r}"})
+        if u.path == "/api/tags":
+          return self._send(200, {"run": run, "tags": store.tags(run)})
         if u.path == "/api/series":
           if "tag" not in q:
-            return self._send(400, {"error": "tag is required"})
+            return self._send(400, {"error": "Missing 'run' or 'tag'"})
           n = max(3, min(int(q.get("points", "1000")), 5000))
           rank = int(q["rank"]) if "rank" in q else None
-          pts = store.series(run, q["tag"], n, rank)
-          return self._send(200, {"run": run, "tag": q["tag"], "points": [[s, v] for s, v in pts]})
+          pts = store.series_ts(run, q["tag"], n, rank)
+          return self._send(200, {"run": run, "tag": q["tag"], "series": [{"step": s, "ts_ms": t, "value": v} for s, t, v in pts]})
         if u.path == "/api/summary":
-          lat = store.latest(run, "%")
-          keep = {t: {"step": s, "value": v} for t, (s, v) in sorted(lat.items())
-                  if not t.startswith(("time_ms/", "gpu/", "router/layer_"))}
-          return self._send(200, {"run": run, "latest": keep})
+          lat = {t: sv for t, sv in sorted(store.latest(run, "%").items())
+                 if not t.startswith(("time_ms/", "gpu/", "router/layer_"))}
+          return self._send(200, {"run": run, "summary": {t: v for t, (_, v) in lat.items()}, "steps": {t: s for t, (s, _) in lat.items()}})
         if u.path == "/api/gpu":
-          return self._send(200, {"run": run, "gpus": group_gpu(store.latest(run, "gpu/%"))})
+          gpus, agg = group_gpu(store.latest(run, "gpu%"))
+          return self._send(200, {"run": run, "gpus": gpus, "agg": agg})
         if u.path == "/api/router":
-          lat = store.latest(run, "router%")
-          return self._send(200, {"run": run, "router": group_router(lat)})
+          layers, agg = group_router(store.latest(run, "router%"))
+          return self._send(200, {"run": run, "layers": layers, "agg": agg})
         return self._send(404, {"error": "not found"})
       except (ValueError, OSError) as e:
         return self._send(400, {"error": str(e)})

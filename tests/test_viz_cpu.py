@@ -1,6 +1,7 @@
 """Dashboard service: merged rank files, LTTB down-sampling, endpoint contract."""
 import json
 import threading
+import urllib.error
 import urllib.request
 
 from nmoe_b200.metrics import MetricsWriter
@@ -37,17 +38,27 @@ def test_endpoints_over_two_rank_files(tmp_path):
   t.start()
   try:
     assert _get(port, "/api/health")["ok"]
-    runs = _get(port, "/api/runs")
-    assert runs[0]["run"] == "runA" and runs[0]["ranks"] == 2 and runs[0]["last_step"] == 299
+    runs = _get(port, "/api/runs")["runs"]
+    assert runs[0]["run"] == "runA" and runs[0]["ranks"] == 2 and runs[0]["last_step"] == 299 and runs[0]["last_ts"] > 0
     s = _get(port, "/api/series?run=runA&tag=train/loss&points=50")
-    assert len(s["points"]) == 50 and s["points"][0] == [0, 10.0]
-    summ = _get(port, "/api/summary?run=runA")["latest"]
-    assert "train/loss" in summ and not any(k.startswith("time_ms/") for k in summ)
-    gpus = _get(port, "/api/gpu?run=runA")["gpus"]
-    assert set(gpus) == {"0", "1"} and gpus["1"]["power_w"] == 710.0
-    router = _get(port, "/api/router?run=runA")["router"]
-    assert router["layer_01"]["cv"] == 0.1 and router["agg"]["mean_cv"] == 0.2
-    assert _get(port, "/api/experiments") == []
+    assert len(s["series"]) == 50 and s["series"][0]["step"] == 0 and s["series"][0]["value"] == 10.0 and s["series"][0]["ts_ms"] > 0
+    tags = _get(port, "/api/tags?run=runA")["tags"]
+    assert "train/loss" in tags and "gpu/1/power_w" in tags
+    summ = _get(port, "/api/summary?run=runA")
+    assert summ["summary"]["train/loss"] == 10.0 - 299 * 0.01 and summ["steps"]["train/loss"] == 299
+    assert not any(k.startswith(("time_ms/", "gpu/")) for k in summ["summary"])
+    g = _get(port, "/api/gpu?run=runA")
+    assert [x["index"] for x in g["gpus"]] == [0, 1] and g["gpus"][1]["power_w"] == 710.0 and g["agg"] == {}
+    router = _get(port, "/api/router?run=runA")
+    assert router["layers"] == [{"idx": 1, "cv": 0.1}] and router["agg"] == {"router_agg/mean_cv": 0.2}
+    assert _get(port, "/api/experiments") == {"experiments": []}
+    assert _get(port, "/api/experiments/runs") == {"runs": []}
+    for path, code in (("/api/series?run=runA", 400), ("/api/summary", 400), ("/api/summary?run=nope", 404), ("/api/experiments/run?run=runA", 404)):
+      try:
+        _get(port, path)
+        raise AssertionError(path)
+      except urllib.error.HTTPError as e:
+        assert e.code == code, (path, e.code)
   finally:
     srv.shutdown()
     srv.server_close()
@@ -100,3 +111,188 @@ def test_dataset_browser_routes(tmp_path, monkeypatch):
         assert e.code == 400
   finally:
     srv.shutdown()
+
+
+def test_runs_merge_with_the_experiments_database_and_its_routes(tmp_path):
+  """The reference dashboard's contract (nviz/tests/api.runs.contract.test.ts, api.experiments.contract.test.ts): a run
+  with metric files takes its status from the experiments database; a run known only to the database is listed with
+  last_step 0 and last_ts 0; experiment summaries count runs by status."""
+  import types
+  from nmoe_b200.experiments import ExperimentTracker
+  w = MetricsWriter("runA", str(tmp_path / "metrics"), 0)
+  w.insert_many(1, [("train/loss", 10.0)])
+  w.insert_many(2, [("train/loss", 8.0)])
+  w.close()
+  db = tmp_path / "experiments.db"
+  cfg = types.SimpleNamespace(experiment_id="exp1", experiments_db=str(db), lr=0.1)
+  tr = ExperimentTracker(cfg)
+  assert tr.start_run("runA") == "runA" and tr.start_run("runB") == "runB" and tr.start_run("runC") == "runC"
+  tr.update_results("runA", {"eval_loss": 3.5})
+  tr.end_run("runB", "completed", {"final_loss": 2.5, "steps_completed": 7})
+  tr.end_run("runC", "failed")
+  assert tr.get_run("runB").status == "completed" and tr.get_run("runB")["ended_at"] and tr.get_run("nope") is None
+  assert [r.id for r in tr.list_runs("exp1", status="running")] == ["runA"] and len(tr.list_runs("exp1")) == 3
+  assert tr.get_experiment("exp1").project == "default" and [e.id for e in tr.list_experiments()] == ["exp1"]
+  tr.start_run("runC")                                   # a resumed job re-opens its row
+  assert tr.get_run("runC").status == "running" and tr.get_run("runC").ended_at is None
+  tr.end_run("runC", "killed")
+  made = tr.create_experiment("sweep", "moe", "lr sweep")
+  assert made.startswith("moe_sweep_") and tr.get_experiment(made).description == "lr sweep"
+  tr.close()
+  srv = serve(str(tmp_path / "metrics"), str(db), port=0)
+  port = srv.server_address[1]
+  threading.Thread(target=srv.serve_forever, daemon=True).start()
+  try:
+    runs = {r["run"]: r for r in _get(port, "/api/runs")["runs"]}
+    assert runs["runA"]["status"] == "running" and runs["runA"]["last_step"] == 2 and runs["runA"]["experiment_id"] == "exp1"
+    assert runs["runB"]["status"] == "completed" and runs["runB"]["last_step"] == 0 and runs["runB"]["last_ts"] == 0
+    assert list(runs)[0] == "runA"                       # newest metric activity first
+    exps = {e["id"]: e for e in _get(port, "/api/experiments")["experiments"]}
+    e = exps["exp1"]
+    assert (e["runs_total"], e["runs_running"], e["runs_completed"], e["runs_failed"], e["runs_killed"]) == (3, 1, 1, 0, 1)
+    assert e["name"] == "exp1" and e["project"] == "default" and e["last_started_at"] and exps[made]["runs_total"] == 0
+    rows = _get(port, "/api/experiments/runs?experiment_id=exp1&limit=2")["runs"]
+    assert len(rows) == 2 and {"run", "experiment_id", "status", "started_at", "ended_at", "git_hash", "git_dirty", "config_json",
+                               "results_json", "last_ts", "last_step"} <= set(rows[0])
+    one = _get(port, "/api/experiments/run?run=runB")["run"]
+    assert one["status"] == "completed" and json.loads(one["results_json"])["steps_completed"] == 7 and json.loads(one["config_json"])["lr"] == 0.1
+  finally:
+    srv.shutdown()
+    srv.server_close()
+
+
+def test_experiments_database_of_the_earlier_layout_is_upgraded(tmp_path):
+  import sqlite3
+  import types
+  from nmoe_b200.experiments import ExperimentTracker
+  db = tmp_path / "old.db"
+  con = sqlite3.connect(db)
+  con.executescript(
+    "CREATE TABLE experiments (id TEXT PRIMARY KEY, created_at REAL, description TEXT);"
+    "CREATE TABLE runs (id TEXT PRIMARY KEY, experiment_id TEXT, config_json TEXT, git_hash TEXT, git_dirty INTEGER,"
+    " started_at REAL, ended_at REAL, status TEXT, results_json TEXT);"
+    "INSERT INTO experiments VALUES ('old', 1700000000.0, '');"
+    "INSERT INTO runs VALUES ('r0', 'old', '{}', 'abc', 0, 1700000000.0, 1700003600.0, 'completed', NULL);")
+  con.commit(); con.close()
+  tr = ExperimentTracker(types.SimpleNamespace(experiment_id="old", experiments_db=str(db)))
+  assert tr.get_experiment("old").name == "old" and tr.get_experiment("old").created_at == "2023-11-14 22:13:20"
+  r = tr.get_run("r0")
+  assert r.started_at == "2023-11-14 22:13:20" and r.ended_at == "2023-11-14 23:13:20"
+  tr.start_run("r1")
+  assert [x.id for x in tr.list_runs("old")] == ["r1", "r0"]
+  tr.close()
+
+
+def _js_balance(src):
+  """A structural check of a script without a JavaScript engine: strings, template literals (with ${} nesting),
+  comments and regex literals are skipped; every bracket must close in order."""
+  stack, i, n, prev = [], 0, len(src), ""
+  pairs = {")": "(", "]": "[", "}": "{"}
+  while i < n:
+    c = src[i]
+    if c in " \t\r\n":
+      i += 1
+      continue
+    if src.startswith("//", i):
+      i = src.index("\n", i) if "\n" in src[i:] else n
+      continue
+    if src.startswith("/*", i):
+      i = src.index("*/", i) + 2
+      continue
+    if c in "'\"":
+      j = i + 1
+      while src[j] != c:
+        assert src[j] != "\n", f"string runs over a line end at offset {i}"
+        j += 2 if src[j] == "\\" else 1
+      i, prev = j + 1, "s"
+      continue
+    if c == "`":
+      stack.append("`")
+      i += 1
+      # template text up to the closing back-tick or a ${ that opens an expression
+      while True:
+        if src[i] == "\\":
+          i += 2
+        elif src[i] == "`":
+          assert stack.pop() == "`"
+          i += 1
+          break
+        elif src.startswith("${", i):
+          stack.append("${")
+          i += 2
+          break
+        else:
+          i += 1
+      prev = "s"
+      continue
+    if c == "/" and prev in "(,=:[!&|?{};\n" + "":
+      j = i + 1
+      in_class = False
+      while src[j] != "/" or in_class:
+        in_class = (src[j] == "[") or (in_class and src[j] != "]")
+        j += 2 if src[j] == "\\" else 1
+      i, prev = j + 1, "s"
+      continue
+    if c in "([{":
+      stack.append(c)
+    elif c in ")]":
+      assert stack and stack.pop() == pairs[c], f"unbalanced {c} at offset {i}: ...{src[max(0, i - 60):i + 1]}"
+    elif c == "}":
+      assert stack, f"unbalanced }} at offset {i}"
+      top = stack.pop()
+      if top == "${":                      # back inside the template text
+        while True:
+          if src[i + 1] == "\\":
+            i += 2
+          elif src[i + 1] == "`":
+            assert stack.pop() == "`"
+            i += 1
+            break
+          elif src.startswith("${", i + 1):
+            stack.append("${")
+            i += 2
+            break
+          else:
+            i += 1
+      else:
+        assert top == "{", f"unbalanced }} at offset {i}: ...{src[max(0, i - 60):i + 1]}"
+    prev = c
+    i += 1
+  assert not stack, f"unclosed {stack[-3:]}"
+
+
+def test_dashboard_page_is_served_and_its_scripts_are_well_formed(tmp_path):
+  from nmoe_b200.viz.server import STATIC_DIR, static_file
+  srv = serve(str(tmp_path), None, port=0)
+  port = srv.server_address[1]
+  threading.Thread(target=srv.serve_forever, daemon=True).start()
+  try:
+    with urllib.request.urlopen(f"http://127.0.0.1:{port}/", timeout=5) as r:
+      page = r.read().decode()
+      assert r.headers["Content-Type"].startswith("text/html")
+    import re
+    scripts = re.findall(r'<script src="/static/([\w.]+)"', page)
+    assert scripts == ["chart.js", "app.js", "panels.js"] and 'href="/static/style.css"' in page
+    ids_in_page = set(re.findall(r'id="([\w-]+)"', page))
+    for name in scripts:
+      with urllib.request.urlopen(f"http://127.0.0.1:{port}/static/{name}", timeout=5) as r:
+        src = r.read().decode()
+        assert "javascript" in r.headers["Content-Type"]
+      _js_balance(src)
+      for ref in re.findall(r"\$\('([\w-]+)'\)", src):        # every element the scripts look up exists
+        assert ref in ids_in_page or ref in ("open-run", "ds-off", "ds-win", "ds-doc", "ds-docbtn", "ds-tokens", "ds-docout"), ref
+      for url in re.findall(r"['`](/api/[\w/]+)", src):          # every route the scripts call is one the server has
+        assert url.rstrip("/") in {"/api/runs", "/api/series", "/api/summary", "/api/tags", "/api/gpu", "/api/router", "/api/experiments",
+                       "/api/experiments/runs", "/api/datasets", "/api/datasets/manifest", "/api/datasets/pipeline",
+                       "/api/datasets/meta", "/api/datasets/shard/stats", "/api/datasets/shard/window",
+                       "/api/datasets/index/doc", "/api/datasets/index/header", "/api/datasets/preview"}, url
+    for bad in ("/static/../server.py", "/static/nope.js", "/static/%2e%2e/server.py"):
+      try:
+        urllib.request.urlopen(f"http://127.0.0.1:{port}{bad}", timeout=5)
+        raise AssertionError(bad)
+      except urllib.error.HTTPError as e:
+        assert e.code == 404
+    assert static_file("../server.py") is None and STATIC_DIR.name == "static"
+  finally:
+    srv.shutdown()
+    srv.server_close()
