@@ -296,3 +296,17 @@ def test_dashboard_page_is_served_and_its_scripts_are_well_formed(tmp_path):
   finally:
     srv.shutdown()
     srv.server_close()
+
+
+def test_gpu_telemetry_rows_use_the_dashboard_tag_names():
+  from nmoe_b200.utils.gpu_telemetry import _FIELDS, dashboard_items
+  snap = [dict(zip(_FIELDS, (0, 97, 40, 150 << 30, 180 << 30, 812000, 71, 1560, 1965, 0x4, 0, 123))),
+          dict(zip(_FIELDS, (1, 91, 38, 148 << 30, 180 << 30, 640000, 78, 1900, 1965, 0x20 | 0x8, 2, 123)))]
+  rows = dict(dashboard_items(snap))
+  assert rows["gpu/0/utilization_gpu"] == 97.0 and rows["gpu/0/memory_used_gib"] == 150.0 and rows["gpu/0/power_draw_w"] == 812.0
+  assert rows["gpu/0/throttle_power"] == 1.0 and rows["gpu/0/throttle_thermal"] == 0.0 and rows["gpu/0/throttle_hw_slowdown"] == 0.0
+  assert rows["gpu/1/throttle_thermal"] == 1.0 and rows["gpu/1/throttle_hw_slowdown"] == 1.0 and rows["gpu/1/ecc_uncorrected"] == 2.0
+  assert rows["gpu/1/clocks_sm_mhz"] == 1900.0 and rows["gpu/1/clocks_sm_max_mhz"] == 1965.0
+  assert rows["gpu_agg/mean_utilization_gpu"] == 94.0 and rows["gpu_agg/total_memory_used_gib"] == 298.0
+  assert rows["gpu_agg/total_power_w"] == 1452.0 and rows["gpu_agg/max_temperature_c"] == 78.0
+  assert dashboard_items([]) == []
