@@ -24,14 +24,32 @@ def cmd_prep(a) -> int:
     kw["text_field"] = a.text_field
   cfg = PrepConfig(output_dir=a.output, dataset=a.name, version=a.version, tokenizer=a.tokenizer, num_shards=a.num_shards,
                    max_documents=a.max_documents, max_tokens=a.max_tokens)
-  if a.runner != "process":
+  audited = None
+  def make_source():
+    return create_source(a.source, **kw)
+  if a.hydra_filter or a.hydra_audit_dir:
+    # grading runs in this process (one model on one GPU): worker processes and the stage graph are for ungraded input
+    if a.workers > 1 or a.runner != "process":
+      raise SystemExit("--hydra-filter / --hydra-audit-dir grade in the main process: use --workers 1 --runner process")
+    from .sources import AuditedSource, FilteredSource, ScoringSource
+    score, tau_keep = _mixture_grader(a, {})
+    if a.hydra_audit_dir:
+      audited = AuditedSource(ScoringSource(make_source(), score, a.hydra_batch_size), a.hydra_audit_dir,
+                              tau_keep if a.hydra_filter else None)
+      src = audited
+    else:
+      src = FilteredSource(make_source(), tau_keep, score_fn=score, batch_size=a.hydra_batch_size)
+    m = PrepPipeline(src, cfg).run()
+  elif a.runner != "process":
     from .prep import run_beam_pipeline
-    m = run_beam_pipeline(create_source(a.source, **kw), cfg, runner=a.runner)
+    m = run_beam_pipeline(make_source(), cfg, runner=a.runner)
   elif a.workers > 1:
-    m = ParallelPrepPipeline(lambda: create_source(a.source, **kw), cfg, a.workers).run()
+    m = ParallelPrepPipeline(make_source, cfg, a.workers).run()
   else:
-    m = PrepPipeline(create_source(a.source, **kw), cfg).run()
+    m = PrepPipeline(make_source(), cfg).run()
   print(f"wrote {m.num_shards} shards, {m.total_documents:,} documents, {m.total_tokens:,} tokens -> {a.output}")
+  if audited is not None:
+    print(f"graded {audited.seen:,} documents, kept {audited.kept:,}; scores of all of them -> {a.hydra_audit_dir}/scores.jsonl")
   return 0
 
 
@@ -213,10 +231,47 @@ def cmd_merge_manifests(a) -> int:
   return 0
 
 
+def _flow_profile(a) -> int:
+  """``flow --config flow_profiles.toml --profile NAME``: a ``[profiles.NAME]`` table names a mixture file, a flow and
+  the arguments of one ``prep-mixture`` call (nmoe/data/cli.py:1212-1266); this runs that call for this worker."""
+  from ..config import load_toml
+  cfg_path = Path(a.config or "configs/flow_profiles.toml")
+  if not cfg_path.exists():
+    print(f"flow profiles file not found: {cfg_path}", file=sys.stderr)
+    return 1
+  profiles = load_toml(cfg_path).get("profiles") or {}
+  prof = profiles.get(a.profile)
+  if not isinstance(prof, dict):
+    print(f"unknown profile {a.profile!r}; {cfg_path} has: {', '.join(sorted(profiles)) or 'none'}", file=sys.stderr)
+    return 1
+  if not prof.get("mixture"):
+    print(f"[profiles.{a.profile}] names no mixture file", file=sys.stderr)
+    return 1
+  argv = ["prep-mixture", "--config", str(prof["mixture"]), "--flow-profiles", str(cfg_path)]
+  for key, flag in (("flow", "--flow"), ("stage", "--stage"), ("splits", "--splits"), ("seed", "--seed"), ("limit", "--limit"),
+                    ("output_root", "--output-root"), ("tokenizer", "--tokenizer"), ("num_shards", "--num-shards"),
+                    ("data_root", "--data-root"), ("max_tokens", "--max-tokens")):
+    if prof.get(key) not in (None, ""):
+      argv += [flag, str(prof[key])]
+  for key, flag in (("dry_run", "--dry-run"), ("force", "--force"), ("hydra_filter", "--hydra-filter"), ("continue_on_error", "--continue-on-error")):
+    if prof.get(key) or getattr(a, key, False):
+      argv.append(flag)
+  for key, flag in (("data_root", "--data-root"), ("output_root", "--output-root")):      # the command line wins over the table
+    if getattr(a, key, None):
+      argv += [flag, str(getattr(a, key))]
+  argv += ["--num-workers", str(a.num_workers), "--worker-index", str(a.worker_index)]
+  return main(argv)
+
+
 def cmd_flow(a) -> int:
   """Run a data flow; its grading / rephrasing stages load the grading model named in the spec
   (``grade.checkpoint`` + ``grade.heads``, ``rephrase.checkpoint``)."""
   from .flow import load_spec, run_flow
+  if a.profile or a.config:
+    return _flow_profile(a)
+  if not a.spec:
+    print("flow needs a specification file, or --config FLOW_PROFILES --profile NAME", file=sys.stderr)
+    return 2
   spec = load_spec(Path(a.spec))
   grader = rephraser = None
   model = None
@@ -520,6 +575,10 @@ def build_parser() -> argparse.ArgumentParser:
   p.add_argument("--max-documents", type=int); p.add_argument("--max-tokens", type=int)
   p.add_argument("--runner", default="process", choices=["process", "beam", "local", "auto"],
                  help="process: worker processes on this host; beam / local / auto: the stage graph on Apache Beam or the built-in runner")
+  p.add_argument("--hydra-filter", action="store_true", help="keep only documents the quality grader scores at or above its keep threshold")
+  p.add_argument("--hydra-audit-dir", help="write the score of every document, kept or not, to this directory")
+  p.add_argument("--checkpoint"); p.add_argument("--heads-dir"); p.add_argument("--calibration")
+  p.add_argument("--hydra-batch-size", type=int, default=32); p.add_argument("--hydra-max-ctx", type=int, default=4096)
   p = sub.add_parser("prep-mixture"); p.set_defaults(fn=cmd_prep_mixture)
   p.add_argument("--mixture"); p.add_argument("--config", help="same as --mixture")
   p.add_argument("--flow-profiles", default="configs/flow_profiles.toml"); p.add_argument("--flow")
@@ -541,7 +600,10 @@ def build_parser() -> argparse.ArgumentParser:
   p = sub.add_parser("inspect"); p.set_defaults(fn=cmd_inspect); p.add_argument("shard"); p.add_argument("--doc", type=int)
   p.add_argument("--start", type=int); p.add_argument("--length", type=int, default=64); p.add_argument("--tokenizer")
   p = sub.add_parser("merge-manifests"); p.set_defaults(fn=cmd_merge_manifests); p.add_argument("parts", nargs="+"); p.add_argument("--output", required=True)
-  p = sub.add_parser("flow"); p.set_defaults(fn=cmd_flow); p.add_argument("spec"); p.add_argument("--staged", action="store_true")
+  p = sub.add_parser("flow"); p.set_defaults(fn=cmd_flow); p.add_argument("spec", nargs="?"); p.add_argument("--staged", action="store_true")
+  p.add_argument("--config", help="flow profiles TOML with [profiles.NAME] tables"); p.add_argument("--profile")
+  p.add_argument("--num-workers", type=int, default=1); p.add_argument("--worker-index", type=int, default=0)
+  p.add_argument("--data-root"); p.add_argument("--output-root"); p.add_argument("--dry-run", action="store_true"); p.add_argument("--force", action="store_true")
   def model_args(p, heads=False):
     p.add_argument("--checkpoint", required=True); p.add_argument("--input", required=not heads); p.add_argument("--output", required=not heads)
     p.add_argument("--text-field", default="text"); p.add_argument("--tokenizer", default="o200k_harmony")

@@ -272,6 +272,30 @@ class FilteredSource(DataSource):
         yield d
 
 
+class AuditedSource(DataSource):
+  """Passes a scored source through and writes one ``{"id", "score", "kept"}`` line per document seen, kept or not, to
+  ``{audit_dir}/scores.jsonl``: the trail that shows what a quality filter dropped (``prep --hydra-audit-dir``).
+  With ``threshold=None`` nothing is dropped and ``kept`` is always true."""
+
+  def __init__(self, base: DataSource, audit_dir, threshold: Optional[float] = None, snippet_chars: int = 160):
+    self.base, self.dir, self.threshold, self.snippet = base, Path(audit_dir), threshold, snippet_chars
+    self.name = f"audited:{base.name}"
+    self.seen = self.kept = 0
+
+  def __iter__(self):
+    self.dir.mkdir(parents=True, exist_ok=True)
+    with open(self.dir / "scores.jsonl", "a", encoding="utf-8") as f:
+      for d in self.base:
+        score = float(d.metadata.get("score", float("nan")))
+        keep = self.threshold is None or score >= self.threshold
+        self.seen += 1
+        self.kept += int(keep)
+        f.write(json.dumps({"id": d.doc_id, "score": score, "kept": keep, "snippet": d.text[:self.snippet]}, ensure_ascii=False) + "\n")
+        if keep:
+          yield d
+    (self.dir / "summary.json").write_text(json.dumps({"seen": self.seen, "kept": self.kept, "threshold": self.threshold}))
+
+
 def content_doc_id(text: str) -> str:
   return hashlib.sha1(text.encode("utf-8")).hexdigest()[:20]
 

@@ -238,6 +238,19 @@ def test_flow_writes_every_rephrased_version(tmp_path):
   assert k2.rephrase["num_versions"] == 10 and k2.grade["enabled"] and k2.source["kind"] == "hf"
 
 
+def test_flow_profile_presets_expand_to_prep_mixture(tmp_path, capsys):
+  """`flow --config flow_profiles.toml --profile NAME` runs the prep-mixture call its [profiles.NAME] table describes."""
+  from nmoe_b200.data.cli import main
+  base = ["flow", "--config", "configs/flow_profiles.toml", "--dry-run", "--data-root", str(tmp_path)]
+  assert main([*base, "--profile", "hydra_fixture"]) == 0
+  out = capsys.readouterr().out
+  assert "plan hydra_fixture:dev" in out and "seed 123" in out and str(tmp_path / "flows" / "hydra_fixture") in out
+  assert main([*base, "--profile", "mini", "--num-workers", "2", "--worker-index", "1"]) == 0
+  assert "worker 1/2" in capsys.readouterr().out
+  assert main([*base, "--profile", "nope"]) == 1 and "hydra_fixture, mini" in capsys.readouterr().err
+  assert main(["flow"]) == 2
+
+
 def test_staged_flow_keeps_stage_files_and_continues_after_an_interruption(tmp_path):
   """Each stage writes its own file; a run cut in the grading or rephrasing stage computes only what is missing when
   it is started again, and ends with the same shards as the streaming flow."""

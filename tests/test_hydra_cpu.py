@@ -369,3 +369,35 @@ def test_cli_docids_grade_from_shards_with_resume_and_train_from_labels(tmp_path
   assert main([*train, "--phase", "A"]) == 0
   assert main([*train, "--phase", "B", "--oracle-labels", str(lab), "--data-root", str(root), "--pairs-per-batch", "2"]) == 0
   assert main([*train, "--phase", "C"]) == 0
+
+
+def test_prep_with_quality_filter_and_audit_trail(tmp_path):
+  """`prep --hydra-filter --hydra-audit-dir`: shards hold only kept documents, the audit file scores every document."""
+  import json
+  from nmoe_b200.data.cli import main
+  from nmoe_b200.data.sinks import load_manifest
+  from nmoe_b200.serve.checkpoint import save_model
+  save_model(backbone(), str(tmp_path / "ckpt"))
+  heads = tmp_path / "heads"
+  H.save_heads(str(heads), H.ProbeHead(32), H.JudgeHead(32))
+  raw = tmp_path / "raw.jsonl"
+  raw.write_text("".join(json.dumps({"id": f"d{i}", "text": f"document number {i} " * (2 + i % 5)}) + "\n" for i in range(30)))
+  base = ["prep", "--source", "jsonl", "--input", str(raw), "--name", "q", "--tokenizer", "bytes", "--num-shards", "2",
+          "--checkpoint", str(tmp_path / "ckpt"), "--heads-dir", str(heads), "--hydra-batch-size", "8", "--hydra-max-ctx", "64"]
+  # audit only: everything is kept, every score is on file
+  H.Calibration(tau_drop=-1.0, tau_keep=0.5).save(str(heads))
+  assert main([*base, "--output", str(tmp_path / "all"), "--hydra-audit-dir", str(tmp_path / "audit_all")]) == 0
+  rows = [json.loads(l) for l in open(tmp_path / "audit_all" / "scores.jsonl")]
+  assert len(rows) == 30 and all(r["kept"] for r in rows) and load_manifest(tmp_path / "all").total_documents == 30
+  scores = sorted(r["score"] for r in rows)
+  # filter at the median score: about half survives, and the audit trail says which
+  H.Calibration(tau_drop=-1.0, tau_keep=scores[15]).save(str(heads))
+  assert main([*base, "--output", str(tmp_path / "kept"), "--hydra-filter", "--hydra-audit-dir", str(tmp_path / "audit")]) == 0
+  rows = [json.loads(l) for l in open(tmp_path / "audit" / "scores.jsonl")]
+  kept = [r for r in rows if r["kept"]]
+  assert len(rows) == 30 and 0 < len(kept) < 30 and all(r["score"] >= scores[15] for r in kept)
+  assert load_manifest(tmp_path / "kept").total_documents == len(kept)
+  assert json.loads((tmp_path / "audit" / "summary.json").read_text()) == {"seen": 30, "kept": len(kept), "threshold": scores[15]}
+  # filter without an audit directory gives the same shards
+  assert main([*base, "--output", str(tmp_path / "kept2"), "--hydra-filter"]) == 0
+  assert load_manifest(tmp_path / "kept2").total_tokens == load_manifest(tmp_path / "kept").total_tokens
