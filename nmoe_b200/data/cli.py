@@ -410,28 +410,51 @@ def cmd_docids(a) -> int:
 
 
 def cmd_hydra_oracle_label(a) -> int:
-  """Ask the grading model itself for rubric scores (JSON answers) through the batching engine."""
+  """Ask the grading model itself for rubric scores (JSON answers) through the batching engine.  Input is a JSONL of
+  texts, or a list of shard references whose tokens are decoded back to text; ``--resume`` skips ids already in the
+  output.  Rows carry ``doc_id`` so that ``hydra-train --oracle-labels`` can join them with the shards again."""
   from ..serve import Engine
   from .score import grade_prompts
+  if not a.output:
+    raise SystemExit("hydra-oracle-label needs --output")
   model, _ = _grading_model(a)
   tok = _tokenizer(a.tokenizer)
-  rows = _read_jsonl(a.input, a.text_field, a.max_documents)
+  ids, docs, n_done = _grading_inputs(a, tok)
+  texts = [tok.decode(d) for d in docs]
   eng = Engine(model, max_seq_len=a.max_ctx, max_batch=a.batch_size)
-  res = grade_prompts(eng, tok, [r[a.text_field] for r in rows], max_new=a.max_new, max_ctx=a.max_ctx,
-                      stop_tokens=[getattr(tok, "eot", -1)])
-  with open(a.output, "w", encoding="utf-8") as f:
-    for r, g in zip(rows, res):
-      f.write(json.dumps({"id": r.get("id"), **g}) + "\n")
-  print(f"labelled {len(res)} documents ({sum(1 for g in res if g['scores'])} parsed) -> {a.output}")
+  parsed = 0
+  with open(a.output, "a" if n_done else "w", encoding="utf-8") as f:
+    for i0 in range(0, len(texts), a.flush_every):
+      res = grade_prompts(eng, tok, texts[i0:i0 + a.flush_every], max_new=a.max_new, max_ctx=a.max_ctx,
+                          stop_tokens=[getattr(tok, "eot", -1)])
+      for did, g in zip(ids[i0:i0 + a.flush_every], res):
+        f.write(json.dumps({"doc_id": did, "id": did, "ok": g["scores"] is not None, **g}) + "\n")
+        parsed += int(g["scores"] is not None)
+      f.flush()
+  print(f"labelled {len(texts)} documents ({parsed} parsed, {n_done} already done) -> {a.output}")
   return 0
 
 
 def cmd_hydra_calibrate(a) -> int:
-  """Fit rubric weights and keep/drop thresholds from judged rows joined with oracle labels."""
+  """Rubric weights and keep / drop thresholds.  ``--labels`` alone fits them to oracle labels at a target keep rate;
+  ``--judged`` with ``--oracle`` fits them to the judge head's own predictions against the oracle's keep decision."""
   import torch
   from . import hydra as H
+  if a.labels:
+    rows = [json.loads(l) for l in open(a.labels, encoding="utf-8") if l.strip()]
+    try:
+      cal, n = H.calibrate_from_labels(rows, a.target_keep)
+    except ValueError as e:
+      print(str(e), file=sys.stderr)
+      return 1
+    p = cal.save(a.output)
+    print(json.dumps({"weights": cal.weights, "tau_drop": cal.tau_drop, "tau_keep": cal.tau_keep, "count": n, "path": str(p)}, indent=1))
+    return 0
+  if not (a.judged and a.oracle):
+    print("hydra-calibrate needs --labels, or --judged with --oracle", file=sys.stderr)
+    return 2
   judged = {str(j["doc_id"]): j for j in map(json.loads, open(a.judged, encoding="utf-8")) if j.get("scores")}
-  oracle = {str(j["id"]): j for j in map(json.loads, open(a.oracle, encoding="utf-8")) if j.get("aggregated") is not None}
+  oracle = {str(j.get("doc_id", j.get("id"))): j for j in map(json.loads, open(a.oracle, encoding="utf-8")) if j.get("aggregated") is not None}
   keys = sorted(set(judged) & set(oracle))
   if not keys:
     print("no overlapping documents between --judged and --oracle", file=sys.stderr)
@@ -604,8 +627,8 @@ def build_parser() -> argparse.ArgumentParser:
   p.add_argument("--config", help="flow profiles TOML with [profiles.NAME] tables"); p.add_argument("--profile")
   p.add_argument("--num-workers", type=int, default=1); p.add_argument("--worker-index", type=int, default=0)
   p.add_argument("--data-root"); p.add_argument("--output-root"); p.add_argument("--dry-run", action="store_true"); p.add_argument("--force", action="store_true")
-  def model_args(p, heads=False):
-    p.add_argument("--checkpoint", required=True); p.add_argument("--input", required=not heads); p.add_argument("--output", required=not heads)
+  def model_args(p, heads=False, optional_io=False):
+    p.add_argument("--checkpoint", required=True); p.add_argument("--input", required=not (heads or optional_io)); p.add_argument("--output", required=not (heads or optional_io))
     p.add_argument("--text-field", default="text"); p.add_argument("--tokenizer", default="o200k_harmony")
     p.add_argument("--max-ctx", type=int, default=4096); p.add_argument("--batch-size", type=int, default=32)
     p.add_argument("--max-documents", type=int)
@@ -619,14 +642,16 @@ def build_parser() -> argparse.ArgumentParser:
   p.add_argument("--data-root", required=True); p.add_argument("--source", required=True); p.add_argument("--output", required=True)
   p.add_argument("--subdir", default=""); p.add_argument("--min-tokens", type=int, default=0); p.add_argument("--fraction", type=float, default=1.0)
   p.add_argument("--seed", type=int, default=0); p.add_argument("--limit", type=int)
-  p = sub.add_parser("hydra-oracle-label"); p.set_defaults(fn=cmd_hydra_oracle_label); model_args(p); p.add_argument("--max-new", type=int, default=256)
+  p = sub.add_parser("hydra-oracle-label"); p.set_defaults(fn=cmd_hydra_oracle_label); model_args(p, optional_io=True); p.add_argument("--max-new", type=int, default=256)
+  p.add_argument("--input-docids"); p.add_argument("--data-root"); p.add_argument("--resume", action="store_true"); p.add_argument("--flush-every", type=int, default=1024)
   p = sub.add_parser("hydra-train"); p.set_defaults(fn=cmd_hydra_train); model_args(p, heads=True)
   p.add_argument("--phase", choices=["A", "B", "C"], required=True); p.add_argument("--steps", type=int, default=1000); p.add_argument("--lr", type=float, default=1e-3)
   p.add_argument("--labels", action="append", help="<eai|fineweb_edu>:<web|code|science|math>:<parquet/JSONL path or glob>; repeatable")
   p.add_argument("--oracle-labels", help="JSONL of {doc_id: shard reference, scores}"); p.add_argument("--data-root")
   p.add_argument("--pairs-per-batch", type=int, default=8); p.add_argument("--seed", type=int, default=0)
   p = sub.add_parser("hydra-calibrate"); p.set_defaults(fn=cmd_hydra_calibrate)
-  p.add_argument("--judged", required=True); p.add_argument("--oracle", required=True); p.add_argument("--output", required=True)
+  p.add_argument("--judged"); p.add_argument("--oracle"); p.add_argument("--output", required=True)
+  p.add_argument("--labels", help="oracle labels JSONL: calibrate from these alone"); p.add_argument("--target-keep", type=float, default=0.5)
   p.add_argument("--oracle-keep", type=float, default=0.6); p.add_argument("--keep-precision", type=float, default=0.9)
   p = sub.add_parser("rephrase"); p.set_defaults(fn=cmd_rephrase); model_args(p)
   p.add_argument("--num-versions", type=int, default=1); p.add_argument("--chunk-size", type=int, default=2048); p.add_argument("--no-filter", action="store_true")

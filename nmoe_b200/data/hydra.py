@@ -152,6 +152,36 @@ def aggregate_scores(scores: Dict[str, float], weights: Optional[Dict[str, float
   return num / den if den > 0 else 0.0
 
 
+def calibrate_from_labels(rows: Sequence[dict], target_keep: float = 0.5) -> Tuple[Calibration, int]:
+  """Calibration from oracle labels alone (nmoe/data/hydra.py:207-251): rubric weights are the non-negative
+  least-squares fit of the five scores (each / 4) to the row's ``aggregated`` value (their mean when it has none),
+  normalised to sum to one; ``tau_keep`` is the score quantile above which ``target_keep`` of the labelled documents
+  lie, ``tau_drop`` the one below which ``target_keep`` of them lie, swapped if needed so that drop <= keep.  Returns the
+  calibration and the number of rows used."""
+  if not 0.0 < target_keep < 1.0:
+    raise ValueError("target_keep must lie strictly between 0 and 1")
+  xs, ys = [], []
+  for r in rows:
+    sc = r.get("scores")
+    if not sc:
+      continue
+    x = [min(max(float(sc.get(k, 0.0)) / 4.0, 0.0), 1.0) for k in RUBRIC]
+    xs.append(x)
+    ys.append(float(r["aggregated"]) if r.get("aggregated") is not None else sum(x) / len(x))
+  if not xs:
+    raise ValueError("no labelled rows with scores")
+  x, y = torch.tensor(xs, dtype=torch.float64), torch.tensor(ys, dtype=torch.float64)
+  w = torch.full((len(RUBRIC),), 1.0 / len(RUBRIC), dtype=torch.float64)
+  step = 1.0 / max(1e-9, float(torch.linalg.matrix_norm(x.t() @ x / len(y), ord=2)))
+  for _ in range(2000):      # projected gradient: a clipped unconstrained solution is not the constrained optimum
+    w = (w - step * (x.t() @ (x @ w - y) / len(y))).clamp(min=0.0)
+  w = w / w.sum() if float(w.sum()) > 0 else torch.full_like(w, 1.0 / len(w))
+  s = x @ w
+  lo, hi = float(torch.quantile(s, target_keep)), float(torch.quantile(s, 1.0 - target_keep))
+  cal = Calibration({k: float(v) for k, v in zip(RUBRIC, w)}, tau_drop=min(lo, hi), tau_keep=max(lo, hi))
+  return cal, len(xs)
+
+
 def calibrate(rubric_pred: torch.Tensor, oracle_keep: torch.Tensor, *, keep_precision: float = 0.9,
               drop_recall_loss: float = 0.02) -> Calibration:
   """Fit rubric weights (non-negative least squares by projected gradient onto the oracle keep label)

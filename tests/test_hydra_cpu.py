@@ -401,3 +401,45 @@ def test_prep_with_quality_filter_and_audit_trail(tmp_path):
   # filter without an audit directory gives the same shards
   assert main([*base, "--output", str(tmp_path / "kept2"), "--hydra-filter"]) == 0
   assert load_manifest(tmp_path / "kept2").total_tokens == load_manifest(tmp_path / "kept").total_tokens
+
+
+def test_calibration_from_labels_alone_and_oracle_labelling_over_shards(tmp_path):
+  import json
+  import random
+  from nmoe_b200.data.cli import main
+  from nmoe_b200.data import docid as D
+  from nmoe_b200.serve.checkpoint import save_model
+  rnd = random.Random(0)
+  rows = []
+  for i in range(400):
+    sc = {d: rnd.randint(0, 4) for d in H.RUBRIC}
+    # the oracle's overall score only looks at two of the five dimensions
+    rows.append({"doc_id": f"d{i}", "scores": sc, "aggregated": 0.75 * sc["correctness"] / 4 + 0.25 * sc["density"] / 4})
+  rows.append({"doc_id": "bad", "scores": None})
+  cal, n = H.calibrate_from_labels(rows, target_keep=0.3)
+  assert n == 400 and abs(cal.weights["correctness"] - 0.75) < 0.02 and abs(cal.weights["density"] - 0.25) < 0.02
+  assert cal.weights["helpfulness"] < 0.02 and abs(sum(cal.weights.values()) - 1.0) < 1e-9 and cal.tau_drop <= cal.tau_keep
+  agg = [H.aggregate_scores(r["scores"], cal.weights) for r in rows[:400]]
+  assert abs(sum(a >= cal.tau_keep for a in agg) / 400 - 0.3) < 0.06 and abs(sum(a <= cal.tau_drop for a in agg) / 400 - 0.3) < 0.06
+  no_agg = [{"scores": r["scores"]} for r in rows[:400]]                      # without "aggregated": the plain mean
+  cal2, _ = H.calibrate_from_labels(no_agg, 0.5)
+  assert all(abs(w - 0.2) < 0.02 for w in cal2.weights.values()) and cal2.tau_drop == cal2.tau_keep
+  lab = tmp_path / "labels.jsonl"
+  lab.write_text("".join(json.dumps(r) + "\n" for r in rows))
+  assert main(["hydra-calibrate", "--labels", str(lab), "--target-keep", "0.3", "--output", str(tmp_path / "cal")]) == 0
+  loaded = H.Calibration.load(str(tmp_path / "cal"))
+  assert abs(loaded.tau_keep - cal.tau_keep) < 1e-9 and abs(loaded.weights["correctness"] - cal.weights["correctness"]) < 1e-9
+  assert main(["hydra-calibrate", "--output", str(tmp_path / "cal")]) == 2
+
+  # oracle labelling from shard references, continued after a first partial run
+  save_model(backbone(), str(tmp_path / "ckpt"))
+  _tiny_dataset(tmp_path / "data", n_docs=12)
+  refs_file = tmp_path / "refs.jsonl"
+  D.write_refs(refs_file, D.enumerate_refs(tmp_path / "data", "web"))
+  out = tmp_path / "oracle.jsonl"
+  cmd = ["hydra-oracle-label", "--checkpoint", str(tmp_path / "ckpt"), "--tokenizer", "bytes", "--max-ctx", "64", "--batch-size", "4",
+         "--max-new", "4", "--input-docids", str(refs_file), "--data-root", str(tmp_path / "data"), "--output", str(out)]
+  assert main([*cmd, "--max-documents", "5"]) == 0
+  assert main([*cmd, "--resume"]) == 0
+  got = [json.loads(l) for l in open(out)]
+  assert [g["doc_id"] for g in got] == [str(r) for r in D.read_refs(refs_file)] and all("ok" in g and "raw" in g for g in got)
