@@ -19,11 +19,13 @@ fingerprint, mixture-plan hash or world size.
 from __future__ import annotations
 
 import json
+import math
 import os
 import queue
 import shutil
 import subprocess
 import threading
+import time
 from pathlib import Path
 from typing import Any, Callable, Dict, Optional, Tuple
 
@@ -66,6 +68,22 @@ def read_tracker(base: str | Path) -> int:
     return int((Path(base) / TRACKER).read_text().strip())
   except (OSError, ValueError):
     return -1
+
+
+def read_latest_run_info(base: str | Path) -> Optional[dict]:
+  """``run_info`` of the latest finalised step (git hash, preset, dtype, expert count, ...) plus ``step`` and ``tokens``,
+  read from ``rd.pt`` on the CPU; None when there is no readable checkpoint (nmoe/checkpoint.py:80-101)."""
+  step = read_tracker(base)
+  if step < 0:
+    return None
+  try:
+    rd = torch.load(iteration_dir(base, step) / "rd.pt", map_location="cpu", weights_only=False)
+  except (OSError, RuntimeError, EOFError, ValueError):
+    return None
+  info = rd.get("run_info")
+  if not isinstance(info, dict):
+    return None
+  return {**info, "step": int(rd.get("step", step)), "tokens": int(rd.get("tokens", 0))}
 
 
 def git_sha() -> str:
@@ -111,6 +129,8 @@ class Checkpointer:
     self.async_io = async_io
     self.fault_hook = fault_hook
     self._err: Optional[BaseException] = None
+    self.last_write_ms = 0.0      # serialise + fsync + finalise of the newest file written, measured on the writer
+    self.last_stage_ms = 0.0      # device -> host copy of the newest submit, measured on the training thread
     self._q: "queue.Queue[Optional[Tuple[Path, dict, int, int]]]" = queue.Queue(maxsize=max(1, async_max_queue))
     self._thread: Optional[threading.Thread] = None
     if async_io:
@@ -119,6 +139,7 @@ class Checkpointer:
 
   # ---------------------------------------------------------------- writer
   def _write(self, path: Path, state: dict, step: int, world: int) -> None:
+    t0 = time.perf_counter()
     if self.fault_hook:
       self.fault_hook("before_write")
     path.parent.mkdir(parents=True, exist_ok=True)
@@ -134,6 +155,15 @@ class Checkpointer:
       self.fault_hook("before_finalize")
     if try_finalize_step(self.base, step, world):
       self._purge()
+    self.last_write_ms = (time.perf_counter() - t0) * 1e3
+
+  def recommend_interval(self, step_time_ms: float, safety: float = 1.3) -> int:
+    """The smallest ``checkpoint_every`` at which the asynchronous writer keeps up: a save must be on disk before the
+    next one is submitted, or ``submit`` blocks the training loop on the queue.  1 until a save has been timed
+    (nmoe/checkpoint.py:534-541)."""
+    if self.last_write_ms <= 0 or step_time_ms <= 0:
+      return 1
+    return max(1, math.ceil(safety * self.last_write_ms / step_time_ms))
 
   def _run(self) -> None:
     while True:
@@ -155,7 +185,9 @@ class Checkpointer:
 
   def submit(self, path: Path, state: dict, step: int, world: int) -> None:
     self._raise_if_failed()
+    t0 = time.perf_counter()
     host = to_host(state)
+    self.last_stage_ms = (time.perf_counter() - t0) * 1e3
     if self.async_io:
       self._q.put((path, host, step, world))
     else:
@@ -249,7 +281,10 @@ def save_checkpoint(ck: Checkpointer, step: int, trainer, loader, plan, cfg: Con
   if rd is not None:
     ck.submit(d / "rd.pt", rd, step, world)
   ck.submit(d / f"dp_rank_{rank:03d}.pt", dp, step, world)
-  print_fn(f"[ckpt] step {step} submitted -> {d}")
+  note = ""
+  if ck.last_write_ms > 0:
+    note = f" (host copy {ck.last_stage_ms:.0f} ms; previous write {ck.last_write_ms / 1e3:.1f} s)"
+  print_fn(f"[ckpt] step {step} submitted -> {d}{note}")
   return True
 
 

@@ -186,9 +186,11 @@ def cmd_regenerate_index(a) -> int:
 
 
 def cmd_dedup(a) -> int:
-  from .dedup import dedup_exact, stream_near_dedup
+  from .dedup import dedup_exact, dedup_within_docs, stream_near_dedup
   from .sources import create_source
   src = create_source("jsonl", paths=a.input, text_field=a.text_field)
+  if a.within:      # repeats inside a document go first, so that pages differing only in boilerplate can match
+    src = dedup_within_docs(src, a.within)
   docs = dedup_exact(src)
   if a.near:
     docs = stream_near_dedup(docs, threshold=a.threshold)
@@ -619,6 +621,7 @@ def build_parser() -> argparse.ArgumentParser:
   p = sub.add_parser("regenerate-index"); p.set_defaults(fn=cmd_regenerate_index); p.add_argument("path"); p.add_argument("--eos-token-id", type=int, default=199999)
   p = sub.add_parser("dedup"); p.set_defaults(fn=cmd_dedup); p.add_argument("--input", required=True); p.add_argument("--output", required=True)
   p.add_argument("--text-field", default="text"); p.add_argument("--near", action="store_true"); p.add_argument("--threshold", type=float, default=0.8)
+  p.add_argument("--within", choices=["lines", "paragraphs"], help="also drop repeated lines / paragraphs inside each document")
   p = sub.add_parser("cluster"); p.set_defaults(fn=cmd_cluster); p.add_argument("--embeddings", required=True); p.add_argument("--k", type=int, default=64); p.add_argument("--output")
   p = sub.add_parser("inspect"); p.set_defaults(fn=cmd_inspect); p.add_argument("shard"); p.add_argument("--doc", type=int)
   p.add_argument("--start", type=int); p.add_argument("--length", type=int, default=64); p.add_argument("--tokenizer")

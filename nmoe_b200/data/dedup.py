@@ -1,5 +1,6 @@
 """Exact and near-duplicate removal (nmoe/data/dedup.py:34-227): sha1 over normalised text for exact
-duplicates; MinHash signatures over word shingles with banded LSH for near duplicates, streamed."""
+duplicates; MinHash signatures over word shingles with banded LSH for near duplicates, streamed;
+repeated lines / paragraphs inside one document (nmoe/data/dedup.py:47-68)."""
 from __future__ import annotations
 
 import hashlib
@@ -23,6 +24,38 @@ def dedup_exact(docs: Iterable[Document]) -> Iterator[Document]:
     if h not in seen:
       seen.add(h)
       yield d
+
+
+def _key(s: str) -> str:
+  return " ".join(s.split()).lower()
+
+
+def dedup_within(text: str, unit: str = "lines", min_chars: int = 12) -> str:
+  """Drop later repeats of a line (``unit="lines"``) or of a blank-line-separated paragraph (``"paragraphs"``) inside
+  one document: navigation bars, cookie banners and footers that a page repeats.  Units are compared after collapsing
+  white space and case; units shorter than ``min_chars`` (list bullets, braces, "}" lines of code) are never dropped,
+  and neither are blank lines, so the document keeps its shape."""
+  if unit not in ("lines", "paragraphs"):
+    raise ValueError("unit must be 'lines' or 'paragraphs'")
+  sep = "\n" if unit == "lines" else "\n\n"
+  parts = text.split(sep) if unit == "lines" else re.split(r"\n\s*\n", text)
+  seen: Set[str] = set()
+  out: List[str] = []
+  for p in parts:
+    k = _key(p)
+    if len(k) >= min_chars:
+      if k in seen:
+        continue
+      seen.add(k)
+    out.append(p)
+  return sep.join(out)
+
+
+def dedup_within_docs(docs: Iterable[Document], unit: str = "lines", min_chars: int = 12) -> Iterator[Document]:
+  for d in docs:
+    t = dedup_within(d.text, unit, min_chars)
+    if t.strip():
+      yield Document(d.doc_id, t, d.metadata) if t != d.text else d
 
 
 def shingles(text: str, k: int = 5) -> Set[int]:

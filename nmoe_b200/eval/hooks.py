@@ -23,6 +23,9 @@ def save_eval_snapshot(model, cfg, run_id: str, step: int) -> Path:
   d = Path(cfg.checkpoint_dir) / "eval_snapshots" / f"{run_id}_step{step:07d}"
   d.mkdir(parents=True, exist_ok=True)
   torch.save({"step": step, "model": {k: v.detach().cpu() for k, v in model.state_dict().items()}}, d / "model.pt")
+  # the runner rebuilds the model from the configuration it was trained with
+  import dataclasses
+  (d / "config.json").write_text(json.dumps({k: v for k, v in dataclasses.asdict(cfg).items() if not k.startswith("_")}, default=str))
   return d
 
 
@@ -39,7 +42,7 @@ def maybe_schedule_eval(step: int, cfg, model, run_id: str, print_fn=print):
   if cfg.eval_mode == "reserved_gpu":
     env = dict(os.environ, CUDA_VISIBLE_DEVICES=str(cfg.eval_reserved_gpu_id), WORLD_SIZE="1", RANK="0", LOCAL_RANK="0")
     cmd = [sys.executable, "-m", "nmoe_b200.eval.runner", "--snapshot", str(snap), "--run", run_id, "--step", str(step),
-           "--tasks-file", cfg.eval_tasks_file, "--max-examples", str(cfg.eval_budget_max_examples),
+           "--tasks-file", cfg.eval_tasks_file, "--tasks", cfg.eval_tasks, "--max-examples", str(cfg.eval_budget_max_examples),
            "--max-time-s", str(cfg.eval_budget_max_time_s)]
     p = subprocess.Popen(cmd, env=env, stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL)
     print_fn(f"[eval] step {step}: runner pid {p.pid} on GPU {cfg.eval_reserved_gpu_id}")

@@ -69,6 +69,26 @@ def test_dedup_exact_and_near():
   assert kept == ["a", "d"]
 
 
+def test_dedup_inside_a_document(tmp_path):
+  page = "Home | About | Contact\nFirst paragraph of the article.\n}\nHome  |  about | contact\n\nSecond one.\n}\nFirst paragraph of the article."
+  assert dedup.dedup_within(page, "lines") == "Home | About | Contact\nFirst paragraph of the article.\n}\n\nSecond one.\n}"
+  paras = "Subscribe to our newsletter today!\n\nReal content here, long enough.\n \nSubscribe to our  newsletter today!\n\nshort\n\nshort"
+  assert dedup.dedup_within(paras, "paragraphs") == "Subscribe to our newsletter today!\n\nReal content here, long enough.\n\nshort\n\nshort"
+  with pytest.raises(ValueError):
+    dedup.dedup_within(page, "words")
+  # through the command: two pages that differ only in a repeated banner become exact duplicates
+  from nmoe_b200.data.cli import main
+  banner = "Accept all cookies to continue"
+  rows = [{"id": "p1", "text": f"{banner}\nThe body of the page, identical.\n{banner}"},
+          {"id": "p2", "text": f"{banner}\nThe body of the page, identical."},
+          {"id": "p3", "text": "Another page entirely."}]
+  (tmp_path / "in.jsonl").write_text("".join(json.dumps(r) + "\n" for r in rows))
+  assert main(["dedup", "--input", str(tmp_path / "in.jsonl"), "--output", str(tmp_path / "plain.jsonl")]) == 0
+  assert main(["dedup", "--input", str(tmp_path / "in.jsonl"), "--output", str(tmp_path / "within.jsonl"), "--within", "lines"]) == 0
+  assert len(open(tmp_path / "plain.jsonl").readlines()) == 3
+  assert [json.loads(l)["id"] for l in open(tmp_path / "within.jsonl")] == ["p1", "p3"]
+
+
 def test_cluster_coverage():
   rng = np.random.default_rng(0)
   x = np.concatenate([rng.normal(c, 0.1, size=(100, 8)) for c in (-3, 0, 3)])

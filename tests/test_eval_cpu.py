@@ -162,3 +162,75 @@ def test_core_suite_row_formats_fewshot_and_span_scoring(tmp_path):
   assert span.is_correct(" The France.\nQuestion: next", "France", sp[0].meta)
   assert not span.is_correct("Germany", "France", sp[0].meta)
   assert abs(span.best_f1("in the country France", ["France", "in France"]) - 0.8) < 1e-6
+
+
+def _task_file(tmp_path, n=40):
+  """A task file with a multiple-choice group, its generation group, and JSONL sources for both."""
+  mc = tmp_path / "mc.jsonl"
+  mc.write_text("".join(json.dumps({"question": f"q{i}?", "choices": ["a", "b", "c", "d"], "answer": i % 4}) + "\n" for i in range(n)))
+  sp = tmp_path / "span.jsonl"
+  sp.write_text("".join(json.dumps({"context": f"the value is v{i}.", "question": "what is the value?", "answers": {"text": [f"v{i}"]}}) + "\n"
+                        for i in range(n)))
+  tf = tmp_path / "tasks.toml"
+  tf.write_text(f'[groups]\ncore = ["mc_a", "mc_b"]\ncore_gen = ["qa"]\n'
+                f'[tasks.mc_a]\nkind = "choices"\nsource = "jsonl:{mc}"\n[tasks.mc_b]\nkind = "choices"\nsource = "jsonl:{mc}"\n'
+                f'[tasks.qa]\nkind = "gen"\nscorer = "span"\nformat = "squad"\nsource = "jsonl:{sp}"\nmax_new = 4\n'
+                f'[tasks.offline]\nkind = "choices"\nsource = "hf:some/dataset:test"\n')
+  return tf
+
+
+def test_runner_task_selection_budget_and_snapshot_roundtrip(tmp_path, monkeypatch):
+  from nmoe_b200.eval import runner
+  from nmoe_b200.eval.hooks import save_eval_snapshot
+  from nmoe_b200.metrics import MetricsWriter
+  tf = _task_file(tmp_path, n=6)
+  assert list(runner.select_tasks(str(tf), "core")) == ["mc_a", "mc_b", "qa"]
+  assert list(runner.select_tasks(str(tf), "qa")) == ["qa"] and list(runner.select_tasks(str(tf), "chat:mc_b|nope|qa")) == ["mc_b", "qa"]
+  assert runner.select_tasks(str(tf), "unknown") == {} and len(runner.select_tasks(str(tf), "all")) == 4
+  cfg = _cfg(metrics_dir=str(tmp_path / "m"), checkpoint_dir=str(tmp_path / "ck"), eval_tasks_file=str(tf), eval_tasks="core")
+  torch.manual_seed(0)
+  tr = Trainer(cfg)
+  res = runner.run_snapshot_eval(tr.model, cfg, run_id="r", step=7, max_examples=4, print_fn=lambda *_: None)
+  assert set(res) == {"mc_a", "mc_b", "qa"} and res["qa"]["n"] == 4 and "f1" in res["qa"] and "centered_acc" in res["mc_a"]
+  w = MetricsWriter("r", cfg.metrics_dir, 0)
+  assert w.query("eval/CORE")[0][0] == 7 and w.query("eval/task/mc_a/centered") and w.query("eval/task/qa/acc") and w.query("eval/qa/f1")
+  w.close()
+  # no time left: the first task still runs, the rest is reported as skipped
+  res = runner.run_snapshot_eval(tr.model, cfg, run_id="r", step=8, max_examples=2, max_time_s=0.0, print_fn=lambda *_: None)
+  assert list(res) == ["mc_a"] and runner.run_snapshot_eval.last_summary["skipped"] == ["mc_b", "qa"]
+  # a snapshot carries its configuration, so the runner can rebuild the model from the directory alone
+  snap = save_eval_snapshot(tr.model, cfg, "r", 9)
+  runner.main(["--snapshot", str(snap), "--run", "r", "--step", "9", "--tasks", "mc_a", "--tasks-file", str(tf), "--max-examples", "3"])
+  summ = json.loads((snap / "summary.json").read_text())
+  assert summ["step"] == 9 and not summ["simulated"] and [t["task"] for t in summ["tasks"]] == ["mc_a"] and summ["tasks"][0]["n"] == 3
+  direct = runner.run_snapshot_eval(tr.model, cfg, run_id="r2", step=9, which="mc_a", max_examples=3, print_fn=lambda *_: None)
+  assert summ["results"]["mc_a"] == direct["mc_a"]                   # same weights, same answer
+
+
+def test_simulated_model_hits_its_target_accuracies_through_the_real_plumbing(tmp_path):
+  from nmoe_b200.eval import runner
+  from nmoe_b200.eval.simulate import SimConfig, SimulatedModel, simulate_suite
+  from nmoe_b200.metrics import MetricsWriter
+  tf = _task_file(tmp_path, n=400)
+  tasks = runner.select_tasks(str(tf), "all")
+  res = simulate_suite(tasks, SimConfig(acc_choices=0.7, acc_span=0.4, seed=1), max_examples=400)
+  assert abs(res["mc_a"]["acc"] - 0.7) < 0.06 and abs(res["qa"]["acc"] - 0.4) < 0.07 and res["qa"]["f1"] >= res["qa"]["acc"]
+  assert abs(res["mc_a"]["centered_acc"] - (res["mc_a"]["acc"] - 0.25) / 0.75) < 1e-9
+  assert res["offline"]["n"] == 400 and abs(res["offline"]["acc"] - 0.7) < 0.06          # unreadable source: synthetic examples
+  assert simulate_suite(tasks, SimConfig(acc_choices=0.7, acc_span=0.4, seed=1), 400) == res  # deterministic
+  assert simulate_suite(tasks, SimConfig(acc_choices=0.7, acc_span=0.4, seed=2), 400) != res
+  m = SimulatedModel(SimConfig(acc_unittest=0.25, acc_judge=0.9))
+  assert abs(sum(m.passes_tests(f"p{i}") for i in range(2000)) / 2000 - 0.25) < 0.03
+  assert abs(sum(m.judged_keep(f"p{i}") for i in range(2000)) / 2000 - 0.9) < 0.03
+  # through the command: no model file needed, summary and metric rows written
+  cfg = _cfg(metrics_dir=str(tmp_path / "m"), eval_tasks_file=str(tf), eval_tasks="core")
+  snap = tmp_path / "snap"
+  snap.mkdir()
+  import dataclasses
+  (snap / "config.json").write_text(json.dumps({k: v for k, v in dataclasses.asdict(cfg).items() if not k.startswith("_")}, default=str))
+  runner.main(["--snapshot", str(snap), "--run", "sim", "--step", "3", "--simulate", "--sim-acc-choices", "0.9", "--max-examples", "300"])
+  summ = json.loads((snap / "summary.json").read_text())
+  assert summ["simulated"] and abs(summ["CORE"] - (0.9 - 0.25) / 0.75) < 0.08 and {t["task"] for t in summ["tasks"]} == {"mc_a", "mc_b", "qa"}
+  w = MetricsWriter("sim", cfg.metrics_dir, 0)
+  assert abs(w.query("eval/CORE")[0][1] - summ["CORE"]) < 1e-12
+  w.close()

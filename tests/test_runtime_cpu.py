@@ -302,3 +302,22 @@ def test_zero2_buckets_walk_parameters_backwards_and_pin_the_checkpoint_layout()
   import pytest
   with pytest.raises(ValueError, match="layout"):
     z.load_state_dict(sd)
+
+
+def test_checkpoint_write_timing_interval_hint_and_run_info(tmp_path, monkeypatch):
+  from nmoe_b200.checkpoint import Checkpointer, read_latest_run_info
+  from nmoe_b200.train import train
+  ck = Checkpointer(str(tmp_path / "plain"), async_io=False)
+  assert ck.recommend_interval(400.0) == 1                       # nothing timed yet
+  ck.submit(tmp_path / "plain" / "iter_0000001" / "dp_rank_000.pt", {"step": 1, "w": torch.zeros(4)}, 1, 1)
+  assert ck.last_write_ms > 0 and ck.last_stage_ms >= 0
+  ck.last_write_ms = 9000.0                                      # a 9 s save against 400 ms steps
+  assert ck.recommend_interval(400.0) == 30 and ck.recommend_interval(400.0, safety=1.0) == 23
+  assert ck.recommend_interval(0.0) == 1
+  ck.close()
+  assert read_latest_run_info(tmp_path / "none") is None
+  monkeypatch.setenv("NMOE_RUN", "info")
+  cfg = _tiny_cfg(tmp_path / "r")
+  train(cfg)
+  info = read_latest_run_info(cfg.checkpoint_dir)
+  assert info["step"] == 6 and info["tokens"] == 6 * cfg.batch_size * cfg.seq_len and info["E"] == cfg.n_routed_experts
