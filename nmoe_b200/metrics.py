@@ -6,7 +6,7 @@ value DOUBLE, PRIMARY KEY(run, tag, step))`` with insert-or-replace semantics, o
 ``{metrics_dir}/{run}/rank_{r}.duckdb``.  DuckDB is used when importable; otherwise the same
 table lives in an SQLite file ``rank_{r}.sqlite`` (a dashboard only needs the table).
 Tags follow the reference: train/loss, optimizer/lr, throughput/*, efficiency/*, memory/*,
-router/layer_NN/*, router_agg/*, time_ms/r{rank}/*, gpu/{i}/*.
+router/layer_NN/*, router_agg/*, time_ms/r{rank}/*, comm/r{rank}/*, gpu/{i}/*, gpu_agg/*.
 """
 from __future__ import annotations
 
@@ -275,6 +275,9 @@ def log_training_step(ms: MetricsSession, step: int, trainer, loss: torch.Tensor
     items.append(("train/grad_norm", gn.item()))
   for tag, v in ms.timers.drain().items():
     items.append((tag.replace("time_ms/", f"time_ms/r{ms.rank}/"), v))
+  rdep = getattr(trainer.model, "rdep", None)
+  if rdep is not None and hasattr(rdep, "comm_counters"):
+    items += [(f"comm/r{ms.rank}/{k}", v) for k, v in rdep.comm_counters().items()]
   rs_line = ""
   loads = trainer.model.expert_loads() if hasattr(trainer.model, "expert_loads") else None
   if loads is not None:

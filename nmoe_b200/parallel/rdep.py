@@ -155,6 +155,8 @@ class Rdep:
     # count of every call (one 4-byte host read per MoE forward) and can never fall short
     self.rows_mode = os.environ.get("NMOE_RDEP_ROWS", "stale")
     self.rows_overflows = 0
+    self.rows_last = 0            # padded expert rows of the newest call whose count has reached the host
+    self.rows_dropped = 0         # rows that calls skipped because they did not fit the bound, since the start
     self._seen = torch.full((256,), -1, dtype=torch.int32).pin_memory() if self.device.type == "cuda" else None
     self._seen_next = 0
     self._seen_pending = collections.deque()
@@ -203,14 +205,25 @@ class Rdep:
       if n < 0:
         break                                   # that kernel has not run yet; later entries have not either
       self._seen_pending.popleft()
+      self.rows_last = n * 128
       if n > limit_tiles:
         self.rows_overflows += 1
+        self.rows_dropped += (n - limit_tiles) * 128
         print(f"[nmoe] rank {self.rank}: {n * 128} expert rows arrived where {limit_tiles * 128} were provided for; "
               f"{(n - limit_tiles) * 128} rows of that call were not computed (raising the bound)", file=sys.stderr, flush=True)
       need = n * 128
       if need > 0.92 * self._rows_hwm:
         g = self._rows_grain
         self._rows_hwm = min(self.capacity, (int(need * 1.08) + g - 1) // g * g)
+
+  def comm_counters(self) -> dict:
+    """Host-side counters of the dispatch path for the metrics store (``comm/*``, nmoe/metrics.py:355-381): rows
+    received by this rank in the newest call whose count is known, the receive capacity and its utilisation, the
+    current row bound, and rows dropped since the start.  Reads nothing from the device."""
+    return {"M_recv": float(self.rows_last), "capacity": float(self.capacity),
+            "capacity_utilization": self.rows_last / self.capacity if self.capacity else 0.0,
+            "row_bound": float(min(self.capacity, self._rows_hwm)), "dropped_rows": float(self.rows_dropped),
+            "overflow_calls": float(self.rows_overflows)}
 
   def plan(self, eid: torch.Tensor) -> Plan:
     T, K = eid.shape

@@ -321,3 +321,19 @@ def test_checkpoint_write_timing_interval_hint_and_run_info(tmp_path, monkeypatc
   train(cfg)
   info = read_latest_run_info(cfg.checkpoint_dir)
   assert info["step"] == 6 and info["tokens"] == 6 * cfg.batch_size * cfg.seq_len and info["E"] == cfg.n_routed_experts
+
+
+def test_dispatch_counters_follow_the_polled_row_counts(capsys):
+  """``Rdep.comm_counters`` reports what ``_poll_seen`` has learnt from pinned memory; no device is involved."""
+  import collections
+  from nmoe_b200.parallel.rdep import Rdep
+  r = Rdep.__new__(Rdep)
+  r.rank, r.capacity, r._rows_hwm, r._rows_grain = 0, 8192, 4096, 4096
+  r.rows_overflows = r.rows_last = r.rows_dropped = 0
+  r._seen = torch.tensor([20, -1, 40], dtype=torch.int32)            # tiles of 128 rows; -1 = that kernel has not run yet
+  r._seen_pending = collections.deque([(0, 32), (2, 32), (1, 32)])
+  r._poll_seen()
+  c = r.comm_counters()
+  assert c["M_recv"] == 5120 and c["dropped_rows"] == 1024 and c["overflow_calls"] == 1 and c["capacity_utilization"] == 0.625
+  assert c["row_bound"] == 8192 and list(r._seen_pending) == [(1, 32)]
+  assert "1024 rows of that call were not computed" in capsys.readouterr().err
