@@ -18,10 +18,17 @@ from .errors import PipelineError
 def cmd_prep(a) -> int:
   from .prep import ParallelPrepPipeline, PrepConfig, PrepPipeline
   from .sources import create_source
-  kw = {"paths": a.input} if a.source in ("jsonl", "jsonl_zst", "text", "arrow", "parquet") else \
-      {"dataset": a.dataset, "subset": a.subset, "split": a.split}
-  if a.source not in ("text",):
-    kw["text_field"] = a.text_field
+  if a.source in ("arxiv_tars", "ar5iv", "arxiv_paired"):
+    # --input is the directory of bulk tars (of ar5iv pages for `ar5iv`); --html-dir the ar5iv tree for the paired form
+    kw = {"arxiv_tars": {"tar_dir": a.input}, "ar5iv": {"html_dir": a.input},
+          "arxiv_paired": {"tar_dir": a.input, "html_dir": a.html_dir}}[a.source]
+    if a.source == "arxiv_paired" and not a.html_dir:
+      raise SystemExit("--source arxiv_paired needs --html-dir")
+  else:
+    kw = {"paths": a.input} if a.source in ("jsonl", "jsonl_zst", "text", "arrow", "parquet") else \
+        {"dataset": a.dataset, "subset": a.subset, "split": a.split}
+    if a.source not in ("text",):
+      kw["text_field"] = a.text_field
   cfg = PrepConfig(output_dir=a.output, dataset=a.name, version=a.version, tokenizer=a.tokenizer, num_shards=a.num_shards,
                    max_documents=a.max_documents, max_tokens=a.max_tokens)
   audited = None
@@ -593,7 +600,9 @@ def build_parser() -> argparse.ArgumentParser:
   ap = argparse.ArgumentParser(prog="nmoe_b200.data.cli")
   sub = ap.add_subparsers(dest="command", required=True)
   p = sub.add_parser("prep"); p.set_defaults(fn=cmd_prep)
-  p.add_argument("--source", default="jsonl"); p.add_argument("--input"); p.add_argument("--dataset"); p.add_argument("--subset")
+  p.add_argument("--source", default="jsonl", help="jsonl | jsonl_zst | text | arrow | parquet | hf | hffs | arxiv_tars | ar5iv | arxiv_paired")
+  p.add_argument("--html-dir", help="ar5iv tree ({tier}/{yymm}/{id}.html) for --source arxiv_paired")
+  p.add_argument("--input"); p.add_argument("--dataset"); p.add_argument("--subset")
   p.add_argument("--split", default="train"); p.add_argument("--text-field", default="text"); p.add_argument("--output", required=True)
   p.add_argument("--name", required=True); p.add_argument("--version", default="v1"); p.add_argument("--tokenizer", default="o200k_harmony")
   p.add_argument("--num-shards", type=int, default=8); p.add_argument("--workers", type=int, default=1)

@@ -304,6 +304,9 @@ def create_source(kind: str, **kw) -> DataSource:
   kinds = {"jsonl": JSONLSource, "jsonl_zst": JSONLZstSource, "text": TextFileSource, "arrow": ArrowSource,
            "parquet": ArrowSource, "hf": HuggingFaceSource, "huggingface": HuggingFaceSource,
            "hffs": HfFileSystemSource}
+  if kind in ("arxiv_tars", "ar5iv", "arxiv_paired"):
+    from . import arxiv_sources as A      # imports this module, hence not at the top
+    return {"arxiv_tars": A.ArxivTarSource, "ar5iv": A.Ar5ivSource, "arxiv_paired": A.ArxivPairedSource}[kind](**kw)
   if kind not in kinds:
-    raise SourceNotFoundError(f"unknown source kind '{kind}'; expected one of {sorted(kinds)}")
+    raise SourceNotFoundError(f"unknown source kind '{kind}'; expected one of {sorted(kinds) + ['ar5iv', 'arxiv_paired', 'arxiv_tars']}")
   return kinds[kind](**kw)

@@ -100,6 +100,22 @@ class EventTimers:
     return {k: sum(v) / len(v) for k, v in sums.items()}
 
 
+def param_counts(model, cfg, world: int = 1) -> Tuple[int, int]:
+  """(parameters of the whole model, parameters a token touches).  Routed experts are rank-local, so the job holds
+  ``world`` times what this rank sees; a token uses ``n_activated_experts`` of ``n_routed_experts`` of them
+  (nmoe/metrics.py:384-421)."""
+  experts, dense = model.param_sets() if hasattr(model, "param_sets") else ([], list(model.parameters()))
+  n_exp = sum(p.numel() for p in experts) * max(1, world)
+  n_dense = sum(p.numel() for p in dense)
+  frac = cfg.n_activated_experts / cfg.n_routed_experts if getattr(cfg, "n_routed_experts", 0) else 0.0
+  return n_dense + n_exp, n_dense + int(n_exp * frac)
+
+
+def param_summary(model, cfg, world: int = 1) -> str:
+  total, active = param_counts(model, cfg, world)
+  return f"({total / 1e9:.2f}B params {active / 1e9:.2f}B active)"
+
+
 def flops_per_token(cfg, seq_len: Optional[int] = None) -> float:
   """6 * (active non-embedding params) + 6 * L * heads * (nope + rope + v) * seq (nmoe/metrics.py:69-124)."""
   S = seq_len or cfg.seq_len

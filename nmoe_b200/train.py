@@ -112,6 +112,8 @@ def train(cfg: Config) -> dict:
   loader, plan = build_loader(cfg, rank, world)
   trainer = Trainer(cfg, rank=rank, world=world, device=device)
   metrics = MetricsSession(run_id or f"run_{int(time.time())}", cfg.metrics_dir, rank, world, trainer.model, cfg)
+  from .metrics import param_summary
+  print0(f"[nmoe] {cfg.preset or 'model'} {param_summary(trainer.model, cfg, world)} on {world} rank(s), run {run_id}")
   start_step, tokens_seen = load_checkpoint(checkpointer, trainer, loader, plan, cfg, rank, print0)
   trainer.step_num, trainer.tokens_seen = start_step, tokens_seen
   fp = fingerprint(cfg)

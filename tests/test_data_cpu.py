@@ -480,3 +480,73 @@ def test_http_fetcher_continues_a_transfer_that_was_cut(tmp_path):
     httpd.shutdown()
   assert dest.read_bytes() == payload
   assert seen[0] is None and seen[1] == f"bytes={len(payload) // 2}-"
+
+
+def _ar5iv_page(pid, body):
+  return (f'<html><head><link rel="canonical" href="https://arxiv.org/abs/{pid}"></head><body><article class="ltx_document">'
+          f'<h1 class="ltx_title ltx_title_document">Paper {pid}</h1><div class="ltx_authors"><span class="ltx_personname">A. Uthor</span></div>'
+          f'<section class="ltx_section"><h2>1 Intro</h2><p>{body} <math alttext="x^{{2}}"><msup><mi>x</mi><mn>2</mn></msup></math></p></section>'
+          f'</article></body></html>')
+
+
+def test_arxiv_sources_latex_html_and_paired(tmp_path):
+  """Bulk tars and ar5iv pages as document sources: worker splits over files, quality tiers, pairing of the two formats
+  of one paper, and the whole thing through `create_source` into shards."""
+  from nmoe_b200.data import arxiv_sources as A
+  from nmoe_b200.data.prep import PrepConfig, PrepPipeline
+  from nmoe_b200.data.sources import create_source
+  body = "Deep networks generalise well. " * 30
+  doc = "\\documentclass{article}\\begin{document}\\section{Intro}" + body + "\\end{document}"
+  tars = tmp_path / "tars"
+  tars.mkdir()
+  _bulk_tar(tars / "arXiv_src_2301_001.tar", {"2301.00001": {"main.tex": doc}, "2301.00002": doc, "2301.00009": None,
+                                              "2301.00004": "\\documentclass{article}\\begin{document}tiny\\end{document}"})
+  _bulk_tar(tars / "arXiv_src_2301_002.tar", {"2301.00003": doc, "2301.00001": doc})          # 00001 again: replaced in-month
+  (tars / "arXiv_src_2301_003.tar").write_bytes(b"this is not a tar file")
+  html = tmp_path / "ar5iv"
+  for tier, pid in (("no_problem", "2301.00001v2"), ("warning", "2301.00001"), ("warning", "2301.00003"), ("error", "2301.00002"),
+                    ("no_problem", "2301.07777")):
+    d = html / tier / "2301"
+    d.mkdir(parents=True, exist_ok=True)
+    (d / f"{pid}.html").write_text(_ar5iv_page(pid, f"Rendered from {tier}. " + "Content sentence. " * 12))
+  (html / "no_problem" / "2301" / "2301.08888.html").write_text("<html><body><p>short</p></body></html>")
+
+  latex = A.ArxivTarSource(tars)
+  docs = list(latex)
+  assert [d.doc_id for d in docs] == ["arxiv:2301.00001:latex", "arxiv:2301.00002:latex", "arxiv:2301.00003:latex", "arxiv:2301.00001:latex"]
+  assert latex.stats["too_short"] == 1 and latex.stats["bad_tars"] == 1 and latex.stats["tars"] == 3 and "Deep networks" in docs[0].text
+  w0, w1 = list(A.ArxivTarSource(tars, worker_index=0, num_workers=2)), list(A.ArxivTarSource(tars, worker_index=1, num_workers=2))
+  assert len(w0) == 2 and len(w1) == 2 and {d.metadata["source_tar"] for d in w1} == {"arXiv_src_2301_002.tar"}
+  assert [d.doc_id for d in latex.shard(1, 2)] == [d.doc_id for d in w1]
+  assert len(list(A.ArxivTarSource(tars, max_docs=2))) == 2
+
+  pages = A.Ar5ivSource(html)
+  got = list(pages)
+  assert [d.doc_id for d in got] == ["arxiv:2301.00001:html", "arxiv:2301.07777:html", "arxiv:2301.00001:html", "arxiv:2301.00003:html"]
+  assert got[0].metadata["tier"] == "no_problem" and got[0].metadata["title"].startswith("Paper") and "$x^{2}$" in got[0].text
+  assert pages.stats == {"pages": 5, "kept": 4, "dropped": 1} and pages.estimate_size() == 5
+  assert len(list(A.Ar5ivSource(html, quality_levels=["error"]))) == 1
+  with pytest.raises(ValueError):
+    list(A.Ar5ivSource(html, quality_levels=["perfect"]))
+  assert sorted(d.doc_id for s in (pages.shard(0, 2), pages.shard(1, 2)) for d in s) == sorted(d.doc_id for d in got)
+
+  paired = A.ArxivPairedSource(tars, html)
+  ids = [d.doc_id for d in paired]
+  assert ids == ["arxiv:2301.00001:latex", "arxiv:2301.00001:html", "arxiv:2301.00002:latex", "arxiv:2301.00003:latex", "arxiv:2301.00003:html"]
+  assert paired.stats == {"latex_only": 1, "both_formats": 2, "total_docs": 5}
+  first = list(paired)
+  assert first[0].metadata["has_paired_format"] and first[1].metadata["has_paired_format"] and "has_paired_format" not in first[2].metadata
+  assert "Rendered from no_problem" in first[1].text                      # the better tier's page wins
+  assert [d.doc_id for d in A.ArxivPairedSource(tars, html, emit_both_formats=False)] == [i for i in ids if i.endswith("latex")]
+
+  src = create_source("arxiv_paired", tar_dir=str(tars), html_dir=str(html))
+  m = PrepPipeline(src, PrepConfig(str(tmp_path / "out"), "arxiv", tokenizer="bytes", num_shards=2, log_every=0)).run()
+  assert m.total_documents == 5
+  sinks.verify_manifest(tmp_path / "out")
+  from nmoe_b200.data.cli import main
+  assert main(["prep", "--source", "arxiv_paired", "--input", str(tars), "--html-dir", str(html), "--output", str(tmp_path / "cli"),
+               "--name", "arxiv", "--tokenizer", "bytes", "--num-shards", "2"]) == 0
+  assert sinks.load_manifest(tmp_path / "cli").total_tokens == m.total_tokens
+  assert main(["prep", "--source", "ar5iv", "--input", str(html), "--output", str(tmp_path / "cli2"), "--name", "a5", "--tokenizer", "bytes",
+               "--num-shards", "1"]) == 0
+  assert sinks.load_manifest(tmp_path / "cli2").total_documents == 4

@@ -337,3 +337,16 @@ def test_dispatch_counters_follow_the_polled_row_counts(capsys):
   assert c["M_recv"] == 5120 and c["dropped_rows"] == 1024 and c["overflow_calls"] == 1 and c["capacity_utilization"] == 0.625
   assert c["row_bound"] == 8192 and list(r._seen_pending) == [(1, 32)]
   assert "1024 rows of that call were not computed" in capsys.readouterr().err
+
+
+def test_param_summary_counts_experts_of_all_ranks(tmp_path):
+  from nmoe_b200.metrics import param_counts, param_summary
+  from nmoe_b200.train import Trainer
+  cfg = _tiny_cfg(tmp_path)
+  m = Trainer(cfg).model
+  n = sum(p.numel() for p in m.parameters())
+  experts = sum(p.numel() for p in m.param_sets()[0])
+  total, active = param_counts(m, cfg, 1)
+  assert total == n and active == n - experts + experts * cfg.n_activated_experts // cfg.n_routed_experts
+  assert param_counts(m, cfg, 4)[0] == n + 3 * experts
+  assert param_summary(m, cfg).startswith("(0.00B params")
