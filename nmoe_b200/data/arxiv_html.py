@@ -376,26 +376,61 @@ def load_metadata_snapshot(path: str, categories: Optional[Iterable[str]] = None
 
 class MetadataClient:
   """arXiv API client with the service's rate limit (one request per ``delay`` seconds, up to 100 ids each).
-  ``fetch`` needs network access; ``parse`` works on a saved response."""
+  ``fetch`` / ``get`` / ``search`` need network access; ``parse`` works on a saved response.  ``opener(url) -> str`` can
+  replace the HTTP call (tests, a caching proxy)."""
 
   API = "http://export.arxiv.org/api/query"
 
-  def __init__(self, delay: float = 3.0):
-    self.delay = delay
-    self._last = 0.0
+  def __init__(self, delay: float = 3.0, opener=None, sleep=time.sleep):
+    self.delay, self._last, self._sleep = delay, 0.0, sleep
+    self._open = opener or self._http
 
   parse = staticmethod(parse_atom_feed)
 
+  @staticmethod
+  def _http(url: str) -> str:
+    from urllib.request import urlopen
+    with urlopen(url, timeout=60) as r:
+      return r.read().decode("utf-8")
+
+  def _request(self, query: str) -> str:
+    wait = self.delay - (time.time() - self._last)
+    if wait > 0:
+      self._sleep(wait)
+    self._last = time.time()
+    return self._open(f"{self.API}?{query}")
+
   def fetch(self, arxiv_ids: List[str], batch_size: int = 100) -> Dict[str, PaperMetadata]:
     from urllib.parse import quote
-    from urllib.request import urlopen
     out: Dict[str, PaperMetadata] = {}
     for i in range(0, len(arxiv_ids), batch_size):
       batch = arxiv_ids[i:i + batch_size]
-      wait = self.delay - (time.time() - self._last)
-      if wait > 0:
-        time.sleep(wait)
-      self._last = time.time()
-      with urlopen(f"{self.API}?id_list={quote(','.join(batch))}&max_results={len(batch)}", timeout=30) as r:
-        out.update(parse_atom_feed(r.read().decode("utf-8")))
+      out.update(parse_atom_feed(self._request(f"id_list={quote(','.join(batch))}&max_results={len(batch)}")))
     return out
+
+  def get(self, arxiv_id: str) -> Optional[PaperMetadata]:
+    return self.fetch([arxiv_id]).get(_ID_RE.sub(lambda m: m.group(1), arxiv_id))
+
+  def search(self, category: str, start_date: Optional[str] = None, end_date: Optional[str] = None, max_results: int = 1000,
+             page: int = 200) -> List[PaperMetadata]:
+    """Papers of a category (``cs.LG``), newest first, optionally submitted within [start_date, end_date]
+    (``YYYYMMDD``).  The service pages its answers; this walks the pages until ``max_results`` papers or an empty page
+    (nmoe/data/arxiv/metadata.py:232-291 lists ids the same way)."""
+    from urllib.parse import quote
+    q = f"cat:{category}"
+    if start_date or end_date:
+      q += f" AND submittedDate:[{start_date or '*'} TO {end_date or '*'}]"
+    out: List[PaperMetadata] = []
+    seen = set()
+    while len(out) < max_results:
+      n = min(page, max_results - len(out))
+      got = parse_atom_feed(self._request(f"search_query={quote(q)}&start={len(seen)}&max_results={n}&sortBy=submittedDate&sortOrder=descending"))
+      fresh = [m for k, m in got.items() if k not in seen]
+      if not fresh:
+        break
+      seen.update(got)
+      out += fresh
+    return out[:max_results]
+
+  def list_ids(self, category: str, start_date: Optional[str] = None, end_date: Optional[str] = None, max_results: int = 1000) -> List[str]:
+    return [m.arxiv_id for m in self.search(category, start_date, end_date, max_results) if m.arxiv_id]

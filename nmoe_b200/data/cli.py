@@ -309,6 +309,11 @@ def cmd_flow(a) -> int:
       out = rephrase_batch(eng, tok, texts, num_versions=n_ver, chunk_size=int(rp.get("chunk_size", 2048)),
                            use_style_diversity=bool(rp.get("style_diversity", True)), temperature=float(rp.get("temperature", 0.8)),
                            top_p=float(rp.get("top_p", 0.9)), stop_tokens=[getattr(tok, "eot", -1)], seed=int(rp.get("seed", 0)))
+      if rp.get("filter", True):          # drop rewrites that lost the source's content (lexical bounds, then embeddings)
+        from .rephrase import filter_by_fidelity, semantic_fidelity
+        thr = rp.get("semantic_threshold")
+        sem = semantic_fidelity(model, tok, texts, out, max_ctx=int(rp.get("max_ctx", 4096))) if thr is not None and out else None
+        out = filter_by_fidelity(texts, out, semantic=sem, min_semantic=float(thr or 0.0))
       by_doc = {}
       for r in out:
         by_doc.setdefault(r.doc, []).append(r.text)
@@ -544,7 +549,11 @@ def cmd_rephrase(a) -> int:
   texts = [r[a.text_field] for r in rows]
   eng = Engine(model, max_seq_len=a.max_ctx, max_batch=a.batch_size)
   rew = rephrase_batch(eng, tok, texts, num_versions=a.num_versions, chunk_size=a.chunk_size, stop_tokens=[getattr(tok, "eot", -1)])
-  kept = filter_by_fidelity(texts, rew) if not a.no_filter else rew
+  sem = None
+  if a.semantic_threshold is not None and not a.no_filter:      # embedding-space agreement with the source, same backbone
+    from .rephrase import semantic_fidelity
+    sem = semantic_fidelity(model, tok, texts, rew, max_ctx=a.max_ctx, batch_size=a.batch_size)
+  kept = rew if a.no_filter else filter_by_fidelity(texts, rew, semantic=sem, min_semantic=a.semantic_threshold or 0.0)
   with open(a.output, "w", encoding="utf-8") as f:
     for r in kept:
       f.write(json.dumps({"id": rows[r.doc].get("id", r.doc), "version": r.version, "style": r.style, "text": r.text}) + "\n")
@@ -667,6 +676,7 @@ def build_parser() -> argparse.ArgumentParser:
   p.add_argument("--oracle-keep", type=float, default=0.6); p.add_argument("--keep-precision", type=float, default=0.9)
   p = sub.add_parser("rephrase"); p.set_defaults(fn=cmd_rephrase); model_args(p)
   p.add_argument("--num-versions", type=int, default=1); p.add_argument("--chunk-size", type=int, default=2048); p.add_argument("--no-filter", action="store_true")
+  p.add_argument("--semantic-threshold", type=float, help="also require this cosine similarity to the source in the backbone's embedding space (0.85 is a usual bar)")
   p = sub.add_parser("arxiv-download"); p.set_defaults(fn=cmd_arxiv_download)
   p.add_argument("--output", required=True); p.add_argument("--manifest"); p.add_argument("--fetch", default="s3", choices=["s3", "http", "file"])
   p.add_argument("--base-url"); p.add_argument("--root"); p.add_argument("--aws-profile"); p.add_argument("--start"); p.add_argument("--end")

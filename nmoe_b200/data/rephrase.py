@@ -128,13 +128,46 @@ def compute_fidelity(source: str, rewrite: str) -> Dict[str, float]:
   }
 
 
+@torch.inference_mode()
+def embed_texts(model, tok: Tokenizer, texts: Sequence[str], *, layer: Optional[int] = None, max_ctx: int = 4096,
+                batch_size: int = 16) -> torch.Tensor:
+  """Unit-norm mean-pooled hidden states of the grading backbone at ``layer`` (default: its probe layer), [N, H] on
+  the CPU.  Texts are padded into batches and the padding is masked out of the mean."""
+  from ..serve.model import pool_hidden
+  from .hydra import pad_batch
+  layer = layer if layer is not None else model.cfg.probe_layer
+  dev = next(model.parameters()).device
+  out = []
+  for i in range(0, len(texts), batch_size):
+    docs = [(tok.encode(t)[:max_ctx] or [0]) for t in texts[i:i + batch_size]]
+    ids, pos, mask = pad_batch(docs, max_ctx, dev)
+    _, taps = model(ids, pos, up_to_layer=layer, return_hidden_states=True, no_logits=True)
+    out.append(torch.nn.functional.normalize(pool_hidden(taps[layer], mask), dim=-1).cpu())
+  return torch.cat(out) if out else torch.zeros(0, model.cfg.hidden_size)
+
+
+def semantic_fidelity(model, tok: Tokenizer, sources: Sequence[str], rewrites: Sequence[Rewrite], **kw) -> List[float]:
+  """Cosine similarity, clamped to [0, 1], between each rewrite and its source in the backbone's embedding space
+  (nmoe/data/rephrase.py:296-361).  Each distinct source is embedded once however many versions it has."""
+  used = sorted({r.doc for r in rewrites})
+  src = dict(zip(used, embed_texts(model, tok, [sources[d] for d in used], **kw)))
+  rew = embed_texts(model, tok, [r.text for r in rewrites], **kw)
+  return [float((src[r.doc] * rew[i]).sum().clamp(0.0, 1.0)) for i, r in enumerate(rewrites)]
+
+
 def filter_by_fidelity(sources: Sequence[str], rewrites: Sequence[Rewrite], *, min_length_ratio: float = 0.5,
                        max_length_ratio: float = 2.0, min_word_recall: float = 0.3, min_number_recall: float = 0.8,
-                       max_novel_numbers: float = 0.2) -> List[Rewrite]:
+                       max_novel_numbers: float = 0.2, semantic: Optional[Sequence[float]] = None,
+                       min_semantic: float = 0.85) -> List[Rewrite]:
+  """Rewrites that pass the lexical bounds and, when ``semantic`` scores (one per rewrite, from ``semantic_fidelity``)
+  are given, reach ``min_semantic``."""
+  if semantic is not None and len(semantic) != len(rewrites):
+    raise ValueError("one semantic score per rewrite is needed")
   keep = []
-  for r in rewrites:
+  for i, r in enumerate(rewrites):
     f = compute_fidelity(sources[r.doc], r.text)
     if (min_length_ratio <= f["length_ratio"] <= max_length_ratio and f["word_recall"] >= min_word_recall
-        and f["number_recall"] >= min_number_recall and f["novel_numbers"] <= max_novel_numbers):
+        and f["number_recall"] >= min_number_recall and f["novel_numbers"] <= max_novel_numbers
+        and (semantic is None or semantic[i] >= min_semantic)):
       keep.append(r)
   return keep

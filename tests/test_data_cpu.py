@@ -550,3 +550,29 @@ def test_arxiv_sources_latex_html_and_paired(tmp_path):
   assert main(["prep", "--source", "ar5iv", "--input", str(html), "--output", str(tmp_path / "cli2"), "--name", "a5", "--tokenizer", "bytes",
                "--num-shards", "1"]) == 0
   assert sinks.load_manifest(tmp_path / "cli2").total_documents == 4
+
+
+def test_arxiv_metadata_client_pages_rate_limits_and_strips_versions():
+  from urllib.parse import parse_qs, urlparse
+  from nmoe_b200.data.arxiv_html import MetadataClient
+  entry = lambda i: (f"<entry><id>http://arxiv.org/abs/2301.{i:05d}v1</id><title>Paper {i}</title><summary>S</summary>"
+                     f"<author><name>A</name></author><category term='cs.LG'/><published>2023-01-{1 + i % 28:02d}T00:00:00Z</published></entry>")
+  feed = lambda es: "<feed xmlns='http://www.w3.org/2005/Atom'>" + "".join(es) + "</feed>"
+  calls, naps = [], []
+  def opener(url):
+    q = parse_qs(urlparse(url).query)
+    calls.append(q)
+    if "id_list" in q:
+      return feed(entry(int(x.split(".")[1][:5])) for x in q["id_list"][0].split(","))
+    start, n = int(q["start"][0]), int(q["max_results"][0])
+    return feed(entry(i) for i in range(start, min(start + n, 450)))            # the category holds 450 papers
+  c = MetadataClient(delay=3.0, opener=opener, sleep=naps.append)
+  got = c.search("cs.LG", "20230101", "20230131", max_results=1000, page=200)
+  assert len(got) == 450 and got[0].arxiv_id == "2301.00000" and got[-1].title == "Paper 449"
+  assert [int(q["start"][0]) for q in calls] == [0, 200, 400, 450] and "submittedDate:[20230101 TO 20230131]" in calls[0]["search_query"][0]
+  assert len(naps) == 3 and all(0 < t <= 3.0 for t in naps)                   # every request after the first waits its turn
+  assert len(c.search("cs.LG", max_results=250)) == 250 and c.list_ids("cs.LG", max_results=3) == ["2301.00000", "2301.00001", "2301.00002"]
+  calls.clear()
+  many = c.fetch([f"2301.{i:05d}" for i in range(230)])
+  assert len(many) == 230 and [len(q["id_list"][0].split(",")) for q in calls] == [100, 100, 30]
+  assert c.get("2301.00007v3").title == "Paper 7" and c.get("2301.00007").arxiv_id == "2301.00007"

@@ -105,6 +105,20 @@ def test_rephrase_pipeline_and_fidelity_filter():
   bad = RP.Rewrite(0, 1, "casual", "The reactor melted in 99 minutes at 3000 degrees, killing 4.")
   kept = RP.filter_by_fidelity(["The reactor reached 450 degrees in 12 minutes."], [good, bad])
   assert kept == [good]
+  # embedding-space agreement with the source: identical text scores 1, batches and padding do not change a score
+  src = ["The reactor reached 450 degrees in 12 minutes.", "Cats sleep most of the day, often in sunny places near windows."]
+  same = [RP.Rewrite(0, 0, "formal", src[0]), RP.Rewrite(1, 0, "formal", src[1]), RP.Rewrite(0, 1, "casual", "zzzz qqqq 0000 !!!!")]
+  sem = RP.semantic_fidelity(m, tok, src, same, max_ctx=64, batch_size=2)
+  assert abs(sem[0] - 1.0) < 1e-5 and abs(sem[1] - 1.0) < 1e-5 and sem[2] < sem[0] and all(0.0 <= v <= 1.0 for v in sem)
+  one_by_one = RP.semantic_fidelity(m, tok, src, same, max_ctx=64, batch_size=1)
+  assert all(abs(a - b) < 1e-5 for a, b in zip(sem, one_by_one))
+  e = RP.embed_texts(m, tok, src, max_ctx=64)
+  assert e.shape == (2, m.cfg.hidden_size) and torch.allclose(e.norm(dim=-1), torch.ones(2), atol=1e-5)
+  lex_ok = [RP.Rewrite(0, 0, "formal", src[0]), RP.Rewrite(0, 1, "casual", src[0] + " Indeed.")]
+  assert RP.filter_by_fidelity(src, lex_ok, semantic=[0.99, 0.5], min_semantic=0.85) == lex_ok[:1]
+  import pytest
+  with pytest.raises(ValueError):
+    RP.filter_by_fidelity(src, lex_ok, semantic=[0.9])
 
 
 def test_cli_train_grade_roundtrip(tmp_path):
