@@ -598,9 +598,29 @@ def cmd_arxiv_prep(a) -> int:
 
 
 def cmd_stack_v2(a) -> int:
+  """The Stack v2 ids -> text.  Two forms: ``--input-root`` (the id table as downloaded, parquet) with ``--output-root``,
+  ``--top-n`` and worker indices: popularity selection, blobs from the Software Heritage bucket (``--s3``) or a mirror
+  directory (``--blobs``), rotating compressed JSONL parts; or ``--table`` (JSONL) with ``--blobs`` and ``--output``:
+  every listed file that is present, into one JSONL."""
+  if a.input_root:
+    from . import stack_v2 as S
+    if not a.output_root or a.top_n is None:
+      raise SystemExit("--input-root needs --output-root and --top-n")
+    if not (a.blobs or a.s3):
+      raise SystemExit("name the blob store: --blobs DIR (a mirror) or --s3 (the Software Heritage bucket)")
+    blobs = S.DirBlobs(a.blobs) if a.blobs else S.S3Blobs()
+    truth = lambda v: str(v).strip().lower() in ("1", "true", "t", "yes", "y")
+    summ = S.run(a.input_root, a.output_root, worker_index=a.worker_index, num_workers=a.num_workers, top_n=a.top_n, blobs=blobs,
+                 min_bytes=a.min_bytes, max_bytes=a.max_bytes or 256_000, exclude_vendor=truth(a.exclude_vendor),
+                 exclude_generated=truth(a.exclude_generated), max_files_per_repo=a.max_files_per_repo,
+                 languages=a.languages.split(",") if a.languages else None, threads=a.threads)
+    print(json.dumps({k: summ[k] for k in ("scanned", "selected", "written", "missing", "binary", "oversize")}))
+    return 0
+  if not (a.table and a.blobs and a.output):
+    raise SystemExit("stack-v2-materialize needs --input-root ..., or --table with --blobs and --output")
   from .arxiv import iter_stack_v2, write_jsonl
   langs = set(a.languages.split(",")) if a.languages else None
-  n = write_jsonl(iter_stack_v2(a.table, a.blobs, langs, a.max_bytes), a.output)
+  n = write_jsonl(iter_stack_v2(a.table, a.blobs, langs, a.max_bytes or (1 << 20)), a.output)
   print(f"{n} files -> {a.output}")
   return 0
 
@@ -686,8 +706,13 @@ def build_parser() -> argparse.ArgumentParser:
   p.add_argument("--input", required=True); p.add_argument("--output", required=True); p.add_argument("--min-chars", type=int, default=500)
   p.add_argument("--bulk", action="store_true", help="--input holds arXiv's monthly bulk tars")
   p = sub.add_parser("stack-v2-materialize"); p.set_defaults(fn=cmd_stack_v2)
-  p.add_argument("--table", required=True); p.add_argument("--blobs", required=True); p.add_argument("--output", required=True)
-  p.add_argument("--languages"); p.add_argument("--max-bytes", type=int, default=1 << 20)
+  p.add_argument("--table"); p.add_argument("--blobs"); p.add_argument("--output")
+  p.add_argument("--languages"); p.add_argument("--max-bytes", type=int, help="default 256000 with --input-root, 1 MiB with --table")
+  p.add_argument("--input-root", help="the id table: {root}/data/**/*.parquet"); p.add_argument("--output-root")
+  p.add_argument("--worker-index", type=int, default=0); p.add_argument("--num-workers", type=int, default=1)
+  p.add_argument("--top-n", type=int, help="files to keep from this worker's slice of the table, most popular first")
+  p.add_argument("--min-bytes", type=int, default=256); p.add_argument("--exclude-vendor", default="true"); p.add_argument("--exclude-generated", default="true")
+  p.add_argument("--max-files-per-repo", type=int, default=200); p.add_argument("--s3", action="store_true"); p.add_argument("--threads", type=int, default=16)
   return ap
 
 

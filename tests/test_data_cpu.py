@@ -576,3 +576,100 @@ def test_arxiv_metadata_client_pages_rate_limits_and_strips_versions():
   many = c.fetch([f"2301.{i:05d}" for i in range(230)])
   assert len(many) == 230 and [len(q["id_list"][0].split(",")) for q in calls] == [100, 100, 30]
   assert c.get("2301.00007v3").title == "Paper 7" and c.get("2301.00007").arxiv_id == "2301.00007"
+
+
+def test_stack_v2_selection_fetch_and_rotating_output(tmp_path):
+  """Id table (parquet, file-level and repository-level rows) -> popularity selection with per-repository caps and
+  path / vendor / size filters -> blobs from a mirror -> rotating compressed parts."""
+  import gzip as gz
+  import random
+  import pyarrow as pa
+  import pyarrow.parquet as pq
+  from nmoe_b200.data import stack_v2 as S
+  from nmoe_b200.data.cli import main
+  assert S.skip_path("src/node_modules/x/index.js") and S.skip_path("Cargo.lock") and S.skip_path("a/b/logo.PNG") and S.skip_path("lib/jquery.min.js")
+  assert not S.skip_path("src/build_utils.py") and not S.skip_path("vendor.py") and not S.skip_path("docs/dist.md")
+  assert S.decode_text(b"\x00\x01\x02binary") is None and S.decode_text("caf\xe9".encode("latin-1"), "") == "caf\xe9"
+  assert S.decode_text("héllo".encode("utf-16"), "utf-16") == "héllo" and S.looks_binary(bytes(range(1, 9)) * 100)
+
+  rnd = random.Random(0)
+  rows = []
+  for i in range(300):
+    repo = f"org/repo{i % 12}"
+    rows.append({"blob_id": f"b{i:04d}", "src_encoding": "utf-8", "path": f"src/f{i}.py", "repo_name": repo, "language": "Python",
+                 "is_vendor": i % 50 == 0, "is_generated": i % 60 == 1, "length_bytes": 300 + i, "star_events_count": rnd.randint(0, 5000),
+                 "fork_events_count": rnd.randint(0, 500), "detected_licenses": ["MIT"], "license_type": "permissive"})
+  rows[5]["path"] = "node_modules/dep/index.js"
+  rows[6]["length_bytes"] = 10
+  rows[7]["length_bytes"] = 10 ** 7
+  brute = [S.FileRef.from_row(r) for r in rows]
+  ok = [f for f in brute if not (f.is_vendor or f.is_generated or S.skip_path(f.path) or not 256 <= f.length_bytes <= 256_000)]
+  def expected(top_n, cap):
+    by_repo = {}
+    for f in sorted(ok, key=lambda f: (f.score, f.blob_id), reverse=True):
+      if len(by_repo.setdefault(f.repo_name, [])) < cap:
+        by_repo[f.repo_name].append(f)
+    return sorted((f for v in by_repo.values() for f in v), key=lambda f: (f.score, f.blob_id), reverse=True)[:top_n]
+  for top_n, cap in ((40, 5), (10, 200), (500, 3), (7, 1)):
+    st = {}
+    got = S.select_top(rows, top_n, max_files_per_repo=cap, stats=st)
+    assert [f.blob_id for f in got] == [f.blob_id for f in expected(top_n, cap)], (top_n, cap)
+    shuffled = rows[:]
+    rnd.shuffle(shuffled)
+    assert [f.blob_id for f in S.select_top(shuffled, top_n, max_files_per_repo=cap)] == [f.blob_id for f in got]      # order-independent
+    assert st["scanned"] == 300 and st["selected"] == len(got)
+  assert S.select_top(rows, 5, languages=["rust"]) == []
+  forks = [dict(rows[20], repo_name=f"fork{k}/repo") for k in range(5)]          # the same blob in five forks: once
+  st = {}
+  assert len({f.blob_id for f in S.select_top(rows + forks, 300, stats=st)}) == len(S.select_top(rows + forks, 300)) and st["duplicates"] == 5
+
+  # on disk: one file-level parquet and one repository-level parquet with a `files` list; a blob mirror
+  root = tmp_path / "stack" / "data" / "Python"
+  root.mkdir(parents=True)
+  pq.write_table(pa.Table.from_pylist(rows[:150]), str(root / "part0.parquet"))
+  grouped = {}
+  for r in rows[150:]:
+    grouped.setdefault(r["repo_name"], []).append({k: v for k, v in r.items() if k != "repo_name"})
+  pq.write_table(pa.Table.from_pylist([{"repo_name": k, "files": v} for k, v in grouped.items()]), str(root / "part1.parquet"))
+  assert sum(1 for _ in S.iter_table(S.table_files(tmp_path / "stack"))) == 300
+  mirror = tmp_path / "mirror"
+  mirror.mkdir()
+  want = expected(30, 4)
+  for k, f in enumerate(want):
+    body = f"# {f.path}\nprint({k})\n".encode()
+    if k == 3:
+      body = b"\x00\x00\x00 not text"
+    if k == 4:
+      continue                                                   # missing from the mirror
+    (mirror / f"{f.blob_id}.gz").write_bytes(gz.compress(body)) if k % 2 else (mirror / f.blob_id).write_bytes(body)
+  out = tmp_path / "out"
+  assert main(["stack-v2-materialize", "--input-root", str(tmp_path / "stack"), "--output-root", str(out), "--top-n", "30",
+               "--max-files-per-repo", "4", "--blobs", str(mirror), "--threads", "4"]) == 0
+  summ = json.loads((out / "worker_0000" / "summary.json").read_text())
+  assert (summ["selected"], summ["written"], summ["missing"], summ["binary"]) == (30, 28, 1, 1) and len(summ["parts"]) == 1
+  part = out / "worker_0000" / summ["parts"][0]
+  if part.suffix == ".zst":
+    import zstandard
+    text = zstandard.ZstdDecompressor().stream_reader(open(part, "rb")).read().decode()
+  else:
+    text = gz.open(part, "rt").read()
+  got = [json.loads(l) for l in text.splitlines()]
+  assert [g["id"] for g in got] == [f.blob_id for k, f in enumerate(want) if k not in (3, 4)]
+  assert got[0]["text"].startswith("# src/") and got[0]["repo_name"].startswith("org/") and got[0]["detected_licenses"] == ["MIT"] and got[0]["score"] > 0
+  # two workers split the table files; rotation by rows
+  w = S.RotatingJsonl(tmp_path / "rot", max_rows=3, compression="none")
+  for i in range(8):
+    w.write({"i": i})
+  w.close()
+  assert w.parts == ["part_00000.jsonl.none", "part_00001.jsonl.none", "part_00002.jsonl.none"] and w.rows == 8
+  s1 = S.run(tmp_path / "stack", tmp_path / "two", worker_index=1, num_workers=2, top_n=5, blobs=S.DirBlobs(mirror), print_fn=lambda *_: None)
+  assert s1["table_files"] == ["part1.parquet"] and s1["scanned"] == 150
+  # the bucket through the command-line client
+  calls = []
+  def fake_run(cmd, capture_output=True):
+    calls.append(cmd)
+    import types
+    return types.SimpleNamespace(returncode=0 if "b0001" in cmd[3] else 1, stdout=gz.compress(b"x = 1\n") if "b0001" in cmd[3] else b"")
+  s3 = S.S3Blobs(run=fake_run, client=None)
+  s3.client = None
+  assert s3.get("b0001") == b"x = 1\n" and s3.get("nope") is None and calls[0][:4] == ["aws", "s3", "cp", "s3://softwareheritage/content/b0001"]
