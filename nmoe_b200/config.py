@@ -159,6 +159,7 @@ class Config:
   validation_steps: int = 100
   profiling_enabled: bool = False
   profiling_steps: int = 10
+  profiling_skip: int = 2             # steps of the run that pass before the profiler starts (allocator, caches warm)
   profiling_output_dir: str = "/data/profiles"
 
   # ---- evaluation

@@ -24,6 +24,7 @@ from torch.utils.checkpoint import checkpoint
 from .. import ops
 from ..config import Config
 from ..parallel.rdep import Rdep
+from ..utils.profiling import scope
 from .attention import get_attention
 from .mlp import MLP
 from .moe import MoE
@@ -54,6 +55,8 @@ class TransformerBlock(nn.Module):
       self.ffn = MLP(cfg.dim, cfg.inter_dim, dtype)
     self.init_std = 0.02 / (2 * (layer_id + 1)) ** 0.5
     self.ckpt = cfg.activation_checkpoint
+    self._scope_attn = f"block_{layer_id:02d}/attn_{'global' if self.is_global else 'local'}"
+    self._scope_ffn = f"block_{layer_id:02d}/{'moe' if self.is_moe else 'mlp'}"
 
   def init_weights(self) -> None:
     self.attn_norm.weight.data.fill_(1.0)
@@ -68,11 +71,13 @@ class TransformerBlock(nn.Module):
     return self.ffn(self.ffn_norm(x))
 
   def forward(self, x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
-    if self.ckpt != "none" and torch.is_grad_enabled():
-      x = x + checkpoint(self._attn, x, cos, sin, use_reentrant=False)
-    else:
-      x = x + self._attn(x, cos, sin)
-    return x + self._ffn(x)
+    with scope(self._scope_attn):
+      if self.ckpt != "none" and torch.is_grad_enabled():
+        x = x + checkpoint(self._attn, x, cos, sin, use_reentrant=False)
+      else:
+        x = x + self._attn(x, cos, sin)
+    with scope(self._scope_ffn):
+      return x + self._ffn(x)
 
 
 class Transformer(nn.Module):
@@ -127,14 +132,16 @@ class Transformer(nn.Module):
 
   # ------------------------------------------------------------------ forward
   def hidden(self, tokens: torch.Tensor) -> torch.Tensor:
-    x = ops.embedding(tokens, self.embedding, MUP_EMBED_SCALE)
+    with scope("embed"):
+      x = ops.embedding(tokens, self.embedding, MUP_EMBED_SCALE)
     S = tokens.size(1)
     cos, sin = self.rope.cos[:S], self.rope.sin[:S]
     for m in self.moe_layers():
       m.loads.zero_()
     for blk in self.blocks:
       x = blk(x, cos, sin)
-    return self.norm(x)
+    with scope("final_norm"):
+      return self.norm(x)
 
   def forward(self, tokens: torch.Tensor) -> torch.Tensor:
     return ops.linear(self.hidden(tokens), self.lm_head) * LOGIT_SCALE
@@ -142,8 +149,9 @@ class Transformer(nn.Module):
   def loss(self, tokens: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
     """Mean CE over targets != eos_token_id (nmoe/train.py:102-105)."""
     h = self.hidden(tokens)
-    return ops.lm_head_loss(h.reshape(-1, h.size(-1)), self.lm_head, targets.reshape(-1), self.cfg.eos_token_id,
-                            LOGIT_SCALE)
+    with scope("lm_head_loss"):
+      return ops.lm_head_loss(h.reshape(-1, h.size(-1)), self.lm_head, targets.reshape(-1), self.cfg.eos_token_id,
+                              LOGIT_SCALE)
 
   @torch.no_grad()
   def expert_loads(self) -> Optional[torch.Tensor]:

@@ -23,6 +23,7 @@ from .config import Config, fingerprint, from_toml
 from .log import print0
 from .models.transformer import Transformer
 from .opt import Optimizer
+from .utils.profiling import StepProfiler, scope
 
 
 class Trainer:
@@ -76,9 +77,9 @@ class Trainer:
     self.lr = self.opt.begin_step(self.step_num, self.tokens_seen, gn)
     with self._range("train/fwd_total"):
       loss = self.model.loss(inputs, targets)
-    with self._range("train/bwd_total"):
+    with self._range("train/bwd_total"), scope("backward"):
       loss.backward()
-    with self._range("train/opt_step"):
+    with self._range("train/opt_step"), scope("optimizer"):
       self.opt.step()
     if self._step_end is not None:
       self._step_end[self.step_num & 1].record()
@@ -123,6 +124,8 @@ def train(cfg: Config) -> dict:
   health = maybe_health(rank, world, stall_s=float(os.environ.get("NMOE_PEER_STALL_S", "600")))
   if device.type == "cuda":
     tc_gemm.check_status_collective(device, world)      # nothing latched by set-up before the first step
+  profiler = StepProfiler(cfg.profiling_enabled, os.path.join(cfg.profiling_output_dir, run_id or "run"), rank,
+                          steps=cfg.profiling_steps, skip=cfg.profiling_skip, print_fn=print)
   try:
     for step_num in range(start_step, cfg.steps):
       if health is not None:
@@ -135,6 +138,7 @@ def train(cfg: Config) -> dict:
       with metrics.timer("time_ms/step"):
         loss = trainer.step(inputs, targets)
       last_loss = loss
+      profiler.step()
       log_training_step(metrics, s, trainer, loss, loader_wait_ms, print0)
       if health is not None:
         health.beat(s)
@@ -173,6 +177,7 @@ def train(cfg: Config) -> dict:
       tracker.end_run(run_id, "failed")
     raise
   finally:
+    profiler.close()
     checkpointer.close()
     metrics.close()
     if tracker is not None:

@@ -350,3 +350,32 @@ def test_param_summary_counts_experts_of_all_ranks(tmp_path):
   assert total == n and active == n - experts + experts * cfg.n_activated_experts // cfg.n_routed_experts
   assert param_counts(m, cfg, 4)[0] == n + 3 * experts
   assert param_summary(m, cfg).startswith("(0.00B params")
+
+
+def test_step_profiler_writes_trace_and_operator_table(tmp_path, monkeypatch):
+  """profiling_enabled: the configured steps are recorded with the module scopes switched on only meanwhile."""
+  from nmoe_b200.train import train
+  from nmoe_b200.utils import profiling as P
+  monkeypatch.setenv("NMOE_RUN", "prof")
+  cfg = _tiny_cfg(tmp_path, steps=7, checkpoint_every=100, profiling_enabled=True, profiling_steps=2, profiling_skip=1,
+                  profiling_output_dir=str(tmp_path / "profiles"))
+  assert not P.scopes_enabled() and P.scope("x") is P.scope("y")           # off: one shared do-nothing context
+  train(cfg)
+  assert not P.scopes_enabled()
+  d = tmp_path / "profiles" / "prof"
+  trace = json.loads((d / "trace_rank0.json").read_text())
+  names = {e.get("name") for e in trace["traceEvents"]}
+  assert {"embed", "block_00/attn_global", "block_00/mlp", "block_01/moe", "lm_head_loss", "backward", "optimizer"} <= names
+  assert sum(1 for e in trace["traceEvents"] if e.get("name") == "lm_head_loss" and e.get("ph") == "X") == 2      # two active steps
+  assert "Self CPU" in (d / "ops_rank0.txt").read_text()
+  # a run that ends inside the profile still leaves its files; a disabled profiler does nothing
+  pr = P.StepProfiler(True, tmp_path / "cut", steps=5, skip=0, print_fn=lambda *_: None)
+  for _ in range(3):
+    with P.scope("work"):
+      torch.ones(4).sum()
+    pr.step()
+  pr.close()
+  assert pr.done and (tmp_path / "cut" / "trace_rank0.json").exists() and not P.scopes_enabled()
+  off = P.StepProfiler(False, tmp_path / "off")
+  off.step(); off.close()
+  assert off.done and not (tmp_path / "off").exists()
