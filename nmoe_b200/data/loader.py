@@ -221,16 +221,29 @@ class SyntheticLoader:
     pass
 
 
-def preflight(plan: MixturePlan, seq_len: int, print_fn=print) -> None:
-  """Warn when a source has fewer tokens on disk than its quota (the stream will wrap)."""
+def preflight(plan: MixturePlan, seq_len: int, print_fn=print, mode: Optional[str] = None) -> None:
+  """Compare every source's tokens on disk with its quota.  A short source makes the stream wrap (the same documents
+  are seen again): ``mode="warn"`` (default) says so, ``"strict"`` refuses to start, as the reference does
+  (nmoe/data/loader.py:286-306), ``"off"`` skips the check.  ``NMOE_PREFLIGHT`` sets the mode from the environment.
+  A source without any shard is an error in every mode."""
+  mode = (mode or os.environ.get("NMOE_PREFLIGHT", "warn")).lower()
+  if mode not in ("warn", "strict", "off"):
+    raise ValueError(f"preflight mode {mode!r}: expected warn, strict or off")
+  short = []
   for st in plan.stages:
     for sp in st.sources:
       if not sp.paths:
         raise RuntimeError(f"stage {st.stage_id}: source '{sp.id}' has no .npy shards")
+      if mode == "off":
+        continue
       have = sum(os.path.getsize(p) for p in sp.paths) // 4
       need = sp.quota_sequences * (seq_len + 1)
       if have < need:
-        print_fn(f"[preflight] source '{sp.id}': {have:,} tokens on disk < {need:,} needed; the stream will wrap")
+        short.append(f"source '{sp.id}' in stage '{st.stage_id}': {have:,} tokens on disk < {need:,} needed")
+  if short and mode == "strict":
+    raise RuntimeError("preflight failed: " + "; ".join(short) + ".  Check data_root, prepare more data or lower the flow's scale.")
+  for line in short:
+    print_fn(f"[preflight] {line}; the stream will wrap")
 
 
 def build_loader(cfg, rank: int, world_size: int, split: str = "train", print_fn=print):

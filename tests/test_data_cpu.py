@@ -673,3 +673,28 @@ def test_stack_v2_selection_fetch_and_rotating_output(tmp_path):
   s3 = S.S3Blobs(run=fake_run, client=None)
   s3.client = None
   assert s3.get("b0001") == b"x = 1\n" and s3.get("nope") is None and calls[0][:4] == ["aws", "s3", "cp", "s3://softwareheritage/content/b0001"]
+
+
+def test_loader_preflight_modes(tmp_path, monkeypatch):
+  from nmoe_b200.data.loader import preflight
+  from nmoe_b200.data.mixture import single_source_plan
+  shard = tmp_path / "s.npy"
+  np.save(shard, np.arange(1000, dtype=np.uint32))
+  said = []
+  ok = single_source_plan([str(shard)], 16, 800)
+  short = single_source_plan([str(shard)], 16, 100_000)
+  preflight(ok, 16, said.append, mode="strict")
+  assert said == []
+  preflight(short, 16, said.append)
+  assert len(said) == 1 and "will wrap" in said[0]
+  with pytest.raises(RuntimeError, match="preflight failed.*data_path"):
+    preflight(short, 16, said.append, mode="strict")
+  preflight(short, 16, said.append, mode="off")
+  assert len(said) == 1
+  monkeypatch.setenv("NMOE_PREFLIGHT", "strict")
+  with pytest.raises(RuntimeError):
+    preflight(short, 16, said.append)
+  with pytest.raises(ValueError):
+    preflight(short, 16, said.append, mode="loud")
+  with pytest.raises(RuntimeError, match="no .npy shards"):
+    preflight(single_source_plan([], 16, 10), 16, said.append, mode="off")
