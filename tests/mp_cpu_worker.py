@@ -65,6 +65,35 @@ def main():
       print(f"DETECTED lost at step {step} {time.time() - t0:.1f}s {e}", flush=True)
     except PeerStalled as e:
       print(f"DETECTED stalled at step {step} {time.time() - t0:.1f}s {e}", flush=True)
+  elif scenario == "eval_budget":
+    # ranks whose clocks disagree about the evaluation's time budget must still run the same tasks: rank 0 decides
+    import json
+    import tempfile
+    import torch
+    from nmoe_b200.config import Config
+    from nmoe_b200.eval import runner
+    from nmoe_b200.train import Trainer
+    d = tempfile.mkdtemp()
+    mc = os.path.join(d, "mc.jsonl")
+    with open(mc, "w") as f:
+      for i in range(4):
+        f.write(json.dumps({"question": f"q{i}?", "choices": ["a", "b"], "answer": i % 2}) + "\n")
+    tf = os.path.join(d, "tasks.toml")
+    with open(tf, "w") as f:
+      f.write('[groups]\ncore = ["t0", "t1", "t2"]\n' + "".join(f'[tasks.t{k}]\nkind = "choices"\nsource = "jsonl:{mc}"\n' for k in range(3)))
+    cfg = Config(vocab_size=257, eos_token_id=256, tokenizer="bytes", dim=64, n_layers=2, n_heads=2, inter_dim=128, moe_inter_dim=32,
+                 n_routed_experts=4, n_activated_experts=2, n_shared_experts=1, n_dense_layers=2, q_lora_rank=32, kv_lora_rank=16,
+                 qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=16, batch_size=2, seq_len=64, max_position_embeddings=512,
+                 activation_checkpoint="none", metrics_dir=os.path.join(d, "m"), eval_tasks_file=tf, eval_tasks="core")
+    torch.manual_seed(0)
+    model = Trainer(cfg, rank=rank, world=world).model
+    # rank 0 has time for everything, the others think the budget is spent after the first task
+    res = runner.run_snapshot_eval(model, cfg, run_id="mp", step=1, max_examples=4, max_time_s=600.0 if rank == 0 else 0.0,
+                                   print_fn=lambda *_: None)
+    print(f"EVAL TASKS {sorted(res)} n={[int(r['n']) for r in res.values()]}", flush=True)
+    res = runner.run_snapshot_eval(model, cfg, run_id="mp", step=2, max_examples=4, max_time_s=0.0 if rank == 0 else 600.0,
+                                   print_fn=lambda *_: None)
+    print(f"EVAL TASKS {sorted(res)}", flush=True)
   os._exit(0)                                      # no destroy_process_group: a peer may be gone
 
 

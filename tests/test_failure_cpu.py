@@ -68,3 +68,12 @@ def test_rank_that_stalls_between_steps_is_reported():
   # rank 1 sees the same stall, unless rank 0 has already raised and taken the store with it (a named PeerLost)
   assert ("DETECTED stalled" in outs[1] and "rank 2" in outs[1]) or ("DETECTED lost" in outs[1] and "store" in outs[1]), outs
   assert took < 45, took
+
+
+def test_eval_time_budget_is_decided_by_rank_zero_for_all_ranks():
+  """Two gloo ranks with different views of the evaluation budget run the same tasks (rank 0's view) and finish."""
+  outs, took = _run("eval_budget", 2, limit_s=120.0)
+  for o in outs:
+    lines = [l for l in o.splitlines() if l.startswith("EVAL TASKS")]
+    assert len(lines) == 2 and "KILLED" not in o, o
+    assert lines[0] == "EVAL TASKS ['t0', 't1', 't2'] n=[4, 4, 4]" and lines[1] == "EVAL TASKS ['t0']", o
