@@ -169,6 +169,9 @@ const CARD_TAGS = [
   ['train/grad_norm', 'grad norm', ''],
   ['gpu_agg/mean_utilization_gpu', 'GPU utilisation', '%'],
   ['gpu_agg/total_power_w', 'power', 'W'],
+  ['eval/CORE', 'CORE (eval)', ''],
+  ['router_agg/mean_cv', 'router load CV', ''],
+  ['memory/max_alloc_gib', 'peak memory', 'GiB'],
 ];
 
 function card(key, value, sub) {
