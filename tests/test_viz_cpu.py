@@ -310,3 +310,38 @@ def test_gpu_telemetry_rows_use_the_dashboard_tag_names():
   assert rows["gpu_agg/mean_utilization_gpu"] == 94.0 and rows["gpu_agg/total_memory_used_gib"] == 298.0
   assert rows["gpu_agg/total_power_w"] == 1452.0 and rows["gpu_agg/max_temperature_c"] == 78.0
   assert dashboard_items([]) == []
+
+
+def test_html_report_is_self_contained_and_compares_runs(tmp_path):
+  import re
+  import types
+  import xml.etree.ElementTree as ET
+  from nmoe_b200.experiments import ExperimentTracker
+  from nmoe_b200.viz.report import build_report, main, svg_chart
+  for run, slope in (("base", 0.01), ("trial", 0.02)):
+    w = MetricsWriter(run, str(tmp_path / "m"), 0)
+    for s in range(1, 121):
+      w.insert_many(s, [("train/loss", 10.0 - slope * s), ("optimizer/lr", 1e-3 * min(1.0, s / 20)), ("router/layer_01/cv", 0.2),
+                        ("router/layer_01/entropy", 1.9), ("router_agg/mean_cv", 0.2), ("eval/task/arc/acc", 0.4), ("eval/task/arc/centered", 0.2),
+                        ("eval/task/arc/n", 100.0), ("eval/CORE", 0.2)])
+    w.close()
+  db = tmp_path / "e.db"
+  tr = ExperimentTracker(types.SimpleNamespace(experiment_id="exp", experiments_db=str(db), lr=0.5))
+  tr.start_run("trial"); tr.end_run("trial", "completed", {"final_loss": 7.6}); tr.close()
+  out = tmp_path / "r.html"
+  assert main(["--metrics-dir", str(tmp_path / "m"), "--run", "trial", "--compare", "base", "--experiments-db", str(db), "--output", str(out)]) == 0
+  page = out.read_text()
+  assert "<script" not in page and "http://" not in page.replace("http://www.w3.org/2000/svg", "") and "https://" not in page
+  assert "status completed" in page and "final_loss" in page and "compared with" in page and "CORE = 0.2000" in page
+  svgs = re.findall(r"<svg.*?</svg>", page, flags=re.S)
+  assert len(svgs) >= 4
+  for s in svgs:
+    ET.fromstring(s)                                              # every chart is well-formed XML
+  loss = next(s for s in svgs if s.count("<polyline") == 2)       # two runs overlaid
+  assert loss.count("<polyline") == 2
+  assert "no data" in svg_chart([("x", [])]) and "<circle" in svg_chart([("x", [(1, 2.0)])])
+  assert "<polyline" in svg_chart([("x", [(1, 1e-4), (2, 1e-2), (3, 0.0)])], log_y=True)          # the zero is left out on a log axis
+  import pytest
+  with pytest.raises(KeyError):
+    build_report(MetricStore(str(tmp_path / "m")), "nope")
+  assert main(["--metrics-dir", str(tmp_path / "m"), "--run", "nope", "--output", str(out)]) == 1
