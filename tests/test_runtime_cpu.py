@@ -379,3 +379,25 @@ def test_step_profiler_writes_trace_and_operator_table(tmp_path, monkeypatch):
   off = P.StepProfiler(False, tmp_path / "off")
   off.step(); off.close()
   assert off.done and not (tmp_path / "off").exists()
+
+
+def test_reference_module_paths_are_aliases_that_cannot_shadow_another_install():
+  """`python -m nmoe.train / nmoe.data.cli / nmoe.eval.*` resolve to this package; the alias tree has no __init__.py
+  anywhere, so a regular `nmoe` package found later on sys.path (the reference, when it is installed) still wins."""
+  import importlib
+  import subprocess
+  import sys
+  from pathlib import Path
+  root = Path(__file__).resolve().parent.parent
+  assert not list((root / "nmoe").rglob("__init__.py"))
+  import nmoe_b200.data.cli, nmoe_b200.eval.runner, nmoe_b200.train
+  sys.path.insert(0, str(root))
+  try:
+    assert importlib.import_module("nmoe.train").main is nmoe_b200.train.main
+    assert importlib.import_module("nmoe.data.cli").main is nmoe_b200.data.cli.main
+    assert importlib.import_module("nmoe.eval.runner").main is nmoe_b200.eval.runner.main
+    assert importlib.import_module("nmoe.eval.choices").run_eval is importlib.import_module("nmoe_b200.eval.choices").run_eval
+  finally:
+    sys.path.remove(str(root))
+  out = subprocess.run([sys.executable, "-m", "nmoe.data.cli", "info", "--help"], cwd=root, capture_output=True, text=True)
+  assert out.returncode == 0 and "usage" in out.stdout
