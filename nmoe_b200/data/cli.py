@@ -525,7 +525,7 @@ def cmd_hydra_train(a) -> int:
     if a.phase == "A":
       return L.probe_batches(L.mix(tables, seed=a.seed), a.batch_size, tok.encode, a.max_ctx, dev)
     graded = [t for t in tables if t.fields.grade]
-    pairs = L.GradedPairs(L.mix(graded, seed=a.seed), seed=a.seed) if graded else None
+    pairs = L.GradedPairs(L.mix(graded, seed=a.seed), seed=a.seed) if graded and a.phase == "B" else None      # only phase B ranks
     if a.oracle_labels:
       oracle = L.OracleLabels(a.oracle_labels, a.data_root, a.max_ctx)
     else:

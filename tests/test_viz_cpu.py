@@ -345,3 +345,36 @@ def test_html_report_is_self_contained_and_compares_runs(tmp_path):
   with pytest.raises(KeyError):
     build_report(MetricStore(str(tmp_path / "m")), "nope")
   assert main(["--metrics-dir", str(tmp_path / "m"), "--run", "nope", "--output", str(out)]) == 1
+
+
+def test_dashboard_image_file_list_covers_the_servers_imports(tmp_path):
+  """docker/Dockerfile.viz copies a hand-picked set of modules: run the server's imports and one dataset route in a
+  tree that holds exactly those files, so a new import cannot silently break the slim image."""
+  import re
+  import shutil
+  import subprocess
+  import sys
+  from pathlib import Path
+  root = Path(__file__).resolve().parent.parent
+  text = (root / "docker" / "Dockerfile.viz").read_text().replace("\\\n", " ")
+  stage = tmp_path / "workspace"
+  for line in text.splitlines():
+    if line.startswith("COPY "):
+      *srcs, dst = line.split()[1:]
+      for s in srcs:
+        target = stage / dst.replace("/workspace/", "")
+        if (root / s).is_dir():
+          shutil.copytree(root / s, target, ignore=shutil.ignore_patterns("__pycache__"))
+        else:
+          dest = target / Path(s).name if dst.endswith("/") else target
+          dest.parent.mkdir(parents=True, exist_ok=True)
+          shutil.copy(root / s, dest)
+  data = tmp_path / "data"
+  data.mkdir()
+  import numpy as np
+  np.save(data / "s.npy", np.arange(10, dtype=np.uint32))
+  code = ("import nmoe_b200.viz.server as S, nmoe_b200.viz.report, nmoe_b200.viz.datasets as D; "
+          "print(D.shard_stats('s.npy')['tokens'], S.static_file('index.html') is not None)")
+  out = subprocess.run([sys.executable, "-c", code], cwd=stage, capture_output=True, text=True,
+                       env={"PATH": "/usr/bin:/bin", "PYTHONPATH": str(stage), "NVIZ_DATASETS_DIR": str(data)})
+  assert out.returncode == 0 and out.stdout.split() == ["10", "True"], out.stderr[-2000:]
