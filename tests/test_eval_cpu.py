@@ -234,3 +234,46 @@ def test_simulated_model_hits_its_target_accuracies_through_the_real_plumbing(tm
   w = MetricsWriter("sim", cfg.metrics_dir, 0)
   assert abs(w.query("eval/CORE")[0][1] - summ["CORE"]) < 1e-12
   w.close()
+
+
+def test_ticket_mode_end_to_end_with_competing_consumers(tmp_path, monkeypatch):
+  """eval_mode = "k8s_job": training writes snapshot + ticket; the consumer claims it by rename, runs the runner in a
+  child process, records the summary, removes the snapshot; a second consumer cannot take the same ticket; a broken
+  ticket fails without stopping the queue; a stale claim is taken over."""
+  import os
+  import time
+  from nmoe_b200.eval import tickets
+  from nmoe_b200.eval.hooks import maybe_schedule_eval
+  tf = _task_file(tmp_path, n=4)
+  cfg = _cfg(metrics_dir=str(tmp_path / "m"), checkpoint_dir=str(tmp_path / "ck"), eval_tasks_file=str(tf), eval_tasks="core",
+             eval_enabled=True, eval_every=5, eval_mode="k8s_job", eval_budget_max_examples=3)
+  torch.manual_seed(0)
+  tr = Trainer(cfg)
+  monkeypatch.setenv("RANK", "0")
+  assert maybe_schedule_eval(4, cfg, tr.model, "runT", lambda *_: None) is None           # not an evaluation step
+  ticket = maybe_schedule_eval(5, cfg, tr.model, "runT", lambda *_: None)
+  qdir = tmp_path / "m" / "eval_tickets"
+  assert ticket.parent == qdir and tickets.pending(qdir) == [ticket]
+  snap = json.loads(ticket.read_text())["snapshot"]
+  assert os.path.exists(os.path.join(snap, "model.pt")) and os.path.exists(os.path.join(snap, "config.json"))
+  (qdir / "broken_0000001.json").write_text("{not json")
+  os.utime(qdir / "broken_0000001.json", (1, 1))                                       # oldest: tried first
+  # another consumer got there first: the rename source is gone
+  stolen = tickets.claim(ticket, "other-1")
+  assert stolen.name == "runT_0000005.json.claimed.other-1" and tickets.claim(ticket, "me-2") is None
+  assert tickets.pending(qdir, stale_s=3600) == [qdir / "broken_0000001.json"]
+  counts = tickets.serve(qdir, once=True, stale_s=3600, print_fn=lambda *_: None)
+  assert counts == {"done": 0, "failed": 1} and (qdir / "broken_0000001.json.failed").exists()
+  # ... and died: after the stale time its claim is up for grabs
+  os.utime(stolen, (time.time() - 7200, time.time() - 7200))
+  counts = tickets.serve(qdir, once=True, stale_s=3600, extra=["--max-examples", "3"], print_fn=lambda *_: None)
+  assert counts == {"done": 1, "failed": 0}
+  done = json.loads((qdir / "runT_0000005.json.done").read_text())
+  assert done["summary"]["step"] == 5 and {t["task"] for t in done["summary"]["tasks"]} == {"mc_a", "mc_b", "qa"}
+  assert not os.path.exists(snap) and tickets.pending(qdir) == []
+  from nmoe_b200.metrics import MetricsWriter
+  w = MetricsWriter("runT", cfg.metrics_dir, 0)
+  assert w.query("eval/CORE")[0][0] == 5                                               # the child process recorded the results
+  w.close()
+  assert tickets.runner_command({"snapshot": "S", "run": "R", "step": 3, "tasks": "core"}, ["--simulate"])[3:] == \
+      ["--snapshot", "S", "--run", "R", "--step", "3", "--tasks", "core", "--simulate"]
