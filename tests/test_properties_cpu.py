@@ -2,6 +2,7 @@
 import random
 
 import numpy as np
+import torch
 from hypothesis import given, settings, strategies as st
 
 from nmoe_b200.data import docid as D
@@ -97,3 +98,48 @@ def test_blob_decoding_never_raises_and_text_stays_text(data, enc):
   assert out is None or isinstance(out, str)
   text = "def f(x):\n    return x + 1  # naïve\n" * 3
   assert S.decode_text(text.encode("utf-8"), enc if enc in ("", "utf-8") else "") == text
+
+
+@FAST
+@given(tokens=st.integers(0, 10 ** 9), seq=st.integers(1, 8192), weights=st.lists(st.floats(0.0, 100.0, allow_nan=False), min_size=1, max_size=12))
+def test_sequence_quotas_sum_to_the_budget_and_follow_the_weights(tokens, seq, weights):
+  from nmoe_b200.data.mixture import largest_remainder_quota
+  q = largest_remainder_quota(tokens, seq, weights)
+  total = tokens // seq
+  assert len(q) == len(weights) and all(x >= 0 for x in q) and sum(q) == (total if sum(weights) > 0 or total == 0 else sum(q))
+  wsum = sum(weights)
+  if wsum > 0 and total > 0:
+    assert sum(q) == total
+    for x, w in zip(q, weights):
+      assert abs(x - total * w / wsum) <= 1.0 + 1e-6 * total        # never more than one sequence off the exact share
+
+
+@settings(max_examples=12, deadline=None)
+@given(weights=st.lists(st.integers(1, 50), min_size=1, max_size=6), world=st.integers(1, 4), seed=st.integers(0, 1000))
+def test_loader_split_over_ranks_is_the_global_stream(tmp_path_factory, weights, world, seed):
+  """Whatever the weights and the number of ranks, the ranks' slices put side by side are the single-rank stream, and
+  each source is drawn in proportion to its weight (smooth weighted round-robin: never more than one draw off)."""
+  from nmoe_b200.data.loader import DeterministicLoader
+  from nmoe_b200.data.mixture import MixturePlan, SourcePlan, StagePlan
+  d = tmp_path_factory.mktemp("ld")
+  rng = np.random.default_rng(seed)
+  seq, steps, per_step = 8, 5, 4 * world
+  srcs = []
+  for i, w in enumerate(weights):
+    p = d / f"s{i}.npy"
+    np.save(p, (rng.integers(0, 1000, size=4000) + 1000 * i).astype(np.uint32))      # the thousands digit names the source
+    srcs.append(SourcePlan(id=f"s{i}", weight_fp=w, quota_sequences=10 ** 6, target_tokens=10 ** 9, paths=[str(p)]))
+  plan = MixturePlan("m", "0", "f", "test", 1.0, seq, [StagePlan("pretrain", 1.0, srcs)])
+  mk = lambda r, n: DeterministicLoader(plan=plan, dp_world_size=n, dp_rank=r, seq_len=seq, tokens_per_update=per_step * seq, device="cpu")
+  one = mk(0, 1)
+  ranks = [mk(r, world) for r in range(world)]
+  counts = [0] * len(weights)
+  for _ in range(steps):
+    whole = one.next_host()
+    parts = torch.cat([ld.next_host() for ld in ranks])
+    assert torch.equal(whole, parts)
+    for row in whole:
+      counts[int(row[0]) // 1000] += 1
+  n = steps * per_step
+  for c, w in zip(counts, weights):
+    assert abs(c - n * w / sum(weights)) <= 1.0 + 1e-9
