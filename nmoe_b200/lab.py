@@ -4,6 +4,7 @@
     t = lab.tiny_trainer(n_layers=4)              # or lab.trainer_from("configs/moonlet.toml", steps=50)
     lab.param_memory(t.model)                     # bytes by parameter group
     lab.time_step(t, iters=10)                    # forward / backward / optimizer, device-timed on a GPU
+    lab.profile_steps(t, steps=3)                 # top kernels / operators / scopes per step (torch.profiler)
     with lab.RouterProbe(t.model) as probe: lab.run_steps(t, 5)
     probe.table()                                 # per-layer load CV, entropy, dead experts, hottest expert
     lab.grad_report(t.model)                      # gradient norms per block
@@ -222,6 +223,34 @@ def time_step(trainer, warmup: int = 3, iters: int = 10, batch=None) -> Dict[str
   out["total_ms"] = sum(out.values())
   out["tokens_per_s"] = trainer.cfg.batch_size * trainer.cfg.seq_len / (out["total_ms"] / 1e3)
   return out
+
+
+def profile_steps(trainer, steps: int = 3, warmup: int = 2, top: int = 25, batch=None) -> List[Row]:
+  """``steps`` training steps under ``torch.profiler`` with the module scopes on; the ``top`` entries by device time
+  (host time without a GPU): kernels, operators and scopes with call counts and milliseconds per step.  For looking at
+  a step interactively; kernel counters come from ``ncu`` and throughput from ``bench.py``, never from here."""
+  from .utils import profiling as P
+  x, y = batch or random_batch(trainer.cfg, trainer.device)
+  for _ in range(warmup):
+    trainer.step(x, y)
+  cuda = trainer.device.type == "cuda"
+  acts = [torch.profiler.ProfilerActivity.CPU] + ([torch.profiler.ProfilerActivity.CUDA] if cuda else [])
+  P.enable_scopes(True)
+  try:
+    with torch.profiler.profile(activities=acts) as prof:
+      for _ in range(steps):
+        trainer.step(x, y)
+      if cuda:
+        torch.cuda.synchronize(trainer.device)
+  finally:
+    P.enable_scopes(False)
+  rows = []
+  for e in prof.key_averages():
+    dev_us = float(getattr(e, "self_device_time_total", 0.0) or getattr(e, "self_cuda_time_total", 0.0) or 0.0)
+    rows.append({"name": e.key[:70], "calls_per_step": e.count / steps, "device_ms_per_step": dev_us / 1e3 / steps,
+                 "host_ms_per_step": float(e.self_cpu_time_total) / 1e3 / steps})
+  rows.sort(key=lambda r: -(r["device_ms_per_step"] if cuda else r["host_ms_per_step"]))
+  return rows[:top]
 
 
 # ---------------------------------------------------------------------------------------------- routing

@@ -98,3 +98,14 @@ def test_quickstart_notebook_cells_run(tmp_path, monkeypatch):
   for c in cells:
     exec(compile("".join(c["source"]), "<quickstart cell>", "exec"), ns)
   assert ns["store"].runs() == ["quickstart"] and set(ns["curves"]) == {"lr 3e-3", "lr 3e-4", "top-4"}
+
+
+def test_profile_steps_lists_operators_and_scopes():
+  from nmoe_b200.utils import profiling as P
+  t = lab.tiny_trainer()
+  rows = lab.profile_steps(t, steps=2, warmup=1, top=400)
+  names = {r["name"] for r in rows}
+  assert {"backward", "optimizer", "lm_head_loss", "block_01/moe"} <= names and not P.scopes_enabled()
+  scope = next(r for r in rows if r["name"] == "lm_head_loss")
+  assert scope["calls_per_step"] == 1.0 and all(r["host_ms_per_step"] >= 0 for r in rows)
+  assert rows == sorted(rows, key=lambda r: -r["host_ms_per_step"])
