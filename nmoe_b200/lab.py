@@ -39,26 +39,38 @@ _TINY = dict(vocab_size=512, eos_token_id=511, dim=64, n_layers=2, n_heads=2, in
              warmup_steps=2, steps=100, data_path="synthetic", activation_checkpoint="none")
 
 
+# The same idea at the smallest sizes the GPU kernels take (head dimensions and widths in multiples of their tiles).
+_TINY_GPU = dict(vocab_size=2048, eos_token_id=2047, dim=512, n_layers=2, n_heads=4, inter_dim=1024, moe_inter_dim=256,
+                 n_routed_experts=8, n_activated_experts=2, n_shared_experts=2, n_dense_layers=1, q_lora_rank=256, kv_lora_rank=128,
+                 qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128, batch_size=4, seq_len=256, max_position_embeddings=512,
+                 warmup_steps=2, steps=100, data_path="synthetic", activation_checkpoint="none")
+
+
 def _device() -> torch.device:
   return torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
 
 
-def tiny_trainer(**overrides):
-  """A two-layer model that steps in milliseconds on a CPU: for trying the tools below, and for tests."""
+def tiny_trainer(fused: bool = False, **overrides):
+  """A two-layer model that steps in milliseconds: for trying the tools below, and for tests.  On a GPU the sizes are
+  the smallest the kernels take (``_TINY_GPU``), on a CPU smaller still.
+
+  ``fused=False`` keeps the expert optimizer out of backward, so that expert gradients are there to look at after
+  ``backward_only`` and a backward pass changes no weight; ``fused=True`` is what training does."""
   from .train import Trainer
-  cfg = Config(**{**_TINY, **overrides})
+  dev = _device()
+  cfg = Config(**{**(_TINY_GPU if dev.type == "cuda" else _TINY), **overrides})
   cfg.validate(1)
   torch.manual_seed(cfg.seed)
-  return Trainer(cfg, device=_device())
+  return Trainer(cfg, device=dev, fuse_expert_opt=fused)
 
 
-def trainer_from(config_path: str, **overrides):
-  """A single-process trainer for a configuration file with ``key=value`` overrides."""
+def trainer_from(config_path: str, fused: bool = False, **overrides):
+  """A single-process trainer for a configuration file with ``key=value`` overrides (``fused``: see ``tiny_trainer``)."""
   from .train import Trainer
   cfg = from_toml(config_path, [f"--{k}={v}" for k, v in overrides.items()], env={})
   cfg.validate(1)
   torch.manual_seed(cfg.seed)
-  return Trainer(cfg, device=_device())
+  return Trainer(cfg, device=_device(), fuse_expert_opt=fused)
 
 
 def random_batch(cfg: Config, device=None, seed: int = 0):
@@ -336,8 +348,9 @@ def grad_report(model: torch.nn.Module) -> List[Row]:
 
 
 def backward_only(trainer, batch=None) -> float:
-  """One forward + backward without an optimizer step, so that ``grad_report`` sees the gradients.  Builds the trainer's
-  model loss directly; expert gradients consumed inside backward by the fused optimizer are reported as ``no_grad``."""
+  """One forward + backward without an optimizer step, so that ``grad_report`` sees the gradients.  With a trainer
+  built with ``fused=True`` the expert optimizer runs inside this backward pass: expert weights move and their
+  gradients are reported as ``no_grad``."""
   x, y = batch or random_batch(trainer.cfg, trainer.device)
   trainer.model.zero_grad(set_to_none=True)
   loss = trainer.model.loss(x, y)
