@@ -124,6 +124,9 @@ def train(cfg: Config) -> dict:
   health = maybe_health(rank, world, stall_s=float(os.environ.get("NMOE_PEER_STALL_S", "600")))
   if device.type == "cuda":
     tc_gemm.check_status_collective(device, world)      # nothing latched by set-up before the first step
+  from .utils.stop import StopRequest
+  stopper = StopRequest(world if dist.is_initialized() else 1)
+  steps_done = cfg.steps
   profiler = StepProfiler(cfg.profiling_enabled, os.path.join(cfg.profiling_output_dir, run_id or "run"), rank,
                           steps=cfg.profiling_steps, skip=cfg.profiling_skip, print_fn=print)
   try:
@@ -163,12 +166,20 @@ def train(cfg: Config) -> dict:
         maybe_schedule_eval(s, cfg, trainer.model, run_id, print0)
       except Exception as e:
         print0(f"[eval] scheduling failed: {e}")
-      save_checkpoint(checkpointer, s, trainer, loader, plan, cfg, rank, fp, print0)
-    print0(f"[nmoe] Training complete. {trainer.tokens_seen:,} tokens.")
+      stopping = stopper.should_stop(s)
+      save_checkpoint(checkpointer, s, trainer, loader, plan, cfg, rank, fp, print0, force=stopping)
+      if stopping:
+        # a stop was asked for (SIGTERM from a scheduler, SIGUSR1 by hand): every rank is at this same step
+        steps_done = s
+        print0(f"[nmoe] stop requested ({stopper.reason or 'by another rank'}): checkpoint written at step {s}, leaving")
+        break
+    stopped = steps_done < cfg.steps
+    if not stopped:
+      print0(f"[nmoe] Training complete. {trainer.tokens_seen:,} tokens.")
     results = {"final_loss": float(last_loss.item()) if last_loss is not None else 0.0,
-               "tokens_seen": trainer.tokens_seen, "steps_completed": cfg.steps}
+               "tokens_seen": trainer.tokens_seen, "steps_completed": steps_done}
     if tracker is not None:
-      tracker.end_run(run_id, "completed", results)
+      tracker.end_run(run_id, "killed" if stopped else "completed", results)
     return results
   except Exception as e:
     if health is not None:
@@ -177,6 +188,7 @@ def train(cfg: Config) -> dict:
       tracker.end_run(run_id, "failed")
     raise
   finally:
+    stopper.restore()
     profiler.close()
     checkpointer.close()
     metrics.close()

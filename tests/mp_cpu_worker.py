@@ -94,6 +94,22 @@ def main():
     res = runner.run_snapshot_eval(model, cfg, run_id="mp", step=2, max_examples=4, max_time_s=0.0 if rank == 0 else 600.0,
                                    print_fn=lambda *_: None)
     print(f"EVAL TASKS {sorted(res)}", flush=True)
+  elif scenario == "stop_agreement":
+    # three ranks step in lock-step (a barrier stands in for the step's collectives); rank 1 is asked to stop after
+    # its step 4.  Every rank must leave at the same step, and that step must lie after the request.
+    from nmoe_b200.utils.stop import StopRequest
+    stopper = StopRequest(world, install=False)
+    left = None
+    for step in range(1, 50):
+      dist.barrier()
+      if rank == 2:
+        time.sleep(0.02)                           # one rank lags inside the step
+      if rank == 1 and step == 4:
+        stopper.request("SIGTERM")
+      if stopper.should_stop(step):
+        left = step
+        break
+    print(f"STOPPED AT {left}", flush=True)
   os._exit(0)                                      # no destroy_process_group: a peer may be gone
 
 

@@ -77,3 +77,13 @@ def test_eval_time_budget_is_decided_by_rank_zero_for_all_ranks():
     lines = [l for l in o.splitlines() if l.startswith("EVAL TASKS")]
     assert len(lines) == 2 and "KILLED" not in o, o
     assert lines[0] == "EVAL TASKS ['t0', 't1', 't2'] n=[4, 4, 4]" and lines[1] == "EVAL TASKS ['t0']", o
+
+
+def test_stop_request_is_agreed_on_one_step_by_all_ranks():
+  outs, _ = _run("stop_agreement", 3, limit_s=60.0)
+  steps = []
+  for o in outs:
+    line = [l for l in o.splitlines() if l.startswith("STOPPED AT")]
+    assert line and "KILLED" not in o, o
+    steps.append(line[0])
+  assert steps == ["STOPPED AT 6"] * 3, steps          # requested after step 4, margin 2

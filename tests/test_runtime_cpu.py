@@ -401,3 +401,45 @@ def test_reference_module_paths_are_aliases_that_cannot_shadow_another_install()
     sys.path.remove(str(root))
   out = subprocess.run([sys.executable, "-m", "nmoe.data.cli", "info", "--help"], cwd=root, capture_output=True, text=True)
   assert out.returncode == 0 and "usage" in out.stdout
+
+
+def test_sigusr1_stops_at_a_checkpoint_and_the_restart_finishes_the_same_run(tmp_path, monkeypatch):
+  """A stop request between steps: checkpoint of that step, run recorded as killed; the restarted job resumes from it
+  and ends with the loss of a run that was never interrupted."""
+  import os
+  import signal
+  import nmoe_b200.train as T
+  from nmoe_b200.checkpoint import read_tracker
+  from nmoe_b200.experiments import ExperimentTracker
+  monkeypatch.setenv("NMOE_RUN", "whole")
+  whole = T.train(_tiny_cfg(tmp_path / "a", checkpoint_every=100))
+  import nmoe_b200.metrics as M
+  real_log = M.log_training_step
+  def log_and_signal(metrics, s, *a, **kw):
+    if s == 3:
+      os.kill(os.getpid(), signal.SIGUSR1)
+    return real_log(metrics, s, *a, **kw)
+  monkeypatch.setattr(M, "log_training_step", log_and_signal)
+  monkeypatch.setenv("NMOE_RUN", "cut")
+  before = signal.getsignal(signal.SIGUSR1)
+  cfg = _tiny_cfg(tmp_path / "b", checkpoint_every=100)
+  part = T.train(cfg)
+  assert part["steps_completed"] == 3 and read_tracker(cfg.checkpoint_dir) == 3
+  assert signal.getsignal(signal.SIGUSR1) == before                       # handlers are put back
+  tr = ExperimentTracker(cfg)
+  assert tr.get_run("cut").status == "killed" and json.loads(tr.get_run("cut").results_json)["steps_completed"] == 3
+  tr.close()
+  monkeypatch.setattr(M, "log_training_step", real_log)
+  rest = T.train(_tiny_cfg(tmp_path / "b", checkpoint_every=100))
+  assert rest["steps_completed"] == 6 and rest["final_loss"] == whole["final_loss"] and rest["tokens_seen"] == whole["tokens_seen"]
+  tr = ExperimentTracker(cfg)
+  assert tr.get_run("cut").status == "completed"
+  tr.close()
+
+
+def test_stop_request_agreement_logic_single_rank():
+  from nmoe_b200.utils.stop import StopRequest
+  s = StopRequest(1, install=False)
+  assert not s.should_stop(1) and not s.should_stop(2)
+  s.request("operator")
+  assert s.should_stop(3) and s.stop_at == 3 and s.reason == "operator" and s.should_stop(4)
