@@ -15,9 +15,52 @@ from typing import Optional
 from .errors import PipelineError
 
 
+def _prep_task(a) -> int:
+  """``prep --task ID``: build a registered corpus from its raw recipe with the registry's preparation steps."""
+  from .registry import Registry
+  reg = Registry.load(a.registry)
+  if a.corpus_root:
+    reg.root = Path(a.corpus_root)
+  t = reg.task(a.task)
+  grader, tau = None, 0.0
+  wants = t.prep.get("hydra_filter") or t.prep.get("hydra_audit")
+  if wants and not a.no_hydra:
+    if not (a.checkpoint and a.heads_dir):
+      print(f"task {a.task!r} is filtered by the quality grader: pass --checkpoint and --heads-dir, or --no-hydra", file=sys.stderr)
+      return 2
+    grader, tau = _mixture_grader(a, {})
+  m = reg.build(a.task, a.split, grader=grader, tau_keep=tau, no_hydra=a.no_hydra or grader is None, max_documents=a.max_documents,
+                tokenizer=a.tokenizer if a.tokenizer != "o200k_harmony" else None, num_shards=a.num_shards if a.num_shards != 8 else None)
+  print(f"wrote {m.num_shards} shards, {m.total_documents:,} documents, {m.total_tokens:,} tokens for task {a.task}")
+  return 0
+
+
+def cmd_tasks(a) -> int:
+  """Which registered corpora are ready to train on (shards found) and which can be built (raw material found)."""
+  from .registry import Registry
+  reg = Registry.load(a.registry)
+  if a.corpus_root:
+    reg.root = Path(a.corpus_root)
+  rows = reg.status()
+  if a.json:
+    print(json.dumps({"root": str(reg.root), "contract": reg.contract, "tasks": rows}, indent=1))
+    return 0
+  print(f"corpus root {reg.root}  contract {reg.contract.get('tokenizer')} / vocab {reg.contract.get('vocab_size')} / eos {reg.contract.get('eos_token_id')}")
+  for r in rows:
+    state = "ready" if r["ready"] else ("buildable" if r["buildable"] else "missing")
+    tok = f"{r['tokens'] / 1e9:.2f} B tokens" if r["tokens"] else ""
+    raw = "" if r["raw_files"] is None else f"{r['raw_files']} raw file(s)"
+    print(f"  {r['task']:<22} {r['domain']:<8} {state:<10} {r['shards']:>6} shard(s) {tok:<16} {r['raw_kind'] or '-':<12} {raw}")
+  return 0
+
+
 def cmd_prep(a) -> int:
   from .prep import ParallelPrepPipeline, PrepConfig, PrepPipeline
   from .sources import create_source
+  if a.task:
+    return _prep_task(a)
+  if not (a.output and a.name):
+    raise SystemExit("prep needs --output and --name (or --task ID to build a registered corpus)")
   if a.source in ("arxiv_tars", "ar5iv", "arxiv_paired"):
     # --input is the directory of bulk tars (of ar5iv pages for `ar5iv`); --html-dir the ar5iv tree for the paired form
     kw = {"arxiv_tars": {"tar_dir": a.input}, "ar5iv": {"html_dir": a.input},
@@ -632,8 +675,10 @@ def build_parser() -> argparse.ArgumentParser:
   p.add_argument("--source", default="jsonl", help="jsonl | jsonl_zst | text | arrow | parquet | hf | hffs | arxiv_tars | ar5iv | arxiv_paired")
   p.add_argument("--html-dir", help="ar5iv tree ({tier}/{yymm}/{id}.html) for --source arxiv_paired")
   p.add_argument("--input"); p.add_argument("--dataset"); p.add_argument("--subset")
-  p.add_argument("--split", default="train"); p.add_argument("--text-field", default="text"); p.add_argument("--output", required=True)
-  p.add_argument("--name", required=True); p.add_argument("--version", default="v1"); p.add_argument("--tokenizer", default="o200k_harmony")
+  p.add_argument("--split", default="train"); p.add_argument("--text-field", default="text"); p.add_argument("--output")
+  p.add_argument("--task", help="build this corpus of the task registry instead of an ad-hoc source"); p.add_argument("--registry", default="configs/tasks.toml")
+  p.add_argument("--corpus-root", help="override [corpus] root of the registry"); p.add_argument("--no-hydra", action="store_true")
+  p.add_argument("--name"); p.add_argument("--version", default="v1"); p.add_argument("--tokenizer", default="o200k_harmony")
   p.add_argument("--num-shards", type=int, default=8); p.add_argument("--workers", type=int, default=1)
   p.add_argument("--max-documents", type=int); p.add_argument("--max-tokens", type=int)
   p.add_argument("--runner", default="process", choices=["process", "beam", "local", "auto"],
@@ -654,6 +699,8 @@ def build_parser() -> argparse.ArgumentParser:
   p.add_argument("--worker-index", type=int, default=0); p.add_argument("--num-workers", type=int, default=1)
   p.add_argument("--hydra-filter", action="store_true"); p.add_argument("--checkpoint"); p.add_argument("--heads-dir"); p.add_argument("--calibration")
   p.add_argument("--hydra-batch-size", type=int, default=32); p.add_argument("--hydra-max-ctx", type=int, default=4096)
+  p = sub.add_parser("tasks"); p.set_defaults(fn=cmd_tasks); p.add_argument("--registry", default="configs/tasks.toml")
+  p.add_argument("--corpus-root"); p.add_argument("--json", action="store_true")
   p = sub.add_parser("verify"); p.set_defaults(fn=cmd_verify); p.add_argument("path"); p.add_argument("--fast", action="store_true")
   p = sub.add_parser("info"); p.set_defaults(fn=cmd_info); p.add_argument("path")
   p = sub.add_parser("regenerate-index"); p.set_defaults(fn=cmd_regenerate_index); p.add_argument("path"); p.add_argument("--eos-token-id", type=int, default=199999)

@@ -698,3 +698,88 @@ def test_loader_preflight_modes(tmp_path, monkeypatch):
     preflight(short, 16, said.append, mode="loud")
   with pytest.raises(RuntimeError, match="no .npy shards"):
     preflight(single_source_plan([], 16, 10), 16, said.append, mode="off")
+
+
+def test_task_registry_status_build_and_contract(tmp_path, capsys):
+  """configs/tasks.toml made executable: status of tasks, a build through the registry's preparation steps (hygiene,
+  exact dedup on text and on tokens), the contract check, the command-line forms."""
+  from nmoe_b200.data.cli import main
+  from nmoe_b200.data.registry import ContractViolation, Registry, TaskNotBuildable
+  shipped = Registry.load("configs/tasks.toml")
+  assert len(shipped.tasks) >= 14 and shipped.contract["eos_token_id"] == 199999 and shipped.task("stack_v2").prep["exact_dedup_text"]
+  assert shipped.task("arxiv").prep["hydra_filter"] is False and shipped.task("dclm").prep["hydra_filter"] is True
+  assert shipped.task("fineweb_edu").shard_dir() == "fineweb_edu/train"
+  raw = tmp_path / "raw"
+  raw.mkdir()
+  rows = [{"id": f"d{i}", "text": f"Document number {i} has enough characters to be kept by hygiene."} for i in range(20)]
+  rows += [{"id": "dup", "text": rows[3]["text"].upper()}, {"id": "tiny", "text": "too short"},
+           {"id": "ctl", "text": "Control \x00characters\x07 are removed from this otherwise fine document."}]
+  (raw / "a.jsonl").write_text("".join(json.dumps(r) + "\n" for r in rows))
+  reg_file = tmp_path / "tasks.toml"
+  reg_file.write_text(f'''
+[corpus]
+root = "{tmp_path / "corpus"}"
+[corpus.contract]
+tokenizer = "bytes"
+vocab_size = 257
+eos_token_id = 256
+dtype = "uint32"
+[corpus.prep_defaults]
+hygiene = true
+exact_dedup_text = true
+hydra_filter = false
+exact_dedup_tokens = true
+num_shards = 2
+[tasks.toy]
+domain = "web"
+[tasks.toy.shards]
+train = "toy/train/**/*.npy"
+[tasks.toy.raw]
+kind = "jsonl"
+glob = "{raw}/*.jsonl"
+text_field = "text"
+id_field = "id"
+[tasks.graded]
+[tasks.graded.shards]
+train = "graded/train/*.npy"
+[tasks.graded.raw]
+kind = "jsonl"
+glob = "{raw}/*.jsonl"
+[tasks.graded.prep]
+hydra_filter = true
+[tasks.no_recipe]
+[tasks.no_recipe.shards]
+train = "nr/train/*.npy"
+''')
+  reg = Registry.load(reg_file)
+  st = {r["task"]: r for r in reg.status()}
+  assert st["toy"]["buildable"] and not st["toy"]["ready"] and st["toy"]["raw_files"] == 1 and not st["no_recipe"]["buildable"]
+  m = reg.build("toy", tokenizer="bytes", print_fn=lambda *_: None)
+  assert m.total_documents == 21                       # 23 rows - the tiny one - the duplicate (case-folded)
+  reg.check_contract(m)
+  st = {r["task"]: r for r in reg.status()}
+  assert st["toy"]["ready"] and st["toy"]["shards"] == 2 and st["toy"]["tokens"] == m.total_tokens
+  shard_text = b"".join(bytes(int(t) for t in np.load(p) if t < 256) for p in reg.shard_files("toy")).decode()
+  assert "Control characters are removed" in shard_text and "too short" not in shard_text
+  m.eos_token_id = 1
+  with pytest.raises(ContractViolation, match="eos_token_id"):
+    reg.check_contract(m)
+  with pytest.raises(TaskNotBuildable):
+    reg.build("no_recipe", tokenizer="bytes")
+  with pytest.raises(TaskNotBuildable, match="grading model"):
+    reg.build("graded", tokenizer="bytes")
+  kept = reg.build("graded", tokenizer="bytes", grader=lambda texts: [float("9" in t) for t in texts], tau_keep=0.5, print_fn=lambda *_: None)
+  assert kept.total_documents == 2                     # documents 9 and 19
+  with pytest.raises(ValueError, match="unknown preparation keys"):
+    Registry({"corpus": {"root": "/x"}, "tasks": {"t": {"prep": {"dedupe": True}}}})
+  # command line
+  assert main(["tasks", "--registry", str(reg_file)]) == 0
+  out = capsys.readouterr().out
+  assert "toy" in out and "ready" in out and "no_recipe" in out and "missing" in out
+  assert main(["tasks", "--registry", str(reg_file), "--json"]) == 0
+  assert {t["task"] for t in json.loads(capsys.readouterr().out)["tasks"]} == {"toy", "graded", "no_recipe"}
+  assert main(["prep", "--task", "toy", "--registry", str(reg_file), "--corpus-root", str(tmp_path / "c2"), "--tokenizer", "bytes",
+               "--output", "unused", "--name", "unused"]) == 0
+  assert sinks.load_manifest(tmp_path / "c2" / "toy" / "train").total_documents == 21
+  assert main(["prep", "--task", "graded", "--registry", str(reg_file), "--tokenizer", "bytes"]) == 2      # needs a grader or --no-hydra
+  assert main(["prep", "--task", "graded", "--registry", str(reg_file), "--corpus-root", str(tmp_path / "c3"), "--tokenizer", "bytes", "--no-hydra"]) == 0
