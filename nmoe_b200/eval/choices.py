@@ -8,12 +8,12 @@ from __future__ import annotations
 
 import argparse
 import math
-import tomllib
 from typing import Any, Dict, List, Optional
 
 import torch
 import torch.distributed as dist
 
+from ..config import load_toml
 from ..data.transforms import get_tokenizer
 from ..models.transformer import LOGIT_SCALE
 from .adapters import Choice, iter_choices
@@ -95,8 +95,7 @@ def eval_task(model, enc, task: Dict[str, Any], *, rank: int, world: int, max_ex
 
 
 def load_tasks(path: str, which: str = "core") -> Dict[str, Dict[str, Any]]:
-  with open(path, "rb") as f:
-    d = tomllib.load(f)
+  d = load_toml(path)          # expands ${NMOE_*:-default} placeholders (task files point at local copies of the sets)
   tasks = d.get("tasks", d)
   groups = d.get("groups", {})
   names = groups.get(which, list(tasks)) if which else list(tasks)

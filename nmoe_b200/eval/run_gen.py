@@ -115,7 +115,6 @@ def eval_gen_task(model, enc, name: str, task: Dict[str, Any], *, rank: int, wor
 
 
 def main(argv=None) -> None:
-  import tomllib
   ap = argparse.ArgumentParser(description="generation evals (gsm8k / gpqa / humaneval) on a checkpointed model")
   ap.add_argument("config"); ap.add_argument("--tasks-file", required=True); ap.add_argument("--max-examples", type=int, default=100)
   ap.add_argument("--max-new", type=int, default=256)
@@ -128,8 +127,8 @@ def main(argv=None) -> None:
   rank, world, dev = runtime.init(cfg.seed)
   tr = Trainer(cfg, rank=rank, world=world, device=dev)
   load_checkpoint(Checkpointer(cfg.checkpoint_dir, async_io=False), tr, None, None, cfg, rank)
-  with open(a.tasks_file, "rb") as f:
-    tasks = {k: v for k, v in tomllib.load(f).get("tasks", {}).items() if v.get("kind") in ("gen", "span")}
+  from ..config import load_toml
+  tasks = {k: v for k, v in load_toml(a.tasks_file).get("tasks", {}).items() if v.get("kind") in ("gen", "span")}
   enc = get_tokenizer(cfg.tokenizer)
   for name, t in tasks.items():
     r = eval_gen_task(tr.model, enc, name, t, rank=rank, world=world, max_examples=a.max_examples, eos_id=cfg.eos_token_id,

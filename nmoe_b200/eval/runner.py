@@ -24,9 +24,8 @@ import torch
 def select_tasks(tasks_file: str, which: str) -> Dict[str, Dict[str, Any]]:
   """Tasks of every kind for a selection: a group of the file (``core`` also takes ``core_gen``), one task name, or
   ``chat:name|name``.  Unknown names are left out."""
-  import tomllib
-  with open(tasks_file, "rb") as f:
-    d = tomllib.load(f)
+  from ..config import load_toml
+  d = load_toml(tasks_file)    # expands ${NMOE_*:-default} placeholders
   tasks = d.get("tasks", d)
   groups = d.get("groups", {})
   if which.startswith("chat"):

@@ -277,3 +277,14 @@ def test_ticket_mode_end_to_end_with_competing_consumers(tmp_path, monkeypatch):
   w.close()
   assert tickets.runner_command({"snapshot": "S", "run": "R", "step": 3, "tasks": "core"}, ["--simulate"])[3:] == \
       ["--snapshot", "S", "--run", "R", "--step", "3", "--tasks", "core", "--simulate"]
+
+
+def test_task_files_expand_environment_placeholders(tmp_path, monkeypatch):
+  """The shipped task files point at local copies of the sets through ${NMOE_EVAL_DATA:-/data/eval}."""
+  from nmoe_b200.eval import runner
+  monkeypatch.setenv("NMOE_EVAL_DATA", str(tmp_path))
+  assert choices.load_tasks("configs/eval/tasks.toml", "core")["piqa"]["source"] == f"jsonl:{tmp_path}/piqa_validation.jsonl"
+  assert runner.select_tasks("configs/eval/tasks.toml", "gsm8k")["gsm8k"]["source"] == f"jsonl:{tmp_path}/gsm8k_test.jsonl"
+  monkeypatch.delenv("NMOE_EVAL_DATA")
+  assert runner.select_tasks("configs/eval/tasks.toml", "piqa")["piqa"]["source"] == "jsonl:/data/eval/piqa_validation.jsonl"
+  assert list(runner.select_tasks("configs/eval/tasks.toml", "chat")) == ["arc_easy", "arc_challenge", "mmlu", "gsm8k", "humaneval"]
