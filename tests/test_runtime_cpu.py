@@ -443,3 +443,29 @@ def test_stop_request_agreement_logic_single_rank():
   assert not s.should_stop(1) and not s.should_stop(2)
   s.request("operator")
   assert s.should_stop(3) and s.stop_at == 3 and s.reason == "operator" and s.should_stop(4)
+
+
+def test_every_shipped_config_loads_with_its_loader():
+  import glob
+  from pathlib import Path
+  from nmoe_b200.config import from_toml, load_toml
+  from nmoe_b200.data.flow import load_spec
+  from nmoe_b200.data.mixture import resolve_plan
+  from nmoe_b200.data.registry import Registry
+  models = [f for f in sorted(glob.glob("configs/*.toml")) if not f.endswith(("flow_profiles.toml", "tasks.toml"))]
+  assert len(models) >= 6
+  for f in models:
+    cfg = from_toml(f, [], env={})
+    cfg.validate(1)
+    if cfg.batch_size % 8 == 0:
+      cfg.validate(8)
+  for f in glob.glob("configs/**/*.toml", recursive=True):
+    load_toml(f)
+  flows = load_toml("configs/flow_profiles.toml")
+  for name, prof in flows["profiles"].items():
+    plan = resolve_plan(mixture_toml=Path(prof["mixture"]), flow_profiles_toml=Path("configs/flow_profiles.toml"),
+                        flow_section=f"flow.{prof['flow']}", seq_len=4096, active_params_b=3.0)
+    assert plan.stages and plan.stages[0].sources, name
+  for f in glob.glob("configs/dataflow/*.toml"):
+    assert load_spec(Path(f), env={}).prep["output_dir"]
+  assert Registry.load("configs/tasks.toml").tasks
