@@ -288,3 +288,27 @@ def test_task_files_expand_environment_placeholders(tmp_path, monkeypatch):
   monkeypatch.delenv("NMOE_EVAL_DATA")
   assert runner.select_tasks("configs/eval/tasks.toml", "piqa")["piqa"]["source"] == "jsonl:/data/eval/piqa_validation.jsonl"
   assert list(runner.select_tasks("configs/eval/tasks.toml", "chat")) == ["arc_easy", "arc_challenge", "mmlu", "gsm8k", "humaneval"]
+
+
+def test_reserved_gpu_mode_spawns_a_runner_that_finishes(tmp_path, monkeypatch):
+  """eval_mode = "reserved_gpu": rank 0 saves a snapshot and starts the runner as a child process; the child rebuilds the
+  model from the snapshot alone and leaves its summary and metric rows (on this machine it runs on the CPU)."""
+  from nmoe_b200.eval.hooks import maybe_schedule_eval
+  from nmoe_b200.metrics import MetricsWriter
+  tf = _task_file(tmp_path, n=4)
+  cfg = _cfg(metrics_dir=str(tmp_path / "m"), checkpoint_dir=str(tmp_path / "ck"), eval_tasks_file=str(tf), eval_tasks="mc_a",
+             eval_enabled=True, eval_every=2, eval_mode="reserved_gpu", eval_reserved_gpu_id=0, eval_budget_max_examples=3)
+  torch.manual_seed(0)
+  tr = Trainer(cfg)
+  monkeypatch.setenv("RANK", "1")
+  assert maybe_schedule_eval(2, cfg, tr.model, "runR", lambda *_: None) is None          # only rank 0 schedules
+  monkeypatch.setenv("RANK", "0")
+  said = []
+  p = maybe_schedule_eval(2, cfg, tr.model, "runR", said.append)
+  assert p.wait(timeout=120) == 0 and "runner pid" in said[0]
+  snap = tmp_path / "ck" / "eval_snapshots" / "runR_step0000002"
+  summ = json.loads((snap / "summary.json").read_text())
+  assert summ["step"] == 2 and [t["task"] for t in summ["tasks"]] == ["mc_a"] and summ["tasks"][0]["n"] == 3
+  w = MetricsWriter("runR", cfg.metrics_dir, 0)
+  assert w.query("eval/task/mc_a/acc")[0][0] == 2
+  w.close()
