@@ -9,6 +9,7 @@ from __future__ import annotations
 
 import hashlib
 import json
+import struct
 import time
 from dataclasses import asdict, dataclass, field
 from pathlib import Path
@@ -151,7 +152,8 @@ def merge_manifests(parts: Sequence[ManifestInfo]) -> ManifestInfo:
 
 
 def verify_manifest(directory: Path, check_checksums: bool = True) -> ManifestInfo:
-  """Every shard exists, has its index, the token counts add up and (optionally) sha256 matches."""
+  """Every shard exists, its index is readable and tiles the shard, the token and document counts add up and
+  (optionally) sha256 matches."""
   directory = Path(directory)
   m = load_manifest(directory)
   for s in m.shards:
@@ -165,6 +167,17 @@ def verify_manifest(directory: Path, check_checksums: bool = True) -> ManifestIn
       raise ShardChecksumError(f"{s.path}: {n} tokens on disk, manifest says {s.num_tokens}")
     if check_checksums and sha256_file(sp) != s.checksum:
       raise ShardChecksumError(f"{s.path}: sha256 differs from the manifest")
+    # the index must describe this shard: readable, as many documents as the manifest says, boundaries that tile
+    # [0, num_tokens) in order.  A loader trusts these offsets without looking at the tokens.
+    from .index import IndexReader
+    try:
+      b = IndexReader(directory / s.index_path).to_array()
+    except (ValueError, OSError, struct.error) as e:
+      raise IndexMissingError(f"{s.index_path} is unreadable: {e}; rebuild it with regenerate-index") from e
+    if len(b) != s.num_documents:
+      raise IndexMissingError(f"{s.index_path}: {len(b)} documents, manifest says {s.num_documents}")
+    if len(b) and (int(b[0, 0]) != 0 or int(b[-1, 1]) != n or bool((b[1:, 0] != b[:-1, 1]).any()) or bool((b[:, 1] <= b[:, 0]).any())):
+      raise IndexMissingError(f"{s.index_path}: document boundaries do not tile the shard's {n} tokens; rebuild it with regenerate-index")
   if sum(s.num_tokens for s in m.shards) != m.total_tokens:
     raise ShardChecksumError("manifest total_tokens does not match its shards")
   return m

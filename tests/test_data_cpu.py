@@ -783,3 +783,57 @@ train = "nr/train/*.npy"
   assert sinks.load_manifest(tmp_path / "c2" / "toy" / "train").total_documents == 21
   assert main(["prep", "--task", "graded", "--registry", str(reg_file), "--tokenizer", "bytes"]) == 2      # needs a grader or --no-hydra
   assert main(["prep", "--task", "graded", "--registry", str(reg_file), "--corpus-root", str(tmp_path / "c3"), "--tokenizer", "bytes", "--no-hydra"]) == 0
+
+
+def test_inspection_and_maintenance_commands_on_a_small_dataset(tmp_path, capsys):
+  """verify / info / inspect / regenerate-index / merge-manifests / cluster through the command line."""
+  from nmoe_b200.data.cli import main
+  _write_jsonl(tmp_path / "raw.jsonl", 30)
+  common = ["prep", "--source", "jsonl", "--input", str(tmp_path / "raw.jsonl"), "--name", "toy", "--tokenizer", "bytes", "--num-shards", "2"]
+  assert main([*common, "--output", str(tmp_path / "a")]) == 0
+  capsys.readouterr()
+  assert main(["verify", str(tmp_path / "a")]) == 0 and "OK: 2 shards" in capsys.readouterr().out
+  assert main(["verify", str(tmp_path / "a"), "--fast"]) == 0
+  capsys.readouterr()
+  assert main(["info", str(tmp_path / "a")]) == 0
+  info = json.loads(capsys.readouterr().out)
+  assert info["dataset"] == "toy" and info["num_shards"] == 2 and info["total_documents"] == 30
+  shard = sorted((tmp_path / "a").glob("*.npy"))[0]
+  assert main(["inspect", str(shard)]) == 0
+  stats = json.loads(capsys.readouterr().out)
+  assert stats["documents"] > 0 and stats["tokens"] > 0
+  assert main(["inspect", str(shard), "--doc", "0", "--tokenizer", "bytes"]) == 0
+  doc = json.loads(capsys.readouterr().out)
+  assert doc["doc"] == 0 and doc["ids"][-1] == 256 and isinstance(doc.get("text"), str)
+  assert main(["inspect", str(shard), "--start", "2", "--length", "5"]) == 0
+  assert len(json.loads(capsys.readouterr().out)["ids"]) == 5
+  # a lost index comes back from the end-of-document tokens
+  idx = shard.with_suffix(".idx")
+  before = idx.read_bytes()
+  idx.unlink()
+  assert main(["regenerate-index", str(shard), "--eos-token-id", "256"]) == 0 and idx.read_bytes() == before
+  capsys.readouterr()
+  def verify_fails(*flags):
+    with pytest.raises(SystemExit):
+      main(["verify", str(tmp_path / "a"), *flags])
+    return capsys.readouterr().err
+  idx.write_bytes(b"garbage")                                                          # unreadable
+  assert "E-INDEX-MISSING" in (err := verify_fails()) and "unreadable" in err
+  idx.write_bytes(before[:32] + before[48:] + before[32:48])                           # first document moved to the end
+  assert "do not tile" in verify_fails("--fast")
+  idx.write_bytes(before[:-16])                                                        # header still promises the last document
+  assert "E-INDEX-MISSING" in verify_fails("--fast")
+  idx.write_bytes(before)
+  assert main(["verify", str(tmp_path / "a")]) == 0
+  # two workers' outputs merged into one manifest
+  assert main([*common, "--output", str(tmp_path / "b"), "--max-documents", "10"]) == 0
+  capsys.readouterr()
+  assert main(["merge-manifests", str(tmp_path / "a"), str(tmp_path / "b"), "--output", str(tmp_path / "merged.json")]) == 0
+  merged = json.loads((tmp_path / "merged.json").read_text())
+  assert merged["total_documents"] == 40 and merged["num_shards"] == 4 and "merged 2 manifests" in capsys.readouterr().out
+  # clustering of embeddings
+  rng = np.random.default_rng(0)
+  np.save(tmp_path / "emb.npy", np.concatenate([rng.normal(c, 0.1, size=(40, 8)) for c in (-2, 2)]).astype(np.float32))
+  assert main(["cluster", "--embeddings", str(tmp_path / "emb.npy"), "--k", "2", "--output", str(tmp_path / "assign.npy")]) == 0
+  cov = json.loads(capsys.readouterr().out)
+  assert cov["empty_clusters"] == 0 and sorted(np.bincount(np.load(tmp_path / "assign.npy")).tolist()) == [40, 40]
