@@ -98,12 +98,20 @@ def load_tasks(path: str, which: str = "core") -> Dict[str, Dict[str, Any]]:
   d = load_toml(path)          # expands ${NMOE_*:-default} placeholders (task files point at local copies of the sets)
   tasks = d.get("tasks", d)
   groups = d.get("groups", {})
-  names = groups.get(which, list(tasks)) if which else list(tasks)
+  if not which or (not groups and which not in tasks):
+    names = list(tasks)                      # a file without groups is one group
+  elif which in groups:
+    names = groups[which]
+  elif which in tasks:
+    names = [which]                          # a single task by name
+  else:
+    raise KeyError(f"{path}: no group or task named {which!r}; groups {sorted(groups)}, tasks {sorted(tasks)}")
   return {n: tasks[n] for n in names if n in tasks and tasks[n].get("kind", "choices") == "choices"}
 
 
-def run_eval(model, cfg, *, rank: int, world: int, max_examples: int = 500, tasks_file: Optional[str] = None):
-  tasks = load_tasks(tasks_file or cfg.eval_tasks_file, cfg.eval_tasks)
+def run_eval(model, cfg, *, rank: int, world: int, max_examples: int = 500, tasks_file: Optional[str] = None,
+             group: Optional[str] = None):
+  tasks = load_tasks(tasks_file or cfg.eval_tasks_file, group or cfg.eval_tasks)
   enc = get_tokenizer(cfg.tokenizer)
   return {name: eval_task(model, enc, t, rank=rank, world=world, max_examples=max_examples, pad_id=cfg.eos_token_id)
           for name, t in tasks.items()}
@@ -127,13 +135,11 @@ def main(argv=None) -> None:
   from ..checkpoint import Checkpointer, load_checkpoint
   from ..config import from_toml
   from ..train import Trainer
-  cfg = from_toml(a.config)
-  if a.group:
-    cfg.eval_tasks = a.group
+  cfg = from_toml(a.config)      # left as trained: the checkpoint refuses a configuration with another fingerprint
   rank, world, dev = runtime.init(cfg.seed)
   tr = Trainer(cfg, rank=rank, world=world, device=dev)
   load_checkpoint(Checkpointer(cfg.checkpoint_dir, async_io=False), tr, None, None, cfg, rank)
-  res = run_eval(tr.model, cfg, rank=rank, world=world, max_examples=a.max_examples, tasks_file=a.tasks_file)
+  res = run_eval(tr.model, cfg, rank=rank, world=world, max_examples=a.max_examples, tasks_file=a.tasks_file, group=a.group)
   if rank == 0:
     print(format_results(res))
   runtime.finalize()

@@ -312,3 +312,40 @@ def test_reserved_gpu_mode_spawns_a_runner_that_finishes(tmp_path, monkeypatch):
   w = MetricsWriter("runR", cfg.metrics_dir, 0)
   assert w.query("eval/task/mc_a/acc")[0][0] == 2
   w.close()
+
+
+def test_checkpoint_evaluation_commands_choices_and_generation(tmp_path, monkeypatch, capsys):
+  """`python -m nmoe_b200.eval.choices CONFIG` and `... eval.run_gen CONFIG`: load the latest checkpoint of a trained
+  configuration and score it, from a TOML file as a user would."""
+  from nmoe_b200.train import train
+  tf = _task_file(tmp_path, n=4)
+  toml = tmp_path / "cfg.toml"
+  keys = dict(vocab_size=257, eos_token_id=256, tokenizer="bytes", dim=64, n_layers=2, n_heads=2, inter_dim=128, moe_inter_dim=32,
+              n_routed_experts=4, n_activated_experts=2, n_shared_experts=1, n_dense_layers=1, q_lora_rank=32, kv_lora_rank=16,
+              qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=16, batch_size=2, seq_len=64, max_position_embeddings=512,
+              activation_checkpoint="none", steps=2, checkpoint_every=2, log_every=1, data_path="synthetic",
+              checkpoint_dir=str(tmp_path / "ck"), metrics_dir=str(tmp_path / "m"), experiments_db=str(tmp_path / "e.db"),
+              eval_tasks_file=str(tf), eval_tasks="core")
+  toml.write_text("".join(f"{k} = {json.dumps(v)}\n" for k, v in keys.items()))
+  from nmoe_b200.config import from_toml
+  monkeypatch.setenv("NMOE_RUN", "evalcmd")
+  train(from_toml(toml, [], env={}))
+  capsys.readouterr()
+  choices.main([str(toml), "--max-examples", "3"])
+  out = capsys.readouterr().out
+  assert "mean_centered=" in out and "mc_a:acc=" in out and "mc_b:acc=" in out and "n=3" in out
+  choices.main([str(toml), "--max-examples", "2", "--group", "mc_b", "--tasks-file", str(tf)])
+  run_gen.main([str(toml), "--tasks-file", str(tf), "--max-examples", "2", "--max-new", "3"])
+  assert "qa: acc=" in capsys.readouterr().out
+
+
+def test_choice_task_selection_by_group_name_or_whole_file(tmp_path):
+  import pytest
+  tf = _task_file(tmp_path, n=2)
+  assert list(choices.load_tasks(str(tf), "core")) == ["mc_a", "mc_b"] and list(choices.load_tasks(str(tf), "mc_b")) == ["mc_b"]
+  assert list(choices.load_tasks(str(tf), "")) == ["mc_a", "mc_b", "offline"]           # everything that is multiple choice
+  with pytest.raises(KeyError, match="no group or task named 'nope'"):
+    choices.load_tasks(str(tf), "nope")
+  flat = tmp_path / "flat.toml"
+  flat.write_text('[tasks.only]\nkind = "choices"\nsource = "jsonl:/nowhere.jsonl"\n')
+  assert list(choices.load_tasks(str(flat), "core")) == ["only"]                         # no groups: the file is the group
