@@ -349,3 +349,18 @@ def test_choice_task_selection_by_group_name_or_whole_file(tmp_path):
   flat = tmp_path / "flat.toml"
   flat.write_text('[tasks.only]\nkind = "choices"\nsource = "jsonl:/nowhere.jsonl"\n')
   assert list(choices.load_tasks(str(flat), "core")) == ["only"]                         # no groups: the file is the group
+
+
+def test_training_with_inline_evaluation_records_both_tag_families(tmp_path, monkeypatch):
+  from nmoe_b200.metrics import MetricsWriter
+  from nmoe_b200.train import train
+  tf = _task_file(tmp_path, n=4)
+  monkeypatch.setenv("NMOE_RUN", "inl")
+  cfg = _cfg(steps=4, log_every=2, checkpoint_every=100, data_path="synthetic", checkpoint_dir=str(tmp_path / "ck"),
+             metrics_dir=str(tmp_path / "m"), experiments_db=str(tmp_path / "e.db"), eval_tasks_file=str(tf), eval_tasks="core",
+             eval_enabled=True, eval_every=2, eval_mode="inline", eval_budget_max_examples=2)
+  train(cfg)
+  w = MetricsWriter("inl", cfg.metrics_dir, 0)
+  assert [s for s, _ in w.query("eval_choices/mc_a/acc")] == [2, 4]                 # the training loop's own evaluation
+  assert [s for s, _ in w.query("eval/CORE")] == [2, 4] and w.query("eval/task/qa/acc")     # the snapshot runner, inline
+  w.close()
