@@ -600,7 +600,9 @@ def cmd_rephrase(a) -> int:
   with open(a.output, "w", encoding="utf-8") as f:
     for r in kept:
       f.write(json.dumps({"id": rows[r.doc].get("id", r.doc), "version": r.version, "style": r.style, "text": r.text}) + "\n")
-  print(f"{len(rew)} rewrites, {len(kept)} kept -> {a.output}")
+  info = rephrase_batch.last_info
+  note = f" (chunks of {info['chunk_size']} tokens to fit the context)" if info["chunk_size"] < a.chunk_size else ""
+  print(f"{len(rew)} rewrites, {len(kept)} kept -> {a.output}{note}")
   return 0
 
 

@@ -37,6 +37,7 @@ def chunk_text(text: str, tok: Tokenizer, chunk_size: int = 2048, overlap: int =
   ids = tok.encode(text)
   if len(ids) <= chunk_size:
     return [text]
+  overlap = min(overlap, chunk_size // 2)      # an overlap of a window or more would never advance
   step = max(1, chunk_size - overlap)
   out = []
   for s in range(0, len(ids), step):
@@ -74,6 +75,16 @@ def rephrase_batch(engine, tok: Tokenizer, texts: Sequence[str], *, num_versions
   styles = list(STYLE_PROMPTS) if use_style_diversity else ["default"]
   stop = set(int(t) for t in stop_tokens)
   gen = torch.Generator(device="cpu").manual_seed(seed)
+  # A chunk, its instructions and its rewrite (up to max_new_factor times the chunk) share the engine's context: the
+  # largest chunk that leaves the rewrite its full budget.  Asking for more would cut rewrites short without a word.
+  overhead = max(len(format_prompt(tok, "", STYLE_PROMPTS.get(st, DEFAULT_INSTRUCTION), fmt)) for st in styles[:max(1, num_versions)])
+  fit = int((engine.max_seq_len - overhead - 18) / (1.0 + max_new_factor))
+  if fit < 16:
+    raise ValueError(f"a context of {engine.max_seq_len} tokens leaves no room to rewrite anything: the instructions alone take "
+                     f"{overhead} tokens with this tokenizer; raise the context length")
+  if chunk_size > fit:
+    chunk_size, overlap = fit, min(overlap, fit // 8)
+  rephrase_batch.last_info = {"chunk_size": chunk_size, "overlap": min(overlap, chunk_size // 2), "dropped_chunks": 0}
   jobs = []                                   # (doc, version, chunk index, style)
   sid_of = {}
   for d, text in enumerate(texts):
@@ -85,7 +96,8 @@ def rephrase_batch(engine, tok: Tokenizer, texts: Sequence[str], *, num_versions
         prompt = format_prompt(tok, ch, instr, fmt)
         budget = int(len(tok.encode(ch)) * max_new_factor) + 16
         room = engine.max_seq_len - len(prompt) - 1
-        if room <= 0:
+        if room <= 0:                         # cannot happen after the fit above unless a tokenizer is wildly non-additive
+          rephrase_batch.last_info["dropped_chunks"] += 1
           continue
         sid = engine.add(prompt, max(1, min(budget, room)))
         sid_of[sid] = (d, v, c, style)

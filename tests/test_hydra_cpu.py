@@ -457,3 +457,23 @@ def test_calibration_from_labels_alone_and_oracle_labelling_over_shards(tmp_path
   assert main([*cmd, "--resume"]) == 0
   got = [json.loads(l) for l in open(out)]
   assert [g["doc_id"] for g in got] == [str(r) for r in D.read_refs(refs_file)] and all("ok" in g and "raw" in g for g in got)
+
+
+def test_rephrase_command_with_and_without_filters(tmp_path):
+  import json
+  from nmoe_b200.data.cli import main
+  from nmoe_b200.serve.checkpoint import save_model
+  save_model(backbone(), str(tmp_path / "ckpt"))
+  docs = tmp_path / "docs.jsonl"
+  docs.write_text("".join(json.dumps({"id": f"d{i}", "text": f"The reactor reached {400 + i} degrees in {10 + i} minutes. " * 2}) + "\n" for i in range(3)))
+  base = ["rephrase", "--checkpoint", str(tmp_path / "ckpt"), "--input", str(docs), "--tokenizer", "bytes", "--max-ctx", "1200", "--batch-size", "4",
+          "--num-versions", "2", "--chunk-size", "2048"]
+  assert main([*base, "--output", str(tmp_path / "raw.jsonl"), "--no-filter"]) == 0
+  rows = [json.loads(l) for l in open(tmp_path / "raw.jsonl")]
+  assert len(rows) == 6 and {r["id"] for r in rows} == {"d0", "d1", "d2"} and {r["version"] for r in rows} == {0, 1} and all("style" in r for r in rows)
+  import pytest
+  with pytest.raises(ValueError, match="leaves no room"):
+    main([*base[:base.index("--max-ctx")], "--max-ctx", "200", *base[base.index("--max-ctx") + 2:], "--output", str(tmp_path / "x.jsonl")])
+  # a random backbone writes noise: the lexical bounds drop all of it, with or without the embedding check
+  assert main([*base, "--output", str(tmp_path / "lex.jsonl")]) == 0 and open(tmp_path / "lex.jsonl").read() == ""
+  assert main([*base, "--output", str(tmp_path / "sem.jsonl"), "--semantic-threshold", "0.85"]) == 0 and open(tmp_path / "sem.jsonl").read() == ""
