@@ -97,6 +97,13 @@ def test_dataset_browser_routes(tmp_path, monkeypatch):
     idx = shard[:-4] + ".idx"
     hdr = _get(port, f"/api/datasets/index/header?path={idx}")
     assert hdr["documents"] == 20 and hdr["tokens_covered"] == st["tokens"]
+    # the reference's parameter names for the same routes
+    assert _get(port, f"/api/datasets/index/doc?shard_path={shard}&doc_idx=1&max_tokens=4")["ids"] == \
+        _get(port, f"/api/datasets/index/doc?path={idx}&doc=1")["ids"][:4]
+    assert len(_get(port, "/api/datasets/manifest?path=flows/dev/web&limit_shards=2")["shards"]) == 2
+    (root / "notes.txt").write_text("line of text\n" * 500)
+    assert _get(port, "/api/datasets/preview?path=notes.txt&max_bytes=2000")["bytes"] == 2000
+    assert _get(port, "/api/datasets/preview?path=notes.txt&max_bytes=10")["bytes"] == 1024          # the floor
     doc = _get(port, f"/api/datasets/index/doc?path={idx}&doc=1")
     assert doc["tokens"] == len(doc["ids"]) and doc["ids"][-1] == 256
     flow = _get(port, "/api/datasets/pipeline?path=flows/dev")
