@@ -837,3 +837,39 @@ def test_inspection_and_maintenance_commands_on_a_small_dataset(tmp_path, capsys
   assert main(["cluster", "--embeddings", str(tmp_path / "emb.npy"), "--k", "2", "--output", str(tmp_path / "assign.npy")]) == 0
   cov = json.loads(capsys.readouterr().out)
   assert cov["empty_clusters"] == 0 and sorted(np.bincount(np.load(tmp_path / "assign.npy")).tolist()) == [40, 40]
+
+
+def test_text_parquet_and_arrow_sources(tmp_path):
+  import pyarrow as pa
+  import pyarrow.parquet as pq
+  from nmoe_b200.data.cli import main
+  from nmoe_b200.data.errors import SourceNotFoundError
+  from nmoe_b200.data.sources import create_source
+  rows = [{"id": f"r{i}", "text": f"row {i} " * 5, "extra": i} for i in range(7)] + [{"id": "empty", "text": "", "extra": -1}]
+  tbl = pa.Table.from_pylist(rows)
+  pq.write_table(tbl, str(tmp_path / "a.parquet"))
+  with pa.ipc.new_file(str(tmp_path / "b.arrow"), tbl.schema) as w:
+    w.write_table(tbl)
+  with pa.ipc.new_stream(str(tmp_path / "c.arrow"), tbl.schema) as w:                  # the streaming variant of the format
+    w.write_table(tbl)
+  for pat in ("a.parquet", "b.arrow", "c.arrow"):
+    docs = list(create_source("arrow", paths=str(tmp_path / pat)))
+    assert [d.doc_id for d in docs] == [f"r{i}" for i in range(7)] and docs[2].text == "row 2 " * 5, pat
+  noid = list(create_source("parquet", paths=str(tmp_path / "a.parquet"), id_field=None))
+  assert noid[0].doc_id == "a.parquet:0" and noid[6].doc_id == "a.parquet:6"
+  (tmp_path / "notes.txt").write_text("first block\nstill first\n\nsecond block\n\n\n")
+  (tmp_path / "readme.md").write_text("a markdown file")
+  whole = list(create_source("text", paths=str(tmp_path)))
+  assert sorted(d.doc_id for d in whole) == ["notes.txt", "readme.md"]
+  parts = list(create_source("text", paths=str(tmp_path / "notes.txt"), split_on="\n\n"))
+  assert [d.text.strip() for d in parts] == ["first block\nstill first", "second block"]
+  with pytest.raises(SourceNotFoundError):
+    create_source("arrow", paths=str(tmp_path / "none"))
+  with pytest.raises(SourceNotFoundError, match="unknown source kind"):
+    create_source("csv", paths=str(tmp_path))
+  assert main(["prep", "--source", "parquet", "--input", str(tmp_path / "a.parquet"), "--output", str(tmp_path / "out"), "--name", "p",
+               "--tokenizer", "bytes", "--num-shards", "1"]) == 0
+  assert sinks.load_manifest(tmp_path / "out").total_documents == 7
+  assert main(["prep", "--source", "text", "--input", str(tmp_path / "notes.txt"), "--output", str(tmp_path / "out2"), "--name", "t",
+               "--tokenizer", "bytes", "--num-shards", "1"]) == 0
+  assert sinks.load_manifest(tmp_path / "out2").total_documents == 1
