@@ -873,3 +873,54 @@ def test_text_parquet_and_arrow_sources(tmp_path):
   assert main(["prep", "--source", "text", "--input", str(tmp_path / "notes.txt"), "--output", str(tmp_path / "out2"), "--name", "t",
                "--tokenizer", "bytes", "--num-shards", "1"]) == 0
   assert sinks.load_manifest(tmp_path / "out2").total_documents == 1
+
+
+def test_journey_prepare_a_mixture_train_on_it_and_resume_exactly(tmp_path, monkeypatch, capsys):
+  """raw JSONL of two sources -> `prep-mixture` -> `train()` with flow_mode on the prepared shards -> a run cut at step 3
+  and restarted ends where the uninterrupted run ends (loader cursors of both sources are part of the checkpoint)."""
+  import nmoe_b200.metrics as M
+  from nmoe_b200.config import Config
+  from nmoe_b200.data.cli import main
+  from nmoe_b200.train import train
+  mix = tmp_path / "mix.toml"
+  mix.write_text('[profiles]\npretrain_profile = "mine"\n[mixtures.mine]\ntotal_tokens_b = 0.001\n'
+                 'sources = [{id = "a", tokens_b = 3.0}, {id = "b", tokens_b = 1.0}]\n')
+  flows = tmp_path / "flows.toml"
+  flows.write_text('[flow.dev]\nmode = "dev"\nstages = ["pretrain"]\ntokens_b = 0.00002\n[flow.dev.mixture]\npretrain = "pretrain_main"\n')
+  for name in ("a", "b"):
+    d = tmp_path / "raw" / name
+    d.mkdir(parents=True)
+    (d / "x.jsonl").write_text("".join(json.dumps({"id": f"{name}{i}", "text": f"{name} document number {i} says hello. " * 12}) + "\n" for i in range(60)))
+  assert main(["prep-mixture", "--config", str(mix), "--flow-profiles", str(flows), "--flow", "dev", "--seq-len", "32", "--tokenizer", "bytes",
+               "--num-shards", "2", "--local-root", str(tmp_path / "raw"), "--data-root", str(tmp_path / "data")]) == 0
+  capsys.readouterr()
+  assert (tmp_path / "data" / "flows" / "dev" / "pretrain" / "a" / "train" / "manifest.json").exists()
+  def cfg_for(tag, **kw):
+    base = dict(vocab_size=257, eos_token_id=256, tokenizer="bytes", dim=64, n_layers=2, n_heads=2, inter_dim=128, moe_inter_dim=32,
+                n_routed_experts=4, n_activated_experts=2, n_shared_experts=1, n_dense_layers=1, q_lora_rank=32, kv_lora_rank=16,
+                qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=16, batch_size=4, seq_len=32, max_position_embeddings=64,
+                warmup_steps=2, steps=6, log_every=1, checkpoint_every=100, activation_checkpoint="none", data_path=None,
+                data_root=str(tmp_path / "data"), mixture_toml=str(mix), flow_profiles_toml=str(flows), flow_mode="dev",
+                checkpoint_dir=str(tmp_path / tag / "ck"), metrics_dir=str(tmp_path / tag / "m"), experiments_db=str(tmp_path / tag / "e.db"))
+    base.update(kw)
+    return Config(**base)
+  monkeypatch.setenv("NMOE_RUN", "whole")
+  whole = train(cfg_for("whole"))
+  assert whole["steps_completed"] == 6 and "streaming" not in capsys.readouterr().out
+  # the same run, stopped after step 3 by a signal and started again
+  import os, signal
+  real_log = M.log_training_step
+  def log_and_signal(metrics, s, *a, **kw):
+    if s == 3:
+      os.kill(os.getpid(), signal.SIGUSR1)
+    return real_log(metrics, s, *a, **kw)
+  monkeypatch.setattr(M, "log_training_step", log_and_signal)
+  monkeypatch.setenv("NMOE_RUN", "cut")
+  assert train(cfg_for("cut"))["steps_completed"] == 3
+  monkeypatch.setattr(M, "log_training_step", real_log)
+  rest = train(cfg_for("cut"))
+  assert rest["steps_completed"] == 6 and rest["final_loss"] == whole["final_loss"]
+  # a different mixture plan under the same checkpoint directory is refused
+  mix.write_text(mix.read_text().replace("tokens_b = 3.0", "tokens_b = 2.0"))
+  with pytest.raises(RuntimeError, match="plan"):
+    train(cfg_for("cut", steps=6))
