@@ -12,12 +12,16 @@ between steps:
   more than a step apart (each step's collectives keep them together), so with ``margin = 2`` every rank learns of the
   stop before it gets there, and all of them checkpoint the same step.
 
+A second signal is not intercepted: it acts as it would have without this module (so a launcher that tears a job
+down is never kept waiting by a rank stuck in a collective).
+
 The training loop then writes a checkpoint for that step, records the run as ``killed`` and returns; a restart with the
 same configuration resumes from it exactly.  The reference has no counterpart (its runs end as ``completed`` or
 ``failed``; the ``killed`` status exists in its schema but nothing sets it, nmoe/experiments.py:150-163).
 """
 from __future__ import annotations
 
+import os
 import signal
 from typing import Iterable, Optional
 
@@ -50,6 +54,12 @@ class StopRequest:
 
   def _on_signal(self, signum, _frame) -> None:
     # nothing but a flag here: the handler can run in the middle of anything
+    if self.requested:
+      # asked twice: the sender is not waiting for a checkpoint (a launcher tearing the job down after another rank
+      # failed, an impatient operator).  Put the original disposition back and let the signal do what it would have done.
+      self.restore()
+      os.kill(os.getpid(), signum)
+      return
     self.requested = True
     self.reason = signal.Signals(signum).name
 

@@ -469,3 +469,22 @@ def test_every_shipped_config_loads_with_its_loader():
   for f in glob.glob("configs/dataflow/*.toml"):
     assert load_spec(Path(f), env={}).prep["output_dir"]
   assert Registry.load("configs/tasks.toml").tasks
+
+
+def test_second_stop_signal_is_not_intercepted():
+  """The first SIGUSR1 asks for a checkpointed stop; the second gets the disposition the process had before."""
+  import os
+  import signal
+  from nmoe_b200.utils.stop import StopRequest
+  hits = []
+  before = signal.signal(signal.SIGUSR1, lambda s, f: hits.append(s))
+  try:
+    st = StopRequest(1, signals=(signal.SIGUSR1,))
+    os.kill(os.getpid(), signal.SIGUSR1)
+    assert st.requested and st.reason == "SIGUSR1" and hits == []
+    os.kill(os.getpid(), signal.SIGUSR1)
+    assert hits == [signal.SIGUSR1]                         # went to the handler that was there before
+    os.kill(os.getpid(), signal.SIGUSR1)
+    assert len(hits) == 2 and st.should_stop(1)
+  finally:
+    signal.signal(signal.SIGUSR1, before)
