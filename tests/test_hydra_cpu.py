@@ -477,3 +477,31 @@ def test_rephrase_command_with_and_without_filters(tmp_path):
   # a random backbone writes noise: the lexical bounds drop all of it, with or without the embedding check
   assert main([*base, "--output", str(tmp_path / "lex.jsonl")]) == 0 and open(tmp_path / "lex.jsonl").read() == ""
   assert main([*base, "--output", str(tmp_path / "sem.jsonl"), "--semantic-threshold", "0.85"]) == 0 and open(tmp_path / "sem.jsonl").read() == ""
+
+
+def test_calibrate_command_from_judged_rows_against_oracle_labels(tmp_path, capsys):
+  """`hydra-calibrate --judged --oracle`: the judge's own predictions joined with oracle labels by document id
+  (`doc_id` or `id` on the oracle side), thresholds that separate the oracle's keeps."""
+  import json
+  import random
+  from nmoe_b200.data.cli import main
+  rnd = random.Random(1)
+  judged, oracle = [], []
+  for i in range(200):
+    good = i % 2 == 0
+    sc = {d: min(4.0, max(0.0, (3.2 if good else 1.0) + rnd.uniform(-0.6, 0.6))) for d in H.RUBRIC}
+    judged.append({"doc_id": f"d{i}", "scores": sc})
+    oracle.append({("doc_id" if i % 3 else "id"): f"d{i}", "aggregated": 0.8 if good else 0.2, "scores": sc})
+  judged.append({"doc_id": "early", "scores": None})                         # dropped at the probe: no rubric scores
+  (tmp_path / "judged.jsonl").write_text("".join(json.dumps(r) + "\n" for r in judged))
+  (tmp_path / "oracle.jsonl").write_text("".join(json.dumps(r) + "\n" for r in oracle))
+  assert main(["hydra-calibrate", "--judged", str(tmp_path / "judged.jsonl"), "--oracle", str(tmp_path / "oracle.jsonl"),
+               "--output", str(tmp_path / "cal"), "--oracle-keep", "0.6", "--keep-precision", "0.95"]) == 0
+  assert "200 documents" in capsys.readouterr().out
+  cal = H.Calibration.load(str(tmp_path / "cal"))
+  agg = lambda r: H.aggregate_scores(r["scores"], cal.weights)
+  keeps = [agg(r) >= cal.tau_keep for r in judged[:200]]
+  assert sum(k and i % 2 == 0 for i, k in enumerate(keeps)) >= 90 and sum(k and i % 2 == 1 for i, k in enumerate(keeps)) <= 5
+  assert cal.tau_drop <= cal.tau_keep
+  (tmp_path / "other.jsonl").write_text(json.dumps({"doc_id": "zzz", "aggregated": 0.5}) + "\n")
+  assert main(["hydra-calibrate", "--judged", str(tmp_path / "judged.jsonl"), "--oracle", str(tmp_path / "other.jsonl"), "--output", str(tmp_path / "c2")]) == 2
