@@ -130,6 +130,7 @@ class Config:
   mixture_toml: Optional[str] = None
   flow_profiles_toml: Optional[str] = None
   flow_mode: Optional[str] = None
+  tasks_toml: Optional[str] = None    # corpus registry: mixture sources without shards under the flow directory resolve as its tasks
   active_params_b: Optional[float] = None
 
   # ---- metrics

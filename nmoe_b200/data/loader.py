@@ -268,7 +268,16 @@ def build_loader(cfg, rank: int, world_size: int, split: str = "train", print_fn
       raise ValueError("flow_mode needs mixture_toml and flow_profiles_toml")
     plan = resolve_plan(mixture_toml=Path(cfg.mixture_toml), flow_profiles_toml=Path(cfg.flow_profiles_toml),
                         flow_section=f"flow.{cfg.flow_mode}", seq_len=cfg.seq_len, active_params_b=cfg.active_params_b)
-    populate_paths(plan, dataset_root=Path(cfg.data_root) / "flows" / cfg.flow_mode, split=split)
+    registry = None
+    if getattr(cfg, "tasks_toml", None):
+      from .registry import Registry
+      registry = Registry.load(cfg.tasks_toml)
+    populate_paths(plan, dataset_root=Path(cfg.data_root) / "flows" / cfg.flow_mode, split=split, registry=registry)
+    missing = [f"{st.stage_id}/{sp.id}" for st in plan.stages for sp in st.sources if not sp.paths]
+    if missing:
+      where = f"{Path(cfg.data_root) / 'flows' / cfg.flow_mode}" + (f" or as tasks of {cfg.tasks_toml}" if registry is not None else "")
+      raise RuntimeError(f"sources without shards (not ready): {', '.join(missing)}; looked under {where}.  "
+                         "Build them with `data.cli prep-mixture` or `data.cli prep --task ID`.")
     flow_tokens = int(sum(s.total_tokens_b for s in plan.stages) * 1e9)
     if cfg.steps <= 0:
       cfg.steps = flow_tokens // (cfg.batch_size * cfg.seq_len)

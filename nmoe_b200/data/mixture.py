@@ -158,12 +158,16 @@ def resolve_plan(*, mixture_toml: Path, flow_profiles_toml: Path, flow_section: 
   return plan
 
 
-def populate_paths(plan: MixturePlan, *, dataset_root: Path, split: str = "train") -> None:
-  """Fill ``paths`` from ``{dataset_root}/{stage}/{source}/{split}/**/*.npy``."""
+def populate_paths(plan: MixturePlan, *, dataset_root: Path, split: str = "train", registry=None) -> None:
+  """Fill ``paths`` from ``{dataset_root}/{stage}/{source}/{split}/**/*.npy``.  A source that has nothing there and is a
+  task of the corpus registry (``data.registry.Registry``, same id) takes the task's shards instead: corpora built once
+  with ``prep --task`` serve every flow without being copied under each flow's directory."""
   for st in plan.stages:
     for sp in st.sources:
       sp.paths = sorted(set(glob.glob(str(Path(dataset_root) / st.stage_id / sp.id / split / "**" / "*.npy"),
                                       recursive=True)))
+      if not sp.paths and registry is not None and sp.id in registry.tasks:
+        sp.paths = registry.shard_files(sp.id, split)
 
 
 def single_source_plan(paths: List[str], seq_len: int, total_tokens: int, source_id: str = "data_path") -> MixturePlan:

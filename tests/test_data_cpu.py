@@ -2,6 +2,7 @@
 import json
 
 import numpy as np
+import torch
 import pytest
 
 from nmoe_b200.data import cli, dedup, diversity, flow as flow_mod, index, inspect as insp, sinks
@@ -924,3 +925,35 @@ def test_journey_prepare_a_mixture_train_on_it_and_resume_exactly(tmp_path, monk
   mix.write_text(mix.read_text().replace("tokens_b = 3.0", "tokens_b = 2.0"))
   with pytest.raises(RuntimeError, match="plan"):
     train(cfg_for("cut", steps=6))
+
+
+def test_mixture_sources_resolve_through_the_corpus_registry(tmp_path, monkeypatch):
+  """A corpus built once with `prep --task` feeds a flow whose directory holds nothing for that source; a source that is
+  nowhere makes training refuse to start with the list of what is missing."""
+  from nmoe_b200.config import Config
+  from nmoe_b200.data.cli import main
+  from nmoe_b200.data.loader import build_loader
+  raw = tmp_path / "raw"
+  raw.mkdir()
+  (raw / "a.jsonl").write_text("".join(json.dumps({"id": f"d{i}", "text": f"registered corpus document {i} with some length. " * 6}) + "\n" for i in range(50)))
+  reg = tmp_path / "tasks.toml"
+  reg.write_text(f'[corpus]\nroot = "{tmp_path / "corpus"}"\n[corpus.contract]\ntokenizer = "bytes"\nvocab_size = 257\neos_token_id = 256\ndtype = "uint32"\n'
+                 f'[corpus.prep_defaults]\nhygiene = true\nnum_shards = 2\n[tasks.web_a]\n[tasks.web_a.shards]\ntrain = "web_a/train/**/*.npy"\n'
+                 f'[tasks.web_a.raw]\nkind = "jsonl"\nglob = "{raw}/*.jsonl"\n')
+  assert main(["prep", "--task", "web_a", "--registry", str(reg), "--tokenizer", "bytes"]) == 0
+  mix = tmp_path / "mix.toml"
+  mix.write_text('[profiles]\npretrain_profile = "mine"\n[mixtures.mine]\ntotal_tokens_b = 0.001\nsources = [{id = "web_a", tokens_b = 1.0}]\n')
+  flows = tmp_path / "flows.toml"
+  flows.write_text('[flow.dev]\nmode = "dev"\nstages = ["pretrain"]\ntokens_b = 0.00001\n[flow.dev.mixture]\npretrain = "pretrain_main"\n')
+  kw = dict(vocab_size=257, eos_token_id=256, tokenizer="bytes", dim=8, n_layers=1, n_heads=1, batch_size=2, seq_len=16, steps=3, data_path=None,
+            data_root=str(tmp_path / "data"), mixture_toml=str(mix), flow_profiles_toml=str(flows), flow_mode="dev")
+  said = []
+  loader, plan = build_loader(Config(**kw, tasks_toml=str(reg)), 0, 1, print_fn=said.append)
+  assert len(plan.stages[0].sources[0].paths) == 2 and str(tmp_path / "corpus") in plan.stages[0].sources[0].paths[0]
+  x, y = loader.next()
+  assert x.shape == (2, 16) and torch.equal(x[:, 1:], y[:, :-1])
+  with pytest.raises(RuntimeError, match="not ready.*pretrain/web_a"):
+    build_loader(Config(**kw), 0, 1, print_fn=said.append)                      # no registry: nothing under the flow directory
+  mix.write_text(mix.read_text().replace('id = "web_a"', 'id = "web_b"'))
+  with pytest.raises(RuntimeError, match="pretrain/web_b.*tasks of"):
+    build_loader(Config(**kw, tasks_toml=str(reg)), 0, 1, print_fn=said.append)
