@@ -288,6 +288,7 @@ class PhaseConfig:
   rank_weight: float = 0.5         # phase B: pairwise ranking term on (better, worse) pairs
   rank_margin: float = 0.1
   log_every: int = 100
+  clip: float = 1.0                # gradient-norm clip; backbone states are not normalised, early steps can be huge
 
 
 Features = Callable[[dict], Tuple[torch.Tensor, torch.Tensor, torch.Tensor]]
@@ -324,6 +325,8 @@ def train_heads(cfg: PhaseConfig, probe: ProbeHead, judge: JudgeHead, batches: I
       raise ValueError(f"unknown phase {cfg.phase!r}")
     opt.zero_grad(set_to_none=True)
     loss.backward()
+    if cfg.clip and cfg.clip > 0:
+      torch.nn.utils.clip_grad_norm_(params, cfg.clip)
     opt.step()
     losses.append(float(loss.detach()))
     if log is not None and (step + 1) % cfg.log_every == 0:

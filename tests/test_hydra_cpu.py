@@ -2,6 +2,8 @@
 early exit (resumed from the probe layer), JSON score parsing, chunked rephrasing, fidelity filter."""
 import itertools
 
+import pytest
+
 import torch
 
 from nmoe_b200.data import hydra as H
@@ -505,3 +507,27 @@ def test_calibrate_command_from_judged_rows_against_oracle_labels(tmp_path, caps
   assert cal.tau_drop <= cal.tau_keep
   (tmp_path / "other.jsonl").write_text(json.dumps({"doc_id": "zzz", "aggregated": 0.5}) + "\n")
   assert main(["hydra-calibrate", "--judged", str(tmp_path / "judged.jsonl"), "--oracle", str(tmp_path / "other.jsonl"), "--output", str(tmp_path / "c2")]) == 2
+
+
+def test_hydra_train_command_phases_b_and_c_from_a_flat_jsonl(tmp_path, capsys):
+  import json
+  from nmoe_b200.data.cli import main
+  from nmoe_b200.serve.checkpoint import save_model
+  save_model(backbone(), str(tmp_path / "ckpt"))
+  data = tmp_path / "docs.jsonl"
+  with open(data, "w") as f:
+    for i in range(16):
+      row = {"id": f"d{i}", "text": ("clear and useful prose " if i % 2 else "zz## 00 ") * 4}
+      if i < 12:
+        row["scores"] = {d: float(3 if i % 2 else 1) for d in H.RUBRIC}
+      f.write(json.dumps(row) + "\n")
+  heads = tmp_path / "heads"
+  common = ["hydra-train", "--checkpoint", str(tmp_path / "ckpt"), "--input", str(data), "--tokenizer", "bytes", "--max-ctx", "64",
+            "--batch-size", "8", "--heads", str(heads), "--steps", "40", "--lr", "0.002"]
+  assert main([*common, "--phase", "B"]) == 0
+  out = capsys.readouterr().out
+  first, last = [float(x) for x in out.strip().splitlines()[-1].split("loss ")[1].split(";")[0].split(" -> ")]
+  assert last < first                                                        # the judge learns the two levels
+  assert main([*common, "--phase", "C"]) == 0 and (heads / "hydra_probe.pt").exists() or any(heads.iterdir())
+  with pytest.raises(SystemExit):
+    main(["hydra-train", "--checkpoint", str(tmp_path / "ckpt"), "--heads", str(heads), "--phase", "A", "--tokenizer", "bytes"])
