@@ -957,3 +957,28 @@ def test_mixture_sources_resolve_through_the_corpus_registry(tmp_path, monkeypat
   mix.write_text(mix.read_text().replace('id = "web_a"', 'id = "web_b"'))
   with pytest.raises(RuntimeError, match="pretrain/web_b.*tasks of"):
     build_loader(Config(**kw, tasks_toml=str(reg)), 0, 1, print_fn=said.append)
+
+
+def test_flow_command_streaming_and_staged_give_the_same_dataset(tmp_path, capsys, monkeypatch):
+  from nmoe_b200.data.cli import main
+  raw = tmp_path / "raw.jsonl"
+  raw.write_text("".join(json.dumps({"id": f"d{i}", "text": f"flow document {i} " * 6}) + "\n" for i in range(25)))
+  def spec(out):
+    p = tmp_path / f"{out}.toml"
+    p.write_text(f'[source]\nkind = "jsonl"\npaths = "{raw}"\n[prep]\noutput_dir = "{tmp_path / out}"\ndataset = "f"\ntokenizer = "bytes"\nnum_shards = 2\n')
+    return str(p)
+  assert main(["flow", spec("s1")]) == 0 and main(["flow", spec("s2"), "--staged"]) == 0
+  a, b = sinks.load_manifest(tmp_path / "s1"), sinks.load_manifest(tmp_path / "s2")
+  assert (a.total_documents, a.total_tokens) == (b.total_documents, b.total_tokens) == (25, a.total_tokens)
+  assert (tmp_path / "s2" / "stages" / "raw.jsonl").exists() and json.loads((tmp_path / "s2" / "stages" / "state.json").read_text())["done"]["shards"] == 25
+  # two indexed workers through the environment, as a batch job sets it
+  monkeypatch.setenv("NMOE_FLOW_WORKERS", "2")
+  for i in (0, 1):
+    monkeypatch.setenv("JOB_COMPLETION_INDEX", str(i))
+    assert main(["flow", spec("s3"), "--staged"]) == 0
+  parts = [sinks.load_manifest(tmp_path / "s3" / f"worker_{i:04d}") for i in (0, 1)]
+  assert sum(p.total_documents for p in parts) == 25 and all(p.total_documents > 0 for p in parts)
+  # a specification that asks for grading without naming a model is refused before any work
+  p = tmp_path / "g.toml"
+  p.write_text(open(spec("s4")).read() + "[grade]\nenabled = true\n")
+  assert main(["flow", str(p)]) == 2 and "names no checkpoint" in capsys.readouterr().err
