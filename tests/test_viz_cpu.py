@@ -385,3 +385,30 @@ def test_dashboard_image_file_list_covers_the_servers_imports(tmp_path):
   out = subprocess.run([sys.executable, "-c", code], cwd=stage, capture_output=True, text=True,
                        env={"PATH": "/usr/bin:/bin", "PYTHONPATH": str(stage), "NVIZ_DATASETS_DIR": str(data)})
   assert out.returncode == 0 and out.stdout.split() == ["10", "True"], out.stderr[-2000:]
+
+
+def test_server_answers_malformed_requests_without_dying(tmp_path):
+  """Bad numbers, unknown routes, odd paths: an error body and the right status, and the next request still works."""
+  w = MetricsWriter("r", str(tmp_path), 0)
+  w.insert_many(1, [("train/loss", 1.0)])
+  w.close()
+  srv = serve(str(tmp_path), None, port=0)
+  port = srv.server_address[1]
+  threading.Thread(target=srv.serve_forever, daemon=True).start()
+  try:
+    for path, code in (("/api/series?run=r&tag=train/loss&points=abc", 400), ("/api/series?run=r&tag=train/loss&rank=x", 400),
+                       ("/api/nope?run=r", 404), ("/api/experiments/runs?limit=many", 400), ("/api/experiments/run", 400),
+                       ("/api/datasets/shard/window?path=x&offset=-1&length=zz", 400), ("/static/", 200), ("/api/runs?x=%ff%fe", 200),
+                       ("/api/series?run=../../etc&tag=t", 404), ("/api/tags?run=r%00", 404)):
+      try:
+        with urllib.request.urlopen(f"http://127.0.0.1:{port}{path}", timeout=5) as r:
+          got = r.status
+      except urllib.error.HTTPError as e:
+        got = e.code
+        json.loads(e.read())                                # errors are JSON too
+      assert got == code, (path, got)
+    assert _get(port, "/api/series?run=r&tag=train/loss")["series"][0]["value"] == 1.0
+    assert _get(port, "/api/series?run=r&tag=no/such/tag")["series"] == []
+  finally:
+    srv.shutdown()
+    srv.server_close()
