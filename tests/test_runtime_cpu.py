@@ -488,3 +488,35 @@ def test_second_stop_signal_is_not_intercepted():
     assert len(hits) == 2 and st.should_stop(1)
   finally:
     signal.signal(signal.SIGUSR1, before)
+
+
+def test_train_entry_point_overrides_and_errors(tmp_path, monkeypatch, capsys):
+  """`python -m nmoe_b200.train cfg.toml --key=value`: precedence TOML < NMOE_* < flags, unknown keys refused, a failed
+  run recorded as failed."""
+  import nmoe_b200.train as T
+  from nmoe_b200.experiments import ExperimentTracker
+  cfg = _tiny_cfg(tmp_path)
+  toml = tmp_path / "c.toml"
+  import dataclasses
+  keep = {k: v for k, v in dataclasses.asdict(cfg).items() if not k.startswith("_") and v is not None and not isinstance(v, dict)}
+  toml.write_text("".join(f"{k} = {json.dumps(v)}\n" for k, v in keep.items()))
+  monkeypatch.setenv("NMOE_RUN", "cli")
+  monkeypatch.setenv("NMOE_STEPS", "5")                       # environment beats the file ...
+  T.main([str(toml), "--steps=2", "--log_every", "1"])         # ... and the flag beats the environment
+  out = capsys.readouterr().out
+  assert "step      2" in out and "step      3" not in out and "Training complete" in out
+  with pytest.raises(TypeError):
+    T.main([str(toml), "--no_such_key=1"])
+  with pytest.raises(SystemExit):
+    T.main([])
+  # a run that dies is recorded as failed, and the error reaches the caller
+  monkeypatch.setenv("NMOE_RUN", "dies")
+  import nmoe_b200.metrics as M
+  def boom(*a, **k):
+    raise RuntimeError("injected")
+  monkeypatch.setattr(M, "log_training_step", boom)
+  with pytest.raises(RuntimeError, match="injected"):
+    T.main([str(toml), "--steps=2", "--resume=false", f"--checkpoint_dir={tmp_path / 'ck2'}"])
+  tr = ExperimentTracker(cfg)
+  assert tr.get_run("dies").status == "failed" and tr.get_run("cli").status == "completed"
+  tr.close()
