@@ -109,3 +109,12 @@ def test_profile_steps_lists_operators_and_scopes():
   scope = next(r for r in rows if r["name"] == "lm_head_loss")
   assert scope["calls_per_step"] == 1.0 and all(r["host_ms_per_step"] >= 0 for r in rows)
   assert rows == sorted(rows, key=lambda r: -r["host_ms_per_step"])
+
+
+def test_trainer_from_a_shipped_configuration_with_overrides():
+  t = lab.trainer_from("configs/toy.toml", steps=3, batch_size=2, seq_len=32)
+  assert t.cfg.preset == "toy" and t.cfg.batch_size == 2 and t.cfg.seq_len == 32
+  losses = lab.run_steps(t, 3)
+  assert len(losses) == 3 and all(math.isfinite(x) for x in losses)
+  est = lab.training_state_estimate(t.cfg)
+  assert est["total_gib"] > 0 and lab.count_params(t.cfg)["dense"] + lab.count_params(t.cfg)["expert"] == sum(p.numel() for p in t.model.parameters())
