@@ -531,3 +531,26 @@ def test_hydra_train_command_phases_b_and_c_from_a_flat_jsonl(tmp_path, capsys):
   assert main([*common, "--phase", "C"]) == 0 and (heads / "hydra_probe.pt").exists() or any(heads.iterdir())
   with pytest.raises(SystemExit):
     main(["hydra-train", "--checkpoint", str(tmp_path / "ckpt"), "--heads", str(heads), "--phase", "A", "--tokenizer", "bytes"])
+
+
+def test_grading_a_jsonl_resumes_by_document_id(tmp_path):
+  import json
+  from nmoe_b200.data.cli import main
+  from nmoe_b200.serve.checkpoint import save_model
+  save_model(backbone(), str(tmp_path / "ckpt"))
+  heads = tmp_path / "heads"
+  H.save_heads(str(heads), H.ProbeHead(32), H.JudgeHead(32))
+  H.Calibration(tau_drop=-1.0, tau_keep=2.0).save(str(heads))
+  data = tmp_path / "docs.jsonl"
+  data.write_text("".join(json.dumps({"id": f"d{i}", "text": f"some text for document {i}"}) + "\n" for i in range(9)))
+  cmd = ["hydra-grade", "--checkpoint", str(tmp_path / "ckpt"), "--input", str(data), "--tokenizer", "bytes", "--max-ctx", "64",
+         "--batch-size", "4", "--heads", str(heads), "--output", str(tmp_path / "g.jsonl"), "--flush-every", "4"]
+  assert main([*cmd, "--max-documents", "5"]) == 0
+  first = [json.loads(l) for l in open(tmp_path / "g.jsonl")]
+  assert [r["doc_id"] for r in first] == [f"d{i}" for i in range(5)]
+  assert main([*cmd, "--resume"]) == 0
+  rows = [json.loads(l) for l in open(tmp_path / "g.jsonl")]
+  assert [r["doc_id"] for r in rows] == [f"d{i}" for i in range(9)] and rows[:5] == first
+  assert main(cmd) == 0 and len(open(tmp_path / "g.jsonl").readlines()) == 9          # without --resume: from scratch
+  one = main([*cmd[:cmd.index("--output")], "--output", str(tmp_path / "h.jsonl"), "--no-early-exit"])
+  assert one == 0 and all(not json.loads(l)["early_exit"] for l in open(tmp_path / "h.jsonl"))
