@@ -982,3 +982,17 @@ def test_flow_command_streaming_and_staged_give_the_same_dataset(tmp_path, capsy
   p = tmp_path / "g.toml"
   p.write_text(open(spec("s4")).read() + "[grade]\nenabled = true\n")
   assert main(["flow", str(p)]) == 2 and "names no checkpoint" in capsys.readouterr().err
+
+
+def test_prep_command_with_worker_processes_matches_the_serial_run(tmp_path):
+  from nmoe_b200.data.cli import main
+  _write_jsonl(tmp_path / "raw.jsonl", 80)
+  common = ["prep", "--source", "jsonl", "--input", str(tmp_path / "raw.jsonl"), "--name", "toy", "--tokenizer", "bytes", "--num-shards", "4"]
+  assert main([*common, "--output", str(tmp_path / "serial")]) == 0
+  assert main([*common, "--output", str(tmp_path / "par"), "--workers", "2"]) == 0
+  a, b = sinks.load_manifest(tmp_path / "serial"), sinks.load_manifest(tmp_path / "par")
+  assert (a.total_documents, a.total_tokens) == (b.total_documents, b.total_tokens)
+  assert [s.num_tokens for s in a.shards] == [s.num_tokens for s in b.shards]          # the same documents land in the same shards
+  sinks.verify_manifest(tmp_path / "par")
+  with pytest.raises(SystemExit, match="main process"):
+    main([*common, "--output", str(tmp_path / "x"), "--workers", "2", "--hydra-filter", "--checkpoint", "c", "--heads-dir", "h"])
