@@ -771,6 +771,12 @@ def main(argv=None) -> int:
     return a.fn(a)
   except PipelineError as e:
     e.exit()
+  except (FileNotFoundError, NotADirectoryError, IsADirectoryError, PermissionError) as e:
+    if os.environ.get("NMOE_DEBUG"):
+      raise
+    # a mistyped path is the commonest failure of a command line: one line, not a traceback (NMOE_DEBUG=1 for the latter)
+    print(f"{a.command}: {e.strerror or e}: {e.filename or ''}".rstrip(": "), file=sys.stderr)
+    return 2
 
 
 if __name__ == "__main__":

@@ -996,3 +996,14 @@ def test_prep_command_with_worker_processes_matches_the_serial_run(tmp_path):
   sinks.verify_manifest(tmp_path / "par")
   with pytest.raises(SystemExit, match="main process"):
     main([*common, "--output", str(tmp_path / "x"), "--workers", "2", "--hydra-filter", "--checkpoint", "c", "--heads-dir", "h"])
+
+
+def test_a_mistyped_path_is_one_line_not_a_traceback(tmp_path, capsys, monkeypatch):
+  from nmoe_b200.data.cli import main
+  assert main(["info", str(tmp_path / "nowhere")]) == 2
+  err = capsys.readouterr().err
+  assert err.startswith("info: ") and "nowhere" in err and "Traceback" not in err
+  assert main(["verify", str(tmp_path)]) == 2 and "manifest.json" in capsys.readouterr().err
+  monkeypatch.setenv("NMOE_DEBUG", "1")
+  with pytest.raises(FileNotFoundError):
+    main(["info", str(tmp_path / "nowhere")])
